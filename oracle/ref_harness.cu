@@ -1,0 +1,298 @@
+// ref_harness.cu - drives the UNMODIFIED reference library (oracle/_ref/libPhantom.so) on
+// synthetic limbs and records per-limb content hashes of every stage of the key-switching
+// path. TEST INFRASTRUCTURE ONLY: its JSON output is what tests/golden/ holds and what pins the
+// CPU oracle (ckks_oracle.c, compiled into this binary for the data generator and the hash).
+//
+// usage: ref_harness --logn 12 --bits 50,36,36,36,36,36,50,50 --special 2 --level 6 --seed 7
+//                    --steps 1,2,-1 --out case.json [--time ITERS]
+// Needs a CUDA device (the reference has no CPU path for any of this).
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <functional>
+#include <sstream>
+#include <string>
+#include <vector>
+
+#include "phantom.h"
+#include "ckks_oracle.h"
+
+using namespace phantom;
+using namespace phantom::arith;
+using namespace phantom::util;
+
+static std::vector<int> parse_ints(const char *s) {
+    std::vector<int> v;
+    std::stringstream ss(s);
+    std::string tok;
+    while (std::getline(ss, tok, ',')) if (!tok.empty()) v.push_back(atoi(tok.c_str()));
+    return v;
+}
+
+struct Rec { std::string name; std::vector<uint64_t> hashes; };
+static std::vector<Rec> g_recs;
+static std::vector<std::pair<std::string, double>> g_times;
+
+static void record(const std::string &name, const uint64_t *dev, size_t n_limbs, size_t N) {
+    std::vector<uint64_t> h(n_limbs * N);
+    cudaDeviceSynchronize();
+    cudaMemcpy(h.data(), dev, n_limbs * N * sizeof(uint64_t), cudaMemcpyDeviceToHost);
+    Rec r;
+    r.name = name;
+    for (size_t l = 0; l < n_limbs; l++) r.hashes.push_back(ora_limb_hash(h.data() + l * N, N));
+    g_recs.push_back(r);
+}
+
+template<typename T> static void put(std::ostream &os, T v) { os.write(reinterpret_cast<const char *>(&v), sizeof(T)); }
+
+// serialised ciphertext header, include/ciphertext.h:173-191
+static void put_ct_header(std::ostream &os, size_t chain, size_t size, size_t N, size_t limbs, double scale) {
+    put<size_t>(os, chain); put<size_t>(os, size); put<size_t>(os, N); put<size_t>(os, limbs);
+    put<double>(os, scale); put<uint64_t>(os, 1); put<size_t>(os, 1);
+    put<bool>(os, true); put<bool>(os, false);
+}
+
+// ciphertext [size][limbs][N] with synthetic limbs of buffer id `buf`
+static PhantomCiphertext make_ct(const std::vector<uint64_t> &primes, size_t chain, size_t size, size_t N,
+                                 size_t limbs, double scale, uint64_t seed, uint64_t buf) {
+    std::stringstream ss;
+    put_ct_header(ss, chain, size, N, limbs, scale);
+    std::vector<uint64_t> d(size * limbs * N);
+    for (size_t p = 0; p < size; p++)
+        ora_fill_limbs(d.data() + p * limbs * N, N, primes.data(), limbs, seed, buf, p * limbs);
+    ss.write(reinterpret_cast<const char *>(d.data()), d.size() * sizeof(uint64_t));
+    PhantomCiphertext ct;
+    ct.load(ss);
+    return ct;
+}
+
+// relin-style key: dnum public keys, each [2][size_QP][N] at chain 0 (include/secretkey.h:192-226)
+static void put_relin_key(std::ostream &os, const std::vector<uint64_t> &primes, size_t dnum, size_t N,
+                          uint64_t seed, uint64_t buf0) {
+    size_t size_QP = primes.size();
+    put<size_t>(os, dnum);
+    std::vector<uint64_t> d(2 * size_QP * N);
+    for (size_t i = 0; i < dnum; i++) {
+        put_ct_header(os, 0, 2, N, size_QP, 1.0);
+        for (size_t p = 0; p < 2; p++)
+            ora_fill_limbs(d.data() + p * size_QP * N, N, primes.data(), size_QP, seed, buf0 + i, p * size_QP);
+        os.write(reinterpret_cast<const char *>(d.data()), d.size() * sizeof(uint64_t));
+    }
+}
+
+static double time_us(const std::function<void()> &op, int warm, int iters) {
+    cudaStream_t s = cudaStreamPerThread;
+    for (int i = 0; i < warm; i++) op();
+    cudaStreamSynchronize(s);
+    cudaEvent_t e0, e1;
+    cudaEventCreate(&e0); cudaEventCreate(&e1);
+    cudaEventRecord(e0, s);
+    for (int i = 0; i < iters; i++) op();
+    cudaEventRecord(e1, s);
+    cudaEventSynchronize(e1);
+    float ms = 0;
+    cudaEventElapsedTime(&ms, e0, e1);
+    return ms * 1000.0 / iters;
+}
+
+int main(int argc, char **argv) {
+    int logn = 12, special = 2, level = -1, time_iters = 0;
+    uint64_t seed = 1;
+    std::vector<int> bits = {50, 36, 36, 36, 36, 36, 50, 50}, steps = {1, 2, -1};
+    std::string out = "case.json";
+    for (int i = 1; i + 1 < argc; i += 2) {
+        std::string k = argv[i];
+        const char *v = argv[i + 1];
+        if (k == "--logn") logn = atoi(v);
+        else if (k == "--bits") bits = parse_ints(v);
+        else if (k == "--special") special = atoi(v);
+        else if (k == "--level") level = atoi(v);
+        else if (k == "--seed") seed = strtoull(v, nullptr, 10);
+        else if (k == "--steps") steps = parse_ints(v);
+        else if (k == "--out") out = v;
+        else if (k == "--time") time_iters = atoi(v);
+        else { fprintf(stderr, "unknown arg %s\n", argv[i]); return 2; }
+    }
+    const size_t N = size_t(1) << logn;
+    const size_t size_QP = bits.size(), size_P = special, size_Q = size_QP - size_P;
+    const size_t l = level < 0 ? size_Q : size_t(level);   // number of Q limbs of the data
+    const size_t chain = size_Q - l + 1;                      // src/context.cu:145-168
+    const size_t beta = (l + size_P - 1) / size_P, lP = l + size_P;
+
+    std::vector<uint32_t> elts;
+    for (int s : steps) elts.push_back(get_elt_from_step(s, N));
+
+    EncryptionParameters parms(scheme_type::ckks);
+    parms.set_poly_modulus_degree(N);
+    auto mods = CoeffModulus::Create(N, bits);
+    parms.set_coeff_modulus(mods);
+    parms.set_special_modulus_size(size_P);
+    parms.set_galois_elts(elts);
+    PhantomContext context(parms);
+    const auto &s = cudaStreamPerThread;
+
+    std::vector<uint64_t> primes;
+    for (auto &m : mods) primes.push_back(m.value());
+
+    // ---- host tables of the reference against the oracle's, word for word ------------------
+    int tables_ok = 1;
+    {
+        std::vector<uint64_t> op(size_QP);
+        if (ora_create_coeff_modulus(N, bits.data(), size_QP, op.data()) != 0 || op != primes) tables_ok = 0;
+        ora_ctx *oc = ora_ctx_create(N, primes.data(), size_QP, size_P);
+        auto &tabs = context.get_context_data(0).small_ntt_tables();
+        for (size_t i = 0; i < size_QP && oc; i++) {
+            auto &t = tabs->get_ntt_at(i);
+            if (memcmp(t.get_from_root_powers().data(), ora_ctx_twiddle(oc, i), N * 8)) tables_ok = 0;
+            if (memcmp(t.get_from_inv_root_powers().data(), ora_ctx_itwiddle(oc, i), N * 8)) tables_ok = 0;
+        }
+        if (!oc) tables_ok = 0;
+        ora_ctx_destroy(oc);
+    }
+
+    // ---- NTT forward / inverse over all size_QP limbs --------------------------------------
+    {
+        std::vector<uint64_t> h(size_QP * N);
+        ora_fill_limbs(h.data(), N, primes.data(), size_QP, seed, 50, 0);
+        auto d = make_cuda_auto_ptr<uint64_t>(size_QP * N, s);
+        cudaMemcpy(d.get(), h.data(), h.size() * 8, cudaMemcpyHostToDevice);
+        nwt_2d_radix8_forward_inplace(d.get(), context.gpu_rns_tables(), size_QP, 0, s);
+        record("ntt_fwd", d.get(), size_QP, N);
+        cudaMemcpy(d.get(), h.data(), h.size() * 8, cudaMemcpyHostToDevice);
+        nwt_2d_radix8_backward_inplace(d.get(), context.gpu_rns_tables(), size_QP, 0, s);
+        record("ntt_inv", d.get(), size_QP, N);
+        if (time_iters) {
+            g_times.push_back({"ntt_fwd_us", time_us([&] {
+                nwt_2d_radix8_forward_inplace(d.get(), context.gpu_rns_tables(), size_QP, 0, s); }, 10, time_iters)});
+            g_times.push_back({"ntt_inv_us", time_us([&] {
+                nwt_2d_radix8_backward_inplace(d.get(), context.gpu_rns_tables(), size_QP, 0, s); }, 10, time_iters)});
+        }
+    }
+
+    // ---- keys ---------------------------------------------------------------------------------
+    // relin key: buffers 10.. ; Galois key for elts[e]: buffers 100 + 8 e ..
+    PhantomRelinKey rlk;
+    { std::stringstream ss; put_relin_key(ss, primes, beta, N, seed, 10); rlk.load(ss); }
+    PhantomGaloisKey glk;
+    {
+        std::stringstream ss;
+        put<size_t>(ss, elts.size());
+        for (size_t e = 0; e < elts.size(); e++) put_relin_key(ss, primes, beta, N, seed, 100 + 8 * e);
+        glk.load(ss);
+    }
+
+    const double scale = 1099511627776.0; // 2^40
+    auto &tool = context.get_context_data(chain).gpu_rns_tool();
+
+    // ---- the three stages of the key switch, separately ---------------------------------------
+    {
+        std::vector<uint64_t> h(l * N);
+        ora_fill_limbs(h.data(), N, primes.data(), l, seed, 3, 0);
+        auto c2 = make_cuda_auto_ptr<uint64_t>(l * N, s);
+        cudaMemcpy(c2.get(), h.data(), h.size() * 8, cudaMemcpyHostToDevice);
+        auto up = make_cuda_auto_ptr<uint64_t>(beta * lP * N, s);
+        tool.modup(up.get(), c2.get(), context.gpu_rns_tables(), scheme_type::ckks, s);
+        record("modup", up.get(), beta * lP, N);
+        auto cx = make_cuda_auto_ptr<uint64_t>(2 * lP * N, s);
+        key_switch_inner_prod(cx.get(), up.get(), rlk.public_keys_ptr(), tool, context.gpu_rns_tables().modulus(), 15, s);
+        record("inner_prod", cx.get(), 2 * lP, N);
+        if (time_iters) {
+            g_times.push_back({"modup_us", time_us([&] {
+                tool.modup(up.get(), c2.get(), context.gpu_rns_tables(), scheme_type::ckks, s); }, 5, time_iters)});
+            g_times.push_back({"inner_prod_us", time_us([&] {
+                key_switch_inner_prod(cx.get(), up.get(), rlk.public_keys_ptr(), tool,
+                                      context.gpu_rns_tables().modulus(), 15, s); }, 5, time_iters)});
+            auto cx2 = make_cuda_auto_ptr<uint64_t>(2 * lP * N, s);
+            g_times.push_back({"moddown_x2_us", time_us([&] {
+                cudaMemcpyAsync(cx2.get(), cx.get(), 2 * lP * N * 8, cudaMemcpyDeviceToDevice, s);
+                tool.moddown_from_NTT(cx2.get(), cx2.get(), context.gpu_rns_tables(), scheme_type::ckks, s);
+                tool.moddown_from_NTT(cx2.get() + lP * N, cx2.get() + lP * N, context.gpu_rns_tables(),
+                                      scheme_type::ckks, s); }, 5, time_iters)});
+        }
+        for (size_t k = 0; k < 2; k++)
+            tool.moddown_from_NTT(cx.get() + k * lP * N, cx.get() + k * lP * N, context.gpu_rns_tables(),
+                                  scheme_type::ckks, s);
+        record("moddown0", cx.get(), l, N);
+        record("moddown1", cx.get() + lP * N, l, N);
+
+        // whole key switch into a synthetic 2-poly ciphertext (buffer 1)
+        PhantomCiphertext ct = make_ct(primes, chain, 2, N, l, scale, seed, 1);
+        cudaMemcpy(c2.get(), h.data(), h.size() * 8, cudaMemcpyHostToDevice);
+        keyswitch_inplace(context, ct, c2.get(), rlk, true, s);
+        record("keyswitch", ct.data(), 2 * l, N);
+        if (time_iters) {
+            g_times.push_back({"keyswitch_us", time_us([&] {
+                keyswitch_inplace(context, ct, c2.get(), rlk, true, s); }, 5, time_iters)});
+        }
+    }
+
+    // ---- HMult + relin, rescale ---------------------------------------------------------------
+    {
+        PhantomCiphertext a = make_ct(primes, chain, 2, N, l, scale, seed, 1);
+        PhantomCiphertext b = make_ct(primes, chain, 2, N, l, scale, seed, 2);
+        PhantomCiphertext m(a);
+        multiply_and_relin_inplace(context, m, b, rlk);
+        record("mul_relin", m.data(), 2 * l, N);
+        if (l >= 2) {
+            PhantomCiphertext r = rescale_to_next(context, m);
+            record("mul_relin_rescale", r.data(), 2 * (l - 1), N);
+            PhantomCiphertext ra = rescale_to_next(context, a);
+            record("rescale", ra.data(), 2 * (l - 1), N);
+        }
+        if (time_iters) {
+            PhantomCiphertext scratch(a);
+            g_times.push_back({"mul_relin_us", time_us([&] {
+                scratch = a; multiply_and_relin_inplace(context, scratch, b, rlk); }, 5, time_iters)});
+            if (l >= 2)
+                g_times.push_back({"mul_relin_rescale_us", time_us([&] {
+                    scratch = a; multiply_and_relin_inplace(context, scratch, b, rlk);
+                    rescale_to_next_inplace(context, scratch); }, 5, time_iters)});
+        }
+    }
+
+    // ---- rotations ------------------------------------------------------------------------------
+    {
+        PhantomCiphertext a = make_ct(primes, chain, 2, N, l, scale, seed, 1);
+        for (size_t e = 0; e < elts.size(); e++) {
+            PhantomCiphertext r(a);
+            apply_galois_inplace(context, r, elts[e], glk);
+            record("rotate_" + std::to_string(steps[e]), r.data(), 2 * l, N);
+        }
+        auto outs = hoist_rotations(context, a, glk, steps);
+        for (size_t e = 0; e < outs.size(); e++)
+            record("hoist_" + std::to_string(steps[e]), outs[e].data(), 2 * l, N);
+        if (time_iters) {
+            PhantomCiphertext r(a);
+            g_times.push_back({"rotate_us", time_us([&] {
+                r = a; apply_galois_inplace(context, r, elts[0], glk); }, 5, time_iters)});
+            g_times.push_back({"hoist_rotations_us", time_us([&] {
+                auto o = hoist_rotations(context, a, glk, steps); }, 2, time_iters / 4 + 1)});
+        }
+    }
+    cudaDeviceSynchronize();
+    cudaError_t err = cudaGetLastError();
+
+    // ---- JSON ---------------------------------------------------------------------------------
+    FILE *f = fopen(out.c_str(), "w");
+    if (!f) { perror("open out"); return 1; }
+    fprintf(f, "{\n \"logn\": %d, \"special\": %zu, \"level\": %zu, \"seed\": %llu, \"chain_index\": %zu,\n",
+            logn, size_P, l, (unsigned long long) seed, chain);
+    fprintf(f, " \"bits\": ["); for (size_t i = 0; i < bits.size(); i++) fprintf(f, "%s%d", i ? "," : "", bits[i]); fprintf(f, "],\n");
+    fprintf(f, " \"steps\": ["); for (size_t i = 0; i < steps.size(); i++) fprintf(f, "%s%d", i ? "," : "", steps[i]); fprintf(f, "],\n");
+    fprintf(f, " \"elts\": ["); for (size_t i = 0; i < elts.size(); i++) fprintf(f, "%s%u", i ? "," : "", elts[i]); fprintf(f, "],\n");
+    fprintf(f, " \"primes\": ["); for (size_t i = 0; i < primes.size(); i++) fprintf(f, "%s%llu", i ? "," : "", (unsigned long long) primes[i]); fprintf(f, "],\n");
+    fprintf(f, " \"host_tables_match_oracle\": %s,\n \"cuda_error\": \"%s\",\n", tables_ok ? "true" : "false", cudaGetErrorString(err));
+    fprintf(f, " \"times_us\": {");
+    for (size_t i = 0; i < g_times.size(); i++) fprintf(f, "%s\"%s\": %.3f", i ? ", " : "", g_times[i].first.c_str(), g_times[i].second);
+    fprintf(f, "},\n \"hashes\": {\n");
+    for (size_t i = 0; i < g_recs.size(); i++) {
+        fprintf(f, "  \"%s\": [", g_recs[i].name.c_str());
+        for (size_t j = 0; j < g_recs[i].hashes.size(); j++)
+            fprintf(f, "%s\"%016llx\"", j ? "," : "", (unsigned long long) g_recs[i].hashes[j]);
+        fprintf(f, "]%s\n", i + 1 < g_recs.size() ? "," : "");
+    }
+    fprintf(f, " }\n}\n");
+    fclose(f);
+    printf("wrote %s (%zu records, tables_ok=%d, cuda=%s)\n", out.c_str(), g_recs.size(), tables_ok, cudaGetErrorString(err));
+    return (tables_ok && err == cudaSuccess) ? 0 : 1;
+}
