@@ -1,0 +1,147 @@
+/*
+ * b200fhe.h - C ABI of libb200fhe.so: CKKS hybrid key switching and the negacyclic NTT under it,
+ * hand-written for NVIDIA B200 (sm_100a).
+ *
+ * This is the boundary a binding of the reference library would call instead of the reference's
+ * own CUDA path. Each entry point names the reference interface it replaces (paths relative to the
+ * reference checkout). Conventions:
+ *   - every function returns 0 on success, a negative B2_E* code on a caller error, a positive
+ *     value (cudaError_t) on a CUDA failure; b2_last_error() gives the message for this thread;
+ *   - all `d_*` pointers are DEVICE pointers to uint64 residues laid out [poly][limb][N]
+ *     (coefficient index contiguous), limbs ordered like the context's primes: the reference's
+ *     layout (include/ciphertext.h:161-163), so buffers interchange byte for byte;
+ *   - NTT-form data is in the bit-reversed order the reference's forward transform produces;
+ *   - `size_Ql` is the number of Q limbs the operand holds (chain index k of the reference holds
+ *     size_Q - (k - 1) limbs, src/context.cu:145-168);
+ *   - nothing allocates behind the caller's back: scratch comes in as `d_ws` / `ws_bytes`
+ *     (size from b2_workspace_bytes); `stream` is a cudaStream_t passed as void*;
+ *   - calls are asynchronous on `stream`; there is no CPU fallback - without a CUDA device
+ *     b2_ctx_create fails.
+ */
+#ifndef B200FHE_H
+#define B200FHE_H
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define B2_OK 0
+#define B2_EINVAL (-1)  /* bad argument (size, level, null pointer)              */
+#define B2_ESIZE (-2)   /* polynomial degree or limb count outside what is built */
+#define B2_EWS (-3)     /* workspace too small                                   */
+#define B2_ENOMEM (-4)  /* host allocation failed                                */
+#define B2_ENOKEY (-5)  /* Galois element has no permutation table               */
+
+typedef struct b2_ctx b2_ctx;
+
+const char *b2_last_error(void);
+int b2_version(void);
+
+/* replaces CoeffModulus::Create (src/host/modulus.cu:80-111; python/src/binding.cu:56) */
+int b2_create_coeff_modulus(size_t N, const int *bit_sizes, size_t count, uint64_t *primes_out);
+
+/* replaces PhantomContext(params) (src/context.cu:125-232; python/src/binding.cu:72):
+ * primes[0..size_QP) = Q primes then the size_P special primes. Builds every table of every
+ * level on the host and uploads it to `device`. N in [2^12, 2^16]. */
+int b2_ctx_create(size_t N, const uint64_t *primes, size_t size_QP, size_t size_P, int device,
+                  b2_ctx **out);
+void b2_ctx_destroy(b2_ctx *ctx);
+size_t b2_ctx_N(const b2_ctx *ctx);
+size_t b2_ctx_size_Q(const b2_ctx *ctx);
+size_t b2_ctx_size_P(const b2_ctx *ctx);
+/* number of digits at a level: ceil(size_Ql / size_P) (src/rns.cu:149) */
+size_t b2_ctx_beta(const b2_ctx *ctx, size_t size_Ql);
+/* host copies of the tables, for word-for-word checks against src/host/ntt.cu:11-56:
+ * which = 0 forward twiddles, 1 inverse twiddles, 2 forward Shoup words, 3 inverse Shoup words */
+int b2_ctx_get_table(const b2_ctx *ctx, int which, size_t prime_idx, uint64_t *host_out);
+
+/* scratch bytes for an operation at a level. op: one of B2_OP_* */
+#define B2_OP_MODUP 1
+#define B2_OP_MODDOWN 2
+#define B2_OP_KEYSWITCH 3
+#define B2_OP_RESCALE 4
+#define B2_OP_MUL_RELIN 5
+#define B2_OP_ROTATE 6
+#define B2_OP_HOIST 7
+size_t b2_workspace_bytes(const b2_ctx *ctx, int op, size_t size_Ql);
+
+/* replaces nwt_2d_radix8_forward_inplace / _backward_inplace (src/ntt/fntt_2d.cu:665-709,
+ * src/ntt/intt_2d.cu:769-813): in place over n_limbs limbs; limb i uses prime first_prime + i. */
+int b2_ntt_forward(b2_ctx *ctx, uint64_t *d_data, size_t n_limbs, size_t first_prime, void *stream);
+int b2_ntt_inverse(b2_ctx *ctx, uint64_t *d_data, size_t n_limbs, size_t first_prime, void *stream);
+
+/* replaces DRNSTool::modup (src/rns_bconv.cu:530-628):
+ * d_c2 [size_Ql][N] (NTT form) -> d_out [beta][size_Ql + size_P][N] (NTT form) */
+int b2_modup(b2_ctx *ctx, size_t size_Ql, const uint64_t *d_c2, uint64_t *d_out, void *d_ws,
+             size_t ws_bytes, void *stream);
+
+/* replaces key_switch_inner_prod (src/eval_key_switch.cu:265-291):
+ * d_digits [beta][size_Ql+size_P][N]; evk[d] = device pointer to digit d of the key,
+ * [2][size_QP][N] at key level (include/secretkey.h:116-226); d_out [2][size_Ql+size_P][N] */
+int b2_ks_inner_prod(b2_ctx *ctx, size_t size_Ql, const uint64_t *d_digits,
+                     const uint64_t *const *evk, size_t n_evk, uint64_t *d_out, void *stream);
+
+/* replaces DRNSTool::moddown_from_NTT (src/rns_bconv.cu:776-828) for n_poly polynomials at once:
+ * d_cx [n_poly][size_Ql+size_P][N] (its P limbs are overwritten) -> d_out [n_poly][size_Ql][N] */
+int b2_moddown(b2_ctx *ctx, size_t size_Ql, size_t n_poly, uint64_t *d_cx, uint64_t *d_out,
+               void *d_ws, size_t ws_bytes, void *stream);
+
+/* replaces keyswitch_inplace (src/eval_key_switch.cu:294-381):
+ * d_ct [2][size_Ql][N] += ModDown(<ModUp(d_c2), evk>) */
+int b2_keyswitch(b2_ctx *ctx, size_t size_Ql, const uint64_t *d_c2, const uint64_t *const *evk,
+                 size_t n_evk, uint64_t *d_ct, void *d_ws, size_t ws_bytes, void *stream);
+
+/* replaces bgv_ckks_multiply's tensor product (src/evaluate.cu:345-397, src/polymath.cu:463-540):
+ * d_a, d_b [2][size_Ql][N] -> d_out [3][size_Ql][N] */
+int b2_tensor_mul(b2_ctx *ctx, size_t size_Ql, const uint64_t *d_a, const uint64_t *d_b,
+                  uint64_t *d_out, void *stream);
+
+/* replaces multiply_and_relin_inplace for CKKS (src/evaluate.cu:1061-1104, 1342-1374):
+ * d_out [2][size_Ql][N] = relinearise(d_a * d_b) */
+int b2_multiply_and_relin(b2_ctx *ctx, size_t size_Ql, const uint64_t *d_a, const uint64_t *d_b,
+                          const uint64_t *const *rlk, size_t n_evk, uint64_t *d_out, void *d_ws,
+                          size_t ws_bytes, void *stream);
+
+/* replaces divide_and_round_q_last_ntt under rescale_to_next (src/rns.cu:1128-1183,
+ * src/evaluate.cu:1413-1464): d_in [n_poly][size_Ql][N] -> d_out [n_poly][size_Ql-1][N] */
+int b2_rescale(b2_ctx *ctx, size_t size_Ql, size_t n_poly, const uint64_t *d_in, uint64_t *d_out,
+               void *d_ws, size_t ws_bytes, void *stream);
+
+/* replaces get_elt_from_step (include/galois.cuh:16-49); returns 0 when the step is out of range */
+uint32_t b2_galois_elt_from_step(int step, size_t N);
+/* replaces PhantomGaloisTool's table construction (include/galois.cuh:98-113): makes the
+ * NTT-domain gather table of one Galois element resident on the device (idempotent) */
+int b2_galois_prepare(b2_ctx *ctx, uint32_t galois_elt);
+/* replaces PhantomGaloisTool::apply_galois_ntt (src/galois.cu:11-18, 86-102):
+ * d_dst[l][i] = d_src[l][perm[i]] over n_limbs limbs (d_dst != d_src) */
+int b2_galois_permute(b2_ctx *ctx, uint32_t galois_elt, const uint64_t *d_src, uint64_t *d_dst,
+                      size_t n_limbs, void *stream);
+
+/* replaces apply_galois_with_ksk / rotate (src/evaluate.cu:1607-1730): d_out may alias d_ct.
+ * d_out [2][size_Ql][N] = key-switched automorphism of d_ct */
+int b2_apply_galois(b2_ctx *ctx, size_t size_Ql, uint32_t galois_elt, const uint64_t *d_ct,
+                    const uint64_t *const *ksk, size_t n_evk, uint64_t *d_out, void *d_ws,
+                    size_t ws_bytes, void *stream);
+
+/* replaces hoist_rotations (src/evaluate.cu:1929-2082): one ModUp of c1 shared by n_steps
+ * automorphisms. ksk[s * n_evk + d] = digit d of the key of elts[s]; d_outs[s] -> [2][size_Ql][N] */
+int b2_hoist_rotations(b2_ctx *ctx, size_t size_Ql, const uint64_t *d_ct, const uint32_t *elts,
+                       size_t n_steps, const uint64_t *const *ksk, size_t n_evk,
+                       uint64_t *const *d_outs, void *d_ws, size_t ws_bytes, void *stream);
+
+/* replaces mac_accumulate_kernel (src/bsgs.cu:51-96): d_out [2][size_Ql][N] =
+ * sum_b pts[b] (.) babies[b], pts[b] -> [size_Ql][N], babies[b] -> [2][size_Ql][N] (device ptrs) */
+int b2_bsgs_mac(b2_ctx *ctx, size_t size_Ql, size_t M, const uint64_t *const *pts,
+                const uint64_t *const *babies, uint64_t *d_out, void *stream);
+
+/* replaces add/sub/multiply_rns_poly (src/polymath.cu:17-180) over [n_limbs][N], limb i on prime i;
+ * op: 0 add, 1 sub, 2 multiply, 3 negate (d_b ignored). d_out may alias an input. */
+int b2_poly_op(b2_ctx *ctx, int op, size_t n_limbs, const uint64_t *d_a, const uint64_t *d_b,
+               uint64_t *d_out, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

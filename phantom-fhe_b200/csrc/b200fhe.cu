@@ -1,0 +1,1027 @@
+// b200fhe.cu - context, kernels and C ABI of libb200fhe.so (see include/b200fhe.h).
+//
+// Device data layout: ciphertext buffers are the reference's [poly][limb][N] uint64 arrays.
+// Tables live in one context: per prime {q, floor(2^128/q)}; forward and inverse twiddles as
+// interleaved {w, shoup(w)} pairs, [size_QP][N] each (64 MiB at N = 2^16 with 32 primes); and per
+// level (number of Q limbs l) one "plan": job lists for every transform of the key switch,
+// base-conversion matrices per digit and the constants folded into the inverse transform.
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <cmath>
+#include <cstdio>
+#include <cstring>
+#include <map>
+#include <mutex>
+#include <string>
+#include <vector>
+
+#include "../../include/b200fhe.h"
+#include "ntt_kernels.cuh"
+
+using namespace b2;
+typedef unsigned __int128 u128_t;
+
+// ------------------------------------------------------------------------------------------------
+// error handling
+// ------------------------------------------------------------------------------------------------
+static thread_local std::string g_err;
+static int fail(int code, const std::string &msg) {
+    g_err = msg;
+    return code;
+}
+#define CUDA_TRY(expr)                                                                            \
+    do {                                                                                          \
+        cudaError_t e_ = (expr);                                                                  \
+        if (e_ != cudaSuccess)                                                                    \
+            return fail((int)e_, std::string(#expr) + ": " + cudaGetErrorString(e_));             \
+    } while (0)
+#define LAUNCH_CHECK(name)                                                                        \
+    do {                                                                                          \
+        cudaError_t e_ = cudaGetLastError();                                                      \
+        if (e_ != cudaSuccess) return fail((int)e_, std::string(name) + ": " + cudaGetErrorString(e_)); \
+    } while (0)
+
+extern "C" const char *b2_last_error(void) { return g_err.c_str(); }
+extern "C" int b2_version(void) { return 1; }
+
+// ------------------------------------------------------------------------------------------------
+// host number theory (own statement of src/host/numth.cu, modulus.cu, ntt.cu, rns.cu semantics)
+// ------------------------------------------------------------------------------------------------
+static inline uint64_t h_mulmod(uint64_t a, uint64_t b, uint64_t q) { return (uint64_t)((u128_t)a * b % q); }
+static uint64_t h_powmod(uint64_t a, uint64_t e, uint64_t q) {
+    uint64_t r = 1;
+    a %= q;
+    for (; e; e >>= 1) {
+        if (e & 1) r = h_mulmod(r, a, q);
+        a = h_mulmod(a, a, q);
+    }
+    return r;
+}
+static inline uint64_t h_invmod(uint64_t a, uint64_t q) { return h_powmod(a % q, q - 2, q); }
+static inline uint64_t h_shoup(uint64_t w, uint64_t q) { return (uint64_t)(((u128_t)w << 64) / q); }
+static inline W2 h_w2(uint64_t w, uint64_t q) { return W2{w, h_shoup(w, q)}; }
+
+static bool h_is_prime(uint64_t v) {
+    static const uint64_t wit[] = {2, 3, 5, 7, 11, 13, 17, 19, 23, 29, 31, 37};
+    if (v < 2) return false;
+    for (uint64_t p : wit) {
+        if (v == p) return true;
+        if (v % p == 0) return false;
+    }
+    uint64_t d = v - 1;
+    int r = 0;
+    while (!(d & 1)) d >>= 1, r++;
+    for (uint64_t a : wit) {
+        uint64_t x = h_powmod(a, d, v);
+        if (x == 1 || x == v - 1) continue;
+        bool composite = true;
+        for (int i = 1; i < r && composite; i++) {
+            x = h_mulmod(x, x, v);
+            if (x == v - 1) composite = false;
+        }
+        if (composite) return false;
+    }
+    return true;
+}
+
+extern "C" int b2_create_coeff_modulus(size_t N, const int *bit_sizes, size_t count, uint64_t *out) {
+    if (!bit_sizes || !out || count == 0 || count > 64) return fail(B2_EINVAL, "create_coeff_modulus: bad count");
+    if (N < 2 || (N & (N - 1)) || N > 131072) return fail(B2_EINVAL, "create_coeff_modulus: poly_modulus_degree is invalid");
+    for (size_t i = 0; i < count; i++)
+        if (bit_sizes[i] < 2 || bit_sizes[i] > 60) return fail(B2_EINVAL, "create_coeff_modulus: bit_sizes is invalid");
+    const uint64_t step = 2 * (uint64_t)N;
+    std::map<int, std::vector<uint64_t>> table;
+    for (size_t i = 0; i < count; i++) table[bit_sizes[i]];
+    for (auto &kv : table) {
+        size_t need = std::count(bit_sizes, bit_sizes + count, kv.first);
+        uint64_t top = (uint64_t)1 << kv.first, low = top >> 1;
+        if (top < step) return fail(B2_EINVAL, "create_coeff_modulus: failed to find enough qualifying primes");
+        for (uint64_t v = top - step + 1; kv.second.size() < need && v > low; v -= step) {
+            if (h_is_prime(v)) kv.second.push_back(v);
+            if (v < step) break;
+        }
+        if (kv.second.size() < need) return fail(B2_EINVAL, "create_coeff_modulus: failed to find enough qualifying primes");
+    }
+    // every bit size hands out its primes smallest-first
+    for (size_t i = 0; i < count; i++) {
+        auto &v = table[bit_sizes[i]];
+        out[i] = v.back();
+        v.pop_back();
+    }
+    return B2_OK;
+}
+
+// smallest primitive 2N-th root of unity mod q (0 if none)
+static uint64_t h_min_root(uint64_t degree, uint64_t q) {
+    if ((q - 1) % degree) return 0;
+    uint64_t cof = (q - 1) / degree, r = 0;
+    for (uint64_t g = 2; g < q && !r; g++) {
+        uint64_t c = h_powmod(g, cof, q);
+        if (h_powmod(c, degree / 2, q) == q - 1) r = c;
+    }
+    uint64_t sq = h_mulmod(r, r, q), cur = r, best = r;
+    for (uint64_t i = 0; i < degree / 2; i++) {
+        best = std::min(best, cur);
+        cur = h_mulmod(cur, sq, q);
+    }
+    return best;
+}
+
+static inline uint32_t h_bitrev(uint32_t x, int bits) {
+    uint32_t r = 0;
+    for (int i = 0; i < bits; i++) r |= ((x >> i) & 1u) << (bits - 1 - i);
+    return r;
+}
+
+// ------------------------------------------------------------------------------------------------
+// context
+// ------------------------------------------------------------------------------------------------
+struct BconvGroup {
+    uint32_t in_slot0;   // first input limb (slot in the source buffer)
+    uint32_t ni;         // number of input limbs
+    uint32_t mat_off;    // offset (in u64) of this group's [n_out][ni] matrix
+    uint32_t out_begin;  // first entry of this group in the output list
+    uint32_t n_out;
+    uint32_t out_slot_base;  // added to every output slot
+    uint32_t copy_dst_slot0; // ModUp: where the digit's own limbs are copied to
+    uint32_t pad;
+};
+
+struct LevelPlan {
+    uint32_t l = 0, beta = 0;
+    // offsets into the level blob (device), counts
+    Job *jobs_up_intt = nullptr;   // l
+    Job *jobs_up_ntt = nullptr;    // n_up_ntt
+    uint32_t n_up_ntt = 0;
+    Job *jobs_dn_intt = nullptr;   // 2*alpha (poly-major), prefix alpha for one polynomial
+    Job *jobs_dn_ntt = nullptr;    // 2*l
+    Job *jobs_rs_intt = nullptr;   // 3 (one per polynomial)
+    Job *jobs_rs_ntt = nullptr;    // 3*(l-1)
+    W2 *fin_up = nullptr;          // [l][2]
+    W2 *qlast_inv = nullptr;       // [size_QP] indexed by prime (valid j < l-1)
+    BconvGroup *grp_up = nullptr;  // beta
+    uint2 *outs_up = nullptr;      // (slot, prime) list, beta groups concatenated
+    uint64_t *mat_up = nullptr;
+    BconvGroup *grp_dn = nullptr;  // 2 (one per polynomial)
+    uint2 *outs_dn = nullptr;      // l entries shared by both groups
+    BconvGroup *grp_rs = nullptr;  // 3
+    uint2 *outs_rs = nullptr;      // l-1
+    void *blob = nullptr;
+};
+
+struct b2_ctx {
+    int device = 0;
+    size_t N = 0;
+    int logN = 0;
+    size_t size_QP = 0, size_Q = 0, size_P = 0;
+    std::vector<uint64_t> q;
+    std::vector<W2> h_tw, h_itw;  // host copies [size_QP][N]
+    Mod *d_mod = nullptr;
+    W2 *d_tw = nullptr, *d_itw = nullptr;
+    W2 *d_fin_plain = nullptr;  // [size_QP][2] = {N^-1, itw[1]}
+    W2 *d_fin_P = nullptr;      // [size_P][2]  = the same times (P/p_i)^-1 mod p_i
+    W2 *d_Pinv = nullptr;       // [size_QP] indexed by prime (valid for Q primes): P^-1 mod q_j
+    uint64_t *d_mat_dn = nullptr;  // [size_Q][size_P]: (P/p_i) mod q_j
+    uint64_t *d_one = nullptr;     // [1] = 1: the 1x1 "matrix" of the rescale reduction
+    std::vector<LevelPlan> plan;   // index l (1..size_Q)
+    std::map<uint32_t, uint32_t *> galois;  // elt -> device gather table
+    std::mutex mu;
+};
+
+template <typename T>
+static T *blob_take(char *&cur, size_t count) {
+    uintptr_t p = (reinterpret_cast<uintptr_t>(cur) + 15) & ~uintptr_t(15);
+    cur = reinterpret_cast<char *>(p + count * sizeof(T));
+    return reinterpret_cast<T *>(p);
+}
+
+static inline uint32_t phys_prime(const b2_ctx *c, size_t l, size_t t) { return (uint32_t)(t < l ? t : c->size_Q + (t - l)); }
+
+// product of the primes in [s, e) except index `skip`, mod p
+static uint64_t punctured(const std::vector<uint64_t> &q, size_t s, size_t e, size_t skip, uint64_t p) {
+    uint64_t r = 1 % p;
+    for (size_t k = s; k < e; k++)
+        if (k != skip) r = h_mulmod(r, q[k] % p, p);
+    return r;
+}
+
+static int build_level(b2_ctx *c, size_t l) {
+    const size_t N = c->N, alpha = c->size_P, sQ = c->size_Q;
+    const size_t beta = (l + alpha - 1) / alpha, lP = l + alpha;
+    LevelPlan &pl = c->plan[l];
+    pl.l = (uint32_t)l;
+    pl.beta = (uint32_t)beta;
+    const size_t n_up_ntt = beta * lP - l;
+    const size_t mat_up_words = beta * lP * alpha;
+    // host staging mirrors the device blob
+    size_t bytes = 64 + sizeof(Job) * (l + n_up_ntt + 2 * alpha + 2 * l + 3 + 3 * l) + sizeof(W2) * (2 * l + c->size_QP) +
+                   sizeof(BconvGroup) * (beta + 2 + 3) + sizeof(uint2) * (n_up_ntt + l + l) + 8 * mat_up_words + 16 * 16;
+    std::vector<char> host(bytes, 0);
+    char *cur = host.data();
+    auto *jobs_up_intt = blob_take<Job>(cur, l);
+    auto *jobs_up_ntt = blob_take<Job>(cur, n_up_ntt);
+    auto *jobs_dn_intt = blob_take<Job>(cur, 2 * alpha);
+    auto *jobs_dn_ntt = blob_take<Job>(cur, 2 * l);
+    auto *jobs_rs_intt = blob_take<Job>(cur, 3);
+    auto *jobs_rs_ntt = blob_take<Job>(cur, 3 * l);
+    auto *fin_up = blob_take<W2>(cur, 2 * l);
+    auto *qlast_inv = blob_take<W2>(cur, c->size_QP);
+    auto *grp_up = blob_take<BconvGroup>(cur, beta);
+    auto *outs_up = blob_take<uint2>(cur, n_up_ntt);
+    auto *mat_up = blob_take<uint64_t>(cur, mat_up_words);
+    auto *grp_dn = blob_take<BconvGroup>(cur, 2);
+    auto *outs_dn = blob_take<uint2>(cur, l);
+    auto *grp_rs = blob_take<BconvGroup>(cur, 3);
+    auto *outs_rs = blob_take<uint2>(cur, l);
+    const size_t used = cur - host.data();
+    if (used > bytes) return fail(B2_ENOMEM, "level blob overflow");
+
+    // ---- ModUp (src/rns_bconv.cu:530-628; constants src/rns.cu:149-189) ----
+    size_t up_i = 0, mat_off = 0;
+    for (size_t d = 0; d < beta; d++) {
+        const size_t s = alpha * d, e = std::min(s + alpha, l), ni = e - s;
+        grp_up[d] = BconvGroup{(uint32_t)s, (uint32_t)ni, (uint32_t)mat_off, (uint32_t)up_i, (uint32_t)(lP - ni),
+                               (uint32_t)(d * lP), (uint32_t)(d * lP + s), 0};
+        for (size_t i = s; i < e; i++) {
+            const uint64_t qi = c->q[i];
+            const uint64_t hatinv = h_invmod(punctured(c->q, s, e, i, qi), qi);
+            // INTT's final-stage constants with (Q_d/q_i)^-1 folded in
+            const uint64_t ninv = h_invmod(N % qi, qi);
+            fin_up[2 * i] = h_w2(h_mulmod(ninv, hatinv, qi), qi);
+            fin_up[2 * i + 1] = h_w2(h_mulmod(c->h_itw[i * N + 1].w, hatinv, qi), qi);
+            jobs_up_intt[i] = make_uint4((uint32_t)i, (uint32_t)i, (uint32_t)i, 0);
+        }
+        for (size_t t = 0; t < lP; t++) {
+            if (t >= s && t < e) continue;
+            const uint32_t pp = phys_prime(c, l, t);
+            jobs_up_ntt[up_i] = make_uint4((uint32_t)(d * lP + t), pp, 0, 0);
+            outs_up[up_i] = make_uint2((uint32_t)t, pp);
+            for (size_t i = s; i < e; i++) mat_up[mat_off++] = punctured(c->q, s, e, i, c->q[pp]);
+            up_i++;
+        }
+    }
+    // ---- ModDown (src/rns_bconv.cu:776-828) ----
+    for (size_t k = 0; k < 2; k++) {
+        for (size_t i = 0; i < alpha; i++)
+            jobs_dn_intt[k * alpha + i] = make_uint4((uint32_t)(k * lP + l + i), (uint32_t)(sQ + i), (uint32_t)i, 0);
+        for (size_t j = 0; j < l; j++)
+            jobs_dn_ntt[k * l + j] = make_uint4((uint32_t)(k * l + j), (uint32_t)j, (uint32_t)(k * lP + j), (uint32_t)(k * l + j));
+        grp_dn[k] = BconvGroup{(uint32_t)(k * lP + l), (uint32_t)alpha, 0, 0, (uint32_t)l, (uint32_t)(k * l), 0, 0};
+    }
+    for (size_t j = 0; j < l; j++) outs_dn[j] = make_uint2((uint32_t)j, (uint32_t)j);
+    // ---- rescale (src/rns.cu:1128-1183; constants src/rns.cu:66-95) ----
+    if (l >= 2) {
+        const uint64_t ql = c->q[l - 1];
+        for (size_t j = 0; j + 1 < l; j++) {
+            qlast_inv[j] = h_w2(h_invmod(ql % c->q[j], c->q[j]), c->q[j]);
+            outs_rs[j] = make_uint2((uint32_t)j, (uint32_t)j);
+        }
+        for (size_t p = 0; p < 3; p++) {
+            jobs_rs_intt[p] = make_uint4((uint32_t)(p * l + l - 1), (uint32_t)(l - 1), (uint32_t)(l - 1), 0);
+            for (size_t j = 0; j + 1 < l; j++)
+                jobs_rs_ntt[p * (l - 1) + j] =
+                    make_uint4((uint32_t)(p * (l - 1) + j), (uint32_t)j, (uint32_t)(p * l + j), (uint32_t)(p * (l - 1) + j));
+            grp_rs[p] = BconvGroup{(uint32_t)p, 1, 0, 0, (uint32_t)(l - 1), (uint32_t)(p * (l - 1)), 0, 0};
+        }
+    }
+    if (cudaMalloc(&pl.blob, used) != cudaSuccess) return fail(B2_ENOMEM, "cudaMalloc(level plan) failed");
+    cudaError_t e = cudaMemcpy(pl.blob, host.data(), used, cudaMemcpyHostToDevice);
+    if (e != cudaSuccess) return fail((int)e, "cudaMemcpy(level plan) failed");
+    auto dev = [&](const void *hp) { return (char *)pl.blob + ((const char *)hp - host.data()); };
+    pl.jobs_up_intt = (Job *)dev(jobs_up_intt);
+    pl.jobs_up_ntt = (Job *)dev(jobs_up_ntt);
+    pl.n_up_ntt = (uint32_t)n_up_ntt;
+    pl.jobs_dn_intt = (Job *)dev(jobs_dn_intt);
+    pl.jobs_dn_ntt = (Job *)dev(jobs_dn_ntt);
+    pl.jobs_rs_intt = (Job *)dev(jobs_rs_intt);
+    pl.jobs_rs_ntt = (Job *)dev(jobs_rs_ntt);
+    pl.fin_up = (W2 *)dev(fin_up);
+    pl.qlast_inv = (W2 *)dev(qlast_inv);
+    pl.grp_up = (BconvGroup *)dev(grp_up);
+    pl.outs_up = (uint2 *)dev(outs_up);
+    pl.mat_up = (uint64_t *)dev(mat_up);
+    pl.grp_dn = (BconvGroup *)dev(grp_dn);
+    pl.outs_dn = (uint2 *)dev(outs_dn);
+    pl.grp_rs = (BconvGroup *)dev(grp_rs);
+    pl.outs_rs = (uint2 *)dev(outs_rs);
+    return B2_OK;
+}
+
+extern "C" void b2_ctx_destroy(b2_ctx *c) {
+    if (!c) return;
+    cudaSetDevice(c->device);
+    cudaFree(c->d_mod);
+    cudaFree(c->d_tw);
+    cudaFree(c->d_itw);
+    cudaFree(c->d_fin_plain);
+    cudaFree(c->d_fin_P);
+    cudaFree(c->d_Pinv);
+    cudaFree(c->d_mat_dn);
+    cudaFree(c->d_one);
+    for (auto &pl : c->plan) cudaFree(pl.blob);
+    for (auto &kv : c->galois) cudaFree(kv.second);
+    delete c;
+}
+
+extern "C" int b2_ctx_create(size_t N, const uint64_t *primes, size_t size_QP, size_t size_P, int device, b2_ctx **out) {
+    if (!primes || !out) return fail(B2_EINVAL, "ctx_create: null argument");
+    *out = nullptr;
+    if (N < 4096 || N > 65536 || (N & (N - 1))) return fail(B2_ESIZE, "ctx_create: poly_modulus_degree must be a power of two in [4096, 65536]");
+    if (size_QP < 2 || size_QP > 64) return fail(B2_ESIZE, "ctx_create: the coefficient modulus must hold 2..64 primes");
+    if (size_P < 1 || size_P >= size_QP) return fail(B2_EINVAL, "ctx_create: special_modulus_size must be in [1, size_QP)");
+    int ndev = 0;
+    cudaError_t de = cudaGetDeviceCount(&ndev);
+    if (de != cudaSuccess || ndev == 0) return fail(de != cudaSuccess ? (int)de : (int)cudaErrorNoDevice, "ctx_create: no CUDA device (this library has no CPU path)");
+    if (device < 0 || device >= ndev) return fail(B2_EINVAL, "ctx_create: bad device index");
+    CUDA_TRY(cudaSetDevice(device));
+
+    b2_ctx *c = new b2_ctx();
+    c->device = device;
+    c->N = N;
+    c->logN = __builtin_ctzll(N);
+    c->size_QP = size_QP;
+    c->size_P = size_P;
+    c->size_Q = size_QP - size_P;
+    c->q.assign(primes, primes + size_QP);
+    for (size_t i = 0; i < size_QP; i++) {
+        const uint64_t q = c->q[i];
+        if (q < 2 || (q >> 61) || !h_is_prime(q) || (q - 1) % (2 * N)) {
+            delete c;
+            return fail(B2_EINVAL, "ctx_create: every modulus must be a prime = 1 (mod 2N) of at most 61 bits");
+        }
+        for (size_t j = 0; j < i; j++)
+            if (c->q[j] == q) {
+                delete c;
+                return fail(B2_EINVAL, "ctx_create: moduli must be distinct");
+            }
+    }
+    // ---- twiddles: tw[br(i)] = psi^i, itw[br(i)] = psi^-i, itw[1] *= N^-1 (src/host/ntt.cu:11-56)
+    c->h_tw.resize(size_QP * N);
+    c->h_itw.resize(size_QP * N);
+    std::vector<Mod> mods(size_QP);
+    std::vector<W2> fin_plain(2 * size_QP);
+    std::vector<uint32_t> br(N);
+    for (size_t i = 0; i < N; i++) br[i] = h_bitrev((uint32_t)i, c->logN);
+#pragma omp parallel for schedule(dynamic)
+    for (size_t l = 0; l < size_QP; l++) {
+        const uint64_t q = c->q[l];
+        const uint64_t psi = h_min_root(2 * N, q), ipsi = h_invmod(psi, q);
+        W2 *tw = c->h_tw.data() + l * N, *itw = c->h_itw.data() + l * N;
+        uint64_t p = psi, ip = ipsi;
+        tw[0] = h_w2(1, q);
+        itw[0] = h_w2(1, q);
+        for (size_t i = 1; i < N; i++) {
+            tw[br[i]] = h_w2(p, q);
+            itw[br[i]] = h_w2(ip, q);
+            p = h_mulmod(p, psi, q);
+            ip = h_mulmod(ip, ipsi, q);
+        }
+        const uint64_t ninv = h_invmod(N % q, q);
+        itw[1] = h_w2(h_mulmod(itw[1].w, ninv, q), q);
+        fin_plain[2 * l] = h_w2(ninv, q);
+        fin_plain[2 * l + 1] = itw[1];
+        // floor(2^128 / q) as two words
+        u128_t hi = ((u128_t)1 << 64);  // 2^64
+        uint64_t r1 = (uint64_t)(hi / q);
+        u128_t rem = hi % q;
+        uint64_t r0 = (uint64_t)((rem << 64) / q);
+        mods[l] = Mod{q, r0, r1, 0};
+    }
+    // ---- P-related constants (src/rns.cu:100-138, 192-194) ----
+    const size_t sQ = c->size_Q, sP = size_P;
+    std::vector<W2> fin_P(2 * sP), Pinv(size_QP, W2{0, 0});
+    std::vector<uint64_t> mat_dn(sQ * sP);
+    for (size_t i = 0; i < sP; i++) {
+        const uint64_t p = c->q[sQ + i];
+        const uint64_t hatinv = h_invmod(punctured(c->q, sQ, size_QP, sQ + i, p), p);
+        fin_P[2 * i] = h_w2(h_mulmod(fin_plain[2 * (sQ + i)].w, hatinv, p), p);
+        fin_P[2 * i + 1] = h_w2(h_mulmod(fin_plain[2 * (sQ + i) + 1].w, hatinv, p), p);
+    }
+    for (size_t j = 0; j < sQ; j++) {
+        const uint64_t qj = c->q[j];
+        uint64_t P = 1;
+        for (size_t i = 0; i < sP; i++) {
+            P = h_mulmod(P, c->q[sQ + i] % qj, qj);
+            mat_dn[j * sP + i] = punctured(c->q, sQ, size_QP, sQ + i, qj);
+        }
+        Pinv[j] = h_w2(h_invmod(P, qj), qj);
+    }
+    const uint64_t one = 1;
+    auto up = [&](void **dptr, const void *src, size_t bytes) -> cudaError_t {
+        cudaError_t e = cudaMalloc(dptr, bytes);
+        if (e != cudaSuccess) return e;
+        return cudaMemcpy(*dptr, src, bytes, cudaMemcpyHostToDevice);
+    };
+    cudaError_t e = cudaSuccess;
+    if (e == cudaSuccess) e = up((void **)&c->d_mod, mods.data(), sizeof(Mod) * size_QP);
+    if (e == cudaSuccess) e = up((void **)&c->d_tw, c->h_tw.data(), sizeof(W2) * size_QP * N);
+    if (e == cudaSuccess) e = up((void **)&c->d_itw, c->h_itw.data(), sizeof(W2) * size_QP * N);
+    if (e == cudaSuccess) e = up((void **)&c->d_fin_plain, fin_plain.data(), sizeof(W2) * 2 * size_QP);
+    if (e == cudaSuccess) e = up((void **)&c->d_fin_P, fin_P.data(), sizeof(W2) * 2 * sP);
+    if (e == cudaSuccess) e = up((void **)&c->d_Pinv, Pinv.data(), sizeof(W2) * size_QP);
+    if (e == cudaSuccess) e = up((void **)&c->d_mat_dn, mat_dn.data(), 8 * sQ * sP);
+    if (e == cudaSuccess) e = up((void **)&c->d_one, &one, 8);
+    if (e != cudaSuccess) {
+        b2_ctx_destroy(c);
+        return fail((int)e, std::string("ctx_create: table upload failed: ") + cudaGetErrorString(e));
+    }
+    c->plan.resize(sQ + 1);
+    for (size_t l = 1; l <= sQ; l++) {
+        int rc = build_level(c, l);
+        if (rc != B2_OK) {
+            b2_ctx_destroy(c);
+            return rc;
+        }
+    }
+    *out = c;
+    return B2_OK;
+}
+
+extern "C" size_t b2_ctx_N(const b2_ctx *c) { return c ? c->N : 0; }
+extern "C" size_t b2_ctx_size_Q(const b2_ctx *c) { return c ? c->size_Q : 0; }
+extern "C" size_t b2_ctx_size_P(const b2_ctx *c) { return c ? c->size_P : 0; }
+extern "C" size_t b2_ctx_beta(const b2_ctx *c, size_t l) { return c ? (l + c->size_P - 1) / c->size_P : 0; }
+
+extern "C" int b2_ctx_get_table(const b2_ctx *c, int which, size_t prime_idx, uint64_t *host_out) {
+    if (!c || !host_out || prime_idx >= c->size_QP || which < 0 || which > 3) return fail(B2_EINVAL, "ctx_get_table: bad argument");
+    const W2 *t = ((which & 1) ? c->h_itw.data() : c->h_tw.data()) + prime_idx * c->N;
+    for (size_t i = 0; i < c->N; i++) host_out[i] = (which & 2) ? t[i].ws : t[i].w;
+    return B2_OK;
+}
+
+// ------------------------------------------------------------------------------------------------
+// transform launchers
+// ------------------------------------------------------------------------------------------------
+// stage split per polynomial degree: {LOG_A (column pass), LOG_B (row pass)}
+template <int LOG_T> struct PassCfg;
+template <> struct PassCfg<8> { static constexpr int R_STRIDED = 4, R_CONTIG = 4, LOG_C = 3; };
+template <> struct PassCfg<7> { static constexpr int R_STRIDED = 3, R_CONTIG = 4, LOG_C = 4; };
+template <> struct PassCfg<6> { static constexpr int R_STRIDED = 3, R_CONTIG = 3, LOG_C = 4; };
+
+template <int LOG_T>
+static constexpr int pass_threads() {
+    using P = PassCfg<LOG_T>;
+    return (1 << (P::LOG_C + LOG_T)) >> (P::R_STRIDED > P::R_CONTIG ? P::R_STRIDED : P::R_CONTIG);
+}
+
+template <int LOG_A, int LOG_B, class Epi>
+static void launch_fwd(const NttArgs &a, uint32_t njobs, const Epi &epi, cudaStream_t s) {
+    using A = PassCfg<LOG_A>;
+    using B = PassCfg<LOG_B>;
+    const uint32_t N = 1u << a.logN;
+    ntt_fwd_pass<LOG_A, A::R_STRIDED, A::R_CONTIG, A::LOG_C, true, false, EpiStore>
+        <<<njobs * (N >> (LOG_A + A::LOG_C)), pass_threads<LOG_A>(), 0, s>>>(a, EpiStore{});
+    NttArgs b = a;
+    b.src = a.dst;  // second pass works in place on the first pass's output
+    ntt_fwd_pass<LOG_B, B::R_STRIDED, B::R_CONTIG, B::LOG_C, false, true, Epi>
+        <<<njobs * (N >> (LOG_B + B::LOG_C)), pass_threads<LOG_B>(), 0, s>>>(b, epi);
+}
+
+template <int LOG_A, int LOG_B>
+static void launch_inv(const NttArgs &a, uint32_t njobs, cudaStream_t s) {
+    using A = PassCfg<LOG_A>;
+    using B = PassCfg<LOG_B>;
+    const uint32_t N = 1u << a.logN;
+    ntt_inv_pass<LOG_B, B::R_CONTIG, B::R_STRIDED, B::LOG_C, false, false>
+        <<<njobs * (N >> (LOG_B + B::LOG_C)), pass_threads<LOG_B>(), 0, s>>>(a);
+    NttArgs b = a;
+    b.src = a.dst;
+    ntt_inv_pass<LOG_A, A::R_CONTIG, A::R_STRIDED, A::LOG_C, true, true>
+        <<<njobs * (N >> (LOG_A + A::LOG_C)), pass_threads<LOG_A>(), 0, s>>>(b);
+}
+
+template <class Epi>
+static int run_fwd(const b2_ctx *c, const uint64_t *src, uint64_t *dst, const Job *jobs, uint32_t njobs, uint32_t first_prime,
+                   const Epi &epi, cudaStream_t s) {
+    if (njobs == 0) return B2_OK;
+    NttArgs a{src, dst, jobs, first_prime, (uint32_t)c->logN, c->d_tw, c->d_mod, nullptr};
+    switch (c->logN) {
+        case 16: launch_fwd<8, 8>(a, njobs, epi, s); break;
+        case 15: launch_fwd<7, 8>(a, njobs, epi, s); break;
+        case 14: launch_fwd<7, 7>(a, njobs, epi, s); break;
+        case 13: launch_fwd<6, 7>(a, njobs, epi, s); break;
+        case 12: launch_fwd<6, 6>(a, njobs, epi, s); break;
+        default: return fail(B2_ESIZE, "unsupported polynomial degree");
+    }
+    LAUNCH_CHECK("ntt_fwd_pass");
+    return B2_OK;
+}
+
+static int run_inv(const b2_ctx *c, const uint64_t *src, uint64_t *dst, const Job *jobs, uint32_t njobs, uint32_t first_prime,
+                   const W2 *fin, cudaStream_t s) {
+    if (njobs == 0) return B2_OK;
+    NttArgs a{src, dst, jobs, first_prime, (uint32_t)c->logN, c->d_itw, c->d_mod, fin};
+    switch (c->logN) {
+        case 16: launch_inv<8, 8>(a, njobs, s); break;
+        case 15: launch_inv<7, 8>(a, njobs, s); break;
+        case 14: launch_inv<7, 7>(a, njobs, s); break;
+        case 13: launch_inv<6, 7>(a, njobs, s); break;
+        case 12: launch_inv<6, 6>(a, njobs, s); break;
+        default: return fail(B2_ESIZE, "unsupported polynomial degree");
+    }
+    LAUNCH_CHECK("ntt_inv_pass");
+    return B2_OK;
+}
+
+// ------------------------------------------------------------------------------------------------
+// base conversion, inner product, elementwise kernels
+// ------------------------------------------------------------------------------------------------
+// Fast base conversion (src/rns_bconv.cu:143-168, 455-485): for every coefficient n and every output
+// prime p_j of the group:  out_j[n] = (sum_i in_i[n] * M[j][i]) mod p_j, the sum kept in 128 bits
+// and reduced once. One thread owns two adjacent coefficients, loads their ni inputs once and walks
+// all outputs, so the inputs cross HBM once and every store is a coalesced 16-byte write.
+// gridDim.y = group (digit of ModUp / polynomial of ModDown). COPY: also copies the group's own
+// limbs from `copy_src` (the NTT-form input) into the output buffer (src/rns_bconv.cu:522-528).
+template <int MAX_NI, bool COPY>
+__global__ void __launch_bounds__(128) bconv_kernel(const uint64_t *__restrict__ in, uint64_t *__restrict__ out,
+                                                    const uint64_t *__restrict__ copy_src, const BconvGroup *groups,
+                                                    const uint2 *outs, const uint64_t *mats, const Mod *mod, uint32_t N) {
+    extern __shared__ uint64_t s_mat[];
+    const BconvGroup g = groups[blockIdx.y];
+    const uint64_t *mat = mats + g.mat_off;
+    for (uint32_t i = threadIdx.x; i < g.n_out * g.ni; i += blockDim.x) s_mat[i] = mat[i];
+    __syncthreads();
+    const uint32_t n = 2 * (blockIdx.x * blockDim.x + threadIdx.x);
+    if (n >= N) return;
+    uint64_t y0[MAX_NI], y1[MAX_NI];
+#pragma unroll
+    for (int i = 0; i < MAX_NI; i++) {
+        if (i < (int)g.ni) {
+            ulonglong2 v = *reinterpret_cast<const ulonglong2 *>(in + (size_t)(g.in_slot0 + i) * N + n);
+            y0[i] = v.x;
+            y1[i] = v.y;
+            if (COPY) {
+                ulonglong2 cv = *reinterpret_cast<const ulonglong2 *>(copy_src + (size_t)(g.in_slot0 + i) * N + n);
+                *reinterpret_cast<ulonglong2 *>(out + (size_t)(g.copy_dst_slot0 + i) * N + n) = cv;
+            }
+        } else {
+            y0[i] = y1[i] = 0;
+        }
+    }
+    const uint2 *ol = outs + g.out_begin;
+    for (uint32_t j = 0; j < g.n_out; j++) {
+        const uint2 o = ol[j];
+        const Mod md = mod[o.y];
+        const uint64_t *m = s_mat + j * g.ni;
+        u128 a0{0, 0}, a1{0, 0};
+#pragma unroll
+        for (int i = 0; i < MAX_NI; i++) {
+            if (i < (int)g.ni) {
+                const uint64_t mm = m[i];
+                mac128(a0, y0[i], mm);
+                mac128(a1, y1[i], mm);
+            }
+        }
+        const uint64_t r0 = barrett128(a0, md.q, md.r0, md.r1);
+        const uint64_t r1 = barrett128(a1, md.q, md.r0, md.r1);
+        *reinterpret_cast<ulonglong2 *>(out + (size_t)(g.out_slot_base + o.x) * N + n) = make_ulonglong2(r0, r1);
+    }
+}
+
+struct EvkPtrs {
+    const uint64_t *p[64];
+};
+
+// Key-switch inner product (src/eval_key_switch.cu:175-230): for logical limb t (physical prime pp)
+//   out[k][t][n] = (sum_d digits[d][t][n] * evk[d][k][pp][n]) mod q_pp,   k = 0, 1
+// accumulated in 128 bits and reduced once. Pure streaming: two coefficients per thread, 16-byte loads.
+__global__ void __launch_bounds__(256) ks_inner_prod_kernel(const uint64_t *__restrict__ digits, EvkPtrs evk, uint64_t *__restrict__ out,
+                                                           const Mod *mod, uint32_t N, uint32_t l, uint32_t lP, uint32_t size_Q,
+                                                           uint32_t size_QP, uint32_t beta) {
+    const size_t idx = 2 * ((size_t)blockIdx.x * blockDim.x + threadIdx.x);
+    if (idx >= (size_t)lP * N) return;
+    const uint32_t t = (uint32_t)(idx / N), n = (uint32_t)(idx % N);
+    const uint32_t pp = t < l ? t : size_Q + (t - l);
+    const Mod md = mod[pp];
+    u128 a00{0, 0}, a01{0, 0}, a10{0, 0}, a11{0, 0};
+    for (uint32_t d = 0; d < beta; d++) {
+        const ulonglong2 x = *reinterpret_cast<const ulonglong2 *>(digits + ((size_t)d * lP + t) * N + n);
+        const uint64_t *e = evk.p[d] + (size_t)pp * N + n;
+        const ulonglong2 e0 = __ldg(reinterpret_cast<const ulonglong2 *>(e));
+        const ulonglong2 e1 = __ldg(reinterpret_cast<const ulonglong2 *>(e + (size_t)size_QP * N));
+        mac128(a00, x.x, e0.x);
+        mac128(a01, x.y, e0.y);
+        mac128(a10, x.x, e1.x);
+        mac128(a11, x.y, e1.y);
+    }
+    *reinterpret_cast<ulonglong2 *>(out + idx) =
+        make_ulonglong2(barrett128(a00, md.q, md.r0, md.r1), barrett128(a01, md.q, md.r0, md.r1));
+    *reinterpret_cast<ulonglong2 *>(out + (size_t)lP * N + idx) =
+        make_ulonglong2(barrett128(a10, md.q, md.r0, md.r1), barrett128(a11, md.q, md.r0, md.r1));
+}
+
+// HMult tensor product (src/polymath.cu:463-498): d0 = a0 b0, d2 = a1 b1, d1 = (a0+a1)(b0+b1) - d0 - d2
+__global__ void __launch_bounds__(256) tensor_mul_kernel(const uint64_t *__restrict__ a, const uint64_t *__restrict__ b, uint64_t *__restrict__ out,
+                                                        const Mod *mod, uint32_t N, uint32_t l) {
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t S = (size_t)l * N;
+    if (idx >= S) return;
+    const Mod md = mod[idx / N];
+    const uint64_t q = md.q;
+    const uint64_t a0 = a[idx], a1 = a[S + idx], b0 = b[idx], b1 = b[S + idx];
+    u128 p{0, 0};
+    mac128(p, a0, b0);
+    const uint64_t d0 = barrett128(p, q, md.r0, md.r1);
+    p = u128{0, 0};
+    mac128(p, a1, b1);
+    const uint64_t d2 = barrett128(p, q, md.r0, md.r1);
+    p = u128{0, 0};
+    mac128(p, add_mod(a0, a1, q), add_mod(b0, b1, q));
+    const uint64_t d1 = barrett128(p, q, md.r0, md.r1);
+    out[idx] = d0;
+    out[S + idx] = sub_mod(sub_mod(d1, d0, q), d2, q);
+    out[2 * S + idx] = d2;
+}
+
+// src/polymath.cu:17-180
+__global__ void __launch_bounds__(256) poly_op_kernel(int op, const uint64_t *a, const uint64_t *b, uint64_t *out, const Mod *mod,
+                                                     uint32_t N, uint32_t n_limbs) {
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (size_t)n_limbs * N) return;
+    const Mod md = mod[idx / N];
+    const uint64_t q = md.q, x = a[idx];
+    uint64_t r;
+    if (op == 0) r = add_mod(x, b[idx], q);
+    else if (op == 1) r = sub_mod(x, b[idx], q);
+    else if (op == 2) {
+        u128 p{0, 0};
+        mac128(p, x, b[idx]);
+        r = barrett128(p, q, md.r0, md.r1);
+    } else r = x ? q - x : 0;
+    out[idx] = r;
+}
+
+// NTT-domain automorphism (src/galois.cu:11-18): dst[l][i] = src[l][perm[i]].
+// Optional second operand pair so that c0 and c1 (or several digit buffers) go in one launch.
+__global__ void __launch_bounds__(256) galois_gather_kernel(const uint64_t *__restrict__ src, uint64_t *__restrict__ dst,
+                                                           const uint32_t *__restrict__ perm, uint32_t N, uint32_t n_limbs) {
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (size_t)n_limbs * N) return;
+    const size_t limb = idx / N;
+    dst[idx] = src[limb * N + perm[idx % N]];
+}
+
+struct MacPtrs {
+    const uint64_t *const *pts;
+    const uint64_t *const *babies;
+};
+
+// BSGS giant-step multiply-accumulate (src/bsgs.cu:51-96): out_k = sum_b pt_b (.) baby_b[k].
+// The reference reduces after every term; the sum of canonical products is the same residue.
+__global__ void __launch_bounds__(256) bsgs_mac_kernel(const uint64_t *const *pts, const uint64_t *const *babies, uint64_t *out, const Mod *mod,
+                                                      uint32_t N, uint32_t l, uint32_t M) {
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t S = (size_t)l * N;
+    if (idx >= S) return;
+    const Mod md = mod[idx / N];
+    u128 a0{0, 0}, a1{0, 0};
+    uint32_t pending = 0;
+    uint64_t r0 = 0, r1 = 0;
+    for (uint32_t b = 0; b < M; b++) {
+        const uint64_t p = pts[b][idx];
+        mac128(a0, p, babies[b][idx]);
+        mac128(a1, p, babies[b][S + idx]);
+        if (++pending == 32) {  // 32 products of two 61-bit values stay below 2^128
+            a0 = u128{barrett128(a0, md.q, md.r0, md.r1), 0};
+            a1 = u128{barrett128(a1, md.q, md.r0, md.r1), 0};
+            pending = 1;
+        }
+    }
+    r0 = barrett128(a0, md.q, md.r0, md.r1);
+    r1 = barrett128(a1, md.q, md.r0, md.r1);
+    out[idx] = r0;
+    out[S + idx] = r1;
+}
+
+static int run_bconv(const b2_ctx *c, bool copy, const uint64_t *in, uint64_t *out, const uint64_t *copy_src, const BconvGroup *groups,
+                     uint32_t n_groups, const uint2 *outs, const uint64_t *mats, uint32_t max_ni, uint32_t max_out, cudaStream_t s) {
+    const uint32_t N = (uint32_t)c->N;
+    dim3 grid(N / 2 / 128, n_groups);
+    const size_t smem = (size_t)max_ni * max_out * 8;
+    if (max_ni > 16) return fail(B2_ESIZE, "special_modulus_size above 16 is not built");
+    if (copy) {
+        if (max_ni <= 8) bconv_kernel<8, true><<<grid, 128, smem, s>>>(in, out, copy_src, groups, outs, mats, c->d_mod, N);
+        else bconv_kernel<16, true><<<grid, 128, smem, s>>>(in, out, copy_src, groups, outs, mats, c->d_mod, N);
+    } else {
+        if (max_ni <= 8) bconv_kernel<8, false><<<grid, 128, smem, s>>>(in, out, copy_src, groups, outs, mats, c->d_mod, N);
+        else bconv_kernel<16, false><<<grid, 128, smem, s>>>(in, out, copy_src, groups, outs, mats, c->d_mod, N);
+    }
+    LAUNCH_CHECK("bconv_kernel");
+    return B2_OK;
+}
+
+// ------------------------------------------------------------------------------------------------
+// C ABI: operations
+// ------------------------------------------------------------------------------------------------
+#define CHECK_CTX(c)                                                       \
+    if (!(c)) return fail(B2_EINVAL, "null context");                      \
+    CUDA_TRY(cudaSetDevice((c)->device));
+#define CHECK_LEVEL(c, l)                                                                          \
+    if ((l) < 1 || (l) > (c)->size_Q) return fail(B2_EINVAL, "size_Ql must be in [1, size_Q]");
+
+static inline size_t limb_bytes(const b2_ctx *c) { return c->N * 8; }
+
+extern "C" size_t b2_workspace_bytes(const b2_ctx *c, int op, size_t l) {
+    if (!c || l < 1 || l > c->size_Q) return 0;
+    const size_t a = c->size_P, beta = (l + a - 1) / a, lP = l + a, L = limb_bytes(c);
+    switch (op) {
+        case B2_OP_MODUP: return l * L;
+        case B2_OP_MODDOWN: return 3 * l * L;
+        case B2_OP_KEYSWITCH: return (l + beta * lP + 2 * lP) * L;
+        case B2_OP_RESCALE: return 3 * L;
+        case B2_OP_MUL_RELIN: return (l + beta * lP + 2 * lP + 3 * l) * L;
+        case B2_OP_ROTATE: return (l + beta * lP + 2 * lP + 2 * l) * L;
+        case B2_OP_HOIST: return (l + 2 * beta * lP + 2 * lP + l) * L;
+        default: return 0;
+    }
+}
+
+extern "C" int b2_ntt_forward(b2_ctx *c, uint64_t *d, size_t n_limbs, size_t first_prime, void *stream) {
+    CHECK_CTX(c);
+    if (!d || first_prime + n_limbs > c->size_QP) return fail(B2_EINVAL, "ntt_forward: limb range outside the modulus chain");
+    return run_fwd(c, d, d, nullptr, (uint32_t)n_limbs, (uint32_t)first_prime, EpiStore{}, (cudaStream_t)stream);
+}
+
+extern "C" int b2_ntt_inverse(b2_ctx *c, uint64_t *d, size_t n_limbs, size_t first_prime, void *stream) {
+    CHECK_CTX(c);
+    if (!d || first_prime + n_limbs > c->size_QP) return fail(B2_EINVAL, "ntt_inverse: limb range outside the modulus chain");
+    return run_inv(c, d, d, nullptr, (uint32_t)n_limbs, (uint32_t)first_prime, c->d_fin_plain, (cudaStream_t)stream);
+}
+
+// ModUp into `out`; `t` = l limbs of scratch for the scaled coefficient form
+static int modup_impl(b2_ctx *c, size_t l, const uint64_t *c2, uint64_t *out, uint64_t *t, cudaStream_t s) {
+    const LevelPlan &pl = c->plan[l];
+    int rc = run_inv(c, c2, t, pl.jobs_up_intt, (uint32_t)l, 0, pl.fin_up, s);
+    if (rc) return rc;
+    rc = run_bconv(c, true, t, out, c2, pl.grp_up, pl.beta, pl.outs_up, pl.mat_up, (uint32_t)c->size_P, (uint32_t)(l + c->size_P), s);
+    if (rc) return rc;
+    return run_fwd(c, out, out, pl.jobs_up_ntt, pl.n_up_ntt, 0, EpiStore{}, s);
+}
+
+extern "C" int b2_modup(b2_ctx *c, size_t l, const uint64_t *d_c2, uint64_t *d_out, void *d_ws, size_t ws_bytes, void *stream) {
+    CHECK_CTX(c);
+    CHECK_LEVEL(c, l);
+    if (!d_c2 || !d_out || !d_ws) return fail(B2_EINVAL, "modup: null pointer");
+    if (ws_bytes < b2_workspace_bytes(c, B2_OP_MODUP, l)) return fail(B2_EWS, "modup: workspace too small");
+    return modup_impl(c, l, d_c2, d_out, (uint64_t *)d_ws, (cudaStream_t)stream);
+}
+
+static int inner_prod_impl(b2_ctx *c, size_t l, const uint64_t *digits, const uint64_t *const *evk, size_t n_evk, uint64_t *out, cudaStream_t s) {
+    const size_t beta = c->plan[l].beta, lP = l + c->size_P;
+    if (n_evk < beta) return fail(B2_EINVAL, "key has fewer digits than this level needs");
+    if (beta > 64) return fail(B2_ESIZE, "more than 64 digits");
+    EvkPtrs ep;
+    for (size_t d = 0; d < beta; d++) {
+        if (!evk[d]) return fail(B2_EINVAL, "null evaluation-key digit");
+        ep.p[d] = evk[d];
+    }
+    const size_t pairs = lP * c->N / 2;
+    ks_inner_prod_kernel<<<(unsigned)((pairs + 255) / 256), 256, 0, s>>>(digits, ep, out, c->d_mod, (uint32_t)c->N, (uint32_t)l, (uint32_t)lP,
+                                                                      (uint32_t)c->size_Q, (uint32_t)c->size_QP, (uint32_t)beta);
+    LAUNCH_CHECK("ks_inner_prod_kernel");
+    return B2_OK;
+}
+
+extern "C" int b2_ks_inner_prod(b2_ctx *c, size_t l, const uint64_t *d_digits, const uint64_t *const *evk, size_t n_evk, uint64_t *d_out,
+                                void *stream) {
+    CHECK_CTX(c);
+    CHECK_LEVEL(c, l);
+    if (!d_digits || !evk || !d_out) return fail(B2_EINVAL, "ks_inner_prod: null pointer");
+    return inner_prod_impl(c, l, d_digits, evk, n_evk, d_out, (cudaStream_t)stream);
+}
+
+// ModDown of n_poly (1 or 2) polynomials held in cx [n_poly][l+alpha][N].
+// ACCUM: out += result (the add_to_ct step of the key switch), else out = result.
+// delta: n_poly * l limbs of scratch.
+static int moddown_impl(b2_ctx *c, size_t l, size_t n_poly, uint64_t *cx, uint64_t *out, uint64_t *delta, bool accum, cudaStream_t s) {
+    const LevelPlan &pl = c->plan[l];
+    const size_t a = c->size_P;
+    int rc = run_inv(c, cx, cx, pl.jobs_dn_intt, (uint32_t)(n_poly * a), 0, c->d_fin_P, s);
+    if (rc) return rc;
+    rc = run_bconv(c, false, cx, delta, nullptr, pl.grp_dn, (uint32_t)n_poly, pl.outs_dn, c->d_mat_dn, (uint32_t)a, (uint32_t)l, s);
+    if (rc) return rc;
+    if (accum) {
+        EpiSubMul<true> epi{cx, out, c->d_Pinv};
+        return run_fwd(c, delta, delta, pl.jobs_dn_ntt, (uint32_t)(n_poly * l), 0, epi, s);
+    }
+    EpiSubMul<false> epi{cx, out, c->d_Pinv};
+    return run_fwd(c, delta, delta, pl.jobs_dn_ntt, (uint32_t)(n_poly * l), 0, epi, s);
+}
+
+extern "C" int b2_moddown(b2_ctx *c, size_t l, size_t n_poly, uint64_t *d_cx, uint64_t *d_out, void *d_ws, size_t ws_bytes, void *stream) {
+    CHECK_CTX(c);
+    CHECK_LEVEL(c, l);
+    if (!d_cx || !d_out || !d_ws) return fail(B2_EINVAL, "moddown: null pointer");
+    if (n_poly < 1 || n_poly > 2) return fail(B2_EINVAL, "moddown: n_poly must be 1 or 2");
+    if (ws_bytes < b2_workspace_bytes(c, B2_OP_MODDOWN, l)) return fail(B2_EWS, "moddown: workspace too small");
+    return moddown_impl(c, l, n_poly, d_cx, d_out, (uint64_t *)d_ws, false, (cudaStream_t)stream);
+}
+
+// ws layout of the key switch: t [l] | up [beta][lP] | cx [2][lP]; delta reuses `up`
+static int keyswitch_impl(b2_ctx *c, size_t l, const uint64_t *c2, const uint64_t *const *evk, size_t n_evk, uint64_t *ct, uint64_t *ws,
+                          cudaStream_t s) {
+    const size_t N = c->N, lP = l + c->size_P, beta = c->plan[l].beta;
+    uint64_t *t = ws, *up = t + l * N, *cx = up + beta * lP * N;
+    int rc = modup_impl(c, l, c2, up, t, s);
+    if (rc) return rc;
+    rc = inner_prod_impl(c, l, up, evk, n_evk, cx, s);
+    if (rc) return rc;
+    return moddown_impl(c, l, 2, cx, ct, up, true, s);
+}
+
+extern "C" int b2_keyswitch(b2_ctx *c, size_t l, const uint64_t *d_c2, const uint64_t *const *evk, size_t n_evk, uint64_t *d_ct, void *d_ws,
+                            size_t ws_bytes, void *stream) {
+    CHECK_CTX(c);
+    CHECK_LEVEL(c, l);
+    if (!d_c2 || !evk || !d_ct || !d_ws) return fail(B2_EINVAL, "keyswitch: null pointer");
+    if (ws_bytes < b2_workspace_bytes(c, B2_OP_KEYSWITCH, l)) return fail(B2_EWS, "keyswitch: workspace too small");
+    return keyswitch_impl(c, l, d_c2, evk, n_evk, d_ct, (uint64_t *)d_ws, (cudaStream_t)stream);
+}
+
+extern "C" int b2_tensor_mul(b2_ctx *c, size_t l, const uint64_t *d_a, const uint64_t *d_b, uint64_t *d_out, void *stream) {
+    CHECK_CTX(c);
+    CHECK_LEVEL(c, l);
+    if (!d_a || !d_b || !d_out) return fail(B2_EINVAL, "tensor_mul: null pointer");
+    const size_t n = l * c->N;
+    tensor_mul_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(d_a, d_b, d_out, c->d_mod, (uint32_t)c->N, (uint32_t)l);
+    LAUNCH_CHECK("tensor_mul_kernel");
+    return B2_OK;
+}
+
+extern "C" int b2_multiply_and_relin(b2_ctx *c, size_t l, const uint64_t *d_a, const uint64_t *d_b, const uint64_t *const *rlk, size_t n_evk,
+                                     uint64_t *d_out, void *d_ws, size_t ws_bytes, void *stream) {
+    CHECK_CTX(c);
+    CHECK_LEVEL(c, l);
+    if (!d_a || !d_b || !rlk || !d_out || !d_ws) return fail(B2_EINVAL, "multiply_and_relin: null pointer");
+    if (ws_bytes < b2_workspace_bytes(c, B2_OP_MUL_RELIN, l)) return fail(B2_EWS, "multiply_and_relin: workspace too small");
+    cudaStream_t s = (cudaStream_t)stream;
+    const size_t S = l * c->N;
+    uint64_t *t3 = (uint64_t *)d_ws, *ws = t3 + 3 * S;
+    int rc = b2_tensor_mul(c, l, d_a, d_b, t3, stream);
+    if (rc) return rc;
+    CUDA_TRY(cudaMemcpyAsync(d_out, t3, 2 * S * 8, cudaMemcpyDeviceToDevice, s));
+    return keyswitch_impl(c, l, t3 + 2 * S, rlk, n_evk, d_out, ws, s);
+}
+
+extern "C" int b2_rescale(b2_ctx *c, size_t l, size_t n_poly, const uint64_t *d_in, uint64_t *d_out, void *d_ws, size_t ws_bytes, void *stream) {
+    CHECK_CTX(c);
+    CHECK_LEVEL(c, l);
+    if (l < 2) return fail(B2_EINVAL, "rescale: no prime left to drop");
+    if (n_poly < 1 || n_poly > 3) return fail(B2_EINVAL, "rescale: n_poly must be in [1, 3]");
+    if (!d_in || !d_out || !d_ws) return fail(B2_EINVAL, "rescale: null pointer");
+    if (ws_bytes < b2_workspace_bytes(c, B2_OP_RESCALE, l)) return fail(B2_EWS, "rescale: workspace too small");
+    cudaStream_t s = (cudaStream_t)stream;
+    const LevelPlan &pl = c->plan[l];
+    uint64_t *r = (uint64_t *)d_ws;  // [n_poly][N] coefficient form of the dropped limbs
+    // INTT of each polynomial's last limb, out of place into r (one launch pair per polynomial,
+    // because source and destination slots differ)
+    for (size_t p = 0; p < n_poly; p++) {
+        int rc = run_inv(c, d_in + (p * l + l - 1) * c->N, r + p * c->N, nullptr, 1, (uint32_t)(l - 1), c->d_fin_plain, s);
+        if (rc) return rc;
+    }
+    // r mod q_j for every remaining prime: a base conversion with one input and the matrix [1]
+    int rc = run_bconv(c, false, r, d_out, nullptr, pl.grp_rs, (uint32_t)n_poly, pl.outs_rs, c->d_one, 1, (uint32_t)(l - 1), s);
+    if (rc) return rc;
+    EpiSubMul<false> epi{d_in, d_out, pl.qlast_inv};
+    return run_fwd(c, d_out, d_out, pl.jobs_rs_ntt, (uint32_t)(n_poly * (l - 1)), 0, epi, s);
+}
+
+extern "C" uint32_t b2_galois_elt_from_step(int step, size_t N) {
+    const uint32_t n = (uint32_t)N, m = 2 * n;
+    if (step == 0) return m - 1;
+    const bool neg = step < 0;
+    const uint32_t pos = (uint32_t)(neg ? -(int64_t)step : step);
+    if (pos >= (n >> 1)) return 0;
+    uint32_t k = neg ? (n >> 1) - pos : pos;
+    uint64_t e = 1;
+    while (k--) e = (e * 5) & (m - 1);
+    return (uint32_t)e;
+}
+
+static int galois_table(b2_ctx *c, uint32_t elt, const uint32_t **out) {
+    std::lock_guard<std::mutex> lk(c->mu);
+    auto it = c->galois.find(elt);
+    if (it != c->galois.end()) {
+        *out = it->second;
+        return B2_OK;
+    }
+    if (!(elt & 1) || elt >= 2 * c->N) return fail(B2_EINVAL, "Galois element must be odd and below 2N");
+    const size_t N = c->N;
+    std::vector<uint32_t> perm(N);
+    for (size_t i = 0; i < N; i++) {
+        const uint32_t rev = h_bitrev((uint32_t)(i + N), c->logN + 1);
+        const uint64_t raw = (((uint64_t)elt * rev) >> 1) & (N - 1);
+        perm[i] = h_bitrev((uint32_t)raw, c->logN);
+    }
+    uint32_t *d = nullptr;
+    CUDA_TRY(cudaMalloc(&d, N * 4));
+    CUDA_TRY(cudaMemcpy(d, perm.data(), N * 4, cudaMemcpyHostToDevice));
+    c->galois[elt] = d;
+    *out = d;
+    return B2_OK;
+}
+
+extern "C" int b2_galois_prepare(b2_ctx *c, uint32_t elt) {
+    CHECK_CTX(c);
+    const uint32_t *t;
+    return galois_table(c, elt, &t);
+}
+
+static int gather_impl(b2_ctx *c, const uint32_t *perm, const uint64_t *src, uint64_t *dst, size_t n_limbs, cudaStream_t s) {
+    const size_t n = n_limbs * c->N;
+    galois_gather_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(src, dst, perm, (uint32_t)c->N, (uint32_t)n_limbs);
+    LAUNCH_CHECK("galois_gather_kernel");
+    return B2_OK;
+}
+
+// tables must exist before an asynchronous sequence starts: creating one synchronises
+static int galois_lookup(b2_ctx *c, uint32_t elt, const uint32_t **out) {
+    std::lock_guard<std::mutex> lk(c->mu);
+    auto it = c->galois.find(elt);
+    if (it == c->galois.end()) return fail(B2_ENOKEY, "Galois elt not present: call b2_galois_prepare first");
+    *out = it->second;
+    return B2_OK;
+}
+
+extern "C" int b2_galois_permute(b2_ctx *c, uint32_t elt, const uint64_t *d_src, uint64_t *d_dst, size_t n_limbs, void *stream) {
+    CHECK_CTX(c);
+    if (!d_src || !d_dst || d_src == d_dst) return fail(B2_EINVAL, "galois_permute: needs distinct source and destination");
+    const uint32_t *perm;
+    int rc = galois_lookup(c, elt, &perm);
+    if (rc) return rc;
+    return gather_impl(c, perm, d_src, d_dst, n_limbs, (cudaStream_t)stream);
+}
+
+extern "C" int b2_apply_galois(b2_ctx *c, size_t l, uint32_t elt, const uint64_t *d_ct, const uint64_t *const *ksk, size_t n_evk, uint64_t *d_out,
+                               void *d_ws, size_t ws_bytes, void *stream) {
+    CHECK_CTX(c);
+    CHECK_LEVEL(c, l);
+    if (!d_ct || !ksk || !d_out || !d_ws) return fail(B2_EINVAL, "apply_galois: null pointer");
+    if (ws_bytes < b2_workspace_bytes(c, B2_OP_ROTATE, l)) return fail(B2_EWS, "apply_galois: workspace too small");
+    const uint32_t *perm;
+    int rc = galois_lookup(c, elt, &perm);
+    if (rc) return rc;
+    cudaStream_t s = (cudaStream_t)stream;
+    const size_t S = l * c->N;
+    uint64_t *p = (uint64_t *)d_ws, *ws = p + 2 * S;  // permuted c0 | permuted c1
+    rc = gather_impl(c, perm, d_ct, p, 2 * l, s);  // both polynomials: limb index only selects the row
+    if (rc) return rc;
+    // (c0, c1) <- (perm(c0), 0) + key switch of perm(c1)   (src/evaluate.cu:1644-1655)
+    CUDA_TRY(cudaMemcpyAsync(d_out, p, S * 8, cudaMemcpyDeviceToDevice, s));
+    CUDA_TRY(cudaMemsetAsync(d_out + S, 0, S * 8, s));
+    return keyswitch_impl(c, l, p + S, ksk, n_evk, d_out, ws, s);
+}
+
+extern "C" int b2_hoist_rotations(b2_ctx *c, size_t l, const uint64_t *d_ct, const uint32_t *elts, size_t n_steps, const uint64_t *const *ksk,
+                                  size_t n_evk, uint64_t *const *d_outs, void *d_ws, size_t ws_bytes, void *stream) {
+    CHECK_CTX(c);
+    CHECK_LEVEL(c, l);
+    if (!d_ct || !elts || !ksk || !d_outs || !d_ws) return fail(B2_EINVAL, "hoist_rotations: null pointer");
+    if (ws_bytes < b2_workspace_bytes(c, B2_OP_HOIST, l)) return fail(B2_EWS, "hoist_rotations: workspace too small");
+    cudaStream_t s = (cudaStream_t)stream;
+    const size_t N = c->N, lP = l + c->size_P, beta = c->plan[l].beta, S = l * N;
+    std::vector<const uint32_t *> perms(n_steps);
+    for (size_t i = 0; i < n_steps; i++) {
+        int rc = galois_lookup(c, elts[i], &perms[i]);
+        if (rc) return rc;
+    }
+    // ws: t [l] | up [beta][lP] | pup [beta][lP] | cx [2][lP] | pc0 [l]
+    uint64_t *t = (uint64_t *)d_ws, *up = t + S, *pup = up + beta * lP * N, *cx = pup + beta * lP * N, *pc0 = cx + 2 * lP * N;
+    int rc = modup_impl(c, l, d_ct + S, up, t, s);  // ModUp(c1) once (src/evaluate.cu:2013-2014)
+    if (rc) return rc;
+    for (size_t i = 0; i < n_steps; i++) {
+        if (!d_outs[i]) return fail(B2_EINVAL, "hoist_rotations: null output");
+        rc = gather_impl(c, perms[i], d_ct, pc0, l, s);
+        if (rc) return rc;
+        rc = gather_impl(c, perms[i], up, pup, beta * lP, s);  // permute AFTER ModUp (src/evaluate.cu:2041-2045)
+        if (rc) return rc;
+        rc = inner_prod_impl(c, l, pup, ksk + i * n_evk, n_evk, cx, s);
+        if (rc) return rc;
+        // c0_out = perm(c0) + ModDown(cx0); c1_out = ModDown(cx1)
+        CUDA_TRY(cudaMemcpyAsync(d_outs[i], pc0, S * 8, cudaMemcpyDeviceToDevice, s));
+        CUDA_TRY(cudaMemsetAsync(d_outs[i] + S, 0, S * 8, s));
+        rc = moddown_impl(c, l, 2, cx, d_outs[i], pup, true, s);
+        if (rc) return rc;
+    }
+    return B2_OK;
+}
+
+extern "C" int b2_bsgs_mac(b2_ctx *c, size_t l, size_t M, const uint64_t *const *pts, const uint64_t *const *babies, uint64_t *d_out, void *stream) {
+    CHECK_CTX(c);
+    CHECK_LEVEL(c, l);
+    if (!pts || !babies || !d_out || M == 0) return fail(B2_EINVAL, "bsgs_mac: bad argument");
+    const size_t n = l * c->N;
+    bsgs_mac_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(pts, babies, d_out, c->d_mod, (uint32_t)c->N, (uint32_t)l, (uint32_t)M);
+    LAUNCH_CHECK("bsgs_mac_kernel");
+    return B2_OK;
+}
+
+extern "C" int b2_poly_op(b2_ctx *c, int op, size_t n_limbs, const uint64_t *d_a, const uint64_t *d_b, uint64_t *d_out, void *stream) {
+    CHECK_CTX(c);
+    if (op < 0 || op > 3 || !d_a || !d_out || (op != 3 && !d_b) || n_limbs < 1 || n_limbs > c->size_QP) return fail(B2_EINVAL, "poly_op: bad argument");
+    const size_t n = n_limbs * c->N;
+    poly_op_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(op, d_a, d_b, d_out, c->d_mod, (uint32_t)c->N, (uint32_t)n_limbs);
+    LAUNCH_CHECK("poly_op_kernel");
+    return B2_OK;
+}

@@ -1,0 +1,263 @@
+"""GPU parity: every C-ABI entry point against (a) the hashes the unmodified reference library
+recorded on a B200 (tests/golden/*.json) and (b) the CPU oracle, bit for bit, on the same seeded
+synthetic limbs. Integer work only: equality is exact, there is no tolerance anywhere."""
+import glob
+import os
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+import pyPhantom as ph
+from pyPhantom import _native
+from pyPhantom._native import LIB, check
+from gpu_helpers import dev, hashes, host, key_dev, load_case, make_ctx, stream
+from oracle_lib import limb_hashes
+
+GOLDEN = sorted(glob.glob(os.path.join(os.path.dirname(__file__), "golden", "*.json")))
+IDS = [os.path.basename(p)[:-5] for p in GOLDEN]
+
+
+def _ws(ctx, op, l):
+    return ctx.workspace(op, l)
+
+
+@pytest.mark.parametrize("logn", [12, 13, 14, 15, 16])
+def test_tables_match_oracle(logn):
+    N = 1 << logn
+    ctx, o = make_ctx(N, [50, 40, 60], 1)
+    for i in range(3):
+        assert np.array_equal(ctx.table(0, i), o.twiddle(i))
+        assert np.array_equal(ctx.table(1, i), o.twiddle(i, inverse=True))
+        q = int(o.primes[i])
+        w = ctx.table(0, i)[:64]
+        ws = ctx.table(2, i)[:64]
+        assert [int(x) for x in ws] == [(int(v) << 64) // q for v in w]  # src/host/ntt.cu compute_shoup
+
+
+@pytest.mark.parametrize("logn", [12, 13, 14, 15, 16])
+def test_ntt_against_oracle_and_roundtrip(logn):
+    N = 1 << logn
+    ctx, o = make_ctx(N, [60, 30, 40, 50, 59, 60], 2)
+    x = o.fill(1, o.primes, 5, 50)[0]
+    d = dev(x)
+    check(LIB.b2_ntt_forward(ctx._h, d.data_ptr(), 6, 0, stream()))
+    fwd = host(d).copy()
+    assert np.array_equal(fwd, o.ntt_forward(x))
+    check(LIB.b2_ntt_inverse(ctx._h, d.data_ptr(), 6, 0, stream()))
+    assert np.array_equal(host(d), x)
+    # a sub-range of the chain: limbs 2..4 only
+    d = dev(x[2:5])
+    check(LIB.b2_ntt_inverse(ctx._h, d.data_ptr(), 3, 2, stream()))
+    assert np.array_equal(host(d), o.ntt_inverse(x[2:5], first_prime=2))
+    # edge values: all zero, all q-1
+    edge = np.stack([np.zeros(N, dtype=np.uint64), np.full(N, int(o.primes[1]) - 1, dtype=np.uint64)])
+    d = dev(edge)
+    check(LIB.b2_ntt_forward(ctx._h, d.data_ptr(), 1, 0, stream()))
+    check(LIB.b2_ntt_forward(ctx._h, d[1].data_ptr(), 1, 1, stream()))
+    got = host(d)
+    assert not got[0].any()
+    assert np.array_equal(got[1], o.ntt_forward(edge[1:2], first_prime=1)[0])
+
+
+@pytest.mark.parametrize("path", GOLDEN, ids=IDS)
+def test_every_stage_matches_the_reference(path):
+    case, ctx, o = load_case(path)
+    N, l, seed, h = o.N, case["level"], case["seed"], ctx._h
+    beta, lP, want = o.beta(l), l + o.size_P, case["hashes"]
+    s = stream()
+
+    # transforms over the whole chain
+    x = o.fill(1, o.primes, seed, 50)[0]
+    d = dev(x)
+    check(LIB.b2_ntt_forward(h, d.data_ptr(), o.size_QP, 0, s))
+    assert hashes(d, N) == want["ntt_fwd"]
+    d = dev(x)
+    check(LIB.b2_ntt_inverse(h, d.data_ptr(), o.size_QP, 0, s))
+    assert hashes(d, N) == want["ntt_inv"]
+
+    # the three stages of the key switch
+    rlk = o.synth_key(beta, seed, 10)
+    rlk_t, rlk_p = key_dev(rlk)
+    c2 = dev(o.fill(1, o.primes[:l], seed, 3)[0])
+    up = ctx.empty(beta, lP)
+    ws, nb = _ws(ctx, _native.OP_MODUP, l)
+    check(LIB.b2_modup(h, l, c2.data_ptr(), up.data_ptr(), ws.data_ptr(), nb, s))
+    assert hashes(up, N) == want["modup"]
+    cx = ctx.empty(2, lP)
+    check(LIB.b2_ks_inner_prod(h, l, up.data_ptr(), rlk_p.ctypes.data, beta, cx.data_ptr(), s))
+    assert hashes(cx, N) == want["inner_prod"]
+    dn = ctx.empty(2, l)
+    ws, nb = _ws(ctx, _native.OP_MODDOWN, l)
+    check(LIB.b2_moddown(h, l, 2, cx.data_ptr(), dn.data_ptr(), ws.data_ptr(), nb, s))
+    assert hashes(dn[0], N) == want["moddown0"]
+    assert hashes(dn[1], N) == want["moddown1"]
+    # one polynomial at a time gives the same limbs
+    check(LIB.b2_ks_inner_prod(h, l, up.data_ptr(), rlk_p.ctypes.data, beta, cx.data_ptr(), s))
+    dn1 = ctx.empty(1, l)
+    check(LIB.b2_moddown(h, l, 1, cx[1].data_ptr(), dn1.data_ptr(), ws.data_ptr(), nb, s))
+    assert hashes(dn1, N) == want["moddown1"]
+
+    # whole key switch, HMult + relin, rescale
+    a_h, b_h = o.synth_ct(l, seed, 1), o.synth_ct(l, seed, 2)
+    ct = dev(a_h)
+    ws, nb = _ws(ctx, _native.OP_KEYSWITCH, l)
+    check(LIB.b2_keyswitch(h, l, c2.data_ptr(), rlk_p.ctypes.data, beta, ct.data_ptr(), ws.data_ptr(), nb, s))
+    assert hashes(ct, N) == want["keyswitch"]
+    a, b = dev(a_h), dev(b_h)
+    m = ctx.empty(2, l)
+    ws, nb = _ws(ctx, _native.OP_MUL_RELIN, l)
+    check(LIB.b2_multiply_and_relin(h, l, a.data_ptr(), b.data_ptr(), rlk_p.ctypes.data, beta, m.data_ptr(),
+                                    ws.data_ptr(), nb, s))
+    assert hashes(m, N) == want["mul_relin"]
+    if l >= 2:
+        ws, nb = _ws(ctx, _native.OP_RESCALE, l)
+        r = ctx.empty(2, l - 1)
+        check(LIB.b2_rescale(h, l, 2, m.data_ptr(), r.data_ptr(), ws.data_ptr(), nb, s))
+        assert hashes(r, N) == want["mul_relin_rescale"]
+        check(LIB.b2_rescale(h, l, 2, a.data_ptr(), r.data_ptr(), ws.data_ptr(), nb, s))
+        assert hashes(r, N) == want["rescale"]
+
+    # rotations: permute-then-switch, and hoisted (ModUp first, then permute)
+    keys = [o.synth_key(beta, seed, 100 + 8 * e) for e in range(len(case["elts"]))]
+    kd = [key_dev(k) for k in keys]
+    ws, nb = _ws(ctx, _native.OP_ROTATE, l)
+    for e, (step, elt) in enumerate(zip(case["steps"], case["elts"])):
+        assert ph.get_elt_from_step(step, N) == elt
+        out = ctx.empty(2, l)
+        check(LIB.b2_apply_galois(h, l, elt, a.data_ptr(), kd[e][1].ctypes.data, beta, out.data_ptr(), ws.data_ptr(), nb, s))
+        assert hashes(out, N) == want[f"rotate_{step}"]
+    outs = [ctx.empty(2, l) for _ in keys]
+    optr = np.array([t.data_ptr() for t in outs], dtype=np.uint64)
+    ksk = np.concatenate([k[1] for k in kd])
+    elts = np.array(case["elts"], dtype=np.uint32)
+    ws, nb = _ws(ctx, _native.OP_HOIST, l)
+    check(LIB.b2_hoist_rotations(h, l, a.data_ptr(), elts.ctypes.data, len(elts), ksk.ctypes.data, beta,
+                                 optr.ctypes.data, ws.data_ptr(), nb, s))
+    for step, out in zip(case["steps"], outs):
+        assert hashes(out, N) == want[f"hoist_{step}"]
+    assert np.array_equal(host(a), a_h), "inputs must stay untouched"
+
+
+@pytest.mark.parametrize("l", [1, 2, 3, 5, 8])
+def test_levels_and_ragged_digits_against_oracle(l):
+    # alpha = 3 over 8 Q limbs: levels with 1, 2 and 3 digits, last digit of size 1, 2 or 3
+    N = 4096
+    ctx, o = make_ctx(N, [55, 40, 41, 42, 43, 44, 45, 46, 58, 59, 60], 3)
+    beta = o.beta(l)
+    key = o.synth_key(beta, 21, 10)
+    kt, kp = key_dev(key)
+    c2_h, ct_h = o.fill(1, o.primes[:l], 21, 3)[0], o.synth_ct(l, 21, 1)
+    c2, ct = dev(c2_h), dev(ct_h)
+    ws, nb = _ws(ctx, _native.OP_KEYSWITCH, l)
+    check(LIB.b2_keyswitch(ctx._h, l, c2.data_ptr(), kp.ctypes.data, beta, ct.data_ptr(), ws.data_ptr(), nb, stream()))
+    assert np.array_equal(host(ct), o.keyswitch(l, c2_h, key, ct_h))
+    if l >= 2:
+        for n_poly in (1, 2, 3):
+            x_h = o.fill(n_poly, o.primes[:l], 22, 4)
+            r = ctx.empty(n_poly, l - 1)
+            ws, nb = _ws(ctx, _native.OP_RESCALE, l)
+            check(LIB.b2_rescale(ctx._h, l, n_poly, dev(x_h).data_ptr(), r.data_ptr(), ws.data_ptr(), nb, stream()))
+            assert np.array_equal(host(r), o.rescale(l, x_h))
+
+
+def test_elementwise_tensor_and_bsgs_mac():
+    N, l = 8192, 5
+    ctx, o = make_ctx(N, [60, 40, 40, 50, 59, 60, 60], 2)
+    a_h, b_h = o.synth_ct(l, 31, 1), o.synth_ct(l, 31, 2)
+    a, b = dev(a_h), dev(b_h)
+    out = ctx.empty(3, l)
+    check(LIB.b2_tensor_mul(ctx._h, l, a.data_ptr(), b.data_ptr(), out.data_ptr(), stream()))
+    assert np.array_equal(host(out), o.tensor_mul(l, a_h, b_h))
+    r = torch.empty_like(a)
+    for p in range(2):
+        check(LIB.b2_poly_op(ctx._h, 0, l, a[p].data_ptr(), b[p].data_ptr(), r[p].data_ptr(), stream()))
+    assert np.array_equal(host(r), np.stack([o.add(a_h[p], b_h[p]) for p in range(2)]))
+    # negate: 0 stays 0
+    z = dev(np.zeros((1, N), dtype=np.uint64))
+    check(LIB.b2_poly_op(ctx._h, 3, 1, z.data_ptr(), 0, z.data_ptr(), stream()))
+    assert not host(z).any()
+    for M in (1, 3, 40):  # 40 > 32 exercises the mid-sum reduction
+        pts_h = [o.fill(1, o.primes[:l], 32, 1000 + i)[0] for i in range(M)]
+        bab_h = [o.synth_ct(l, 32, 2000 + i) for i in range(M)]
+        pts, bab = [dev(p) for p in pts_h], [dev(x) for x in bab_h]
+        pp = torch.tensor([t.data_ptr() for t in pts], dtype=torch.int64).cuda()
+        bp = torch.tensor([t.data_ptr() for t in bab], dtype=torch.int64).cuda()
+        acc = ctx.empty(2, l)
+        check(LIB.b2_bsgs_mac(ctx._h, l, M, pp.data_ptr(), bp.data_ptr(), acc.data_ptr(), stream()))
+        assert np.array_equal(host(acc), o.bsgs_mac(l, pts_h, bab_h))
+
+
+def test_galois_permute_matches_oracle_table():
+    N = 4096
+    ctx, o = make_ctx(N, [40, 40, 50], 1)
+    x_h = o.fill(1, o.primes[:2], 41, 1)[0]
+    for step in (1, -1, 5, 0):
+        elt = ph.get_elt_from_step(step, N)
+        check(LIB.b2_galois_prepare(ctx._h, elt))
+        out = ctx.empty(2)
+        check(LIB.b2_galois_permute(ctx._h, elt, dev(x_h).data_ptr(), out.data_ptr(), 2, stream()))
+        perm = o.galois_perm(elt)
+        assert np.array_equal(host(out), x_h[:, perm])
+
+
+def test_error_behaviour():
+    N = 4096
+    ctx, o = make_ctx(N, [40, 40, 40, 50, 50], 2)
+    h, s = ctx._h, stream()
+    x = ctx.empty(2, 3)
+    ws, nb = _ws(ctx, _native.OP_KEYSWITCH, 3)
+    kt, kp = key_dev(o.synth_key(2, 1, 10))
+    with pytest.raises(ValueError, match="size_Ql"):
+        check(LIB.b2_keyswitch(h, 4, x.data_ptr(), kp.ctypes.data, 2, x.data_ptr(), ws.data_ptr(), nb, s))
+    with pytest.raises(ValueError, match="workspace"):
+        check(LIB.b2_keyswitch(h, 3, x[0].data_ptr(), kp.ctypes.data, 2, x.data_ptr(), ws.data_ptr(), 16, s))
+    with pytest.raises(ValueError, match="fewer digits"):
+        check(LIB.b2_keyswitch(h, 3, x[0].data_ptr(), kp.ctypes.data, 1, x.data_ptr(), ws.data_ptr(), nb, s))
+    with pytest.raises(ValueError, match="null"):
+        check(LIB.b2_keyswitch(h, 3, 0, kp.ctypes.data, 2, x.data_ptr(), ws.data_ptr(), nb, s))
+    with pytest.raises(ValueError, match="limb range"):
+        check(LIB.b2_ntt_forward(h, x.data_ptr(), 6, 0, s))
+    with pytest.raises(ValueError, match="no prime left"):
+        check(LIB.b2_rescale(h, 1, 2, x.data_ptr(), x.data_ptr(), ws.data_ptr(), nb, s))
+    with pytest.raises(ValueError, match="not present"):
+        check(LIB.b2_galois_permute(h, 12345, x.data_ptr(), ws.data_ptr(), 1, s))
+    import ctypes
+    hh = ctypes.c_void_p()
+    for bad_n in (2048, 1 << 17, 5000):
+        assert LIB.b2_ctx_create(bad_n, o.primes.ctypes.data, 5, 2, 0, ctypes.byref(hh)) == -2
+    comp = np.array([4097 * 3, int(o.primes[1])], dtype=np.uint64)
+    assert LIB.b2_ctx_create(4096, comp.ctypes.data, 2, 1, 0, ctypes.byref(hh)) == -1
+    torch.cuda.synchronize()
+
+
+def test_full_size_properties():
+    """N = 2^16, 24+8 limbs: size-independent properties on the headline configuration."""
+    N = 1 << 16
+    bits = [60] + [40] * 23 + [60] * 8
+    ctx, o = make_ctx(N, bits, 8)
+    h, s = ctx._h, stream()
+    x_h = o.fill(1, o.primes, 77, 1)[0]
+    y_h = o.fill(1, o.primes, 77, 2)[0]
+    x, y = dev(x_h), dev(y_h)
+    # round trip
+    t = x.clone()
+    check(LIB.b2_ntt_forward(h, t.data_ptr(), 32, 0, s))
+    fx = t.clone()
+    check(LIB.b2_ntt_inverse(h, t.data_ptr(), 32, 0, s))
+    assert torch.equal(t, x)
+    # linearity: NTT(x + y) = NTT(x) + NTT(y)
+    sxy = torch.empty_like(x)
+    check(LIB.b2_poly_op(h, 0, 32, x.data_ptr(), y.data_ptr(), sxy.data_ptr(), s))
+    check(LIB.b2_ntt_forward(h, sxy.data_ptr(), 32, 0, s))
+    fy = y.clone()
+    check(LIB.b2_ntt_forward(h, fy.data_ptr(), 32, 0, s))
+    lin = torch.empty_like(x)
+    check(LIB.b2_poly_op(h, 0, 32, fx.data_ptr(), fy.data_ptr(), lin.data_ptr(), s))
+    assert torch.equal(lin, sxy)
+    # canonical outputs: every residue below its prime
+    fxh = host(fx)
+    for i in range(32):
+        assert int(fxh[i].max()) < int(o.primes[i])
