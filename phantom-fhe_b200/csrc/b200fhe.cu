@@ -183,7 +183,7 @@ struct b2_ctx {
     W2 *d_fin_P = nullptr;      // [size_P][2]  = the same times (P/p_i)^-1 mod p_i
     W2 *d_Pinv = nullptr;       // [size_QP] indexed by prime (valid for Q primes): P^-1 mod q_j
     uint64_t *d_mat_dn = nullptr;  // [size_Q][size_P]: (P/p_i) mod q_j
-    uint64_t *d_one = nullptr;     // [1] = 1: the 1x1 "matrix" of the rescale reduction
+    uint64_t *d_one = nullptr;     // [size_QP] ones: the [n_out][1] "matrix" of the rescale reduction
     std::vector<LevelPlan> plan;   // index l (1..size_Q)
     std::map<uint32_t, uint32_t *> galois;  // elt -> device gather table
     std::mutex mu;
@@ -407,7 +407,7 @@ extern "C" int b2_ctx_create(size_t N, const uint64_t *primes, size_t size_QP, s
         }
         Pinv[j] = h_w2(h_invmod(P, qj), qj);
     }
-    const uint64_t one = 1;
+    const std::vector<uint64_t> ones(size_QP, 1);
     auto up = [&](void **dptr, const void *src, size_t bytes) -> cudaError_t {
         cudaError_t e = cudaMalloc(dptr, bytes);
         if (e != cudaSuccess) return e;
@@ -421,7 +421,7 @@ extern "C" int b2_ctx_create(size_t N, const uint64_t *primes, size_t size_QP, s
     if (e == cudaSuccess) e = up((void **)&c->d_fin_P, fin_P.data(), sizeof(W2) * 2 * sP);
     if (e == cudaSuccess) e = up((void **)&c->d_Pinv, Pinv.data(), sizeof(W2) * size_QP);
     if (e == cudaSuccess) e = up((void **)&c->d_mat_dn, mat_dn.data(), 8 * sQ * sP);
-    if (e == cudaSuccess) e = up((void **)&c->d_one, &one, 8);
+    if (e == cudaSuccess) e = up((void **)&c->d_one, ones.data(), 8 * size_QP);
     if (e != cudaSuccess) {
         b2_ctx_destroy(c);
         return fail((int)e, std::string("ctx_create: table upload failed: ") + cudaGetErrorString(e));
