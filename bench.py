@@ -1,0 +1,349 @@
+#!/usr/bin/env python
+"""bench.py - KeySwitch/s of CKKS hybrid key switching at N = 2^16, L = 24, dnum = 3 on B200.
+
+Workload (the configuration the headline metric is quoted on): 24 Q limbs (one 60-bit prime and 23
+primes of 40 bits), 8 special primes of 60 bits, alpha = 8, 3 digits; ciphertext and evaluation-key
+limbs uniform in [0, q_i) from a seeded generator (synthetic; the path is integer-only).
+A step = one batch of BATCH key switches on distinct ciphertexts cycling over KEYS distinct
+evaluation keys, so one step touches ~670 MB, far more than the 126 MB L2 (that is this file's
+answer to the L2-flush rule: inputs larger than L2).
+
+  value : KeySwitch/s over all ranks, inputs resident in HBM, device time (CUDA events, max over ranks)
+  e2e   : the same metric through the reference-facing Python call (pyPhantom.relinearize, the
+          pybind11 surface of the reference) with HOST buffers: every key switch copies its
+          3-polynomial ciphertext in from pinned memory and its 2-polynomial result back out
+  roofline : the dominant kernel, timed live with CUDA events on its own stream
+  cpu_baseline : the CPU restatement (oracle/) timed on this box's cores on a bounded sample
+
+Multi-GPU: one process per GPU (torchrun); the path shards by independent ciphertexts, every rank
+runs its own batch with its own copy of the keys, no data-path collective ("weak" scaling).
+`--impl reference` times the reference's algorithm on the host cores: the reference has no CPU
+implementation of this path (its src/host only builds tables), so the arm runs the CPU
+restatement under oracle/ with every host thread.
+"""
+import argparse
+import ctypes
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, os.path.join(ROOT, "phantom-fhe_b200"))
+
+LOGN, N = 16, 1 << 16
+BITS = [60] + [40] * 23 + [60] * 8
+SPECIAL, LEVEL = 8, 24
+BETA = 3
+LIMB_BYTES = 8 * N
+# algorithmic bytes of one key switch: c2 + evk + ct in + ct out = 5l + 2*beta*(l+alpha) limbs
+KS_LIMBS = 5 * LEVEL + 2 * BETA * (LEVEL + SPECIAL)
+KS_BYTES = KS_LIMBS * LIMB_BYTES
+WORKLOAD = "hybrid_keyswitch_N65536_L24_dnum3_alpha8"
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        return float(json.load(open(p))["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """samples nvidia-smi clocks and throttle reasons while the timed region runs"""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.idx, self.lines, self.proc = gpu_index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "100", "-i", str(self.idx)], stdout=subprocess.PIPE, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=2)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+        sm, mx, reasons = [], 0.0, set()
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx = max(mx, float(f[2]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": mx or None, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def run_reference_arm(args, rank):
+    """the reference's algorithm on the host cores (CPU restatement, all threads); rank 0 only"""
+    if rank != 0:
+        return
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    from oracle_lib import Oracle, create_coeff_modulus, LIB as ORA
+    primes = create_coeff_modulus(N, BITS)
+    o = Oracle(N, primes, SPECIAL)
+    key = o.synth_key(BETA, 2, 10)
+    c2 = o.fill(1, primes[:LEVEL], 2, 3)[0]
+    ct = o.synth_ct(LEVEL, 2, 1)
+    for _ in range(args.warmup):
+        o.keyswitch(LEVEL, c2, key, ct)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        o.keyswitch(LEVEL, c2, key, ct)
+    dt = time.perf_counter() - t0
+    v = args.steps / dt
+    cores = int(ORA.ora_num_threads())
+    line = {"impl": "reference", "metric": "KeySwitch/s", "value": v, "unit": "KeySwitch/s", "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * dt / args.steps, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "u64", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "batch_per_step": 1},
+            "cpu_baseline": {"value": v, "unit": "KeySwitch/s", "cores": cores, "kind": "port",
+                             "sample": f"{args.steps} key switches, one per step"},
+            "e2e": {"value": v, "unit": "KeySwitch/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "note": "the reference has no CPU implementation of this path; this is the CPU restatement in oracle/"}
+    print(json.dumps(line), flush=True)
+
+
+def cpu_baseline_sample(budget_s=12.0):
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    from oracle_lib import Oracle, create_coeff_modulus, LIB as ORA
+    primes = create_coeff_modulus(N, BITS)
+    o = Oracle(N, primes, SPECIAL)
+    key = o.synth_key(BETA, 2, 10)
+    c2 = o.fill(1, primes[:LEVEL], 2, 3)[0]
+    ct = o.synth_ct(LEVEL, 2, 1)
+    o.keyswitch(LEVEL, c2, key, ct)
+    n, t0 = 0, time.perf_counter()
+    while True:
+        o.keyswitch(LEVEL, c2, key, ct)
+        n += 1
+        dt = time.perf_counter() - t0
+        if dt > budget_s or n >= 64:
+            break
+    return {"value": n / dt, "unit": "KeySwitch/s", "cores": int(ORA.ora_num_threads()), "kind": "port",
+            "sample": f"{n} key switches of the same workload in {dt:.1f} s"}
+
+
+# algorithmic limbs moved per launch class inside ONE key switch at this workload
+# (a two-pass transform moves 2 limb-passes per limb algorithmically, so each pass is credited one)
+def kernel_alg_bytes_per_keyswitch():
+    l, a, b, lP = LEVEL, SPECIAL, BETA, LEVEL + SPECIAL
+    up_ntt = b * lP - l
+    return {
+        "ntt_inv_rows": (l + 2 * a) * LIMB_BYTES,
+        "ntt_inv_cols": (l + 2 * a) * LIMB_BYTES,
+        "ntt_fwd_cols": (up_ntt + 2 * l) * LIMB_BYTES,
+        "ntt_fwd_rows": (up_ntt + 2 * l) * LIMB_BYTES,
+        "bconv": ((l + l + b * lP) + (2 * a + 2 * l)) * LIMB_BYTES,
+        "ks_inner_prod": (b * lP + 2 * b * lP + 2 * lP) * LIMB_BYTES,
+    }
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--batch", type=int, default=8, help="key switches per step per GPU")
+    ap.add_argument("--keys", type=int, default=4, help="distinct evaluation keys cycled over")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+
+    if args.impl == "reference":
+        run_reference_arm(args, rank)
+        return
+
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+    import pyPhantom as ph
+    from pyPhantom import _native, synth
+    from pyPhantom._native import LIB, check
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the product has no CPU path")
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+
+    # ---- context, keys and ciphertexts ---------------------------------------------------------
+    mods = ph.create_coeff_modulus(N, BITS)
+    primes = [m.value() for m in mods]
+    parms = ph.params(ph.scheme_type.ckks)
+    parms.set_poly_modulus_degree(N)
+    parms.set_coeff_modulus(mods)
+    parms.set_special_modulus_size(SPECIAL)
+    parms.set_galois_elts([2 * N - 1])
+    ctx = ph.context(parms)
+    B, K = args.batch, args.keys
+    seed = 1000 + rank
+    keys = [ph.relin_key.from_numpy(ctx, [synth.poly(N, primes, 2, seed, 10 + 8 * k + d) for d in range(BETA)])
+            for k in range(K)]
+    key_tabs = [k.pointer_table() for k in keys]
+    host_ct3 = [torch.from_numpy(synth.poly(N, primes[:LEVEL], 3, seed, 200 + b).view(np.int64)).pin_memory()
+                for b in range(B)]
+    dev_ct3 = [t.cuda() for t in host_ct3]          # resident inputs: (c0, c1, c2)
+    host_out = [torch.empty(2, LEVEL, N, dtype=torch.int64).pin_memory() for _ in range(B)]
+    ws, ws_bytes = ctx.workspace(_native.OP_KEYSWITCH, LEVEL)
+    stream = torch.cuda.current_stream()
+    s = stream.cuda_stream
+
+    def step_resident():
+        for b in range(B):
+            t = dev_ct3[b]
+            check(LIB.b2_keyswitch(ctx._h, LEVEL, t[2].data_ptr(), key_tabs[b % K].ctypes.data, BETA, t.data_ptr(),
+                                   ws.data_ptr(), ws_bytes, s))
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    # ---- value: inputs resident --------------------------------------------------------------------
+    for _ in range(args.warmup):
+        step_resident()
+    barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    launches0 = int(LIB.b2_launch_count())
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(args.steps):
+        step_resident()
+    e1.record(stream)
+    barrier()
+    ms = e0.elapsed_time(e1)
+    launches = int(LIB.b2_launch_count()) - launches0
+    clocks = sampler.stop() if rank == 0 else None
+    if world > 1:
+        t = torch.tensor([ms], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    value = world * B * args.steps / (ms / 1e3)
+
+    # ---- e2e: host buffers through the pyPhantom surface, copies inside the timed region -----------
+    streams = [torch.cuda.Stream() for _ in range(3)]
+    stage = [torch.empty(3, LEVEL, N, dtype=torch.int64, device="cuda") for _ in streams]
+
+    def step_e2e():
+        for b in range(B):
+            st = streams[b % len(streams)]
+            with torch.cuda.stream(st):
+                buf = stage[b % len(streams)]
+                buf.copy_(host_ct3[b], non_blocking=True)
+                ct = ph.ciphertext()
+                ct._chain_index, ct._size, ct._N, ct._limbs, ct.data = 1, 3, N, LEVEL, buf
+                res = ph.relinearize(ctx, ct, keys[b % K])
+                host_out[b].copy_(res.data, non_blocking=True)
+        for st in streams:
+            st.synchronize()
+
+    for _ in range(2):
+        step_e2e()
+    barrier()
+    e2e_steps = max(3, min(args.steps, 10))
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        step_e2e()
+    barrier()
+    e2e_s = time.perf_counter() - t0
+    if world > 1:
+        t = torch.tensor([e2e_s], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_s = float(t.item())
+    e2e_value = world * B * e2e_steps / e2e_s
+
+    # ---- per-kernel timing (live, CUDA events on the launching stream) and roofline -------------
+    roofline, kernels = None, None
+    if rank == 0:
+        check(LIB.b2_profile_start(ctx._h))
+        prof_steps = 2
+        for _ in range(prof_steps):
+            step_resident()
+        names = ctypes.create_string_buffer(4096)
+        tot = (ctypes.c_float * 64)()
+        cnt = (ctypes.c_uint32 * 64)()
+        n_out = ctypes.c_size_t()
+        check(LIB.b2_profile_stop(ctx._h, names, 4096, tot, cnt, 64, ctypes.byref(n_out)))
+        nm = names.value.decode().strip(";").split(";")
+        alg = kernel_alg_bytes_per_keyswitch()
+        n_ks = prof_steps * B
+        total_ms = sum(tot[i] for i in range(n_out.value))
+        kernels = {}
+        for i in range(n_out.value):
+            per_ks_ms = tot[i] / n_ks
+            gbs = alg.get(nm[i], 0) / (per_ks_ms * 1e-3) / 1e9 if per_ks_ms > 0 else 0.0
+            kernels[nm[i]] = {"launches_per_keyswitch": cnt[i] / n_ks, "us_per_keyswitch": 1e3 * per_ks_ms,
+                              "share": tot[i] / total_ms, "alg_gbs": gbs}
+        top = max(kernels, key=lambda k: kernels[k]["us_per_keyswitch"])
+        peak, peak_kind = peaks()
+        traffic = None
+        tp = os.path.join(ROOT, "profiles", "ncu_traffic.json")
+        if os.path.exists(tp):
+            traffic = json.load(open(tp)).get(top, {}).get("dram_bytes_per_keyswitch")
+        roofline = {"kernel": top, "bound": "hbm", "achieved": kernels[top]["alg_gbs"], "peak": peak, "unit": "GB/s",
+                    "frac": kernels[top]["alg_gbs"] / peak, "peak_kind": peak_kind, "traffic": traffic,
+                    "alg_bytes_per_keyswitch": alg.get(top)}
+
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        cpu = cpu_baseline_sample()
+
+    if rank == 0:
+        peak, peak_kind = peaks()
+        ks_us = 1e3 * ms / (B * args.steps)
+        line = {
+            "metric": "KeySwitch/s", "value": value, "unit": "KeySwitch/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "u64", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "batch_per_step_per_gpu": B, "distinct_keys": K,
+                       "l2": "inputs larger than L2 (one step touches ~670 MB)", "parallelism": f"dp{world}"},
+            "clocks": clocks,
+            "e2e": {"value": e2e_value, "unit": "KeySwitch/s", "h2d_bytes_per_step": B * 3 * LEVEL * LIMB_BYTES,
+                    "d2h_bytes_per_step": B * 2 * LEVEL * LIMB_BYTES, "api": "pyPhantom.relinearize", "steps": e2e_steps},
+            "gpu_launches": launches,
+            "roofline": roofline,
+            "roofline_keyswitch": {"bound": "hbm", "alg_bytes": KS_BYTES, "us_per_keyswitch": ks_us,
+                                   "achieved": KS_BYTES / (ks_us * 1e-6) / 1e9 * 1.0, "peak": peak, "unit": "GB/s",
+                                   "frac": KS_BYTES / (ks_us * 1e-6) / 1e9 / peak, "peak_kind": peak_kind},
+            "kernels": kernels,
+            "cpu_baseline": cpu,
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -141,6 +141,16 @@ int b2_bsgs_mac(b2_ctx *ctx, size_t size_Ql, size_t M, const uint64_t *const *pt
 int b2_poly_op(b2_ctx *ctx, int op, size_t n_limbs, const uint64_t *d_a, const uint64_t *d_b,
                uint64_t *d_out, void *stream);
 
+/* Measurement hooks (no counterpart in the reference, which times with CUDATimer around whole
+ * calls, include/cuda_wrapper.cuh:191-283). b2_launch_count: kernels launched by this library in
+ * this process so far. b2_profile_start/stop: while on, every kernel launch is bracketed by CUDA
+ * events on its own stream; stop synchronises the device and returns, per kernel name (names
+ * joined by ';'), the summed duration in ms and the number of launches. */
+uint64_t b2_launch_count(void);
+int b2_profile_start(b2_ctx *ctx);
+int b2_profile_stop(b2_ctx *ctx, char *names, size_t names_cap, float *total_ms, uint32_t *launches,
+                    size_t cap, size_t *n_out);
+
 #ifdef __cplusplus
 }
 #endif

@@ -42,7 +42,11 @@ static int fail(int code, const std::string &msg) {
         if (e_ != cudaSuccess) return fail((int)e_, std::string(name) + ": " + cudaGetErrorString(e_)); \
     } while (0)
 
+#include <atomic>
+static std::atomic<uint64_t> g_launches{0};
+
 extern "C" const char *b2_last_error(void) { return g_err.c_str(); }
+extern "C" uint64_t b2_launch_count(void) { return g_launches.load(); }
 extern "C" int b2_version(void) { return 1; }
 
 // ------------------------------------------------------------------------------------------------
@@ -187,6 +191,34 @@ struct b2_ctx {
     std::vector<LevelPlan> plan;   // index l (1..size_Q)
     std::map<uint32_t, uint32_t *> galois;  // elt -> device gather table
     std::mutex mu;
+    // optional per-kernel timing: CUDA events recorded around every launch on the launching stream
+    bool profiling = false;
+    struct ProfRec {
+        const char *name;
+        cudaEvent_t e0, e1;
+    };
+    std::vector<ProfRec> prof;
+};
+
+// Brackets one kernel launch: counts it and, when profiling is on, records events around it.
+struct LaunchScope {
+    b2_ctx *c;
+    cudaStream_t s;
+    int idx = -1;
+    LaunchScope(const b2_ctx *ctx, cudaStream_t st, const char *name) : c(const_cast<b2_ctx *>(ctx)), s(st) {
+        g_launches.fetch_add(1, std::memory_order_relaxed);
+        if (c->profiling) {
+            b2_ctx::ProfRec r{name, nullptr, nullptr};
+            cudaEventCreate(&r.e0);
+            cudaEventCreate(&r.e1);
+            cudaEventRecord(r.e0, s);
+            c->prof.push_back(r);
+            idx = (int)c->prof.size() - 1;
+        }
+    }
+    ~LaunchScope() {
+        if (idx >= 0) cudaEventRecord(c->prof[idx].e1, s);
+    }
 };
 
 template <typename T>
@@ -466,27 +498,35 @@ static constexpr int pass_threads() {
 }
 
 template <int LOG_A, int LOG_B, class Epi>
-static void launch_fwd(const NttArgs &a, uint32_t njobs, const Epi &epi, cudaStream_t s) {
+static void launch_fwd(const b2_ctx *c, const NttArgs &a, uint32_t njobs, const Epi &epi, cudaStream_t s) {
     using A = PassCfg<LOG_A>;
     using B = PassCfg<LOG_B>;
     const uint32_t N = 1u << a.logN;
-    ntt_fwd_pass<LOG_A, A::R_STRIDED, A::R_CONTIG, A::LOG_C, true, false, EpiStore>
-        <<<njobs * (N >> (LOG_A + A::LOG_C)), pass_threads<LOG_A>(), 0, s>>>(a, EpiStore{});
+    {
+        LaunchScope ls(c, s, "ntt_fwd_cols");
+        ntt_fwd_pass<LOG_A, A::R_STRIDED, A::R_CONTIG, A::LOG_C, true, false, EpiStore>
+            <<<njobs * (N >> (LOG_A + A::LOG_C)), pass_threads<LOG_A>(), 0, s>>>(a, EpiStore{});
+    }
     NttArgs b = a;
     b.src = a.dst;  // second pass works in place on the first pass's output
+    LaunchScope ls(c, s, "ntt_fwd_rows");
     ntt_fwd_pass<LOG_B, B::R_STRIDED, B::R_CONTIG, B::LOG_C, false, true, Epi>
         <<<njobs * (N >> (LOG_B + B::LOG_C)), pass_threads<LOG_B>(), 0, s>>>(b, epi);
 }
 
 template <int LOG_A, int LOG_B>
-static void launch_inv(const NttArgs &a, uint32_t njobs, cudaStream_t s) {
+static void launch_inv(const b2_ctx *c, const NttArgs &a, uint32_t njobs, cudaStream_t s) {
     using A = PassCfg<LOG_A>;
     using B = PassCfg<LOG_B>;
     const uint32_t N = 1u << a.logN;
-    ntt_inv_pass<LOG_B, B::R_CONTIG, B::R_STRIDED, B::LOG_C, false, false>
-        <<<njobs * (N >> (LOG_B + B::LOG_C)), pass_threads<LOG_B>(), 0, s>>>(a);
+    {
+        LaunchScope ls(c, s, "ntt_inv_rows");
+        ntt_inv_pass<LOG_B, B::R_CONTIG, B::R_STRIDED, B::LOG_C, false, false>
+            <<<njobs * (N >> (LOG_B + B::LOG_C)), pass_threads<LOG_B>(), 0, s>>>(a);
+    }
     NttArgs b = a;
     b.src = a.dst;
+    LaunchScope ls(c, s, "ntt_inv_cols");
     ntt_inv_pass<LOG_A, A::R_CONTIG, A::R_STRIDED, A::LOG_C, true, true>
         <<<njobs * (N >> (LOG_A + A::LOG_C)), pass_threads<LOG_A>(), 0, s>>>(b);
 }
@@ -497,11 +537,11 @@ static int run_fwd(const b2_ctx *c, const uint64_t *src, uint64_t *dst, const Jo
     if (njobs == 0) return B2_OK;
     NttArgs a{src, dst, jobs, first_prime, (uint32_t)c->logN, c->d_tw, c->d_mod, nullptr};
     switch (c->logN) {
-        case 16: launch_fwd<8, 8>(a, njobs, epi, s); break;
-        case 15: launch_fwd<7, 8>(a, njobs, epi, s); break;
-        case 14: launch_fwd<7, 7>(a, njobs, epi, s); break;
-        case 13: launch_fwd<6, 7>(a, njobs, epi, s); break;
-        case 12: launch_fwd<6, 6>(a, njobs, epi, s); break;
+        case 16: launch_fwd<8, 8>(c, a, njobs, epi, s); break;
+        case 15: launch_fwd<7, 8>(c, a, njobs, epi, s); break;
+        case 14: launch_fwd<7, 7>(c, a, njobs, epi, s); break;
+        case 13: launch_fwd<6, 7>(c, a, njobs, epi, s); break;
+        case 12: launch_fwd<6, 6>(c, a, njobs, epi, s); break;
         default: return fail(B2_ESIZE, "unsupported polynomial degree");
     }
     LAUNCH_CHECK("ntt_fwd_pass");
@@ -513,11 +553,11 @@ static int run_inv(const b2_ctx *c, const uint64_t *src, uint64_t *dst, const Jo
     if (njobs == 0) return B2_OK;
     NttArgs a{src, dst, jobs, first_prime, (uint32_t)c->logN, c->d_itw, c->d_mod, fin};
     switch (c->logN) {
-        case 16: launch_inv<8, 8>(a, njobs, s); break;
-        case 15: launch_inv<7, 8>(a, njobs, s); break;
-        case 14: launch_inv<7, 7>(a, njobs, s); break;
-        case 13: launch_inv<6, 7>(a, njobs, s); break;
-        case 12: launch_inv<6, 6>(a, njobs, s); break;
+        case 16: launch_inv<8, 8>(c, a, njobs, s); break;
+        case 15: launch_inv<7, 8>(c, a, njobs, s); break;
+        case 14: launch_inv<7, 7>(c, a, njobs, s); break;
+        case 13: launch_inv<6, 7>(c, a, njobs, s); break;
+        case 12: launch_inv<6, 6>(c, a, njobs, s); break;
         default: return fail(B2_ESIZE, "unsupported polynomial degree");
     }
     LAUNCH_CHECK("ntt_inv_pass");
@@ -700,6 +740,7 @@ static int run_bconv(const b2_ctx *c, bool copy, const uint64_t *in, uint64_t *o
     dim3 grid(N / 2 / 128, n_groups);
     const size_t smem = (size_t)max_ni * max_out * 8;
     if (max_ni > 16) return fail(B2_ESIZE, "special_modulus_size above 16 is not built");
+    LaunchScope ls(c, s, "bconv");
     if (copy) {
         if (max_ni <= 8) bconv_kernel<8, true><<<grid, 128, smem, s>>>(in, out, copy_src, groups, outs, mats, c->d_mod, N);
         else bconv_kernel<16, true><<<grid, 128, smem, s>>>(in, out, copy_src, groups, outs, mats, c->d_mod, N);
@@ -777,6 +818,7 @@ static int inner_prod_impl(b2_ctx *c, size_t l, const uint64_t *digits, const ui
         ep.p[d] = evk[d];
     }
     const size_t pairs = lP * c->N / 2;
+    LaunchScope ls(c, s, "ks_inner_prod");
     ks_inner_prod_kernel<<<(unsigned)((pairs + 255) / 256), 256, 0, s>>>(digits, ep, out, c->d_mod, (uint32_t)c->N, (uint32_t)l, (uint32_t)lP,
                                                                       (uint32_t)c->size_Q, (uint32_t)c->size_QP, (uint32_t)beta);
     LAUNCH_CHECK("ks_inner_prod_kernel");
@@ -844,6 +886,7 @@ extern "C" int b2_tensor_mul(b2_ctx *c, size_t l, const uint64_t *d_a, const uin
     CHECK_LEVEL(c, l);
     if (!d_a || !d_b || !d_out) return fail(B2_EINVAL, "tensor_mul: null pointer");
     const size_t n = l * c->N;
+    LaunchScope ls(c, (cudaStream_t)stream, "tensor_mul");
     tensor_mul_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(d_a, d_b, d_out, c->d_mod, (uint32_t)c->N, (uint32_t)l);
     LAUNCH_CHECK("tensor_mul_kernel");
     return B2_OK;
@@ -930,6 +973,7 @@ extern "C" int b2_galois_prepare(b2_ctx *c, uint32_t elt) {
 
 static int gather_impl(b2_ctx *c, const uint32_t *perm, const uint64_t *src, uint64_t *dst, size_t n_limbs, cudaStream_t s) {
     const size_t n = n_limbs * c->N;
+    LaunchScope ls(c, s, "galois_gather");
     galois_gather_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(src, dst, perm, (uint32_t)c->N, (uint32_t)n_limbs);
     LAUNCH_CHECK("galois_gather_kernel");
     return B2_OK;
@@ -1012,6 +1056,7 @@ extern "C" int b2_bsgs_mac(b2_ctx *c, size_t l, size_t M, const uint64_t *const 
     CHECK_LEVEL(c, l);
     if (!pts || !babies || !d_out || M == 0) return fail(B2_EINVAL, "bsgs_mac: bad argument");
     const size_t n = l * c->N;
+    LaunchScope ls(c, (cudaStream_t)stream, "bsgs_mac");
     bsgs_mac_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(pts, babies, d_out, c->d_mod, (uint32_t)c->N, (uint32_t)l, (uint32_t)M);
     LAUNCH_CHECK("bsgs_mac_kernel");
     return B2_OK;
@@ -1021,7 +1066,54 @@ extern "C" int b2_poly_op(b2_ctx *c, int op, size_t n_limbs, const uint64_t *d_a
     CHECK_CTX(c);
     if (op < 0 || op > 3 || !d_a || !d_out || (op != 3 && !d_b) || n_limbs < 1 || n_limbs > c->size_QP) return fail(B2_EINVAL, "poly_op: bad argument");
     const size_t n = n_limbs * c->N;
+    LaunchScope ls(c, (cudaStream_t)stream, "poly_op");
     poly_op_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(op, d_a, d_b, d_out, c->d_mod, (uint32_t)c->N, (uint32_t)n_limbs);
     LAUNCH_CHECK("poly_op_kernel");
+    return B2_OK;
+}
+
+// ------------------------------------------------------------------------------------------------
+// per-kernel timing for the benchmark
+// ------------------------------------------------------------------------------------------------
+extern "C" int b2_profile_start(b2_ctx *c) {
+    CHECK_CTX(c);
+    for (auto &r : c->prof) {
+        cudaEventDestroy(r.e0);
+        cudaEventDestroy(r.e1);
+    }
+    c->prof.clear();
+    c->profiling = true;
+    return B2_OK;
+}
+
+extern "C" int b2_profile_stop(b2_ctx *c, char *names, size_t names_cap, float *total_ms, uint32_t *launches, size_t cap, size_t *n_out) {
+    CHECK_CTX(c);
+    if (!names || !total_ms || !launches || !n_out) return fail(B2_EINVAL, "profile_stop: null pointer");
+    c->profiling = false;
+    CUDA_TRY(cudaDeviceSynchronize());
+    std::vector<std::string> order;
+    std::map<std::string, std::pair<float, uint32_t>> agg;
+    for (auto &r : c->prof) {
+        float ms = 0;
+        cudaEventElapsedTime(&ms, r.e0, r.e1);
+        cudaEventDestroy(r.e0);
+        cudaEventDestroy(r.e1);
+        if (!agg.count(r.name)) order.push_back(r.name);
+        agg[r.name].first += ms;
+        agg[r.name].second += 1;
+    }
+    c->prof.clear();
+    std::string joined;
+    size_t n = 0;
+    for (auto &nm : order) {
+        if (n >= cap) break;
+        joined += nm + ";";
+        total_ms[n] = agg[nm].first;
+        launches[n] = agg[nm].second;
+        n++;
+    }
+    if (joined.size() + 1 > names_cap) return fail(B2_EINVAL, "profile_stop: name buffer too small");
+    memcpy(names, joined.c_str(), joined.size() + 1);
+    *n_out = n;
     return B2_OK;
 }

@@ -40,6 +40,9 @@ SIGNATURES = {
     "b2_hoist_rotations": (_int, [_vp, _sz, _vp, _vp, _sz, _vp, _sz, _vp, _vp, _sz, _vp]),
     "b2_bsgs_mac": (_int, [_vp, _sz, _sz, _vp, _vp, _vp, _vp]),
     "b2_poly_op": (_int, [_vp, _int, _sz, _vp, _vp, _vp, _vp]),
+    "b2_launch_count": (_u64, []),
+    "b2_profile_start": (_int, [_vp]),
+    "b2_profile_stop": (_int, [_vp, _vp, _sz, _vp, _vp, _sz, _vp]),
 }
 
 OP_MODUP, OP_MODDOWN, OP_KEYSWITCH, OP_RESCALE, OP_MUL_RELIN, OP_ROTATE, OP_HOIST = 1, 2, 3, 4, 5, 6, 7

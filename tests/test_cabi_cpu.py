@@ -82,3 +82,13 @@ def test_serialisation_header_layout():
     # include/ciphertext.h:173-191: four size_t, double, u64, size_t, two bools = 58 bytes
     assert ph.ciphertext._HDR.size == 58
     assert ph.plaintext._HDR.size == 32
+
+
+def test_numpy_generator_matches_the_golden_generator():
+    from pyPhantom import synth
+    from oracle_lib import Oracle
+    N = 4096
+    pr = create_coeff_modulus(N, [60, 36, 50])
+    o = Oracle(N, pr, 1)
+    assert np.array_equal(synth.poly(N, pr, 2, 7, 3), o.fill(2, pr, 7, 3))
+    assert np.array_equal(synth.fill_limbs(N, pr[:2], 9, 50), o.fill(1, pr[:2], 9, 50)[0])
