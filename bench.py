@@ -52,35 +52,45 @@ def peaks():
 
 
 class ClockSampler:
-    """samples nvidia-smi clocks and throttle reasons while the timed region runs"""
-    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+    """samples nvidia-smi clocks and throttle reasons; start() early (the tool needs about a second to
+    come up), then mark() the timed region; only samples taken inside it are summarised"""
+    Q = ("timestamp,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
          "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
          "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
     def __init__(self, gpu_index):
-        self.idx, self.lines, self.proc = gpu_index, [], None
+        self.idx, self.lines, self.proc, self.t0, self.t1 = gpu_index, [], None, None, None
 
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
-                                          "-lms", "100", "-i", str(self.idx)], stdout=subprocess.PIPE, text=True)
+                                          "-lms", "50", "-i", str(self.idx)], stdout=subprocess.PIPE, text=True)
             threading.Thread(target=self._read, daemon=True).start()
         except OSError:
             self.proc = None
 
     def _read(self):
         for line in self.proc.stdout:
-            self.lines.append(line.strip())
+            self.lines.append((time.time(), line.strip()))
+
+    def mark_begin(self):
+        self.t0 = time.time()
+
+    def mark_end(self):
+        self.t1 = time.time()
 
     def stop(self):
         if self.proc:
+            time.sleep(0.12)
             self.proc.terminate()
             try:
                 self.proc.wait(timeout=2)
             except subprocess.TimeoutExpired:
                 self.proc.kill()
+        inside = [ln for (t, ln) in self.lines if self.t0 is not None and self.t0 <= t <= self.t1 + 0.1]
+        used = inside or [ln for (_, ln) in self.lines]
         sm, mx, reasons = [], 0.0, set()
-        for ln in self.lines:
+        for ln in used:
             f = [x.strip() for x in ln.split(",")]
             if len(f) < 9:
                 continue
@@ -94,7 +104,7 @@ class ClockSampler:
                     reasons.add(name)
         sm.sort()
         return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": mx or None, "reasons": sorted(reasons),
-                "samples": len(sm)}
+                "samples": len(sm), "window": "timed region" if inside else "whole run (timed region shorter than the sampling period)"}
 
 
 def run_reference_arm(args, rank):
@@ -165,12 +175,14 @@ def kernel_alg_bytes_per_keyswitch():
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=8, help="key switches per step per GPU")
     ap.add_argument("--keys", type=int, default=4, help="distinct evaluation keys cycled over")
+    ap.add_argument("--streams", type=int, default=4, help="CUDA streams the batch of independent key switches is spread over")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer arm (used for ncu captures)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
@@ -213,15 +225,28 @@ def main():
                 for b in range(B)]
     dev_ct3 = [t.cuda() for t in host_ct3]          # resident inputs: (c0, c1, c2)
     host_out = [torch.empty(2, LEVEL, N, dtype=torch.int64).pin_memory() for _ in range(B)]
-    ws, ws_bytes = ctx.workspace(_native.OP_KEYSWITCH, LEVEL)
+    S = max(1, min(args.streams, B))
+    wss = [ctx.workspace(_native.OP_KEYSWITCH, LEVEL) for _ in range(S)]
     stream = torch.cuda.current_stream()
-    s = stream.cuda_stream
+    side = [torch.cuda.Stream() for _ in range(S)] if S > 1 else [stream]
+    fork, joins = torch.cuda.Event(), [torch.cuda.Event() for _ in range(S)]
 
     def step_resident():
-        for b in range(B):
-            t = dev_ct3[b]
-            check(LIB.b2_keyswitch(ctx._h, LEVEL, t[2].data_ptr(), key_tabs[b % K].ctypes.data, BETA, t.data_ptr(),
-                                   ws.data_ptr(), ws_bytes, s))
+        # the batch's key switches are independent: spread them over S streams (each with its own
+        # scratch) so that one ciphertext's memory phases overlap another's arithmetic
+        if S > 1:
+            fork.record(stream)
+        for i, st in enumerate(side):
+            if S > 1:
+                st.wait_event(fork)
+            ws, ws_bytes = wss[i]
+            for b in range(i, B, S):
+                t = dev_ct3[b]
+                check(LIB.b2_keyswitch(ctx._h, LEVEL, t[2].data_ptr(), key_tabs[b % K].ctypes.data, BETA, t.data_ptr(),
+                                       ws.data_ptr(), ws_bytes, st.cuda_stream))
+            if S > 1:
+                joins[i].record(st)
+                stream.wait_event(joins[i])
 
     def barrier():
         torch.cuda.synchronize()
@@ -230,12 +255,13 @@ def main():
             torch.cuda.synchronize()
 
     # ---- value: inputs resident --------------------------------------------------------------------
-    for _ in range(args.warmup):
-        step_resident()
-    barrier()
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
+    for _ in range(args.warmup):
+        step_resident()
+    barrier()
+    sampler.mark_begin()
     launches0 = int(LIB.b2_launch_count())
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record(stream)
@@ -243,6 +269,7 @@ def main():
         step_resident()
     e1.record(stream)
     barrier()
+    sampler.mark_end()
     ms = e0.elapsed_time(e1)
     launches = int(LIB.b2_launch_count()) - launches0
     clocks = sampler.stop() if rank == 0 else None
@@ -269,15 +296,15 @@ def main():
         for st in streams:
             st.synchronize()
 
-    for _ in range(2):
+    e2e_steps = 0 if args.no_e2e else max(3, min(args.steps, 10))
+    for _ in range(0 if args.no_e2e else 2):
         step_e2e()
     barrier()
-    e2e_steps = max(3, min(args.steps, 10))
     t0 = time.perf_counter()
     for _ in range(e2e_steps):
         step_e2e()
     barrier()
-    e2e_s = time.perf_counter() - t0
+    e2e_s = max(time.perf_counter() - t0, 1e-9)
     if world > 1:
         t = torch.tensor([e2e_s], device="cuda")
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -327,7 +354,7 @@ def main():
             "metric": "KeySwitch/s", "value": value, "unit": "KeySwitch/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "u64", "data": "synthetic",
-            "config": {"workload": WORKLOAD, "batch_per_step_per_gpu": B, "distinct_keys": K,
+            "config": {"workload": WORKLOAD, "batch_per_step_per_gpu": B, "distinct_keys": K, "streams": S,
                        "l2": "inputs larger than L2 (one step touches ~670 MB)", "parallelism": f"dp{world}"},
             "clocks": clocks,
             "e2e": {"value": e2e_value, "unit": "KeySwitch/s", "h2d_bytes_per_step": B * 3 * LEVEL * LIMB_BYTES,

@@ -65,6 +65,16 @@ static uint64_t h_powmod(uint64_t a, uint64_t e, uint64_t q) {
 static inline uint64_t h_invmod(uint64_t a, uint64_t q) { return h_powmod(a % q, q - 2, q); }
 static inline uint64_t h_shoup(uint64_t w, uint64_t q) { return (uint64_t)(((u128_t)w << 64) / q); }
 static inline W2 h_w2(uint64_t w, uint64_t q) { return W2{w, h_shoup(w, q)}; }
+// Transform constants as the kernels want them for this prime: {w, shoup(w)} for the integer
+// butterflies, the bit patterns of {double(w), double(w/q)} for primes on the FP64 path.
+static inline W2 h_tw_enc(uint64_t w, uint64_t q) {
+    if (q >= b2::FP_LIMIT) return h_w2(w, q);
+    const double wd = (double)w, wq = (double)w / (double)q;
+    W2 r;
+    memcpy(&r.w, &wd, 8);
+    memcpy(&r.ws, &wq, 8);
+    return r;
+}
 
 static bool h_is_prime(uint64_t v) {
     static const uint64_t wit[] = {2, 3, 5, 7, 11, 13, 17, 19, 23, 29, 31, 37};
@@ -149,7 +159,7 @@ struct BconvGroup {
     uint32_t n_out;
     uint32_t out_slot_base;  // added to every output slot
     uint32_t copy_dst_slot0; // ModUp: where the digit's own limbs are copied to
-    uint32_t pad;
+    uint32_t in_pieces;      // 21-bit pieces needed to hold an input residue (2 below 2^42, else 3)
 };
 
 struct LevelPlan {
@@ -160,6 +170,9 @@ struct LevelPlan {
     uint32_t n_up_ntt = 0;
     Job *jobs_dn_intt = nullptr;   // 2*alpha (poly-major), prefix alpha for one polynomial
     Job *jobs_dn_ntt = nullptr;    // 2*l
+    Job *jobs_dnf_intt = nullptr;  // fused key switch: P limbs live compactly in [2][alpha][N]
+    Job *jobs_dnf_ntt = nullptr;   // 2*l, epilogue subtracts from the ciphertext
+    BconvGroup *grp_dnf = nullptr; // 2
     Job *jobs_rs_intt = nullptr;   // 3 (one per polynomial)
     Job *jobs_rs_ntt = nullptr;    // 3*(l-1)
     W2 *fin_up = nullptr;          // [l][2]
@@ -167,6 +180,7 @@ struct LevelPlan {
     BconvGroup *grp_up = nullptr;  // beta
     uint2 *outs_up = nullptr;      // (slot, prime) list, beta groups concatenated
     uint64_t *mat_up = nullptr;
+    double *matd_up = nullptr;     // mat_up as 21-bit pieces of (entry * 2^64 mod p), [..][3]
     BconvGroup *grp_dn = nullptr;  // 2 (one per polynomial)
     uint2 *outs_dn = nullptr;      // l entries shared by both groups
     BconvGroup *grp_rs = nullptr;  // 3
@@ -187,7 +201,16 @@ struct b2_ctx {
     W2 *d_fin_P = nullptr;      // [size_P][2]  = the same times (P/p_i)^-1 mod p_i
     W2 *d_Pinv = nullptr;       // [size_QP] indexed by prime (valid for Q primes): P^-1 mod q_j
     uint64_t *d_mat_dn = nullptr;  // [size_Q][size_P]: (P/p_i) mod q_j
+    uint64_t *d_mat_dn_pinv = nullptr;  // the same times P^-1 mod q_j (fused key switch)
     uint64_t *d_one = nullptr;     // [size_QP] ones: the [n_out][1] "matrix" of the rescale reduction
+    double *d_matd_dn = nullptr, *d_matd_dn_pinv = nullptr, *d_matd_one = nullptr;  // FP64 piece forms
+    struct RedcMeta {
+        uint64_t p, ninv;  // ninv = -p^-1 mod 2^64
+        uint32_t pieces, pad;
+        uint64_t pad2;
+    };
+    RedcMeta *d_redc = nullptr;    // [size_QP]
+    bool bconv_fp = false;         // every digit satisfies sum(q_i) < 2^64 and alpha <= 8
     std::vector<LevelPlan> plan;   // index l (1..size_Q)
     std::map<uint32_t, uint32_t *> galois;  // elt -> device gather table
     std::mutex mu;
@@ -238,6 +261,15 @@ static uint64_t punctured(const std::vector<uint64_t> &q, size_t s, size_t e, si
     return r;
 }
 
+// 21-bit pieces (as doubles) of (m * 2^64 mod p): the operand form of the FP64 base conversion
+static inline void h_pieces(uint64_t m, uint64_t p, double *out3) {
+    const uint64_t v = (uint64_t)((((u128_t)m) << 64) % p);
+    out3[0] = (double)(v & 0x1FFFFF);
+    out3[1] = (double)((v >> 21) & 0x1FFFFF);
+    out3[2] = (double)(v >> 42);
+}
+static inline uint32_t h_npieces(uint64_t q) { return q < (1ull << 42) ? 2u : 3u; }
+
 static int build_level(b2_ctx *c, size_t l) {
     const size_t N = c->N, alpha = c->size_P, sQ = c->size_Q;
     const size_t beta = (l + alpha - 1) / alpha, lP = l + alpha;
@@ -247,14 +279,17 @@ static int build_level(b2_ctx *c, size_t l) {
     const size_t n_up_ntt = beta * lP - l;
     const size_t mat_up_words = beta * lP * alpha;
     // host staging mirrors the device blob
-    size_t bytes = 64 + sizeof(Job) * (l + n_up_ntt + 2 * alpha + 2 * l + 3 + 3 * l) + sizeof(W2) * (2 * l + c->size_QP) +
-                   sizeof(BconvGroup) * (beta + 2 + 3) + sizeof(uint2) * (n_up_ntt + l + l) + 8 * mat_up_words + 16 * 16;
+    size_t bytes = 64 + sizeof(Job) * (l + n_up_ntt + 4 * alpha + 4 * l + 3 + 3 * l) + sizeof(W2) * (2 * l + c->size_QP) +
+                   sizeof(BconvGroup) * (beta + 4 + 3) + sizeof(uint2) * (n_up_ntt + l + l) + 8 * mat_up_words * 4 + 16 * 24;
     std::vector<char> host(bytes, 0);
     char *cur = host.data();
     auto *jobs_up_intt = blob_take<Job>(cur, l);
     auto *jobs_up_ntt = blob_take<Job>(cur, n_up_ntt);
     auto *jobs_dn_intt = blob_take<Job>(cur, 2 * alpha);
     auto *jobs_dn_ntt = blob_take<Job>(cur, 2 * l);
+    auto *jobs_dnf_intt = blob_take<Job>(cur, 2 * alpha);
+    auto *jobs_dnf_ntt = blob_take<Job>(cur, 2 * l);
+    auto *grp_dnf = blob_take<BconvGroup>(cur, 2);
     auto *jobs_rs_intt = blob_take<Job>(cur, 3);
     auto *jobs_rs_ntt = blob_take<Job>(cur, 3 * l);
     auto *fin_up = blob_take<W2>(cur, 2 * l);
@@ -262,6 +297,7 @@ static int build_level(b2_ctx *c, size_t l) {
     auto *grp_up = blob_take<BconvGroup>(cur, beta);
     auto *outs_up = blob_take<uint2>(cur, n_up_ntt);
     auto *mat_up = blob_take<uint64_t>(cur, mat_up_words);
+    auto *matd_up = blob_take<double>(cur, mat_up_words * 3);
     auto *grp_dn = blob_take<BconvGroup>(cur, 2);
     auto *outs_dn = blob_take<uint2>(cur, l);
     auto *grp_rs = blob_take<BconvGroup>(cur, 3);
@@ -273,15 +309,17 @@ static int build_level(b2_ctx *c, size_t l) {
     size_t up_i = 0, mat_off = 0;
     for (size_t d = 0; d < beta; d++) {
         const size_t s = alpha * d, e = std::min(s + alpha, l), ni = e - s;
+        uint32_t in_pieces = 2;
+        for (size_t i = s; i < e; i++) in_pieces = std::max(in_pieces, h_npieces(c->q[i]));
         grp_up[d] = BconvGroup{(uint32_t)s, (uint32_t)ni, (uint32_t)mat_off, (uint32_t)up_i, (uint32_t)(lP - ni),
-                               (uint32_t)(d * lP), (uint32_t)(d * lP + s), 0};
+                               (uint32_t)(d * lP), (uint32_t)(d * lP + s), in_pieces};
         for (size_t i = s; i < e; i++) {
             const uint64_t qi = c->q[i];
             const uint64_t hatinv = h_invmod(punctured(c->q, s, e, i, qi), qi);
             // INTT's final-stage constants with (Q_d/q_i)^-1 folded in
             const uint64_t ninv = h_invmod(N % qi, qi);
-            fin_up[2 * i] = h_w2(h_mulmod(ninv, hatinv, qi), qi);
-            fin_up[2 * i + 1] = h_w2(h_mulmod(c->h_itw[i * N + 1].w, hatinv, qi), qi);
+            fin_up[2 * i] = h_tw_enc(h_mulmod(ninv, hatinv, qi), qi);
+            fin_up[2 * i + 1] = h_tw_enc(h_mulmod(c->h_itw[i * N + 1].w, hatinv, qi), qi);
             jobs_up_intt[i] = make_uint4((uint32_t)i, (uint32_t)i, (uint32_t)i, 0);
         }
         for (size_t t = 0; t < lP; t++) {
@@ -289,17 +327,28 @@ static int build_level(b2_ctx *c, size_t l) {
             const uint32_t pp = phys_prime(c, l, t);
             jobs_up_ntt[up_i] = make_uint4((uint32_t)(d * lP + t), pp, 0, 0);
             outs_up[up_i] = make_uint2((uint32_t)t, pp);
-            for (size_t i = s; i < e; i++) mat_up[mat_off++] = punctured(c->q, s, e, i, c->q[pp]);
+            for (size_t i = s; i < e; i++) {
+                mat_up[mat_off] = punctured(c->q, s, e, i, c->q[pp]);
+                h_pieces(mat_up[mat_off], c->q[pp], matd_up + 3 * mat_off);
+                mat_off++;
+            }
             up_i++;
         }
     }
     // ---- ModDown (src/rns_bconv.cu:776-828) ----
+    uint32_t p_pieces = 2;
+    for (size_t i = 0; i < alpha; i++) p_pieces = std::max(p_pieces, h_npieces(c->q[sQ + i]));
     for (size_t k = 0; k < 2; k++) {
         for (size_t i = 0; i < alpha; i++)
             jobs_dn_intt[k * alpha + i] = make_uint4((uint32_t)(k * lP + l + i), (uint32_t)(sQ + i), (uint32_t)i, 0);
         for (size_t j = 0; j < l; j++)
             jobs_dn_ntt[k * l + j] = make_uint4((uint32_t)(k * l + j), (uint32_t)j, (uint32_t)(k * lP + j), (uint32_t)(k * l + j));
-        grp_dn[k] = BconvGroup{(uint32_t)(k * lP + l), (uint32_t)alpha, 0, 0, (uint32_t)l, (uint32_t)(k * l), 0, 0};
+        grp_dn[k] = BconvGroup{(uint32_t)(k * lP + l), (uint32_t)alpha, 0, 0, (uint32_t)l, (uint32_t)(k * l), 0, p_pieces};
+        for (size_t i = 0; i < alpha; i++)
+            jobs_dnf_intt[k * alpha + i] = make_uint4((uint32_t)(k * alpha + i), (uint32_t)(sQ + i), (uint32_t)i, 0);
+        for (size_t j = 0; j < l; j++)
+            jobs_dnf_ntt[k * l + j] = make_uint4((uint32_t)(k * l + j), (uint32_t)j, 0, (uint32_t)(k * l + j));
+        grp_dnf[k] = BconvGroup{(uint32_t)(k * alpha), (uint32_t)alpha, 0, 0, (uint32_t)l, (uint32_t)(k * l), 0, p_pieces};
     }
     for (size_t j = 0; j < l; j++) outs_dn[j] = make_uint2((uint32_t)j, (uint32_t)j);
     // ---- rescale (src/rns.cu:1128-1183; constants src/rns.cu:66-95) ----
@@ -314,7 +363,7 @@ static int build_level(b2_ctx *c, size_t l) {
             for (size_t j = 0; j + 1 < l; j++)
                 jobs_rs_ntt[p * (l - 1) + j] =
                     make_uint4((uint32_t)(p * (l - 1) + j), (uint32_t)j, (uint32_t)(p * l + j), (uint32_t)(p * (l - 1) + j));
-            grp_rs[p] = BconvGroup{(uint32_t)p, 1, 0, 0, (uint32_t)(l - 1), (uint32_t)(p * (l - 1)), 0, 0};
+            grp_rs[p] = BconvGroup{(uint32_t)p, 1, 0, 0, (uint32_t)(l - 1), (uint32_t)(p * (l - 1)), 0, h_npieces(ql)};
         }
     }
     if (cudaMalloc(&pl.blob, used) != cudaSuccess) return fail(B2_ENOMEM, "cudaMalloc(level plan) failed");
@@ -326,6 +375,9 @@ static int build_level(b2_ctx *c, size_t l) {
     pl.n_up_ntt = (uint32_t)n_up_ntt;
     pl.jobs_dn_intt = (Job *)dev(jobs_dn_intt);
     pl.jobs_dn_ntt = (Job *)dev(jobs_dn_ntt);
+    pl.jobs_dnf_intt = (Job *)dev(jobs_dnf_intt);
+    pl.jobs_dnf_ntt = (Job *)dev(jobs_dnf_ntt);
+    pl.grp_dnf = (BconvGroup *)dev(grp_dnf);
     pl.jobs_rs_intt = (Job *)dev(jobs_rs_intt);
     pl.jobs_rs_ntt = (Job *)dev(jobs_rs_ntt);
     pl.fin_up = (W2 *)dev(fin_up);
@@ -333,6 +385,7 @@ static int build_level(b2_ctx *c, size_t l) {
     pl.grp_up = (BconvGroup *)dev(grp_up);
     pl.outs_up = (uint2 *)dev(outs_up);
     pl.mat_up = (uint64_t *)dev(mat_up);
+    pl.matd_up = (double *)dev(matd_up);
     pl.grp_dn = (BconvGroup *)dev(grp_dn);
     pl.outs_dn = (uint2 *)dev(outs_dn);
     pl.grp_rs = (BconvGroup *)dev(grp_rs);
@@ -350,7 +403,12 @@ extern "C" void b2_ctx_destroy(b2_ctx *c) {
     cudaFree(c->d_fin_P);
     cudaFree(c->d_Pinv);
     cudaFree(c->d_mat_dn);
+    cudaFree(c->d_mat_dn_pinv);
     cudaFree(c->d_one);
+    cudaFree(c->d_matd_dn);
+    cudaFree(c->d_matd_dn_pinv);
+    cudaFree(c->d_matd_one);
+    cudaFree(c->d_redc);
     for (auto &pl : c->plan) cudaFree(pl.blob);
     for (auto &kv : c->galois) cudaFree(kv.second);
     delete c;
@@ -423,12 +481,12 @@ extern "C" int b2_ctx_create(size_t N, const uint64_t *primes, size_t size_QP, s
     // ---- P-related constants (src/rns.cu:100-138, 192-194) ----
     const size_t sQ = c->size_Q, sP = size_P;
     std::vector<W2> fin_P(2 * sP), Pinv(size_QP, W2{0, 0});
-    std::vector<uint64_t> mat_dn(sQ * sP);
+    std::vector<uint64_t> mat_dn(sQ * sP), mat_dn_pinv(sQ * sP);
     for (size_t i = 0; i < sP; i++) {
         const uint64_t p = c->q[sQ + i];
         const uint64_t hatinv = h_invmod(punctured(c->q, sQ, size_QP, sQ + i, p), p);
-        fin_P[2 * i] = h_w2(h_mulmod(fin_plain[2 * (sQ + i)].w, hatinv, p), p);
-        fin_P[2 * i + 1] = h_w2(h_mulmod(fin_plain[2 * (sQ + i) + 1].w, hatinv, p), p);
+        fin_P[2 * i] = h_tw_enc(h_mulmod(fin_plain[2 * (sQ + i)].w, hatinv, p), p);
+        fin_P[2 * i + 1] = h_tw_enc(h_mulmod(fin_plain[2 * (sQ + i) + 1].w, hatinv, p), p);
     }
     for (size_t j = 0; j < sQ; j++) {
         const uint64_t qj = c->q[j];
@@ -438,8 +496,30 @@ extern "C" int b2_ctx_create(size_t N, const uint64_t *primes, size_t size_QP, s
             mat_dn[j * sP + i] = punctured(c->q, sQ, size_QP, sQ + i, qj);
         }
         Pinv[j] = h_w2(h_invmod(P, qj), qj);
+        for (size_t i = 0; i < sP; i++) mat_dn_pinv[j * sP + i] = h_mulmod(mat_dn[j * sP + i], Pinv[j].w, qj);
     }
     const std::vector<uint64_t> ones(size_QP, 1);
+    std::vector<double> matd_dn(3 * sQ * sP), matd_dn_pinv(3 * sQ * sP), matd_one(3 * size_QP);
+    std::vector<b2_ctx::RedcMeta> redc(size_QP);
+    for (size_t j = 0; j < sQ; j++)
+        for (size_t i = 0; i < sP; i++) {
+            h_pieces(mat_dn[j * sP + i], c->q[j], &matd_dn[3 * (j * sP + i)]);
+            h_pieces(mat_dn_pinv[j * sP + i], c->q[j], &matd_dn_pinv[3 * (j * sP + i)]);
+        }
+    for (size_t j = 0; j < size_QP; j++) {
+        h_pieces(1, c->q[j], &matd_one[3 * j]);
+        uint64_t inv = 1;  // Newton: inv = q^-1 mod 2^64
+        for (int it = 0; it < 6; it++) inv *= 2 - c->q[j] * inv;
+        redc[j] = b2_ctx::RedcMeta{c->q[j], (uint64_t)(0 - inv), h_npieces(c->q[j]), 0, 0};
+    }
+    // the FP64 base conversion needs sum_i(in_i * M_i) < p * 2^64: every digit's primes must sum
+    // below 2^64 (true for up to 8 primes of 61 bits, 16 of 60); otherwise the integer kernel runs
+    c->bconv_fp = sP <= 8;
+    for (size_t s0 = 0; s0 < size_QP && c->bconv_fp; s0 += sP) {
+        u128_t sum = 0;
+        for (size_t i = s0; i < std::min(s0 + sP, size_QP); i++) sum += c->q[i];
+        if (sum >> 64) c->bconv_fp = false;
+    }
     auto up = [&](void **dptr, const void *src, size_t bytes) -> cudaError_t {
         cudaError_t e = cudaMalloc(dptr, bytes);
         if (e != cudaSuccess) return e;
@@ -447,13 +527,32 @@ extern "C" int b2_ctx_create(size_t N, const uint64_t *primes, size_t size_QP, s
     };
     cudaError_t e = cudaSuccess;
     if (e == cudaSuccess) e = up((void **)&c->d_mod, mods.data(), sizeof(Mod) * size_QP);
-    if (e == cudaSuccess) e = up((void **)&c->d_tw, c->h_tw.data(), sizeof(W2) * size_QP * N);
-    if (e == cudaSuccess) e = up((void **)&c->d_itw, c->h_itw.data(), sizeof(W2) * size_QP * N);
-    if (e == cudaSuccess) e = up((void **)&c->d_fin_plain, fin_plain.data(), sizeof(W2) * 2 * size_QP);
+    {
+        // device copies carry the per-prime encoding (FP64 constants for small primes)
+        std::vector<W2> enc(size_QP * N);
+        for (int which = 0; which < 2; which++) {
+            const std::vector<W2> &src = which ? c->h_itw : c->h_tw;
+#pragma omp parallel for schedule(static)
+            for (size_t l = 0; l < size_QP; l++)
+                for (size_t i = 0; i < N; i++) enc[l * N + i] = h_tw_enc(src[l * N + i].w, c->q[l]);
+            if (e == cudaSuccess) e = up(which ? (void **)&c->d_itw : (void **)&c->d_tw, enc.data(), sizeof(W2) * size_QP * N);
+        }
+        std::vector<W2> fp(2 * size_QP);
+        for (size_t l = 0; l < size_QP; l++) {
+            fp[2 * l] = h_tw_enc(fin_plain[2 * l].w, c->q[l]);
+            fp[2 * l + 1] = h_tw_enc(fin_plain[2 * l + 1].w, c->q[l]);
+        }
+        if (e == cudaSuccess) e = up((void **)&c->d_fin_plain, fp.data(), sizeof(W2) * 2 * size_QP);
+    }
     if (e == cudaSuccess) e = up((void **)&c->d_fin_P, fin_P.data(), sizeof(W2) * 2 * sP);
     if (e == cudaSuccess) e = up((void **)&c->d_Pinv, Pinv.data(), sizeof(W2) * size_QP);
     if (e == cudaSuccess) e = up((void **)&c->d_mat_dn, mat_dn.data(), 8 * sQ * sP);
+    if (e == cudaSuccess) e = up((void **)&c->d_mat_dn_pinv, mat_dn_pinv.data(), 8 * sQ * sP);
     if (e == cudaSuccess) e = up((void **)&c->d_one, ones.data(), 8 * size_QP);
+    if (e == cudaSuccess) e = up((void **)&c->d_matd_dn, matd_dn.data(), 8 * matd_dn.size());
+    if (e == cudaSuccess) e = up((void **)&c->d_matd_dn_pinv, matd_dn_pinv.data(), 8 * matd_dn_pinv.size());
+    if (e == cudaSuccess) e = up((void **)&c->d_matd_one, matd_one.data(), 8 * matd_one.size());
+    if (e == cudaSuccess) e = up((void **)&c->d_redc, redc.data(), sizeof(b2_ctx::RedcMeta) * size_QP);
     if (e != cudaSuccess) {
         b2_ctx_destroy(c);
         return fail((int)e, std::string("ctx_create: table upload failed: ") + cudaGetErrorString(e));
@@ -573,14 +672,25 @@ static int run_inv(const b2_ctx *c, const uint64_t *src, uint64_t *dst, const Jo
 // all outputs, so the inputs cross HBM once and every store is a coalesced 16-byte write.
 // gridDim.y = group (digit of ModUp / polynomial of ModDown). COPY: also copies the group's own
 // limbs from `copy_src` (the NTT-form input) into the output buffer (src/rns_bconv.cu:522-528).
+struct BconvOut {
+    uint64_t q, r0, r1, slot;
+};
+
 template <int MAX_NI, bool COPY>
 __global__ void __launch_bounds__(128) bconv_kernel(const uint64_t *__restrict__ in, uint64_t *__restrict__ out,
                                                     const uint64_t *__restrict__ copy_src, const BconvGroup *groups,
                                                     const uint2 *outs, const uint64_t *mats, const Mod *mod, uint32_t N) {
-    extern __shared__ uint64_t s_mat[];
+    extern __shared__ uint64_t s_raw[];
     const BconvGroup g = groups[blockIdx.y];
+    BconvOut *s_out = reinterpret_cast<BconvOut *>(s_raw);          // [n_out]
+    uint64_t *s_mat = s_raw + 4 * (size_t)g.n_out;                  // [n_out][ni]
     const uint64_t *mat = mats + g.mat_off;
     for (uint32_t i = threadIdx.x; i < g.n_out * g.ni; i += blockDim.x) s_mat[i] = mat[i];
+    for (uint32_t j = threadIdx.x; j < g.n_out; j += blockDim.x) {
+        const uint2 o = outs[g.out_begin + j];
+        const Mod md = mod[o.y];
+        s_out[j] = BconvOut{md.q, md.r0, md.r1, (uint64_t)(g.out_slot_base + o.x)};
+    }
     __syncthreads();
     const uint32_t n = 2 * (blockIdx.x * blockDim.x + threadIdx.x);
     if (n >= N) return;
@@ -599,10 +709,8 @@ __global__ void __launch_bounds__(128) bconv_kernel(const uint64_t *__restrict__
             y0[i] = y1[i] = 0;
         }
     }
-    const uint2 *ol = outs + g.out_begin;
-    for (uint32_t j = 0; j < g.n_out; j++) {
-        const uint2 o = ol[j];
-        const Mod md = mod[o.y];
+    auto one = [&](uint32_t j) {
+        const BconvOut o = s_out[j];
         const uint64_t *m = s_mat + j * g.ni;
         u128 a0{0, 0}, a1{0, 0};
 #pragma unroll
@@ -613,10 +721,103 @@ __global__ void __launch_bounds__(128) bconv_kernel(const uint64_t *__restrict__
                 mac128(a1, y1[i], mm);
             }
         }
-        const uint64_t r0 = barrett128(a0, md.q, md.r0, md.r1);
-        const uint64_t r1 = barrett128(a1, md.q, md.r0, md.r1);
-        *reinterpret_cast<ulonglong2 *>(out + (size_t)(g.out_slot_base + o.x) * N + n) = make_ulonglong2(r0, r1);
+        *reinterpret_cast<ulonglong2 *>(out + o.slot * N + n) =
+            make_ulonglong2(barrett128(a0, o.q, o.r0, o.r1), barrett128(a1, o.q, o.r0, o.r1));
+    };
+    uint32_t j = 0;
+    for (; j + 1 < g.n_out; j += 2) {
+        one(j);
+        one(j + 1);
     }
+    if (j < g.n_out) one(j);
+}
+
+// FP64 form of the same base conversion. On B200 a 64-bit-result integer multiply issues at a quarter
+// of the FP64 FMA rate, so the products are done on 21-bit pieces held as doubles: an input residue
+// y = y0 + y1 2^21 + y2 2^42 and a matrix entry m (stored as pieces of m * 2^64 mod p) give nine
+// exact products below 2^42; five accumulators collect them by weight (sums stay below 2^48, exact),
+// are recombined into one 128-bit integer and Montgomery-reduced (the 2^-64 of the reduction cancels
+// the 2^64 folded into the matrix). The result is the same residue the integer kernel produces.
+// One coefficient per thread; the inputs live in registers, the matrix pieces in shared memory.
+struct BconvMetaS {
+    uint64_t p, ninv, slot;
+    uint32_t pieces, pad;
+};
+
+template <int INP, int OUTP>
+__device__ __forceinline__ void bconv_acc(const double (&yp)[8][3], const double *m, uint32_t ni, double (&A)[5]) {
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+        if (i < (int)ni) {
+#pragma unroll
+            for (int b = 0; b < OUTP; b++) {
+                const double mb = m[3 * i + b];
+#pragma unroll
+                for (int a = 0; a < INP; a++) A[a + b] = __fma_rn(yp[i][a], mb, A[a + b]);
+            }
+        }
+    }
+}
+
+template <int INP, bool COPY>
+__device__ __forceinline__ void bconv_fp_body(const uint64_t *__restrict__ in, uint64_t *__restrict__ out, const uint64_t *__restrict__ copy_src,
+                                              const BconvGroup &g, const BconvMetaS *s_meta, const double *s_m, uint32_t N, uint32_t n) {
+    double yp[8][3];
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+        if (i < (int)g.ni) {
+            const uint64_t y = in[(size_t)(g.in_slot0 + i) * N + n];
+            if (COPY) out[(size_t)(g.copy_dst_slot0 + i) * N + n] = copy_src[(size_t)(g.in_slot0 + i) * N + n];
+            const uint64_t magic = 0x4330000000000000ull;
+            yp[i][0] = __dsub_rn(__longlong_as_double((long long)((y & 0x1FFFFF) | magic)), 4503599627370496.0);
+            yp[i][1] = __dsub_rn(__longlong_as_double((long long)(((y >> 21) & 0x1FFFFF) | magic)), 4503599627370496.0);
+            yp[i][2] = INP == 3 ? __dsub_rn(__longlong_as_double((long long)((y >> 42) | magic)), 4503599627370496.0) : 0.0;
+        } else {
+            yp[i][0] = yp[i][1] = yp[i][2] = 0.0;
+        }
+    }
+    for (uint32_t j = 0; j < g.n_out; j++) {
+        const BconvMetaS o = s_meta[j];
+        const double *m = s_m + 3 * (size_t)j * g.ni;
+        double A[5] = {0.0, 0.0, 0.0, 0.0, 0.0};
+        if (o.pieces == 2) bconv_acc<INP, 2>(yp, m, g.ni, A);
+        else bconv_acc<INP, 3>(yp, m, g.ni, A);
+        // exact integers below 2^48 -> one 128-bit value
+        unsigned __int128 V = 0;
+#pragma unroll
+        for (int w = 4; w >= 0; w--) {
+            const uint64_t u = (uint64_t)__double_as_longlong(__dadd_rn(A[w], 4503599627370496.0)) & 0x000FFFFFFFFFFFFFull;
+            V = (V << 21) + u;
+        }
+        // Montgomery reduction: (V + m p) / 2^64 with m = V_lo * (-p^-1); V < p 2^64 so the result is < 2p
+        const uint64_t vlo = (uint64_t)V, vhi = (uint64_t)(V >> 64);
+        const uint64_t mm = vlo * o.ninv;
+        uint64_t r = vhi + __umul64hi(mm, o.p) + (vlo != 0 ? 1 : 0);
+        r = csub(r, o.p);
+        out[o.slot * N + n] = r;
+    }
+}
+
+template <bool COPY>
+__global__ void __launch_bounds__(128) bconv_fp_kernel(const uint64_t *__restrict__ in, uint64_t *__restrict__ out,
+                                                       const uint64_t *__restrict__ copy_src, const BconvGroup *groups, const uint2 *outs,
+                                                       const double *matd, const b2_ctx::RedcMeta *redc, uint32_t N) {
+    extern __shared__ uint64_t s_raw[];
+    const BconvGroup g = groups[blockIdx.y];
+    BconvMetaS *s_meta = reinterpret_cast<BconvMetaS *>(s_raw);                      // [n_out]
+    double *s_m = reinterpret_cast<double *>(s_raw + 4 * (size_t)g.n_out);           // [n_out][ni][3]
+    const double *mat = matd + 3 * (size_t)g.mat_off;
+    for (uint32_t i = threadIdx.x; i < 3 * g.n_out * g.ni; i += blockDim.x) s_m[i] = mat[i];
+    for (uint32_t j = threadIdx.x; j < g.n_out; j += blockDim.x) {
+        const uint2 o = outs[g.out_begin + j];
+        const b2_ctx::RedcMeta r = redc[o.y];
+        s_meta[j] = BconvMetaS{r.p, r.ninv, (uint64_t)(g.out_slot_base + o.x), r.pieces, 0};
+    }
+    __syncthreads();
+    const uint32_t n = blockIdx.x * blockDim.x + threadIdx.x;
+    if (n >= N) return;
+    if (g.in_pieces == 2) bconv_fp_body<2, COPY>(in, out, copy_src, g, s_meta, s_m, N, n);
+    else bconv_fp_body<3, COPY>(in, out, copy_src, g, s_meta, s_m, N, n);
 }
 
 struct EvkPtrs {
@@ -624,31 +825,62 @@ struct EvkPtrs {
 };
 
 // Key-switch inner product (src/eval_key_switch.cu:175-230): for logical limb t (physical prime pp)
-//   out[k][t][n] = (sum_d digits[d][t][n] * evk[d][k][pp][n]) mod q_pp,   k = 0, 1
-// accumulated in 128 bits and reduced once. Pure streaming: two coefficients per thread, 16-byte loads.
+//   acc[k][t][n] = (sum_d digits[d][t][n] * evk[d][k][pp][n]) mod q_pp,   k = 0, 1
+// accumulated in 128 bits and reduced once. Pure streaming: two coefficients per thread, 16-byte
+// loads, every load of a thread issued before the first multiply.
+// FUSED = false: out[k][t] = acc (the reference's cx buffer, [2][l+alpha][N]).
+// FUSED = true (whole key switch): Q limbs go straight into the ciphertext as
+//   ct[k][t] += acc * P^-1  and only the P limbs are kept, compactly, in outP [2][alpha][N];
+// together with a ModDown matrix that carries P^-1 this equals ct + (acc - delta) * P^-1.
+template <int MAX_BETA, bool FUSED>
 __global__ void __launch_bounds__(256) ks_inner_prod_kernel(const uint64_t *__restrict__ digits, EvkPtrs evk, uint64_t *__restrict__ out,
-                                                           const Mod *mod, uint32_t N, uint32_t l, uint32_t lP, uint32_t size_Q,
-                                                           uint32_t size_QP, uint32_t beta) {
+                                                           uint64_t *__restrict__ ct, const W2 *__restrict__ pinv, const Mod *mod, uint32_t N,
+                                                           uint32_t l, uint32_t lP, uint32_t size_Q, uint32_t size_QP, uint32_t beta) {
     const size_t idx = 2 * ((size_t)blockIdx.x * blockDim.x + threadIdx.x);
     if (idx >= (size_t)lP * N) return;
     const uint32_t t = (uint32_t)(idx / N), n = (uint32_t)(idx % N);
     const uint32_t pp = t < l ? t : size_Q + (t - l);
     const Mod md = mod[pp];
     u128 a00{0, 0}, a01{0, 0}, a10{0, 0}, a11{0, 0};
-    for (uint32_t d = 0; d < beta; d++) {
-        const ulonglong2 x = *reinterpret_cast<const ulonglong2 *>(digits + ((size_t)d * lP + t) * N + n);
-        const uint64_t *e = evk.p[d] + (size_t)pp * N + n;
-        const ulonglong2 e0 = __ldg(reinterpret_cast<const ulonglong2 *>(e));
-        const ulonglong2 e1 = __ldg(reinterpret_cast<const ulonglong2 *>(e + (size_t)size_QP * N));
-        mac128(a00, x.x, e0.x);
-        mac128(a01, x.y, e0.y);
-        mac128(a10, x.x, e1.x);
-        mac128(a11, x.y, e1.y);
+    for (uint32_t d0 = 0; d0 < beta; d0 += MAX_BETA) {
+        ulonglong2 x[MAX_BETA], e0[MAX_BETA], e1[MAX_BETA];
+#pragma unroll
+        for (int i = 0; i < MAX_BETA; i++) {
+            if (d0 + i < beta) {
+                x[i] = *reinterpret_cast<const ulonglong2 *>(digits + ((size_t)(d0 + i) * lP + t) * N + n);
+                const uint64_t *e = evk.p[d0 + i] + (size_t)pp * N + n;
+                e0[i] = __ldcs(reinterpret_cast<const ulonglong2 *>(e));
+                e1[i] = __ldcs(reinterpret_cast<const ulonglong2 *>(e + (size_t)size_QP * N));
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < MAX_BETA; i++) {
+            if (d0 + i < beta) {
+                mac128(a00, x[i].x, e0[i].x);
+                mac128(a01, x[i].y, e0[i].y);
+                mac128(a10, x[i].x, e1[i].x);
+                mac128(a11, x[i].y, e1[i].y);
+            }
+        }
     }
-    *reinterpret_cast<ulonglong2 *>(out + idx) =
-        make_ulonglong2(barrett128(a00, md.q, md.r0, md.r1), barrett128(a01, md.q, md.r0, md.r1));
-    *reinterpret_cast<ulonglong2 *>(out + (size_t)lP * N + idx) =
-        make_ulonglong2(barrett128(a10, md.q, md.r0, md.r1), barrett128(a11, md.q, md.r0, md.r1));
+    uint64_t r00 = barrett128(a00, md.q, md.r0, md.r1), r01 = barrett128(a01, md.q, md.r0, md.r1);
+    uint64_t r10 = barrett128(a10, md.q, md.r0, md.r1), r11 = barrett128(a11, md.q, md.r0, md.r1);
+    if (!FUSED) {
+        *reinterpret_cast<ulonglong2 *>(out + idx) = make_ulonglong2(r00, r01);
+        *reinterpret_cast<ulonglong2 *>(out + (size_t)lP * N + idx) = make_ulonglong2(r10, r11);
+    } else if (t < l) {
+        const W2 pi = pinv[pp];
+        uint64_t *c0 = ct + idx, *c1 = ct + (size_t)l * N + idx;
+        const ulonglong2 u0 = *reinterpret_cast<const ulonglong2 *>(c0), u1 = *reinterpret_cast<const ulonglong2 *>(c1);
+        *reinterpret_cast<ulonglong2 *>(c0) =
+            make_ulonglong2(add_mod(u0.x, mul_shoup(r00, pi, md.q), md.q), add_mod(u0.y, mul_shoup(r01, pi, md.q), md.q));
+        *reinterpret_cast<ulonglong2 *>(c1) =
+            make_ulonglong2(add_mod(u1.x, mul_shoup(r10, pi, md.q), md.q), add_mod(u1.y, mul_shoup(r11, pi, md.q), md.q));
+    } else {
+        const size_t alpha = lP - l, o = (size_t)(t - l) * N + n;
+        *reinterpret_cast<ulonglong2 *>(out + o) = make_ulonglong2(r00, r01);
+        *reinterpret_cast<ulonglong2 *>(out + alpha * N + o) = make_ulonglong2(r10, r11);
+    }
 }
 
 // HMult tensor product (src/polymath.cu:463-498): d0 = a0 b0, d2 = a1 b1, d1 = (a0+a1)(b0+b1) - d0 - d2
@@ -735,12 +967,22 @@ __global__ void __launch_bounds__(256) bsgs_mac_kernel(const uint64_t *const *pt
 }
 
 static int run_bconv(const b2_ctx *c, bool copy, const uint64_t *in, uint64_t *out, const uint64_t *copy_src, const BconvGroup *groups,
-                     uint32_t n_groups, const uint2 *outs, const uint64_t *mats, uint32_t max_ni, uint32_t max_out, cudaStream_t s) {
+                     uint32_t n_groups, const uint2 *outs, const uint64_t *mats, const double *matd, uint32_t max_ni, uint32_t max_out,
+                     bool in3, cudaStream_t s) {
     const uint32_t N = (uint32_t)c->N;
-    dim3 grid(N / 2 / 128, n_groups);
-    const size_t smem = (size_t)max_ni * max_out * 8;
     if (max_ni > 16) return fail(B2_ESIZE, "special_modulus_size above 16 is not built");
     LaunchScope ls(c, s, "bconv");
+    if (c->bconv_fp && matd) {
+        dim3 grid(N / 128, n_groups);
+        const size_t smem = (size_t)max_out * 32 + (size_t)max_ni * max_out * 24;
+        (void)in3;
+        if (copy) bconv_fp_kernel<true><<<grid, 128, smem, s>>>(in, out, copy_src, groups, outs, matd, c->d_redc, N);
+        else bconv_fp_kernel<false><<<grid, 128, smem, s>>>(in, out, copy_src, groups, outs, matd, c->d_redc, N);
+        LAUNCH_CHECK("bconv_fp_kernel");
+        return B2_OK;
+    }
+    dim3 grid(N / 2 / 128, n_groups);
+    const size_t smem = ((size_t)max_ni + 4) * max_out * 8;
     if (copy) {
         if (max_ni <= 8) bconv_kernel<8, true><<<grid, 128, smem, s>>>(in, out, copy_src, groups, outs, mats, c->d_mod, N);
         else bconv_kernel<16, true><<<grid, 128, smem, s>>>(in, out, copy_src, groups, outs, mats, c->d_mod, N);
@@ -795,7 +1037,7 @@ static int modup_impl(b2_ctx *c, size_t l, const uint64_t *c2, uint64_t *out, ui
     const LevelPlan &pl = c->plan[l];
     int rc = run_inv(c, c2, t, pl.jobs_up_intt, (uint32_t)l, 0, pl.fin_up, s);
     if (rc) return rc;
-    rc = run_bconv(c, true, t, out, c2, pl.grp_up, pl.beta, pl.outs_up, pl.mat_up, (uint32_t)c->size_P, (uint32_t)(l + c->size_P), s);
+    rc = run_bconv(c, true, t, out, c2, pl.grp_up, pl.beta, pl.outs_up, pl.mat_up, pl.matd_up, (uint32_t)c->size_P, (uint32_t)(l + c->size_P), true, s);
     if (rc) return rc;
     return run_fwd(c, out, out, pl.jobs_up_ntt, pl.n_up_ntt, 0, EpiStore{}, s);
 }
@@ -808,7 +1050,9 @@ extern "C" int b2_modup(b2_ctx *c, size_t l, const uint64_t *d_c2, uint64_t *d_o
     return modup_impl(c, l, d_c2, d_out, (uint64_t *)d_ws, (cudaStream_t)stream);
 }
 
-static int inner_prod_impl(b2_ctx *c, size_t l, const uint64_t *digits, const uint64_t *const *evk, size_t n_evk, uint64_t *out, cudaStream_t s) {
+// fused = false: out = cx [2][lP][N]. fused = true: Q limbs accumulate into ct, out = [2][alpha][N].
+static int inner_prod_impl(b2_ctx *c, size_t l, const uint64_t *digits, const uint64_t *const *evk, size_t n_evk, uint64_t *out, uint64_t *ct,
+                           bool fused, cudaStream_t s) {
     const size_t beta = c->plan[l].beta, lP = l + c->size_P;
     if (n_evk < beta) return fail(B2_EINVAL, "key has fewer digits than this level needs");
     if (beta > 64) return fail(B2_ESIZE, "more than 64 digits");
@@ -818,9 +1062,14 @@ static int inner_prod_impl(b2_ctx *c, size_t l, const uint64_t *digits, const ui
         ep.p[d] = evk[d];
     }
     const size_t pairs = lP * c->N / 2;
+    const unsigned grid = (unsigned)((pairs + 255) / 256);
     LaunchScope ls(c, s, "ks_inner_prod");
-    ks_inner_prod_kernel<<<(unsigned)((pairs + 255) / 256), 256, 0, s>>>(digits, ep, out, c->d_mod, (uint32_t)c->N, (uint32_t)l, (uint32_t)lP,
-                                                                      (uint32_t)c->size_Q, (uint32_t)c->size_QP, (uint32_t)beta);
+    if (fused)
+        ks_inner_prod_kernel<3, true><<<grid, 256, 0, s>>>(digits, ep, out, ct, c->d_Pinv, c->d_mod, (uint32_t)c->N, (uint32_t)l, (uint32_t)lP,
+                                                         (uint32_t)c->size_Q, (uint32_t)c->size_QP, (uint32_t)beta);
+    else
+        ks_inner_prod_kernel<3, false><<<grid, 256, 0, s>>>(digits, ep, out, nullptr, nullptr, c->d_mod, (uint32_t)c->N, (uint32_t)l, (uint32_t)lP,
+                                                          (uint32_t)c->size_Q, (uint32_t)c->size_QP, (uint32_t)beta);
     LAUNCH_CHECK("ks_inner_prod_kernel");
     return B2_OK;
 }
@@ -830,7 +1079,7 @@ extern "C" int b2_ks_inner_prod(b2_ctx *c, size_t l, const uint64_t *d_digits, c
     CHECK_CTX(c);
     CHECK_LEVEL(c, l);
     if (!d_digits || !evk || !d_out) return fail(B2_EINVAL, "ks_inner_prod: null pointer");
-    return inner_prod_impl(c, l, d_digits, evk, n_evk, d_out, (cudaStream_t)stream);
+    return inner_prod_impl(c, l, d_digits, evk, n_evk, d_out, nullptr, false, (cudaStream_t)stream);
 }
 
 // ModDown of n_poly (1 or 2) polynomials held in cx [n_poly][l+alpha][N].
@@ -841,7 +1090,7 @@ static int moddown_impl(b2_ctx *c, size_t l, size_t n_poly, uint64_t *cx, uint64
     const size_t a = c->size_P;
     int rc = run_inv(c, cx, cx, pl.jobs_dn_intt, (uint32_t)(n_poly * a), 0, c->d_fin_P, s);
     if (rc) return rc;
-    rc = run_bconv(c, false, cx, delta, nullptr, pl.grp_dn, (uint32_t)n_poly, pl.outs_dn, c->d_mat_dn, (uint32_t)a, (uint32_t)l, s);
+    rc = run_bconv(c, false, cx, delta, nullptr, pl.grp_dn, (uint32_t)n_poly, pl.outs_dn, c->d_mat_dn, c->d_matd_dn, (uint32_t)a, (uint32_t)l, true, s);
     if (rc) return rc;
     if (accum) {
         EpiSubMul<true> epi{cx, out, c->d_Pinv};
@@ -860,16 +1109,31 @@ extern "C" int b2_moddown(b2_ctx *c, size_t l, size_t n_poly, uint64_t *d_cx, ui
     return moddown_impl(c, l, n_poly, d_cx, d_out, (uint64_t *)d_ws, false, (cudaStream_t)stream);
 }
 
-// ws layout of the key switch: t [l] | up [beta][lP] | cx [2][lP]; delta reuses `up`
+// Everything after ModUp, fused: ct += ModDown(<digits, evk>).
+// The inner product adds acc * P^-1 into the Q limbs of ct and keeps only the P limbs (cxP,
+// [2][alpha][N]); their inverse transform, the base conversion with the P^-1-carrying matrix and a
+// forward transform whose epilogue subtracts from ct finish the job. `delta`: 2*l limbs of scratch.
+static int ks_tail_fused(b2_ctx *c, size_t l, const uint64_t *digits, const uint64_t *const *evk, size_t n_evk, uint64_t *ct, uint64_t *cxP,
+                         uint64_t *delta, cudaStream_t s) {
+    const LevelPlan &pl = c->plan[l];
+    const size_t a = c->size_P;
+    int rc = inner_prod_impl(c, l, digits, evk, n_evk, cxP, ct, true, s);
+    if (rc) return rc;
+    rc = run_inv(c, cxP, cxP, pl.jobs_dnf_intt, (uint32_t)(2 * a), 0, c->d_fin_P, s);
+    if (rc) return rc;
+    rc = run_bconv(c, false, cxP, delta, nullptr, pl.grp_dnf, 2, pl.outs_dn, c->d_mat_dn_pinv, c->d_matd_dn_pinv, (uint32_t)a, (uint32_t)l, true, s);
+    if (rc) return rc;
+    return run_fwd(c, delta, delta, pl.jobs_dnf_ntt, (uint32_t)(2 * l), 0, EpiSubFrom{ct}, s);
+}
+
+// ws layout of the key switch: t [l] | up [beta][lP] | cxP [2][alpha]; delta reuses `up`
 static int keyswitch_impl(b2_ctx *c, size_t l, const uint64_t *c2, const uint64_t *const *evk, size_t n_evk, uint64_t *ct, uint64_t *ws,
                           cudaStream_t s) {
     const size_t N = c->N, lP = l + c->size_P, beta = c->plan[l].beta;
-    uint64_t *t = ws, *up = t + l * N, *cx = up + beta * lP * N;
+    uint64_t *t = ws, *up = t + l * N, *cxP = up + beta * lP * N;
     int rc = modup_impl(c, l, c2, up, t, s);
     if (rc) return rc;
-    rc = inner_prod_impl(c, l, up, evk, n_evk, cx, s);
-    if (rc) return rc;
-    return moddown_impl(c, l, 2, cx, ct, up, true, s);
+    return ks_tail_fused(c, l, up, evk, n_evk, ct, cxP, up, s);
 }
 
 extern "C" int b2_keyswitch(b2_ctx *c, size_t l, const uint64_t *d_c2, const uint64_t *const *evk, size_t n_evk, uint64_t *d_ct, void *d_ws,
@@ -924,7 +1188,7 @@ extern "C" int b2_rescale(b2_ctx *c, size_t l, size_t n_poly, const uint64_t *d_
         if (rc) return rc;
     }
     // r mod q_j for every remaining prime: a base conversion with one input and the matrix [1]
-    int rc = run_bconv(c, false, r, d_out, nullptr, pl.grp_rs, (uint32_t)n_poly, pl.outs_rs, c->d_one, 1, (uint32_t)(l - 1), s);
+    int rc = run_bconv(c, false, r, d_out, nullptr, pl.grp_rs, (uint32_t)n_poly, pl.outs_rs, c->d_one, c->d_matd_one, 1, (uint32_t)(l - 1), true, s);
     if (rc) return rc;
     EpiSubMul<false> epi{d_in, d_out, pl.qlast_inv};
     return run_fwd(c, d_out, d_out, pl.jobs_rs_ntt, (uint32_t)(n_poly * (l - 1)), 0, epi, s);
@@ -1040,12 +1304,10 @@ extern "C" int b2_hoist_rotations(b2_ctx *c, size_t l, const uint64_t *d_ct, con
         if (rc) return rc;
         rc = gather_impl(c, perms[i], up, pup, beta * lP, s);  // permute AFTER ModUp (src/evaluate.cu:2041-2045)
         if (rc) return rc;
-        rc = inner_prod_impl(c, l, pup, ksk + i * n_evk, n_evk, cx, s);
-        if (rc) return rc;
         // c0_out = perm(c0) + ModDown(cx0); c1_out = ModDown(cx1)
         CUDA_TRY(cudaMemcpyAsync(d_outs[i], pc0, S * 8, cudaMemcpyDeviceToDevice, s));
         CUDA_TRY(cudaMemsetAsync(d_outs[i] + S, 0, S * 8, s));
-        rc = moddown_impl(c, l, 2, cx, d_outs[i], pup, true, s);
+        rc = ks_tail_fused(c, l, pup, ksk + i * n_evk, n_evk, d_outs[i], cx, pup, s);
         if (rc) return rc;
     }
     return B2_OK;

@@ -46,20 +46,24 @@ __device__ __forceinline__ Job get_job(const NttArgs &a, uint32_t j) {
     return make_uint4(j, a.first_prime + j, a.first_prime + j, 0);
 }
 
-// ---- epilogues of the last forward pass ------------------------------------------------------
-// Each receives canonical values and decides where they go.
+// ---- epilogues of the last forward (row) pass ---------------------------------------------------
+// The row pass leaves every thread with E consecutive canonical residues starting at limb offset o.
+// An epilogue first preloads whatever else it needs for those positions (before the butterflies, so
+// the loads are in flight while the ALUs work) and then finishes and stores them.
 struct EpiStore {
     uint64_t *dst;
+    template <int E> struct Regs {};
     __device__ __forceinline__ void init(const NttArgs &a, const Job &job, size_t N) { dst = a.dst + (size_t)job.x * N; }
-    __device__ __forceinline__ void put(size_t i, uint64_t v, uint64_t) const { dst[i] = v; }
-    __device__ __forceinline__ void put2(size_t i, uint64_t v0, uint64_t v1, uint64_t) const {
-        *reinterpret_cast<ulonglong2 *>(dst + i) = make_ulonglong2(v0, v1);
+    template <int E> __device__ __forceinline__ void preload(Regs<E> &, size_t) const {}
+    template <int E> __device__ __forceinline__ void finish(const Regs<E> &, size_t o, uint64_t (&x)[E], uint64_t) const {
+#pragma unroll
+        for (int i = 0; i < E; i += 2) *reinterpret_cast<ulonglong2 *>(dst + o + i) = make_ulonglong2(x[i], x[i + 1]);
     }
 };
 
-// out[job.w] = acc[job.w] + (minuend[job.z] - v) * k[prime]   (ModDown + add-to-ciphertext:
-// src/rns_bconv.cu:820-821 with include/ntt_radix8_tmpl.cuh:203-233, then :763-769), or without
-// the accumulate (rescale: src/rns.cu:1146-1158).
+// out[job.w] = (ACCUM ? out[job.w] : 0) + (minuend[job.z] - v) * k[prime]
+// ModDown (src/rns_bconv.cu:820-821 with include/ntt_radix8_tmpl.cuh:203-233) followed by the
+// add-to-ciphertext (:763-769) when ACCUM; rescale (src/rns.cu:1146-1158) without.
 template <bool ACCUM>
 struct EpiSubMul {
     const uint64_t *minuend;  // [slots][N]
@@ -68,91 +72,228 @@ struct EpiSubMul {
     const uint64_t *m_;
     uint64_t *o_;
     W2 kk;
+    template <int E> struct Regs {
+        ulonglong2 m[E / 2];
+        ulonglong2 acc[ACCUM ? E / 2 : 1];
+    };
     __device__ __forceinline__ void init(const NttArgs &, const Job &job, size_t N) {
         m_ = minuend + (size_t)job.z * N;
         o_ = out + (size_t)job.w * N;
         kk = k[job.y];
     }
-    __device__ __forceinline__ uint64_t one(size_t i, uint64_t v, uint64_t q) const {
-        uint64_t r = mul_shoup(sub_mod(m_[i], v, q), kk, q);
-        if (ACCUM) r = add_mod(o_[i], r, q);
-        return r;
-    }
-    __device__ __forceinline__ void put(size_t i, uint64_t v, uint64_t q) const { o_[i] = one(i, v, q); }
-    __device__ __forceinline__ void put2(size_t i, uint64_t v0, uint64_t v1, uint64_t q) const {
-        ulonglong2 m = *reinterpret_cast<const ulonglong2 *>(m_ + i);
-        uint64_t r0 = mul_shoup(sub_mod(m.x, v0, q), kk, q);
-        uint64_t r1 = mul_shoup(sub_mod(m.y, v1, q), kk, q);
-        if (ACCUM) {
-            ulonglong2 o = *reinterpret_cast<const ulonglong2 *>(o_ + i);
-            r0 = add_mod(o.x, r0, q);
-            r1 = add_mod(o.y, r1, q);
+    template <int E> __device__ __forceinline__ void preload(Regs<E> &r, size_t o) const {
+#pragma unroll
+        for (int i = 0; i < E / 2; i++) {
+            r.m[i] = *reinterpret_cast<const ulonglong2 *>(m_ + o + 2 * i);
+            if (ACCUM) r.acc[i] = *reinterpret_cast<const ulonglong2 *>(o_ + o + 2 * i);
         }
-        *reinterpret_cast<ulonglong2 *>(o_ + i) = make_ulonglong2(r0, r1);
+    }
+    template <int E> __device__ __forceinline__ void finish(const Regs<E> &r, size_t o, uint64_t (&x)[E], uint64_t q) const {
+#pragma unroll
+        for (int i = 0; i < E / 2; i++) {
+            uint64_t r0 = mul_shoup(sub_mod(r.m[i].x, x[2 * i], q), kk, q);
+            uint64_t r1 = mul_shoup(sub_mod(r.m[i].y, x[2 * i + 1], q), kk, q);
+            if (ACCUM) {
+                r0 = add_mod(r.acc[i].x, r0, q);
+                r1 = add_mod(r.acc[i].y, r1, q);
+            }
+            *reinterpret_cast<ulonglong2 *>(o_ + o + 2 * i) = make_ulonglong2(r0, r1);
+        }
+    }
+};
+
+// out[job.w] -= v  (the fused key switch: the inner-product kernel has already left
+// ct + cx * P^-1 in `out`, and the ModDown matrix carries P^-1, so only the subtraction remains)
+struct EpiSubFrom {
+    uint64_t *out;
+    uint64_t *o_;
+    template <int E> struct Regs {
+        ulonglong2 u[E / 2];
+    };
+    __device__ __forceinline__ void init(const NttArgs &, const Job &job, size_t N) { o_ = out + (size_t)job.w * N; }
+    template <int E> __device__ __forceinline__ void preload(Regs<E> &r, size_t o) const {
+#pragma unroll
+        for (int i = 0; i < E / 2; i++) r.u[i] = *reinterpret_cast<const ulonglong2 *>(o_ + o + 2 * i);
+    }
+    template <int E> __device__ __forceinline__ void finish(const Regs<E> &r, size_t o, uint64_t (&x)[E], uint64_t q) const {
+#pragma unroll
+        for (int i = 0; i < E / 2; i++)
+            *reinterpret_cast<ulonglong2 *>(o_ + o + 2 * i) =
+                make_ulonglong2(sub_mod(r.u[i].x, x[2 * i], q), sub_mod(r.u[i].y, x[2 * i + 1], q));
     }
 };
 
 template <int LOG_T, int RC>
 __device__ __forceinline__ int pad_idx(int e) { return e + (e >> RC); }
 
+// ================================================================================================
+// arithmetic policies
+// ================================================================================================
+// On B200 a 32x32->64-bit integer multiply issues at a quarter of the rate of a double-precision
+// FMA (measured: ~16 vs 64 lanes per clock per SM), and a 64-bit Shoup product needs six of them.
+// Primes below 2^41 therefore run their butterflies in FP64: residues are held as doubles with
+// exact integer values, a modular product is
+//     h = y*w,  l = fma(y,w,-h)            (h + l = y*w exactly)
+//     c = rint(y * (w/q))                  (quotient estimate, off by at most one)
+//     r = fma(-c, q, h) + l                (exact: |h - c q| < 2^53), r = y*w (mod q), |r| < q
+// and a butterfly costs 8 FP64 instructions and no integer multiply. Ranges: a forward stage grows
+// a residue by < q (|x| < 17q after 16 stages); an inverse stage doubles the bound and every pass
+// renormalises once, so products never see |y| >= 2^50. Results are converted back to canonical
+// uint64 at the end, so outputs are bit-identical to the integer path.
+// Larger primes use 64-bit Shoup/Harvey butterflies; below 2^46 without any conditional
+// subtraction (forward: < 33q after 16 stages; inverse: < 2^17 q), above with one per butterfly.
+constexpr uint64_t FP_LIMIT = 1ull << 41;
+constexpr uint64_t WIDE_LIMIT = 1ull << 46;
+constexpr double FP_MAGIC = 6755399441055744.0;  // 1.5 * 2^52: (v + M) - M = rint(v) for |v| < 2^51
+constexpr double FP_2_52 = 4503599627370496.0;
+
+template <bool WIDE>
+struct ArithInt {
+    using T = uint64_t;
+    struct K {
+        uint64_t q, q2, r1;
+        int logN;
+    };
+    __device__ __forceinline__ static K make(const Mod &md, int logN) { return K{md.q, 2 * md.q, md.r1, logN}; }
+    __device__ __forceinline__ static T from_u64(uint64_t v, const K &) { return v; }
+    __device__ __forceinline__ static T from_raw(uint64_t v) { return v; }
+    __device__ __forceinline__ static uint64_t to_raw(T v) { return v; }
+    __device__ __forceinline__ static void ct(T &a, T &b, W2 w, const K &k) {
+        if (WIDE) {
+            const uint64_t t = mul_shoup_lazy(b, w, k.q);
+            b = a + k.q2 - t;
+            a = a + t;
+        } else {
+            ct_bfly(a, b, w, k.q, k.q2);
+        }
+    }
+    // g = number of stages of the whole inverse transform already done
+    __device__ __forceinline__ static void gs(T &a, T &b, W2 w, const K &k, int g) {
+        if (WIDE) {
+            const uint64_t d = a - b + (k.q << (g + 1));
+            a = a + b;
+            b = mul_shoup_lazy(d, w, k.q);
+        } else {
+            gs_bfly(a, b, w, k.q, k.q2);
+        }
+    }
+    __device__ __forceinline__ static void gs_last(T &a, T &b, W2 sx, W2 sy, const K &k) {
+        const uint64_t s = a + b;
+        const uint64_t d = a - b + (WIDE ? (k.q << k.logN) : k.q2);
+        a = mul_shoup(s, sx, k.q);
+        b = mul_shoup(d, sy, k.q);
+    }
+    __device__ __forceinline__ static T pass_end(T v, const K &) { return v; }  // nothing to renormalise
+    __device__ __forceinline__ static uint64_t canon_fwd(T v, const K &k) {
+        return WIDE ? barrett64(v, k.q, k.r1) : csub(csub(v, k.q2), k.q);
+    }
+    __device__ __forceinline__ static uint64_t canon_inv(T v, const K &) { return v; }  // gs_last is canonical
+};
+
+struct ArithFp {
+    using T = double;
+    struct K {
+        double q, qinv;
+        int logN;
+    };
+    __device__ __forceinline__ static K make(const Mod &md, int logN) {
+        const double q = (double)md.q;
+        return K{q, 1.0 / q, logN};
+    }
+    __device__ __forceinline__ static T from_u64(uint64_t v, const K &) {
+        return __dsub_rn(__longlong_as_double((long long)(v | 0x4330000000000000ull)), FP_2_52);
+    }
+    __device__ __forceinline__ static T from_raw(uint64_t v) { return __longlong_as_double((long long)v); }
+    __device__ __forceinline__ static uint64_t to_raw(T v) { return (uint64_t)__double_as_longlong(v); }
+    // w.w / w.ws hold the bit patterns of double(w) and double(w / q)
+    __device__ __forceinline__ static T mulmod(T y, W2 w, const K &k) {
+        const double wd = __longlong_as_double((long long)w.w), wq = __longlong_as_double((long long)w.ws);
+        const double h = __dmul_rn(y, wd);
+        const double l = __fma_rn(y, wd, -h);
+        const double c = __dsub_rn(__fma_rn(y, wq, FP_MAGIC), FP_MAGIC);
+        return __dadd_rn(__fma_rn(-c, k.q, h), l);
+    }
+    __device__ __forceinline__ static T reduce(T v, const K &k) {
+        const double c = __dsub_rn(__fma_rn(v, k.qinv, FP_MAGIC), FP_MAGIC);
+        return __fma_rn(-c, k.q, v);
+    }
+    __device__ __forceinline__ static void ct(T &a, T &b, W2 w, const K &k) {
+        const double t = mulmod(b, w, k);
+        b = __dsub_rn(a, t);
+        a = __dadd_rn(a, t);
+    }
+    __device__ __forceinline__ static void gs(T &a, T &b, W2 w, const K &k, int) {
+        const double d = __dsub_rn(a, b);
+        a = __dadd_rn(a, b);
+        b = mulmod(d, w, k);
+    }
+    __device__ __forceinline__ static void gs_last(T &a, T &b, W2 sx, W2 sy, const K &k) {
+        const double s = __dadd_rn(a, b), d = __dsub_rn(a, b);
+        a = mulmod(s, sx, k);
+        b = mulmod(d, sy, k);
+    }
+    __device__ __forceinline__ static T pass_end(T v, const K &k) { return reduce(v, k); }
+    __device__ __forceinline__ static uint64_t to_canon(T v, const K &k) {  // |v| < q
+        if (v < 0.0) v = __dadd_rn(v, k.q);
+        return (uint64_t)__double_as_longlong(__dadd_rn(v, FP_2_52)) & 0x000FFFFFFFFFFFFFull;
+    }
+    __device__ __forceinline__ static uint64_t canon_fwd(T v, const K &k) { return to_canon(reduce(v, k), k); }
+    __device__ __forceinline__ static uint64_t canon_inv(T v, const K &k) { return to_canon(v, k); }
+};
 
 // ---- stage runners: compile-time recursion keeps every register index a constant --------------
-// forward: E residues x[], local stages S..R-1 of this round; twiddle index = tw0 + ((k0 << S) + g)
-// where tw0 = P << (stage offset) is folded by the caller through `shift`.
-template <int S, int R, int E>
-__device__ __forceinline__ void ct_stages(uint64_t (&x)[E], const W2 *tw, size_t P, int shift, size_t k0, uint64_t q, uint64_t q2) {
+// forward: E residues x[], local stages S..R-1 of this round; twiddle index
+// (P << (shift + S)) + (k0 << S) + g.
+template <class A, int S, int R, int E>
+__device__ __forceinline__ void ct_stages(typename A::T (&x)[E], const W2 *tw, size_t P, int shift, size_t k0, const typename A::K &k) {
     if constexpr (S < R) {
         constexpr int half = E >> (S + 1);
 #pragma unroll
         for (int g = 0; g < (1 << S); g++) {
             const W2 w = ldg_w2(tw + (P << (shift + S)) + (k0 << S) + g);
 #pragma unroll
-            for (int j = 0; j < half; j++) ct_bfly(x[g * 2 * half + j], x[g * 2 * half + j + half], w, q, q2);
+            for (int j = 0; j < half; j++) A::ct(x[g * 2 * half + j], x[g * 2 * half + j + half], w, k);
         }
-        ct_stages<S + 1, R, E>(x, tw, P, shift, k0, q, q2);
+        ct_stages<A, S + 1, R, E>(x, tw, P, shift, k0, k);
     }
 }
 
-// inverse: local stages U..R-1 (gap 2^U); twiddle index = (m0 >> U) * P + (k0 >> U) + g with
-// m0 = sub-transform size >> (1 + stages already done), k0 = first pair group of this thread at U = 0.
-template <int U, int R, int E>
-__device__ __forceinline__ void gs_stages(uint64_t (&x)[E], const W2 *tw, size_t P, int m0, size_t k0, uint64_t q, uint64_t q2) {
+// inverse: local stages U..R-1 (gap 2^U); twiddle index (m0 >> U) * P + (k0 >> U) + g with
+// m0 = sub-transform size >> (1 + stages already done), k0 = first pair group of this thread at
+// U = 0. g0 = stages of the whole transform already done.
+template <class A, int U, int R, int E>
+__device__ __forceinline__ void gs_stages(typename A::T (&x)[E], const W2 *tw, size_t P, int m0, size_t k0, int g0, const typename A::K &k) {
     if constexpr (U < R) {
         constexpr int gap = 1 << U;
 #pragma unroll
         for (int g = 0; g < (E >> (U + 1)); g++) {
             const W2 w = ldg_w2(tw + (size_t)(m0 >> U) * P + (k0 >> U) + g);
 #pragma unroll
-            for (int j = 0; j < gap; j++) gs_bfly(x[g * 2 * gap + j], x[g * 2 * gap + j + gap], w, q, q2);
+            for (int j = 0; j < gap; j++) A::gs(x[g * 2 * gap + j], x[g * 2 * gap + j + gap], w, k, g0 + U);
         }
-        gs_stages<U + 1, R, E>(x, tw, P, m0, k0, q, q2);
+        gs_stages<A, U + 1, R, E>(x, tw, P, m0, k0, g0, k);
     }
 }
 
 // ================================================================================================
 // forward pass: R1 strided stages, exchange, R2 contiguous stages
+// FIRST: the input holds canonical residues (else the raw lazy values of the previous pass)
 // ================================================================================================
-template <int LOG_T, int R1, int R2, int LOG_C, bool COLS, bool LAST, class Epi>
-__global__ void __launch_bounds__((1 << (LOG_C + LOG_T)) / (1 << (R1 > R2 ? R1 : R2)))
-ntt_fwd_pass(NttArgs a, Epi epi) {
-    static_assert(R1 + R2 == LOG_T, "stage split");
-    constexpr int T = 1 << LOG_T, E1 = 1 << R1, E2 = 1 << R2, C = 1 << LOG_C;
+template <class A, int LOG_T, int R1, int R2, int LOG_C, bool COLS, bool LAST, class Epi>
+__device__ __forceinline__ void fwd_body(const NttArgs &a, const Epi &epi, uint64_t *sm, const Job &job, const Mod &md, uint32_t tile) {
+    using T = typename A::T;
+    constexpr bool FIRST = COLS;
+    constexpr int TT = 1 << LOG_T, E1 = 1 << R1, E2 = 1 << R2, C = 1 << LOG_C;
     constexpr int EPT = E1 > E2 ? E1 : E2;
-    constexpr int THREADS = C * T / EPT;
-    constexpr int TPAD = T + (T >> R2);
-    __shared__ uint64_t sm[C * TPAD];
-
+    constexpr int THREADS = C * TT / EPT;
+    constexpr int TPAD = TT + (TT >> R2);
     const size_t N = (size_t)1 << a.logN;
-    const uint32_t tiles = (uint32_t)(N >> (LOG_T + LOG_C));
-    const uint32_t jobi = blockIdx.x / tiles, tile = blockIdx.x % tiles;
-    const Job job = get_job(a, jobi);
-    const Mod md = a.mod[job.y];
-    const uint64_t q = md.q, q2 = 2 * md.q;
+    const typename A::K k = A::make(md, (int)a.logN);
     const W2 *tw = a.tw + (size_t)job.y * N;
     const uint64_t *src = a.src + (size_t)job.x * N;
     const size_t estride = COLS ? (N >> LOG_T) : 1;
-    const size_t cstride = COLS ? 1 : T;
-    const size_t base = COLS ? (size_t)tile * C : (size_t)tile * C * T;
+    const size_t cstride = COLS ? 1 : TT;
+    const size_t base = COLS ? (size_t)tile * C : (size_t)tile * C * TT;
     const uint32_t n1 = (uint32_t)(N >> LOG_T);  // number of sub-transforms per limb
     const int tid = threadIdx.x;
 
@@ -163,15 +304,18 @@ ntt_fwd_pass(NttArgs a, Epi epi) {
         const int c = COLS ? (gid % C) : (gid / E2);
         const int elo = COLS ? (gid / C) : (gid % E2);
         const uint32_t P = COLS ? 1u : (n1 + tile * C + c);
-        uint64_t x[E1];
+        T x[E1];
         const uint64_t *p = src + base + (size_t)c * cstride + (size_t)elo * estride;
 #pragma unroll
-        for (int i = 0; i < E1; i++) x[i] = p[(size_t)i * E2 * estride];
-        ct_stages<0, R1, E1>(x, tw, P, 0, 0, q, q2);
+        for (int i = 0; i < E1; i++) {
+            const uint64_t v = p[(size_t)i * E2 * estride];
+            x[i] = FIRST ? A::from_u64(v, k) : A::from_raw(v);
+        }
+        ct_stages<A, 0, R1, E1>(x, tw, P, 0, 0, k);
 #pragma unroll
         for (int i = 0; i < E1; i++) {
             const int pe = pad_idx<LOG_T, R2>(elo + i * E2);
-            sm[COLS ? (pe * C + c) : (c * TPAD + pe)] = x[i];
+            sm[COLS ? (pe * C + c) : (c * TPAD + pe)] = A::to_raw(x[i]);
         }
     }
     __syncthreads();
@@ -185,58 +329,67 @@ ntt_fwd_pass(NttArgs a, Epi epi) {
         const int c = COLS ? (gid % C) : (gid / E1);
         const int ehi = COLS ? (gid / C) : (gid % E1);
         const uint32_t P = COLS ? 1u : (n1 + tile * C + c);
-        uint64_t x[E2];
+        const size_t o = base + (size_t)c * cstride + (size_t)ehi * E2 * estride;
+        typename Epi::template Regs<E2> regs;
+        if (LAST) e.template preload<E2>(regs, o);
+        T x[E2];
 #pragma unroll
         for (int i = 0; i < E2; i++) {
             const int pe = pad_idx<LOG_T, R2>(ehi * E2 + i);
-            x[i] = sm[COLS ? (pe * C + c) : (c * TPAD + pe)];
+            x[i] = A::from_raw(sm[COLS ? (pe * C + c) : (c * TPAD + pe)]);
         }
-        ct_stages<0, R2, E2>(x, tw, P, R1, ehi, q, q2);
-        const size_t o = base + (size_t)c * cstride + (size_t)ehi * E2 * estride;
+        ct_stages<A, 0, R2, E2>(x, tw, P, R1, ehi, k);
         if (LAST) {
+            static_assert(!LAST || !COLS, "the last forward pass is the row pass");
+            uint64_t y[E2];
 #pragma unroll
-            for (int i = 0; i < E2; i++) x[i] = csub(csub(x[i], q2), q);
-            if (COLS) {
-#pragma unroll
-                for (int i = 0; i < E2; i++) e.put(o + (size_t)i * estride, x[i], q);
-            } else {
-#pragma unroll
-                for (int i = 0; i < E2; i += 2) e.put2(o + i, x[i], x[i + 1], q);
-            }
+            for (int i = 0; i < E2; i++) y[i] = A::canon_fwd(x[i], k);
+            e.template finish<E2>(regs, o, y, md.q);
         } else {
 #pragma unroll
-            for (int i = 0; i < E2; i++) dst[o + (size_t)i * estride] = x[i];
+            for (int i = 0; i < E2; i++) dst[o + (size_t)i * estride] = A::to_raw(x[i]);
         }
     }
+}
+
+template <int LOG_T, int R1, int R2, int LOG_C, bool COLS, bool LAST, class Epi>
+__global__ void __launch_bounds__((1 << (LOG_C + LOG_T)) / (1 << (R1 > R2 ? R1 : R2)))
+ntt_fwd_pass(NttArgs a, Epi epi) {
+    static_assert(R1 + R2 == LOG_T, "stage split");
+    constexpr int TT = 1 << LOG_T, C = 1 << LOG_C;
+    __shared__ uint64_t sm[C * (TT + (TT >> R2))];
+    const uint32_t tiles = (uint32_t)(((size_t)1 << a.logN) >> (LOG_T + LOG_C));
+    const uint32_t jobi = blockIdx.x / tiles, tile = blockIdx.x % tiles;
+    const Job job = get_job(a, jobi);
+    const Mod md = a.mod[job.y];
+    if (md.q < FP_LIMIT) fwd_body<ArithFp, LOG_T, R1, R2, LOG_C, COLS, LAST, Epi>(a, epi, sm, job, md, tile);
+    else if (md.q < WIDE_LIMIT) fwd_body<ArithInt<true>, LOG_T, R1, R2, LOG_C, COLS, LAST, Epi>(a, epi, sm, job, md, tile);
+    else fwd_body<ArithInt<false>, LOG_T, R1, R2, LOG_C, COLS, LAST, Epi>(a, epi, sm, job, md, tile);
 }
 
 // ================================================================================================
 // inverse pass: RA contiguous stages, exchange, RB strided stages
 // ================================================================================================
-template <int LOG_T, int RA, int RB, int LOG_C, bool COLS, bool LAST>
-__global__ void __launch_bounds__((1 << (LOG_C + LOG_T)) / (1 << (RA > RB ? RA : RB)))
-ntt_inv_pass(NttArgs a) {
-    static_assert(RA + RB == LOG_T, "stage split");
-    constexpr int T = 1 << LOG_T, EA = 1 << RA, EB = 1 << RB, C = 1 << LOG_C;
+template <class A, int LOG_T, int RA, int RB, int LOG_C, bool COLS, bool LAST>
+__device__ __forceinline__ void inv_body(const NttArgs &a, uint64_t *sm, const Job &job, const Mod &md, uint32_t tile) {
+    using T = typename A::T;
+    constexpr bool FIRST = !COLS;
+    constexpr int TT = 1 << LOG_T, EA = 1 << RA, EB = 1 << RB, C = 1 << LOG_C;
     constexpr int EPT = EA > EB ? EA : EB;
-    constexpr int THREADS = C * T / EPT;
-    constexpr int TPAD = T + (T >> RA);
-    __shared__ uint64_t sm[C * TPAD];
-
+    constexpr int THREADS = C * TT / EPT;
+    constexpr int TPAD = TT + (TT >> RA);
     const size_t N = (size_t)1 << a.logN;
-    const uint32_t tiles = (uint32_t)(N >> (LOG_T + LOG_C));
-    const uint32_t jobi = blockIdx.x / tiles, tile = blockIdx.x % tiles;
-    const Job job = get_job(a, jobi);
-    const Mod md = a.mod[job.y];
-    const uint64_t q = md.q, q2 = 2 * md.q;
+    const typename A::K k = A::make(md, (int)a.logN);
     const W2 *tw = a.tw + (size_t)job.y * N;
     const uint64_t *src = a.src + (size_t)job.x * N;
     uint64_t *dst = a.dst + (size_t)job.x * N;
     const size_t estride = COLS ? (N >> LOG_T) : 1;
-    const size_t cstride = COLS ? 1 : T;
-    const size_t base = COLS ? (size_t)tile * C : (size_t)tile * C * T;
+    const size_t cstride = COLS ? 1 : TT;
+    const size_t base = COLS ? (size_t)tile * C : (size_t)tile * C * TT;
     const uint32_t n1 = (uint32_t)(N >> LOG_T);
     const int tid = threadIdx.x;
+    // stages of the whole transform done before this pass: the row pass comes first
+    const int g_pass = COLS ? ((int)a.logN - LOG_T) : 0;
 
     // ---- round 1: contiguous runs of EA residues ----------------------------------------------
 #pragma unroll
@@ -245,24 +398,27 @@ ntt_inv_pass(NttArgs a) {
         const int c = COLS ? (gid % C) : (gid / EB);
         const int ehi = COLS ? (gid / C) : (gid % EB);
         const uint32_t P = COLS ? 1u : (n1 + tile * C + c);
-        uint64_t x[EA];
+        T x[EA];
         const uint64_t *p = src + base + (size_t)c * cstride + (size_t)ehi * EA * estride;
         if (COLS) {
 #pragma unroll
-            for (int i = 0; i < EA; i++) x[i] = p[(size_t)i * estride];
+            for (int i = 0; i < EA; i++) {
+                const uint64_t v = p[(size_t)i * estride];
+                x[i] = FIRST ? A::from_u64(v, k) : A::from_raw(v);
+            }
         } else {
 #pragma unroll
             for (int i = 0; i < EA; i += 2) {
                 ulonglong2 v = *reinterpret_cast<const ulonglong2 *>(p + i);
-                x[i] = v.x;
-                x[i + 1] = v.y;
+                x[i] = FIRST ? A::from_u64(v.x, k) : A::from_raw(v.x);
+                x[i + 1] = FIRST ? A::from_u64(v.y, k) : A::from_raw(v.y);
             }
         }
-        gs_stages<0, RA, EA>(x, tw, P, T >> 1, (size_t)ehi * (EA >> 1), q, q2);
+        gs_stages<A, 0, RA, EA>(x, tw, P, TT >> 1, (size_t)ehi * (EA >> 1), g_pass, k);
 #pragma unroll
         for (int i = 0; i < EA; i++) {
             const int pe = pad_idx<LOG_T, RA>(ehi * EA + i);
-            sm[COLS ? (pe * C + c) : (c * TPAD + pe)] = x[i];
+            sm[COLS ? (pe * C + c) : (c * TPAD + pe)] = A::to_raw(x[i]);
         }
     }
     __syncthreads();
@@ -273,13 +429,14 @@ ntt_inv_pass(NttArgs a) {
         const int c = COLS ? (gid % C) : (gid / EA);
         const int elo = COLS ? (gid / C) : (gid % EA);
         const uint32_t P = COLS ? 1u : (n1 + tile * C + c);
-        uint64_t x[EB];
+        T x[EB];
 #pragma unroll
         for (int i = 0; i < EB; i++) {
             const int pe = pad_idx<LOG_T, RA>(elo + i * EA);
-            x[i] = sm[COLS ? (pe * C + c) : (c * TPAD + pe)];
+            x[i] = A::from_raw(sm[COLS ? (pe * C + c) : (c * TPAD + pe)]);
         }
-        gs_stages<0, (LAST ? RB - 1 : RB), EB>(x, tw, P, T >> (RA + 1), 0, q, q2);
+        gs_stages<A, 0, (LAST ? RB - 1 : RB), EB>(x, tw, P, TT >> (RA + 1), 0, g_pass + RA, k);
+        uint64_t *o = dst + base + (size_t)c * cstride + (size_t)elo * estride;
         if (LAST) {
             // last stage of the whole transform (twiddle index 1): the x outputs take the scale,
             // the y outputs a twiddle that already carries it (src/host/ntt.cu:53-55,
@@ -288,17 +445,29 @@ ntt_inv_pass(NttArgs a) {
             const W2 sx = ldg_w2(a.fin + 2 * (size_t)job.z);
             const W2 sy = ldg_w2(a.fin + 2 * (size_t)job.z + 1);
 #pragma unroll
-            for (int j = 0; j < gap; j++) {
-                const uint64_t sm_ = x[j] + x[j + gap];
-                const uint64_t df_ = x[j] - x[j + gap] + q2;
-                x[j] = mul_shoup(sm_, sx, q);
-                x[j + gap] = mul_shoup(df_, sy, q);
-            }
-        }
-        uint64_t *o = dst + base + (size_t)c * cstride + (size_t)elo * estride;
+            for (int j = 0; j < gap; j++) A::gs_last(x[j], x[j + gap], sx, sy, k);
 #pragma unroll
-        for (int i = 0; i < EB; i++) o[(size_t)i * EA * estride] = x[i];
+            for (int i = 0; i < EB; i++) o[(size_t)i * EA * estride] = A::canon_inv(x[i], k);
+        } else {
+#pragma unroll
+            for (int i = 0; i < EB; i++) o[(size_t)i * EA * estride] = A::to_raw(A::pass_end(x[i], k));
+        }
     }
+}
+
+template <int LOG_T, int RA, int RB, int LOG_C, bool COLS, bool LAST>
+__global__ void __launch_bounds__((1 << (LOG_C + LOG_T)) / (1 << (RA > RB ? RA : RB)))
+ntt_inv_pass(NttArgs a) {
+    static_assert(RA + RB == LOG_T, "stage split");
+    constexpr int TT = 1 << LOG_T, C = 1 << LOG_C;
+    __shared__ uint64_t sm[C * (TT + (TT >> RA))];
+    const uint32_t tiles = (uint32_t)(((size_t)1 << a.logN) >> (LOG_T + LOG_C));
+    const uint32_t jobi = blockIdx.x / tiles, tile = blockIdx.x % tiles;
+    const Job job = get_job(a, jobi);
+    const Mod md = a.mod[job.y];
+    if (md.q < FP_LIMIT) inv_body<ArithFp, LOG_T, RA, RB, LOG_C, COLS, LAST>(a, sm, job, md, tile);
+    else if (md.q < WIDE_LIMIT) inv_body<ArithInt<true>, LOG_T, RA, RB, LOG_C, COLS, LAST>(a, sm, job, md, tile);
+    else inv_body<ArithInt<false>, LOG_T, RA, RB, LOG_C, COLS, LAST>(a, sm, job, md, tile);
 }
 
 }  // namespace b2
