@@ -163,6 +163,8 @@ def kernel_alg_bytes_per_keyswitch():
     l, a, b, lP = LEVEL, SPECIAL, BETA, LEVEL + SPECIAL
     up_ntt = b * lP - l
     return {
+        "ntt_inv_cluster": 2 * (l + 2 * a) * LIMB_BYTES,
+        "ntt_fwd_cluster": 2 * (up_ntt + 2 * l) * LIMB_BYTES,
         "ntt_inv_rows": (l + 2 * a) * LIMB_BYTES,
         "ntt_inv_cols": (l + 2 * a) * LIMB_BYTES,
         "ntt_fwd_cols": (up_ntt + 2 * l) * LIMB_BYTES,

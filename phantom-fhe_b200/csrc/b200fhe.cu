@@ -211,6 +211,7 @@ struct b2_ctx {
     };
     RedcMeta *d_redc = nullptr;    // [size_QP]
     bool bconv_fp = false;         // every digit satisfies sum(q_i) < 2^64 and alpha <= 8
+    bool use_cluster = false;      // N = 2^16: single-launch transforms on 8-CTA clusters
     std::vector<LevelPlan> plan;   // index l (1..size_Q)
     std::map<uint32_t, uint32_t *> galois;  // elt -> device gather table
     std::mutex mu;
@@ -533,8 +534,15 @@ extern "C" int b2_ctx_create(size_t N, const uint64_t *primes, size_t size_QP, s
         for (int which = 0; which < 2; which++) {
             const std::vector<W2> &src = which ? c->h_itw : c->h_tw;
 #pragma omp parallel for schedule(static)
-            for (size_t l = 0; l < size_QP; l++)
-                for (size_t i = 0; i < N; i++) enc[l * N + i] = h_tw_enc(src[l * N + i].w, c->q[l]);
+            for (size_t l = 0; l < size_QP; l++) {
+                if (c->q[l] < b2::FP_LIMIT) {  // FP64 primes: one double per entry in the front half
+                    double *dd = reinterpret_cast<double *>(&enc[l * N]);
+                    for (size_t i = 0; i < N; i++) dd[i] = (double)src[l * N + i].w;
+                    for (size_t i = N; i < 2 * N; i++) dd[i] = 0.0;
+                } else {
+                    for (size_t i = 0; i < N; i++) enc[l * N + i] = src[l * N + i];
+                }
+            }
             if (e == cudaSuccess) e = up(which ? (void **)&c->d_itw : (void **)&c->d_tw, enc.data(), sizeof(W2) * size_QP * N);
         }
         std::vector<W2> fp(2 * size_QP);
@@ -557,6 +565,11 @@ extern "C" int b2_ctx_create(size_t N, const uint64_t *primes, size_t size_QP, s
         b2_ctx_destroy(c);
         return fail((int)e, std::string("ctx_create: table upload failed: ") + cudaGetErrorString(e));
     }
+    // B2_NTT_CLUSTER=1 selects the single-launch cluster transforms at N = 2^16. They are bit-exact
+    // but measured slower than the two-launch transforms on B200 (register pressure, two CTAs per
+    // SM), so they stay opt-in.
+    const char *env_cl = getenv("B2_NTT_CLUSTER");
+    c->use_cluster = (c->logN == 16) && env_cl && env_cl[0] == '1';
     c->plan.resize(sQ + 1);
     for (size_t l = 1; l <= sQ; l++) {
         int rc = build_level(c, l);
@@ -635,6 +648,17 @@ static int run_fwd(const b2_ctx *c, const uint64_t *src, uint64_t *dst, const Jo
                    const Epi &epi, cudaStream_t s) {
     if (njobs == 0) return B2_OK;
     NttArgs a{src, dst, jobs, first_prime, (uint32_t)c->logN, c->d_tw, c->d_mod, nullptr};
+    if (c->use_cluster) {
+        static thread_local bool attr_set = false;  // per instantiation (one per epilogue type) and thread
+        if (!attr_set) {
+            CUDA_TRY(cudaFuncSetAttribute(ntt_fwd_cluster<Epi>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)CL_SMEM));
+            attr_set = true;
+        }
+        LaunchScope ls(c, s, "ntt_fwd_cluster");
+        ntt_fwd_cluster<Epi><<<njobs * CL_SIZE, CL_THREADS, CL_SMEM, s>>>(a, epi);
+        LAUNCH_CHECK("ntt_fwd_cluster");
+        return B2_OK;
+    }
     switch (c->logN) {
         case 16: launch_fwd<8, 8>(c, a, njobs, epi, s); break;
         case 15: launch_fwd<7, 8>(c, a, njobs, epi, s); break;
@@ -651,6 +675,17 @@ static int run_inv(const b2_ctx *c, const uint64_t *src, uint64_t *dst, const Jo
                    const W2 *fin, cudaStream_t s) {
     if (njobs == 0) return B2_OK;
     NttArgs a{src, dst, jobs, first_prime, (uint32_t)c->logN, c->d_itw, c->d_mod, fin};
+    if (c->use_cluster) {
+        static thread_local bool attr_set = false;
+        if (!attr_set) {
+            CUDA_TRY(cudaFuncSetAttribute(ntt_inv_cluster, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)CL_SMEM));
+            attr_set = true;
+        }
+        LaunchScope ls(c, s, "ntt_inv_cluster");
+        ntt_inv_cluster<<<njobs * CL_SIZE, CL_THREADS, CL_SMEM, s>>>(a);
+        LAUNCH_CHECK("ntt_inv_cluster");
+        return B2_OK;
+    }
     switch (c->logN) {
         case 16: launch_inv<8, 8>(c, a, njobs, s); break;
         case 15: launch_inv<7, 8>(c, a, njobs, s); break;
@@ -833,21 +868,26 @@ struct EvkPtrs {
 //   ct[k][t] += acc * P^-1  and only the P limbs are kept, compactly, in outP [2][alpha][N];
 // together with a ModDown matrix that carries P^-1 this equals ct + (acc - delta) * P^-1.
 template <int MAX_BETA, bool FUSED>
-__global__ void __launch_bounds__(256) ks_inner_prod_kernel(const uint64_t *__restrict__ digits, EvkPtrs evk, uint64_t *__restrict__ out,
-                                                           uint64_t *__restrict__ ct, const W2 *__restrict__ pinv, const Mod *mod, uint32_t N,
-                                                           uint32_t l, uint32_t lP, uint32_t size_Q, uint32_t size_QP, uint32_t beta) {
+__global__ void __launch_bounds__(256) ks_inner_prod_kernel(const uint64_t *__restrict__ digits, const uint64_t *__restrict__ own,
+                                                           EvkPtrs evk, uint64_t *__restrict__ out, uint64_t *__restrict__ ct,
+                                                           const W2 *__restrict__ pinv, const Mod *mod, uint32_t N, uint32_t l, uint32_t lP,
+                                                           uint32_t size_Q, uint32_t size_QP, uint32_t beta) {
     const size_t idx = 2 * ((size_t)blockIdx.x * blockDim.x + threadIdx.x);
     if (idx >= (size_t)lP * N) return;
     const uint32_t t = (uint32_t)(idx / N), n = (uint32_t)(idx % N);
     const uint32_t pp = t < l ? t : size_Q + (t - l);
     const Mod md = mod[pp];
+    // `own` (optional): the NTT-form input of ModUp; limb t of digit t / alpha is that input itself
+    // (src/rns_bconv.cu:522-528), so the digit buffer need not hold a copy of it
+    const uint32_t own_d = (own && t < l) ? t / (lP - l) : 0xFFFFFFFFu;
     u128 a00{0, 0}, a01{0, 0}, a10{0, 0}, a11{0, 0};
     for (uint32_t d0 = 0; d0 < beta; d0 += MAX_BETA) {
         ulonglong2 x[MAX_BETA], e0[MAX_BETA], e1[MAX_BETA];
 #pragma unroll
         for (int i = 0; i < MAX_BETA; i++) {
             if (d0 + i < beta) {
-                x[i] = *reinterpret_cast<const ulonglong2 *>(digits + ((size_t)(d0 + i) * lP + t) * N + n);
+                x[i] = (d0 + i == own_d) ? *reinterpret_cast<const ulonglong2 *>(own + (size_t)t * N + n)
+                                         : *reinterpret_cast<const ulonglong2 *>(digits + ((size_t)(d0 + i) * lP + t) * N + n);
                 const uint64_t *e = evk.p[d0 + i] + (size_t)pp * N + n;
                 e0[i] = __ldcs(reinterpret_cast<const ulonglong2 *>(e));
                 e1[i] = __ldcs(reinterpret_cast<const ulonglong2 *>(e + (size_t)size_QP * N));
@@ -1033,11 +1073,11 @@ extern "C" int b2_ntt_inverse(b2_ctx *c, uint64_t *d, size_t n_limbs, size_t fir
 }
 
 // ModUp into `out`; `t` = l limbs of scratch for the scaled coefficient form
-static int modup_impl(b2_ctx *c, size_t l, const uint64_t *c2, uint64_t *out, uint64_t *t, cudaStream_t s) {
+static int modup_impl(b2_ctx *c, size_t l, const uint64_t *c2, uint64_t *out, uint64_t *t, bool copy_own, cudaStream_t s) {
     const LevelPlan &pl = c->plan[l];
     int rc = run_inv(c, c2, t, pl.jobs_up_intt, (uint32_t)l, 0, pl.fin_up, s);
     if (rc) return rc;
-    rc = run_bconv(c, true, t, out, c2, pl.grp_up, pl.beta, pl.outs_up, pl.mat_up, pl.matd_up, (uint32_t)c->size_P, (uint32_t)(l + c->size_P), true, s);
+    rc = run_bconv(c, copy_own, t, out, c2, pl.grp_up, pl.beta, pl.outs_up, pl.mat_up, pl.matd_up, (uint32_t)c->size_P, (uint32_t)(l + c->size_P), true, s);
     if (rc) return rc;
     return run_fwd(c, out, out, pl.jobs_up_ntt, pl.n_up_ntt, 0, EpiStore{}, s);
 }
@@ -1047,12 +1087,12 @@ extern "C" int b2_modup(b2_ctx *c, size_t l, const uint64_t *d_c2, uint64_t *d_o
     CHECK_LEVEL(c, l);
     if (!d_c2 || !d_out || !d_ws) return fail(B2_EINVAL, "modup: null pointer");
     if (ws_bytes < b2_workspace_bytes(c, B2_OP_MODUP, l)) return fail(B2_EWS, "modup: workspace too small");
-    return modup_impl(c, l, d_c2, d_out, (uint64_t *)d_ws, (cudaStream_t)stream);
+    return modup_impl(c, l, d_c2, d_out, (uint64_t *)d_ws, true, (cudaStream_t)stream);
 }
 
 // fused = false: out = cx [2][lP][N]. fused = true: Q limbs accumulate into ct, out = [2][alpha][N].
-static int inner_prod_impl(b2_ctx *c, size_t l, const uint64_t *digits, const uint64_t *const *evk, size_t n_evk, uint64_t *out, uint64_t *ct,
-                           bool fused, cudaStream_t s) {
+static int inner_prod_impl(b2_ctx *c, size_t l, const uint64_t *digits, const uint64_t *own, const uint64_t *const *evk, size_t n_evk,
+                           uint64_t *out, uint64_t *ct, bool fused, cudaStream_t s) {
     const size_t beta = c->plan[l].beta, lP = l + c->size_P;
     if (n_evk < beta) return fail(B2_EINVAL, "key has fewer digits than this level needs");
     if (beta > 64) return fail(B2_ESIZE, "more than 64 digits");
@@ -1065,10 +1105,10 @@ static int inner_prod_impl(b2_ctx *c, size_t l, const uint64_t *digits, const ui
     const unsigned grid = (unsigned)((pairs + 255) / 256);
     LaunchScope ls(c, s, "ks_inner_prod");
     if (fused)
-        ks_inner_prod_kernel<3, true><<<grid, 256, 0, s>>>(digits, ep, out, ct, c->d_Pinv, c->d_mod, (uint32_t)c->N, (uint32_t)l, (uint32_t)lP,
+        ks_inner_prod_kernel<3, true><<<grid, 256, 0, s>>>(digits, own, ep, out, ct, c->d_Pinv, c->d_mod, (uint32_t)c->N, (uint32_t)l, (uint32_t)lP,
                                                          (uint32_t)c->size_Q, (uint32_t)c->size_QP, (uint32_t)beta);
     else
-        ks_inner_prod_kernel<3, false><<<grid, 256, 0, s>>>(digits, ep, out, nullptr, nullptr, c->d_mod, (uint32_t)c->N, (uint32_t)l, (uint32_t)lP,
+        ks_inner_prod_kernel<3, false><<<grid, 256, 0, s>>>(digits, own, ep, out, nullptr, nullptr, c->d_mod, (uint32_t)c->N, (uint32_t)l, (uint32_t)lP,
                                                           (uint32_t)c->size_Q, (uint32_t)c->size_QP, (uint32_t)beta);
     LAUNCH_CHECK("ks_inner_prod_kernel");
     return B2_OK;
@@ -1079,7 +1119,7 @@ extern "C" int b2_ks_inner_prod(b2_ctx *c, size_t l, const uint64_t *d_digits, c
     CHECK_CTX(c);
     CHECK_LEVEL(c, l);
     if (!d_digits || !evk || !d_out) return fail(B2_EINVAL, "ks_inner_prod: null pointer");
-    return inner_prod_impl(c, l, d_digits, evk, n_evk, d_out, nullptr, false, (cudaStream_t)stream);
+    return inner_prod_impl(c, l, d_digits, nullptr, evk, n_evk, d_out, nullptr, false, (cudaStream_t)stream);
 }
 
 // ModDown of n_poly (1 or 2) polynomials held in cx [n_poly][l+alpha][N].
@@ -1113,11 +1153,11 @@ extern "C" int b2_moddown(b2_ctx *c, size_t l, size_t n_poly, uint64_t *d_cx, ui
 // The inner product adds acc * P^-1 into the Q limbs of ct and keeps only the P limbs (cxP,
 // [2][alpha][N]); their inverse transform, the base conversion with the P^-1-carrying matrix and a
 // forward transform whose epilogue subtracts from ct finish the job. `delta`: 2*l limbs of scratch.
-static int ks_tail_fused(b2_ctx *c, size_t l, const uint64_t *digits, const uint64_t *const *evk, size_t n_evk, uint64_t *ct, uint64_t *cxP,
-                         uint64_t *delta, cudaStream_t s) {
+static int ks_tail_fused(b2_ctx *c, size_t l, const uint64_t *digits, const uint64_t *own, const uint64_t *const *evk, size_t n_evk, uint64_t *ct,
+                         uint64_t *cxP, uint64_t *delta, cudaStream_t s) {
     const LevelPlan &pl = c->plan[l];
     const size_t a = c->size_P;
-    int rc = inner_prod_impl(c, l, digits, evk, n_evk, cxP, ct, true, s);
+    int rc = inner_prod_impl(c, l, digits, own, evk, n_evk, cxP, ct, true, s);
     if (rc) return rc;
     rc = run_inv(c, cxP, cxP, pl.jobs_dnf_intt, (uint32_t)(2 * a), 0, c->d_fin_P, s);
     if (rc) return rc;
@@ -1131,9 +1171,9 @@ static int keyswitch_impl(b2_ctx *c, size_t l, const uint64_t *c2, const uint64_
                           cudaStream_t s) {
     const size_t N = c->N, lP = l + c->size_P, beta = c->plan[l].beta;
     uint64_t *t = ws, *up = t + l * N, *cxP = up + beta * lP * N;
-    int rc = modup_impl(c, l, c2, up, t, s);
+    int rc = modup_impl(c, l, c2, up, t, false, s);  // the inner product reads the own limbs from c2
     if (rc) return rc;
-    return ks_tail_fused(c, l, up, evk, n_evk, ct, cxP, up, s);
+    return ks_tail_fused(c, l, up, c2, evk, n_evk, ct, cxP, up, s);
 }
 
 extern "C" int b2_keyswitch(b2_ctx *c, size_t l, const uint64_t *d_c2, const uint64_t *const *evk, size_t n_evk, uint64_t *d_ct, void *d_ws,
@@ -1296,7 +1336,7 @@ extern "C" int b2_hoist_rotations(b2_ctx *c, size_t l, const uint64_t *d_ct, con
     }
     // ws: t [l] | up [beta][lP] | pup [beta][lP] | cx [2][lP] | pc0 [l]
     uint64_t *t = (uint64_t *)d_ws, *up = t + S, *pup = up + beta * lP * N, *cx = pup + beta * lP * N, *pc0 = cx + 2 * lP * N;
-    int rc = modup_impl(c, l, d_ct + S, up, t, s);  // ModUp(c1) once (src/evaluate.cu:2013-2014)
+    int rc = modup_impl(c, l, d_ct + S, up, t, true, s);  // ModUp(c1) once (src/evaluate.cu:2013-2014)
     if (rc) return rc;
     for (size_t i = 0; i < n_steps; i++) {
         if (!d_outs[i]) return fail(B2_EINVAL, "hoist_rotations: null output");
@@ -1307,7 +1347,7 @@ extern "C" int b2_hoist_rotations(b2_ctx *c, size_t l, const uint64_t *d_ct, con
         // c0_out = perm(c0) + ModDown(cx0); c1_out = ModDown(cx1)
         CUDA_TRY(cudaMemcpyAsync(d_outs[i], pc0, S * 8, cudaMemcpyDeviceToDevice, s));
         CUDA_TRY(cudaMemsetAsync(d_outs[i] + S, 0, S * 8, s));
-        rc = ks_tail_fused(c, l, pup, ksk + i * n_evk, n_evk, d_outs[i], cx, pup, s);
+        rc = ks_tail_fused(c, l, pup, nullptr, ksk + i * n_evk, n_evk, d_outs[i], cx, pup, s);
         if (rc) return rc;
     }
     return B2_OK;

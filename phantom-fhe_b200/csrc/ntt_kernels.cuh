@@ -150,11 +150,14 @@ constexpr double FP_2_52 = 4503599627370496.0;
 template <bool WIDE>
 struct ArithInt {
     using T = uint64_t;
+    using Tw = W2;
     struct K {
         uint64_t q, q2, r1;
         int logN;
     };
     __device__ __forceinline__ static K make(const Mod &md, int logN) { return K{md.q, 2 * md.q, md.r1, logN}; }
+    __device__ __forceinline__ static Tw ldtw(const W2 *tw, size_t idx, const K &) { return ldg_w2(tw + idx); }
+    __device__ __forceinline__ static Tw ldfin(const W2 *p, const K &) { return ldg_w2(p); }
     __device__ __forceinline__ static T from_u64(uint64_t v, const K &) { return v; }
     __device__ __forceinline__ static T from_raw(uint64_t v) { return v; }
     __device__ __forceinline__ static uint64_t to_raw(T v) { return v; }
@@ -192,10 +195,23 @@ struct ArithInt {
 
 struct ArithFp {
     using T = double;
+    struct Tw {
+        double w, wq;  // w and w / q
+    };
     struct K {
         double q, qinv;
         int logN;
     };
+    // table entry i of an FP64 prime is one double (8 bytes); w / q is rebuilt as w * (1/q), whose
+    // relative error of 2^-52 is far inside the slack of the quotient estimate
+    __device__ __forceinline__ static Tw ldtw(const W2 *tw, size_t idx, const K &k) {
+        const double w = __ldg(reinterpret_cast<const double *>(tw) + idx);
+        return Tw{w, __dmul_rn(w, k.qinv)};
+    }
+    __device__ __forceinline__ static Tw ldfin(const W2 *p, const K &) {
+        const W2 v = ldg_w2(p);
+        return Tw{__longlong_as_double((long long)v.w), __longlong_as_double((long long)v.ws)};
+    }
     __device__ __forceinline__ static K make(const Mod &md, int logN) {
         const double q = (double)md.q;
         return K{q, 1.0 / q, logN};
@@ -205,9 +221,8 @@ struct ArithFp {
     }
     __device__ __forceinline__ static T from_raw(uint64_t v) { return __longlong_as_double((long long)v); }
     __device__ __forceinline__ static uint64_t to_raw(T v) { return (uint64_t)__double_as_longlong(v); }
-    // w.w / w.ws hold the bit patterns of double(w) and double(w / q)
-    __device__ __forceinline__ static T mulmod(T y, W2 w, const K &k) {
-        const double wd = __longlong_as_double((long long)w.w), wq = __longlong_as_double((long long)w.ws);
+    __device__ __forceinline__ static T mulmod(T y, Tw w, const K &k) {
+        const double wd = w.w, wq = w.wq;
         const double h = __dmul_rn(y, wd);
         const double l = __fma_rn(y, wd, -h);
         const double c = __dsub_rn(__fma_rn(y, wq, FP_MAGIC), FP_MAGIC);
@@ -217,17 +232,17 @@ struct ArithFp {
         const double c = __dsub_rn(__fma_rn(v, k.qinv, FP_MAGIC), FP_MAGIC);
         return __fma_rn(-c, k.q, v);
     }
-    __device__ __forceinline__ static void ct(T &a, T &b, W2 w, const K &k) {
+    __device__ __forceinline__ static void ct(T &a, T &b, Tw w, const K &k) {
         const double t = mulmod(b, w, k);
         b = __dsub_rn(a, t);
         a = __dadd_rn(a, t);
     }
-    __device__ __forceinline__ static void gs(T &a, T &b, W2 w, const K &k, int) {
+    __device__ __forceinline__ static void gs(T &a, T &b, Tw w, const K &k, int) {
         const double d = __dsub_rn(a, b);
         a = __dadd_rn(a, b);
         b = mulmod(d, w, k);
     }
-    __device__ __forceinline__ static void gs_last(T &a, T &b, W2 sx, W2 sy, const K &k) {
+    __device__ __forceinline__ static void gs_last(T &a, T &b, Tw sx, Tw sy, const K &k) {
         const double s = __dadd_rn(a, b), d = __dsub_rn(a, b);
         a = mulmod(s, sx, k);
         b = mulmod(d, sy, k);
@@ -250,7 +265,7 @@ __device__ __forceinline__ void ct_stages(typename A::T (&x)[E], const W2 *tw, s
         constexpr int half = E >> (S + 1);
 #pragma unroll
         for (int g = 0; g < (1 << S); g++) {
-            const W2 w = ldg_w2(tw + (P << (shift + S)) + (k0 << S) + g);
+            const typename A::Tw w = A::ldtw(tw, (P << (shift + S)) + (k0 << S) + g, k);
 #pragma unroll
             for (int j = 0; j < half; j++) A::ct(x[g * 2 * half + j], x[g * 2 * half + j + half], w, k);
         }
@@ -267,7 +282,7 @@ __device__ __forceinline__ void gs_stages(typename A::T (&x)[E], const W2 *tw, s
         constexpr int gap = 1 << U;
 #pragma unroll
         for (int g = 0; g < (E >> (U + 1)); g++) {
-            const W2 w = ldg_w2(tw + (size_t)(m0 >> U) * P + (k0 >> U) + g);
+            const typename A::Tw w = A::ldtw(tw, (size_t)(m0 >> U) * P + (k0 >> U) + g, k);
 #pragma unroll
             for (int j = 0; j < gap; j++) A::gs(x[g * 2 * gap + j], x[g * 2 * gap + j + gap], w, k, g0 + U);
         }
@@ -442,8 +457,8 @@ __device__ __forceinline__ void inv_body(const NttArgs &a, uint64_t *sm, const J
             // the y outputs a twiddle that already carries it (src/host/ntt.cu:53-55,
             // include/ntt_radix8_tmpl.cuh:566-568); callers fold further per-limb factors in.
             constexpr int gap = EB / 2;
-            const W2 sx = ldg_w2(a.fin + 2 * (size_t)job.z);
-            const W2 sy = ldg_w2(a.fin + 2 * (size_t)job.z + 1);
+            const typename A::Tw sx = A::ldfin(a.fin + 2 * (size_t)job.z, k);
+            const typename A::Tw sy = A::ldfin(a.fin + 2 * (size_t)job.z + 1, k);
 #pragma unroll
             for (int j = 0; j < gap; j++) A::gs_last(x[j], x[j + gap], sx, sy, k);
 #pragma unroll
@@ -468,6 +483,201 @@ ntt_inv_pass(NttArgs a) {
     if (md.q < FP_LIMIT) inv_body<ArithFp, LOG_T, RA, RB, LOG_C, COLS, LAST>(a, sm, job, md, tile);
     else if (md.q < WIDE_LIMIT) inv_body<ArithInt<true>, LOG_T, RA, RB, LOG_C, COLS, LAST>(a, sm, job, md, tile);
     else inv_body<ArithInt<false>, LOG_T, RA, RB, LOG_C, COLS, LAST>(a, sm, job, md, tile);
+}
+
+}  // namespace b2
+
+// ================================================================================================
+// single-launch transforms for N = 2^16 on a thread-block cluster
+// ================================================================================================
+// A cluster of 8 CTAs owns one limb (256 x 256 residues, 512 KiB). The two passes exchange through
+// distributed shared memory instead of global memory: every CTA keeps a 256 x 32 (forward: its
+// column block after the column pass) or 32 x 256 (inverse: its row block after the row pass)
+// slab of 64 KiB in shared memory, the cluster synchronises with the hardware cluster barrier, and
+// the second pass gathers its inputs from the eight slabs. A limb therefore crosses global memory
+// once in and once out. No flag or spin wait is involved: cluster.sync() is the only rendezvous
+// and every thread of every CTA reaches it unconditionally.
+#include <cooperative_groups.h>
+
+namespace b2 {
+namespace cg = cooperative_groups;
+
+constexpr int CL_SIZE = 8;        // CTAs per cluster
+constexpr int CL_THREADS = 256;   // two tile groups of 128 threads
+constexpr int CL_SLAB = 256 * 32; // residues per slab
+constexpr int CL_EX = 8 * (256 + 16);
+constexpr size_t CL_SMEM = (size_t)(CL_SLAB + 2 * CL_EX) * 8;
+
+// slab indexing with a rotation of the 8-column groups by (row >> 4): rows 16 apart fall into
+// different bank groups, which is what the two access patterns below need
+__device__ __forceinline__ int slab_fwd(int row, int col32) { return row * 32 + ((col32 + 8 * (row >> 4)) & 31); }
+__device__ __forceinline__ int slab_inv(int row32, int col) { return row32 * 256 + (col ^ (8 * ((row32 >> 4) & 1))); }
+
+template <class A, class Epi>
+__device__ __forceinline__ void fwd_cluster_body(const NttArgs &a, const Epi &epi, uint64_t *smem, const Job &job, const Mod &md) {
+    using T = typename A::T;
+    constexpr int LOG_T = 8, R1 = 4, R2 = 4, E = 16, C = 8, TPAD = 256 + 16;
+    cg::cluster_group cluster = cg::this_cluster();
+    const int rank = (int)cluster.block_rank();
+    const size_t N = 65536;
+    const typename A::K k = A::make(md, 16);
+    const W2 *tw = a.tw + (size_t)job.y * N;
+    const uint64_t *src = a.src + (size_t)job.x * N;
+    uint64_t *slab = smem;
+    const int tg = threadIdx.x >> 7, t = threadIdx.x & 127;
+    uint64_t *ex = smem + CL_SLAB + tg * CL_EX;
+
+    // ---- column pass on this CTA's 32 columns: 4 tiles of 8, two at a time -------------------
+#pragma unroll 1
+    for (int it = 0; it < 2; it++) {
+        const int ti = it * 2 + tg;
+        const int c = t % C, e_lo = t / C;
+        T x[E];
+        const uint64_t *p = src + (size_t)e_lo * 256 + rank * 32 + ti * 8 + c;
+#pragma unroll
+        for (int i = 0; i < E; i++) x[i] = A::from_u64(p[(size_t)i * 16 * 256], k);
+        ct_stages<A, 0, R1, E>(x, tw, 1, 0, 0, k);
+#pragma unroll
+        for (int i = 0; i < E; i++) ex[pad_idx<LOG_T, R2>(e_lo + i * 16) * C + c] = A::to_raw(x[i]);
+        __syncthreads();
+        const int e_hi = t / C;
+#pragma unroll
+        for (int i = 0; i < E; i++) x[i] = A::from_raw(ex[pad_idx<LOG_T, R2>(e_hi * 16 + i) * C + c]);
+        ct_stages<A, 0, R2, E>(x, tw, 1, R1, e_hi, k);
+#pragma unroll
+        for (int i = 0; i < E; i++) slab[slab_fwd(e_hi * 16 + i, ti * 8 + c)] = A::to_raw(x[i]);
+        __syncthreads();
+    }
+    cluster.sync();
+    // ---- row pass on this CTA's 32 rows, inputs gathered from the eight slabs -------------------
+    Epi e = epi;
+    e.init(a, job, N);
+    (void)TPAD;
+#pragma unroll 1
+    for (int it = 0; it < 2; it++) {
+        const int ti = it * 2 + tg;
+        const int ch = t / 16, e_lo = t % 16;
+        const int row = rank * 32 + ti * 8 + ch;
+        const uint32_t P = 256u + (uint32_t)row;
+        T x[E];
+#pragma unroll
+        for (int i = 0; i < E; i++) {
+            const int col = e_lo + 16 * i;
+            const uint64_t *peer = cluster.map_shared_rank(slab, col >> 5);
+            x[i] = A::from_raw(peer[slab_fwd(row, col & 31)]);
+        }
+        ct_stages<A, 0, R1, E>(x, tw, P, 0, 0, k);
+#pragma unroll
+        for (int i = 0; i < E; i++) ex[ch * TPAD + pad_idx<LOG_T, R2>(e_lo + i * 16)] = A::to_raw(x[i]);
+        __syncthreads();
+        const int e_hi = t % 16;
+        const size_t o = (size_t)row * 256 + (size_t)e_hi * 16;
+        typename Epi::template Regs<E> regs;
+        e.template preload<E>(regs, o);
+#pragma unroll
+        for (int i = 0; i < E; i++) x[i] = A::from_raw(ex[ch * TPAD + pad_idx<LOG_T, R2>(e_hi * 16 + i)]);
+        ct_stages<A, 0, R2, E>(x, tw, P, R1, e_hi, k);
+        uint64_t y[E];
+#pragma unroll
+        for (int i = 0; i < E; i++) y[i] = A::canon_fwd(x[i], k);
+        e.template finish<E>(regs, o, y, md.q);
+        __syncthreads();
+    }
+    cluster.sync();  // nobody leaves while a peer may still read its slab
+}
+
+template <class Epi>
+__global__ void __cluster_dims__(CL_SIZE, 1, 1) __launch_bounds__(CL_THREADS, 2) ntt_fwd_cluster(NttArgs a, Epi epi) {
+    extern __shared__ __align__(16) uint64_t cl_smem[];
+    const Job job = get_job(a, blockIdx.x / CL_SIZE);
+    const Mod md = a.mod[job.y];
+    if (md.q < FP_LIMIT) fwd_cluster_body<ArithFp, Epi>(a, epi, cl_smem, job, md);
+    else if (md.q < WIDE_LIMIT) fwd_cluster_body<ArithInt<true>, Epi>(a, epi, cl_smem, job, md);
+    else fwd_cluster_body<ArithInt<false>, Epi>(a, epi, cl_smem, job, md);
+}
+
+template <class A>
+__device__ __forceinline__ void inv_cluster_body(const NttArgs &a, uint64_t *smem, const Job &job, const Mod &md) {
+    using T = typename A::T;
+    constexpr int LOG_T = 8, RA = 4, RB = 4, E = 16, C = 8, TPAD = 256 + 16;
+    cg::cluster_group cluster = cg::this_cluster();
+    const int rank = (int)cluster.block_rank();
+    const size_t N = 65536;
+    const typename A::K k = A::make(md, 16);
+    const W2 *tw = a.tw + (size_t)job.y * N;
+    const uint64_t *src = a.src + (size_t)job.x * N;
+    uint64_t *dst = a.dst + (size_t)job.x * N;
+    uint64_t *slab = smem;
+    const int tg = threadIdx.x >> 7, t = threadIdx.x & 127;
+    uint64_t *ex = smem + CL_SLAB + tg * CL_EX;
+
+    // ---- row pass on this CTA's 32 rows (bit-reversed input, contiguous) ------------------------
+#pragma unroll 1
+    for (int it = 0; it < 2; it++) {
+        const int ti = it * 2 + tg;
+        const int ch = t / 16, e_hi = t % 16;
+        const int row32 = ti * 8 + ch;
+        const uint32_t P = 256u + (uint32_t)(rank * 32 + row32);
+        T x[E];
+        const uint64_t *p = src + (size_t)(rank * 32 + row32) * 256 + (size_t)e_hi * 16;
+#pragma unroll
+        for (int i = 0; i < E; i += 2) {
+            const ulonglong2 v = *reinterpret_cast<const ulonglong2 *>(p + i);
+            x[i] = A::from_u64(v.x, k);
+            x[i + 1] = A::from_u64(v.y, k);
+        }
+        gs_stages<A, 0, RA, E>(x, tw, P, 128, (size_t)e_hi * 8, 0, k);
+#pragma unroll
+        for (int i = 0; i < E; i++) ex[ch * TPAD + pad_idx<LOG_T, RA>(e_hi * 16 + i)] = A::to_raw(x[i]);
+        __syncthreads();
+        const int e_lo = t % 16;
+#pragma unroll
+        for (int i = 0; i < E; i++) x[i] = A::from_raw(ex[ch * TPAD + pad_idx<LOG_T, RA>(e_lo + i * 16)]);
+        gs_stages<A, 0, RB, E>(x, tw, P, 128 >> RA, 0, RA, k);
+#pragma unroll
+        for (int i = 0; i < E; i++) slab[slab_inv(row32, e_lo + 16 * i)] = A::to_raw(A::pass_end(x[i], k));
+        __syncthreads();
+    }
+    cluster.sync();
+    // ---- column pass on this CTA's 32 columns, inputs gathered from the eight slabs ----------------
+#pragma unroll 1
+    for (int it = 0; it < 2; it++) {
+        const int ti = it * 2 + tg;
+        const int c = t % C, e_hi = t / C;
+        const int col = rank * 32 + ti * 8 + c;
+        T x[E];
+        {
+            const uint64_t *peer = cluster.map_shared_rank(slab, e_hi >> 1);
+#pragma unroll
+            for (int i = 0; i < E; i++) x[i] = A::from_raw(peer[slab_inv((e_hi & 1) * 16 + i, col)]);
+        }
+        gs_stages<A, 0, RA, E>(x, tw, 1, 128, (size_t)e_hi * 8, 8, k);
+#pragma unroll
+        for (int i = 0; i < E; i++) ex[pad_idx<LOG_T, RA>(e_hi * 16 + i) * C + c] = A::to_raw(x[i]);
+        __syncthreads();
+        const int e_lo = t / C;
+#pragma unroll
+        for (int i = 0; i < E; i++) x[i] = A::from_raw(ex[pad_idx<LOG_T, RA>(e_lo + i * 16) * C + c]);
+        gs_stages<A, 0, RB - 1, E>(x, tw, 1, 128 >> RA, 0, 8 + RA, k);
+        const typename A::Tw sx = A::ldfin(a.fin + 2 * (size_t)job.z, k);
+        const typename A::Tw sy = A::ldfin(a.fin + 2 * (size_t)job.z + 1, k);
+#pragma unroll
+        for (int j = 0; j < E / 2; j++) A::gs_last(x[j], x[j + E / 2], sx, sy, k);
+        uint64_t *o = dst + (size_t)e_lo * 256 + col;
+#pragma unroll
+        for (int i = 0; i < E; i++) o[(size_t)i * 16 * 256] = A::canon_inv(x[i], k);
+        __syncthreads();
+    }
+    cluster.sync();
+}
+
+__global__ void __cluster_dims__(CL_SIZE, 1, 1) __launch_bounds__(CL_THREADS, 2) ntt_inv_cluster(NttArgs a) {
+    extern __shared__ __align__(16) uint64_t cl_smem[];
+    const Job job = get_job(a, blockIdx.x / CL_SIZE);
+    const Mod md = a.mod[job.y];
+    if (md.q < FP_LIMIT) inv_cluster_body<ArithFp>(a, cl_smem, job, md);
+    else if (md.q < WIDE_LIMIT) inv_cluster_body<ArithInt<true>>(a, cl_smem, job, md);
+    else inv_cluster_body<ArithInt<false>>(a, cl_smem, job, md);
 }
 
 }  // namespace b2

@@ -261,3 +261,26 @@ def test_full_size_properties():
     fxh = host(fx)
     for i in range(32):
         assert int(fxh[i].max()) < int(o.primes[i])
+
+
+def test_cluster_transforms_opt_in(monkeypatch):
+    """the single-launch cluster transforms (opt-in) give the same limbs as the reference"""
+    import json
+    monkeypatch.setenv("B2_NTT_CLUSTER", "1")
+    path = [p for p in GOLDEN if p.endswith("n16_l5_a8.json")][0]
+    case, ctx, o = load_case(path)
+    N, l, seed, h = o.N, case["level"], case["seed"], ctx._h
+    x = o.fill(1, o.primes, seed, 50)[0]
+    d = dev(x)
+    check(LIB.b2_ntt_forward(h, d.data_ptr(), o.size_QP, 0, stream()))
+    assert hashes(d, N) == case["hashes"]["ntt_fwd"]
+    d = dev(x)
+    check(LIB.b2_ntt_inverse(h, d.data_ptr(), o.size_QP, 0, stream()))
+    assert hashes(d, N) == case["hashes"]["ntt_inv"]
+    beta = o.beta(l)
+    kt, kp = key_dev(o.synth_key(beta, seed, 10))
+    c2 = dev(o.fill(1, o.primes[:l], seed, 3)[0])
+    ct = dev(o.synth_ct(l, seed, 1))
+    ws, nb = _ws(ctx, _native.OP_KEYSWITCH, l)
+    check(LIB.b2_keyswitch(h, l, c2.data_ptr(), kp.ctypes.data, beta, ct.data_ptr(), ws.data_ptr(), nb, stream()))
+    assert hashes(ct, N) == case["hashes"]["keyswitch"]
