@@ -109,6 +109,20 @@ int b2_multiply_and_relin(b2_ctx *ctx, size_t size_Ql, const uint64_t *d_a, cons
 int b2_rescale(b2_ctx *ctx, size_t size_Ql, size_t n_poly, const uint64_t *d_in, uint64_t *d_out,
                void *d_ws, size_t ws_bytes, void *stream);
 
+/* No counterpart in the reference (which takes every scratch buffer from cudaMallocAsync).
+ * Same result as b2_rescale, for callers that cannot supply scratch and must not allocate: a
+ * process whose device memory is already fully reserved by another allocator, or a thread that
+ * may not enter an allocating CUDA call at that point. The scratch is a 1.5 MiB array inside the
+ * library image (3 polynomials x 65536 coefficients, held by every GPU that loads the library);
+ * larger requests return B2_ESIZE. The entry point calls no cudaMalloc/cudaFree and no
+ * allocating library routine. The first call on a device looks up the array's device address
+ * (cudaGetSymbolAddress with that device current); make that first call at set-up, before any
+ * stream capture. All calls share the one array and it keeps the previous call's contents (every
+ * word read is written first, so nothing needs clearing): two calls that overlap on the GPU -
+ * different streams, or different contexts on one device - race on it; serialise them. */
+int b2_rescale_static(b2_ctx *ctx, size_t size_Ql, size_t n_poly, const uint64_t *d_in,
+                      uint64_t *d_out, void *stream);
+
 /* replaces get_elt_from_step (include/galois.cuh:16-49); returns 0 when the step is out of range */
 uint32_t b2_galois_elt_from_step(int step, size_t N);
 /* replaces PhantomGaloisTool's table construction (include/galois.cuh:98-113): makes the

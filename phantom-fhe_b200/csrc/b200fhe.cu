@@ -1234,6 +1234,64 @@ extern "C" int b2_rescale(b2_ctx *c, size_t l, size_t n_poly, const uint64_t *d_
     return run_fwd(c, d_out, d_out, pl.jobs_rs_ntt, (uint32_t)(n_poly * (l - 1)), 0, epi, s);
 }
 
+// ------------------------------------------------------------------------------------------------
+// rescale without any caller-provided or allocated scratch
+// ------------------------------------------------------------------------------------------------
+// Some callers can hand over inputs and outputs but no scratch buffer and must not allocate one:
+// a process whose device memory has been reserved up front by another allocator (so a late
+// cudaMalloc fails), or a host thread that is not allowed to enter an allocating CUDA call at
+// that point. For them the coefficient-form copies of the dropped limbs live in a fixed array
+// that is part of the library image: B2_STATIC_RESCALE_MAX_POLY polynomials of at most
+// B2_STATIC_RESCALE_MAX_N coefficients, 1.5 MiB, held by every GPU that loads the library until
+// the process exits.
+#define B2_STATIC_RESCALE_MAX_N 65536
+#define B2_STATIC_RESCALE_MAX_POLY 3
+static __device__ __align__(256) uint64_t g_rescale_scratch[B2_STATIC_RESCALE_MAX_POLY * B2_STATIC_RESCALE_MAX_N];
+
+// In host code the symbol above is only a handle, not a device address. The address is looked up
+// once per device (with that device current) and cached.
+static std::mutex g_scratch_mu;
+static uint64_t *g_scratch_ptr[64] = {nullptr};
+
+static int rescale_scratch_for_device(int device, uint64_t **out) {
+    if (device < 0 || device >= 64) return fail(B2_EINVAL, "rescale_static: device index out of range");
+    std::lock_guard<std::mutex> lk(g_scratch_mu);
+    if (!g_scratch_ptr[device]) {
+        void *p = nullptr;
+        cudaError_t e = cudaGetSymbolAddress(&p, g_rescale_scratch);
+        if (e != cudaSuccess) return fail((int)e, std::string("rescale_static: cudaGetSymbolAddress: ") + cudaGetErrorString(e));
+        g_scratch_ptr[device] = static_cast<uint64_t *>(p);
+    }
+    *out = g_scratch_ptr[device];
+    return B2_OK;
+}
+
+extern "C" int b2_rescale_static(b2_ctx *c, size_t l, size_t n_poly, const uint64_t *d_in, uint64_t *d_out, void *stream) {
+    CHECK_CTX(c);
+    CHECK_LEVEL(c, l);
+    if (l < 2) return fail(B2_EINVAL, "rescale_static: no prime left to drop");
+    if (!d_in || !d_out) return fail(B2_EINVAL, "rescale_static: null pointer");
+    if (n_poly < 1 || n_poly > B2_STATIC_RESCALE_MAX_POLY)
+        return fail(B2_ESIZE, "rescale_static: n_poly exceeds the built-in scratch (at most 3 polynomials)");
+    if (c->N > B2_STATIC_RESCALE_MAX_N)
+        return fail(B2_ESIZE, "rescale_static: polynomial degree exceeds the built-in scratch (at most 65536 coefficients)");
+    uint64_t *r = nullptr;
+    int rc = rescale_scratch_for_device(c->device, &r);
+    if (rc) return rc;
+    cudaStream_t s = (cudaStream_t)stream;
+    const LevelPlan &pl = c->plan[l];
+    // every word of r that is read below is written first by the inverse transforms, so nothing
+    // left over from an earlier call needs clearing
+    for (size_t p = 0; p < n_poly; p++) {
+        rc = run_inv(c, d_in + (p * l + l - 1) * c->N, r + p * c->N, nullptr, 1, (uint32_t)(l - 1), c->d_fin_plain, s);
+        if (rc) return rc;
+    }
+    rc = run_bconv(c, false, r, d_out, nullptr, pl.grp_rs, (uint32_t)n_poly, pl.outs_rs, c->d_one, c->d_matd_one, 1, (uint32_t)(l - 1), true, s);
+    if (rc) return rc;
+    EpiSubMul<false> epi{d_in, d_out, pl.qlast_inv};
+    return run_fwd(c, d_out, d_out, pl.jobs_rs_ntt, (uint32_t)(n_poly * (l - 1)), 0, epi, s);
+}
+
 extern "C" uint32_t b2_galois_elt_from_step(int step, size_t N) {
     const uint32_t n = (uint32_t)N, m = 2 * n;
     if (step == 0) return m - 1;

@@ -33,6 +33,7 @@ SIGNATURES = {
     "b2_tensor_mul": (_int, [_vp, _sz, _vp, _vp, _vp, _vp]),
     "b2_multiply_and_relin": (_int, [_vp, _sz, _vp, _vp, _vp, _sz, _vp, _vp, _sz, _vp]),
     "b2_rescale": (_int, [_vp, _sz, _sz, _vp, _vp, _vp, _sz, _vp]),
+    "b2_rescale_static": (_int, [_vp, _sz, _sz, _vp, _vp, _vp]),
     "b2_galois_elt_from_step": (_u32, [_int, _sz]),
     "b2_galois_prepare": (_int, [_vp, _u32]),
     "b2_galois_permute": (_int, [_vp, _u32, _vp, _vp, _sz, _vp]),
