@@ -316,10 +316,15 @@ def main():
     # ---- per-kernel timing (live, CUDA events on the launching stream) and roofline -------------
     roofline, kernels = None, None
     if rank == 0:
+        # one stream here: a kernel's event pair must time that kernel alone, not a mix of streams
         check(LIB.b2_profile_start(ctx._h))
         prof_steps = 2
+        ws0, ws0_bytes = wss[0]
         for _ in range(prof_steps):
-            step_resident()
+            for b in range(B):
+                t = dev_ct3[b]
+                check(LIB.b2_keyswitch(ctx._h, LEVEL, t[2].data_ptr(), key_tabs[b % K].ctypes.data, BETA, t.data_ptr(),
+                                       ws0.data_ptr(), ws0_bytes, stream.cuda_stream))
         names = ctypes.create_string_buffer(4096)
         tot = (ctypes.c_float * 64)()
         cnt = (ctypes.c_uint32 * 64)()

@@ -155,6 +155,22 @@ int b2_bsgs_mac(b2_ctx *ctx, size_t size_Ql, size_t M, const uint64_t *const *pt
 int b2_poly_op(b2_ctx *ctx, int op, size_t n_limbs, const uint64_t *d_a, const uint64_t *d_b,
                uint64_t *d_out, void *stream);
 
+/* RNS-limb sharding of one key switch over `world` GPUs (no counterpart in the reference, which
+ * has no multi-GPU path; replaces keyswitch_inplace, src/eval_key_switch.cu:294-381, on a slice).
+ * Rank r owns the Q limbs [r l/world, (r+1) l/world) and the P limbs [r alpha/world, (r+1) alpha/world).
+ * b2_ctx_set_shard builds this rank's lists (synchronises the device; call at set-up).
+ * b2_shard_limbs: out4 = {first Q limb, Q count, first P limb, P count} at a level.
+ * b2_shard_keyswitch_phase runs the rank-local part of phase 0, 1 or 2; between the phases the
+ * caller all-gathers, over all ranks, (after 0) the l limbs at d_ws[0 .. l N) and (after 1) the
+ * 2 alpha limbs at d_ws[(l + beta (l+alpha)) N ..), laid out [2][alpha][N]. Buffers are full size on
+ * every rank; only the owned limbs of d_c2, evk and d_ct are read, only the owned limbs of d_ct
+ * are updated. */
+int b2_ctx_set_shard(b2_ctx *ctx, int rank, int world);
+int b2_shard_limbs(const b2_ctx *ctx, size_t size_Ql, uint32_t *out4);
+int b2_shard_keyswitch_phase(b2_ctx *ctx, size_t size_Ql, int phase, const uint64_t *d_c2,
+                             const uint64_t *const *evk, size_t n_evk, uint64_t *d_ct, void *d_ws,
+                             size_t ws_bytes, void *stream);
+
 /* Measurement hooks (no counterpart in the reference, which times with CUDATimer around whole
  * calls, include/cuda_wrapper.cuh:191-283). b2_launch_count: kernels launched by this library in
  * this process so far. b2_profile_start/stop: while on, every kernel launch is bracketed by CUDA

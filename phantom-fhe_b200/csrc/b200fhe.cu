@@ -208,10 +208,23 @@ struct b2_ctx {
         uint64_t p, ninv;  // ninv = -p^-1 mod 2^64
         uint32_t pieces, pad;
         uint64_t pad2;
+        double cw[4], cwq[4];  // p < 2^42: 2^(21 w) mod p for w = 1..4, and the same divided by p
     };
     RedcMeta *d_redc = nullptr;    // [size_QP]
     bool bconv_fp = false;         // every digit satisfies sum(q_i) < 2^64 and alpha <= 8
     bool use_cluster = false;      // N = 2^16: single-launch transforms on 8-CTA clusters
+    // RNS-limb sharding of one ciphertext over `shard_world` GPUs: this rank's slice of every list
+    int shard_rank = 0, shard_world = 1;
+    struct ShardPlan {
+        uint32_t q0 = 0, nq = 0, p0 = 0, np = 0, n_up_ntt = 0;
+        Job *jobs_up_ntt = nullptr, *jobs_dn_intt = nullptr, *jobs_dn_ntt = nullptr;
+        BconvGroup *grp_up = nullptr, *grp_dn = nullptr;
+        uint2 *outs_up = nullptr, *outs_dn = nullptr;
+        uint64_t *mat_up = nullptr, *mat_dn = nullptr;
+        double *matd_up = nullptr, *matd_dn = nullptr;
+        void *blob = nullptr;
+    };
+    std::vector<ShardPlan> shard;  // index l; empty until b2_ctx_set_shard
     std::vector<LevelPlan> plan;   // index l (1..size_Q)
     std::map<uint32_t, uint32_t *> galois;  // elt -> device gather table
     std::mutex mu;
@@ -262,9 +275,10 @@ static uint64_t punctured(const std::vector<uint64_t> &q, size_t s, size_t e, si
     return r;
 }
 
-// 21-bit pieces (as doubles) of (m * 2^64 mod p): the operand form of the FP64 base conversion
+// 21-bit pieces (as doubles) of a matrix entry: the operand form of the FP64 base conversion
 static inline void h_pieces(uint64_t m, uint64_t p, double *out3) {
-    const uint64_t v = (uint64_t)((((u128_t)m) << 64) % p);
+    // outputs below 2^42 are reduced in FP64 (no Montgomery factor); larger ones by Montgomery reduction
+    const uint64_t v = p < (1ull << 42) ? m % p : (uint64_t)((((u128_t)m) << 64) % p);
     out3[0] = (double)(v & 0x1FFFFF);
     out3[1] = (double)((v >> 21) & 0x1FFFFF);
     out3[2] = (double)(v >> 42);
@@ -411,6 +425,7 @@ extern "C" void b2_ctx_destroy(b2_ctx *c) {
     cudaFree(c->d_matd_one);
     cudaFree(c->d_redc);
     for (auto &pl : c->plan) cudaFree(pl.blob);
+    for (auto &sp : c->shard) cudaFree(sp.blob);
     for (auto &kv : c->galois) cudaFree(kv.second);
     delete c;
 }
@@ -511,7 +526,12 @@ extern "C" int b2_ctx_create(size_t N, const uint64_t *primes, size_t size_QP, s
         h_pieces(1, c->q[j], &matd_one[3 * j]);
         uint64_t inv = 1;  // Newton: inv = q^-1 mod 2^64
         for (int it = 0; it < 6; it++) inv *= 2 - c->q[j] * inv;
-        redc[j] = b2_ctx::RedcMeta{c->q[j], (uint64_t)(0 - inv), h_npieces(c->q[j]), 0, 0};
+        redc[j] = b2_ctx::RedcMeta{c->q[j], (uint64_t)(0 - inv), h_npieces(c->q[j]), 0, 0, {0, 0, 0, 0}, {0, 0, 0, 0}};
+        for (int w = 1; w <= 4; w++) {
+            const uint64_t cw = h_powmod(2, 21 * w, c->q[j]);
+            redc[j].cw[w - 1] = (double)cw;
+            redc[j].cwq[w - 1] = (double)cw / (double)c->q[j];
+        }
     }
     // the FP64 base conversion needs sum_i(in_i * M_i) < p * 2^64: every digit's primes must sum
     // below 2^64 (true for up to 8 primes of 61 bits, 16 of 60); otherwise the integer kernel runs
@@ -777,7 +797,19 @@ __global__ void __launch_bounds__(128) bconv_kernel(const uint64_t *__restrict__
 struct BconvMetaS {
     uint64_t p, ninv, slot;
     uint32_t pieces, pad;
+    double cw[4], cwq[4];
+    double pd, pinv;
 };
+
+// y * c mod p in FP64 for |y| < 2^50, c < p < 2^42 (the product of ntt_kernels.cuh's ArithFp)
+__device__ __forceinline__ double fp_mulmod(double y, double c, double cq, double p) {
+    const double h = __dmul_rn(y, c);
+    const double l = __fma_rn(y, c, -h);
+    const double k = __dsub_rn(__fma_rn(y, cq, b2::FP_MAGIC), b2::FP_MAGIC);
+    return __dadd_rn(__fma_rn(-k, p, h), l);
+}
+
+static_assert(sizeof(BconvMetaS) == 14 * 8, "shared-memory layout of the base conversion");
 
 template <int INP, int OUTP>
 __device__ __forceinline__ void bconv_acc(const double (&yp)[8][3], const double *m, uint32_t ni, double (&A)[5]) {
@@ -815,8 +847,19 @@ __device__ __forceinline__ void bconv_fp_body(const uint64_t *__restrict__ in, u
         const BconvMetaS o = s_meta[j];
         const double *m = s_m + 3 * (size_t)j * g.ni;
         double A[5] = {0.0, 0.0, 0.0, 0.0, 0.0};
-        if (o.pieces == 2) bconv_acc<INP, 2>(yp, m, g.ni, A);
-        else bconv_acc<INP, 3>(yp, m, g.ni, A);
+        if (o.pieces == 2) {
+            // small output prime: sum_w A_w 2^(21 w) mod p entirely in FP64 (A_w exact, below 2^48)
+            bconv_acc<INP, 2>(yp, m, g.ni, A);
+            const double pd = o.pd, pinv = o.pinv;
+            double r = A[0];
+#pragma unroll
+            for (int w = 1; w <= INP; w++) r = __dadd_rn(r, fp_mulmod(A[w], o.cw[w - 1], o.cwq[w - 1], pd));
+            r = __fma_rn(-__dsub_rn(__fma_rn(r, pinv, b2::FP_MAGIC), b2::FP_MAGIC), pd, r);
+            if (r < 0.0) r = __dadd_rn(r, pd);
+            out[o.slot * N + n] = (uint64_t)__double_as_longlong(__dadd_rn(r, 4503599627370496.0)) & 0x000FFFFFFFFFFFFFull;
+            continue;
+        }
+        bconv_acc<INP, 3>(yp, m, g.ni, A);
         // exact integers below 2^48 -> one 128-bit value
         unsigned __int128 V = 0;
 #pragma unroll
@@ -840,13 +883,18 @@ __global__ void __launch_bounds__(128) bconv_fp_kernel(const uint64_t *__restric
     extern __shared__ uint64_t s_raw[];
     const BconvGroup g = groups[blockIdx.y];
     BconvMetaS *s_meta = reinterpret_cast<BconvMetaS *>(s_raw);                      // [n_out]
-    double *s_m = reinterpret_cast<double *>(s_raw + 4 * (size_t)g.n_out);           // [n_out][ni][3]
+    double *s_m = reinterpret_cast<double *>(s_raw + 14 * (size_t)g.n_out);          // [n_out][ni][3]
     const double *mat = matd + 3 * (size_t)g.mat_off;
     for (uint32_t i = threadIdx.x; i < 3 * g.n_out * g.ni; i += blockDim.x) s_m[i] = mat[i];
     for (uint32_t j = threadIdx.x; j < g.n_out; j += blockDim.x) {
         const uint2 o = outs[g.out_begin + j];
         const b2_ctx::RedcMeta r = redc[o.y];
-        s_meta[j] = BconvMetaS{r.p, r.ninv, (uint64_t)(g.out_slot_base + o.x), r.pieces, 0};
+        BconvMetaS m{r.p, r.ninv, (uint64_t)(g.out_slot_base + o.x), r.pieces, 0, {}, {}, (double)r.p, 1.0 / (double)r.p};
+        for (int w = 0; w < 4; w++) {
+            m.cw[w] = r.cw[w];
+            m.cwq[w] = r.cwq[w];
+        }
+        s_meta[j] = m;
     }
     __syncthreads();
     const uint32_t n = blockIdx.x * blockDim.x + threadIdx.x;
@@ -870,16 +918,74 @@ struct EvkPtrs {
 template <int MAX_BETA, bool FUSED>
 __global__ void __launch_bounds__(256) ks_inner_prod_kernel(const uint64_t *__restrict__ digits, const uint64_t *__restrict__ own,
                                                            EvkPtrs evk, uint64_t *__restrict__ out, uint64_t *__restrict__ ct,
-                                                           const W2 *__restrict__ pinv, const Mod *mod, uint32_t N, uint32_t l, uint32_t lP,
-                                                           uint32_t size_Q, uint32_t size_QP, uint32_t beta) {
-    const size_t idx = 2 * ((size_t)blockIdx.x * blockDim.x + threadIdx.x);
-    if (idx >= (size_t)lP * N) return;
-    const uint32_t t = (uint32_t)(idx / N), n = (uint32_t)(idx % N);
+                                                           const W2 *__restrict__ pinv, const Mod *mod, const b2_ctx::RedcMeta *redc,
+                                                           uint32_t N, uint32_t l, uint32_t lP, uint32_t size_Q, uint32_t size_QP,
+                                                           uint32_t beta, uint4 own_range) {
+    // own_range = (first Q limb, number of Q limbs, first P limb, number of P limbs) this launch
+    // covers: everything on one GPU, the rank's slice under RNS-limb sharding
+    const size_t jdx = 2 * ((size_t)blockIdx.x * blockDim.x + threadIdx.x);
+    if (jdx >= (size_t)(own_range.y + own_range.w) * N) return;
+    const uint32_t jl = (uint32_t)(jdx / N), n = (uint32_t)(jdx % N);
+    const uint32_t t = jl < own_range.y ? own_range.x + jl : l + own_range.z + (jl - own_range.y);
+    const size_t idx = (size_t)t * N + n;
     const uint32_t pp = t < l ? t : size_Q + (t - l);
     const Mod md = mod[pp];
     // `own` (optional): the NTT-form input of ModUp; limb t of digit t / alpha is that input itself
     // (src/rns_bconv.cu:522-528), so the digit buffer need not hold a copy of it
     const uint32_t own_d = (own && t < l) ? t / (lP - l) : 0xFFFFFFFFu;
+    if (md.q < b2::FP_LIMIT) {
+        // Small prime (uniform over the block): digits and key words are below 2^41, so each product
+        // is four exact FP64 FMAs on 21-bit pieces instead of five wide integer multiplies, and the
+        // reduction of sum_w A_w 2^(21 w) stays in FP64 too. Same residues as the integer path.
+        const b2_ctx::RedcMeta rm = redc[pp];
+        const double qd = (double)md.q, qinv = 1.0 / qd;
+        double A[4][3];
+#pragma unroll
+        for (int o = 0; o < 4; o++) A[o][0] = A[o][1] = A[o][2] = 0.0;
+        auto lo = [](uint64_t v) { return __dsub_rn(__longlong_as_double((long long)((v & 0x1FFFFF) | 0x4330000000000000ull)), 4503599627370496.0); };
+        auto hi = [](uint64_t v) { return __dsub_rn(__longlong_as_double((long long)((v >> 21) | 0x4330000000000000ull)), 4503599627370496.0); };
+        for (uint32_t d = 0; d < beta; d++) {
+            const ulonglong2 x = (d == own_d) ? *reinterpret_cast<const ulonglong2 *>(own + (size_t)t * N + n)
+                                              : *reinterpret_cast<const ulonglong2 *>(digits + ((size_t)d * lP + t) * N + n);
+            const uint64_t *e = evk.p[d] + (size_t)pp * N + n;
+            const ulonglong2 e0 = __ldcs(reinterpret_cast<const ulonglong2 *>(e));
+            const ulonglong2 e1 = __ldcs(reinterpret_cast<const ulonglong2 *>(e + (size_t)size_QP * N));
+            const double xl[2] = {lo(x.x), lo(x.y)}, xh[2] = {hi(x.x), hi(x.y)};
+            const double el[4] = {lo(e0.x), lo(e0.y), lo(e1.x), lo(e1.y)}, eh[4] = {hi(e0.x), hi(e0.y), hi(e1.x), hi(e1.y)};
+#pragma unroll
+            for (int o = 0; o < 4; o++) {
+                const int c = o & 1;
+                A[o][0] = __fma_rn(xl[c], el[o], A[o][0]);
+                A[o][1] = __fma_rn(xl[c], eh[o], __fma_rn(xh[c], el[o], A[o][1]));
+                A[o][2] = __fma_rn(xh[c], eh[o], A[o][2]);
+            }
+        }
+        uint64_t r[4];
+        const W2 pi = FUSED && t < l ? pinv[pp] : W2{0, 0};
+        const double pid = (double)pi.w, piq = __dmul_rn(pid, qinv);
+#pragma unroll
+        for (int o = 0; o < 4; o++) {
+            double v = __dadd_rn(A[o][0], __dadd_rn(fp_mulmod(A[o][1], rm.cw[0], rm.cwq[0], qd), fp_mulmod(A[o][2], rm.cw[1], rm.cwq[1], qd)));
+            if (FUSED && t < l) v = fp_mulmod(v, pid, piq, qd);          // times P^-1 (|v| < 2^50)
+            else v = __fma_rn(-__dsub_rn(__fma_rn(v, qinv, b2::FP_MAGIC), b2::FP_MAGIC), qd, v);
+            if (v < 0.0) v = __dadd_rn(v, qd);
+            r[o] = (uint64_t)__double_as_longlong(__dadd_rn(v, 4503599627370496.0)) & 0x000FFFFFFFFFFFFFull;
+        }
+        if (!FUSED) {
+            *reinterpret_cast<ulonglong2 *>(out + idx) = make_ulonglong2(r[0], r[1]);
+            *reinterpret_cast<ulonglong2 *>(out + (size_t)lP * N + idx) = make_ulonglong2(r[2], r[3]);
+        } else if (t < l) {
+            uint64_t *c0 = ct + idx, *c1 = ct + (size_t)l * N + idx;
+            const ulonglong2 u0 = *reinterpret_cast<const ulonglong2 *>(c0), u1 = *reinterpret_cast<const ulonglong2 *>(c1);
+            *reinterpret_cast<ulonglong2 *>(c0) = make_ulonglong2(add_mod(u0.x, r[0], md.q), add_mod(u0.y, r[1], md.q));
+            *reinterpret_cast<ulonglong2 *>(c1) = make_ulonglong2(add_mod(u1.x, r[2], md.q), add_mod(u1.y, r[3], md.q));
+        } else {
+            const size_t alpha = lP - l, o = (size_t)(t - l) * N + n;
+            *reinterpret_cast<ulonglong2 *>(out + o) = make_ulonglong2(r[0], r[1]);
+            *reinterpret_cast<ulonglong2 *>(out + alpha * N + o) = make_ulonglong2(r[2], r[3]);
+        }
+        return;
+    }
     u128 a00{0, 0}, a01{0, 0}, a10{0, 0}, a11{0, 0};
     for (uint32_t d0 = 0; d0 < beta; d0 += MAX_BETA) {
         ulonglong2 x[MAX_BETA], e0[MAX_BETA], e1[MAX_BETA];
@@ -1014,7 +1120,7 @@ static int run_bconv(const b2_ctx *c, bool copy, const uint64_t *in, uint64_t *o
     LaunchScope ls(c, s, "bconv");
     if (c->bconv_fp && matd) {
         dim3 grid(N / 128, n_groups);
-        const size_t smem = (size_t)max_out * 32 + (size_t)max_ni * max_out * 24;
+        const size_t smem = (size_t)max_out * sizeof(BconvMetaS) + (size_t)max_ni * max_out * 24;
         (void)in3;
         if (copy) bconv_fp_kernel<true><<<grid, 128, smem, s>>>(in, out, copy_src, groups, outs, matd, c->d_redc, N);
         else bconv_fp_kernel<false><<<grid, 128, smem, s>>>(in, out, copy_src, groups, outs, matd, c->d_redc, N);
@@ -1092,7 +1198,7 @@ extern "C" int b2_modup(b2_ctx *c, size_t l, const uint64_t *d_c2, uint64_t *d_o
 
 // fused = false: out = cx [2][lP][N]. fused = true: Q limbs accumulate into ct, out = [2][alpha][N].
 static int inner_prod_impl(b2_ctx *c, size_t l, const uint64_t *digits, const uint64_t *own, const uint64_t *const *evk, size_t n_evk,
-                           uint64_t *out, uint64_t *ct, bool fused, cudaStream_t s) {
+                           uint64_t *out, uint64_t *ct, bool fused, cudaStream_t s, const uint4 *range = nullptr) {
     const size_t beta = c->plan[l].beta, lP = l + c->size_P;
     if (n_evk < beta) return fail(B2_EINVAL, "key has fewer digits than this level needs");
     if (beta > 64) return fail(B2_ESIZE, "more than 64 digits");
@@ -1101,15 +1207,17 @@ static int inner_prod_impl(b2_ctx *c, size_t l, const uint64_t *digits, const ui
         if (!evk[d]) return fail(B2_EINVAL, "null evaluation-key digit");
         ep.p[d] = evk[d];
     }
-    const size_t pairs = lP * c->N / 2;
+    const uint4 rg = range ? *range : make_uint4(0, (uint32_t)l, 0, (uint32_t)c->size_P);
+    const size_t pairs = (size_t)(rg.y + rg.w) * c->N / 2;
+    if (pairs == 0) return B2_OK;
     const unsigned grid = (unsigned)((pairs + 255) / 256);
     LaunchScope ls(c, s, "ks_inner_prod");
     if (fused)
-        ks_inner_prod_kernel<3, true><<<grid, 256, 0, s>>>(digits, own, ep, out, ct, c->d_Pinv, c->d_mod, (uint32_t)c->N, (uint32_t)l, (uint32_t)lP,
-                                                         (uint32_t)c->size_Q, (uint32_t)c->size_QP, (uint32_t)beta);
+        ks_inner_prod_kernel<3, true><<<grid, 256, 0, s>>>(digits, own, ep, out, ct, c->d_Pinv, c->d_mod, c->d_redc, (uint32_t)c->N, (uint32_t)l, (uint32_t)lP,
+                                                         (uint32_t)c->size_Q, (uint32_t)c->size_QP, (uint32_t)beta, rg);
     else
-        ks_inner_prod_kernel<3, false><<<grid, 256, 0, s>>>(digits, own, ep, out, nullptr, nullptr, c->d_mod, (uint32_t)c->N, (uint32_t)l, (uint32_t)lP,
-                                                          (uint32_t)c->size_Q, (uint32_t)c->size_QP, (uint32_t)beta);
+        ks_inner_prod_kernel<3, false><<<grid, 256, 0, s>>>(digits, own, ep, out, nullptr, nullptr, c->d_mod, c->d_redc, (uint32_t)c->N, (uint32_t)l, (uint32_t)lP,
+                                                          (uint32_t)c->size_Q, (uint32_t)c->size_QP, (uint32_t)beta, rg);
     LAUNCH_CHECK("ks_inner_prod_kernel");
     return B2_OK;
 }
@@ -1476,4 +1584,177 @@ extern "C" int b2_profile_stop(b2_ctx *c, char *names, size_t names_cap, float *
     memcpy(names, joined.c_str(), joined.size() + 1);
     *n_out = n;
     return B2_OK;
+}
+
+// ------------------------------------------------------------------------------------------------
+// RNS-limb sharding of one key switch over several GPUs
+// ------------------------------------------------------------------------------------------------
+// Rank r of G owns the Q limbs [r l / G, (r+1) l / G) and the P limbs [r alpha / G, (r+1) alpha / G)
+// of every buffer. Transforms, the inner product and all elementwise work are limb-local; the two
+// base conversions need every input limb of a coefficient, so the caller all-gathers (NCCL) between
+// the phases below:
+//   phase 0: t[own Q] = INTT(c2[own Q]) * (Q_d/q_i)^-1          -> all-gather t (l limbs)
+//   phase 1: up[d][own] = NTT(bconv_d(t)); inner product on the own limbs: ct[own Q] += acc P^-1,
+//            cxP[k][own P] = INTT(acc) * (P/p_i)^-1               -> all-gather cxP (2 alpha limbs)
+//   phase 2: ct[own Q] -= NTT(bconv(cxP) with the P^-1-carrying matrix)
+// The results on the own limbs are the same residues the unsharded key switch produces.
+static void shard_range(size_t n, int rank, int world, uint32_t *begin, uint32_t *count) {
+    const size_t b = n * (size_t)rank / world, e = n * (size_t)(rank + 1) / world;
+    *begin = (uint32_t)b;
+    *count = (uint32_t)(e - b);
+}
+
+static int build_shard_level(b2_ctx *c, size_t l) {
+    const size_t alpha = c->size_P, sQ = c->size_Q, beta = (l + alpha - 1) / alpha, lP = l + alpha;
+    b2_ctx::ShardPlan &sp = c->shard[l];
+    shard_range(l, c->shard_rank, c->shard_world, &sp.q0, &sp.nq);
+    shard_range(alpha, c->shard_rank, c->shard_world, &sp.p0, &sp.np);
+    auto owned = [&](size_t t) { return t < l ? (t >= sp.q0 && t < sp.q0 + sp.nq) : (t - l >= sp.p0 && t - l < sp.p0 + sp.np); };
+    std::vector<Job> jobs_up, jobs_di, jobs_dn;
+    std::vector<BconvGroup> grp_up(beta), grp_dn(2);
+    std::vector<uint2> outs_up, outs_dn;
+    std::vector<uint64_t> mat_up, mat_dn;
+    std::vector<double> matd_up, matd_dn;
+    uint32_t p_pieces = 2;
+    for (size_t i = 0; i < alpha; i++) p_pieces = std::max(p_pieces, h_npieces(c->q[sQ + i]));
+    for (size_t d = 0; d < beta; d++) {
+        const size_t s0 = alpha * d, e0 = std::min(s0 + alpha, l), ni = e0 - s0;
+        uint32_t in_pieces = 2;
+        for (size_t i = s0; i < e0; i++) in_pieces = std::max(in_pieces, h_npieces(c->q[i]));
+        const uint32_t begin = (uint32_t)outs_up.size(), moff = (uint32_t)mat_up.size();
+        for (size_t t = 0; t < lP; t++) {
+            if ((t >= s0 && t < e0) || !owned(t)) continue;
+            const uint32_t pp = phys_prime(c, l, t);
+            jobs_up.push_back(make_uint4((uint32_t)(d * lP + t), pp, 0, 0));
+            outs_up.push_back(make_uint2((uint32_t)t, pp));
+            for (size_t i = s0; i < e0; i++) {
+                const uint64_t m = punctured(c->q, s0, e0, i, c->q[pp]);
+                double pc[3];
+                h_pieces(m, c->q[pp], pc);
+                mat_up.push_back(m);
+                matd_up.insert(matd_up.end(), pc, pc + 3);
+            }
+        }
+        grp_up[d] = BconvGroup{(uint32_t)s0, (uint32_t)ni, moff, begin, (uint32_t)outs_up.size() - begin, (uint32_t)(d * lP),
+                               (uint32_t)(d * lP + s0), in_pieces};
+    }
+    for (size_t j = sp.q0; j < sp.q0 + sp.nq; j++) {
+        outs_dn.push_back(make_uint2((uint32_t)j, (uint32_t)j));
+        const uint64_t qj = c->q[j];
+        uint64_t P = 1;
+        for (size_t i = 0; i < alpha; i++) P = h_mulmod(P, c->q[sQ + i] % qj, qj);
+        const uint64_t Pinv = h_invmod(P, qj);
+        for (size_t i = 0; i < alpha; i++) {
+            const uint64_t m = h_mulmod(punctured(c->q, sQ, c->size_QP, sQ + i, qj), Pinv, qj);
+            double pc[3];
+            h_pieces(m, qj, pc);
+            mat_dn.push_back(m);
+            matd_dn.insert(matd_dn.end(), pc, pc + 3);
+        }
+    }
+    for (size_t k = 0; k < 2; k++) {
+        for (size_t i = sp.p0; i < sp.p0 + sp.np; i++)
+            jobs_di.push_back(make_uint4((uint32_t)(k * alpha + i), (uint32_t)(sQ + i), (uint32_t)i, 0));
+        for (size_t j = sp.q0; j < sp.q0 + sp.nq; j++)
+            jobs_dn.push_back(make_uint4((uint32_t)(k * l + j), (uint32_t)j, 0, (uint32_t)(k * l + j)));
+        grp_dn[k] = BconvGroup{(uint32_t)(k * alpha), (uint32_t)alpha, 0, 0, sp.nq, (uint32_t)(k * l), 0, p_pieces};
+    }
+    sp.n_up_ntt = (uint32_t)jobs_up.size();
+    // one blob
+    auto al = [](size_t b) { return (b + 255) & ~size_t(255); };
+    const size_t sz[] = {al(jobs_up.size() * sizeof(Job)), al(jobs_di.size() * sizeof(Job)), al(jobs_dn.size() * sizeof(Job)),
+                         al(grp_up.size() * sizeof(BconvGroup)), al(grp_dn.size() * sizeof(BconvGroup)), al(outs_up.size() * sizeof(uint2)),
+                         al(outs_dn.size() * sizeof(uint2)), al(mat_up.size() * 8), al(mat_dn.size() * 8), al(matd_up.size() * 8),
+                         al(matd_dn.size() * 8)};
+    const void *srcs[] = {jobs_up.data(), jobs_di.data(), jobs_dn.data(), grp_up.data(), grp_dn.data(), outs_up.data(),
+                          outs_dn.data(), mat_up.data(), mat_dn.data(), matd_up.data(), matd_dn.data()};
+    const size_t raw[] = {jobs_up.size() * sizeof(Job), jobs_di.size() * sizeof(Job), jobs_dn.size() * sizeof(Job),
+                          grp_up.size() * sizeof(BconvGroup), grp_dn.size() * sizeof(BconvGroup), outs_up.size() * sizeof(uint2),
+                          outs_dn.size() * sizeof(uint2), mat_up.size() * 8, mat_dn.size() * 8, matd_up.size() * 8, matd_dn.size() * 8};
+    size_t total = 256;
+    for (size_t x : sz) total += x;
+    CUDA_TRY(cudaMalloc(&sp.blob, total));
+    char *base = (char *)sp.blob;
+    void *dptr[11];
+    size_t off = 0;
+    for (int i = 0; i < 11; i++) {
+        dptr[i] = base + off;
+        if (raw[i]) CUDA_TRY(cudaMemcpy(dptr[i], srcs[i], raw[i], cudaMemcpyHostToDevice));
+        off += sz[i];
+    }
+    sp.jobs_up_ntt = (Job *)dptr[0];
+    sp.jobs_dn_intt = (Job *)dptr[1];
+    sp.jobs_dn_ntt = (Job *)dptr[2];
+    sp.grp_up = (BconvGroup *)dptr[3];
+    sp.grp_dn = (BconvGroup *)dptr[4];
+    sp.outs_up = (uint2 *)dptr[5];
+    sp.outs_dn = (uint2 *)dptr[6];
+    sp.mat_up = (uint64_t *)dptr[7];
+    sp.mat_dn = (uint64_t *)dptr[8];
+    sp.matd_up = (double *)dptr[9];
+    sp.matd_dn = (double *)dptr[10];
+    return B2_OK;
+}
+
+extern "C" int b2_ctx_set_shard(b2_ctx *c, int rank, int world) {
+    CHECK_CTX(c);
+    if (world < 1 || rank < 0 || rank >= world) return fail(B2_EINVAL, "set_shard: rank must be in [0, world)");
+    CUDA_TRY(cudaDeviceSynchronize());
+    for (auto &sp : c->shard) cudaFree(sp.blob);
+    c->shard.clear();
+    c->shard_rank = rank;
+    c->shard_world = world;
+    c->shard.resize(c->size_Q + 1);
+    for (size_t l = 1; l <= c->size_Q; l++) {
+        int rc = build_shard_level(c, l);
+        if (rc) return rc;
+    }
+    return B2_OK;
+}
+
+extern "C" int b2_shard_limbs(const b2_ctx *c, size_t l, uint32_t *out4) {
+    if (!c || !out4 || l < 1 || l > c->size_Q) return fail(B2_EINVAL, "shard_limbs: bad argument");
+    if (c->shard.empty()) return fail(B2_EINVAL, "shard_limbs: call b2_ctx_set_shard first");
+    const b2_ctx::ShardPlan &sp = c->shard[l];
+    out4[0] = sp.q0;
+    out4[1] = sp.nq;
+    out4[2] = sp.p0;
+    out4[3] = sp.np;
+    return B2_OK;
+}
+
+extern "C" int b2_shard_keyswitch_phase(b2_ctx *c, size_t l, int phase, const uint64_t *d_c2, const uint64_t *const *evk, size_t n_evk,
+                                        uint64_t *d_ct, void *d_ws, size_t ws_bytes, void *stream) {
+    CHECK_CTX(c);
+    CHECK_LEVEL(c, l);
+    if (c->shard.empty()) return fail(B2_EINVAL, "shard_keyswitch_phase: call b2_ctx_set_shard first");
+    if (!d_c2 || !evk || !d_ct || !d_ws) return fail(B2_EINVAL, "shard_keyswitch_phase: null pointer");
+    if (ws_bytes < b2_workspace_bytes(c, B2_OP_KEYSWITCH, l)) return fail(B2_EWS, "shard_keyswitch_phase: workspace too small");
+    cudaStream_t s = (cudaStream_t)stream;
+    const LevelPlan &pl = c->plan[l];
+    const b2_ctx::ShardPlan &sp = c->shard[l];
+    const size_t N = c->N, a = c->size_P, lP = l + a, beta = pl.beta;
+    uint64_t *t = (uint64_t *)d_ws, *up = t + l * N, *cxP = up + beta * lP * N;
+    int rc;
+    switch (phase) {
+        case 0:
+            return run_inv(c, d_c2, t, pl.jobs_up_intt + sp.q0, sp.nq, 0, pl.fin_up, s);
+        case 1: {
+            rc = run_bconv(c, false, t, up, d_c2, sp.grp_up, (uint32_t)beta, sp.outs_up, sp.mat_up, sp.matd_up, (uint32_t)a, (uint32_t)lP, true, s);
+            if (rc) return rc;
+            rc = run_fwd(c, up, up, sp.jobs_up_ntt, sp.n_up_ntt, 0, EpiStore{}, s);
+            if (rc) return rc;
+            const uint4 rg = make_uint4(sp.q0, sp.nq, sp.p0, sp.np);
+            rc = inner_prod_impl(c, l, up, d_c2, evk, n_evk, cxP, d_ct, true, s, &rg);
+            if (rc) return rc;
+            return run_inv(c, cxP, cxP, sp.jobs_dn_intt, 2 * sp.np, 0, c->d_fin_P, s);
+        }
+        case 2:
+            if (sp.nq == 0) return B2_OK;
+            rc = run_bconv(c, false, cxP, up, nullptr, sp.grp_dn, 2, sp.outs_dn, sp.mat_dn, sp.matd_dn, (uint32_t)a, (uint32_t)l, true, s);
+            if (rc) return rc;
+            return run_fwd(c, up, up, sp.jobs_dn_ntt, 2 * sp.nq, 0, EpiSubFrom{d_ct}, s);
+        default:
+            return fail(B2_EINVAL, "shard_keyswitch_phase: phase must be 0, 1 or 2");
+    }
 }

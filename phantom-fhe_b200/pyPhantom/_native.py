@@ -41,6 +41,9 @@ SIGNATURES = {
     "b2_hoist_rotations": (_int, [_vp, _sz, _vp, _vp, _sz, _vp, _sz, _vp, _vp, _sz, _vp]),
     "b2_bsgs_mac": (_int, [_vp, _sz, _sz, _vp, _vp, _vp, _vp]),
     "b2_poly_op": (_int, [_vp, _int, _sz, _vp, _vp, _vp, _vp]),
+    "b2_ctx_set_shard": (_int, [_vp, _int, _int]),
+    "b2_shard_limbs": (_int, [_vp, _sz, _vp]),
+    "b2_shard_keyswitch_phase": (_int, [_vp, _sz, _int, _vp, _vp, _sz, _vp, _vp, _sz, _vp]),
     "b2_launch_count": (_u64, []),
     "b2_profile_start": (_int, [_vp]),
     "b2_profile_stop": (_int, [_vp, _vp, _sz, _vp, _vp, _sz, _vp]),

@@ -1,0 +1,105 @@
+"""RNS-limb sharding of one key switch. On one GPU the ranks are emulated one after another on
+shared buffers (the all-gathers are then implicit): the union of what the ranks compute must be the
+unsharded result, bit for bit. With two or more GPUs the same thing runs as real NCCL ranks."""
+import os
+import socket
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+from pyPhantom import _native
+from pyPhantom._native import LIB, check
+from gpu_helpers import dev, host, key_dev, make_ctx, stream
+
+
+@pytest.mark.parametrize("world", [1, 2, 3, 8])
+@pytest.mark.parametrize("l", [8, 5, 2])
+def test_emulated_ranks_reproduce_the_key_switch(world, l):
+    N = 4096
+    ctx, o = make_ctx(N, [55, 40, 41, 42, 43, 44, 45, 46, 58, 59, 60], 3)
+    beta = o.beta(l)
+    key = o.synth_key(beta, 61, 10)
+    kt, kp = key_dev(key)
+    c2_h, ct_h = o.fill(1, o.primes[:l], 61, 3)[0], o.synth_ct(l, 61, 1)
+    want = o.keyswitch(l, c2_h, key, ct_h)
+    c2, ct = dev(c2_h), dev(ct_h)
+    ws, nb = ctx.workspace(_native.OP_KEYSWITCH, l)
+    ws.zero_()
+    seen_q, seen_p = [], []
+    for phase in range(3):
+        for r in range(world):
+            check(LIB.b2_ctx_set_shard(ctx._h, r, world))
+            if phase == 0:
+                rg = np.zeros(4, dtype=np.uint32)
+                check(LIB.b2_shard_limbs(ctx._h, l, rg.ctypes.data))
+                seen_q += list(range(rg[0], rg[0] + rg[1]))
+                seen_p += list(range(rg[2], rg[2] + rg[3]))
+            check(LIB.b2_shard_keyswitch_phase(ctx._h, l, phase, c2.data_ptr(), kp.ctypes.data, beta, ct.data_ptr(),
+                                               ws.data_ptr(), nb, stream()))
+    assert seen_q == list(range(l)) and seen_p == list(range(o.size_P))
+    assert np.array_equal(host(ct), want)
+    # the unsharded entry point still works on a context that has shard lists
+    ct2 = dev(ct_h)
+    check(LIB.b2_keyswitch(ctx._h, l, c2.data_ptr(), kp.ctypes.data, beta, ct2.data_ptr(), ws.data_ptr(), nb, stream()))
+    assert np.array_equal(host(ct2), want)
+
+
+def test_shard_argument_checks():
+    ctx, o = make_ctx(4096, [40, 40, 50], 1)
+    x = ctx.empty(2, 2)
+    ws, nb = ctx.workspace(_native.OP_KEYSWITCH, 2)
+    kt, kp = key_dev(o.synth_key(2, 1, 10))
+    with pytest.raises(ValueError, match="set_shard first"):
+        check(LIB.b2_shard_keyswitch_phase(ctx._h, 2, 0, x.data_ptr(), kp.ctypes.data, 2, x.data_ptr(), ws.data_ptr(), nb, stream()))
+    with pytest.raises(ValueError, match="rank must be"):
+        check(LIB.b2_ctx_set_shard(ctx._h, 2, 2))
+    check(LIB.b2_ctx_set_shard(ctx._h, 0, 2))
+    with pytest.raises(ValueError, match="phase must be"):
+        check(LIB.b2_shard_keyswitch_phase(ctx._h, 2, 3, x.data_ptr(), kp.ctypes.data, 2, x.data_ptr(), ws.data_ptr(), nb, stream()))
+
+
+_NCCL_WORKER = r"""
+import os, sys
+sys.path.insert(0, os.path.join(os.environ["REPO"], "phantom-fhe_b200")); sys.path.insert(0, os.path.join(os.environ["REPO"], "tests"))
+import numpy as np, torch, torch.distributed as dist
+import pyPhantom as ph
+from pyPhantom.parallel import LimbShardedKeySwitch
+from gpu_helpers import make_ctx, dev, host
+rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+torch.cuda.set_device(rank)
+dist.init_process_group("nccl", device_id=torch.device("cuda", rank))
+N, l = 8192, 7
+ctx, o = make_ctx(N, [58, 40, 40, 40, 40, 40, 40, 60, 60, 60], 3)
+key_h = o.synth_key(o.beta(l), 71, 10)
+key = ph.relin_key.from_numpy(ctx, key_h)
+c2_h, ct_h = o.fill(1, o.primes[:l], 71, 3)[0], o.synth_ct(l, 71, 1)
+sh = LimbShardedKeySwitch(ctx)
+c2, ct = dev(c2_h), dev(ct_h)
+sh.keyswitch(l, c2, key, ct)
+sh.allgather_ct(l, ct)
+ok = np.array_equal(host(ct), o.keyswitch(l, c2_h, key_h, ct_h))
+t = torch.tensor([1 if ok else 0], device="cuda"); dist.all_reduce(t, op=dist.ReduceOp.MIN)
+dist.destroy_process_group()
+sys.exit(0 if int(t.item()) == 1 else 1)
+"""
+
+
+def test_two_real_ranks_over_nccl(tmp_path):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    script = tmp_path / "worker.py"
+    script.write_text(_NCCL_WORKER)
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    env = dict(os.environ, REPO=os.path.dirname(os.path.dirname(os.path.abspath(__file__))), NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", str(port), str(script)]
+    res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-2000:]
