@@ -150,6 +150,12 @@ int b2_hoist_rotations(b2_ctx *ctx, size_t size_Ql, const uint64_t *d_ct, const 
 int b2_bsgs_mac(b2_ctx *ctx, size_t size_Ql, size_t M, const uint64_t *const *pts,
                 const uint64_t *const *babies, uint64_t *d_out, void *stream);
 
+/* replaces expand_single_chain_to_full and the per-diagonal expansion inside the BSGS driver
+ * (src/single_chain_plaintext.cu:93-192, src/bsgs.cu:282-315, src/bootstrap.cu:660-686):
+ * d_signed int64[N] (signed, centred coefficients, device) -> d_out [size_Ql][N] in NTT form */
+int b2_expand_single_chain(b2_ctx *ctx, size_t size_Ql, const int64_t *d_signed, uint64_t *d_out,
+                           void *stream);
+
 /* replaces add/sub/multiply_rns_poly (src/polymath.cu:17-180) over [n_limbs][N], limb i on prime i;
  * op: 0 add, 1 sub, 2 multiply, 3 negate (d_b ignored). d_out may alias an input. */
 int b2_poly_op(b2_ctx *ctx, int op, size_t n_limbs, const uint64_t *d_a, const uint64_t *d_b,

@@ -560,6 +560,24 @@ void ora_bsgs_mac(const ora_ctx *c, size_t size_Ql, size_t M, const uint64_t *co
     }
 }
 
+/* src/bootstrap.cu:660-686 (light_pt_expand_per_tower_kernel) followed by the forward NTT of
+ * src/bsgs.cu:308-314 / src/single_chain_plaintext.cu:93-192 */
+void ora_expand_single_chain(const ora_ctx *c, size_t size_Ql, const int64_t *coeffs, uint64_t *out) {
+    size_t N = c->N;
+#pragma omp parallel for schedule(dynamic)
+    for (size_t l = 0; l < size_Ql; l++) {
+        uint64_t q = c->q[l];
+        uint64_t *d = out + l * N;
+        for (size_t i = 0; i < N; i++) {
+            int64_t v = coeffs[i];
+            uint64_t mag = v >= 0 ? (uint64_t)v : (uint64_t)0 - (uint64_t)v;
+            uint64_t r = mag % q;
+            d[i] = (v >= 0 || r == 0) ? r : q - r;
+        }
+        ntt_fwd_limb(d, N, q, c->tw[l]);
+    }
+}
+
 int ora_num_threads(void) {
 #ifdef _OPENMP
     return omp_get_max_threads();

@@ -110,6 +110,8 @@ void ora_hoist_rotations(const ora_ctx *c, size_t size_Ql, const uint64_t *ct,
  * pts[b] -> [l][N]; babies[b] -> [2][l][N]; out [2][l][N]. */
 void ora_bsgs_mac(const ora_ctx *c, size_t size_Ql, size_t M, const uint64_t *const *pts,
                   const uint64_t *const *babies, uint64_t *out);
+/* src/bootstrap.cu:660-686 + forward NTT: signed centred int64[N] -> [size_Ql][N] NTT form */
+void ora_expand_single_chain(const ora_ctx *c, size_t size_Ql, const int64_t *coeffs, uint64_t *out);
 /* src/polymath.cu:17-180 elementwise helpers over [n_limbs][N] starting at prime 0 */
 void ora_add(const ora_ctx *c, size_t n_limbs, const uint64_t *a, const uint64_t *b, uint64_t *o);
 void ora_sub(const ora_ctx *c, size_t n_limbs, const uint64_t *a, const uint64_t *b, uint64_t *o);

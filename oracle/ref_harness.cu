@@ -15,6 +15,7 @@
 #include <vector>
 
 #include "phantom.h"
+#include "bsgs.h"
 #include "ckks_oracle.h"
 
 using namespace phantom;
@@ -97,6 +98,7 @@ static double time_us(const std::function<void()> &op, int warm, int iters) {
 
 int main(int argc, char **argv) {
     int logn = 12, special = 2, level = -1, time_iters = 0;
+    std::vector<int> bsgs;  // {baby steps M, giant steps G}: also run the BSGS matrix-vector driver
     uint64_t seed = 1;
     std::vector<int> bits = {50, 36, 36, 36, 36, 36, 50, 50}, steps = {1, 2, -1};
     std::string out = "case.json";
@@ -110,6 +112,7 @@ int main(int argc, char **argv) {
         else if (k == "--seed") seed = strtoull(v, nullptr, 10);
         else if (k == "--steps") steps = parse_ints(v);
         else if (k == "--out") out = v;
+        else if (k == "--bsgs") bsgs = parse_ints(v);
         else if (k == "--time") time_iters = atoi(v);
         else { fprintf(stderr, "unknown arg %s\n", argv[i]); return 2; }
     }
@@ -269,6 +272,32 @@ int main(int argc, char **argv) {
                 auto o = hoist_rotations(context, a, glk, steps); }, 2, time_iters / 4 + 1)});
         }
     }
+    // ---- BSGS matrix-vector driver on synthetic single-chain plaintexts ----------------------------
+    // diagonal d = signed centred coefficients in [-2^39, 2^39): uniform draw of stream
+    // (seed << 40) ^ ((3000 + d) << 16) below 2^40, minus 2^39. Needs --steps 1,2,..,M/2,M.
+    if (bsgs.size() == 2) {
+        const size_t M = bsgs[0], G = bsgs[1];
+        BsgsDiagonals diags;
+        diags.d_pad = M * G;
+        diags.baby_steps = M;
+        diags.giant_steps = G;
+        std::vector<uint64_t> u(N);
+        for (size_t d = 0; d < M * G; d++) {
+            SingleChainPlaintext scp;
+            scp.coeffs = PinnedHostInt64Buffer(N);
+            scp.scale = scale;
+            ora_fill_uniform(u.data(), N, uint64_t(1) << 40, (seed << 40) ^ (uint64_t(3000 + d) << 16));
+            for (size_t i = 0; i < N; i++) scp.coeffs.data()[i] = (int64_t) u[i] - (int64_t(1) << 39);
+            diags.diagonals.push_back(std::move(scp));
+        }
+        PhantomCiphertext x = make_ct(primes, chain, 2, N, l, scale, seed, 1);
+        PhantomCiphertext y = bsgs_matmul_preencoded(context, glk, x, diags);
+        record("bsgs", y.data(), 2 * (l - 1), N);
+        PhantomPlaintext full = expand_single_chain_to_full(context, diags.diagonals[0], chain);
+        record("expand_single_chain", full.data(), l, N);
+        if (time_iters)
+            g_times.push_back({"bsgs_us", time_us([&] { auto r = bsgs_matmul_preencoded(context, glk, x, diags); }, 2, time_iters / 4 + 1)});
+    }
     cudaDeviceSynchronize();
     cudaError_t err = cudaGetLastError();
 
@@ -279,6 +308,7 @@ int main(int argc, char **argv) {
             logn, size_P, l, (unsigned long long) seed, chain);
     fprintf(f, " \"bits\": ["); for (size_t i = 0; i < bits.size(); i++) fprintf(f, "%s%d", i ? "," : "", bits[i]); fprintf(f, "],\n");
     fprintf(f, " \"steps\": ["); for (size_t i = 0; i < steps.size(); i++) fprintf(f, "%s%d", i ? "," : "", steps[i]); fprintf(f, "],\n");
+    fprintf(f, " \"bsgs\": ["); for (size_t i = 0; i < bsgs.size(); i++) fprintf(f, "%s%d", i ? "," : "", bsgs[i]); fprintf(f, "],\n");
     fprintf(f, " \"elts\": ["); for (size_t i = 0; i < elts.size(); i++) fprintf(f, "%s%u", i ? "," : "", elts[i]); fprintf(f, "],\n");
     fprintf(f, " \"primes\": ["); for (size_t i = 0; i < primes.size(); i++) fprintf(f, "%s%llu", i ? "," : "", (unsigned long long) primes[i]); fprintf(f, "],\n");
     fprintf(f, " \"host_tables_match_oracle\": %s,\n \"cuda_error\": \"%s\",\n", tables_ok ? "true" : "false", cudaGetErrorString(err));

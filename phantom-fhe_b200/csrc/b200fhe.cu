@@ -735,7 +735,7 @@ template <int MAX_NI, bool COPY>
 __global__ void __launch_bounds__(128) bconv_kernel(const uint64_t *__restrict__ in, uint64_t *__restrict__ out,
                                                     const uint64_t *__restrict__ copy_src, const BconvGroup *groups,
                                                     const uint2 *outs, const uint64_t *mats, const Mod *mod, uint32_t N) {
-    extern __shared__ uint64_t s_raw[];
+    extern __shared__ __align__(16) uint64_t s_raw[];
     const BconvGroup g = groups[blockIdx.y];
     BconvOut *s_out = reinterpret_cast<BconvOut *>(s_raw);          // [n_out]
     uint64_t *s_mat = s_raw + 4 * (size_t)g.n_out;                  // [n_out][ni]
@@ -880,7 +880,7 @@ template <bool COPY>
 __global__ void __launch_bounds__(128) bconv_fp_kernel(const uint64_t *__restrict__ in, uint64_t *__restrict__ out,
                                                        const uint64_t *__restrict__ copy_src, const BconvGroup *groups, const uint2 *outs,
                                                        const double *matd, const b2_ctx::RedcMeta *redc, uint32_t N) {
-    extern __shared__ uint64_t s_raw[];
+    extern __shared__ __align__(16) uint64_t s_raw[];
     const BconvGroup g = groups[blockIdx.y];
     BconvMetaS *s_meta = reinterpret_cast<BconvMetaS *>(s_raw);                      // [n_out]
     double *s_m = reinterpret_cast<double *>(s_raw + 14 * (size_t)g.n_out);          // [n_out][ni][3]
@@ -1080,6 +1080,20 @@ __global__ void __launch_bounds__(256) galois_gather_kernel(const uint64_t *__re
     dst[idx] = src[limb * N + perm[idx % N]];
 }
 
+// Single-chain plaintext expansion (src/bootstrap.cu:660-686, light_pt_expand_per_tower_kernel):
+// one signed, centred int64 coefficient vector -> its residue in each of n_limbs primes.
+__global__ void __launch_bounds__(256) expand_signed_kernel(const int64_t *__restrict__ src, uint64_t *__restrict__ dst, const Mod *mod, uint32_t N,
+                                                           uint32_t n_limbs) {
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (size_t)n_limbs * N) return;
+    const Mod md = mod[idx / N];
+    const int64_t c = src[idx % N];
+    const uint64_t mag = c >= 0 ? (uint64_t)c : (uint64_t)0 - (uint64_t)c;
+    u128 v{mag, 0};
+    const uint64_t r = barrett128(v, md.q, md.r0, md.r1);
+    dst[idx] = (c >= 0 || r == 0) ? r : md.q - r;
+}
+
 struct MacPtrs {
     const uint64_t *const *pts;
     const uint64_t *const *babies;
@@ -1120,7 +1134,7 @@ static int run_bconv(const b2_ctx *c, bool copy, const uint64_t *in, uint64_t *o
     LaunchScope ls(c, s, "bconv");
     if (c->bconv_fp && matd) {
         dim3 grid(N / 128, n_groups);
-        const size_t smem = (size_t)max_out * sizeof(BconvMetaS) + (size_t)max_ni * max_out * 24;
+        const size_t smem = (size_t)max_out * sizeof(BconvMetaS) + (size_t)max_out * 24 * 8;
         (void)in3;
         if (copy) bconv_fp_kernel<true><<<grid, 128, smem, s>>>(in, out, copy_src, groups, outs, matd, c->d_redc, N);
         else bconv_fp_kernel<false><<<grid, 128, smem, s>>>(in, out, copy_src, groups, outs, matd, c->d_redc, N);
@@ -1528,6 +1542,20 @@ extern "C" int b2_bsgs_mac(b2_ctx *c, size_t l, size_t M, const uint64_t *const 
     bsgs_mac_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(pts, babies, d_out, c->d_mod, (uint32_t)c->N, (uint32_t)l, (uint32_t)M);
     LAUNCH_CHECK("bsgs_mac_kernel");
     return B2_OK;
+}
+
+extern "C" int b2_expand_single_chain(b2_ctx *c, size_t l, const int64_t *d_signed, uint64_t *d_out, void *stream) {
+    CHECK_CTX(c);
+    CHECK_LEVEL(c, l);
+    if (!d_signed || !d_out) return fail(B2_EINVAL, "expand_single_chain: null pointer");
+    cudaStream_t s = (cudaStream_t)stream;
+    const size_t n = l * c->N;
+    {
+        LaunchScope ls(c, s, "expand_signed");
+        expand_signed_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(d_signed, d_out, c->d_mod, (uint32_t)c->N, (uint32_t)l);
+        LAUNCH_CHECK("expand_signed_kernel");
+    }
+    return run_fwd(c, d_out, d_out, nullptr, (uint32_t)l, 0, EpiStore{}, s);
 }
 
 extern "C" int b2_poly_op(b2_ctx *c, int op, size_t n_limbs, const uint64_t *d_a, const uint64_t *d_b, uint64_t *d_out, void *stream) {

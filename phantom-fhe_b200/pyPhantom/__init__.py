@@ -374,6 +374,7 @@ class galois_key:
 
     def __init__(self):
         self.relin_keys = []
+        self.fallback_relin_keys = []  # non-owning, indexed like relin_keys (include/secretkey.h:236-246)
 
     @classmethod
     def from_keys(cls, keys):
@@ -385,16 +386,27 @@ class galois_key:
         return self.relin_keys[index]
 
     def resolve(self, index):
+        """owned key if populated, else the registered fallback, else None (include/secretkey.h:266-274)"""
         if index < len(self.relin_keys) and self.relin_keys[index].dnum() > 0:
             return self.relin_keys[index]
+        if index < len(self.fallback_relin_keys) and self.fallback_relin_keys[index] is not None:
+            return self.fallback_relin_keys[index]
         return None
+
+    def set_fallback(self, index, ksk):
+        """include/secretkey.h:278-286"""
+        if len(self.fallback_relin_keys) < len(self.relin_keys):
+            self.fallback_relin_keys += [None] * (len(self.relin_keys) - len(self.fallback_relin_keys))
+        if index >= len(self.fallback_relin_keys):
+            raise IndexError("PhantomGaloisKey::set_fallback: index out of range")
+        self.fallback_relin_keys[index] = ksk
 
     def save(self, stream):
         if not self.relin_keys:
             raise ValueError("PhantomGaloisKey has not been generated")
         stream.write(struct.pack("<Q", len(self.relin_keys)))
         for k in self.relin_keys:
-            k.save(stream)
+            k.save(stream)  # an empty slot throws, like the reference (include/secretkey.h:290-302)
 
     def load(self, stream, device=None):
         (n,) = struct.unpack("<Q", _read_exact(stream, 8))
@@ -675,3 +687,112 @@ def hoist_rotations(context, ct, glk, steps):
     check(LIB.b2_hoist_rotations(ctx._h, l, ct.data.data_ptr(), elts.ctypes.data, len(steps), ksk.ctypes.data, n_evk,
                                  out_ptrs.ctypes.data, ws.data_ptr(), nbytes, _stream()))
     return [ct._like(o) for o in outs]
+
+
+# ---------------------------------------------------------------------------------------------
+# single-chain plaintexts and the BSGS matrix-vector driver (binding.cu:405-568; src/bsgs.cu)
+# ---------------------------------------------------------------------------------------------
+class single_chain_plaintext:
+    """N signed, centred int64 coefficients in pinned host memory plus a scale
+    (include/single_chain_plaintext.h:40-43)."""
+
+    def __init__(self, coeffs=None, scale=1.0):
+        self.scale = float(scale)
+        self.coeffs = None
+        if coeffs is not None:
+            t = torch.from_numpy(np.ascontiguousarray(coeffs, dtype=np.int64).copy())
+            self.coeffs = t.pin_memory() if torch.cuda.is_available() else t
+
+    def coeffs_bytes(self):
+        return self.coeffs.numpy().tobytes()
+
+
+def scp_from_bytes(raw, scale):
+    """binding.cu:416-516: rebuild a single-chain plaintext from its int64 little-endian bytes"""
+    return single_chain_plaintext(np.frombuffer(raw, dtype=np.int64), scale)
+
+
+def expand_single_chain_to_full(ctx, scp, target_chain_index):
+    """src/single_chain_plaintext.cu:93-192: residues in every limb of the level, NTT form"""
+    l = ctx.limbs_at(target_chain_index)
+    if scp.coeffs.numel() != ctx.N:
+        raise ValueError("scp coeff length != N")
+    pt = plaintext()
+    pt._chain_index, pt._N, pt._limbs, pt._scale = target_chain_index, ctx.N, l, scp.scale
+    pt.data = ctx.empty(l)
+    d = scp.coeffs.to(ctx.device, non_blocking=True)
+    check(LIB.b2_expand_single_chain(ctx._h, l, d.data_ptr(), pt.data.data_ptr(), _stream()))
+    return pt
+
+
+class bsgs_diagonals:
+    """include/bsgs.h:14-19: d_pad = baby_steps * giant_steps diagonals, diagonal g*M + b pre-rotated"""
+
+    def __init__(self, diagonals, d_pad, baby_steps, giant_steps):
+        self.diagonals, self.d_pad = list(diagonals), int(d_pad)
+        self.baby_steps, self.giant_steps = int(baby_steps), int(giant_steps)
+
+
+def bsgs_required_steps(baby_steps):
+    """src/bsgs.cu:180-191"""
+    if baby_steps <= 1:
+        return []
+    steps, s = [], 1
+    while s < baby_steps:
+        steps.append(s)
+        s <<= 1
+    steps.append(int(baby_steps))
+    return steps
+
+
+def compute_bsgs_babies(ctx, galois_key_, x, baby_steps):
+    """src/bsgs.cu:194-214: babies[b] = rotate(babies[b - msb(b)], msb(b)) - chained, not hoisted"""
+    if baby_steps == 0:
+        raise ValueError("compute_bsgs_babies: baby_steps must be > 0")
+    babies = [x]
+    for b in range(1, baby_steps):
+        bit = 1 << (b.bit_length() - 1)
+        babies.append(rotate(ctx, babies[b - bit], bit, galois_key_))
+    return babies
+
+
+def bsgs_apply_giants_with_babies(ctx, galois_key_, babies, diags):
+    """src/bsgs.cu:216-359: per giant expand M plaintexts and run the fused MAC; Horner
+    acc = rotate(acc, M) + partial_g from the last giant down; one rescale; scale reset to x's."""
+    M, G = diags.baby_steps, diags.giant_steps
+    if M == 0 or G == 0 or M * G != diags.d_pad:
+        raise ValueError("bsgs_apply_giants_with_babies: M*G must equal d_pad")
+    if len(babies) != M:
+        raise ValueError("bsgs_apply_giants_with_babies: babies size != baby_steps")
+    if len(diags.diagonals) != diags.d_pad:
+        raise ValueError("bsgs_apply_giants_with_babies: diagonals size mismatch")
+    x = babies[0]
+    l, N = x._limbs, ctx.N
+    pool = ctx.empty(M, l)  # M expanded plaintexts, reused by every giant
+    pt_ptrs = torch.tensor([pool[b].data_ptr() for b in range(M)], dtype=torch.int64, device=ctx.device)
+    baby_ptrs = torch.tensor([c.data.data_ptr() for c in babies], dtype=torch.int64, device=ctx.device)
+    staged = [None] * M
+
+    def partial(g):
+        for b in range(M):
+            scp = diags.diagonals[g * M + b]
+            if scp.coeffs.numel() != N:
+                raise ValueError("bsgs_apply_giants_with_babies: scp coeff length != N")
+            staged[b] = scp.coeffs.to(ctx.device, non_blocking=True)
+            check(LIB.b2_expand_single_chain(ctx._h, l, staged[b].data_ptr(), pool[b].data_ptr(), _stream()))
+        out = ctx.empty(2, l)
+        check(LIB.b2_bsgs_mac(ctx._h, l, M, pt_ptrs.data_ptr(), baby_ptrs.data_ptr(), out.data_ptr(), _stream()))
+        return x._like(out, scale=x._scale * diags.diagonals[g * M].scale)
+
+    acc = partial(G - 1)
+    for g in range(G - 2, -1, -1):
+        acc = rotate(ctx, acc, M, galois_key_)
+        acc = add(ctx, acc, partial(g))
+    acc = rescale_to_next(ctx, acc)
+    acc.set_scale(x._scale)
+    return acc
+
+
+def bsgs_matmul_preencoded(ctx, galois_key_, x, diags):
+    """src/bsgs.cu:361-367"""
+    return bsgs_apply_giants_with_babies(ctx, galois_key_, compute_bsgs_babies(ctx, galois_key_, x, diags.baby_steps), diags)

@@ -16,6 +16,9 @@ B40x23=$(printf '40,%.0s' $(seq 23))
 "$H" --logn 12 --bits 50,36,36,36,36,36,50,50 --special 2 --level 5 --seed 8 --steps 3,0 --out "$OUT/n12_l5_a2.json"
 "$H" --logn 13 --bits 60,40,40,40,40,40,40,60,60,60 --special 3 --level 7 --seed 9 --steps 1,-2 --out "$OUT/n13_l7_a3.json"
 "$H" --logn 13 --bits 60,40,40,40,40,40,40,60,60,60 --special 3 --level 4 --seed 10 --steps 5 --out "$OUT/n13_l4_a3.json"
+# BSGS matrix-vector driver (chained baby rotations, fused MAC, Horner over giants, one rescale)
+"$H" --logn 12 --bits 50,36,36,36,36,36,50,50 --special 2 --level 6 --seed 12 --steps 1,2,4 --bsgs 4,2 --out "$OUT/n12_bsgs_m4g2.json"
+"$H" --logn 13 --bits 60,40,40,40,40,40,40,60,60,60 --special 3 --level 5 --seed 13 --steps 1,2 --bsgs 2,3 --out "$OUT/n13_bsgs_m2g3.json"
 # the NTT configuration: N = 2^14, 8 limbs of 50 bits, seed 0 (alpha = 1 exercises the single-P path)
 "$H" --logn 14 --bits 50,50,50,50,50,50,50,50 --special 1 --level 7 --seed 0 --steps 1 --out "$OUT/n14_ntt8x50.json"
 "$H" --logn 15 --bits 58,45,45,45,45,45,45,45,45,58,58 --special 2 --level 9 --seed 11 --steps 1,64 --out "$OUT/n15_l9_a2.json"

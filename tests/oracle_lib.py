@@ -30,6 +30,7 @@ def _load():
     sig = {
         "ora_create_coeff_modulus": (_int, [_sz, _vp, _sz, _vp]),
         "ora_minimal_primitive_root": (_u64, [_u64, _u64]),
+        "ora_fill_uniform": (None, [_vp, _sz, _u64, _u64]),
         "ora_fill_limbs": (None, [_vp, _sz, _vp, _sz, _u64, _u64, _u64]),
         "ora_limb_hash": (_u64, [_vp, _sz]),
         "ora_ctx_create": (_vp, [_sz, _vp, _sz, _sz]),
@@ -52,6 +53,7 @@ def _load():
         "ora_apply_galois": (None, [_vp, _sz, _u32, _vp, _vp]),
         "ora_hoist_rotations": (None, [_vp, _sz, _vp, _vp, _sz, _vp, _vp]),
         "ora_bsgs_mac": (None, [_vp, _sz, _sz, _vp, _vp, _vp]),
+        "ora_expand_single_chain": (None, [_vp, _sz, _vp, _vp]),
         "ora_add": (None, [_vp, _sz, _vp, _vp, _vp]),
         "ora_sub": (None, [_vp, _sz, _vp, _vp, _vp]),
         "ora_mul": (None, [_vp, _sz, _vp, _vp, _vp]),
@@ -222,6 +224,36 @@ class Oracle:
         LIB.ora_bsgs_mac(self.h, l, len(pts), _p(pp), _p(bp), _p(out))
         return out
 
+    def expand_single_chain(self, l, coeffs):
+        coeffs = np.ascontiguousarray(coeffs, dtype=np.int64)
+        out = np.empty((l, self.N), dtype=np.uint64)
+        LIB.ora_expand_single_chain(self.h, l, _p(coeffs), _p(out))
+        return out
+
+    def synth_signed(self, seed, buf, bits=40):
+        """signed centred coefficients in [-2^(bits-1), 2^(bits-1)): uniform draw minus the offset"""
+        u = np.empty(self.N, dtype=np.uint64)
+        LIB.ora_fill_uniform(_p(u), self.N, 1 << bits, (seed << 40) ^ (buf << 16))
+        return (u.astype(np.int64) - (1 << (bits - 1))).astype(np.int64)
+
+    def bsgs_matmul(self, l, x, diag_coeffs, M, G, keys_by_step):
+        """src/bsgs.cu:194-359 composed from the oracle's pieces; keys_by_step: step -> key digits"""
+        def rot(ct, step):
+            return self.apply_galois(l, self.galois_elt(step), keys_by_step[step], ct)
+        babies = [x]
+        for b in range(1, M):
+            bit = 1 << (b.bit_length() - 1)
+            babies.append(rot(babies[b - bit], bit))
+        def partial(g):
+            pts = [self.expand_single_chain(l, diag_coeffs[g * M + b]) for b in range(M)]
+            return self.bsgs_mac(l, pts, babies)
+        acc = partial(G - 1)
+        for g in range(G - 2, -1, -1):
+            acc = rot(acc, M)
+            p = partial(g)
+            acc = np.stack([self.add(acc[k], p[k]) for k in range(2)])
+        return self.rescale(l, acc)
+
     def add(self, a, b):
         a = np.ascontiguousarray(a, dtype=np.uint64)
         b = np.ascontiguousarray(b, dtype=np.uint64)
@@ -264,4 +296,10 @@ def golden_case_stages(o, case):
     outs = o.hoist_rotations(l, a, case["elts"], keys)
     for step, out in zip(case["steps"], outs):
         res[f"hoist_{step}"] = limb_hashes(out, N)
+    if case.get("bsgs"):
+        M, G = case["bsgs"]
+        diags = [o.synth_signed(seed, 3000 + d) for d in range(M * G)]
+        by_step = dict(zip(case["steps"], keys))
+        res["bsgs"] = limb_hashes(o.bsgs_matmul(l, a, diags, M, G, by_step), N)
+        res["expand_single_chain"] = limb_hashes(o.expand_single_chain(l, diags[0]), N)
     return res

@@ -168,3 +168,43 @@ def test_serialisation_round_trip_and_layout(env):
         ph.ciphertext().load(io.BytesIO(raw[:100]))
     with pytest.raises(ValueError):
         ph.relin_key().save(io.BytesIO())
+
+
+def test_bsgs_driver_matches_the_reference():
+    """bsgs_matmul_preencoded on synthetic single-chain diagonals against the reference's hashes"""
+    import glob, json, os
+    from gpu_helpers import load_case, hashes
+    paths = sorted(glob.glob(os.path.join(os.path.dirname(__file__), "golden", "*bsgs*.json")))
+    assert paths, "no BSGS golden record"
+    for path in paths:
+        case, ctx, o = load_case(path)
+        N, l, seed = o.N, case["level"], case["seed"]
+        M, G = case["bsgs"]
+        chain = o.size_Q - l + 1
+        keys = [ph.relin_key.from_numpy(ctx, o.synth_key(o.beta(l), seed, 100 + 8 * e)) for e in range(len(case["elts"]))]
+        glk = ph.galois_key.from_keys(keys)
+        x = ph.ciphertext.from_numpy(ctx, o.synth_ct(l, seed, 1), chain, SCALE)
+        diag_h = [o.synth_signed(seed, 3000 + d) for d in range(M * G)]
+        diags = ph.bsgs_diagonals([ph.single_chain_plaintext(c, SCALE) for c in diag_h], M * G, M, G)
+        assert ph.bsgs_required_steps(M) == case["steps"]
+        y = ph.bsgs_matmul_preencoded(ctx, glk, x, diags)
+        assert hashes(y.data, N) == case["hashes"]["bsgs"]
+        assert y.chain_index() == chain + 1 and y.scale() == SCALE
+        full = ph.expand_single_chain_to_full(ctx, diags.diagonals[0], chain)
+        assert hashes(full.data, N) == case["hashes"]["expand_single_chain"]
+        # round trip of the on-disk form of a single-chain plaintext
+        back = ph.scp_from_bytes(diags.diagonals[1].coeffs_bytes(), SCALE)
+        assert np.array_equal(back.coeffs.numpy(), diag_h[1])
+        with pytest.raises(ValueError, match="M\\*G must equal d_pad"):
+            ph.bsgs_apply_giants_with_babies(ctx, glk, [x] * M, ph.bsgs_diagonals(diags.diagonals, M * G + 1, M, G))
+
+
+def test_galois_key_fallback(env):
+    ctx, a = env["ctx"], env["a"]
+    g = ph.galois_key.from_keys([ph.relin_key() for _ in env["elts"]])  # every owned slot empty
+    with pytest.raises(ValueError, match="no owned key, no fallback"):
+        ph.rotate(ctx, a, 1, g)
+    g.set_fallback(0, env["glk"].get_relin_keys(0))
+    assert np.array_equal(ph.rotate(ctx, a, 1, g).numpy(), ph.rotate(ctx, a, 1, env["glk"]).numpy())
+    with pytest.raises(IndexError):
+        g.set_fallback(99, env["glk"].get_relin_keys(0))
