@@ -156,6 +156,12 @@ int b2_bsgs_mac(b2_ctx *ctx, size_t size_Ql, size_t M, const uint64_t *const *pt
 int b2_expand_single_chain(b2_ctx *ctx, size_t size_Ql, const int64_t *d_signed, uint64_t *d_out,
                            void *stream);
 
+/* the same over any limb range [first_prime, first_prime + n_limbs), optionally left in coefficient
+ * form: what the samplers and the encoder of the reference do per limb when they reduce a small
+ * signed value into every prime (src/rns_base.cu:49-73, src/prng.cu:142-240) */
+int b2_expand_signed(b2_ctx *ctx, size_t first_prime, size_t n_limbs, const int64_t *d_signed,
+                     uint64_t *d_out, int to_ntt, void *stream);
+
 /* replaces add/sub/multiply_rns_poly (src/polymath.cu:17-180) over [n_limbs][N], limb i on prime i;
  * op: 0 add, 1 sub, 2 multiply, 3 negate (d_b ignored). d_out may alias an input. */
 int b2_poly_op(b2_ctx *ctx, int op, size_t n_limbs, const uint64_t *d_a, const uint64_t *d_b,

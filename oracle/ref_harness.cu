@@ -9,6 +9,8 @@
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <cmath>
+#include <fstream>
 #include <functional>
 #include <sstream>
 #include <string>
@@ -101,7 +103,7 @@ int main(int argc, char **argv) {
     std::vector<int> bsgs;  // {baby steps M, giant steps G}: also run the BSGS matrix-vector driver
     uint64_t seed = 1;
     std::vector<int> bits = {50, 36, 36, 36, 36, 36, 50, 50}, steps = {1, 2, -1};
-    std::string out = "case.json";
+    std::string out = "case.json", interop_write, interop_read, interop_prefix = "b2";
     for (int i = 1; i + 1 < argc; i += 2) {
         std::string k = argv[i];
         const char *v = argv[i + 1];
@@ -113,6 +115,9 @@ int main(int argc, char **argv) {
         else if (k == "--steps") steps = parse_ints(v);
         else if (k == "--out") out = v;
         else if (k == "--bsgs") bsgs = parse_ints(v);
+        else if (k == "--interop-write") interop_write = v;
+        else if (k == "--interop-read") interop_read = v;
+        else if (k == "--interop-prefix") interop_prefix = v;
         else if (k == "--time") time_iters = atoi(v);
         else { fprintf(stderr, "unknown arg %s\n", argv[i]); return 2; }
     }
@@ -185,6 +190,44 @@ int main(int argc, char **argv) {
     }
 
     const double scale = 1099511627776.0; // 2^40
+    // ---- interchange with the other library through save()/load() bytes --------------------------------
+    // message: slot j = cos(j) + i sin(2j)/2. --interop-write DIR: the reference makes a secret key,
+    // encodes, encrypts and saves ref_sk.bin / ref_ct.bin. --interop-read DIR: the reference loads
+    // b2_sk.bin / b2_ct.bin written by the other library, decrypts, decodes and prints the error.
+    if (!interop_write.empty() || !interop_read.empty()) {
+        PhantomCKKSEncoder encoder(context);
+        const size_t slots = encoder.slot_count();
+        std::vector<cuDoubleComplex> z(slots);
+        for (size_t j = 0; j < slots; j++) z[j] = make_cuDoubleComplex(cos((double) j), sin(2.0 * j) / 2);
+        if (!interop_write.empty()) {
+            PhantomSecretKey sk(context);
+            PhantomPlaintext pt;
+            encoder.encode(context, z, scale, pt);
+            PhantomCiphertext ct;
+            sk.encrypt_symmetric(context, pt, ct);
+            std::ofstream f1(interop_write + "/ref_sk.bin", std::ios::binary), f2(interop_write + "/ref_ct.bin", std::ios::binary);
+            sk.save(f1);
+            ct.save(f2);
+            printf("interop: wrote ref_sk.bin ref_ct.bin\n");
+        }
+        if (!interop_read.empty()) {
+            std::ifstream f1(interop_read + "/" + interop_prefix + "_sk.bin", std::ios::binary), f2(interop_read + "/" + interop_prefix + "_ct.bin", std::ios::binary);
+            if (!f1 || !f2) { fprintf(stderr, "interop: b2 files missing\n"); return 3; }
+            PhantomSecretKey sk;
+            sk.load(f1);
+            PhantomCiphertext ct;
+            ct.load(f2);
+            PhantomPlaintext pt = sk.decrypt(context, ct);
+            std::vector<cuDoubleComplex> got;
+            encoder.decode(context, pt, got);
+            double err = 0;
+            for (size_t j = 0; j < slots; j++)
+                err = std::max(err, std::hypot(got[j].x - z[j].x, got[j].y - z[j].y));
+            printf("interop: reference decrypts the other library's ciphertext, max error %.3e\n", err);
+            return err < 1e-6 ? 0 : 4;
+        }
+        return 0;
+    }
     auto &tool = context.get_context_data(chain).gpu_rns_tool();
 
     // ---- the three stages of the key switch, separately ---------------------------------------

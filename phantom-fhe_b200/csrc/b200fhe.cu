@@ -1083,10 +1083,10 @@ __global__ void __launch_bounds__(256) galois_gather_kernel(const uint64_t *__re
 // Single-chain plaintext expansion (src/bootstrap.cu:660-686, light_pt_expand_per_tower_kernel):
 // one signed, centred int64 coefficient vector -> its residue in each of n_limbs primes.
 __global__ void __launch_bounds__(256) expand_signed_kernel(const int64_t *__restrict__ src, uint64_t *__restrict__ dst, const Mod *mod, uint32_t N,
-                                                           uint32_t n_limbs) {
+                                                           uint32_t n_limbs, uint32_t first_prime) {
     const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= (size_t)n_limbs * N) return;
-    const Mod md = mod[idx / N];
+    const Mod md = mod[first_prime + idx / N];
     const int64_t c = src[idx % N];
     const uint64_t mag = c >= 0 ? (uint64_t)c : (uint64_t)0 - (uint64_t)c;
     u128 v{mag, 0};
@@ -1544,18 +1544,27 @@ extern "C" int b2_bsgs_mac(b2_ctx *c, size_t l, size_t M, const uint64_t *const 
     return B2_OK;
 }
 
+extern "C" int b2_expand_signed(b2_ctx *c, size_t first_prime, size_t n_limbs, const int64_t *d_signed, uint64_t *d_out, int to_ntt,
+                                void *stream) {
+    CHECK_CTX(c);
+    if (!d_signed || !d_out) return fail(B2_EINVAL, "expand_signed: null pointer");
+    if (n_limbs < 1 || first_prime + n_limbs > c->size_QP) return fail(B2_EINVAL, "expand_signed: limb range outside the modulus chain");
+    cudaStream_t s = (cudaStream_t)stream;
+    const size_t n = n_limbs * c->N;
+    {
+        LaunchScope ls(c, s, "expand_signed");
+        expand_signed_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(d_signed, d_out, c->d_mod, (uint32_t)c->N, (uint32_t)n_limbs,
+                                                                        (uint32_t)first_prime);
+        LAUNCH_CHECK("expand_signed_kernel");
+    }
+    if (!to_ntt) return B2_OK;
+    return run_fwd(c, d_out, d_out, nullptr, (uint32_t)n_limbs, (uint32_t)first_prime, EpiStore{}, s);
+}
+
 extern "C" int b2_expand_single_chain(b2_ctx *c, size_t l, const int64_t *d_signed, uint64_t *d_out, void *stream) {
     CHECK_CTX(c);
     CHECK_LEVEL(c, l);
-    if (!d_signed || !d_out) return fail(B2_EINVAL, "expand_single_chain: null pointer");
-    cudaStream_t s = (cudaStream_t)stream;
-    const size_t n = l * c->N;
-    {
-        LaunchScope ls(c, s, "expand_signed");
-        expand_signed_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(d_signed, d_out, c->d_mod, (uint32_t)c->N, (uint32_t)l);
-        LAUNCH_CHECK("expand_signed_kernel");
-    }
-    return run_fwd(c, d_out, d_out, nullptr, (uint32_t)l, 0, EpiStore{}, s);
+    return b2_expand_signed(c, 0, l, d_signed, d_out, 1, stream);
 }
 
 extern "C" int b2_poly_op(b2_ctx *c, int op, size_t n_limbs, const uint64_t *d_a, const uint64_t *d_b, uint64_t *d_out, void *stream) {

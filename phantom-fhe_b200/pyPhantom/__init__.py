@@ -151,7 +151,7 @@ class context:
 
     def __del__(self):
         h = getattr(self, "_h", None)
-        if h:
+        if h and LIB is not None:  # LIB is already gone when the interpreter shuts down
             LIB.b2_ctx_destroy(h)
             self._h = None
 
@@ -201,7 +201,7 @@ class context:
 # data carriers (include/ciphertext.h, include/plaintext.h, include/secretkey.h)
 # ---------------------------------------------------------------------------------------------
 def _to_device(arr, device):
-    a = np.ascontiguousarray(arr, dtype=np.uint64).view(np.int64)
+    a = np.array(arr, dtype=np.uint64, order="C", copy=True).view(np.int64)  # own, writable copy for torch
     return torch.from_numpy(a).to(device=device, non_blocking=False)
 
 
@@ -687,6 +687,10 @@ def hoist_rotations(context, ct, glk, steps):
     check(LIB.b2_hoist_rotations(ctx._h, l, ct.data.data_ptr(), elts.ctypes.data, len(steps), ksk.ctypes.data, n_evk,
                                  out_ptrs.ctypes.data, ws.data_ptr(), nbytes, _stream()))
     return [ct._like(o) for o in outs]
+
+
+from .keys import public_key, secret_key  # noqa: E402,F401
+from .encoder import ckks_encoder  # noqa: E402,F401
 
 
 # ---------------------------------------------------------------------------------------------

@@ -1,0 +1,202 @@
+"""Key generation, symmetric encryption and decryption (binding.cu:77-98; src/secretkey.cu).
+
+Sampling is done on the host with numpy (key generation is set-up work, not the hot path); every
+polynomial operation - reduction into the limbs, NTT, products, sums - is a call into the C ABI.
+The reference seeds its samplers from std::random_device (include/prng.cuh:12-21), so keys are not
+reproducible there either: what is kept is the distributions (ternary or fixed-Hamming-weight
+secret, centred-binomial error with 21 coin pairs, uniform masks), the algebra
+(pk = (-(a s + e), a); digit d of a switching key adds P s' on the Q limbs of digit d,
+src/secretkey.cu:354-398, src/polymath.cu:317-337) and the save()/load() byte layouts, so keys and
+ciphertexts made here work with the reference's evaluator and the other way round.
+"""
+import struct
+
+import numpy as np
+import torch
+
+from ._native import LIB, check
+
+_SK_HDR = struct.Struct("<QQQ")  # sk_max_power, N, coeff_mod_size (include/secretkey.h:537-554)
+
+
+def _stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _poly(ctx, op, n_limbs, a, b, out):
+    check(LIB.b2_poly_op(ctx._h, op, n_limbs, a.data_ptr(), 0 if b is None else b.data_ptr(), out.data_ptr(), _stream()))
+
+
+def _expand(ctx, coeffs_i64, n_limbs, ntt=True):
+    """signed int64[N] on the host -> [n_limbs][N] residues (limb i <-> prime i), NTT form by default"""
+    d = torch.from_numpy(np.ascontiguousarray(coeffs_i64, dtype=np.int64)).to(ctx.device)
+    out = ctx.empty(n_limbs)
+    check(LIB.b2_expand_signed(ctx._h, 0, n_limbs, d.data_ptr(), out.data_ptr(), 1 if ntt else 0, _stream()))
+    return out
+
+
+def _uniform(ctx, rng, n_limbs):
+    """[n_limbs][N] uniform residues (already a valid NTT-form polynomial)"""
+    host = np.stack([rng.integers(0, int(q), ctx.N, dtype=np.uint64) for q in ctx.primes[:n_limbs]])
+    return torch.from_numpy(host.view(np.int64)).to(ctx.device)
+
+
+def _error(ctx, rng, n_limbs):
+    """centred binomial, 21 coin pairs: standard deviation sqrt(21/2) = 3.24 (include/prng.cuh:67-76)"""
+    e = rng.binomial(21, 0.5, ctx.N).astype(np.int64) - rng.binomial(21, 0.5, ctx.N).astype(np.int64)
+    return _expand(ctx, e, n_limbs)
+
+
+class public_key:
+    def __init__(self):
+        self.pk = None  # ciphertext at the key level
+
+    def save(self, stream):
+        if self.pk is None:
+            raise ValueError("PhantomPublicKey has not been generated")
+        self.pk.save(stream)
+
+    def load(self, stream, device=None):
+        from . import ciphertext
+        self.pk = ciphertext().load(stream, device)
+        return self
+
+
+class secret_key:
+    """binding.cu:77-98. `secret_key(ctx)` draws a uniform ternary secret; `generate_sparse` replaces it
+    by one with exactly `hamming_weight` non-zero (+-1) coefficients (src/secretkey.cu:513-590)."""
+
+    def __init__(self, ctx=None, seed=None):
+        self._rng = np.random.default_rng(seed)
+        self.data = None  # [size_QP][N], NTT form, key level
+        self.coeffs = None
+        if ctx is not None:
+            self._set(ctx, self._rng.integers(-1, 2, ctx.N).astype(np.int64))
+
+    def _set(self, ctx, coeffs):
+        self.coeffs = coeffs
+        self.data = _expand(ctx, coeffs, ctx.size_QP)
+
+    def generate_sparse(self, context, hamming_weight):
+        ctx, h = context, int(hamming_weight)
+        if not 0 < h <= ctx.N:
+            raise ValueError("hamming_weight out of range")
+        c = np.zeros(ctx.N, dtype=np.int64)
+        pos = self._rng.choice(ctx.N, size=h, replace=False)
+        c[pos] = self._rng.choice(np.array([-1, 1], dtype=np.int64), size=h)
+        self._set(ctx, c)
+
+    # ---- encryption of zero under this secret: (-(a s + e), a) over the first n_limbs primes -------
+    def _encrypt_zero(self, ctx, n_limbs):
+        a = _uniform(ctx, self._rng, n_limbs)
+        e = _error(ctx, self._rng, n_limbs)
+        c0 = ctx.empty(n_limbs)
+        _poly(ctx, 2, n_limbs, a, self.data[:n_limbs], c0)
+        _poly(ctx, 0, n_limbs, c0, e, c0)
+        _poly(ctx, 3, n_limbs, c0, None, c0)
+        return torch.stack([c0, a])
+
+    def gen_publickey(self, ctx):
+        from . import ciphertext
+        pk = public_key()
+        ct = ciphertext()
+        ct._chain_index, ct._size, ct._N, ct._limbs = 0, 2, ctx.N, ctx.size_QP
+        ct.data = self._encrypt_zero(ctx, ctx.size_QP)
+        pk.pk = ct
+        return pk
+
+    def _kswitch_key(self, ctx, new_key):
+        """src/secretkey.cu:354-398: one (-(a s + e) + P s' [limb in digit d], a) per digit"""
+        from . import ciphertext, relin_key
+        a, sQ, N = ctx.size_P, ctx.size_Q, ctx.N
+        dnum = (sQ + a - 1) // a
+        P = 1
+        for p in ctx.primes[sQ:]:
+            P *= int(p)
+        out = relin_key()
+        for d in range(dnum):
+            data = self._encrypt_zero(ctx, ctx.size_QP)
+            lo, hi = d * a, min((d + 1) * a, sQ)
+            fac = torch.from_numpy(np.stack([np.full(N, P % int(ctx.primes[i]), dtype=np.uint64) for i in range(lo, hi)])
+                                   .view(np.int64)).to(ctx.device)
+            # multiply limb i of new_key by (P mod q_i) and add into c0's limb i
+            self._scaled_add(ctx, data[0], new_key, fac, lo, hi)
+            ct = ciphertext()
+            ct._chain_index, ct._size, ct._N, ct._limbs = 0, 2, N, ctx.size_QP
+            ct.data = data
+            out.public_keys.append(ct)
+        return out
+
+    @staticmethod
+    def _scaled_add(ctx, c0, new_key, fac, lo, hi):
+        # b2_poly_op works on limbs [0, n): operate on the prefix [0, hi) of scratch copies so that limb i
+        # meets prime i, then keep only [lo, hi)
+        N = ctx.N
+        full_fac = torch.zeros(hi, N, dtype=torch.int64, device=ctx.device)
+        full_fac[lo:hi] = fac
+        prod = ctx.empty(hi)
+        _poly(ctx, 2, hi, new_key[:hi].contiguous(), full_fac, prod)
+        summed = ctx.empty(hi)
+        _poly(ctx, 0, hi, c0[:hi].contiguous(), prod, summed)
+        c0[lo:hi] = summed[lo:hi]
+
+    def gen_relinkey(self, ctx):
+        s2 = ctx.empty(ctx.size_QP)
+        _poly(ctx, 2, ctx.size_QP, self.data, self.data, s2)
+        return self._kswitch_key(ctx, s2)
+
+    def create_one_galois_key(self, ctx, galois_elt_idx, target_chain_index=0):
+        elt = ctx.galois_elts[galois_elt_idx]
+        rot = ctx.empty(ctx.size_QP)
+        check(LIB.b2_galois_permute(ctx._h, elt, self.data.data_ptr(), rot.data_ptr(), ctx.size_QP, _stream()))
+        return self._kswitch_key(ctx, rot)
+
+    def create_galois_keys(self, ctx):
+        """one key per Galois element of the context, same order (src/secretkey.cu:642-682)"""
+        from . import galois_key
+        return galois_key.from_keys([self.create_one_galois_key(ctx, i) for i in range(len(ctx.galois_elts))])
+
+    # ---- data path ------------------------------------------------------------------------------------
+    def encrypt_symmetric(self, ctx, pt):
+        """(c0, c1) = (-(a s + e) + m, a) at the plaintext's level (src/secretkey.cu:236-299, 771-812)"""
+        from . import ciphertext
+        l = pt._limbs
+        data = self._encrypt_zero(ctx, l)
+        _poly(ctx, 0, l, data[0], pt.data, data[0])
+        ct = ciphertext()
+        ct._chain_index, ct._size, ct._N, ct._limbs, ct._scale = pt._chain_index, 2, ctx.N, l, pt._scale
+        ct.data = data
+        return ct
+
+    def decrypt(self, ctx, ct):
+        """m = c0 + c1 s (+ c2 s^2) on the first l limbs of the key-level secret (src/secretkey.cu:883-919)"""
+        from . import plaintext
+        l = ct._limbs
+        s = self.data[:l]
+        acc = ct.data[0].clone()
+        t = ctx.empty(l)
+        sp = s
+        for k in range(1, ct._size):
+            _poly(ctx, 2, l, ct.data[k], sp, t)
+            _poly(ctx, 0, l, acc, t, acc)
+            if k + 1 < ct._size:
+                nxt = ctx.empty(l)
+                _poly(ctx, 2, l, sp.contiguous(), s, nxt)
+                sp = nxt
+        pt = plaintext()
+        pt._chain_index, pt._N, pt._limbs, pt._scale = ct._chain_index, ctx.N, l, ct._scale
+        pt.data = acc
+        return pt
+
+    # ---- serialisation ------------------------------------------------------------------------------------
+    def save(self, stream):
+        n_limbs, N = self.data.shape
+        stream.write(_SK_HDR.pack(1, N, n_limbs))
+        stream.write(self.data.cpu().numpy().view(np.uint64).tobytes())
+
+    def load(self, stream, device=None):
+        powers, N, n_limbs = _SK_HDR.unpack(stream.read(_SK_HDR.size))
+        # the reference keeps s, s^2, ... once it has made relinearisation keys; only s is needed here
+        arr = np.frombuffer(stream.read(powers * n_limbs * N * 8), dtype=np.uint64).reshape(powers, n_limbs, N)[0]
+        self.data = torch.from_numpy(arr.view(np.int64).copy()).to(torch.cuda.current_device() if device is None else device)
+        return self

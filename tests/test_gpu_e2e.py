@@ -1,0 +1,172 @@
+"""End-to-end CKKS on the GPU through the pyPhantom surface: encode, encrypt, evaluate, decrypt,
+decode, compared with the same arithmetic on the clear vectors. Floating point enters only through
+the encoder, so the tolerances are the reference's own for the same flows: round trip 1e-7 and
+multiply+rescale 1e-5 (test/ckks_engine_test.cu:56, :96), rotations and matrix-vector products 1e-3
+(examples/3_ckks.cu:18-25, python/llm_project/blocks/bsgs_test.py:84-89)."""
+import io
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+import pyPhantom as ph
+
+N = 1 << 13
+SCALE = 2.0 ** 40
+
+
+@pytest.fixture(scope="module")
+def kit():
+    steps = [1, 2, 4, 8, -1]
+    parms = ph.params(ph.scheme_type.ckks)
+    parms.set_poly_modulus_degree(N)
+    parms.set_coeff_modulus(ph.create_coeff_modulus(N, [60, 40, 40, 40, 40, 60, 60]))
+    parms.set_special_modulus_size(2)
+    parms.set_galois_elts(ph.get_elts_from_steps(steps, N) + [2 * N - 1])
+    ctx = ph.context(parms)
+    sk = ph.secret_key(ctx, seed=1234)
+    enc = ph.ckks_encoder(ctx)
+    rng = np.random.default_rng(7)
+    x = rng.uniform(-1, 1, enc.slot_count()) + 1j * rng.uniform(-1, 1, enc.slot_count())
+    y = rng.uniform(-1, 1, enc.slot_count()) + 1j * rng.uniform(-1, 1, enc.slot_count())
+    return dict(ctx=ctx, sk=sk, enc=enc, rlk=sk.gen_relinkey(ctx), glk=sk.create_galois_keys(ctx), x=x, y=y, steps=steps,
+                cx=sk.encrypt_symmetric(ctx, enc.encode_complex_vector(ctx, x, SCALE)),
+                cy=sk.encrypt_symmetric(ctx, enc.encode_complex_vector(ctx, y, SCALE)))
+
+
+def _dec(kit, ct):
+    return kit["enc"].decode_complex_vector(kit["ctx"], kit["sk"].decrypt(kit["ctx"], ct))
+
+
+def test_encode_decode_and_encrypt_decrypt_round_trip(kit):
+    ctx, enc = kit["ctx"], kit["enc"]
+    assert enc.slot_count() == N // 2
+    pt = enc.encode_complex_vector(ctx, kit["x"], SCALE)
+    assert np.max(np.abs(enc.decode_complex_vector(ctx, pt) - kit["x"])) < 1e-9
+    assert np.max(np.abs(_dec(kit, kit["cx"]) - kit["x"])) < 1e-7
+    short = enc.encode_double_vector(ctx, [1.0, 2.0, 3.0], SCALE)
+    d = enc.decode_double_vector(ctx, short)
+    assert np.allclose(d[:3], [1, 2, 3], atol=1e-9) and np.max(np.abs(d[3:])) < 1e-9
+    with pytest.raises(ValueError, match="exceeds max slots"):
+        enc.encode_double_vector(ctx, np.zeros(N), SCALE)
+    with pytest.raises(ValueError, match="empty"):
+        enc.encode_double_vector(ctx, [], SCALE)
+
+
+def test_add_multiply_rescale(kit):
+    ctx = kit["ctx"]
+    assert np.max(np.abs(_dec(kit, ph.add(ctx, kit["cx"], kit["cy"])) - (kit["x"] + kit["y"]))) < 1e-7
+    m = ph.rescale_to_next(ctx, ph.multiply_and_relin(ctx, kit["cx"], kit["cy"], kit["rlk"]))
+    assert m.chain_index() == 2 and abs(np.log2(m.scale()) - 40) < 0.01
+    assert np.max(np.abs(_dec(kit, m) - kit["x"] * kit["y"])) < 1e-5
+    # depth 3: ((x*y)*x) then squared, all the way down the chain
+    x2 = ph.mod_switch_to(ctx, kit["cx"], 2)
+    x2.set_scale(m.scale())  # same level; scales differ by a factor 2^40 / q_last, keep it exact in the reference sense
+    x2 = kit["sk"].encrypt_symmetric(ctx, kit["enc"].encode_complex_vector(ctx, kit["x"], m.scale(), 2))
+    m3 = ph.rescale_to_next(ctx, ph.multiply_and_relin(ctx, m, x2, kit["rlk"]))
+    assert np.max(np.abs(_dec(kit, m3) - kit["x"] * kit["y"] * kit["x"])) < 1e-4
+    # unrelinearised product decrypts with s^2 as well
+    m_raw = ph.multiply(ctx, kit["cx"], kit["cy"])
+    assert np.max(np.abs(_dec(kit, m_raw) - kit["x"] * kit["y"])) < 1e-5
+    pt = kit["enc"].encode_complex_vector(ctx, kit["y"], SCALE)
+    mp = ph.rescale_to_next(ctx, ph.multiply_plain(ctx, kit["cx"], pt))
+    assert np.max(np.abs(_dec(kit, mp) - kit["x"] * kit["y"])) < 1e-5
+
+
+def test_rotations_conjugation_and_hoisting(kit):
+    ctx = kit["ctx"]
+    for s in kit["steps"]:
+        got = _dec(kit, ph.rotate(ctx, kit["cx"], s, kit["glk"]))
+        assert np.max(np.abs(got - np.roll(kit["x"], -s))) < 1e-3, s
+    got = _dec(kit, ph.rotate(ctx, kit["cx"], 7, kit["glk"]))  # NAF chain 8 - 1
+    assert np.max(np.abs(got - np.roll(kit["x"], -7))) < 1e-3
+    conj = _dec(kit, ph.apply_galois(ctx, kit["cx"], 2 * N - 1, kit["glk"]))
+    assert np.max(np.abs(conj - np.conj(kit["x"]))) < 1e-3
+    outs = ph.hoist_rotations(ctx, kit["cx"], kit["glk"], [1, 2, 8])
+    for s, o in zip([1, 2, 8], outs):
+        assert np.max(np.abs(_dec(kit, o) - np.roll(kit["x"], -s))) < 1e-3
+    low = ph.mod_switch_to(ctx, kit["cx"], 4)  # two limbs left: one digit only
+    assert np.max(np.abs(_dec(kit, ph.rotate(ctx, low, 2, kit["glk"])) - np.roll(kit["x"], -2))) < 1e-3
+
+
+def test_sparse_secret_and_key_serialisation(kit):
+    ctx, enc = kit["ctx"], kit["enc"]
+    sk = ph.secret_key(ctx, seed=5)
+    sk.generate_sparse(ctx, 192)
+    assert int(np.count_nonzero(sk.coeffs)) == 192 and set(np.unique(sk.coeffs)) <= {-1, 0, 1}
+    ct = sk.encrypt_symmetric(ctx, enc.encode_complex_vector(ctx, kit["x"], SCALE))
+    buf = io.BytesIO()
+    sk.save(buf)
+    assert len(buf.getvalue()) == 24 + ctx.size_QP * N * 8
+    sk2 = ph.secret_key().load(io.BytesIO(buf.getvalue()))
+    assert np.max(np.abs(enc.decode_complex_vector(ctx, sk2.decrypt(ctx, ct)) - kit["x"])) < 1e-7
+    pk = sk.gen_publickey(ctx)
+    pb = io.BytesIO()
+    pk.save(pb)
+    assert ph.public_key().load(io.BytesIO(pb.getvalue())).pk.coeff_modulus_size() == ctx.size_QP
+
+
+def test_bsgs_matrix_vector_product(kit):
+    ctx, enc, sk = kit["ctx"], kit["enc"], kit["sk"]
+    d, M, G = 16, 4, 4
+    rng = np.random.default_rng(11)
+    W = rng.normal(0, 0.5, (d, d))
+    v = rng.normal(0, 1, d)
+    slots = enc.slot_count()
+    xv = np.tile(v, slots // d)
+    cx = sk.encrypt_symmetric(ctx, enc.encode_double_vector(ctx, xv, SCALE))
+    diags = []
+    for g in range(G):
+        for b in range(M):
+            k = g * M + b
+            diag = np.array([W[i, (i + k) % d] for i in range(d)])
+            diag = np.roll(np.tile(diag, slots // d), g * M)  # pre-rotated by -g*M (src/bsgs.cu:131-176)
+            pt = enc.encode_double_vector(ctx, diag, SCALE)
+            pt0 = pt.data[:1].clone()
+            ph._native.check(ph._native.LIB.b2_ntt_inverse(ctx._h, pt0.data_ptr(), 1, 0, torch.cuda.current_stream().cuda_stream))
+            c = pt0.cpu().numpy().view(np.uint64)[0].astype(object)
+            q0 = int(ctx.primes[0])
+            c = np.where(c >= (q0 + 1) // 2, c - q0, c)
+            diags.append(ph.single_chain_plaintext(np.array([int(t) for t in c], dtype=np.int64), SCALE))
+    y = ph.bsgs_matmul_preencoded(ctx, kit["glk"], cx, ph.bsgs_diagonals(diags, d, M, G))
+    got = enc.decode_double_vector(ctx, sk.decrypt(ctx, y))[:d]
+    assert np.max(np.abs(got - W @ v)) < 1e-3
+    assert y.chain_index() == 2
+
+
+def test_interchange_with_the_reference_library(tmp_path):
+    """Both directions through save()/load() bytes, on this GPU: the reference's secret key and
+    ciphertext decrypt and decode here, and what this library encrypts decrypts in the reference.
+    Needs oracle/_ref/ref_harness (the reference compiled from its own sources)."""
+    import os
+    import subprocess
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    harness = os.path.join(root, "oracle", "_ref", "ref_harness")
+    if not os.path.exists(harness):
+        pytest.skip("reference harness not built")
+    n, bits, special = 1 << 13, [60, 40, 40, 40, 60, 60], 2
+    args = [harness, "--logn", "13", "--bits", ",".join(map(str, bits)), "--special", str(special), "--steps", "1"]
+    subprocess.run(args + ["--interop-write", str(tmp_path)], check=True, capture_output=True, timeout=300)
+    parms = ph.params(ph.scheme_type.ckks)
+    parms.set_poly_modulus_degree(n)
+    parms.set_coeff_modulus(ph.create_coeff_modulus(n, bits))
+    parms.set_special_modulus_size(special)
+    parms.set_galois_elts([ph.get_elt_from_step(1, n)])
+    ctx = ph.context(parms)
+    enc = ph.ckks_encoder(ctx)
+    j = np.arange(enc.slot_count(), dtype=np.float64)
+    z = np.cos(j) + 0.5j * np.sin(2 * j)
+    sk = ph.secret_key().load(open(tmp_path / "ref_sk.bin", "rb"))
+    ct = ph.ciphertext().load(open(tmp_path / "ref_ct.bin", "rb"))
+    assert ct.chain_index() == 1 and ct.scale() == SCALE
+    assert np.max(np.abs(enc.decode_complex_vector(ctx, sk.decrypt(ctx, ct)) - z)) < 1e-6
+    mine = ph.secret_key(ctx, seed=99)
+    with open(tmp_path / "b2_sk.bin", "wb") as f:
+        mine.save(f)
+    with open(tmp_path / "b2_ct.bin", "wb") as f:
+        mine.encrypt_symmetric(ctx, enc.encode_complex_vector(ctx, z, SCALE)).save(f)
+    res = subprocess.run(args + ["--interop-read", str(tmp_path)], capture_output=True, text=True, timeout=300)
+    assert res.returncode == 0, res.stdout + res.stderr
+    assert "max error" in res.stdout
