@@ -165,8 +165,13 @@ def test_interchange_with_the_reference_library(tmp_path):
     mine = ph.secret_key(ctx, seed=99)
     with open(tmp_path / "b2_sk.bin", "wb") as f:
         mine.save(f)
+    my_ct = mine.encrypt_symmetric(ctx, enc.encode_complex_vector(ctx, z, SCALE))
     with open(tmp_path / "b2_ct.bin", "wb") as f:
-        mine.encrypt_symmetric(ctx, enc.encode_complex_vector(ctx, z, SCALE)).save(f)
+        my_ct.save(f)
     res = subprocess.run(args + ["--interop-read", str(tmp_path)], capture_output=True, text=True, timeout=300)
     assert res.returncode == 0, res.stdout + res.stderr
-    assert "max error" in res.stdout
+    line = [ln for ln in res.stdout.splitlines() if ln.startswith("interop-plain:")][0]
+    from oracle_lib import limb_hashes
+    want = limb_hashes(mine.decrypt(ctx, my_ct).data.cpu().numpy().view(np.uint64), n)
+    assert line.split()[1:] == want, "the reference decrypts this library's bytes to a different plaintext"
+    assert np.max(np.abs(enc.decode_complex_vector(ctx, mine.decrypt(ctx, my_ct)) - z)) < 1e-6
