@@ -109,6 +109,14 @@ int b2_multiply_and_relin(b2_ctx *ctx, size_t size_Ql, const uint64_t *d_a, cons
 int b2_rescale(b2_ctx *ctx, size_t size_Ql, size_t n_poly, const uint64_t *d_in, uint64_t *d_out,
                void *d_ws, size_t ws_bytes, void *stream);
 
+/* b2_rescale with the remainder of the dropped prime taken centred, so that every coefficient is
+ * rounded to nearest instead of floored. No counterpart in the reference (its rescale, src/rns.cu:
+ * 1128-1183, adds no rounding offset); the bootstrapping pipeline uses it because the half-unit bias
+ * of flooring, summed over all coefficients, is what limits the precision of EvalRound. Same
+ * arguments and workspace as b2_rescale. */
+int b2_rescale_rounded(b2_ctx *ctx, size_t size_Ql, size_t n_poly, const uint64_t *d_in,
+                       uint64_t *d_out, void *d_ws, size_t ws_bytes, void *stream);
+
 /* No counterpart in the reference (which takes every scratch buffer from cudaMallocAsync).
  * Same result as b2_rescale, for callers that cannot supply scratch and must not allocate: a
  * process whose device memory is already fully reserved by another allocator, or a thread that
@@ -166,6 +174,13 @@ int b2_expand_signed(b2_ctx *ctx, size_t first_prime, size_t n_limbs, const int6
  * op: 0 add, 1 sub, 2 multiply, 3 negate (d_b ignored). d_out may alias an input. */
 int b2_poly_op(b2_ctx *ctx, int op, size_t n_limbs, const uint64_t *d_a, const uint64_t *d_b,
                uint64_t *d_out, void *stream);
+
+/* per-limb integer constants over [n_limbs][N], limb i on prime i: op 0 adds h_scalars[i] to every
+ * value of limb i (in NTT form that is adding the constant polynomial h_scalars[i]); op 1 multiplies
+ * limb i by h_scalars[i] (replaces multiply_scalar_per_tower_kernel, src/bootstrap.cu:1535-1565).
+ * h_scalars is a HOST array of n_limbs (<= 64) reduced residues. d_out may alias d_a. */
+int b2_poly_scalar(b2_ctx *ctx, int op, size_t n_limbs, const uint64_t *d_a, const uint64_t *h_scalars,
+                   uint64_t *d_out, void *stream);
 
 /* RNS-limb sharding of one key switch over `world` GPUs (no counterpart in the reference, which
  * has no multi-GPU path; replaces keyswitch_inplace, src/eval_key_switch.cu:294-381, on a slice).

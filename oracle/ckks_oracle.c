@@ -471,6 +471,30 @@ void ora_rescale(const ora_ctx *c, size_t size_Ql, size_t n_poly, const uint64_t
     }
 }
 
+/* The same with the remainder of the dropped prime taken centred (v > q_last/2 stands for v - q_last),
+ * so that coefficients are rounded to nearest. Not in the reference: it states what
+ * b2_rescale_rounded computes, for the parity test of that entry point. */
+void ora_rescale_rounded(const ora_ctx *c, size_t size_Ql, size_t n_poly, const uint64_t *in, uint64_t *out) {
+    size_t N = c->N, last = size_Ql - 1;
+    uint64_t qlast = c->q[last], half = qlast >> 1;
+    for (size_t p = 0; p < n_poly; p++) {
+        const uint64_t *ci = in + p * size_Ql * N;
+        uint64_t *co = out + p * last * N;
+        uint64_t *r = (uint64_t *)malloc(N * sizeof(uint64_t));
+        memcpy(r, ci + last * N, N * sizeof(uint64_t));
+        ntt_inv_limb(r, N, qlast, c->itw[last], c->ninv[last]);
+#pragma omp parallel for schedule(dynamic)
+        for (size_t j = 0; j < last; j++) {
+            uint64_t q = c->q[j], inv = ora_invmod(qlast % q, q);
+            uint64_t *d = co + j * N;
+            for (size_t i = 0; i < N; i++) d[i] = r[i] > half ? submod(r[i] % q, qlast % q, q) : r[i] % q;
+            ntt_fwd_limb(d, N, q, c->tw[j]);
+            for (size_t i = 0; i < N; i++) d[i] = ora_mulmod(submod(ci[j * N + i], d[i], q), inv, q);
+        }
+        free(r);
+    }
+}
+
 /* include/galois.cuh:16-49 */
 uint32_t ora_galois_elt_from_step(int step, size_t N) {
     uint32_t n = (uint32_t)N, m = 2 * n;

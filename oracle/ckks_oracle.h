@@ -94,6 +94,7 @@ void ora_multiply_and_relin(const ora_ctx *c, size_t size_Ql, const uint64_t *a,
 /* src/rns.cu:1128-1183: in [n_poly][l][N] -> out [n_poly][l-1][N], floor-style RNS rescale */
 void ora_rescale(const ora_ctx *c, size_t size_Ql, size_t n_poly, const uint64_t *in,
                  uint64_t *out);
+void ora_rescale_rounded(const ora_ctx *c, size_t size_Ql, size_t n_poly, const uint64_t *in, uint64_t *out);
 /* include/galois.cuh:16-49 */
 uint32_t ora_galois_elt_from_step(int step, size_t N);
 /* include/galois.cuh:98-113: NTT-domain gather table, dst[i] = src[perm[i]] */

@@ -1070,6 +1070,26 @@ __global__ void __launch_bounds__(256) poly_op_kernel(int op, const uint64_t *a,
     out[idx] = r;
 }
 
+// Per-limb integer constants (src/bootstrap.cu:1535-1565, multiply_scalar_per_tower_kernel; adding
+// a constant polynomial c to NTT-form data adds c to every value of the limb).
+struct ScalarTab { uint64_t v[64]; };
+__global__ void __launch_bounds__(256) poly_scalar_kernel(int op, const uint64_t *a, ScalarTab tab, uint64_t *out, const Mod *mod,
+                                                        uint32_t N, uint32_t n_limbs) {
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (size_t)n_limbs * N) return;
+    const uint32_t limb = (uint32_t)(idx / N);
+    const Mod md = mod[limb];
+    const uint64_t q = md.q, x = a[idx], s = tab.v[limb];
+    uint64_t r;
+    if (op == 0) r = add_mod(x, s, q);
+    else {
+        u128 p{0, 0};
+        mac128(p, x, s);
+        r = barrett128(p, q, md.r0, md.r1);
+    }
+    out[idx] = r;
+}
+
 // NTT-domain automorphism (src/galois.cu:11-18): dst[l][i] = src[l][perm[i]].
 // Optional second operand pair so that c0 and c1 (or several digit buffers) go in one launch.
 __global__ void __launch_bounds__(256) galois_gather_kernel(const uint64_t *__restrict__ src, uint64_t *__restrict__ dst,
@@ -1092,6 +1112,21 @@ __global__ void __launch_bounds__(256) expand_signed_kernel(const int64_t *__res
     u128 v{mag, 0};
     const uint64_t r = barrett128(v, md.q, md.r0, md.r1);
     dst[idx] = (c >= 0 || r == 0) ? r : md.q - r;
+}
+
+// Centred remainder of the dropped limb, reduced into every remaining prime: with it the rescale
+// rounds to nearest instead of flooring. r: [n_poly][N] coefficient form mod q_last.
+__global__ void __launch_bounds__(256) rescale_centre_kernel(const uint64_t *__restrict__ r, uint64_t *__restrict__ out, const Mod *mod, uint32_t N,
+                                                            uint32_t n_out, uint32_t n_poly) {
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (size_t)n_poly * n_out * N) return;
+    const uint32_t i = (uint32_t)(idx % N), j = (uint32_t)((idx / N) % n_out), p = (uint32_t)(idx / ((size_t)N * n_out));
+    const Mod md = mod[j];
+    const uint64_t ql = mod[n_out].q, half = ql >> 1;
+    const uint64_t v = r[(size_t)p * N + i];
+    uint64_t d = barrett64(v, md.q, md.r1);
+    if (v > half) d = sub_mod(d, barrett64(ql, md.q, md.r1), md.q);  // v - q_last, the negative representative
+    out[idx] = d;
 }
 
 struct MacPtrs {
@@ -1356,6 +1391,31 @@ extern "C" int b2_rescale(b2_ctx *c, size_t l, size_t n_poly, const uint64_t *d_
     return run_fwd(c, d_out, d_out, pl.jobs_rs_ntt, (uint32_t)(n_poly * (l - 1)), 0, epi, s);
 }
 
+extern "C" int b2_rescale_rounded(b2_ctx *c, size_t l, size_t n_poly, const uint64_t *d_in, uint64_t *d_out, void *d_ws, size_t ws_bytes,
+                                  void *stream) {
+    CHECK_CTX(c);
+    CHECK_LEVEL(c, l);
+    if (l < 2) return fail(B2_EINVAL, "rescale_rounded: no prime left to drop");
+    if (n_poly < 1 || n_poly > 3) return fail(B2_EINVAL, "rescale_rounded: n_poly must be in [1, 3]");
+    if (!d_in || !d_out || !d_ws) return fail(B2_EINVAL, "rescale_rounded: null pointer");
+    if (ws_bytes < b2_workspace_bytes(c, B2_OP_RESCALE, l)) return fail(B2_EWS, "rescale_rounded: workspace too small");
+    cudaStream_t s = (cudaStream_t)stream;
+    const LevelPlan &pl = c->plan[l];
+    uint64_t *r = (uint64_t *)d_ws;
+    for (size_t p = 0; p < n_poly; p++) {
+        int rc = run_inv(c, d_in + (p * l + l - 1) * c->N, r + p * c->N, nullptr, 1, (uint32_t)(l - 1), c->d_fin_plain, s);
+        if (rc) return rc;
+    }
+    {
+        const size_t n = n_poly * (l - 1) * c->N;
+        LaunchScope ls(c, s, "rescale_centre");
+        rescale_centre_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(r, d_out, c->d_mod, (uint32_t)c->N, (uint32_t)(l - 1), (uint32_t)n_poly);
+        LAUNCH_CHECK("rescale_centre_kernel");
+    }
+    EpiSubMul<false> epi{d_in, d_out, pl.qlast_inv};
+    return run_fwd(c, d_out, d_out, pl.jobs_rs_ntt, (uint32_t)(n_poly * (l - 1)), 0, epi, s);
+}
+
 // ------------------------------------------------------------------------------------------------
 // rescale without any caller-provided or allocated scratch
 // ------------------------------------------------------------------------------------------------
@@ -1574,6 +1634,22 @@ extern "C" int b2_poly_op(b2_ctx *c, int op, size_t n_limbs, const uint64_t *d_a
     LaunchScope ls(c, (cudaStream_t)stream, "poly_op");
     poly_op_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(op, d_a, d_b, d_out, c->d_mod, (uint32_t)c->N, (uint32_t)n_limbs);
     LAUNCH_CHECK("poly_op_kernel");
+    return B2_OK;
+}
+
+extern "C" int b2_poly_scalar(b2_ctx *c, int op, size_t n_limbs, const uint64_t *d_a, const uint64_t *h_scalars, uint64_t *d_out, void *stream) {
+    CHECK_CTX(c);
+    if (op < 0 || op > 1 || !d_a || !d_out || !h_scalars || n_limbs < 1 || n_limbs > c->size_QP || n_limbs > 64)
+        return fail(B2_EINVAL, "poly_scalar: bad argument");
+    ScalarTab tab;
+    for (size_t i = 0; i < n_limbs; i++) {
+        if (h_scalars[i] >= c->q[i]) return fail(B2_EINVAL, "poly_scalar: scalar not reduced");
+        tab.v[i] = h_scalars[i];
+    }
+    const size_t n = n_limbs * c->N;
+    LaunchScope ls(c, (cudaStream_t)stream, "poly_scalar");
+    poly_scalar_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(op, d_a, tab, d_out, c->d_mod, (uint32_t)c->N, (uint32_t)n_limbs);
+    LAUNCH_CHECK("poly_scalar_kernel");
     return B2_OK;
 }
 

@@ -33,6 +33,7 @@ SIGNATURES = {
     "b2_tensor_mul": (_int, [_vp, _sz, _vp, _vp, _vp, _vp]),
     "b2_multiply_and_relin": (_int, [_vp, _sz, _vp, _vp, _vp, _sz, _vp, _vp, _sz, _vp]),
     "b2_rescale": (_int, [_vp, _sz, _sz, _vp, _vp, _vp, _sz, _vp]),
+    "b2_rescale_rounded": (_int, [_vp, _sz, _sz, _vp, _vp, _vp, _sz, _vp]),
     "b2_rescale_static": (_int, [_vp, _sz, _sz, _vp, _vp, _vp]),
     "b2_galois_elt_from_step": (_u32, [_int, _sz]),
     "b2_galois_prepare": (_int, [_vp, _u32]),
@@ -43,6 +44,7 @@ SIGNATURES = {
     "b2_expand_single_chain": (_int, [_vp, _sz, _vp, _vp, _vp]),
     "b2_expand_signed": (_int, [_vp, _sz, _sz, _vp, _vp, _int, _vp]),
     "b2_poly_op": (_int, [_vp, _int, _sz, _vp, _vp, _vp, _vp]),
+    "b2_poly_scalar": (_int, [_vp, _int, _sz, _vp, _vp, _vp, _vp]),
     "b2_ctx_set_shard": (_int, [_vp, _int, _int]),
     "b2_shard_limbs": (_int, [_vp, _sz, _vp]),
     "b2_shard_keyswitch_phase": (_int, [_vp, _sz, _int, _vp, _vp, _sz, _vp, _vp, _sz, _vp]),

@@ -1,0 +1,385 @@
+"""CKKS bootstrapping as a host composition over the C ABI (python/src/binding.cu:292-336;
+src/bootstrap.cu:1702-1949, src/evalmod.cu).
+
+Same surface as the reference - bootstrap_required_galois_elts, create_bootstrap_key, bootstrap -
+and the same overall route: key switch to a sparse secret, raise the modulus, CoeffToSlot as layered
+BSGS linear transforms, EvalRound on the real and imaginary halves, SlotToCoeff, and a final
+subtraction  ct_raised - q0 * I  that leaves the message on the user levels. The linear transforms
+and the polynomial evaluation are this library's own arrangement (see bootmath.py):
+
+* the top three primes carry CoeffToSlot (three layers; they may be short primes, because EvalRound
+  is flat around the integers and does not pass CoeffToSlot's rounding errors on);
+* the next ten carry EvalRound: a degree-63 Chebyshev cosine by Paterson-Stockmeyer (7 levels) and
+  three double-angle steps;
+* the next two carry SlotToCoeff in two layers, whose last plaintext scale is chosen so that the
+  result is q0 * I to the last bit that double precision can place.
+
+Every ciphertext operation below is a call into the C ABI; numpy is used for the diagonals, the
+Chebyshev coefficients and the scale bookkeeping only.
+"""
+import math
+
+import numpy as np
+import torch
+
+from . import _native, bootmath
+from ._native import LIB, check
+
+C2S_LAYERS, EVAL_LEVELS, S2C_LAYERS = 3, 10, 2
+BOOT_LEVELS = C2S_LAYERS + EVAL_LEVELS + S2C_LAYERS
+K_RANGE, DOUBLE_ANGLES, COS_DEGREE = 28, 3, 63
+SCALE_UP_MARGIN_BITS = 10  # the raised message stays below q0 / 2^10
+
+
+def _stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _elt(step, N):
+    return int(LIB.b2_galois_elt_from_step(int(step), N))
+
+
+def bootstrap_required_galois_elts(log_n, stages_per_layer=(5, 5, 5)):
+    """python/src/binding.cu:301-318: Galois elements of every rotation CoeffToSlot and SlotToCoeff use,
+    plus the conjugation 2N - 1. `stages_per_layer` is CoeffToSlot's grouping of the log2(N/2) radix-2
+    stages; SlotToCoeff always runs in two layers."""
+    N = 1 << log_n
+    stages = list(stages_per_layer)
+    if sum(stages) != log_n - 1:
+        stages = bootmath.split_stages(log_n - 1, C2S_LAYERS)
+    steps = bootmath.required_rotation_steps(log_n, stages, bootmath.split_stages(log_n - 1, S2C_LAYERS))
+    return [_elt(s, N) for s in steps] + [2 * N - 1]
+
+
+# ---- arithmetic on ciphertexts with (level, scale) bookkeeping: the `ops` of bootmath ---------------------
+class CtOps:
+    def __init__(self, ctx, rlk):
+        self.ctx, self.rlk = ctx, rlk
+        self.counts = {"mul": 0, "rescale": 0}
+
+    def prime(self, level):
+        return float(self.ctx.primes[level - 1])
+
+    def level(self, x):
+        return x._limbs
+
+    def scale(self, x):
+        return x._scale
+
+    def with_scale(self, x, s):
+        return x._like(x.data, scale=float(s))
+
+    def drop(self, x, level):
+        if level == x._limbs:
+            return x
+        if level > x._limbs:
+            raise ValueError("cannot raise a level")
+        return x._like(x.data[:, :level].contiguous(), chain_index=x._chain_index + (x._limbs - level))
+
+    def mul(self, x, y):
+        ctx, l = self.ctx, x._limbs
+        if y._limbs != l:
+            raise ValueError("operands at different levels")
+        out = ctx.empty(2, l)
+        ws, nbytes = ctx.workspace(_native.OP_MUL_RELIN, l)
+        tab = self.rlk.pointer_table()
+        check(LIB.b2_multiply_and_relin(ctx._h, l, x.data.data_ptr(), y.data.data_ptr(), tab.ctypes.data, len(tab),
+                                        out.data_ptr(), ws.data_ptr(), nbytes, _stream()))
+        self.counts["mul"] += 1
+        return x._like(out, scale=x._scale * y._scale)
+
+    def rescale(self, x):
+        ctx, l = self.ctx, x._limbs
+        if l < 2:
+            raise ValueError("out of levels")
+        out = ctx.empty(x._size, l - 1)
+        ws, nbytes = ctx.workspace(_native.OP_RESCALE, l)
+        check(LIB.b2_rescale_rounded(ctx._h, l, x._size, x.data.data_ptr(), out.data_ptr(), ws.data_ptr(), nbytes, _stream()))
+        self.counts["rescale"] += 1
+        return x._like(out, chain_index=x._chain_index + 1, scale=x._scale / self.prime(l))
+
+    def _scalars(self, k, l):
+        return np.array([k % int(q) for q in self.ctx.primes[:l]], dtype=np.uint64)
+
+    def mul_const(self, x, c, const_scale):
+        k = int(round(c * const_scale))
+        sc = self._scalars(k, x._limbs)
+        out = torch.empty_like(x.data)
+        for p in range(x._size):
+            check(LIB.b2_poly_scalar(self.ctx._h, 1, x._limbs, x.data[p].data_ptr(), sc.ctypes.data, out[p].data_ptr(), _stream()))
+        return x._like(out, scale=x._scale * const_scale)
+
+    def add_const(self, x, c):
+        sc = self._scalars(int(round(c * x._scale)), x._limbs)
+        out = x.data.clone()
+        check(LIB.b2_poly_scalar(self.ctx._h, 0, x._limbs, x.data[0].data_ptr(), sc.ctypes.data, out[0].data_ptr(), _stream()))
+        return x._like(out)
+
+    def _lin(self, op, x, y):
+        if x._limbs != y._limbs or x._size != y._size:
+            raise ValueError("operands at different levels")
+        if abs(x._scale / y._scale - 1.0) > 2.0 ** -40:
+            raise ValueError("scale mismatch")
+        out = torch.empty_like(x.data)
+        for p in range(x._size):
+            check(LIB.b2_poly_op(self.ctx._h, op, x._limbs, x.data[p].data_ptr(), y.data[p].data_ptr(), out[p].data_ptr(), _stream()))
+        return x._like(out)
+
+    def add(self, x, y):
+        return self._lin(0, x, y)
+
+    def sub(self, x, y):
+        return self._lin(1, x, y)
+
+
+# ---- one layer of a linear transform, compiled to device plaintexts ----------------------------------------
+class _Layer:
+    """the LayerPlan of bootmath with every pre-rotated diagonal encoded at (limbs, scale) and resident in HBM"""
+
+    def __init__(self, ctx, encoder, plan, limbs, scale, value_factor=1.0):
+        self.limbs, self.scale, self.n = limbs, float(scale), plan.n
+        self.baby_steps = [(b, (b * plan.unit) % plan.n) for b in plan.babies]
+        chain_index = ctx.size_Q - limbs + 1
+        self.giants = []  # (rotation step, [baby position], device pointer table, plaintext tensors)
+        pos = {b: i for i, (b, _) in enumerate(self.baby_steps)}
+        for g in plan.giants:
+            pts, idx = [], []
+            for b, d in plan.terms[g]:
+                pts.append(encoder.encode_complex_vector(ctx, d * value_factor, self.scale, chain_index).data)
+                idx.append(pos[b])
+            tab = torch.tensor([p.data_ptr() for p in pts], dtype=torch.int64, device=ctx.device)
+            self.giants.append(((g * plan.n1 * plan.unit) % plan.n, idx, tab, pts))
+        # the baby rotations land in buffers owned by the layer, so the pointer tables of the fused
+        # multiply-accumulate are built once
+        self.baby_buf = ctx.empty(len(self.baby_steps), 2, limbs)
+        self.baby_tabs = [torch.tensor([self.baby_buf[i].data_ptr() for i in idx], dtype=torch.int64, device=ctx.device)
+                          for _, idx, _, _ in self.giants]
+
+    def steps(self):
+        return [s for _, s in self.baby_steps if s] + [s for s, _, _, _ in self.giants if s]
+
+
+class small_bootstrap_key:
+    """the two switching keys of the sparse-secret encapsulation (include/bootstrap.h SmallBootstrapKey)"""
+
+    def __init__(self):
+        self.to_sparse = None
+        self.to_dense = None
+
+
+class bootstrap_key:
+    def __init__(self):
+        self.small = small_bootstrap_key()
+        self.relin = None
+        self.rot = {}     # slot rotation step -> switching key
+        self.conj = None
+        self.c2s, self.s2c = [], []
+        self.user_limbs = 0
+        self.eval_scale = 0.0
+        self.mono_i = None  # NTT form of X^(N/2): multiplication by i on the slots
+
+
+def _key_for_elt(sk, ctx, elt):
+    check(LIB.b2_galois_prepare(ctx._h, elt))
+    rot = ctx.empty(ctx.size_QP)
+    check(LIB.b2_galois_permute(ctx._h, elt, sk.data.data_ptr(), rot.data_ptr(), ctx.size_QP, _stream()))
+    return sk._kswitch_key(ctx, rot)
+
+
+def create_bootstrap_key(context, encoder, dense_sk, sparse_hamming_weight=128, eval_mod_levels=0, user_scale=0.0,
+                         split_scale_down=False, stages_per_layer=None):
+    """python/src/binding.cu:320-327; src/bootstrap.cu:895-1199.
+
+    The chain must hold q0, at least one user level and BOOT_LEVELS = 15 further primes above them.
+    `eval_mod_levels` is accepted for compatibility (the reference spends 9 levels on EvalMod and 3 on
+    SlotToCoeff, this pipeline 10 and 2: the same 12 primes)."""
+    from .keys import secret_key
+    ctx = context
+    if split_scale_down:
+        raise ValueError("split_scale_down is not built")
+    if eval_mod_levels not in (0, 9, EVAL_LEVELS):
+        raise ValueError("eval_mod_levels: this pipeline uses the 12 primes below CoeffToSlot as 10 + 2")
+    if ctx.size_Q < BOOT_LEVELS + 2:
+        raise ValueError("the modulus chain is too short for bootstrapping")
+    N, n, sQ = ctx.N, ctx.N // 2, ctx.size_Q
+    logn = n.bit_length() - 1
+    bk = bootstrap_key()
+    bk.user_limbs = sQ - BOOT_LEVELS
+    # sparse-secret encapsulation: s -> s' at the bottom prime, s' -> s at the top (src/bootstrap.cu:183-216)
+    sparse = secret_key(seed=None)
+    sparse._rng = dense_sk._rng
+    sparse.generate_sparse(ctx, sparse_hamming_weight)
+    bk.small.to_sparse = sparse._kswitch_key(ctx, dense_sk.data)
+    bk.small.to_dense = dense_sk._kswitch_key(ctx, sparse.data)
+    bk.relin = dense_sk.gen_relinkey(ctx)
+    # linear transforms
+    c2s_stages = list(stages_per_layer) if stages_per_layer and sum(stages_per_layer) == logn else bootmath.split_stages(logn, C2S_LAYERS)
+    s2c_stages = bootmath.split_stages(logn, S2C_LAYERS)
+    q0 = float(ctx.primes[0])
+    eval_top = sQ - C2S_LAYERS                     # limbs at EvalRound's input
+    bk.eval_scale = float(ctx.primes[eval_top - 1])
+    # CoeffToSlot: slots of the raised ciphertext read at scale q0*K are t/(q0 K); the unnormalised inverse
+    # FFT multiplies by n and the real/imaginary split wants another 1/2: both go into the plaintext scales
+    sigma0 = q0 * K_RANGE
+    ratio = (bk.eval_scale / (2.0 * n * sigma0)) ** (1.0 / C2S_LAYERS)
+    for i, layer in enumerate(bootmath.fft_layers(n, c2s_stages, True)):
+        limbs = sQ - i
+        bk.c2s.append(_Layer(ctx, encoder, bootmath.LayerPlan(layer, n), limbs, float(ctx.primes[limbs - 1]) * ratio))
+    # SlotToCoeff: the first layer at its own prime; the last one is scaled at bootstrap time (it depends on
+    # the exact scale EvalRound ends with), so keep its diagonals and encode against the known target here
+    s2c_top = eval_top - EVAL_LEVELS
+    layers = bootmath.fft_layers(n, s2c_stages, False)
+    pa, pb = float(ctx.primes[s2c_top - 1]), float(ctx.primes[s2c_top - 2])
+    e0 = pa
+    e1 = q0 * float(int(ctx.primes[s2c_top - 1])) * float(int(ctx.primes[s2c_top - 2])) / (bk.eval_scale * e0)
+    bk.s2c.append(_Layer(ctx, encoder, bootmath.LayerPlan(layers[0], n), s2c_top, e0))
+    bk.s2c.append(_Layer(ctx, encoder, bootmath.LayerPlan(layers[1], n), s2c_top - 1, e1))
+    # rotation keys
+    steps = set()
+    for layer in bk.c2s + bk.s2c:
+        steps.update(layer.steps())
+    for s in sorted(steps):
+        bk.rot[s] = _key_for_elt(dense_sk, ctx, _elt(s, N))
+    bk.conj = _key_for_elt(dense_sk, ctx, 2 * N - 1)
+    mono = np.zeros(N, dtype=np.int64)
+    mono[N // 2] = 1
+    d = torch.from_numpy(mono).to(ctx.device)
+    bk.mono_i = ctx.empty(sQ)
+    check(LIB.b2_expand_signed(ctx._h, 0, sQ, d.data_ptr(), bk.mono_i.data_ptr(), 1, _stream()))
+    torch.cuda.synchronize()
+    return bk
+
+
+# ---- the pipeline --------------------------------------------------------------------------------------------
+def _keyswitch_c1(ctx, ct, key):
+    """(c0, c1) under one secret -> (c0 + ks0, ks1) under the other"""
+    l = ct._limbs
+    out = torch.stack([ct.data[0], torch.zeros_like(ct.data[1])])
+    ws, nbytes = ctx.workspace(_native.OP_KEYSWITCH, l)
+    tab = key.pointer_table()
+    check(LIB.b2_keyswitch(ctx._h, l, ct.data[1].data_ptr(), tab.ctypes.data, len(tab), out.data_ptr(), ws.data_ptr(), nbytes, _stream()))
+    return ct._like(out)
+
+
+def _galois(ctx, ct, elt, key):
+    l = ct._limbs
+    out = ctx.empty(2, l)
+    ws, nbytes = ctx.workspace(_native.OP_ROTATE, l)
+    tab = key.pointer_table()
+    check(LIB.b2_apply_galois(ctx._h, l, int(elt), ct.data.data_ptr(), tab.ctypes.data, len(tab), out.data_ptr(), ws.data_ptr(), nbytes, _stream()))
+    return ct._like(out)
+
+
+def mod_raise(ctx, bk, ct):
+    """src/bootstrap.cu:105-216: a ciphertext on q0 alone -> the same c0 + c1 s = t over every Q prime, where
+    now t = scale*m + q0*I with |I| bounded by the sparse secret's weight"""
+    if ct._limbs != 1:
+        raise ValueError("mod_raise wants a ciphertext on the bottom prime only")
+    sQ, N = ctx.size_Q, ctx.N
+    x = _keyswitch_c1(ctx, ct, bk.small.to_sparse)
+    coeff = x.data.clone()
+    for p in range(2):
+        check(LIB.b2_ntt_inverse(ctx._h, coeff[p].data_ptr(), 1, 0, _stream()))
+    q0 = int(ctx.primes[0])
+    centred = torch.where(coeff > q0 // 2, coeff - q0, coeff)  # residues of one 58-bit prime fit int64
+    out = ctx.empty(2, sQ)
+    for p in range(2):
+        check(LIB.b2_expand_signed(ctx._h, 0, sQ, centred[p, 0].data_ptr(), out[p].data_ptr(), 1, _stream()))
+    raised = ct._like(out, chain_index=1)
+    return _keyswitch_c1(ctx, raised, bk.small.to_dense)
+
+
+def linear_transform(ctx, bk, ct, layer, ops):
+    """one BSGS layer: hoisted baby rotations, a fused multiply-accumulate per giant, giant rotations, one rescale
+    (src/bootstrap.cu:1201-1353 does the same with one key switch per baby)"""
+    ct = ops.drop(ct, layer.limbs)
+    l, N = layer.limbs, ctx.N
+    steps = [(i, s) for i, (_, s) in enumerate(layer.baby_steps) if s]
+    for i, (_, s) in enumerate(layer.baby_steps):
+        if s == 0:
+            layer.baby_buf[i].copy_(ct.data)
+    if steps:
+        elts = np.array([_elt(s, N) for _, s in steps], dtype=np.uint32)
+        n_evk = ctx.beta(l)
+        ksk = np.concatenate([bk.rot[s].pointer_table()[:n_evk] for _, s in steps]).astype(np.uint64)
+        outs = np.array([layer.baby_buf[i].data_ptr() for i, _ in steps], dtype=np.uint64)
+        ws, nbytes = ctx.workspace(_native.OP_HOIST, l)
+        check(LIB.b2_hoist_rotations(ctx._h, l, ct.data.data_ptr(), elts.ctypes.data, len(steps), ksk.ctypes.data, n_evk,
+                                     outs.ctypes.data, ws.data_ptr(), nbytes, _stream()))
+    acc = None
+    for (step, idx, tab, _), btab in zip(layer.giants, layer.baby_tabs):
+        part = ctx.empty(2, l)
+        check(LIB.b2_bsgs_mac(ctx._h, l, len(idx), tab.data_ptr(), btab.data_ptr(), part.data_ptr(), _stream()))
+        part = ct._like(part, scale=ct._scale * layer.scale)
+        if step:
+            part = _galois(ctx, part, _elt(step, N), bk.rot[step])
+        acc = part if acc is None else ops.add(acc, part)
+    return ops.rescale(acc)
+
+
+def _times_i(ctx, bk, ct, negate=False):
+    """multiply the slots by i (or -i): the monomial X^(N/2), exact and free of levels (shift_poly_N2_kernel,
+    src/bootstrap.cu:76-98, does it in coefficient form)"""
+    l = ct._limbs
+    out = torch.empty_like(ct.data)
+    for p in range(2):
+        check(LIB.b2_poly_op(ctx._h, 2, l, ct.data[p].data_ptr(), bk.mono_i.data_ptr(), out[p].data_ptr(), _stream()))
+        if negate:
+            check(LIB.b2_poly_op(ctx._h, 3, l, out[p].data_ptr(), 0, out[p].data_ptr(), _stream()))
+    return ct._like(out)
+
+
+def coeff_to_slot(ctx, bk, raised, ops):
+    """-> (u_lo, u_hi): slots t_k / (q0 K) and t_(k+N/2) / (q0 K) in bit-reversed order, at bk.eval_scale"""
+    x = ops.with_scale(raised, float(ctx.primes[0]) * K_RANGE)
+    for layer in bk.c2s:
+        x = linear_transform(ctx, bk, x, layer, ops)
+    x = ops.with_scale(x, x._scale * 2.0 * layer.n)  # the same integers read as w/2, w = (t_lo + i t_hi)/(q0 K)
+    xc = _galois(ctx, x, 2 * ctx.N - 1, bk.conj)
+    return ops.add(x, xc), _times_i(ctx, bk, ops.sub(x, xc), negate=True)
+
+
+def slot_to_coeff(ctx, bk, lo, hi, ops):
+    x = ops.add(lo, _times_i(ctx, bk, hi))
+    for layer in bk.s2c:
+        x = linear_transform(ctx, bk, x, layer, ops)
+    return x
+
+
+def bootstrap(context, encoder, ct, bk, user_scale, split_scale_down=False, stats=None):
+    """python/src/binding.cu:329-336; src/bootstrap.cu:1702-1949. `ct`: any level, scale about user_scale with
+    |message| <= 1; returns a ciphertext at the input's scale with bk.user_limbs limbs, or one fewer when the
+    input scale had to be raised first (an input with at least two limbs and scale below q0 / 2^10)."""
+    ctx = context
+    if split_scale_down:
+        raise ValueError("split_scale_down is not built")
+    if ct._size != 2 or not ct._is_ntt_form:
+        raise ValueError("bootstrap wants a 2-polynomial ciphertext in NTT form")
+    ops = CtOps(ctx, bk.relin)
+    scale_in = ct._scale
+    # scale_up_for_bootstrap (src/bootstrap.cu:1435-1512): every error of EvalRound comes back multiplied by
+    # q0 / scale, so raise the scale to about q0 / 2^10 with one integer multiply and the rescale that drops
+    # the prime above q0 (|message| <= 1 then stays inside the range where the sine is cubic-flat)
+    x = ct
+    if x._limbs >= 2:
+        x = ops.drop(x, 2)
+        up = int(math.floor(math.log2(float(ctx.primes[0]) / x._scale))) - SCALE_UP_MARGIN_BITS
+        if up > 0:
+            x = ops.rescale(ops.mul_const(x, 1.0, ops.prime(2) * 2.0 ** up))
+    raised = mod_raise(ctx, bk, ops.drop(x, 1))
+    lo, hi = coeff_to_slot(ctx, bk, raised, ops)
+    ints = [bootmath.eval_round(ops, u, K_RANGE, DOUBLE_ANGLES, COS_DEGREE, bk.eval_scale) for u in (lo, hi)]
+    qi = slot_to_coeff(ctx, bk, ints[0], ints[1], ops)  # coefficients q0 * I at "scale" q0, i.e. the integers themselves
+    out = ops.drop(raised, qi._limbs)
+    res = torch.empty_like(out.data)
+    for p in range(2):
+        check(LIB.b2_poly_op(ctx._h, 1, out._limbs, out.data[p].data_ptr(), qi.data[p].data_ptr(), res[p].data_ptr(), _stream()))
+    res = out._like(res, scale=x._scale)
+    if abs(x._scale / scale_in - 1.0) > 2.0 ** -40:
+        # back to the caller's scale: costs the top user prime
+        res = ops.rescale(ops.mul_const(res, 1.0, scale_in * ops.prime(res._limbs) / res._scale))
+    if stats is not None:
+        stats.update(ops.counts)
+        stats["final_scale_over_q0"] = qi._scale / float(int(ctx.primes[0]))
+        stats["raised_scale_log2"] = math.log2(x._scale)
+    return res._like(res.data, scale=scale_in)

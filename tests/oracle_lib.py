@@ -48,6 +48,7 @@ def _load():
         "ora_tensor_mul": (None, [_vp, _sz, _vp, _vp, _vp]),
         "ora_multiply_and_relin": (None, [_vp, _sz, _vp, _vp, _vp, _vp]),
         "ora_rescale": (None, [_vp, _sz, _sz, _vp, _vp]),
+        "ora_rescale_rounded": (None, [_vp, _sz, _sz, _vp, _vp]),
         "ora_galois_elt_from_step": (_u32, [_int, _sz]),
         "ora_galois_perm": (None, [_sz, _u32, _vp]),
         "ora_apply_galois": (None, [_vp, _sz, _u32, _vp, _vp]),
@@ -190,6 +191,13 @@ class Oracle:
         n_poly = ct.shape[0]
         out = np.empty((n_poly, l - 1, self.N), dtype=np.uint64)
         LIB.ora_rescale(self.h, l, n_poly, _p(ct), _p(out))
+        return out
+
+    def rescale_rounded(self, l, ct):
+        ct = np.ascontiguousarray(ct, dtype=np.uint64)
+        n_poly = ct.shape[0]
+        out = np.empty((n_poly, l - 1, self.N), dtype=np.uint64)
+        LIB.ora_rescale_rounded(self.h, l, n_poly, _p(ct), _p(out))
         return out
 
     def galois_elt(self, step):

@@ -161,6 +161,47 @@ def test_levels_and_ragged_digits_against_oracle(l):
             ws, nb = _ws(ctx, _native.OP_RESCALE, l)
             check(LIB.b2_rescale(ctx._h, l, n_poly, dev(x_h).data_ptr(), r.data_ptr(), ws.data_ptr(), nb, stream()))
             assert np.array_equal(host(r), o.rescale(l, x_h))
+            check(LIB.b2_rescale_rounded(ctx._h, l, n_poly, dev(x_h).data_ptr(), r.data_ptr(), ws.data_ptr(), nb, stream()))
+            assert np.array_equal(host(r), o.rescale_rounded(l, x_h))
+
+
+def test_rounded_rescale_rounds_to_nearest():
+    # a small integer polynomial v lifted as v * q_last + e: flooring gives v or v - 1, rounding gives v for |e| < q_last / 2
+    N, l = 4096, 3
+    ctx, o = make_ctx(N, [50, 40, 40, 60], 1)
+    primes = [int(q) for q in o.primes[:l]]
+    rng = np.random.default_rng(5)
+    v = rng.integers(-1000, 1000, N)
+    e = rng.integers(-(primes[-1] // 2) + 1, primes[-1] // 2, N)
+    val = [int(a) * primes[-1] + int(b) for a, b in zip(v, e)]
+    x_h = np.array([[c % q for c in val] for q in primes], dtype=np.uint64)[None]
+    x = dev(x_h)
+    check(LIB.b2_ntt_forward(ctx._h, x.data_ptr(), l, 0, stream()))
+    r = ctx.empty(1, l - 1)
+    ws, nb = _ws(ctx, _native.OP_RESCALE, l)
+    check(LIB.b2_rescale_rounded(ctx._h, l, 1, x.data_ptr(), r.data_ptr(), ws.data_ptr(), nb, stream()))
+    check(LIB.b2_ntt_inverse(ctx._h, r.data_ptr(), l - 1, 0, stream()))
+    want = np.array([[int(a) % q for a in v] for q in primes[:-1]], dtype=np.uint64)[None]
+    assert np.array_equal(host(r), want)
+
+
+def test_per_limb_scalars():
+    N, l = 4096, 4
+    ctx, o = make_ctx(N, [60, 29, 40, 58, 60], 1)
+    a_h = o.fill(1, o.primes[:l], 41, 1)[0]
+    a = dev(a_h)
+    sc = np.array([int(q) - 3 - i for i, q in enumerate(o.primes[:l])], dtype=np.uint64)
+    out = ctx.empty(l)
+    check(LIB.b2_poly_scalar(ctx._h, 0, l, a.data_ptr(), sc.ctypes.data, out.data_ptr(), stream()))
+    want = np.stack([(a_h[i].astype(object) + int(sc[i])) % int(o.primes[i]) for i in range(l)]).astype(np.uint64)
+    assert np.array_equal(host(out), want)
+    check(LIB.b2_poly_scalar(ctx._h, 1, l, a.data_ptr(), sc.ctypes.data, out.data_ptr(), stream()))
+    want = np.stack([(a_h[i].astype(object) * int(sc[i])) % int(o.primes[i]) for i in range(l)]).astype(np.uint64)
+    assert np.array_equal(host(out), want)
+    bad = sc.copy()
+    bad[1] = o.primes[1]
+    with pytest.raises(ValueError):
+        check(LIB.b2_poly_scalar(ctx._h, 1, l, a.data_ptr(), bad.ctypes.data, out.data_ptr(), stream()))
 
 
 def test_elementwise_tensor_and_bsgs_mac():
