@@ -174,6 +174,71 @@ def kernel_alg_bytes_per_keyswitch():
     }
 
 
+def ntt_section(ph, ctx, torch, LIB, check, N, n_limbs, reps=20):
+    """forward and inverse transforms over n_limbs limbs, cycling through 16 buffers (268 MB at 32 limbs: larger than L2)"""
+    bufs = torch.randint(0, 1 << 30, (16, n_limbs, N), dtype=torch.int64, device="cuda")
+    st = torch.cuda.current_stream()
+    out = {}
+    for name, fn in (("forward", LIB.b2_ntt_forward), ("inverse", LIB.b2_ntt_inverse)):
+        for i in range(16):
+            check(fn(ctx._h, bufs[i].data_ptr(), n_limbs, 0, st.cuda_stream))
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record(st)
+        for r in range(reps):
+            for i in range(16):
+                check(fn(ctx._h, bufs[i].data_ptr(), n_limbs, 0, st.cuda_stream))
+        e1.record(st)
+        torch.cuda.synchronize()
+        sec = e0.elapsed_time(e1) / 1e3
+        per_s = reps * 16 * n_limbs / sec
+        out[name] = {"limb_transforms_per_s": per_s, "alg_gbs": per_s * 2 * 8 * N / 1e9}
+    return {"N": N, "limbs_per_call": n_limbs, **out}
+
+
+def bootstrap_section(ph, torch, np):
+    """one CKKS bootstrap at N = 2^16 on a 24-limb chain (dnum 3), sparse ternary secret of weight 192,
+    2^15 slots uniform in [-1, 1] scaled into |m| <= 0.5; decryption error against the message"""
+    import math
+    log_n, alpha = 16, 8
+    n_ring = 1 << log_n
+    bits = [58] + [40] * 8 + [58] * 12 + [29] * 3 + [58] * alpha
+    parms = ph.params(ph.scheme_type.ckks)
+    parms.set_poly_modulus_degree(n_ring)
+    parms.set_special_modulus_size(alpha)
+    parms.set_coeff_modulus(ph.create_coeff_modulus(n_ring, bits))
+    parms.set_galois_elts(ph.bootstrap_required_galois_elts(log_n, [5, 5, 5]))
+    ctx = ph.context(parms)
+    sk = ph.secret_key(ctx, seed=5)
+    sk.generate_sparse(ctx, 192)
+    enc = ph.ckks_encoder(ctx)
+    t0 = time.perf_counter()
+    bk = ph.create_bootstrap_key(ctx, enc, sk, sparse_hamming_weight=128, eval_mod_levels=9, user_scale=2.0 ** 40)
+    torch.cuda.synchronize()
+    keygen_s = time.perf_counter() - t0
+    msg = 0.5 * np.random.default_rng(5).uniform(-1.0, 1.0, n_ring // 2)
+    ct = sk.encrypt_symmetric(ctx, enc.encode_double_vector(ctx, msg, 2.0 ** 40, chain_index=1))
+    ph.mod_switch_to_inplace(ctx, ct, ctx.total_parm_size() - 2)
+    for _ in range(3):
+        out = ph.bootstrap(ctx, enc, ct, bk, 2.0 ** 40)
+    torch.cuda.synchronize()
+    launches0 = int(ph._native.LIB.b2_launch_count())
+    times = []
+    for _ in range(5):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        out = ph.bootstrap(ctx, enc, ct, bk, 2.0 ** 40)
+        e1.record()
+        torch.cuda.synchronize()
+        times.append(e0.elapsed_time(e1))
+    launches = (int(ph._native.LIB.b2_launch_count()) - launches0) // 5
+    err = np.abs(enc.decode_double_vector(ctx, sk.decrypt(ctx, out)) - msg)
+    return {"ms": float(np.median(times)), "ms_min": float(min(times)), "launches": launches,
+            "log2_max_err": math.log2(float(err.max())), "max_err": float(err.max()), "mean_err": float(err.mean()),
+            "limbs_in": 2, "limbs_out": out.coeff_modulus_size(), "chain_bits": "58|40x8|58x12|29x3|P 58x8",
+            "secret_hamming_weight": 192, "keygen_s": keygen_s}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -185,6 +250,7 @@ def main():
     ap.add_argument("--streams", type=int, default=4, help="CUDA streams the batch of independent key switches is spread over")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer arm (used for ncu captures)")
+    ap.add_argument("--no-extras", action="store_true", help="skip the NTT and bootstrap sections of the line")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
@@ -354,6 +420,13 @@ def main():
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         cpu = cpu_baseline_sample()
 
+    ntt, bootstrap = None, None
+    if rank == 0 and world == 1 and not args.no_extras:
+        ntt = ntt_section(ph, ctx, torch, LIB, check, N, len(primes))
+        del dev_ct3, keys, stage
+        torch.cuda.empty_cache()
+        bootstrap = bootstrap_section(ph, torch, np)
+
     if rank == 0:
         peak, peak_kind = peaks()
         ks_us = 1e3 * ms / (B * args.steps)
@@ -373,6 +446,8 @@ def main():
                                    "frac": KS_BYTES / (ks_us * 1e-6) / 1e9 / peak, "peak_kind": peak_kind},
             "kernels": kernels,
             "cpu_baseline": cpu,
+            "ntt": ntt,
+            "bootstrap": bootstrap,
         }
         print(json.dumps(line), flush=True)
     if world > 1:

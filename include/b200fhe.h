@@ -175,6 +175,15 @@ int b2_expand_signed(b2_ctx *ctx, size_t first_prime, size_t n_limbs, const int6
 int b2_poly_op(b2_ctx *ctx, int op, size_t n_limbs, const uint64_t *d_a, const uint64_t *d_b,
                uint64_t *d_out, void *stream);
 
+/* b2_poly_op over a whole ciphertext [n_poly][size_Ql][N] in one launch (limb t of polynomial p on prime t).
+ * op 0 add, 1 sub: d_b is a ciphertext of the same shape; op 2: d_b is ONE polynomial [size_Ql][N] (a
+ * plaintext) multiplied into every polynomial (multiply_plain, src/evaluate.cu:1150-1200); op 3 negate. */
+int b2_ct_op(b2_ctx *ctx, int op, size_t size_Ql, size_t n_poly, const uint64_t *d_a, const uint64_t *d_b,
+             uint64_t *d_out, void *stream);
+/* every polynomial of a ciphertext times the per-limb integer h_scalars[i] (see b2_poly_scalar, op 1) */
+int b2_ct_scalar(b2_ctx *ctx, size_t size_Ql, size_t n_poly, const uint64_t *d_a, const uint64_t *h_scalars,
+                 uint64_t *d_out, void *stream);
+
 /* per-limb integer constants over [n_limbs][N], limb i on prime i: op 0 adds h_scalars[i] to every
  * value of limb i (in NTT form that is adding the constant polynomial h_scalars[i]); op 1 multiplies
  * limb i by h_scalars[i] (replaces multiply_scalar_per_tower_kernel, src/bootstrap.cu:1535-1565).

@@ -335,7 +335,7 @@ static int build_level(b2_ctx *c, size_t l) {
             const uint64_t ninv = h_invmod(N % qi, qi);
             fin_up[2 * i] = h_tw_enc(h_mulmod(ninv, hatinv, qi), qi);
             fin_up[2 * i + 1] = h_tw_enc(h_mulmod(c->h_itw[i * N + 1].w, hatinv, qi), qi);
-            jobs_up_intt[i] = make_uint4((uint32_t)i, (uint32_t)i, (uint32_t)i, 0);
+            jobs_up_intt[i] = make_uint4((uint32_t)i, (uint32_t)i, (uint32_t)i, (uint32_t)i);
         }
         for (size_t t = 0; t < lP; t++) {
             if (t >= s && t < e) continue;
@@ -355,12 +355,12 @@ static int build_level(b2_ctx *c, size_t l) {
     for (size_t i = 0; i < alpha; i++) p_pieces = std::max(p_pieces, h_npieces(c->q[sQ + i]));
     for (size_t k = 0; k < 2; k++) {
         for (size_t i = 0; i < alpha; i++)
-            jobs_dn_intt[k * alpha + i] = make_uint4((uint32_t)(k * lP + l + i), (uint32_t)(sQ + i), (uint32_t)i, 0);
+            jobs_dn_intt[k * alpha + i] = make_uint4((uint32_t)(k * lP + l + i), (uint32_t)(sQ + i), (uint32_t)i, (uint32_t)(k * lP + l + i));
         for (size_t j = 0; j < l; j++)
             jobs_dn_ntt[k * l + j] = make_uint4((uint32_t)(k * l + j), (uint32_t)j, (uint32_t)(k * lP + j), (uint32_t)(k * l + j));
         grp_dn[k] = BconvGroup{(uint32_t)(k * lP + l), (uint32_t)alpha, 0, 0, (uint32_t)l, (uint32_t)(k * l), 0, p_pieces};
         for (size_t i = 0; i < alpha; i++)
-            jobs_dnf_intt[k * alpha + i] = make_uint4((uint32_t)(k * alpha + i), (uint32_t)(sQ + i), (uint32_t)i, 0);
+            jobs_dnf_intt[k * alpha + i] = make_uint4((uint32_t)(k * alpha + i), (uint32_t)(sQ + i), (uint32_t)i, (uint32_t)(k * alpha + i));
         for (size_t j = 0; j < l; j++)
             jobs_dnf_ntt[k * l + j] = make_uint4((uint32_t)(k * l + j), (uint32_t)j, 0, (uint32_t)(k * l + j));
         grp_dnf[k] = BconvGroup{(uint32_t)(k * alpha), (uint32_t)alpha, 0, 0, (uint32_t)l, (uint32_t)(k * l), 0, p_pieces};
@@ -374,7 +374,7 @@ static int build_level(b2_ctx *c, size_t l) {
             outs_rs[j] = make_uint2((uint32_t)j, (uint32_t)j);
         }
         for (size_t p = 0; p < 3; p++) {
-            jobs_rs_intt[p] = make_uint4((uint32_t)(p * l + l - 1), (uint32_t)(l - 1), (uint32_t)(l - 1), 0);
+            jobs_rs_intt[p] = make_uint4((uint32_t)(p * l + l - 1), (uint32_t)(l - 1), (uint32_t)(l - 1), (uint32_t)p);
             for (size_t j = 0; j + 1 < l; j++)
                 jobs_rs_ntt[p * (l - 1) + j] =
                     make_uint4((uint32_t)(p * (l - 1) + j), (uint32_t)j, (uint32_t)(p * l + j), (uint32_t)(p * (l - 1) + j));
@@ -1053,18 +1053,21 @@ __global__ void __launch_bounds__(256) tensor_mul_kernel(const uint64_t *__restr
 }
 
 // src/polymath.cu:17-180
+// `period` limbs per polynomial: limb t of the buffer uses prime t % period, so one launch covers a whole
+// ciphertext. b_wrap: the second operand is one polynomial shared by all (a plaintext).
 __global__ void __launch_bounds__(256) poly_op_kernel(int op, const uint64_t *a, const uint64_t *b, uint64_t *out, const Mod *mod,
-                                                     uint32_t N, uint32_t n_limbs) {
+                                                     uint32_t N, uint32_t n_limbs, uint32_t period, int b_wrap) {
     const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= (size_t)n_limbs * N) return;
-    const Mod md = mod[idx / N];
+    const Mod md = mod[(idx / N) % period];
     const uint64_t q = md.q, x = a[idx];
+    const size_t bi = b_wrap ? idx % ((size_t)period * N) : idx;
     uint64_t r;
-    if (op == 0) r = add_mod(x, b[idx], q);
-    else if (op == 1) r = sub_mod(x, b[idx], q);
+    if (op == 0) r = add_mod(x, b[bi], q);
+    else if (op == 1) r = sub_mod(x, b[bi], q);
     else if (op == 2) {
         u128 p{0, 0};
-        mac128(p, x, b[idx]);
+        mac128(p, x, b[bi]);
         r = barrett128(p, q, md.r0, md.r1);
     } else r = x ? q - x : 0;
     out[idx] = r;
@@ -1074,10 +1077,10 @@ __global__ void __launch_bounds__(256) poly_op_kernel(int op, const uint64_t *a,
 // a constant polynomial c to NTT-form data adds c to every value of the limb).
 struct ScalarTab { uint64_t v[64]; };
 __global__ void __launch_bounds__(256) poly_scalar_kernel(int op, const uint64_t *a, ScalarTab tab, uint64_t *out, const Mod *mod,
-                                                        uint32_t N, uint32_t n_limbs) {
+                                                        uint32_t N, uint32_t n_limbs, uint32_t period) {
     const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= (size_t)n_limbs * N) return;
-    const uint32_t limb = (uint32_t)(idx / N);
+    const uint32_t limb = (uint32_t)((idx / N) % period);
     const Mod md = mod[limb];
     const uint64_t q = md.q, x = a[idx], s = tab.v[limb];
     uint64_t r;
@@ -1378,10 +1381,9 @@ extern "C" int b2_rescale(b2_ctx *c, size_t l, size_t n_poly, const uint64_t *d_
     cudaStream_t s = (cudaStream_t)stream;
     const LevelPlan &pl = c->plan[l];
     uint64_t *r = (uint64_t *)d_ws;  // [n_poly][N] coefficient form of the dropped limbs
-    // INTT of each polynomial's last limb, out of place into r (one launch pair per polynomial,
-    // because source and destination slots differ)
-    for (size_t p = 0; p < n_poly; p++) {
-        int rc = run_inv(c, d_in + (p * l + l - 1) * c->N, r + p * c->N, nullptr, 1, (uint32_t)(l - 1), c->d_fin_plain, s);
+    {
+        // dropped limb of every polynomial in one launch pair: limb p*l + l-1 of the input -> limb p of r
+        int rc = run_inv(c, d_in, r, pl.jobs_rs_intt, (uint32_t)n_poly, 0, c->d_fin_plain, s);
         if (rc) return rc;
     }
     // r mod q_j for every remaining prime: a base conversion with one input and the matrix [1]
@@ -1402,8 +1404,9 @@ extern "C" int b2_rescale_rounded(b2_ctx *c, size_t l, size_t n_poly, const uint
     cudaStream_t s = (cudaStream_t)stream;
     const LevelPlan &pl = c->plan[l];
     uint64_t *r = (uint64_t *)d_ws;
-    for (size_t p = 0; p < n_poly; p++) {
-        int rc = run_inv(c, d_in + (p * l + l - 1) * c->N, r + p * c->N, nullptr, 1, (uint32_t)(l - 1), c->d_fin_plain, s);
+    {
+        // dropped limb of every polynomial in one launch pair: limb p*l + l-1 of the input -> limb p of r
+        int rc = run_inv(c, d_in, r, pl.jobs_rs_intt, (uint32_t)n_poly, 0, c->d_fin_plain, s);
         if (rc) return rc;
     }
     {
@@ -1632,7 +1635,20 @@ extern "C" int b2_poly_op(b2_ctx *c, int op, size_t n_limbs, const uint64_t *d_a
     if (op < 0 || op > 3 || !d_a || !d_out || (op != 3 && !d_b) || n_limbs < 1 || n_limbs > c->size_QP) return fail(B2_EINVAL, "poly_op: bad argument");
     const size_t n = n_limbs * c->N;
     LaunchScope ls(c, (cudaStream_t)stream, "poly_op");
-    poly_op_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(op, d_a, d_b, d_out, c->d_mod, (uint32_t)c->N, (uint32_t)n_limbs);
+    poly_op_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(op, d_a, d_b, d_out, c->d_mod, (uint32_t)c->N, (uint32_t)n_limbs,
+                                                                                   (uint32_t)n_limbs, 0);
+    LAUNCH_CHECK("poly_op_kernel");
+    return B2_OK;
+}
+
+extern "C" int b2_ct_op(b2_ctx *c, int op, size_t l, size_t n_poly, const uint64_t *d_a, const uint64_t *d_b, uint64_t *d_out, void *stream) {
+    CHECK_CTX(c);
+    if (op < 0 || op > 3 || !d_a || !d_out || (op != 3 && !d_b) || l < 1 || l > c->size_QP || n_poly < 1 || n_poly > 3)
+        return fail(B2_EINVAL, "ct_op: bad argument");
+    const size_t n = n_poly * l * c->N;
+    LaunchScope ls(c, (cudaStream_t)stream, "poly_op");
+    poly_op_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(op, d_a, d_b, d_out, c->d_mod, (uint32_t)c->N, (uint32_t)(n_poly * l),
+                                                                                   (uint32_t)l, op == 2);
     LAUNCH_CHECK("poly_op_kernel");
     return B2_OK;
 }
@@ -1648,7 +1664,24 @@ extern "C" int b2_poly_scalar(b2_ctx *c, int op, size_t n_limbs, const uint64_t 
     }
     const size_t n = n_limbs * c->N;
     LaunchScope ls(c, (cudaStream_t)stream, "poly_scalar");
-    poly_scalar_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(op, d_a, tab, d_out, c->d_mod, (uint32_t)c->N, (uint32_t)n_limbs);
+    poly_scalar_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(op, d_a, tab, d_out, c->d_mod, (uint32_t)c->N, (uint32_t)n_limbs,
+                                                                                       (uint32_t)n_limbs);
+    LAUNCH_CHECK("poly_scalar_kernel");
+    return B2_OK;
+}
+
+extern "C" int b2_ct_scalar(b2_ctx *c, size_t l, size_t n_poly, const uint64_t *d_a, const uint64_t *h_scalars, uint64_t *d_out, void *stream) {
+    CHECK_CTX(c);
+    if (!d_a || !d_out || !h_scalars || l < 1 || l > c->size_QP || l > 64 || n_poly < 1 || n_poly > 3) return fail(B2_EINVAL, "ct_scalar: bad argument");
+    ScalarTab tab;
+    for (size_t i = 0; i < l; i++) {
+        if (h_scalars[i] >= c->q[i]) return fail(B2_EINVAL, "ct_scalar: scalar not reduced");
+        tab.v[i] = h_scalars[i];
+    }
+    const size_t n = n_poly * l * c->N;
+    LaunchScope ls(c, (cudaStream_t)stream, "poly_scalar");
+    poly_scalar_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(1, d_a, tab, d_out, c->d_mod, (uint32_t)c->N, (uint32_t)(n_poly * l),
+                                                                                       (uint32_t)l);
     LAUNCH_CHECK("poly_scalar_kernel");
     return B2_OK;
 }
@@ -1767,7 +1800,7 @@ static int build_shard_level(b2_ctx *c, size_t l) {
     }
     for (size_t k = 0; k < 2; k++) {
         for (size_t i = sp.p0; i < sp.p0 + sp.np; i++)
-            jobs_di.push_back(make_uint4((uint32_t)(k * alpha + i), (uint32_t)(sQ + i), (uint32_t)i, 0));
+            jobs_di.push_back(make_uint4((uint32_t)(k * alpha + i), (uint32_t)(sQ + i), (uint32_t)i, (uint32_t)(k * alpha + i)));
         for (size_t j = sp.q0; j < sp.q0 + sp.nq; j++)
             jobs_dn.push_back(make_uint4((uint32_t)(k * l + j), (uint32_t)j, 0, (uint32_t)(k * l + j)));
         grp_dn[k] = BconvGroup{(uint32_t)(k * alpha), (uint32_t)alpha, 0, 0, sp.nq, (uint32_t)(k * l), 0, p_pieces};

@@ -28,6 +28,7 @@ struct Mod {
 
 // One job = one limb transform: where the limb lives and which prime's tables it uses.
 // x = slot in the transform's own buffer, y = prime index, z/w = extra slots for epilogues.
+// Inverse transforms read limb x of src and write limb w of dst (z selects the final scaling).
 using Job = uint4;
 
 struct NttArgs {
@@ -43,7 +44,7 @@ struct NttArgs {
 
 __device__ __forceinline__ Job get_job(const NttArgs &a, uint32_t j) {
     if (a.jobs) return a.jobs[j];
-    return make_uint4(j, a.first_prime + j, a.first_prime + j, 0);
+    return make_uint4(j, a.first_prime + j, a.first_prime + j, j);
 }
 
 // ---- epilogues of the last forward (row) pass ---------------------------------------------------
@@ -396,8 +397,8 @@ __device__ __forceinline__ void inv_body(const NttArgs &a, uint64_t *sm, const J
     const size_t N = (size_t)1 << a.logN;
     const typename A::K k = A::make(md, (int)a.logN);
     const W2 *tw = a.tw + (size_t)job.y * N;
-    const uint64_t *src = a.src + (size_t)job.x * N;
-    uint64_t *dst = a.dst + (size_t)job.x * N;
+    const uint64_t *src = a.src + (size_t)(FIRST ? job.x : job.w) * N;  // the second pass works in place on dst
+    uint64_t *dst = a.dst + (size_t)job.w * N;
     const size_t estride = COLS ? (N >> LOG_T) : 1;
     const size_t cstride = COLS ? 1 : TT;
     const size_t base = COLS ? (size_t)tile * C : (size_t)tile * C * TT;
@@ -606,7 +607,7 @@ __device__ __forceinline__ void inv_cluster_body(const NttArgs &a, uint64_t *sme
     const typename A::K k = A::make(md, 16);
     const W2 *tw = a.tw + (size_t)job.y * N;
     const uint64_t *src = a.src + (size_t)job.x * N;
-    uint64_t *dst = a.dst + (size_t)job.x * N;
+    uint64_t *dst = a.dst + (size_t)job.w * N;
     uint64_t *slab = smem;
     const int tg = threadIdx.x >> 7, t = threadIdx.x & 127;
     uint64_t *ex = smem + CL_SLAB + tg * CL_EX;

@@ -436,6 +436,9 @@ def _check_pair(a, b):
 
 def _limb_op(ctx, op, a, b, out):
     """a, b, out: [size][l][N] tensors; the library maps limb i to prime i, so go per polynomial"""
+    if a.is_contiguous() and out.is_contiguous() and (b is None or b.is_contiguous()) and a.shape[0] <= 3:
+        check(LIB.b2_ct_op(ctx._h, op, a.shape[1], a.shape[0], a.data_ptr(), 0 if b is None else b.data_ptr(), out.data_ptr(), _stream()))
+        return
     for p in range(a.shape[0]):
         check(LIB.b2_poly_op(ctx._h, op, a.shape[1], a[p].data_ptr(), 0 if b is None else b[p].data_ptr(),
                              out[p].data_ptr(), _stream()))
@@ -482,8 +485,11 @@ def multiply_plain(ctx, ct, pt):
     _check_plain(ct, pt)
     out = torch.empty_like(ct.data)
     l = ct._limbs
-    for p in range(ct._size):
-        check(LIB.b2_poly_op(ctx._h, 2, l, ct.data[p].data_ptr(), pt.data.data_ptr(), out[p].data_ptr(), _stream()))
+    if ct.data.is_contiguous() and ct._size <= 3:
+        check(LIB.b2_ct_op(ctx._h, 2, l, ct._size, ct.data.data_ptr(), pt.data.data_ptr(), out.data_ptr(), _stream()))
+    else:
+        for p in range(ct._size):
+            check(LIB.b2_poly_op(ctx._h, 2, l, ct.data[p].data_ptr(), pt.data.data_ptr(), out[p].data_ptr(), _stream()))
     return ct._like(out, scale=ct._scale * pt._scale)
 
 

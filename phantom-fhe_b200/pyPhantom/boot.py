@@ -53,9 +53,15 @@ def bootstrap_required_galois_elts(log_n, stages_per_layer=(5, 5, 5)):
 
 # ---- arithmetic on ciphertexts with (level, scale) bookkeeping: the `ops` of bootmath ---------------------
 class CtOps:
-    def __init__(self, ctx, rlk):
+    def __init__(self, ctx, rlk, counts=None):
         self.ctx, self.rlk = ctx, rlk
-        self.counts = {"mul": 0, "rescale": 0}
+        self.counts = {"mul": 0, "rescale": 0} if counts is None else counts
+        self.stream = _stream()  # the stream current when the ops object is made: one lookup, not one per call
+        self.tab = rlk.pointer_table()
+
+    def on_current_stream(self):
+        """the same arithmetic bound to whatever stream is current now (shares the counters)"""
+        return CtOps(self.ctx, self.rlk, self.counts)
 
     def prime(self, level):
         return float(self.ctx.primes[level - 1])
@@ -82,9 +88,9 @@ class CtOps:
             raise ValueError("operands at different levels")
         out = ctx.empty(2, l)
         ws, nbytes = ctx.workspace(_native.OP_MUL_RELIN, l)
-        tab = self.rlk.pointer_table()
+        tab = self.tab
         check(LIB.b2_multiply_and_relin(ctx._h, l, x.data.data_ptr(), y.data.data_ptr(), tab.ctypes.data, len(tab),
-                                        out.data_ptr(), ws.data_ptr(), nbytes, _stream()))
+                                        out.data_ptr(), ws.data_ptr(), nbytes, self.stream))
         self.counts["mul"] += 1
         return x._like(out, scale=x._scale * y._scale)
 
@@ -94,7 +100,7 @@ class CtOps:
             raise ValueError("out of levels")
         out = ctx.empty(x._size, l - 1)
         ws, nbytes = ctx.workspace(_native.OP_RESCALE, l)
-        check(LIB.b2_rescale_rounded(ctx._h, l, x._size, x.data.data_ptr(), out.data_ptr(), ws.data_ptr(), nbytes, _stream()))
+        check(LIB.b2_rescale_rounded(ctx._h, l, x._size, x.data.data_ptr(), out.data_ptr(), ws.data_ptr(), nbytes, self.stream))
         self.counts["rescale"] += 1
         return x._like(out, chain_index=x._chain_index + 1, scale=x._scale / self.prime(l))
 
@@ -105,14 +111,13 @@ class CtOps:
         k = int(round(c * const_scale))
         sc = self._scalars(k, x._limbs)
         out = torch.empty_like(x.data)
-        for p in range(x._size):
-            check(LIB.b2_poly_scalar(self.ctx._h, 1, x._limbs, x.data[p].data_ptr(), sc.ctypes.data, out[p].data_ptr(), _stream()))
+        check(LIB.b2_ct_scalar(self.ctx._h, x._limbs, x._size, x.data.data_ptr(), sc.ctypes.data, out.data_ptr(), self.stream))
         return x._like(out, scale=x._scale * const_scale)
 
     def add_const(self, x, c):
         sc = self._scalars(int(round(c * x._scale)), x._limbs)
         out = x.data.clone()
-        check(LIB.b2_poly_scalar(self.ctx._h, 0, x._limbs, x.data[0].data_ptr(), sc.ctypes.data, out[0].data_ptr(), _stream()))
+        check(LIB.b2_poly_scalar(self.ctx._h, 0, x._limbs, x.data[0].data_ptr(), sc.ctypes.data, out[0].data_ptr(), self.stream))
         return x._like(out)
 
     def _lin(self, op, x, y):
@@ -121,8 +126,7 @@ class CtOps:
         if abs(x._scale / y._scale - 1.0) > 2.0 ** -40:
             raise ValueError("scale mismatch")
         out = torch.empty_like(x.data)
-        for p in range(x._size):
-            check(LIB.b2_poly_op(self.ctx._h, op, x._limbs, x.data[p].data_ptr(), y.data[p].data_ptr(), out[p].data_ptr(), _stream()))
+        check(LIB.b2_ct_op(self.ctx._h, op, x._limbs, x._size, x.data.data_ptr(), y.data.data_ptr(), out.data_ptr(), self.stream))
         return x._like(out)
 
     def add(self, x, y):
@@ -174,9 +178,11 @@ class bootstrap_key:
         self.rot = {}     # slot rotation step -> switching key
         self.conj = None
         self.c2s, self.s2c = [], []
+        self.side_stream = None
         self.user_limbs = 0
         self.eval_scale = 0.0
-        self.mono_i = None  # NTT form of X^(N/2): multiplication by i on the slots
+        self.mono_i = None      # NTT form of X^(N/2): multiplication by i on the slots
+        self.mono_i_neg = None  # -X^(N/2)
 
 
 def _key_for_elt(sk, ctx, elt):
@@ -244,8 +250,9 @@ def create_bootstrap_key(context, encoder, dense_sk, sparse_hamming_weight=128, 
     mono = np.zeros(N, dtype=np.int64)
     mono[N // 2] = 1
     d = torch.from_numpy(mono).to(ctx.device)
-    bk.mono_i = ctx.empty(sQ)
+    bk.mono_i, bk.mono_i_neg = ctx.empty(sQ), ctx.empty(sQ)
     check(LIB.b2_expand_signed(ctx._h, 0, sQ, d.data_ptr(), bk.mono_i.data_ptr(), 1, _stream()))
+    check(LIB.b2_expand_signed(ctx._h, 0, sQ, (-d).data_ptr(), bk.mono_i_neg.data_ptr(), 1, _stream()))
     torch.cuda.synchronize()
     return bk
 
@@ -322,10 +329,8 @@ def _times_i(ctx, bk, ct, negate=False):
     src/bootstrap.cu:76-98, does it in coefficient form)"""
     l = ct._limbs
     out = torch.empty_like(ct.data)
-    for p in range(2):
-        check(LIB.b2_poly_op(ctx._h, 2, l, ct.data[p].data_ptr(), bk.mono_i.data_ptr(), out[p].data_ptr(), _stream()))
-        if negate:
-            check(LIB.b2_poly_op(ctx._h, 3, l, out[p].data_ptr(), 0, out[p].data_ptr(), _stream()))
+    mono = bk.mono_i_neg if negate else bk.mono_i
+    check(LIB.b2_ct_op(ctx._h, 2, l, 2, ct.data.data_ptr(), mono.data_ptr(), out.data_ptr(), _stream()))
     return ct._like(out)
 
 
@@ -344,6 +349,23 @@ def slot_to_coeff(ctx, bk, lo, hi, ops):
     for layer in bk.s2c:
         x = linear_transform(ctx, bk, x, layer, ops)
     return x
+
+
+def _eval_round_pair(ops, bk, lo, hi):
+    """the real and the imaginary track are independent: the second one runs on a side stream, with its own
+    scratch (everything it allocates belongs to that stream), and joins before SlotToCoeff"""
+    main = torch.cuda.current_stream()
+    if bk.side_stream is None:
+        bk.side_stream = torch.cuda.Stream()
+    side = bk.side_stream
+    side.wait_stream(main)
+    with torch.cuda.stream(side):
+        b = bootmath.eval_round(ops.on_current_stream(), hi, K_RANGE, DOUBLE_ANGLES, COS_DEGREE, bk.eval_scale)
+    a = bootmath.eval_round(ops, lo, K_RANGE, DOUBLE_ANGLES, COS_DEGREE, bk.eval_scale)
+    main.wait_stream(side)
+    for t in (b.data, hi.data):
+        t.record_stream(main)
+    return a, b
 
 
 def bootstrap(context, encoder, ct, bk, user_scale, split_scale_down=False, stats=None):
@@ -368,12 +390,11 @@ def bootstrap(context, encoder, ct, bk, user_scale, split_scale_down=False, stat
             x = ops.rescale(ops.mul_const(x, 1.0, ops.prime(2) * 2.0 ** up))
     raised = mod_raise(ctx, bk, ops.drop(x, 1))
     lo, hi = coeff_to_slot(ctx, bk, raised, ops)
-    ints = [bootmath.eval_round(ops, u, K_RANGE, DOUBLE_ANGLES, COS_DEGREE, bk.eval_scale) for u in (lo, hi)]
+    ints = _eval_round_pair(ops, bk, lo, hi)
     qi = slot_to_coeff(ctx, bk, ints[0], ints[1], ops)  # coefficients q0 * I at "scale" q0, i.e. the integers themselves
     out = ops.drop(raised, qi._limbs)
     res = torch.empty_like(out.data)
-    for p in range(2):
-        check(LIB.b2_poly_op(ctx._h, 1, out._limbs, out.data[p].data_ptr(), qi.data[p].data_ptr(), res[p].data_ptr(), _stream()))
+    check(LIB.b2_ct_op(ctx._h, 1, out._limbs, 2, out.data.data_ptr(), qi.data.data_ptr(), res.data_ptr(), _stream()))
     res = out._like(res, scale=x._scale)
     if abs(x._scale / scale_in - 1.0) > 2.0 ** -40:
         # back to the caller's scale: costs the top user prime
