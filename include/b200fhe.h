@@ -184,6 +184,15 @@ int b2_ct_op(b2_ctx *ctx, int op, size_t size_Ql, size_t n_poly, const uint64_t 
 int b2_ct_scalar(b2_ctx *ctx, size_t size_Ql, size_t n_poly, const uint64_t *d_a, const uint64_t *h_scalars,
                  uint64_t *d_out, void *stream);
 
+/* d_out [n_poly][size_Ql][N] = sum_t term_t * h_scalars[t][limb]  (+ h_const[limb] on polynomial 0, may be NULL):
+ * the weighted sums of Chebyshev basis ciphertexts in EvalMod, which the reference forms with one
+ * multiply_plain by an encoded constant vector and one add per term (src/evalmod.cu:287-334). Term t is a
+ * ciphertext with h_term_limbs[t] >= size_Ql limbs per polynomial (only its first size_Ql are read).
+ * All h_* arrays live on the host; at most 8 terms and 32 limbs. */
+int b2_ct_lincomb(b2_ctx *ctx, size_t size_Ql, size_t n_poly, size_t n_terms, const uint64_t *const *h_terms,
+                  const uint32_t *h_term_limbs, const uint64_t *h_scalars, const uint64_t *h_const,
+                  uint64_t *d_out, void *stream);
+
 /* per-limb integer constants over [n_limbs][N], limb i on prime i: op 0 adds h_scalars[i] to every
  * value of limb i (in NTT form that is adding the constant polynomial h_scalars[i]); op 1 multiplies
  * limb i by h_scalars[i] (replaces multiply_scalar_per_tower_kernel, src/bootstrap.cu:1535-1565).

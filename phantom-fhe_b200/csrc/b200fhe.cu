@@ -1132,6 +1132,27 @@ __global__ void __launch_bounds__(256) rescale_centre_kernel(const uint64_t *__r
     out[idx] = d;
 }
 
+// out = sum_t x_t * s_t (+ c on polynomial 0): per-limb integer weights, one reduction per value. The terms may
+// sit at higher levels than the output (more limbs per polynomial): lt[t] is term t's limb count.
+#define B2_LINCOMB_MAX_TERMS 8
+#define B2_LINCOMB_MAX_LIMBS 32
+struct LincombArgs {
+    const uint64_t *x[B2_LINCOMB_MAX_TERMS];
+    uint32_t lt[B2_LINCOMB_MAX_TERMS];
+    uint64_t s[B2_LINCOMB_MAX_TERMS][B2_LINCOMB_MAX_LIMBS];
+    uint64_t c[B2_LINCOMB_MAX_LIMBS];
+};
+__global__ void __launch_bounds__(256) lincomb_kernel(const __grid_constant__ LincombArgs a, uint64_t *out, const Mod *mod, uint32_t N, uint32_t l,
+                                                     uint32_t n_poly, uint32_t n_terms) {
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (size_t)n_poly * l * N) return;
+    const uint32_t i = (uint32_t)(idx % N), limb = (uint32_t)((idx / N) % l), p = (uint32_t)(idx / ((size_t)N * l));
+    const Mod md = mod[limb];
+    u128 acc{p == 0 ? a.c[limb] : 0, 0};
+    for (uint32_t t = 0; t < n_terms; t++) mac128(acc, a.x[t][((size_t)p * a.lt[t] + limb) * N + i], a.s[t][limb]);
+    out[idx] = barrett128(acc, md.q, md.r0, md.r1);
+}
+
 struct MacPtrs {
     const uint64_t *const *pts;
     const uint64_t *const *babies;
@@ -1683,6 +1704,35 @@ extern "C" int b2_ct_scalar(b2_ctx *c, size_t l, size_t n_poly, const uint64_t *
     poly_scalar_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(1, d_a, tab, d_out, c->d_mod, (uint32_t)c->N, (uint32_t)(n_poly * l),
                                                                                        (uint32_t)l);
     LAUNCH_CHECK("poly_scalar_kernel");
+    return B2_OK;
+}
+
+extern "C" int b2_ct_lincomb(b2_ctx *c, size_t l, size_t n_poly, size_t n_terms, const uint64_t *const *h_terms, const uint32_t *h_term_limbs,
+                             const uint64_t *h_scalars, const uint64_t *h_const, uint64_t *d_out, void *stream) {
+    CHECK_CTX(c);
+    if (!h_terms || !h_term_limbs || !h_scalars || !d_out || l < 1 || l > c->size_QP || l > B2_LINCOMB_MAX_LIMBS || n_poly < 1 || n_poly > 3 ||
+        n_terms < 1 || n_terms > B2_LINCOMB_MAX_TERMS)
+        return fail(B2_EINVAL, "ct_lincomb: bad argument (at most 8 terms and 32 limbs)");
+    LincombArgs a;
+    memset(&a, 0, sizeof(a));
+    for (size_t t = 0; t < n_terms; t++) {
+        if (!h_terms[t] || h_term_limbs[t] < l) return fail(B2_EINVAL, "ct_lincomb: a term is missing or below the output level");
+        a.x[t] = h_terms[t];
+        a.lt[t] = h_term_limbs[t];
+        for (size_t i = 0; i < l; i++) {
+            if (h_scalars[t * l + i] >= c->q[i]) return fail(B2_EINVAL, "ct_lincomb: scalar not reduced");
+            a.s[t][i] = h_scalars[t * l + i];
+        }
+    }
+    for (size_t i = 0; i < l && h_const; i++) {
+        if (h_const[i] >= c->q[i]) return fail(B2_EINVAL, "ct_lincomb: constant not reduced");
+        a.c[i] = h_const[i];
+    }
+    const size_t n = n_poly * l * c->N;
+    LaunchScope ls(c, (cudaStream_t)stream, "lincomb");
+    lincomb_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(a, d_out, c->d_mod, (uint32_t)c->N, (uint32_t)l, (uint32_t)n_poly,
+                                                                                   (uint32_t)n_terms);
+    LAUNCH_CHECK("lincomb_kernel");
     return B2_OK;
 }
 

@@ -697,7 +697,7 @@ def hoist_rotations(context, ct, glk, steps):
 
 from .keys import public_key, secret_key  # noqa: E402,F401
 from .encoder import ckks_encoder  # noqa: E402,F401
-from .boot import (bootstrap, bootstrap_key, bootstrap_required_galois_elts, create_bootstrap_key,  # noqa: E402,F401
+from .boot import (bootstrap, bootstrap_eager, bootstrap_key, bootstrap_required_galois_elts, create_bootstrap_key,  # noqa: E402,F401
                         small_bootstrap_key)
 
 

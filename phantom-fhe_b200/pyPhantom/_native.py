@@ -46,6 +46,7 @@ SIGNATURES = {
     "b2_poly_op": (_int, [_vp, _int, _sz, _vp, _vp, _vp, _vp]),
     "b2_ct_op": (_int, [_vp, _int, _sz, _sz, _vp, _vp, _vp, _vp]),
     "b2_ct_scalar": (_int, [_vp, _sz, _sz, _vp, _vp, _vp, _vp]),
+    "b2_ct_lincomb": (_int, [_vp, _sz, _sz, _sz, _vp, _vp, _vp, _vp, _vp, _vp]),
     "b2_poly_scalar": (_int, [_vp, _int, _sz, _vp, _vp, _vp, _vp]),
     "b2_ctx_set_shard": (_int, [_vp, _int, _int]),
     "b2_shard_limbs": (_int, [_vp, _sz, _vp]),

@@ -29,6 +29,7 @@ C2S_LAYERS, EVAL_LEVELS, S2C_LAYERS = 3, 10, 2
 BOOT_LEVELS = C2S_LAYERS + EVAL_LEVELS + S2C_LAYERS
 K_RANGE, DOUBLE_ANGLES, COS_DEGREE = 28, 3, 63
 SCALE_UP_MARGIN_BITS = 10  # the raised message stays below q0 / 2^10
+GIANT_LANES = 3            # streams the giant steps of a linear transform are dealt over
 
 
 def _stream():
@@ -114,6 +115,25 @@ class CtOps:
         check(LIB.b2_ct_scalar(self.ctx._h, x._limbs, x._size, x.data.data_ptr(), sc.ctypes.data, out.data_ptr(), self.stream))
         return x._like(out, scale=x._scale * const_scale)
 
+    def lincomb(self, terms, c0, level, scale):
+        """sum_i round(c_i * s_i) * x_i + round(c0 * scale) at `level`; x_i may sit higher, every x_i.scale * s_i ~ scale"""
+        n = len(terms)
+        if n > 8 or level > 32:
+            acc = None
+            for x, c, cs in terms:
+                t = self.mul_const(self.drop(x, level), c, cs)
+                acc = t if acc is None else self.add(acc, t)
+            return self.add_const(acc, c0)
+        ptrs = np.array([x.data.data_ptr() for x, _, _ in terms], dtype=np.uint64)
+        limbs = np.array([x._limbs for x, _, _ in terms], dtype=np.uint32)
+        sc = np.concatenate([self._scalars(int(round(c * cs)), level) for _, c, cs in terms])
+        c0v = self._scalars(int(round(c0 * scale)), level)
+        x0 = terms[0][0]
+        out = self.ctx.empty(x0._size, level)
+        check(LIB.b2_ct_lincomb(self.ctx._h, level, x0._size, n, ptrs.ctypes.data, limbs.ctypes.data, sc.ctypes.data, c0v.ctypes.data,
+                                out.data_ptr(), self.stream))
+        return x0._like(out, chain_index=x0._chain_index + (x0._limbs - level), scale=scale)
+
     def add_const(self, x, c):
         sc = self._scalars(int(round(c * x._scale)), x._limbs)
         out = x.data.clone()
@@ -178,7 +198,14 @@ class bootstrap_key:
         self.rot = {}     # slot rotation step -> switching key
         self.conj = None
         self.c2s, self.s2c = [], []
-        self.side_stream = None
+        self._streams = []
+        self.use_graph = True   # replay a captured CUDA graph per (input limbs, input scale) after the first call
+        self._graphs = {}
+
+    def side_streams(self, n):
+        while len(self._streams) < n:
+            self._streams.append(torch.cuda.Stream())
+        return self._streams[:n]
         self.user_limbs = 0
         self.eval_scale = 0.0
         self.mono_i = None      # NTT form of X^(N/2): multiplication by i on the slots
@@ -313,14 +340,31 @@ def linear_transform(ctx, bk, ct, layer, ops):
         ws, nbytes = ctx.workspace(_native.OP_HOIST, l)
         check(LIB.b2_hoist_rotations(ctx._h, l, ct.data.data_ptr(), elts.ctypes.data, len(steps), ksk.ctypes.data, n_evk,
                                      outs.ctypes.data, ws.data_ptr(), nbytes, _stream()))
-    acc = None
-    for (step, idx, tab, _), btab in zip(layer.giants, layer.baby_tabs):
-        part = ctx.empty(2, l)
-        check(LIB.b2_bsgs_mac(ctx._h, l, len(idx), tab.data_ptr(), btab.data_ptr(), part.data_ptr(), _stream()))
-        part = ct._like(part, scale=ct._scale * layer.scale)
-        if step:
-            part = _galois(ctx, part, _elt(step, N), bk.rot[step])
-        acc = part if acc is None else ops.add(acc, part)
+    # the giants are independent until the final sum: deal them round-robin over the key's streams
+    main = torch.cuda.current_stream()
+    lanes = [main] + bk.side_streams(GIANT_LANES - 1)
+    for st in lanes[1:]:
+        st.wait_stream(main)
+    accs = [None] * len(lanes)
+    capturing = torch.cuda.is_current_stream_capturing()
+    for gi, ((step, idx, tab, _), btab) in enumerate(zip(layer.giants, layer.baby_tabs)):
+        k = gi % len(lanes)
+        with torch.cuda.stream(lanes[k]):
+            o = ops if k == 0 else ops.on_current_stream()
+            part = ctx.empty(2, l)
+            check(LIB.b2_bsgs_mac(ctx._h, l, len(idx), tab.data_ptr(), btab.data_ptr(), part.data_ptr(), o.stream))
+            part = ct._like(part, scale=ct._scale * layer.scale)
+            if step:
+                part = _galois(ctx, part, _elt(step, N), bk.rot[step])
+            accs[k] = part if accs[k] is None else o.add(accs[k], part)
+    acc = accs[0]
+    for k in range(1, len(lanes)):
+        if accs[k] is None:
+            continue
+        main.wait_stream(lanes[k])
+        if not capturing:
+            accs[k].data.record_stream(main)
+        acc = ops.add(acc, accs[k])
     return ops.rescale(acc)
 
 
@@ -355,20 +399,45 @@ def _eval_round_pair(ops, bk, lo, hi):
     """the real and the imaginary track are independent: the second one runs on a side stream, with its own
     scratch (everything it allocates belongs to that stream), and joins before SlotToCoeff"""
     main = torch.cuda.current_stream()
-    if bk.side_stream is None:
-        bk.side_stream = torch.cuda.Stream()
-    side = bk.side_stream
+    side = bk.side_streams(1)[0]
     side.wait_stream(main)
     with torch.cuda.stream(side):
         b = bootmath.eval_round(ops.on_current_stream(), hi, K_RANGE, DOUBLE_ANGLES, COS_DEGREE, bk.eval_scale)
     a = bootmath.eval_round(ops, lo, K_RANGE, DOUBLE_ANGLES, COS_DEGREE, bk.eval_scale)
     main.wait_stream(side)
-    for t in (b.data, hi.data):
-        t.record_stream(main)
+    if not torch.cuda.is_current_stream_capturing():
+        for t in (b.data, hi.data):
+            t.record_stream(main)
     return a, b
 
 
 def bootstrap(context, encoder, ct, bk, user_scale, split_scale_down=False, stats=None):
+    """python/src/binding.cu:329-336; src/bootstrap.cu:1702-1949: see bootstrap_eager for the pipeline. The
+    sequence of launches depends only on the input's level and scale, so after one eager run (which also
+    warms every lazily built table) the whole pipeline is captured into a CUDA graph - its streams become
+    parallel branches - and later calls copy the input into the graph's buffer and replay it."""
+    if not bk.use_graph or stats is not None or torch.cuda.is_current_stream_capturing():
+        return bootstrap_eager(context, encoder, ct, bk, user_scale, split_scale_down, stats)
+    key = (ct._limbs, ct._chain_index, ct._scale, ct._size, torch.cuda.current_device())
+    entry = bk._graphs.get(key)
+    if entry is None:
+        out = bootstrap_eager(context, encoder, ct, bk, user_scale, split_scale_down)
+        bk._graphs[key] = "warm"
+        return out
+    if entry == "warm":
+        static_in = ct._like(ct.data.clone())
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            static_out = bootstrap_eager(context, encoder, static_in, bk, user_scale, split_scale_down)
+        entry = bk._graphs[key] = (graph, static_in, static_out)
+    graph, static_in, static_out = entry
+    static_in.data.copy_(ct.data)
+    graph.replay()
+    return static_out._like(static_out.data.clone())
+
+
+def bootstrap_eager(context, encoder, ct, bk, user_scale, split_scale_down=False, stats=None):
     """python/src/binding.cu:329-336; src/bootstrap.cu:1702-1949. `ct`: any level, scale about user_scale with
     |message| <= 1; returns a ciphertext at the input's scale with bk.user_limbs limbs, or one fewer when the
     input scale had to be raised first (an input with at least two limbs and scale below q0 / 2^10)."""

@@ -262,6 +262,10 @@ class ChebyshevEvaluator:
         ops = self.ops
         up = level + 1
         target = scale * ops.prime(up)
+        if hasattr(ops, "lincomb"):  # one fused launch where the arithmetic has it
+            terms = [(self.T[i], float(c[i]), target / ops.scale(self.T[i])) for i in range(1, len(c)) if c[i] != 0.0]
+            if terms:
+                return ops.rescale(ops.lincomb(terms, float(c[0]), up, target))
         acc = None
         for i in range(1, len(c)):
             if c[i] == 0.0 and not (acc is None and i == len(c) - 1):
