@@ -51,6 +51,14 @@ def test_bootstrap_round_trip(log_n, n_user, alpha, c2s_bits, sparse_main):
     err = np.max(np.abs(got - msg))
     assert err < 2e-5, err            # the reference's example accepts 1e-3, its C++ test 5e-6 at N = 2^16
     assert abs(stats["final_scale_over_q0"] - 1.0) < 2.0 ** -45
+    # second call captures the CUDA graph, third replays it: both must reproduce the eager result bit for bit
+    for _ in range(2):
+        again = ph.bootstrap(ctx, enc, ct, bk, scale)
+        assert torch.equal(again.data, out.data)
+    other = sk.encrypt_symmetric(ctx, enc.encode_double_vector(ctx, -msg, scale, chain_index=ctx.total_parm_size() - 2))
+    replayed = ph.bootstrap(ctx, enc, other, bk, scale)
+    assert torch.equal(replayed.data, ph.bootstrap_eager(ctx, enc, other, bk, scale).data)
+    assert np.max(np.abs(enc.decode_double_vector(ctx, sk.decrypt(ctx, replayed)) + msg)) < 2e-5
     # the refreshed ciphertext computes: one multiplication and a rescale on the new levels
     sq = ph.rescale_to_next(ctx, ph.multiply_and_relin(ctx, out, out, bk.relin))
     got2 = enc.decode_double_vector(ctx, sk.decrypt(ctx, sq))

@@ -204,6 +204,48 @@ def test_per_limb_scalars():
         check(LIB.b2_poly_scalar(ctx._h, 1, l, a.data_ptr(), bad.ctypes.data, out.data_ptr(), stream()))
 
 
+def test_ciphertext_wide_ops_and_weighted_sum():
+    N, l = 4096, 4
+    ctx, o = make_ctx(N, [60, 29, 40, 58, 50, 60], 1)
+    primes = [int(q) for q in o.primes]
+    a_h, b_h, pt_h = o.synth_ct(l, 51, 1), o.synth_ct(l, 51, 2), o.fill(1, o.primes[:l], 51, 3)[0]
+    a, b, pt = dev(a_h), dev(b_h), dev(pt_h)
+    out, ref = ctx.empty(2, l), ctx.empty(2, l)
+    for op, second in ((0, b), (1, b), (2, pt), (3, None)):
+        check(LIB.b2_ct_op(ctx._h, op, l, 2, a.data_ptr(), 0 if second is None else second.data_ptr(), out.data_ptr(), stream()))
+        for p in range(2):
+            other = 0 if second is None else (second.data_ptr() if op == 2 else second[p].data_ptr())
+            check(LIB.b2_poly_op(ctx._h, op, l, a[p].data_ptr(), other, ref[p].data_ptr(), stream()))
+        assert torch.equal(out, ref), op
+    sc = np.array([q - 5 - i for i, q in enumerate(primes[:l])], dtype=np.uint64)
+    check(LIB.b2_ct_scalar(ctx._h, l, 2, a.data_ptr(), sc.ctypes.data, out.data_ptr(), stream()))
+    for p in range(2):
+        check(LIB.b2_poly_scalar(ctx._h, 1, l, a[p].data_ptr(), sc.ctypes.data, ref[p].data_ptr(), stream()))
+    assert torch.equal(out, ref)
+    # weighted sum of three terms, one of them held at a higher level (5 limbs per polynomial)
+    hi_h = o.synth_ct(5, 51, 4)
+    terms_h, limbs = [a_h, b_h, hi_h], np.array([l, l, 5], dtype=np.uint32)
+    terms = [dev(t) for t in terms_h]
+    ptrs = np.array([t.data_ptr() for t in terms], dtype=np.uint64)
+    rng = np.random.default_rng(9)
+    w = np.array([[int(rng.integers(0, q)) for q in primes[:l]] for _ in terms], dtype=np.uint64)
+    c0 = np.array([int(rng.integers(0, q)) for q in primes[:l]], dtype=np.uint64)
+    check(LIB.b2_ct_lincomb(ctx._h, l, 2, 3, ptrs.ctypes.data, limbs.ctypes.data, w.ctypes.data, c0.ctypes.data, out.data_ptr(), stream()))
+    want = np.zeros((2, l, N), dtype=object)
+    for t, th in enumerate(terms_h):
+        for i in range(l):
+            want[:, i] += th[:, i].astype(object) * int(w[t, i])
+    for i in range(l):
+        want[0, i] += int(c0[i])
+        want[:, i] %= primes[i]
+    assert np.array_equal(host(out), want.astype(np.uint64))
+    with pytest.raises(ValueError):
+        check(LIB.b2_ct_lincomb(ctx._h, l, 2, 9, ptrs.ctypes.data, limbs.ctypes.data, w.ctypes.data, c0.ctypes.data, out.data_ptr(), stream()))
+    low = np.array([l, l - 1, 5], dtype=np.uint32)
+    with pytest.raises(ValueError):
+        check(LIB.b2_ct_lincomb(ctx._h, l, 2, 3, ptrs.ctypes.data, low.ctypes.data, w.ctypes.data, c0.ctypes.data, out.data_ptr(), stream()))
+
+
 def test_elementwise_tensor_and_bsgs_mac():
     N, l = 8192, 5
     ctx, o = make_ctx(N, [60, 40, 40, 50, 59, 60, 60], 2)
