@@ -253,7 +253,7 @@ def bootstrap_section(ph, torch, np):
     err = np.abs(enc.decode_double_vector(ctx, sk.decrypt(ctx, out)) - msg)
     return {"ms": float(np.median(times)), "ms_min": float(min(times)), "kernels_per_bootstrap": launches, "mode": "CUDA graph replay",
             "log2_max_err": math.log2(float(err.max())), "max_err": float(err.max()), "mean_err": float(err.mean()),
-            "limbs_in": 2, "limbs_out": out.coeff_modulus_size(), "chain_bits": "58|40x8|58x12|29x3|P 58x8",
+            "limbs_in": 2, "limbs_out": out.coeff_modulus_size(), "usable_levels_out": out.coeff_modulus_size() - 1, "chain_bits": "58|40x8|58x12|29x3|P 58x8",
             "secret_hamming_weight": 192, "keygen_s": keygen_s}
 
 

@@ -207,6 +207,7 @@ class bootstrap_key:
             self._streams.append(torch.cuda.Stream())
         return self._streams[:n]
         self.user_limbs = 0
+        self.user_scale, self.up_bits, self.down_const, self.final_target = 0.0, 0, 0, 0.0
         self.eval_scale = 0.0
         self.mono_i = None      # NTT form of X^(N/2): multiplication by i on the slots
         self.mono_i_neg = None  # -X^(N/2)
@@ -217,6 +218,24 @@ def _key_for_elt(sk, ctx, elt):
     rot = ctx.empty(ctx.size_QP)
     check(LIB.b2_galois_permute(ctx._h, elt, sk.data.data_ptr(), rot.data_ptr(), ctx.size_QP, _stream()))
     return sk._kswitch_key(ctx, rot)
+
+
+def _configure_scale(ctx, encoder, bk, user_scale):
+    """scale_up_for_bootstrap (src/bootstrap.cu:1435-1512): every error of EvalRound comes back multiplied by
+    q0 / scale, so a ciphertext at `user_scale` is first raised by 2^up_bits to about q0 / 2^10. The way back costs
+    no user level: the raised ciphertext is multiplied by down_const ~ p_x / 2^up_bits and rescaled by p_x (the prime
+    just above the user levels), and the last SlotToCoeff layer is encoded at the scale that makes the transform
+    deliver q0 * I * down_const / p_x to the last bit double precision can place. Re-run when the scale changes."""
+    plan, s2c_top, pa, pb = bk._s2c_last
+    q0 = float(ctx.primes[0])
+    bk.user_scale = float(user_scale) if user_scale and user_scale > 0 else 0.0
+    bk.up_bits = max(0, int(math.floor(math.log2(q0 / bk.user_scale))) - SCALE_UP_MARGIN_BITS) if bk.user_scale else 0
+    p_x = int(ctx.primes[bk.user_limbs])
+    bk.down_const = int(round(p_x / 2.0 ** bk.up_bits)) if bk.up_bits else 0
+    bk.final_target = q0 * (bk.down_const / p_x) if bk.up_bits else q0
+    e1 = bk.final_target * pa * pb / (bk.eval_scale * pa)
+    bk.s2c[1] = _Layer(ctx, encoder, plan, s2c_top - 1, e1)
+    bk._graphs = {}
 
 
 def create_bootstrap_key(context, encoder, dense_sk, sparse_hamming_weight=128, eval_mod_levels=0, user_scale=0.0,
@@ -258,15 +277,15 @@ def create_bootstrap_key(context, encoder, dense_sk, sparse_hamming_weight=128, 
     for i, layer in enumerate(bootmath.fft_layers(n, c2s_stages, True)):
         limbs = sQ - i
         bk.c2s.append(_Layer(ctx, encoder, bootmath.LayerPlan(layer, n), limbs, float(ctx.primes[limbs - 1]) * ratio))
-    # SlotToCoeff: the first layer at its own prime; the last one is scaled at bootstrap time (it depends on
-    # the exact scale EvalRound ends with), so keep its diagonals and encode against the known target here
+    # SlotToCoeff: the first layer at its own prime; the scale of the last one depends on the caller's scale
+    # (see _configure_scale), so its plan is kept for re-encoding
     s2c_top = eval_top - EVAL_LEVELS
     layers = bootmath.fft_layers(n, s2c_stages, False)
     pa, pb = float(ctx.primes[s2c_top - 1]), float(ctx.primes[s2c_top - 2])
-    e0 = pa
-    e1 = q0 * float(int(ctx.primes[s2c_top - 1])) * float(int(ctx.primes[s2c_top - 2])) / (bk.eval_scale * e0)
-    bk.s2c.append(_Layer(ctx, encoder, bootmath.LayerPlan(layers[0], n), s2c_top, e0))
-    bk.s2c.append(_Layer(ctx, encoder, bootmath.LayerPlan(layers[1], n), s2c_top - 1, e1))
+    bk._s2c_last = (bootmath.LayerPlan(layers[1], n), s2c_top, pa, pb)
+    bk.s2c.append(_Layer(ctx, encoder, bootmath.LayerPlan(layers[0], n), s2c_top, pa))
+    bk.s2c.append(None)
+    _configure_scale(ctx, encoder, bk, user_scale)
     # rotation keys
     steps = set()
     for layer in bk.c2s + bk.s2c:
@@ -439,8 +458,8 @@ def bootstrap(context, encoder, ct, bk, user_scale, split_scale_down=False, stat
 
 def bootstrap_eager(context, encoder, ct, bk, user_scale, split_scale_down=False, stats=None):
     """python/src/binding.cu:329-336; src/bootstrap.cu:1702-1949. `ct`: any level, scale about user_scale with
-    |message| <= 1; returns a ciphertext at the input's scale with bk.user_limbs limbs, or one fewer when the
-    input scale had to be raised first (an input with at least two limbs and scale below q0 / 2^10)."""
+    |message| <= 1 and at least two limbs; returns a ciphertext at the input's scale with bk.user_limbs limbs
+    (q0 and every user prime: the reference's "freshest" chain index)."""
     ctx = context
     if split_scale_down:
         raise ValueError("split_scale_down is not built")
@@ -448,28 +467,25 @@ def bootstrap_eager(context, encoder, ct, bk, user_scale, split_scale_down=False
         raise ValueError("bootstrap wants a 2-polynomial ciphertext in NTT form")
     ops = CtOps(ctx, bk.relin)
     scale_in = ct._scale
-    # scale_up_for_bootstrap (src/bootstrap.cu:1435-1512): every error of EvalRound comes back multiplied by
-    # q0 / scale, so raise the scale to about q0 / 2^10 with one integer multiply and the rescale that drops
-    # the prime above q0 (|message| <= 1 then stays inside the range where the sine is cubic-flat)
     x = ct
-    if x._limbs >= 2:
-        x = ops.drop(x, 2)
-        up = int(math.floor(math.log2(float(ctx.primes[0]) / x._scale))) - SCALE_UP_MARGIN_BITS
-        if up > 0:
-            x = ops.rescale(ops.mul_const(x, 1.0, ops.prime(2) * 2.0 ** up))
+    if bk.user_scale == 0.0 or abs(scale_in / bk.user_scale - 1.0) > 2.0 ** -20:
+        _configure_scale(ctx, encoder, bk, scale_in)  # first use at this scale: re-encode the last SlotToCoeff layer
+    if bk.up_bits:
+        if x._limbs < 2:
+            raise ValueError("bootstrap wants the prime above q0 still present (two limbs or more)")
+        x = ops.rescale(ops.mul_const(ops.drop(x, 2), 1.0, ops.prime(2) * 2.0 ** bk.up_bits))
     raised = mod_raise(ctx, bk, ops.drop(x, 1))
     lo, hi = coeff_to_slot(ctx, bk, raised, ops)
     ints = _eval_round_pair(ops, bk, lo, hi)
-    qi = slot_to_coeff(ctx, bk, ints[0], ints[1], ops)  # coefficients q0 * I at "scale" q0, i.e. the integers themselves
-    out = ops.drop(raised, qi._limbs)
+    qi = slot_to_coeff(ctx, bk, ints[0], ints[1], ops)  # the integers q0 * I (times down_const / p_x) in the coefficients
+    if bk.up_bits:
+        out = ops.rescale(ops.mul_const(ops.drop(raised, qi._limbs + 1), 1.0, float(bk.down_const)))
+    else:
+        out = ops.drop(raised, qi._limbs)
     res = torch.empty_like(out.data)
     check(LIB.b2_ct_op(ctx._h, 1, out._limbs, 2, out.data.data_ptr(), qi.data.data_ptr(), res.data_ptr(), _stream()))
-    res = out._like(res, scale=x._scale)
-    if abs(x._scale / scale_in - 1.0) > 2.0 ** -40:
-        # back to the caller's scale: costs the top user prime
-        res = ops.rescale(ops.mul_const(res, 1.0, scale_in * ops.prime(res._limbs) / res._scale))
     if stats is not None:
         stats.update(ops.counts)
-        stats["final_scale_over_q0"] = qi._scale / float(int(ctx.primes[0]))
+        stats["final_scale_over_target"] = qi._scale / bk.final_target
         stats["raised_scale_log2"] = math.log2(x._scale)
-    return res._like(res.data, scale=scale_in)
+    return out._like(res, scale=scale_in)

@@ -16,7 +16,7 @@ boot = importlib.import_module("pyPhantom.boot")
 bm = importlib.import_module("pyPhantom.bootmath")
 
 
-def _setup(log_n, n_user, alpha, c2s_bits, sparse_main):
+def _setup(log_n, n_user, alpha, c2s_bits, sparse_main, user_scale=2.0 ** 40):
     N = 1 << log_n
     bits = [58] + [40] * n_user + [58] * 12 + [c2s_bits] * 3 + [58] * alpha
     parms = ph.params(ph.scheme_type.ckks)
@@ -29,7 +29,7 @@ def _setup(log_n, n_user, alpha, c2s_bits, sparse_main):
     if sparse_main:
         sk.generate_sparse(ctx, 128)
     enc = ph.ckks_encoder(ctx)
-    bk = ph.create_bootstrap_key(ctx, enc, sk, sparse_hamming_weight=128, eval_mod_levels=9, user_scale=2.0 ** 40)
+    bk = ph.create_bootstrap_key(ctx, enc, sk, sparse_hamming_weight=128, eval_mod_levels=9, user_scale=user_scale)
     return ctx, sk, enc, bk
 
 
@@ -45,12 +45,12 @@ def test_bootstrap_round_trip(log_n, n_user, alpha, c2s_bits, sparse_main):
     assert ct.coeff_modulus_size() == 2
     stats = {}
     out = ph.bootstrap(ctx, enc, ct, bk, scale, stats=stats)
-    assert out.coeff_modulus_size() == bk.user_limbs - 1 == n_user  # fresh levels
+    assert out.coeff_modulus_size() == bk.user_limbs == n_user + 1  # q0 and every user prime
     assert out.scale() == scale
     got = enc.decode_double_vector(ctx, sk.decrypt(ctx, out))
     err = np.max(np.abs(got - msg))
     assert err < 2e-5, err            # the reference's example accepts 1e-3, its C++ test 5e-6 at N = 2^16
-    assert abs(stats["final_scale_over_q0"] - 1.0) < 2.0 ** -45
+    assert abs(stats["final_scale_over_target"] - 1.0) < 2.0 ** -45
     # second call captures the CUDA graph, third replays it: both must reproduce the eager result bit for bit
     for _ in range(2):
         again = ph.bootstrap(ctx, enc, ct, bk, scale)
@@ -94,7 +94,8 @@ def test_stages_against_the_plain_computation():
     assert np.max(np.abs(dec(ints[1]) - I[n:][P])) < 1e-8
     qi = boot.slot_to_coeff(ctx, bk, ints[0], ints[1], ops)
     cq = enc._centred_coefficients(ctx, sk.decrypt(ctx, qi))
-    assert max(abs(int(a) - int(i) * q0) for a, i in zip(cq, I)) < scale * 1e-5
+    # the coefficients hold I times the key's target scale (q0, times down_const / p_x when the key scales the input up)
+    assert max(abs(float(int(a)) / bk.final_target - float(i)) for a, i in zip(cq, I)) < 1e-8
 
 
 def test_errors():
@@ -105,3 +106,17 @@ def test_errors():
         ph.create_bootstrap_key(ctx, enc, sk, eval_mod_levels=5)
     assert len(ph.bootstrap_required_galois_elts(12, [4, 4, 3])) == len(set(ph.bootstrap_required_galois_elts(12, [4, 4, 3])))
     assert (2 * ctx.N - 1) in ph.bootstrap_required_galois_elts(12)
+    pt = enc.encode_double_vector(ctx, np.zeros(4), 2.0 ** 40, chain_index=ctx.size_Q)
+    with pytest.raises(ValueError):     # one limb: the prime needed for the scale-up is gone
+        ph.bootstrap(ctx, enc, sk.encrypt_symmetric(ctx, pt), bk, 2.0 ** 40)
+
+
+def test_scale_follows_the_input():
+    # a key made without user_scale, then used at 2^40 and at 2^36: the last SlotToCoeff layer is re-encoded
+    ctx, sk, enc, bk = _setup(12, 2, 6, 29, True, user_scale=0.0)
+    msg = np.random.default_rng(2).uniform(-0.5, 0.5, ctx.N // 2)
+    for scale in (2.0 ** 40, 2.0 ** 36):
+        ct = sk.encrypt_symmetric(ctx, enc.encode_double_vector(ctx, msg, scale, chain_index=ctx.size_Q - 1))
+        out = ph.bootstrap(ctx, enc, ct, bk, scale)
+        assert bk.user_scale == scale and out.scale() == scale and out.coeff_modulus_size() == bk.user_limbs
+        assert np.max(np.abs(enc.decode_double_vector(ctx, sk.decrypt(ctx, out)) - msg)) < 5e-5
