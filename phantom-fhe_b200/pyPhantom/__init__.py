@@ -808,3 +808,6 @@ def bsgs_apply_giants_with_babies(ctx, galois_key_, babies, diags):
 def bsgs_matmul_preencoded(ctx, galois_key_, x, diags):
     """src/bsgs.cu:361-367"""
     return bsgs_apply_giants_with_babies(ctx, galois_key_, compute_bsgs_babies(ctx, galois_key_, x, diags.baby_steps), diags)
+
+
+from .engine import ckks_engine, ckks_engine_config  # noqa: E402,F401
