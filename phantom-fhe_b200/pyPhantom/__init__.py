@@ -745,6 +745,36 @@ class bsgs_diagonals:
         self.baby_steps, self.giant_steps = int(baby_steps), int(giant_steps)
 
 
+def pre_encode_bsgs_diagonals(context, encoder, matrix, num_rows, num_cols, d_pad, baby_steps, scale):
+    """python/src/binding.cu:542-553; src/bsgs.cu:100-178: diag[d][t] = padded[t][(t + d) mod d_pad]; diagonal g*M + b is
+    pre-rotated by -g*M, tiled over the slots and kept as one signed int64 coefficient vector"""
+    m = np.asarray(matrix, dtype=np.float64).ravel()
+    if num_rows == 0 or num_cols == 0:
+        raise ValueError("pre_encode_bsgs_diagonals: dimensions must be non-zero")
+    if m.size != num_rows * num_cols:
+        raise ValueError("pre_encode_bsgs_diagonals: matrix size mismatch")
+    if d_pad & (d_pad - 1) or d_pad == 0:
+        raise ValueError("pre_encode_bsgs_diagonals: d_pad must be a power of 2")
+    if d_pad < num_rows or d_pad < num_cols:
+        raise ValueError("pre_encode_bsgs_diagonals: d_pad must be >= max(num_rows, num_cols)")
+    if baby_steps == 0 or d_pad % baby_steps:
+        raise ValueError("pre_encode_bsgs_diagonals: baby_steps must divide d_pad")
+    slots = encoder.slot_count()
+    if slots % d_pad:
+        raise ValueError("pre_encode_bsgs_diagonals: num_slots must be multiple of d_pad")
+    padded = np.zeros((d_pad, d_pad))
+    padded[:num_rows, :num_cols] = m.reshape(num_rows, num_cols)
+    t = np.arange(d_pad)
+    out = []
+    for g in range(d_pad // baby_steps):
+        for b in range(baby_steps):
+            d = g * baby_steps + b
+            diag = padded[t, (t + d) % d_pad]
+            row = np.tile(np.roll(diag, g * baby_steps), slots // d_pad)  # entry i takes diag[(i - g*M) mod d_pad]
+            out.append(single_chain_plaintext(encoder.signed_coefficients(context, row, scale, 1), scale))
+    return bsgs_diagonals(out, d_pad, baby_steps, d_pad // baby_steps)
+
+
 def bsgs_required_steps(baby_steps):
     """src/bsgs.cu:180-191"""
     if baby_steps <= 1:

@@ -51,6 +51,31 @@ class public_key:
     def __init__(self):
         self.pk = None  # ciphertext at the key level
 
+    def encrypt_asymmetric(self, ctx, pt, seed=None):
+        """src/secretkey.cu:20-175: (u pk0 + e0, u pk1 + e1) over all QP primes with a ternary u, ModDown by P,
+        then the plaintext added to c0. Levels below the first are reached by dropping limbs."""
+        from . import _native, ciphertext
+        if self.pk is None:
+            raise ValueError("PhantomPublicKey has not been generated")
+        rng = np.random.default_rng(seed)
+        n_all, sQ = ctx.size_QP, ctx.size_Q
+        u = _expand(ctx, rng.integers(-1, 2, ctx.N).astype(np.int64), n_all)
+        cx = ctx.empty(2, n_all)
+        for i in range(2):
+            _poly(ctx, 2, n_all, self.pk.data[i], u, cx[i])
+            _poly(ctx, 0, n_all, cx[i], _error(ctx, rng, n_all), cx[i])
+        out = ctx.empty(2, sQ)
+        ws, nbytes = ctx.workspace(_native.OP_MODDOWN, sQ)
+        check(LIB.b2_moddown(ctx._h, sQ, 2, cx.data_ptr(), out.data_ptr(), ws.data_ptr(), nbytes, _stream()))
+        l = pt._limbs
+        data = out[:, :l].contiguous()
+        _poly(ctx, 0, l, data[0], pt.data, data[0])
+        ct = ciphertext()
+        ct._chain_index, ct._size, ct._N, ct._limbs, ct._scale = pt._chain_index, 2, ctx.N, l, pt._scale
+        ct._is_asymmetric = True
+        ct.data = data
+        return ct
+
     def save(self, stream):
         if self.pk is None:
             raise ValueError("PhantomPublicKey has not been generated")

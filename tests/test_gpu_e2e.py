@@ -175,3 +175,34 @@ def test_interchange_with_the_reference_library(tmp_path):
     want = limb_hashes(mine.decrypt(ctx, my_ct).data.cpu().numpy().view(np.uint64), n)
     assert line.split()[1:] == want, "the reference decrypts this library's bytes to a different plaintext"
     assert np.max(np.abs(enc.decode_complex_vector(ctx, mine.decrypt(ctx, my_ct)) - z)) < 1e-6
+
+
+def test_asymmetric_encryption_round_trip(kit):
+    ctx, enc, sk = kit["ctx"], kit["enc"], kit["sk"]
+    pk = sk.gen_publickey(ctx)
+    v = kit["x"]
+    for chain in (1, 3):
+        ct = pk.encrypt_asymmetric(ctx, enc.encode_complex_vector(ctx, v, SCALE, chain), seed=chain)
+        assert ct.chain_index() == chain and ct.coeff_modulus_size() == ctx.limbs_at(chain)
+        assert np.max(np.abs(_dec(kit, ct) - v)) < 1e-6
+    prod = ph.rescale_to_next(ctx, ph.multiply_and_relin(ctx, ct, ct, kit["rlk"]))
+    assert np.max(np.abs(_dec(kit, prod) - v * v)) < 1e-4
+
+
+def test_pre_encoded_bsgs_matches_numpy(kit):
+    ctx, enc, sk = kit["ctx"], kit["enc"], kit["sk"]
+    d_pad, M = 16, 4
+    rng = np.random.default_rng(4)
+    W = rng.normal(0, 0.5, (12, 10))
+    x = np.zeros(d_pad)
+    x[:10] = rng.normal(size=10)
+    diags = ph.pre_encode_bsgs_diagonals(ctx, enc, W.ravel(), 12, 10, d_pad, M, SCALE)
+    assert (diags.d_pad, diags.baby_steps, diags.giant_steps, len(diags.diagonals)) == (16, 4, 4, 16)
+    ct = sk.encrypt_symmetric(ctx, enc.encode_double_vector(ctx, np.tile(x, enc.slot_count() // d_pad), SCALE, 1))
+    y = ph.bsgs_matmul_preencoded(ctx, kit["glk"], ct, diags)
+    got = enc.decode_double_vector(ctx, sk.decrypt(ctx, y))[:12]
+    assert np.max(np.abs(got - W @ x[:10])) < 2e-5       # python/llm_project/blocks/bsgs_test.py:84-89
+    with pytest.raises(ValueError):
+        ph.pre_encode_bsgs_diagonals(ctx, enc, W.ravel(), 12, 10, 12, 4, SCALE)
+    with pytest.raises(ValueError):
+        ph.pre_encode_bsgs_diagonals(ctx, enc, W.ravel(), 12, 11, 16, 4, SCALE)
