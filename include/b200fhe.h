@@ -9,7 +9,9 @@
  *     value (cudaError_t) on a CUDA failure; b2_last_error() gives the message for this thread;
  *   - all `d_*` pointers are DEVICE pointers to uint64 residues laid out [poly][limb][N]
  *     (coefficient index contiguous), limbs ordered like the context's primes: the reference's
- *     layout (include/ciphertext.h:161-163), so buffers interchange byte for byte;
+ *     layout (include/ciphertext.h:161-163), so buffers interchange byte for byte; they must be
+ *     32-byte aligned (the transforms use 256-bit accesses; B2_EINVAL otherwise - cudaMalloc and
+ *     torch allocations are);
  *   - NTT-form data is in the bit-reversed order the reference's forward transform produces;
  *   - `size_Ql` is the number of Q limbs the operand holds (chain index k of the reference holds
  *     size_Q - (k - 1) limbs, src/context.cu:145-168);

@@ -213,6 +213,8 @@ struct b2_ctx {
     RedcMeta *d_redc = nullptr;    // [size_QP]
     bool bconv_fp = false;         // every digit satisfies sum(q_i) < 2^64 and alpha <= 8
     bool use_cluster = false;      // N = 2^16: single-launch transforms on 8-CTA clusters
+    bool use_pipe = false;         // N = 2^16: persistent passes with asynchronous double-buffered tile loads
+    int sm_count = 148;
     // RNS-limb sharding of one ciphertext over `shard_world` GPUs: this rank's slice of every list
     int shard_rank = 0, shard_world = 1;
     struct ShardPlan {
@@ -590,6 +592,10 @@ extern "C" int b2_ctx_create(size_t N, const uint64_t *primes, size_t size_QP, s
     // SM), so they stay opt-in.
     const char *env_cl = getenv("B2_NTT_CLUSTER");
     c->use_cluster = (c->logN == 16) && env_cl && env_cl[0] == '1';
+    const char *env_pipe = getenv("B2_NTT_PIPE");
+    c->use_pipe = (c->logN == 16) && env_pipe && env_pipe[0] == '1';
+    cudaDeviceGetAttribute(&c->sm_count, cudaDevAttrMultiProcessorCount, c->device);
+    if (c->sm_count < 1) c->sm_count = 148;
     c->plan.resize(sQ + 1);
     for (size_t l = 1; l <= sQ; l++) {
         int rc = build_level(c, l);
@@ -619,14 +625,26 @@ extern "C" int b2_ctx_get_table(const b2_ctx *c, int which, size_t prime_idx, ui
 // ------------------------------------------------------------------------------------------------
 // stage split per polynomial degree: {LOG_A (column pass), LOG_B (row pass)}
 template <int LOG_T> struct PassCfg;
-template <> struct PassCfg<8> { static constexpr int R_STRIDED = 4, R_CONTIG = 4, LOG_C = 3; };
-template <> struct PassCfg<7> { static constexpr int R_STRIDED = 3, R_CONTIG = 4, LOG_C = 4; };
-template <> struct PassCfg<6> { static constexpr int R_STRIDED = 3, R_CONTIG = 3, LOG_C = 4; };
+// LOG_C: sub-transforms per CTA in the row pass; LOG_CC: columns per CTA in the column pass (2^LOG_CC * 8 bytes is
+// the contiguous run a row of the tile covers: 128 bytes, one full line, at LOG_CC = 4)
+#ifndef B2_NTT_LOG_CC8
+#define B2_NTT_LOG_CC8 3
+#endif
+template <> struct PassCfg<8> { static constexpr int R_STRIDED = 4, R_CONTIG = 4, LOG_C = 3, LOG_CC = B2_NTT_LOG_CC8; };
+template <> struct PassCfg<7> { static constexpr int R_STRIDED = 3, R_CONTIG = 4, LOG_C = 4, LOG_CC = 4; };
+template <> struct PassCfg<6> { static constexpr int R_STRIDED = 3, R_CONTIG = 3, LOG_C = 4, LOG_CC = 4; };
 
-template <int LOG_T>
+template <int LOG_T, bool COLS = false>
 static constexpr int pass_threads() {
     using P = PassCfg<LOG_T>;
-    return (1 << (P::LOG_C + LOG_T)) >> (P::R_STRIDED > P::R_CONTIG ? P::R_STRIDED : P::R_CONTIG);
+    return (1 << ((COLS ? P::LOG_CC : P::LOG_C) + LOG_T)) >> (P::R_STRIDED > P::R_CONTIG ? P::R_STRIDED : P::R_CONTIG);
+}
+
+// grid of a pipelined pass: every CTA gets the same number of tiles (as far as divisibility allows)
+static uint32_t pipe_grid(const b2_ctx *c, uint32_t total) {
+    const uint32_t slots = (uint32_t)c->sm_count * 6;
+    const uint32_t per_cta = (total + slots - 1) / slots;
+    return (total + per_cta - 1) / per_cta;
 }
 
 template <int LOG_A, int LOG_B, class Epi>
@@ -634,10 +652,25 @@ static void launch_fwd(const b2_ctx *c, const NttArgs &a, uint32_t njobs, const 
     using A = PassCfg<LOG_A>;
     using B = PassCfg<LOG_B>;
     const uint32_t N = 1u << a.logN;
+    if constexpr (LOG_A == 8 && LOG_B == 8) {
+        if (c->use_pipe) {
+            const uint32_t total = njobs * (N >> (LOG_A + A::LOG_C));
+            {
+                LaunchScope ls(c, s, "ntt_fwd_cols");
+                ntt_fwd_pipe<LOG_A, A::R_STRIDED, A::R_CONTIG, A::LOG_C, true, false, EpiStore>
+                    <<<pipe_grid(c, total), pass_threads<LOG_A>(), 0, s>>>(a, EpiStore{}, total);  // the pipelined passes keep 8 columns
+            }
+            NttArgs b = a;
+            b.src = a.dst;
+            LaunchScope ls(c, s, "ntt_fwd_rows");
+            ntt_fwd_pipe<LOG_B, B::R_STRIDED, B::R_CONTIG, B::LOG_C, false, true, Epi><<<pipe_grid(c, total), pass_threads<LOG_B>(), 0, s>>>(b, epi, total);
+            return;
+        }
+    }
     {
         LaunchScope ls(c, s, "ntt_fwd_cols");
-        ntt_fwd_pass<LOG_A, A::R_STRIDED, A::R_CONTIG, A::LOG_C, true, false, EpiStore>
-            <<<njobs * (N >> (LOG_A + A::LOG_C)), pass_threads<LOG_A>(), 0, s>>>(a, EpiStore{});
+        ntt_fwd_pass<LOG_A, A::R_STRIDED, A::R_CONTIG, A::LOG_CC, true, false, EpiStore>
+            <<<njobs * (N >> (LOG_A + A::LOG_CC)), pass_threads<LOG_A, true>(), 0, s>>>(a, EpiStore{});
     }
     NttArgs b = a;
     b.src = a.dst;  // second pass works in place on the first pass's output
@@ -651,6 +684,20 @@ static void launch_inv(const b2_ctx *c, const NttArgs &a, uint32_t njobs, cudaSt
     using A = PassCfg<LOG_A>;
     using B = PassCfg<LOG_B>;
     const uint32_t N = 1u << a.logN;
+    if constexpr (LOG_A == 8 && LOG_B == 8) {
+        if (c->use_pipe) {
+            const uint32_t total = njobs * (N >> (LOG_B + B::LOG_C));
+            {
+                LaunchScope ls(c, s, "ntt_inv_rows");
+                ntt_inv_pipe<LOG_B, B::R_CONTIG, B::R_STRIDED, B::LOG_C, false, false><<<pipe_grid(c, total), pass_threads<LOG_B>(), 0, s>>>(a, total);
+            }
+            NttArgs b = a;
+            b.src = a.dst;
+            LaunchScope ls(c, s, "ntt_inv_cols");
+            ntt_inv_pipe<LOG_A, A::R_CONTIG, A::R_STRIDED, A::LOG_C, true, true><<<pipe_grid(c, total), pass_threads<LOG_A>(), 0, s>>>(b, total);
+            return;
+        }
+    }
     {
         LaunchScope ls(c, s, "ntt_inv_rows");
         ntt_inv_pass<LOG_B, B::R_CONTIG, B::R_STRIDED, B::LOG_C, false, false>
@@ -659,14 +706,15 @@ static void launch_inv(const b2_ctx *c, const NttArgs &a, uint32_t njobs, cudaSt
     NttArgs b = a;
     b.src = a.dst;
     LaunchScope ls(c, s, "ntt_inv_cols");
-    ntt_inv_pass<LOG_A, A::R_CONTIG, A::R_STRIDED, A::LOG_C, true, true>
-        <<<njobs * (N >> (LOG_A + A::LOG_C)), pass_threads<LOG_A>(), 0, s>>>(b);
+    ntt_inv_pass<LOG_A, A::R_CONTIG, A::R_STRIDED, A::LOG_CC, true, true>
+        <<<njobs * (N >> (LOG_A + A::LOG_CC)), pass_threads<LOG_A, true>(), 0, s>>>(b);
 }
 
 template <class Epi>
 static int run_fwd(const b2_ctx *c, const uint64_t *src, uint64_t *dst, const Job *jobs, uint32_t njobs, uint32_t first_prime,
                    const Epi &epi, cudaStream_t s) {
     if (njobs == 0) return B2_OK;
+    if (!aligned32(src) || !aligned32(dst) || !epi.aligned()) return fail(B2_EINVAL, "device buffers must be 32-byte aligned (256-bit accesses)");
     NttArgs a{src, dst, jobs, first_prime, (uint32_t)c->logN, c->d_tw, c->d_mod, nullptr};
     if (c->use_cluster) {
         static thread_local bool attr_set = false;  // per instantiation (one per epilogue type) and thread
@@ -694,6 +742,7 @@ static int run_fwd(const b2_ctx *c, const uint64_t *src, uint64_t *dst, const Jo
 static int run_inv(const b2_ctx *c, const uint64_t *src, uint64_t *dst, const Job *jobs, uint32_t njobs, uint32_t first_prime,
                    const W2 *fin, cudaStream_t s) {
     if (njobs == 0) return B2_OK;
+    if (!aligned32(src) || !aligned32(dst)) return fail(B2_EINVAL, "device buffers must be 32-byte aligned (256-bit accesses)");
     NttArgs a{src, dst, jobs, first_prime, (uint32_t)c->logN, c->d_itw, c->d_mod, fin};
     if (c->use_cluster) {
         static thread_local bool attr_set = false;

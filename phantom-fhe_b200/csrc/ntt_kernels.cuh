@@ -31,6 +31,12 @@ struct Mod {
 // Inverse transforms read limb x of src and write limb w of dst (z selects the final scaling).
 using Job = uint4;
 
+// resident threads per SM the pass kernels are compiled for (register cap = 65536 / this)
+#ifndef B2_NTT_RESIDENT_THREADS
+#define B2_NTT_RESIDENT_THREADS 768
+#endif
+constexpr int ntt_min_blocks(int threads) { return B2_NTT_RESIDENT_THREADS / threads > 0 ? B2_NTT_RESIDENT_THREADS / threads : 1; }
+
 struct NttArgs {
     const uint64_t *src;  // limb `slot` at src + slot * N
     uint64_t *dst;
@@ -47,18 +53,35 @@ __device__ __forceinline__ Job get_job(const NttArgs &a, uint32_t j) {
     return make_uint4(j, a.first_prime + j, a.first_prime + j, j);
 }
 
+// 256-bit global accesses (sm_100): one lane moves a whole 32-byte sector, so a thread that owns a run of
+// consecutive residues touches every sector once instead of twice with 16-byte accesses. p: 32-byte aligned.
+struct u64x4 {
+    uint64_t a, b, c, d;
+};
+__device__ __forceinline__ u64x4 ld256(const uint64_t *p) {
+    u64x4 v;
+    asm("ld.global.v4.u64 {%0, %1, %2, %3}, [%4];" : "=l"(v.a), "=l"(v.b), "=l"(v.c), "=l"(v.d) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ void st256(uint64_t *p, uint64_t a, uint64_t b, uint64_t c, uint64_t d) {
+    asm volatile("st.global.v4.u64 [%0], {%1, %2, %3, %4};" ::"l"(p), "l"(a), "l"(b), "l"(c), "l"(d) : "memory");
+}
+
 // ---- epilogues of the last forward (row) pass ---------------------------------------------------
 // The row pass leaves every thread with E consecutive canonical residues starting at limb offset o.
 // An epilogue first preloads whatever else it needs for those positions (before the butterflies, so
 // the loads are in flight while the ALUs work) and then finishes and stores them.
+__host__ __device__ inline bool aligned32(const void *p) { return ((uintptr_t)p & 31) == 0; }
+
 struct EpiStore {
     uint64_t *dst;
+    bool aligned() const { return true; }  // dst is the transform's own output, checked by the launcher
     template <int E> struct Regs {};
     __device__ __forceinline__ void init(const NttArgs &a, const Job &job, size_t N) { dst = a.dst + (size_t)job.x * N; }
     template <int E> __device__ __forceinline__ void preload(Regs<E> &, size_t) const {}
     template <int E> __device__ __forceinline__ void finish(const Regs<E> &, size_t o, uint64_t (&x)[E], uint64_t) const {
 #pragma unroll
-        for (int i = 0; i < E; i += 2) *reinterpret_cast<ulonglong2 *>(dst + o + i) = make_ulonglong2(x[i], x[i + 1]);
+        for (int i = 0; i < E; i += 4) st256(dst + o + i, x[i], x[i + 1], x[i + 2], x[i + 3]);
     }
 };
 
@@ -73,9 +96,10 @@ struct EpiSubMul {
     const uint64_t *m_;
     uint64_t *o_;
     W2 kk;
+    bool aligned() const { return aligned32(minuend) && aligned32(out); }
     template <int E> struct Regs {
-        ulonglong2 m[E / 2];
-        ulonglong2 acc[ACCUM ? E / 2 : 1];
+        u64x4 m[E / 4];
+        u64x4 acc[ACCUM ? E / 4 : 1];
     };
     __device__ __forceinline__ void init(const NttArgs &, const Job &job, size_t N) {
         m_ = minuend + (size_t)job.z * N;
@@ -84,21 +108,25 @@ struct EpiSubMul {
     }
     template <int E> __device__ __forceinline__ void preload(Regs<E> &r, size_t o) const {
 #pragma unroll
-        for (int i = 0; i < E / 2; i++) {
-            r.m[i] = *reinterpret_cast<const ulonglong2 *>(m_ + o + 2 * i);
-            if (ACCUM) r.acc[i] = *reinterpret_cast<const ulonglong2 *>(o_ + o + 2 * i);
+        for (int i = 0; i < E / 4; i++) {
+            r.m[i] = ld256(m_ + o + 4 * i);
+            if (ACCUM) r.acc[i] = ld256(o_ + o + 4 * i);
         }
     }
     template <int E> __device__ __forceinline__ void finish(const Regs<E> &r, size_t o, uint64_t (&x)[E], uint64_t q) const {
 #pragma unroll
-        for (int i = 0; i < E / 2; i++) {
-            uint64_t r0 = mul_shoup(sub_mod(r.m[i].x, x[2 * i], q), kk, q);
-            uint64_t r1 = mul_shoup(sub_mod(r.m[i].y, x[2 * i + 1], q), kk, q);
+        for (int i = 0; i < E / 4; i++) {
+            uint64_t r0 = mul_shoup(sub_mod(r.m[i].a, x[4 * i], q), kk, q);
+            uint64_t r1 = mul_shoup(sub_mod(r.m[i].b, x[4 * i + 1], q), kk, q);
+            uint64_t r2 = mul_shoup(sub_mod(r.m[i].c, x[4 * i + 2], q), kk, q);
+            uint64_t r3 = mul_shoup(sub_mod(r.m[i].d, x[4 * i + 3], q), kk, q);
             if (ACCUM) {
-                r0 = add_mod(r.acc[i].x, r0, q);
-                r1 = add_mod(r.acc[i].y, r1, q);
+                r0 = add_mod(r.acc[i].a, r0, q);
+                r1 = add_mod(r.acc[i].b, r1, q);
+                r2 = add_mod(r.acc[i].c, r2, q);
+                r3 = add_mod(r.acc[i].d, r3, q);
             }
-            *reinterpret_cast<ulonglong2 *>(o_ + o + 2 * i) = make_ulonglong2(r0, r1);
+            st256(o_ + o + 4 * i, r0, r1, r2, r3);
         }
     }
 };
@@ -108,19 +136,20 @@ struct EpiSubMul {
 struct EpiSubFrom {
     uint64_t *out;
     uint64_t *o_;
+    bool aligned() const { return aligned32(out); }
     template <int E> struct Regs {
-        ulonglong2 u[E / 2];
+        u64x4 u[E / 4];
     };
     __device__ __forceinline__ void init(const NttArgs &, const Job &job, size_t N) { o_ = out + (size_t)job.w * N; }
     template <int E> __device__ __forceinline__ void preload(Regs<E> &r, size_t o) const {
 #pragma unroll
-        for (int i = 0; i < E / 2; i++) r.u[i] = *reinterpret_cast<const ulonglong2 *>(o_ + o + 2 * i);
+        for (int i = 0; i < E / 4; i++) r.u[i] = ld256(o_ + o + 4 * i);
     }
     template <int E> __device__ __forceinline__ void finish(const Regs<E> &r, size_t o, uint64_t (&x)[E], uint64_t q) const {
 #pragma unroll
-        for (int i = 0; i < E / 2; i++)
-            *reinterpret_cast<ulonglong2 *>(o_ + o + 2 * i) =
-                make_ulonglong2(sub_mod(r.u[i].x, x[2 * i], q), sub_mod(r.u[i].y, x[2 * i + 1], q));
+        for (int i = 0; i < E / 4; i++)
+            st256(o_ + o + 4 * i, sub_mod(r.u[i].a, x[4 * i], q), sub_mod(r.u[i].b, x[4 * i + 1], q), sub_mod(r.u[i].c, x[4 * i + 2], q),
+                  sub_mod(r.u[i].d, x[4 * i + 3], q));
     }
 };
 
@@ -295,7 +324,10 @@ __device__ __forceinline__ void gs_stages(typename A::T (&x)[E], const W2 *tw, s
 // forward pass: R1 strided stages, exchange, R2 contiguous stages
 // FIRST: the input holds canonical residues (else the raw lazy values of the previous pass)
 // ================================================================================================
-template <class A, int LOG_T, int R1, int R2, int LOG_C, bool COLS, bool LAST, class Epi>
+// STAGED: the tile's input already sits in `sm` itself, dense ([e][c] for the column pass, [c][e] for the row
+// pass), put there by asynchronous copies; it is read into registers, and after a barrier the same buffer
+// serves as the exchange buffer.
+template <class A, int LOG_T, int R1, int R2, int LOG_C, bool COLS, bool LAST, class Epi, bool STAGED = false>
 __device__ __forceinline__ void fwd_body(const NttArgs &a, const Epi &epi, uint64_t *sm, const Job &job, const Mod &md, uint32_t tile) {
     using T = typename A::T;
     constexpr bool FIRST = COLS;
@@ -324,8 +356,13 @@ __device__ __forceinline__ void fwd_body(const NttArgs &a, const Epi &epi, uint6
         const uint64_t *p = src + base + (size_t)c * cstride + (size_t)elo * estride;
 #pragma unroll
         for (int i = 0; i < E1; i++) {
-            const uint64_t v = p[(size_t)i * E2 * estride];
+            const int e = elo + i * E2;
+            const uint64_t v = STAGED ? sm[COLS ? (e * C + c) : (c * TT + e)] : p[(size_t)i * E2 * estride];
             x[i] = FIRST ? A::from_u64(v, k) : A::from_raw(v);
+        }
+        if (STAGED) {
+            static_assert(!STAGED || E1 == EPT, "staged input wants one register group per thread");
+            __syncthreads();  // every staged value is in registers: the buffer may now take the exchange
         }
         ct_stages<A, 0, R1, E1>(x, tw, P, 0, 0, k);
 #pragma unroll
@@ -369,7 +406,7 @@ __device__ __forceinline__ void fwd_body(const NttArgs &a, const Epi &epi, uint6
 }
 
 template <int LOG_T, int R1, int R2, int LOG_C, bool COLS, bool LAST, class Epi>
-__global__ void __launch_bounds__((1 << (LOG_C + LOG_T)) / (1 << (R1 > R2 ? R1 : R2)))
+__global__ void __launch_bounds__((1 << (LOG_C + LOG_T)) / (1 << (R1 > R2 ? R1 : R2)), ntt_min_blocks((1 << (LOG_C + LOG_T)) / (1 << (R1 > R2 ? R1 : R2))))
 ntt_fwd_pass(NttArgs a, Epi epi) {
     static_assert(R1 + R2 == LOG_T, "stage split");
     constexpr int TT = 1 << LOG_T, C = 1 << LOG_C;
@@ -386,7 +423,7 @@ ntt_fwd_pass(NttArgs a, Epi epi) {
 // ================================================================================================
 // inverse pass: RA contiguous stages, exchange, RB strided stages
 // ================================================================================================
-template <class A, int LOG_T, int RA, int RB, int LOG_C, bool COLS, bool LAST>
+template <class A, int LOG_T, int RA, int RB, int LOG_C, bool COLS, bool LAST, bool STAGED = false>
 __device__ __forceinline__ void inv_body(const NttArgs &a, uint64_t *sm, const Job &job, const Mod &md, uint32_t tile) {
     using T = typename A::T;
     constexpr bool FIRST = !COLS;
@@ -416,7 +453,16 @@ __device__ __forceinline__ void inv_body(const NttArgs &a, uint64_t *sm, const J
         const uint32_t P = COLS ? 1u : (n1 + tile * C + c);
         T x[EA];
         const uint64_t *p = src + base + (size_t)c * cstride + (size_t)ehi * EA * estride;
-        if (COLS) {
+        if (STAGED) {
+            static_assert(!STAGED || EA == EPT, "staged input wants one register group per thread");
+#pragma unroll
+            for (int i = 0; i < EA; i++) {
+                const int e = ehi * EA + i;
+                const uint64_t v = sm[COLS ? (e * C + c) : (c * TT + e)];
+                x[i] = FIRST ? A::from_u64(v, k) : A::from_raw(v);
+            }
+            __syncthreads();
+        } else if (COLS) {
 #pragma unroll
             for (int i = 0; i < EA; i++) {
                 const uint64_t v = p[(size_t)i * estride];
@@ -424,10 +470,12 @@ __device__ __forceinline__ void inv_body(const NttArgs &a, uint64_t *sm, const J
             }
         } else {
 #pragma unroll
-            for (int i = 0; i < EA; i += 2) {
-                ulonglong2 v = *reinterpret_cast<const ulonglong2 *>(p + i);
-                x[i] = FIRST ? A::from_u64(v.x, k) : A::from_raw(v.x);
-                x[i + 1] = FIRST ? A::from_u64(v.y, k) : A::from_raw(v.y);
+            for (int i = 0; i < EA; i += 4) {
+                const u64x4 v = ld256(p + i);
+                x[i] = FIRST ? A::from_u64(v.a, k) : A::from_raw(v.a);
+                x[i + 1] = FIRST ? A::from_u64(v.b, k) : A::from_raw(v.b);
+                x[i + 2] = FIRST ? A::from_u64(v.c, k) : A::from_raw(v.c);
+                x[i + 3] = FIRST ? A::from_u64(v.d, k) : A::from_raw(v.d);
             }
         }
         gs_stages<A, 0, RA, EA>(x, tw, P, TT >> 1, (size_t)ehi * (EA >> 1), g_pass, k);
@@ -472,7 +520,7 @@ __device__ __forceinline__ void inv_body(const NttArgs &a, uint64_t *sm, const J
 }
 
 template <int LOG_T, int RA, int RB, int LOG_C, bool COLS, bool LAST>
-__global__ void __launch_bounds__((1 << (LOG_C + LOG_T)) / (1 << (RA > RB ? RA : RB)))
+__global__ void __launch_bounds__((1 << (LOG_C + LOG_T)) / (1 << (RA > RB ? RA : RB)), ntt_min_blocks((1 << (LOG_C + LOG_T)) / (1 << (RA > RB ? RA : RB))))
 ntt_inv_pass(NttArgs a) {
     static_assert(RA + RB == LOG_T, "stage split");
     constexpr int TT = 1 << LOG_T, C = 1 << LOG_C;
@@ -484,6 +532,104 @@ ntt_inv_pass(NttArgs a) {
     if (md.q < FP_LIMIT) inv_body<ArithFp, LOG_T, RA, RB, LOG_C, COLS, LAST>(a, sm, job, md, tile);
     else if (md.q < WIDE_LIMIT) inv_body<ArithInt<true>, LOG_T, RA, RB, LOG_C, COLS, LAST>(a, sm, job, md, tile);
     else inv_body<ArithInt<false>, LOG_T, RA, RB, LOG_C, COLS, LAST>(a, sm, job, md, tile);
+}
+
+// ================================================================================================
+// pipelined passes: a resident CTA walks over several tiles, and while it transforms one tile the next one
+// is already on its way from global memory into the second shared-memory buffer (cp.async, 16 bytes per
+// copy, L1 bypassed). The plain kernels above have bytes in flight only during the load phase of each CTA,
+// which bounds them near 2.5 TB/s; here every resident CTA always has a whole tile in flight.
+// ================================================================================================
+__device__ __forceinline__ void cp_async16(void *smem_dst, const void *gsrc) {
+    const uint32_t d = (uint32_t)__cvta_generic_to_shared(smem_dst);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(gsrc) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int KEEP>
+__device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;" ::"n"(KEEP) : "memory");
+}
+
+// tile `tile` of limb slot `slot` of src -> dense buffer ([e][c] or [c][e])
+template <int LOG_T, int LOG_C, bool COLS, int THREADS>
+__device__ __forceinline__ void stage_tile(uint64_t *buf, const uint64_t *src, size_t N, uint32_t slot, uint32_t tile) {
+    constexpr int TT = 1 << LOG_T, C = 1 << LOG_C;
+    constexpr int GRAN = C * TT / 2;  // 16-byte granules per tile
+    const uint64_t *s = src + (size_t)slot * N + (COLS ? (size_t)tile * C : (size_t)tile * C * TT);
+#pragma unroll
+    for (int g = threadIdx.x; g < GRAN; g += THREADS) {
+        if (COLS) {
+            const int row = g / (C / 2), part = g % (C / 2);
+            cp_async16(buf + row * C + part * 2, s + (size_t)row * (N >> LOG_T) + part * 2);
+        } else {
+            cp_async16(buf + g * 2, s + (size_t)g * 2);
+        }
+    }
+}
+
+template <int LOG_T, int R1, int R2, int LOG_C, bool COLS, bool LAST, class Epi>
+__global__ void __launch_bounds__((1 << (LOG_C + LOG_T)) / (1 << (R1 > R2 ? R1 : R2)), ntt_min_blocks((1 << (LOG_C + LOG_T)) / (1 << (R1 > R2 ? R1 : R2))))
+ntt_fwd_pipe(NttArgs a, Epi epi, uint32_t total) {
+    static_assert(R1 == R2, "pipelined passes are built for equal rounds");
+    constexpr int TT = 1 << LOG_T, C = 1 << LOG_C, THREADS = (C * TT) >> R1;
+    __shared__ __align__(16) uint64_t buf[2][C * (TT + (TT >> R2))];
+    const size_t N = (size_t)1 << a.logN;
+    const uint32_t tiles = (uint32_t)(N >> (LOG_T + LOG_C));
+    uint32_t item = blockIdx.x;
+    if (item < total) stage_tile<LOG_T, LOG_C, COLS, THREADS>(buf[0], a.src, N, get_job(a, item / tiles).x, item % tiles);
+    cp_async_commit();
+    for (uint32_t it = 0; item < total; it++, item += gridDim.x) {
+        const uint32_t nxt = item + gridDim.x;
+        if (nxt < total) stage_tile<LOG_T, LOG_C, COLS, THREADS>(buf[(it + 1) & 1], a.src, N, get_job(a, nxt / tiles).x, nxt % tiles);
+        cp_async_commit();
+        cp_async_wait<1>();
+        __syncthreads();
+        uint64_t *sm = buf[it & 1];
+        const Job job = get_job(a, item / tiles);
+        const Mod md = a.mod[job.y];
+        const uint32_t tile = item % tiles;
+        if (md.q < FP_LIMIT) fwd_body<ArithFp, LOG_T, R1, R2, LOG_C, COLS, LAST, Epi, true>(a, epi, sm, job, md, tile);
+        else if (md.q < WIDE_LIMIT) fwd_body<ArithInt<true>, LOG_T, R1, R2, LOG_C, COLS, LAST, Epi, true>(a, epi, sm, job, md, tile);
+        else fwd_body<ArithInt<false>, LOG_T, R1, R2, LOG_C, COLS, LAST, Epi, true>(a, epi, sm, job, md, tile);
+        __syncthreads();  // the buffer is refilled two iterations from now, by the prefetch of the next one
+    }
+    cp_async_wait<0>();
+}
+
+template <int LOG_T, int RA, int RB, int LOG_C, bool COLS, bool LAST>
+__global__ void __launch_bounds__((1 << (LOG_C + LOG_T)) / (1 << (RA > RB ? RA : RB)), ntt_min_blocks((1 << (LOG_C + LOG_T)) / (1 << (RA > RB ? RA : RB))))
+ntt_inv_pipe(NttArgs a, uint32_t total) {
+    static_assert(RA == RB, "pipelined passes are built for equal rounds");
+    constexpr int TT = 1 << LOG_T, C = 1 << LOG_C, THREADS = (C * TT) >> RA;
+    constexpr bool FIRST = !COLS;
+    __shared__ __align__(16) uint64_t buf[2][C * (TT + (TT >> RA))];
+    const size_t N = (size_t)1 << a.logN;
+    const uint32_t tiles = (uint32_t)(N >> (LOG_T + LOG_C));
+    uint32_t item = blockIdx.x;
+    if (item < total) {
+        const Job j0 = get_job(a, item / tiles);
+        stage_tile<LOG_T, LOG_C, COLS, THREADS>(buf[0], a.src, N, FIRST ? j0.x : j0.w, item % tiles);
+    }
+    cp_async_commit();
+    for (uint32_t it = 0; item < total; it++, item += gridDim.x) {
+        const uint32_t nxt = item + gridDim.x;
+        if (nxt < total) {
+            const Job jn = get_job(a, nxt / tiles);
+            stage_tile<LOG_T, LOG_C, COLS, THREADS>(buf[(it + 1) & 1], a.src, N, FIRST ? jn.x : jn.w, nxt % tiles);
+        }
+        cp_async_commit();
+        cp_async_wait<1>();
+        __syncthreads();
+        uint64_t *sm = buf[it & 1];
+        const Job job = get_job(a, item / tiles);
+        const Mod md = a.mod[job.y];
+        const uint32_t tile = item % tiles;
+        if (md.q < FP_LIMIT) inv_body<ArithFp, LOG_T, RA, RB, LOG_C, COLS, LAST, true>(a, sm, job, md, tile);
+        else if (md.q < WIDE_LIMIT) inv_body<ArithInt<true>, LOG_T, RA, RB, LOG_C, COLS, LAST, true>(a, sm, job, md, tile);
+        else inv_body<ArithInt<false>, LOG_T, RA, RB, LOG_C, COLS, LAST, true>(a, sm, job, md, tile);
+        __syncthreads();
+    }
+    cp_async_wait<0>();
 }
 
 }  // namespace b2

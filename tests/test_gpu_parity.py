@@ -313,6 +313,9 @@ def test_error_behaviour():
         assert LIB.b2_ctx_create(bad_n, o.primes.ctypes.data, 5, 2, 0, ctypes.byref(hh)) == -2
     comp = np.array([4097 * 3, int(o.primes[1])], dtype=np.uint64)
     assert LIB.b2_ctx_create(4096, comp.ctypes.data, 2, 1, 0, ctypes.byref(hh)) == -1
+    # a buffer that is only 16-byte aligned is refused before any kernel touches it (256-bit accesses)
+    with pytest.raises(ValueError, match="32-byte aligned"):
+        check(LIB.b2_ntt_forward(h, x.data_ptr() + 16, 1, 0, s))
     torch.cuda.synchronize()
 
 
@@ -346,10 +349,11 @@ def test_full_size_properties():
         assert int(fxh[i].max()) < int(o.primes[i])
 
 
-def test_cluster_transforms_opt_in(monkeypatch):
-    """the single-launch cluster transforms (opt-in) give the same limbs as the reference"""
-    import json
-    monkeypatch.setenv("B2_NTT_CLUSTER", "1")
+@pytest.mark.parametrize("env", ["B2_NTT_CLUSTER", "B2_NTT_PIPE"])
+def test_optional_transform_kernels(monkeypatch, env):
+    """the single-launch cluster transforms and the cp.async-pipelined passes (both opt-in: measured slower than the
+    default two-pass kernels) give the same limbs as the reference"""
+    monkeypatch.setenv(env, "1")
     path = [p for p in GOLDEN if p.endswith("n16_l5_a8.json")][0]
     case, ctx, o = load_case(path)
     N, l, seed, h = o.N, case["level"], case["seed"], ctx._h
