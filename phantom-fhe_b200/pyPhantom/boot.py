@@ -351,19 +351,29 @@ def linear_transform(ctx, bk, ct, layer, ops):
     for i, (_, s) in enumerate(layer.baby_steps):
         if s == 0:
             layer.baby_buf[i].copy_(ct.data)
-    if steps:
-        elts = np.array([_elt(s, N) for _, s in steps], dtype=np.uint32)
-        n_evk = ctx.beta(l)
-        ksk = np.concatenate([bk.rot[s].pointer_table()[:n_evk] for _, s in steps]).astype(np.uint64)
-        outs = np.array([layer.baby_buf[i].data_ptr() for i, _ in steps], dtype=np.uint64)
-        ws, nbytes = ctx.workspace(_native.OP_HOIST, l)
-        check(LIB.b2_hoist_rotations(ctx._h, l, ct.data.data_ptr(), elts.ctypes.data, len(steps), ksk.ctypes.data, n_evk,
-                                     outs.ctypes.data, ws.data_ptr(), nbytes, _stream()))
-    # the giants are independent until the final sum: deal them round-robin over the key's streams
     main = torch.cuda.current_stream()
     lanes = [main] + bk.side_streams(GIANT_LANES - 1)
     for st in lanes[1:]:
         st.wait_stream(main)
+    if steps:
+        # the babies are independent too: each lane hoists its share (its own ModUp of c1 - cheaper than waiting
+        # for the other lanes' steps, since one lane alone leaves most of the GPU idle at these sizes)
+        n_evk = ctx.beta(l)
+        n_lanes = min(len(lanes), max(1, len(steps) // 2))
+        for k in range(n_lanes):
+            mine = steps[k::n_lanes]
+            with torch.cuda.stream(lanes[k]):
+                elts = np.array([_elt(s, N) for _, s in mine], dtype=np.uint32)
+                ksk = np.concatenate([bk.rot[s].pointer_table()[:n_evk] for _, s in mine]).astype(np.uint64)
+                outs = np.array([layer.baby_buf[i].data_ptr() for i, _ in mine], dtype=np.uint64)
+                ws, nbytes = ctx.workspace(_native.OP_HOIST, l)
+                check(LIB.b2_hoist_rotations(ctx._h, l, ct.data.data_ptr(), elts.ctypes.data, len(mine), ksk.ctypes.data, n_evk,
+                                             outs.ctypes.data, ws.data_ptr(), nbytes, _stream()))
+        for st in lanes[1:n_lanes]:   # every giant reads every baby: join, then fork again
+            main.wait_stream(st)
+        for st in lanes[1:]:
+            st.wait_stream(main)
+    # the giants are independent until the final sum: deal them round-robin over the key's streams
     accs = [None] * len(lanes)
     capturing = torch.cuda.is_current_stream_capturing()
     for gi, ((step, idx, tab, _), btab) in enumerate(zip(layer.giants, layer.baby_tabs)):

@@ -138,9 +138,8 @@ class LayerPlan:
                 k -= span  # a layer that does not wrap: signed indices keep the giant steps few
             ks.append(k)
         if n1 is None:
-            n1 = 1 << max(1, int(round(math.log2(max(2.0, math.sqrt(len(ks) / 2.0))))))
-            if len(ks) > 128:
-                n1 = 16
+            # baby rotations share one ModUp (hoisting) and cost about two thirds of a giant rotation: lean to babies
+            n1 = 1 << max(1, math.ceil(math.log2(math.sqrt(max(len(ks), 4)))))
         self.n1 = n1
         self.terms = {}  # g -> [(b, diagonal pre-rotated)]
         for r, k in zip(offs, ks):
