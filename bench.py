@@ -397,6 +397,30 @@ def main():
         e2e_s = float(t.item())
     e2e_value = world * B * e2e_steps / e2e_s
 
+    # ---- N > 1: ONE key switch with its RNS limbs spread over the ranks (two NCCL all-gathers inside) ---------
+    limb_sharded = None
+    if world > 1:
+        from pyPhantom.parallel import LimbShardedKeySwitch
+        sh = LimbShardedKeySwitch(ctx)
+        ws_sh, _ = sh.workspace(LEVEL)
+        c2_sh, ct_sh = dev_ct3[0][2], dev_ct3[0][:2].clone()
+        for _ in range(3):
+            sh.keyswitch(LEVEL, c2_sh, keys[0], ct_sh, ws_sh)
+        barrier()
+        n_sh = max(10, min(args.steps, 50))
+        s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s0.record(stream)
+        for _ in range(n_sh):
+            sh.keyswitch(LEVEL, c2_sh, keys[0], ct_sh, ws_sh)
+        s1.record(stream)
+        barrier()
+        t = torch.tensor([s0.elapsed_time(s1)], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        us = 1e3 * float(t.item()) / n_sh
+        limb_sharded = {"us_per_keyswitch": us, "keyswitch_per_s": 1e6 / us, "ranks": world,
+                        "nvlink_bytes_received_per_gpu_per_keyswitch": int((LEVEL + 2 * SPECIAL) * LIMB_BYTES * (1 - 1 / world)),
+                        "note": "latency of one key switch sharded by RNS limb (weak-scaling value above is data parallel)"}
+
     # ---- per-kernel timing (live, CUDA events on the launching stream) and roofline -------------
     roofline, kernels = None, None
     if rank == 0:
@@ -466,6 +490,7 @@ def main():
             "cpu_baseline": cpu,
             "ntt": ntt,
             "bootstrap": bootstrap,
+            "limb_sharded": limb_sharded,
         }
         print(json.dumps(line), flush=True)
     if world > 1:

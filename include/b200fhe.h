@@ -149,6 +149,20 @@ int b2_apply_galois(b2_ctx *ctx, size_t size_Ql, uint32_t galois_elt, const uint
                     const uint64_t *const *ksk, size_t n_evk, uint64_t *d_out, void *d_ws,
                     size_t ws_bytes, void *stream);
 
+/* Rotations that are summed afterwards (the giant steps of a BSGS linear transform) can share one ModDown.
+ * No counterpart in the reference, which runs apply_galois per giant (src/bootstrap.cu:1290-1340):
+ *   b2_apply_galois_accumulate: d_acc [2][size_Ql][N] (+)= (perm(c0), 0) + Q limbs of <ModUp(perm(c1)), key> * P^-1,
+ *                               d_accP [2][size_P][N] (+)= P limbs of the same inner product;
+ *                               first != 0 starts a new sum (both accumulators are overwritten);
+ *   b2_keyswitch_finish:        d_acc -= NTT(BConv(INTT(d_accP)) * P^-1); d_accP is consumed.
+ * One accumulate + finish equals b2_apply_galois bit for bit. Workspace: B2_OP_ROTATE bytes for accumulate,
+ * 2 * size_Ql limbs for finish. */
+int b2_apply_galois_accumulate(b2_ctx *ctx, size_t size_Ql, uint32_t galois_elt, const uint64_t *d_ct,
+                               const uint64_t *const *ksk, size_t n_evk, uint64_t *d_acc, uint64_t *d_accP,
+                               int first, void *d_ws, size_t ws_bytes, void *stream);
+int b2_keyswitch_finish(b2_ctx *ctx, size_t size_Ql, uint64_t *d_accP, uint64_t *d_acc, void *d_ws,
+                        size_t ws_bytes, void *stream);
+
 /* replaces hoist_rotations (src/evaluate.cu:1929-2082): one ModUp of c1 shared by n_steps
  * automorphisms. ksk[s * n_evk + d] = digit d of the key of elts[s]; d_outs[s] -> [2][size_Ql][N] */
 int b2_hoist_rotations(b2_ctx *ctx, size_t size_Ql, const uint64_t *d_ct, const uint32_t *elts,

@@ -964,7 +964,9 @@ struct EvkPtrs {
 // FUSED = true (whole key switch): Q limbs go straight into the ciphertext as
 //   ct[k][t] += acc * P^-1  and only the P limbs are kept, compactly, in outP [2][alpha][N];
 // together with a ModDown matrix that carries P^-1 this equals ct + (acc - delta) * P^-1.
-template <int MAX_BETA, bool FUSED>
+// ACCP (with FUSED): the P limbs are added to what outP already holds, so that several key switches share
+// one ModDown ("double hoisting": the Q limbs accumulate in ct anyway).
+template <int MAX_BETA, bool FUSED, bool ACCP = false>
 __global__ void __launch_bounds__(256) ks_inner_prod_kernel(const uint64_t *__restrict__ digits, const uint64_t *__restrict__ own,
                                                            EvkPtrs evk, uint64_t *__restrict__ out, uint64_t *__restrict__ ct,
                                                            const W2 *__restrict__ pinv, const Mod *mod, const b2_ctx::RedcMeta *redc,
@@ -1030,6 +1032,10 @@ __global__ void __launch_bounds__(256) ks_inner_prod_kernel(const uint64_t *__re
             *reinterpret_cast<ulonglong2 *>(c1) = make_ulonglong2(add_mod(u1.x, r[2], md.q), add_mod(u1.y, r[3], md.q));
         } else {
             const size_t alpha = lP - l, o = (size_t)(t - l) * N + n;
+            if (ACCP) {
+                const ulonglong2 p0 = *reinterpret_cast<const ulonglong2 *>(out + o), p1 = *reinterpret_cast<const ulonglong2 *>(out + alpha * N + o);
+                r[0] = add_mod(r[0], p0.x, md.q), r[1] = add_mod(r[1], p0.y, md.q), r[2] = add_mod(r[2], p1.x, md.q), r[3] = add_mod(r[3], p1.y, md.q);
+            }
             *reinterpret_cast<ulonglong2 *>(out + o) = make_ulonglong2(r[0], r[1]);
             *reinterpret_cast<ulonglong2 *>(out + alpha * N + o) = make_ulonglong2(r[2], r[3]);
         }
@@ -1073,6 +1079,10 @@ __global__ void __launch_bounds__(256) ks_inner_prod_kernel(const uint64_t *__re
             make_ulonglong2(add_mod(u1.x, mul_shoup(r10, pi, md.q), md.q), add_mod(u1.y, mul_shoup(r11, pi, md.q), md.q));
     } else {
         const size_t alpha = lP - l, o = (size_t)(t - l) * N + n;
+        if (ACCP) {
+            const ulonglong2 p0 = *reinterpret_cast<const ulonglong2 *>(out + o), p1 = *reinterpret_cast<const ulonglong2 *>(out + alpha * N + o);
+            r00 = add_mod(r00, p0.x, md.q), r01 = add_mod(r01, p0.y, md.q), r10 = add_mod(r10, p1.x, md.q), r11 = add_mod(r11, p1.y, md.q);
+        }
         *reinterpret_cast<ulonglong2 *>(out + o) = make_ulonglong2(r00, r01);
         *reinterpret_cast<ulonglong2 *>(out + alpha * N + o) = make_ulonglong2(r10, r11);
     }
@@ -1320,7 +1330,7 @@ extern "C" int b2_modup(b2_ctx *c, size_t l, const uint64_t *d_c2, uint64_t *d_o
 
 // fused = false: out = cx [2][lP][N]. fused = true: Q limbs accumulate into ct, out = [2][alpha][N].
 static int inner_prod_impl(b2_ctx *c, size_t l, const uint64_t *digits, const uint64_t *own, const uint64_t *const *evk, size_t n_evk,
-                           uint64_t *out, uint64_t *ct, bool fused, cudaStream_t s, const uint4 *range = nullptr) {
+                           uint64_t *out, uint64_t *ct, bool fused, cudaStream_t s, const uint4 *range = nullptr, bool acc_p = false) {
     const size_t beta = c->plan[l].beta, lP = l + c->size_P;
     if (n_evk < beta) return fail(B2_EINVAL, "key has fewer digits than this level needs");
     if (beta > 64) return fail(B2_ESIZE, "more than 64 digits");
@@ -1334,7 +1344,10 @@ static int inner_prod_impl(b2_ctx *c, size_t l, const uint64_t *digits, const ui
     if (pairs == 0) return B2_OK;
     const unsigned grid = (unsigned)((pairs + 255) / 256);
     LaunchScope ls(c, s, "ks_inner_prod");
-    if (fused)
+    if (fused && acc_p)
+        ks_inner_prod_kernel<3, true, true><<<grid, 256, 0, s>>>(digits, own, ep, out, ct, c->d_Pinv, c->d_mod, c->d_redc, (uint32_t)c->N, (uint32_t)l,
+                                                               (uint32_t)lP, (uint32_t)c->size_Q, (uint32_t)c->size_QP, (uint32_t)beta, rg);
+    else if (fused)
         ks_inner_prod_kernel<3, true><<<grid, 256, 0, s>>>(digits, own, ep, out, ct, c->d_Pinv, c->d_mod, c->d_redc, (uint32_t)c->N, (uint32_t)l, (uint32_t)lP,
                                                          (uint32_t)c->size_Q, (uint32_t)c->size_QP, (uint32_t)beta, rg);
     else
@@ -1632,6 +1645,52 @@ extern "C" int b2_apply_galois(b2_ctx *c, size_t l, uint32_t elt, const uint64_t
     CUDA_TRY(cudaMemcpyAsync(d_out, p, S * 8, cudaMemcpyDeviceToDevice, s));
     CUDA_TRY(cudaMemsetAsync(d_out + S, 0, S * 8, s));
     return keyswitch_impl(c, l, p + S, ksk, n_evk, d_out, ws, s);
+}
+
+// Rotations whose results are summed share one ModDown: each call adds perm(c0) + (inner product) * P^-1 on the Q limbs
+// of d_acc and the P limbs of the inner product to d_accP; b2_keyswitch_finish converts the P limbs once.
+extern "C" int b2_apply_galois_accumulate(b2_ctx *c, size_t l, uint32_t elt, const uint64_t *d_ct, const uint64_t *const *ksk, size_t n_evk,
+                                          uint64_t *d_acc, uint64_t *d_accP, int first, void *d_ws, size_t ws_bytes, void *stream) {
+    CHECK_CTX(c);
+    CHECK_LEVEL(c, l);
+    if (!d_ct || !ksk || !d_acc || !d_accP || !d_ws) return fail(B2_EINVAL, "apply_galois_accumulate: null pointer");
+    if (ws_bytes < b2_workspace_bytes(c, B2_OP_ROTATE, l)) return fail(B2_EWS, "apply_galois_accumulate: workspace too small");
+    const uint32_t *perm;
+    int rc = galois_lookup(c, elt, &perm);
+    if (rc) return rc;
+    cudaStream_t s = (cudaStream_t)stream;
+    const size_t N = c->N, S = l * N, lP = l + c->size_P, beta = c->plan[l].beta;
+    uint64_t *p = (uint64_t *)d_ws, *t = p + 2 * S, *up = t + S;  // permuted c0 | permuted c1 | t | up
+    rc = gather_impl(c, perm, d_ct, p, 2 * l, s);
+    if (rc) return rc;
+    if (first) {
+        CUDA_TRY(cudaMemcpyAsync(d_acc, p, S * 8, cudaMemcpyDeviceToDevice, s));
+        CUDA_TRY(cudaMemsetAsync(d_acc + S, 0, S * 8, s));
+    } else {
+        rc = b2_poly_op(c, 0, l, d_acc, p, d_acc, stream);
+        if (rc) return rc;
+    }
+    rc = modup_impl(c, l, p + S, up, t, false, s);
+    if (rc) return rc;
+    (void)beta;
+    (void)lP;
+    return inner_prod_impl(c, l, up, p + S, ksk, n_evk, d_accP, d_acc, true, s, nullptr, !first);
+}
+
+extern "C" int b2_keyswitch_finish(b2_ctx *c, size_t l, uint64_t *d_accP, uint64_t *d_acc, void *d_ws, size_t ws_bytes, void *stream) {
+    CHECK_CTX(c);
+    CHECK_LEVEL(c, l);
+    if (!d_accP || !d_acc || !d_ws) return fail(B2_EINVAL, "keyswitch_finish: null pointer");
+    if (ws_bytes < 2 * l * c->N * sizeof(uint64_t)) return fail(B2_EWS, "keyswitch_finish: workspace too small (2 * size_Ql limbs)");
+    cudaStream_t s = (cudaStream_t)stream;
+    const LevelPlan &pl = c->plan[l];
+    const size_t a = c->size_P;
+    uint64_t *delta = (uint64_t *)d_ws;
+    int rc = run_inv(c, d_accP, d_accP, pl.jobs_dnf_intt, (uint32_t)(2 * a), 0, c->d_fin_P, s);
+    if (rc) return rc;
+    rc = run_bconv(c, false, d_accP, delta, nullptr, pl.grp_dnf, 2, pl.outs_dn, c->d_mat_dn_pinv, c->d_matd_dn_pinv, (uint32_t)a, (uint32_t)l, true, s);
+    if (rc) return rc;
+    return run_fwd(c, delta, delta, pl.jobs_dnf_ntt, (uint32_t)(2 * l), 0, EpiSubFrom{d_acc}, s);
 }
 
 extern "C" int b2_hoist_rotations(b2_ctx *c, size_t l, const uint64_t *d_ct, const uint32_t *elts, size_t n_steps, const uint64_t *const *ksk,

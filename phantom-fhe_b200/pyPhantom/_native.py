@@ -39,6 +39,8 @@ SIGNATURES = {
     "b2_galois_prepare": (_int, [_vp, _u32]),
     "b2_galois_permute": (_int, [_vp, _u32, _vp, _vp, _sz, _vp]),
     "b2_apply_galois": (_int, [_vp, _sz, _u32, _vp, _vp, _sz, _vp, _vp, _sz, _vp]),
+    "b2_apply_galois_accumulate": (_int, [_vp, _sz, _u32, _vp, _vp, _sz, _vp, _vp, _int, _vp, _sz, _vp]),
+    "b2_keyswitch_finish": (_int, [_vp, _sz, _vp, _vp, _vp, _sz, _vp]),
     "b2_hoist_rotations": (_int, [_vp, _sz, _vp, _vp, _sz, _vp, _sz, _vp, _vp, _sz, _vp]),
     "b2_bsgs_mac": (_int, [_vp, _sz, _sz, _vp, _vp, _vp, _vp]),
     "b2_expand_single_chain": (_int, [_vp, _sz, _vp, _vp, _vp]),

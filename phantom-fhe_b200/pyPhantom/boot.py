@@ -30,6 +30,7 @@ BOOT_LEVELS = C2S_LAYERS + EVAL_LEVELS + S2C_LAYERS
 K_RANGE, DOUBLE_ANGLES, COS_DEGREE = 28, 3, 63
 SCALE_UP_MARGIN_BITS = 10  # the raised message stays below q0 / 2^10
 GIANT_LANES = 3            # streams the giant steps of a linear transform are dealt over
+FORK_LANES = 6             # extra streams shared by the two EvalRound tracks for their independent pieces
 
 
 def _stream():
@@ -59,10 +60,45 @@ class CtOps:
         self.counts = {"mul": 0, "rescale": 0} if counts is None else counts
         self.stream = _stream()  # the stream current when the ops object is made: one lookup, not one per call
         self.tab = rlk.pointer_table()
+        self.pool = []           # free streams that fork() may use
+        self.keep = []           # results that crossed streams during a graph capture (see fork)
 
     def on_current_stream(self):
-        """the same arithmetic bound to whatever stream is current now (shares the counters)"""
-        return CtOps(self.ctx, self.rlk, self.counts)
+        """the same arithmetic bound to whatever stream is current now (shares the counters and the lane pool)"""
+        o = CtOps(self.ctx, self.rlk, self.counts)
+        o.pool, o.keep = self.pool, self.keep
+        return o
+
+    def fork(self, thunks):
+        """independent pieces of work: all but the first go to free streams of the pool (if any are left), the first
+        runs here; everything joins before this returns. Each thunk gets the arithmetic bound to its stream."""
+        pool = self.pool
+        here = torch.cuda.current_stream()
+        capturing = torch.cuda.is_current_stream_capturing()
+        results, lanes = [None] * len(thunks), []
+        for i in range(1, len(thunks)):
+            if not pool:
+                break
+            lane = pool.pop()
+            lanes.append((i, lane))
+            lane.wait_stream(here)
+            with torch.cuda.stream(lane):
+                results[i] = thunks[i](self.on_current_stream())
+        for i, t in enumerate(thunks):
+            if results[i] is None:
+                results[i] = t(self)
+        for i, lane in lanes:
+            here.wait_stream(lane)
+            if hasattr(results[i], "data"):
+                if capturing:
+                    # record_stream does nothing for the allocator of a capture: once freed, this block could be
+                    # handed to the lane's next user - which may hang off another stream, unordered with the reads
+                    # that follow here. Keep it allocated until the whole pipeline has been issued.
+                    self.keep.append(results[i])
+                else:
+                    results[i].data.record_stream(here)
+            pool.append(lane)
+        return results
 
     def prime(self, level):
         return float(self.ctx.primes[level - 1])
@@ -199,8 +235,15 @@ class bootstrap_key:
         self.conj = None
         self.c2s, self.s2c = [], []
         self._streams = []
+        self._fork_streams = None
         self.use_graph = True   # replay a captured CUDA graph per (input limbs, input scale) after the first call
         self._graphs = {}
+
+    def fork_pool(self):
+        """streams for the independent sub-computations inside EvalRound (disjoint from side_streams)"""
+        if self._fork_streams is None:
+            self._fork_streams = [torch.cuda.Stream() for _ in range(FORK_LANES)]
+        return list(self._fork_streams)
 
     def side_streams(self, n):
         while len(self._streams) < n:
@@ -374,27 +417,50 @@ def linear_transform(ctx, bk, ct, layer, ops):
         for st in lanes[1:]:
             st.wait_stream(main)
     # the giants are independent until the final sum: deal them round-robin over the key's streams
-    accs = [None] * len(lanes)
+    # Giants on one lane are summed anyway, so they share one ModDown: every rotation adds its Q limbs to the lane's
+    # ciphertext accumulator and its P limbs to accP, and b2_keyswitch_finish converts the P limbs once per lane.
     capturing = torch.cuda.is_current_stream_capturing()
+    a = ctx.size_P
+    accs, plain = [None] * len(lanes), None
+    n_evk = ctx.beta(l)
     for gi, ((step, idx, tab, _), btab) in enumerate(zip(layer.giants, layer.baby_tabs)):
         k = gi % len(lanes)
         with torch.cuda.stream(lanes[k]):
-            o = ops if k == 0 else ops.on_current_stream()
+            st = _stream()
             part = ctx.empty(2, l)
-            check(LIB.b2_bsgs_mac(ctx._h, l, len(idx), tab.data_ptr(), btab.data_ptr(), part.data_ptr(), o.stream))
-            part = ct._like(part, scale=ct._scale * layer.scale)
-            if step:
-                part = _galois(ctx, part, _elt(step, N), bk.rot[step])
-            accs[k] = part if accs[k] is None else o.add(accs[k], part)
-    acc = accs[0]
-    for k in range(1, len(lanes)):
+            check(LIB.b2_bsgs_mac(ctx._h, l, len(idx), tab.data_ptr(), btab.data_ptr(), part.data_ptr(), st))
+            if not step:
+                plain = (k, part)  # the giant without rotation
+                continue
+            first = accs[k] is None
+            if first:
+                accs[k] = (ctx.empty(2, l), ctx.empty(2, a), ctx.workspace(_native.OP_ROTATE, l))
+            acc, accP, (ws, nbytes) = accs[k]
+            ktab = bk.rot[step].pointer_table()
+            check(LIB.b2_apply_galois_accumulate(ctx._h, l, _elt(step, N), part.data_ptr(), ktab.ctypes.data, n_evk, acc.data_ptr(),
+                                                 accP.data_ptr(), 1 if first else 0, ws.data_ptr(), nbytes, st))
+    total = None
+    for k, lane in enumerate(lanes):
         if accs[k] is None:
             continue
-        main.wait_stream(lanes[k])
-        if not capturing:
-            accs[k].data.record_stream(main)
-        acc = ops.add(acc, accs[k])
-    return ops.rescale(acc)
+        acc, accP, (ws, nbytes) = accs[k]
+        with torch.cuda.stream(lane):
+            check(LIB.b2_keyswitch_finish(ctx._h, l, accP.data_ptr(), acc.data_ptr(), ws.data_ptr(), nbytes, _stream()))
+        if k:
+            main.wait_stream(lane)
+            if not capturing:
+                acc.record_stream(main)
+        piece = ct._like(acc, scale=ct._scale * layer.scale)
+        total = piece if total is None else ops.add(total, piece)
+    if plain is not None:
+        k, part = plain
+        if k:
+            main.wait_stream(lanes[k])
+            if not capturing:
+                part.record_stream(main)
+        piece = ct._like(part, scale=ct._scale * layer.scale)
+        total = piece if total is None else ops.add(total, piece)
+    return ops.rescale(total)
 
 
 def _times_i(ctx, bk, ct, negate=False):
@@ -476,6 +542,7 @@ def bootstrap_eager(context, encoder, ct, bk, user_scale, split_scale_down=False
     if ct._size != 2 or not ct._is_ntt_form:
         raise ValueError("bootstrap wants a 2-polynomial ciphertext in NTT form")
     ops = CtOps(ctx, bk.relin)
+    ops.pool = bk.fork_pool()
     scale_in = ct._scale
     x = ct
     if bk.user_scale == 0.0 or abs(scale_in / bk.user_scale - 1.0) > 2.0 ** -20:

@@ -216,10 +216,11 @@ class ChebyshevEvaluator:
     def __init__(self, ops, u, babies=8):
         self.ops, self.m = ops, babies
         self.T = {1: u}
+        self.giants = None
 
-    def match(self, x, level, scale):
+    def match(self, x, level, scale, ops=None):
         """bring x down to (level, scale): free if it is already there, else one integer multiply and rescale"""
-        ops = self.ops
+        ops = ops or self.ops
         if ops.level(x) == level:
             if abs(ops.scale(x) / scale - 1.0) > 2.0 ** -40:
                 raise ValueError("operand already at the target level with a different scale")
@@ -230,35 +231,38 @@ class ChebyshevEvaluator:
         x = ops.mul_const(x, 1.0, scale * ops.prime(level + 1) / ops.scale(x))
         return ops.rescale(x)
 
-    def power(self, k):
-        """T_k from T_ceil(k/2), T_floor(k/2): 2 T_a T_b - T_(a-b), a - b in {0, 1}"""
-        if k in self.T:
-            return self.T[k]
-        ops = self.ops
+    def _power(self, k, ops):
+        """T_k from T_ceil(k/2), T_floor(k/2), both already there: 2 T_a T_b - T_(a-b), a - b in {0, 1}"""
         a, b = (k + 1) // 2, k // 2
-        xa, xb = self.power(a), self.power(b)
+        xa, xb = self.T[a], self.T[b]
         lvl = min(ops.level(xa), ops.level(xb))
         prod = ops.mul(ops.drop(xa, lvl), ops.drop(xb, lvl))
         prod = ops.rescale(ops.add(prod, prod))
         if a == b:
-            out = ops.add_const(prod, -1.0)
-        else:
-            out = ops.sub(prod, self.match(self.T[1], ops.level(prod), ops.scale(prod)))
-        self.T[k] = out
-        return out
+            return ops.add_const(prod, -1.0)
+        return ops.sub(prod, self.match(self.T[1], ops.level(prod), ops.scale(prod), ops))
 
     def prepare(self, degree):
-        for k in range(2, min(self.m, degree + 1)):
-            self.power(k)
-        g = self.m
-        self.giants = []
+        """T_2 .. T_(m-1) and the giants T_m, T_2m, ...: powers of equal depth ceil(log2 k) only need shallower ones,
+        so each depth is one fork (independent work the arithmetic may spread over streams)"""
+        if getattr(self, "giants", None) is not None:
+            return
+        g, giants = self.m, []
         while g <= degree:
-            self.power(g)
-            self.giants.append(g)
+            giants.append(g)
             g *= 2
+        need = sorted(set(range(2, min(self.m, degree + 1))) | set(giants))
+        by_depth = {}
+        for k in need:
+            by_depth.setdefault((k - 1).bit_length(), []).append(k)
+        for depth in sorted(by_depth):
+            ks = by_depth[depth]
+            outs = self.ops.fork([(lambda o, k=k: self._power(k, o)) for k in ks])
+            for k, v in zip(ks, outs):
+                self.T[k] = v
+        self.giants = giants
 
-    def _leaf(self, c, level, scale):
-        ops = self.ops
+    def _leaf(self, c, level, scale, ops):
         up = level + 1
         target = scale * ops.prime(up)
         if hasattr(ops, "lincomb"):  # one fused launch where the arithmetic has it
@@ -278,21 +282,23 @@ class ChebyshevEvaluator:
         acc = ops.add_const(acc, float(c[0]))
         return ops.rescale(acc)
 
-    def _eval(self, c, level, scale):
+    def _eval(self, c, level, scale, ops=None):
+        ops = ops or self.ops
         c = np.asarray(c, dtype=np.float64)
         d = len(c) - 1
         while d > 0 and c[d] == 0.0:
             d -= 1
         c = c[: d + 1]
         if d < self.m:
-            return self._leaf(c, level, scale)
-        ops = self.ops
+            return self._leaf(c, level, scale, ops)
         g = max(x for x in self.giants if x <= d)
         q, r = cheb_divide(c, g)
         tg = ops.drop(self.T[g], level + 1)
-        qv = self._eval(q, level + 1, scale * ops.prime(level + 1) / ops.scale(tg))
+        q_scale = scale * ops.prime(level + 1) / ops.scale(tg)
+        # quotient and remainder are independent until the final sum
+        qv, rv = ops.fork([lambda o: self._eval(q, level + 1, q_scale, o), lambda o: self._eval(r, level, scale, o)])
         prod = ops.rescale(ops.mul(qv, tg))
-        return ops.add(prod, self._eval(r, level, scale))
+        return ops.add(prod, rv)
 
     def evaluate(self, coeffs, scale):
         """-> value at level (input level - depth) whose scale is `scale` to about 2^-50"""
@@ -342,6 +348,10 @@ class FloatOps:
 
     def prime(self, level):
         return float(self.primes[level - 1])
+
+    def fork(self, thunks):
+        """independent pieces of work, each given the arithmetic to use: here simply one after the other"""
+        return [t(self) for t in thunks]
 
     def level(self, x):
         return x.level

@@ -246,6 +246,46 @@ def test_ciphertext_wide_ops_and_weighted_sum():
         check(LIB.b2_ct_lincomb(ctx._h, l, 2, 3, ptrs.ctypes.data, low.ctypes.data, w.ctypes.data, c0.ctypes.data, out.data_ptr(), stream()))
 
 
+def test_rotations_sharing_one_moddown():
+    # two rotations accumulated and converted once == the oracle's ModDown of the summed inner products;
+    # a single accumulate + finish == b2_apply_galois
+    N, l = 4096, 5
+    ctx, o = make_ctx(N, [55, 40, 41, 42, 43, 44, 45, 46, 58, 59, 60], 3)
+    beta, a, sQ = o.beta(l), o.size_P, 8
+    ext_primes = [int(q) for q in o.primes[:l]] + [int(q) for q in o.primes[sQ:]]
+    cts = [o.synth_ct(l, 61, 1), o.synth_ct(l, 61, 2)]
+    elts = [o.galois_elt(1), o.galois_elt(3)]
+    keys = [o.synth_key(beta, 61, 10), o.synth_key(beta, 61, 40)]
+    kd = [key_dev(k) for k in keys]
+    for e in elts:
+        check(LIB.b2_galois_prepare(ctx._h, e))
+    want_c0 = np.zeros((l, N), dtype=np.uint64)
+    cx_sum = np.zeros((2, l + a, N), dtype=np.uint64)
+    for ct_h, e, key in zip(cts, elts, keys):
+        perm = o.galois_perm(e)
+        pc = ct_h[:, :, perm]
+        cx = o.ks_inner_prod(l, o.modup(l, pc[1]), key)
+        for t, q in enumerate(ext_primes):
+            cx_sum[:, t] = (cx_sum[:, t] + cx[:, t]) % np.uint64(q)
+        for t in range(l):
+            want_c0[t] = (want_c0[t] + pc[0, t]) % np.uint64(ext_primes[t])
+    want = np.stack([o.moddown(l, cx_sum[0]), o.moddown(l, cx_sum[1])])
+    for t in range(l):
+        want[0, t] = (want[0, t] + want_c0[t]) % np.uint64(ext_primes[t])
+    acc, accP = ctx.empty(2, l), ctx.empty(2, a)
+    ws, nb = _ws(ctx, _native.OP_ROTATE, l)
+    for i, (ct_h, e) in enumerate(zip(cts, elts)):
+        check(LIB.b2_apply_galois_accumulate(ctx._h, l, e, dev(ct_h).data_ptr(), kd[i][1].ctypes.data, beta, acc.data_ptr(), accP.data_ptr(),
+                                             1 if i == 0 else 0, ws.data_ptr(), nb, stream()))
+    check(LIB.b2_keyswitch_finish(ctx._h, l, accP.data_ptr(), acc.data_ptr(), ws.data_ptr(), nb, stream()))
+    assert np.array_equal(host(acc), want)
+    # one rotation alone
+    check(LIB.b2_apply_galois_accumulate(ctx._h, l, elts[0], dev(cts[0]).data_ptr(), kd[0][1].ctypes.data, beta, acc.data_ptr(), accP.data_ptr(), 1,
+                                         ws.data_ptr(), nb, stream()))
+    check(LIB.b2_keyswitch_finish(ctx._h, l, accP.data_ptr(), acc.data_ptr(), ws.data_ptr(), nb, stream()))
+    assert np.array_equal(host(acc), o.apply_galois(l, elts[0], keys[0], cts[0]))
+
+
 def test_elementwise_tensor_and_bsgs_mac():
     N, l = 8192, 5
     ctx, o = make_ctx(N, [60, 40, 40, 50, 59, 60, 60], 2)
