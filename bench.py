@@ -257,6 +257,59 @@ def bootstrap_section(ph, torch, np):
             "secret_hamming_weight": 192, "keygen_s": keygen_s}
 
 
+def compositions_section(ph, ctx, torch, np, synth, primes, keys, N, level, reps=20):
+    """the evaluator calls built on the key switch, at the bench level (24 limbs), through the pyPhantom surface:
+    one stream (latency, what the reference's own timings in tests/golden/n16_l24_a8.json measure) and a batch of 8
+    over 4 streams (throughput)"""
+    from pyPhantom import _native
+    def ct_of(buf, n_poly=2):
+        c = ph.ciphertext()
+        c._chain_index, c._size, c._N, c._limbs = 1, n_poly, N, level
+        c.data = torch.from_numpy(synth.poly(N, primes[:level], n_poly, 77, buf).view(np.int64)).cuda()
+        return c
+    cts = [ct_of(300 + i) for i in range(8)]
+    rlk = keys[0]
+    glk = ph.galois_key.from_keys([keys[i % len(keys)] for i in range(len(ctx.galois_elts))])
+    steps = [s for s in (1, 2, 3) if ph.get_elt_from_step(s, N) in ctx.galois_elts]
+    ops = {
+        "multiply_and_relin": lambda c: ph.multiply_and_relin(ctx, c, c, rlk),
+        "multiply_and_relin_rescale": lambda c: ph.rescale_to_next(ctx, ph.multiply_and_relin(ctx, c, c, rlk)),
+        "rescale": lambda c: ph.rescale_to_next(ctx, c),
+    }
+    if steps:
+        ops["rotate"] = lambda c: ph.rotate(ctx, c, steps[0], glk)
+        ops["hoist_rotations_x%d" % len(steps)] = lambda c: ph.hoist_rotations(ctx, c, glk, steps)
+    out = {}
+    main = torch.cuda.current_stream()
+    side = [torch.cuda.Stream() for _ in range(4)]
+    for name, fn in ops.items():
+        for _ in range(3):
+            fn(cts[0])
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for r in range(reps):
+            fn(cts[r % 8])
+        e1.record()
+        torch.cuda.synchronize()
+        one = 1e3 * e0.elapsed_time(e1) / reps
+        for sd in side:
+            sd.wait_stream(main)
+        e0.record()
+        for r in range(reps):
+            for b in range(8):
+                with torch.cuda.stream(side[b % 4]):
+                    fn(cts[b])
+        for sd in side:
+            main.wait_stream(sd)
+        e1.record()
+        torch.cuda.synchronize()
+        out[name] = {"us_one_stream": one, "per_s_batch8_streams4": 8 * reps / (e0.elapsed_time(e1) / 1e3)}
+    out["reference_us_same_gpu"] = {"multiply_and_relin": 580.5, "multiply_and_relin_rescale": 720.1, "rotate": 559.3,
+                                    "hoist_rotations_x3": 1239.4, "source": "tests/golden/n16_l24_a8.json times_us"}
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -302,7 +355,7 @@ def main():
     parms.set_poly_modulus_degree(N)
     parms.set_coeff_modulus(mods)
     parms.set_special_modulus_size(SPECIAL)
-    parms.set_galois_elts([2 * N - 1])
+    parms.set_galois_elts([2 * N - 1] + ph.get_elts_from_steps([1, 2, 3], N))
     ctx = ph.context(parms)
     B, K = args.batch, args.keys
     seed = 1000 + rank
@@ -464,9 +517,10 @@ def main():
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         cpu = cpu_baseline_sample()
 
-    ntt, bootstrap = None, None
+    ntt, bootstrap, compositions = None, None, None
     if rank == 0 and world == 1 and not args.no_extras:
         ntt = ntt_section(ph, ctx, torch, LIB, check, N, len(primes))
+        compositions = compositions_section(ph, ctx, torch, np, synth, primes, keys, N, LEVEL)
         del dev_ct3, keys, stage
         torch.cuda.empty_cache()
         bootstrap = bootstrap_section(ph, torch, np)
@@ -491,6 +545,7 @@ def main():
             "kernels": kernels,
             "cpu_baseline": cpu,
             "ntt": ntt,
+            "compositions": compositions,
             "bootstrap": bootstrap,
             "limb_sharded": limb_sharded,
         }
