@@ -695,6 +695,13 @@ def hoist_rotations(context, ct, glk, steps):
     return [ct._like(o) for o in outs]
 
 
+def hoisting(context, ct, glk, steps):
+    """python/src/binding.cu:285; src/evaluate.cu:1732-1927: the SUM of the rotations of ct by `steps`, computed from one
+    ModUp. The reference also shares the ModDown (it sums the inner products first), so its limbs differ from this sum of
+    separately converted rotations by the rounding of one ModDown; the decrypted values agree to the noise level."""
+    return add_many(context, hoist_rotations(context, ct, glk, steps))
+
+
 from .keys import public_key, secret_key  # noqa: E402,F401
 from .encoder import ckks_encoder  # noqa: E402,F401
 from .boot import (bootstrap, bootstrap_eager, bootstrap_key, bootstrap_required_galois_elts, create_bootstrap_key,  # noqa: E402,F401
@@ -743,6 +750,15 @@ class bsgs_diagonals:
     def __init__(self, diagonals, d_pad, baby_steps, giant_steps):
         self.diagonals, self.d_pad = list(diagonals), int(d_pad)
         self.baby_steps, self.giant_steps = int(baby_steps), int(giant_steps)
+
+
+def encode_single_chain_plaintext(context, encoder, slots, scale):
+    """python/src/binding.cu:405-470; src/single_chain_plaintext.cu:93-192: encode, then keep one signed, centred int64
+    coefficient vector instead of the residues in every limb"""
+    arr = np.asarray(slots)
+    if arr.ndim != 1:
+        raise RuntimeError("encode_single_chain_plaintext: array must be 1-D")
+    return single_chain_plaintext(encoder.signed_coefficients(context, arr, scale, 1), scale)
 
 
 def pre_encode_bsgs_diagonals(context, encoder, matrix, num_rows, num_cols, d_pad, baby_steps, scale):

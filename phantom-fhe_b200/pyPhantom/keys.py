@@ -181,6 +181,20 @@ class secret_key:
         from . import galois_key
         return galois_key.from_keys([self.create_one_galois_key(ctx, i) for i in range(len(ctx.galois_elts))])
 
+    def create_galois_keys_per_level(self, ctx, indices, target_chain_indices):
+        """src/secretkey.cu:726-775: keys only for the listed Galois-element indices; the other slots stay empty (to be
+        served by fallbacks). The reference truncates each key to the limbs its target chain index needs; here every key
+        is generated at full size, which serves any level."""
+        from . import galois_key, relin_key
+        if len(indices) != len(target_chain_indices):
+            raise ValueError("create_galois_keys_per_level: indices and target_chain_indices must have the same length")
+        out = galois_key.from_keys([relin_key() for _ in ctx.galois_elts])
+        for idx in indices:
+            if idx >= len(ctx.galois_elts):
+                raise IndexError("create_galois_keys_per_level: index out of range")
+            out.relin_keys[idx] = self.create_one_galois_key(ctx, idx)
+        return out
+
     # ---- data path ------------------------------------------------------------------------------------
     def encrypt_symmetric(self, ctx, pt):
         """(c0, c1) = (-(a s + e) + m, a) at the plaintext's level (src/secretkey.cu:236-299, 771-812)"""

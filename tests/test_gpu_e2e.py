@@ -206,3 +206,25 @@ def test_pre_encoded_bsgs_matches_numpy(kit):
         ph.pre_encode_bsgs_diagonals(ctx, enc, W.ravel(), 12, 10, 12, 4, SCALE)
     with pytest.raises(ValueError):
         ph.pre_encode_bsgs_diagonals(ctx, enc, W.ravel(), 12, 11, 16, 4, SCALE)
+
+
+def test_remaining_surface_names(kit):
+    ctx, enc, sk = kit["ctx"], kit["enc"], kit["sk"]
+    x = kit["x"]
+    # hoisting = sum of the rotations
+    got = _dec(kit, ph.hoisting(ctx, kit["cx"], kit["glk"], [1, 2, 4]))
+    assert np.max(np.abs(got - (np.roll(x, -1) + np.roll(x, -2) + np.roll(x, -4)))) < 1e-5
+    # keys for a subset of the elements, the rest served by a fallback
+    idx = [ctx.galois_elts.index(ph.get_elt_from_step(s, N)) for s in (1, 2)]
+    some = sk.create_galois_keys_per_level(ctx, idx, [1, 1])
+    assert np.max(np.abs(_dec(kit, ph.rotate(ctx, kit["cx"], 2, some)) - np.roll(x, -2))) < 1e-6
+    with pytest.raises(ValueError):
+        ph.rotate(ctx, kit["cx"], 4, some)
+    some.set_fallback(ctx.galois_elts.index(ph.get_elt_from_step(4, N)), kit["glk"].get_relin_keys(ctx.galois_elts.index(ph.get_elt_from_step(4, N))))
+    assert np.max(np.abs(_dec(kit, ph.rotate(ctx, kit["cx"], 4, some)) - np.roll(x, -4))) < 1e-6
+    with pytest.raises(ValueError):
+        sk.create_galois_keys_per_level(ctx, idx, [1])
+    # single-chain encoding of a slot vector expands to the plaintext the encoder makes
+    scp = ph.encode_single_chain_plaintext(ctx, enc, x, SCALE)
+    full = ph.expand_single_chain_to_full(ctx, scp, 2)
+    assert torch.equal(full.data, enc.encode_complex_vector(ctx, x, SCALE, 2).data)
