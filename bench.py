@@ -321,6 +321,7 @@ def main():
     ap.add_argument("--streams", type=int, default=4, help="CUDA streams the batch of independent key switches is spread over")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer arm (used for ncu captures)")
+    ap.add_argument("--e2e-streams", type=int, default=3, help="streams of the host-buffer arm (copy in, key switch, copy out per stream)")
     ap.add_argument("--no-extras", action="store_true", help="skip the NTT and bootstrap sections of the line")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
@@ -421,7 +422,7 @@ def main():
     value = world * B * args.steps / (ms / 1e3)
 
     # ---- e2e: host buffers through the pyPhantom surface, copies inside the timed region -----------
-    streams = [torch.cuda.Stream() for _ in range(3)]
+    streams = [torch.cuda.Stream() for _ in range(args.e2e_streams)]
     stage = [torch.empty(3, LEVEL, N, dtype=torch.int64, device="cuda") for _ in streams]
 
     def step_e2e():
