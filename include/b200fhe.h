@@ -149,6 +149,13 @@ int b2_apply_galois(b2_ctx *ctx, size_t size_Ql, uint32_t galois_elt, const uint
                     const uint64_t *const *ksk, size_t n_evk, uint64_t *d_out, void *d_ws,
                     size_t ws_bytes, void *stream);
 
+/* replaces hoisting_inplace (src/evaluate.cu:1732-1927): d_out [2][size_Ql][N] = the SUM over the n_steps Galois
+ * elements of the rotated d_ct, from one ModUp of c1 and one ModDown per polynomial (ksk and workspace as for
+ * b2_hoist_rotations; d_out must not alias d_ct) */
+int b2_hoisting_sum(b2_ctx *ctx, size_t size_Ql, const uint64_t *d_ct, const uint32_t *elts, size_t n_steps,
+                    const uint64_t *const *ksk, size_t n_evk, uint64_t *d_out, void *d_ws, size_t ws_bytes,
+                    void *stream);
+
 /* Rotations that are summed afterwards (the giant steps of a BSGS linear transform) can share one ModDown.
  * No counterpart in the reference, which runs apply_galois per giant (src/bootstrap.cu:1290-1340):
  *   b2_apply_galois_accumulate: d_acc [2][size_Ql][N] (+)= (perm(c0), 0) + Q limbs of <ModUp(perm(c1)), key> * P^-1,

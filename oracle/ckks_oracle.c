@@ -563,6 +563,41 @@ void ora_hoist_rotations(const ora_ctx *c, size_t size_Ql, const uint64_t *ct, c
     free(up); free(pup); free(cx); free(pc0); free(dn); free(perm);
 }
 
+/* src/evaluate.cu:1732-1927 (hoisting_inplace): ModUp(c1) once (:1826-1829); per step gather c0 and every extended
+ * digit, inner product, everything summed - c0 over Q_l (:1861-1863), the inner products over Q_l and P (:1876-1882);
+ * then one ModDown per polynomial (:1885-1888); out0 = sum perm(c0) + cx0, out1 = cx1 (:1895-1906). */
+void ora_hoisting_sum(const ora_ctx *c, size_t size_Ql, const uint64_t *ct, const uint32_t *elts, size_t n_steps,
+                      const uint64_t *const *const *ksk, uint64_t *out) {
+    size_t N = c->N, alpha = c->size_P, beta = ora_beta(c, size_Ql), size_QlP = size_Ql + alpha, S = size_Ql * N;
+    uint64_t *up = (uint64_t *)malloc(beta * size_QlP * N * sizeof(uint64_t));
+    uint64_t *pup = (uint64_t *)malloc(beta * size_QlP * N * sizeof(uint64_t));
+    uint64_t *cx = (uint64_t *)malloc(2 * size_QlP * N * sizeof(uint64_t));
+    uint64_t *acc = (uint64_t *)calloc(2 * size_QlP * N, sizeof(uint64_t));
+    uint64_t *acc0 = (uint64_t *)calloc(S, sizeof(uint64_t));
+    uint64_t *pc0 = (uint64_t *)malloc(S * sizeof(uint64_t));
+    uint64_t *dn = (uint64_t *)malloc(S * sizeof(uint64_t));
+    uint32_t *perm = (uint32_t *)malloc(N * sizeof(uint32_t));
+    ora_modup(c, size_Ql, ct + S, up);
+    for (size_t s = 0; s < n_steps; s++) {
+        ora_galois_perm(N, elts[s], perm);
+        gather(ct, perm, size_Ql, N, pc0);
+        ora_add(c, size_Ql, acc0, pc0, acc0);
+        gather(up, perm, beta * size_QlP, N, pup);
+        ora_ks_inner_prod(c, size_Ql, pup, ksk[s], cx);
+        for (size_t k = 0; k < 2; k++)
+            for (size_t t = 0; t < size_QlP; t++) {
+                uint64_t q = c->q[t < size_Ql ? t : c->size_Q + (t - size_Ql)];
+                uint64_t *a = acc + (k * size_QlP + t) * N;
+                const uint64_t *x = cx + (k * size_QlP + t) * N;
+                for (size_t i = 0; i < N; i++) a[i] = addmod(a[i], x[i], q);
+            }
+    }
+    ora_moddown(c, size_Ql, acc, dn);
+    ora_add(c, size_Ql, acc0, dn, out);
+    ora_moddown(c, size_Ql, acc + size_QlP * N, out + S);
+    free(up); free(pup); free(cx); free(acc); free(acc0); free(pc0); free(dn); free(perm);
+}
+
 /* src/bsgs.cu:51-96 */
 void ora_bsgs_mac(const ora_ctx *c, size_t size_Ql, size_t M, const uint64_t *const *pts,
                   const uint64_t *const *babies, uint64_t *out) {

@@ -107,6 +107,8 @@ void ora_apply_galois(const ora_ctx *c, size_t size_Ql, uint32_t galois_elt,
 void ora_hoist_rotations(const ora_ctx *c, size_t size_Ql, const uint64_t *ct,
                          const uint32_t *elts, size_t n_steps,
                          const uint64_t *const *const *ksk, uint64_t *const *outs);
+void ora_hoisting_sum(const ora_ctx *c, size_t size_Ql, const uint64_t *ct, const uint32_t *elts, size_t n_steps,
+                      const uint64_t *const *const *ksk, uint64_t *out);
 /* src/bsgs.cu:51-96: acc_k = sum_b pt_b (.) baby_b[k], reduced after every term.
  * pts[b] -> [l][N]; babies[b] -> [2][l][N]; out [2][l][N]. */
 void ora_bsgs_mac(const ora_ctx *c, size_t size_Ql, size_t M, const uint64_t *const *pts,

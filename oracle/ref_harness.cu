@@ -310,6 +310,12 @@ int main(int argc, char **argv) {
         auto outs = hoist_rotations(context, a, glk, steps);
         for (size_t e = 0; e < outs.size(); e++)
             record("hoist_" + std::to_string(steps[e]), outs[e].data(), 2 * l, N);
+        {
+            // hoisting_inplace: the SUM of the rotations, one ModUp and one ModDown pair for all steps
+            PhantomCiphertext h(a);
+            hoisting_inplace(context, h, glk, steps);
+            record("hoisting_sum", h.data(), 2 * l, N);
+        }
         if (time_iters) {
             PhantomCiphertext r(a);
             g_times.push_back({"rotate_us", time_us([&] {

@@ -1725,6 +1725,43 @@ extern "C" int b2_hoist_rotations(b2_ctx *c, size_t l, const uint64_t *d_ct, con
     return B2_OK;
 }
 
+// hoisting_inplace (src/evaluate.cu:1732-1927): the SUM of n_steps rotations from one ModUp and one ModDown pair.
+extern "C" int b2_hoisting_sum(b2_ctx *c, size_t l, const uint64_t *d_ct, const uint32_t *elts, size_t n_steps, const uint64_t *const *ksk,
+                               size_t n_evk, uint64_t *d_out, void *d_ws, size_t ws_bytes, void *stream) {
+    CHECK_CTX(c);
+    CHECK_LEVEL(c, l);
+    if (!d_ct || !elts || !ksk || !d_out || !d_ws || n_steps == 0) return fail(B2_EINVAL, "hoisting_sum: bad argument");
+    if (ws_bytes < b2_workspace_bytes(c, B2_OP_HOIST, l)) return fail(B2_EWS, "hoisting_sum: workspace too small");
+    cudaStream_t s = (cudaStream_t)stream;
+    const size_t N = c->N, a = c->size_P, lP = l + a, beta = c->plan[l].beta, S = l * N;
+    const LevelPlan &pl = c->plan[l];
+    std::vector<const uint32_t *> perms(n_steps);
+    for (size_t i = 0; i < n_steps; i++) {
+        int rc = galois_lookup(c, elts[i], &perms[i]);
+        if (rc) return rc;
+    }
+    // ws: t [l] | up [beta][lP] | pup [beta][lP] | accP [2][alpha] + delta [2][l] (the 2*lP limbs of cx) | pc0 [l]
+    uint64_t *t = (uint64_t *)d_ws, *up = t + S, *pup = up + beta * lP * N, *accP = pup + beta * lP * N, *delta = accP + 2 * a * N,
+             *pc0 = accP + 2 * lP * N;
+    int rc = modup_impl(c, l, d_ct + S, up, t, true, s);
+    if (rc) return rc;
+    for (size_t i = 0; i < n_steps; i++) {
+        rc = gather_impl(c, perms[i], d_ct, i == 0 ? d_out : pc0, l, s);
+        if (rc) return rc;
+        if (i == 0) CUDA_TRY(cudaMemsetAsync(d_out + S, 0, S * 8, s));
+        else if ((rc = b2_poly_op(c, 0, l, d_out, pc0, d_out, stream))) return rc;
+        rc = gather_impl(c, perms[i], up, pup, beta * lP, s);
+        if (rc) return rc;
+        rc = inner_prod_impl(c, l, pup, nullptr, ksk + i * n_evk, n_evk, accP, d_out, true, s, nullptr, i > 0);
+        if (rc) return rc;
+    }
+    rc = run_inv(c, accP, accP, pl.jobs_dnf_intt, (uint32_t)(2 * a), 0, c->d_fin_P, s);
+    if (rc) return rc;
+    rc = run_bconv(c, false, accP, delta, nullptr, pl.grp_dnf, 2, pl.outs_dn, c->d_mat_dn_pinv, c->d_matd_dn_pinv, (uint32_t)a, (uint32_t)l, true, s);
+    if (rc) return rc;
+    return run_fwd(c, delta, delta, pl.jobs_dnf_ntt, (uint32_t)(2 * l), 0, EpiSubFrom{d_out}, s);
+}
+
 extern "C" int b2_bsgs_mac(b2_ctx *c, size_t l, size_t M, const uint64_t *const *pts, const uint64_t *const *babies, uint64_t *d_out, void *stream) {
     CHECK_CTX(c);
     CHECK_LEVEL(c, l);

@@ -696,10 +696,28 @@ def hoist_rotations(context, ct, glk, steps):
 
 
 def hoisting(context, ct, glk, steps):
-    """python/src/binding.cu:285; src/evaluate.cu:1732-1927: the SUM of the rotations of ct by `steps`, computed from one
-    ModUp. The reference also shares the ModDown (it sums the inner products first), so its limbs differ from this sum of
-    separately converted rotations by the rounding of one ModDown; the decrypted values agree to the noise level."""
-    return add_many(context, hoist_rotations(context, ct, glk, steps))
+    """python/src/binding.cu:285; src/evaluate.cu:1732-1927: the SUM of the rotations of ct by `steps`, from one ModUp and
+    one ModDown per polynomial"""
+    ctx = context
+    if ct._size > 2:
+        raise ValueError("ciphertext size must be 2")
+    steps = list(steps)
+    if not steps:
+        raise ValueError("steps cannot be empty")
+    l = ct._limbs
+    elts = np.array([get_elt_from_step(s, ctx.N) for s in steps], dtype=np.uint32)
+    tabs = []
+    for e in elts:
+        if int(e) not in ctx.galois_elts:
+            raise RuntimeError("Galois key not present in hoisting")
+        tabs.append(_key_table(ctx, glk.get_relin_keys(ctx.galois_elts.index(int(e))), l))
+    n_evk = ctx.beta(l)
+    ksk = np.concatenate([t[:n_evk] for t in tabs]).astype(np.uint64)
+    out = ctx.empty(2, l)
+    ws, nbytes = ctx.workspace(_native.OP_HOIST, l)
+    check(LIB.b2_hoisting_sum(ctx._h, l, ct.data.data_ptr(), elts.ctypes.data, len(steps), ksk.ctypes.data, n_evk,
+                              out.data_ptr(), ws.data_ptr(), nbytes, _stream()))
+    return ct._like(out)
 
 
 from .keys import public_key, secret_key  # noqa: E402,F401

@@ -42,6 +42,7 @@ SIGNATURES = {
     "b2_apply_galois_accumulate": (_int, [_vp, _sz, _u32, _vp, _vp, _sz, _vp, _vp, _int, _vp, _sz, _vp]),
     "b2_keyswitch_finish": (_int, [_vp, _sz, _vp, _vp, _vp, _sz, _vp]),
     "b2_hoist_rotations": (_int, [_vp, _sz, _vp, _vp, _sz, _vp, _sz, _vp, _vp, _sz, _vp]),
+    "b2_hoisting_sum": (_int, [_vp, _sz, _vp, _vp, _sz, _vp, _sz, _vp, _vp, _sz, _vp]),
     "b2_bsgs_mac": (_int, [_vp, _sz, _sz, _vp, _vp, _vp, _vp]),
     "b2_expand_single_chain": (_int, [_vp, _sz, _vp, _vp, _vp]),
     "b2_expand_signed": (_int, [_vp, _sz, _sz, _vp, _vp, _int, _vp]),

@@ -53,6 +53,7 @@ def _load():
         "ora_galois_perm": (None, [_sz, _u32, _vp]),
         "ora_apply_galois": (None, [_vp, _sz, _u32, _vp, _vp]),
         "ora_hoist_rotations": (None, [_vp, _sz, _vp, _vp, _sz, _vp, _vp]),
+        "ora_hoisting_sum": (None, [_vp, _sz, _vp, _vp, _sz, _vp, _vp]),
         "ora_bsgs_mac": (None, [_vp, _sz, _sz, _vp, _vp, _vp]),
         "ora_expand_single_chain": (None, [_vp, _sz, _vp, _vp]),
         "ora_add": (None, [_vp, _sz, _vp, _vp, _vp]),
@@ -224,6 +225,15 @@ class Oracle:
         LIB.ora_hoist_rotations(self.h, l, _p(ct), _p(e), len(e), _p(tabptrs), _p(outptrs))
         return outs
 
+    def hoisting_sum(self, l, ct, elts, keys):
+        ct = np.ascontiguousarray(ct, dtype=np.uint64)
+        e = np.asarray(elts, dtype=np.uint32)
+        tabs = [_ptr_array(k) for k in keys]
+        tabptrs = _ptr_array(tabs)
+        out = np.empty((2, l, self.N), dtype=np.uint64)
+        LIB.ora_hoisting_sum(self.h, l, _p(ct), _p(e), len(e), _p(tabptrs), _p(out))
+        return out
+
     def bsgs_mac(self, l, pts, babies):
         pts = [np.ascontiguousarray(p, dtype=np.uint64) for p in pts]
         babies = [np.ascontiguousarray(b, dtype=np.uint64) for b in babies]
@@ -304,6 +314,7 @@ def golden_case_stages(o, case):
     outs = o.hoist_rotations(l, a, case["elts"], keys)
     for step, out in zip(case["steps"], outs):
         res[f"hoist_{step}"] = limb_hashes(out, N)
+    res["hoisting_sum"] = limb_hashes(o.hoisting_sum(l, a, case["elts"], keys), N)
     if case.get("bsgs"):
         M, G = case["bsgs"]
         diags = [o.synth_signed(seed, 3000 + d) for d in range(M * G)]

@@ -138,6 +138,9 @@ def test_every_stage_matches_the_reference(path):
                                  optr.ctypes.data, ws.data_ptr(), nb, s))
     for step, out in zip(case["steps"], outs):
         assert hashes(out, N) == want[f"hoist_{step}"]
+    summed = ctx.empty(2, l)
+    check(LIB.b2_hoisting_sum(h, l, a.data_ptr(), elts.ctypes.data, len(elts), ksk.ctypes.data, beta, summed.data_ptr(), ws.data_ptr(), nb, s))
+    assert hashes(summed, N) == want["hoisting_sum"]
     assert np.array_equal(host(a), a_h), "inputs must stay untouched"
 
 
