@@ -290,8 +290,6 @@ def create_bootstrap_key(context, encoder, dense_sk, sparse_hamming_weight=128, 
     SlotToCoeff, this pipeline 10 and 2: the same 12 primes)."""
     from .keys import secret_key
     ctx = context
-    if split_scale_down:
-        raise ValueError("split_scale_down is not built")
     if eval_mod_levels not in (0, 9, EVAL_LEVELS):
         raise ValueError("eval_mod_levels: this pipeline uses the 12 primes below CoeffToSlot as 10 + 2")
     if ctx.size_Q < BOOT_LEVELS + 2:
@@ -513,7 +511,7 @@ def bootstrap(context, encoder, ct, bk, user_scale, split_scale_down=False, stat
     parallel branches - and later calls copy the input into the graph's buffer and replay it."""
     if not bk.use_graph or stats is not None or torch.cuda.is_current_stream_capturing():
         return bootstrap_eager(context, encoder, ct, bk, user_scale, split_scale_down, stats)
-    key = (ct._limbs, ct._chain_index, ct._scale, ct._size, torch.cuda.current_device())
+    key = (ct._limbs, ct._chain_index, ct._scale, ct._size, bool(split_scale_down), torch.cuda.current_device())
     entry = bk._graphs.get(key)
     if entry is None:
         out = bootstrap_eager(context, encoder, ct, bk, user_scale, split_scale_down)
@@ -535,10 +533,9 @@ def bootstrap(context, encoder, ct, bk, user_scale, split_scale_down=False, stat
 def bootstrap_eager(context, encoder, ct, bk, user_scale, split_scale_down=False, stats=None):
     """python/src/binding.cu:329-336; src/bootstrap.cu:1702-1949. `ct`: any level, scale about user_scale with
     |message| <= 1 and at least two limbs; returns a ciphertext at the input's scale with bk.user_limbs limbs
-    (q0 and every user prime: the reference's "freshest" chain index)."""
+    (q0 and every user prime: the reference's "freshest" chain index); with split_scale_down one limb fewer, where the
+    reference's split mode returns."""
     ctx = context
-    if split_scale_down:
-        raise ValueError("split_scale_down is not built")
     if ct._size != 2 or not ct._is_ntt_form:
         raise ValueError("bootstrap wants a 2-polynomial ciphertext in NTT form")
     ops = CtOps(ctx, bk.relin)
@@ -565,4 +562,9 @@ def bootstrap_eager(context, encoder, ct, bk, user_scale, split_scale_down=False
         stats.update(ops.counts)
         stats["final_scale_over_target"] = qi._scale / bk.final_target
         stats["raised_scale_log2"] = math.log2(x._scale)
-    return out._like(res, scale=scale_in)
+    out = out._like(res, scale=scale_in)
+    if split_scale_down:
+        # the reference's split mode gives up the top user prime for precision (src/ckks_engine.cu:563-566); this
+        # pipeline has that precision already, so the flag only selects where the result is handed over
+        out = out._like(out.data[:, : out._limbs - 1].contiguous(), chain_index=out._chain_index + 1)
+    return out

@@ -39,9 +39,6 @@ class ckks_engine:
             raise ValueError("CKKSEngine: num_special_primes must be >= 1")
         if cfg.use_bootstrap_to_17_levels:
             raise ValueError("CKKSEngine: the use_bootstrap_to_17_levels chain is not built")
-        if cfg.split_scale_down:
-            raise ValueError("CKKSEngine: split_scale_down is not built (the bootstrap already returns at user level 0 "
-                             "with the raised-scale precision)")
         if cfg.user_rotation_target_chain_indices and len(cfg.user_rotation_target_chain_indices) != len(cfg.user_rotation_steps):
             raise ValueError("CKKSEngine: user_rotation_target_chain_indices size must match user_rotation_steps size")
         size_q = 1 + cfg.num_scale_levels + 3 + 9 + 3
@@ -65,7 +62,7 @@ class ckks_engine:
         self._ctx = context(parms)
         self._sk = secret_key(self._ctx)
         self._enc = ckks_encoder(self._ctx)
-        self._bk = boot.create_bootstrap_key(self._ctx, self._enc, self._sk, cfg.sparse_hw, 9, cfg.user_scale, False)
+        self._bk = boot.create_bootstrap_key(self._ctx, self._enc, self._sk, cfg.sparse_hw, 9, cfg.user_scale, cfg.split_scale_down)
         # user rotation keys: steps the bootstrap already owns are shared (src/ckks_engine.cu:268-360 registers them as
         # non-owning fallbacks), the rest are generated
         n = N // 2
@@ -157,9 +154,10 @@ class ckks_engine:
         if ct.chain_index() != self._bottom - 1:
             mod_switch_to_inplace(self._ctx, ct, self._bottom - 1)
         ct.set_scale(self._cfg.user_scale)
-        out = boot.bootstrap(self._ctx, self._enc, ct, self._bk, self._cfg.user_scale)
-        if out.chain_index() != self._freshest:
-            raise RuntimeError("CKKSEngine::bootstrap_inplace: post-bootstrap chain_index != expected (freshest)")
+        out = boot.bootstrap(self._ctx, self._enc, ct, self._bk, self._cfg.user_scale, self._cfg.split_scale_down)
+        if out.chain_index() != self._freshest + (1 if self._cfg.split_scale_down else 0):
+            raise RuntimeError("CKKSEngine::bootstrap_inplace: post-bootstrap chain_index != expected (freshest"
+                               + ("+1)" if self._cfg.split_scale_down else ")"))
         out.set_scale(self._cfg.user_scale)
         self._assign(ct, out)
 

@@ -100,8 +100,10 @@ def test_stages_against_the_plain_computation():
 
 def test_errors():
     ctx, sk, enc, bk = _setup(12, 2, 6, 29, True)
-    with pytest.raises(ValueError):
-        ph.create_bootstrap_key(ctx, enc, sk, split_scale_down=True)
+    ct = sk.encrypt_symmetric(ctx, enc.encode_double_vector(ctx, np.full(8, 0.25), 2.0 ** 40, chain_index=ctx.size_Q - 1))
+    split = ph.bootstrap(ctx, enc, ct, bk, 2.0 ** 40, True)      # the reference's split mode hands back one level lower
+    assert split.coeff_modulus_size() == bk.user_limbs - 1 and split.chain_index() == ctx.size_Q - bk.user_limbs + 2
+    assert np.max(np.abs(enc.decode_double_vector(ctx, sk.decrypt(ctx, split))[:8] - 0.25)) < 1e-5
     with pytest.raises(ValueError):
         ph.create_bootstrap_key(ctx, enc, sk, eval_mod_levels=5)
     assert len(ph.bootstrap_required_galois_elts(12, [4, 4, 3])) == len(set(ph.bootstrap_required_galois_elts(12, [4, 4, 3])))
