@@ -315,6 +315,60 @@ def compositions_section(ph, ctx, torch, np, synth, primes, keys, N, level, reps
     return out
 
 
+def bsgs_section(ph, torch, np, synth):
+    """plaintext 4096 x 4096 matrix times ciphertext by the diagonal method: N = 2^16, 16 limbs at input, baby step 64,
+    giant step 64, synthetic diagonals and keys (8 distinct keys cycled over the 126 rotation steps).
+    reference_driver: pyPhantom.bsgs_matmul_preencoded, the reference's algorithm (host-resident int64 diagonals expanded
+    per giant, chained babies, Horner giants; limb-identical to the reference, tests/golden/full).
+    resident: pyPhantom.linalg.resident_bsgs (expanded diagonals resident in HBM, hoisted babies, giants sharing a ModDown)."""
+    from pyPhantom.linalg import resident_bsgs
+    n_ring, level, M, G = 1 << 16, 16, 64, 64
+    steps = list(range(1, M)) + [g * M for g in range(1, G)]
+    mods = ph.create_coeff_modulus(n_ring, [60] + [40] * 23 + [60] * 8)
+    primes = [m.value() for m in mods]
+    parms = ph.params(ph.scheme_type.ckks)
+    parms.set_poly_modulus_degree(n_ring)
+    parms.set_coeff_modulus(mods)
+    parms.set_special_modulus_size(8)
+    parms.set_galois_elts(ph.get_elts_from_steps(steps, n_ring))
+    ctx = ph.context(parms)
+    chain = ctx.size_Q - level + 1
+    beta = ctx.beta(level)
+    keys = [ph.relin_key.from_numpy(ctx, [synth.poly(n_ring, primes, 2, 91, 10 + 8 * k + d) for d in range(beta)]) for k in range(8)]
+    glk = ph.galois_key.from_keys([keys[i % 8] for i in range(len(ctx.galois_elts))])
+    x = ph.ciphertext()
+    x._chain_index, x._size, x._N, x._limbs, x._scale = chain, 2, n_ring, level, 2.0 ** 40
+    x.data = torch.from_numpy(synth.poly(n_ring, primes[:level], 2, 91, 1).view(np.int64)).cuda()
+    rng = np.random.default_rng(91)
+    base = [ph.single_chain_plaintext(rng.integers(-(1 << 39), 1 << 39, n_ring, dtype=np.int64), 2.0 ** 40) for _ in range(64)]
+    diags = ph.bsgs_diagonals([base[d % 64] for d in range(M * G)], M * G, M, G)
+
+    def timed(fn, reps):
+        fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / reps
+
+    ref_driver_ms = timed(lambda: ph.bsgs_matmul_preencoded(ctx, glk, x, diags), 2)
+    t0 = time.perf_counter()
+    op = resident_bsgs(ctx, glk, diags, chain)
+    setup_s = time.perf_counter() - t0
+    resident_ms = timed(lambda: op.apply(x), 5)
+    ref_ms = None
+    try:
+        ref_ms = json.load(open(os.path.join(ROOT, "tests", "golden", "full", "n16_l16_bsgs_m64g64.json")))["times_us"]["bsgs_us"] / 1e3
+    except (OSError, KeyError, ValueError):
+        pass
+    return {"workload": "4096x4096 plaintext matrix x ciphertext, N=65536, 16 limbs, M=G=64", "resident_ms": resident_ms,
+            "resident_setup_s": setup_s, "resident_hbm_gb": op.pts.numel() * 8 / 1e9, "reference_driver_ms": ref_driver_ms,
+            "reference_ms_same_gpu": ref_ms, "reference_source": "tests/golden/full/n16_l16_bsgs_m64g64.json times_us.bsgs_us"}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -523,11 +577,13 @@ def main():
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         cpu = cpu_baseline_sample()
 
-    ntt, bootstrap, compositions = None, None, None
+    ntt, bootstrap, compositions, bsgs = None, None, None, None
     if rank == 0 and world == 1 and not args.no_extras:
         ntt = ntt_section(ph, ctx, torch, LIB, check, N, len(primes))
         compositions = compositions_section(ph, ctx, torch, np, synth, primes, keys, N, LEVEL)
         del dev_ct3, keys, stage
+        torch.cuda.empty_cache()
+        bsgs = bsgs_section(ph, torch, np, synth)
         torch.cuda.empty_cache()
         bootstrap = bootstrap_section(ph, torch, np)
 
@@ -552,6 +608,7 @@ def main():
             "cpu_baseline": cpu,
             "ntt": ntt,
             "compositions": compositions,
+            "bsgs_matvec": bsgs,
             "bootstrap": bootstrap,
             "limb_sharded": limb_sharded,
         }

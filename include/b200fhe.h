@@ -181,6 +181,12 @@ int b2_hoist_rotations(b2_ctx *ctx, size_t size_Ql, const uint64_t *d_ct, const 
 int b2_bsgs_mac(b2_ctx *ctx, size_t size_Ql, size_t M, const uint64_t *const *pts,
                 const uint64_t *const *babies, uint64_t *d_out, void *stream);
 
+/* the same for 1 to 4 giants in one launch (no counterpart in the reference): d_outs[g] = sum_b pts[g * M + b] (.) babies[b],
+ * a null pts entry skips that term. The babies are read once per launch instead of once per giant.
+ * pts, babies, d_outs are DEVICE arrays of device pointers. */
+int b2_bsgs_mac_multi(b2_ctx *ctx, size_t size_Ql, size_t M, size_t n_giants, const uint64_t *const *pts,
+                      const uint64_t *const *babies, uint64_t *const *d_outs, void *stream);
+
 /* replaces expand_single_chain_to_full and the per-diagonal expansion inside the BSGS driver
  * (src/single_chain_plaintext.cu:93-192, src/bsgs.cu:282-315, src/bootstrap.cu:660-686):
  * d_signed int64[N] (signed, centred coefficients, device) -> d_out [size_Ql][N] in NTT form */

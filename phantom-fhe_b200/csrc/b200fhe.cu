@@ -1244,6 +1244,51 @@ __global__ void __launch_bounds__(256) bsgs_mac_kernel(const uint64_t *const *pt
     out[S + idx] = r1;
 }
 
+// Up to four giants at once: every baby value is loaded once and multiplied into each giant's own plaintext, so the
+// babies (two thirds of the bytes of the single-giant kernel) cross HBM once per group instead of once per giant.
+// pts[g * M + b] may be null: that giant has no diagonal for baby b.
+template <int G>
+__global__ void __launch_bounds__(256) bsgs_mac_multi_kernel(const uint64_t *const *pts, const uint64_t *const *babies, uint64_t *const *outs,
+                                                            const Mod *mod, uint32_t N, uint32_t l, uint32_t M, uint32_t n_g) {
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t S = (size_t)l * N;
+    if (idx >= S) return;
+    const Mod md = mod[idx / N];
+    u128 a[G][2];
+#pragma unroll
+    for (int g = 0; g < G; g++) a[g][0] = a[g][1] = u128{0, 0};
+    uint32_t pending = 0;
+    for (uint32_t b = 0; b < M; b++) {
+        const uint64_t *bb = babies[b];
+        const uint64_t y0 = bb[idx], y1 = bb[S + idx];
+#pragma unroll
+        for (int g = 0; g < G; g++) {
+            const uint64_t *pp = g < (int)n_g ? pts[(size_t)g * M + b] : nullptr;
+            if (pp) {
+                const uint64_t p = pp[idx];
+                mac128(a[g][0], p, y0);
+                mac128(a[g][1], p, y1);
+            }
+        }
+        if (++pending == 32) {  // 32 products of two 61-bit values stay below 2^128
+#pragma unroll
+            for (int g = 0; g < G; g++) {
+                a[g][0] = u128{barrett128(a[g][0], md.q, md.r0, md.r1), 0};
+                a[g][1] = u128{barrett128(a[g][1], md.q, md.r0, md.r1), 0};
+            }
+            pending = 1;
+        }
+    }
+#pragma unroll
+    for (int g = 0; g < G; g++) {
+        if (g < (int)n_g) {
+            uint64_t *o = outs[g];
+            o[idx] = barrett128(a[g][0], md.q, md.r0, md.r1);
+            o[S + idx] = barrett128(a[g][1], md.q, md.r0, md.r1);
+        }
+    }
+}
+
 static int run_bconv(const b2_ctx *c, bool copy, const uint64_t *in, uint64_t *out, const uint64_t *copy_src, const BconvGroup *groups,
                      uint32_t n_groups, const uint2 *outs, const uint64_t *mats, const double *matd, uint32_t max_ni, uint32_t max_out,
                      bool in3, cudaStream_t s) {
@@ -1770,6 +1815,19 @@ extern "C" int b2_bsgs_mac(b2_ctx *c, size_t l, size_t M, const uint64_t *const 
     LaunchScope ls(c, (cudaStream_t)stream, "bsgs_mac");
     bsgs_mac_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(pts, babies, d_out, c->d_mod, (uint32_t)c->N, (uint32_t)l, (uint32_t)M);
     LAUNCH_CHECK("bsgs_mac_kernel");
+    return B2_OK;
+}
+
+extern "C" int b2_bsgs_mac_multi(b2_ctx *c, size_t l, size_t M, size_t n_giants, const uint64_t *const *pts, const uint64_t *const *babies,
+                                 uint64_t *const *outs, void *stream) {
+    CHECK_CTX(c);
+    CHECK_LEVEL(c, l);
+    if (!pts || !babies || !outs || M == 0 || n_giants < 1 || n_giants > 4) return fail(B2_EINVAL, "bsgs_mac_multi: bad argument (1 to 4 giants)");
+    const size_t n = l * c->N;
+    LaunchScope ls(c, (cudaStream_t)stream, "bsgs_mac");
+    bsgs_mac_multi_kernel<4><<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(pts, babies, outs, c->d_mod, (uint32_t)c->N, (uint32_t)l,
+                                                                                            (uint32_t)M, (uint32_t)n_giants);
+    LAUNCH_CHECK("bsgs_mac_multi_kernel");
     return B2_OK;
 }
 

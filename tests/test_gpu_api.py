@@ -199,6 +199,24 @@ def test_bsgs_driver_matches_the_reference():
             ph.bsgs_apply_giants_with_babies(ctx, glk, [x] * M, ph.bsgs_diagonals(diags.diagonals, M * G + 1, M, G))
 
 
+def test_bsgs_driver_matches_the_reference_at_full_size():
+    """the 4096 x 4096 product (N = 2^16, 16 limbs, M = G = 64): same limbs as the reference's bsgs_matmul_preencoded"""
+    import glob, json, os
+    from gpu_helpers import load_case, hashes
+    paths = sorted(glob.glob(os.path.join(os.path.dirname(__file__), "golden", "full", "*bsgs*.json")))
+    assert paths, "no full-size BSGS record"
+    case, ctx, o = load_case(paths[0])
+    N, l, seed = o.N, case["level"], case["seed"]
+    M, G = case["bsgs"]
+    chain = o.size_Q - l + 1
+    keys = [ph.relin_key.from_numpy(ctx, o.synth_key(o.beta(l), seed, 100 + 8 * e)) for e in range(len(case["elts"]))]
+    glk = ph.galois_key.from_keys(keys)
+    x = ph.ciphertext.from_numpy(ctx, o.synth_ct(l, seed, 1), chain, SCALE)
+    diags = ph.bsgs_diagonals([ph.single_chain_plaintext(o.synth_signed(seed, 3000 + d), SCALE) for d in range(M * G)], M * G, M, G)
+    y = ph.bsgs_matmul_preencoded(ctx, glk, x, diags)
+    assert hashes(y.data, N) == case["hashes"]["bsgs"]
+
+
 def test_galois_key_fallback(env):
     ctx, a = env["ctx"], env["a"]
     g = ph.galois_key.from_keys([ph.relin_key() for _ in env["elts"]])  # every owned slot empty

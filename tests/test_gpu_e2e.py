@@ -228,3 +228,34 @@ def test_remaining_surface_names(kit):
     scp = ph.encode_single_chain_plaintext(ctx, enc, x, SCALE)
     full = ph.expand_single_chain_to_full(ctx, scp, 2)
     assert torch.equal(full.data, enc.encode_complex_vector(ctx, x, SCALE, 2).data)
+
+
+def test_resident_bsgs_product():
+    """diagonals resident in HBM, hoisted babies, giants with one ModDown per stream: same product as numpy"""
+    from pyPhantom.linalg import resident_bsgs
+    n_ring, d_pad, M = 1 << 12, 16, 4
+    steps = [1, 2, 3, 4, 8, 12]
+    parms = ph.params(ph.scheme_type.ckks)
+    parms.set_poly_modulus_degree(n_ring)
+    parms.set_coeff_modulus(ph.create_coeff_modulus(n_ring, [60, 40, 40, 40, 60, 60]))
+    parms.set_special_modulus_size(2)
+    parms.set_galois_elts(ph.get_elts_from_steps(steps, n_ring))
+    ctx = ph.context(parms)
+    sk = ph.secret_key(ctx, seed=5)
+    enc = ph.ckks_encoder(ctx)
+    glk = sk.create_galois_keys(ctx)
+    rng = np.random.default_rng(6)
+    W = rng.normal(0, 0.5, (d_pad, d_pad))
+    v = rng.normal(size=d_pad)
+    diags = ph.pre_encode_bsgs_diagonals(ctx, enc, W.ravel(), d_pad, d_pad, d_pad, M, SCALE)
+    x = sk.encrypt_symmetric(ctx, enc.encode_double_vector(ctx, np.tile(v, enc.slot_count() // d_pad), SCALE, 1))
+    op = resident_bsgs(ctx, glk, diags, 1)
+    for _ in range(2):   # the buffers of the operator are reused from call to call
+        y = op.apply(x)
+        assert y.chain_index() == 2 and y.scale() == SCALE
+        got = enc.decode_double_vector(ctx, sk.decrypt(ctx, y))[:d_pad]
+        assert np.max(np.abs(got - W @ v)) < 2e-5
+    ref = enc.decode_double_vector(ctx, sk.decrypt(ctx, ph.bsgs_matmul_preencoded(ctx, sk.create_galois_keys(ctx), x, diags)))[:d_pad]
+    assert np.max(np.abs(got - ref)) < 1e-5
+    with pytest.raises(ValueError):
+        op.apply(ph.mod_switch_to_next(ctx, x))

@@ -249,6 +249,32 @@ def test_ciphertext_wide_ops_and_weighted_sum():
         check(LIB.b2_ct_lincomb(ctx._h, l, 2, 3, ptrs.ctypes.data, low.ctypes.data, w.ctypes.data, c0.ctypes.data, out.data_ptr(), stream()))
 
 
+def test_multi_giant_mac_equals_single_giant_calls():
+    N, l, M = 4096, 3, 5
+    ctx, o = make_ctx(N, [60, 58, 40, 50, 60], 1)
+    babies = [dev(o.synth_ct(l, 71, 10 + b)) for b in range(M)]
+    pts = [[dev(o.fill(1, o.primes[:l], 71, 100 + 10 * g + b)[0]) for b in range(M)] for g in range(3)]
+    tab = np.zeros((3, M), dtype=np.int64)
+    for g in range(3):
+        for b in range(M):
+            if (g, b) not in ((1, 0), (2, 4)):      # ragged: two giants lack one diagonal each
+                tab[g, b] = pts[g][b].data_ptr()
+    outs = [ctx.empty(2, l) for _ in range(3)]
+    d_tab = torch.from_numpy(tab.ravel().copy()).cuda()
+    d_bab = torch.tensor([t.data_ptr() for t in babies], dtype=torch.int64, device="cuda")
+    d_out = torch.tensor([t.data_ptr() for t in outs], dtype=torch.int64, device="cuda")
+    check(LIB.b2_bsgs_mac_multi(ctx._h, l, M, 3, d_tab.data_ptr(), d_bab.data_ptr(), d_out.data_ptr(), stream()))
+    for g in range(3):
+        keep = [b for b in range(M) if tab[g, b]]
+        p1 = torch.tensor([pts[g][b].data_ptr() for b in keep], dtype=torch.int64, device="cuda")
+        b1 = torch.tensor([babies[b].data_ptr() for b in keep], dtype=torch.int64, device="cuda")
+        ref = ctx.empty(2, l)
+        check(LIB.b2_bsgs_mac(ctx._h, l, len(keep), p1.data_ptr(), b1.data_ptr(), ref.data_ptr(), stream()))
+        assert torch.equal(outs[g], ref)
+    with pytest.raises(ValueError):
+        check(LIB.b2_bsgs_mac_multi(ctx._h, l, M, 5, d_tab.data_ptr(), d_bab.data_ptr(), d_out.data_ptr(), stream()))
+
+
 def test_rotations_sharing_one_moddown():
     # two rotations accumulated and converted once == the oracle's ModDown of the summed inner products;
     # a single accumulate + finish == b2_apply_galois
