@@ -259,3 +259,28 @@ def test_resident_bsgs_product():
     assert np.max(np.abs(got - ref)) < 1e-5
     with pytest.raises(ValueError):
         op.apply(ph.mod_switch_to_next(ctx, x))
+
+
+def test_flow_of_the_ckks_example():
+    """the calls of python/examples/ckks.py in its order: asymmetric encryption, square, rescale, summed hoisted
+    rotations, add; checked against the same computation on the plain vector"""
+    n_ring = 1 << 14
+    parms = ph.params(ph.scheme_type.ckks)
+    parms.set_poly_modulus_degree(n_ring)
+    parms.set_coeff_modulus(ph.create_coeff_modulus(n_ring, [60, 40, 40, 60]))
+    parms.set_special_modulus_size(1)
+    steps = [1, 2, 3, 4, 5, 6, 7]
+    parms.set_galois_elts(ph.get_elts_from_steps(steps, n_ring))
+    ctx = ph.context(parms)
+    sk = ph.secret_key(ctx)
+    pk, rlk, glk = sk.gen_publickey(ctx), sk.gen_relinkey(ctx), sk.create_galois_keys(ctx)
+    enc = ph.ckks_encoder(ctx)
+    msg = np.zeros(enc.slot_count())
+    msg[:8] = np.arange(1.0, 9.0)
+    ct = pk.encrypt_asymmetric(ctx, enc.encode_double_vector(ctx, list(msg), 2.0 ** 40, chain_index=1))
+    ct = ph.rescale_to_next(ctx, ph.multiply_and_relin(ctx, ct, ct, rlk))
+    ct = ph.add(ctx, ct, ph.hoisting(ctx, ct, glk, steps))
+    got = enc.decode_double_vector(ctx, sk.decrypt(ctx, ct))
+    sq = msg * msg
+    want = sq + sum(np.roll(sq, -k) for k in steps)
+    assert np.max(np.abs(got - want)) < 1e-3
