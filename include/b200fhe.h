@@ -193,6 +193,11 @@ int b2_bsgs_mac_multi(b2_ctx *ctx, size_t size_Ql, size_t M, size_t n_giants, co
 int b2_expand_single_chain(b2_ctx *ctx, size_t size_Ql, const int64_t *d_signed, uint64_t *d_out,
                            void *stream);
 
+/* M of them in one go (what the BSGS driver does per giant step, src/bsgs.cu:282-315):
+ * d_signed int64[M][N] -> d_out [M][size_Ql][N] in NTT form, two launches for the expansion and two for all transforms */
+int b2_expand_single_chain_batch(b2_ctx *ctx, size_t size_Ql, size_t M, const int64_t *d_signed, uint64_t *d_out,
+                                 void *stream);
+
 /* the same over any limb range [first_prime, first_prime + n_limbs), optionally left in coefficient
  * form: what the samplers and the encoder of the reference do per limb when they reduce a small
  * signed value into every prime (src/rns_base.cu:49-73, src/prng.cu:142-240) */

@@ -712,10 +712,10 @@ static void launch_inv(const b2_ctx *c, const NttArgs &a, uint32_t njobs, cudaSt
 
 template <class Epi>
 static int run_fwd(const b2_ctx *c, const uint64_t *src, uint64_t *dst, const Job *jobs, uint32_t njobs, uint32_t first_prime,
-                   const Epi &epi, cudaStream_t s) {
+                   const Epi &epi, cudaStream_t s, uint32_t period = 0) {
     if (njobs == 0) return B2_OK;
     if (!aligned32(src) || !aligned32(dst) || !epi.aligned()) return fail(B2_EINVAL, "device buffers must be 32-byte aligned (256-bit accesses)");
-    NttArgs a{src, dst, jobs, first_prime, (uint32_t)c->logN, c->d_tw, c->d_mod, nullptr};
+    NttArgs a{src, dst, jobs, first_prime, (uint32_t)c->logN, c->d_tw, c->d_mod, nullptr, period};
     if (c->use_cluster) {
         static thread_local bool attr_set = false;  // per instantiation (one per epilogue type) and thread
         if (!attr_set) {
@@ -743,7 +743,7 @@ static int run_inv(const b2_ctx *c, const uint64_t *src, uint64_t *dst, const Jo
                    const W2 *fin, cudaStream_t s) {
     if (njobs == 0) return B2_OK;
     if (!aligned32(src) || !aligned32(dst)) return fail(B2_EINVAL, "device buffers must be 32-byte aligned (256-bit accesses)");
-    NttArgs a{src, dst, jobs, first_prime, (uint32_t)c->logN, c->d_itw, c->d_mod, fin};
+    NttArgs a{src, dst, jobs, first_prime, (uint32_t)c->logN, c->d_itw, c->d_mod, fin, 0};
     if (c->use_cluster) {
         static thread_local bool attr_set = false;
         if (!attr_set) {
@@ -1210,6 +1210,20 @@ __global__ void __launch_bounds__(256) lincomb_kernel(const __grid_constant__ Li
     u128 acc{p == 0 ? a.c[limb] : 0, 0};
     for (uint32_t t = 0; t < n_terms; t++) mac128(acc, a.x[t][((size_t)p * a.lt[t] + limb) * N + i], a.s[t][limb]);
     out[idx] = barrett128(acc, md.q, md.r0, md.r1);
+}
+
+// M signed coefficient vectors at once: src [M][N] -> dst [M][l][N] (limb j of every polynomial on prime j)
+__global__ void __launch_bounds__(256) expand_signed_batch_kernel(const int64_t *__restrict__ src, uint64_t *__restrict__ dst, const Mod *mod, uint32_t N,
+                                                                 uint32_t l, uint32_t M) {
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (size_t)M * l * N) return;
+    const uint32_t i = (uint32_t)(idx % N), limb = (uint32_t)((idx / N) % l), m = (uint32_t)(idx / ((size_t)N * l));
+    const Mod md = mod[limb];
+    const int64_t c = src[(size_t)m * N + i];
+    const uint64_t mag = c >= 0 ? (uint64_t)c : (uint64_t)0 - (uint64_t)c;
+    u128 v{mag, 0};
+    const uint64_t r = barrett128(v, md.q, md.r0, md.r1);
+    dst[idx] = (c >= 0 || r == 0) ? r : md.q - r;
 }
 
 struct MacPtrs {
@@ -1852,6 +1866,20 @@ extern "C" int b2_expand_single_chain(b2_ctx *c, size_t l, const int64_t *d_sign
     CHECK_CTX(c);
     CHECK_LEVEL(c, l);
     return b2_expand_signed(c, 0, l, d_signed, d_out, 1, stream);
+}
+
+extern "C" int b2_expand_single_chain_batch(b2_ctx *c, size_t l, size_t M, const int64_t *d_signed, uint64_t *d_out, void *stream) {
+    CHECK_CTX(c);
+    CHECK_LEVEL(c, l);
+    if (!d_signed || !d_out || M == 0) return fail(B2_EINVAL, "expand_single_chain_batch: bad argument");
+    cudaStream_t s = (cudaStream_t)stream;
+    const size_t n = M * l * c->N;
+    {
+        LaunchScope ls(c, s, "expand_signed");
+        expand_signed_batch_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(d_signed, d_out, c->d_mod, (uint32_t)c->N, (uint32_t)l, (uint32_t)M);
+        LAUNCH_CHECK("expand_signed_batch_kernel");
+    }
+    return run_fwd(c, d_out, d_out, nullptr, (uint32_t)(M * l), 0, EpiStore{}, s, (uint32_t)l);
 }
 
 extern "C" int b2_poly_op(b2_ctx *c, int op, size_t n_limbs, const uint64_t *d_a, const uint64_t *d_b, uint64_t *d_out, void *stream) {

@@ -46,11 +46,13 @@ struct NttArgs {
     const W2 *tw;          // [size_QP][N] {w, shoup(w)}
     const Mod *mod;        // [size_QP]
     const W2 *fin;         // inverse only: [idx][2] = {scale of the x outputs, last-stage twiddle}
+    uint32_t period;       // without a job list: limb j uses prime first_prime + j % period (0: + j), a batch of polynomials
 };
 
 __device__ __forceinline__ Job get_job(const NttArgs &a, uint32_t j) {
     if (a.jobs) return a.jobs[j];
-    return make_uint4(j, a.first_prime + j, a.first_prime + j, j);
+    const uint32_t p = a.first_prime + (a.period ? j % a.period : j);
+    return make_uint4(j, p, p, j);
 }
 
 // 256-bit global accesses (sm_100): one lane moves a whole 32-byte sector, so a thread that owns a run of

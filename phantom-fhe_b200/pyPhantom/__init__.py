@@ -847,15 +847,16 @@ def bsgs_apply_giants_with_babies(ctx, galois_key_, babies, diags):
     pool = ctx.empty(M, l)  # M expanded plaintexts, reused by every giant
     pt_ptrs = torch.tensor([pool[b].data_ptr() for b in range(M)], dtype=torch.int64, device=ctx.device)
     baby_ptrs = torch.tensor([c.data.data_ptr() for c in babies], dtype=torch.int64, device=ctx.device)
-    staged = [None] * M
+    staged = torch.empty(M, N, dtype=torch.int64, device=ctx.device)
 
     def partial(g):
         for b in range(M):
             scp = diags.diagonals[g * M + b]
             if scp.coeffs.numel() != N:
                 raise ValueError("bsgs_apply_giants_with_babies: scp coeff length != N")
-            staged[b] = scp.coeffs.to(ctx.device, non_blocking=True)
-            check(LIB.b2_expand_single_chain(ctx._h, l, staged[b].data_ptr(), pool[b].data_ptr(), _stream()))
+            staged[b].copy_(scp.coeffs, non_blocking=True)
+        # all M plaintexts of the giant expanded and transformed by one call
+        check(LIB.b2_expand_single_chain_batch(ctx._h, l, M, staged.data_ptr(), pool.data_ptr(), _stream()))
         out = ctx.empty(2, l)
         check(LIB.b2_bsgs_mac(ctx._h, l, M, pt_ptrs.data_ptr(), baby_ptrs.data_ptr(), out.data_ptr(), _stream()))
         return x._like(out, scale=x._scale * diags.diagonals[g * M].scale)

@@ -46,6 +46,7 @@ SIGNATURES = {
     "b2_bsgs_mac": (_int, [_vp, _sz, _sz, _vp, _vp, _vp, _vp]),
     "b2_bsgs_mac_multi": (_int, [_vp, _sz, _sz, _sz, _vp, _vp, _vp, _vp]),
     "b2_expand_single_chain": (_int, [_vp, _sz, _vp, _vp, _vp]),
+    "b2_expand_single_chain_batch": (_int, [_vp, _sz, _sz, _vp, _vp, _vp]),
     "b2_expand_signed": (_int, [_vp, _sz, _sz, _vp, _vp, _int, _vp]),
     "b2_poly_op": (_int, [_vp, _int, _sz, _vp, _vp, _vp, _vp]),
     "b2_ct_op": (_int, [_vp, _int, _sz, _sz, _vp, _vp, _vp, _vp]),

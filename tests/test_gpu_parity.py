@@ -275,6 +275,20 @@ def test_multi_giant_mac_equals_single_giant_calls():
         check(LIB.b2_bsgs_mac_multi(ctx._h, l, M, 5, d_tab.data_ptr(), d_bab.data_ptr(), d_out.data_ptr(), stream()))
 
 
+def test_batched_expansion_equals_single_calls():
+    N, l, M = 4096, 4, 5
+    ctx, o = make_ctx(N, [60, 29, 40, 58, 50, 60], 1)
+    src_h = np.stack([o.synth_signed(81, 10 + m) for m in range(M)])
+    src = torch.from_numpy(src_h).cuda()
+    out = ctx.empty(M, l)
+    check(LIB.b2_expand_single_chain_batch(ctx._h, l, M, src.data_ptr(), out.data_ptr(), stream()))
+    one = ctx.empty(l)
+    for m in range(M):
+        check(LIB.b2_expand_single_chain(ctx._h, l, src[m].data_ptr(), one.data_ptr(), stream()))
+        assert torch.equal(out[m], one)
+        assert np.array_equal(host(one), o.expand_single_chain(l, src_h[m]))
+
+
 def test_rotations_sharing_one_moddown():
     # two rotations accumulated and converted once == the oracle's ModDown of the summed inner products;
     # a single accumulate + finish == b2_apply_galois
