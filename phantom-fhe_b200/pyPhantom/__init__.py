@@ -844,27 +844,46 @@ def bsgs_apply_giants_with_babies(ctx, galois_key_, babies, diags):
         raise ValueError("bsgs_apply_giants_with_babies: diagonals size mismatch")
     x = babies[0]
     l, N = x._limbs, ctx.N
-    pool = ctx.empty(M, l)  # M expanded plaintexts, reused by every giant
-    pt_ptrs = torch.tensor([pool[b].data_ptr() for b in range(M)], dtype=torch.int64, device=ctx.device)
+    # Two pools of M expanded plaintexts: while the multiply-accumulate and the rotation of one giant run on the
+    # caller's stream, the next giant's diagonals are copied in and expanded on a second stream.
+    main = torch.cuda.current_stream()
+    side = torch.cuda.Stream()
+    pools = [ctx.empty(M, l) for _ in range(2)]
+    stages = [torch.empty(M, N, dtype=torch.int64, device=ctx.device) for _ in range(2)]
+    pt_ptrs = [torch.tensor([p[b].data_ptr() for b in range(M)], dtype=torch.int64, device=ctx.device) for p in pools]
     baby_ptrs = torch.tensor([c.data.data_ptr() for c in babies], dtype=torch.int64, device=ctx.device)
-    staged = torch.empty(M, N, dtype=torch.int64, device=ctx.device)
+    ready = [torch.cuda.Event() for _ in range(2)]
+    free = [torch.cuda.Event() for _ in range(2)]
+    side.wait_stream(main)
 
-    def partial(g):
-        for b in range(M):
-            scp = diags.diagonals[g * M + b]
-            if scp.coeffs.numel() != N:
-                raise ValueError("bsgs_apply_giants_with_babies: scp coeff length != N")
-            staged[b].copy_(scp.coeffs, non_blocking=True)
-        # all M plaintexts of the giant expanded and transformed by one call
-        check(LIB.b2_expand_single_chain_batch(ctx._h, l, M, staged.data_ptr(), pool.data_ptr(), _stream()))
+    def prepare(g, slot, wait_free):
+        with torch.cuda.stream(side):
+            if wait_free:
+                side.wait_event(free[slot])
+            for b in range(M):
+                scp = diags.diagonals[g * M + b]
+                if scp.coeffs.numel() != N:
+                    raise ValueError("bsgs_apply_giants_with_babies: scp coeff length != N")
+                stages[slot][b].copy_(scp.coeffs, non_blocking=True)
+            check(LIB.b2_expand_single_chain_batch(ctx._h, l, M, stages[slot].data_ptr(), pools[slot].data_ptr(), side.cuda_stream))
+            ready[slot].record(side)
+
+    def partial(g, slot):
+        main.wait_event(ready[slot])
         out = ctx.empty(2, l)
-        check(LIB.b2_bsgs_mac(ctx._h, l, M, pt_ptrs.data_ptr(), baby_ptrs.data_ptr(), out.data_ptr(), _stream()))
+        check(LIB.b2_bsgs_mac(ctx._h, l, M, pt_ptrs[slot].data_ptr(), baby_ptrs.data_ptr(), out.data_ptr(), _stream()))
+        free[slot].record(main)
         return x._like(out, scale=x._scale * diags.diagonals[g * M].scale)
 
-    acc = partial(G - 1)
-    for g in range(G - 2, -1, -1):
-        acc = rotate(ctx, acc, M, galois_key_)
-        acc = add(ctx, acc, partial(g))
+    order = list(range(G - 1, -1, -1))
+    prepare(order[0], 0, False)
+    acc = None
+    for i, g in enumerate(order):
+        if i + 1 < len(order):
+            prepare(order[i + 1], (i + 1) & 1, i >= 1)
+        part = partial(g, i & 1)
+        acc = part if acc is None else add(ctx, rotate(ctx, acc, M, galois_key_), part)
+    main.wait_stream(side)
     acc = rescale_to_next(ctx, acc)
     acc.set_scale(x._scale)
     return acc
