@@ -809,6 +809,59 @@ def pre_encode_bsgs_diagonals(context, encoder, matrix, num_rows, num_cols, d_pa
     return bsgs_diagonals(out, d_pad, baby_steps, d_pad // baby_steps)
 
 
+class complex_fold_mode(enum.IntEnum):
+    """include/bsgs.h:81-96"""
+    Rows = 0      # rows i and i + ceil(rows/2) become the real and imaginary part of one row
+    ColsConj = 1  # columns j and j + ceil(cols/2) become one complex column, imaginary part negated
+
+
+class complex_bsgs_diagonals:
+    """include/bsgs.h:77-79: the same container, its plaintexts carry complex slots"""
+
+    def __init__(self, inner):
+        self.inner = inner
+
+
+def pre_encode_bsgs_diagonals_complex(ctx, encoder, matrix, num_rows, num_cols, d_pad, baby_steps, scale, fold_mode):
+    """python/src/binding.cu:574-587; src/bsgs.cu:373-515: fold the real matrix into a complex one of half the rows (or
+    half the columns), then the diagonals as in pre_encode_bsgs_diagonals with complex slot values"""
+    m = np.asarray(matrix, dtype=np.float64).ravel()
+    if num_rows == 0 or num_cols == 0:
+        raise ValueError("pre_encode_bsgs_diagonals_complex: dimensions must be non-zero")
+    if m.size != num_rows * num_cols:
+        raise ValueError("pre_encode_bsgs_diagonals_complex: matrix size mismatch")
+    if d_pad & (d_pad - 1) or d_pad == 0:
+        raise ValueError("pre_encode_bsgs_diagonals_complex: d_pad must be a power of 2")
+    if baby_steps == 0 or d_pad % baby_steps:
+        raise ValueError("pre_encode_bsgs_diagonals_complex: baby_steps must divide d_pad")
+    m = m.reshape(num_rows, num_cols)
+    if complex_fold_mode(fold_mode) == complex_fold_mode.Rows:
+        half = (num_rows + 1) // 2
+        w = np.zeros((half, num_cols), dtype=np.complex128)
+        w.real = m[:half]
+        w.imag[: num_rows - half] = m[half:]
+    else:
+        half = (num_cols + 1) // 2
+        w = np.zeros((num_rows, half), dtype=np.complex128)
+        w.real = m[:, :half]
+        w.imag[:, : num_cols - half] = -m[:, half:]
+    if d_pad < w.shape[0] or d_pad < w.shape[1]:
+        raise ValueError("pre_encode_bsgs_diagonals_complex: d_pad must be >= max(folded_rows, folded_cols)")
+    slots = encoder.slot_count()
+    if slots % d_pad:
+        raise ValueError("pre_encode_bsgs_diagonals_complex: num_slots must be multiple of d_pad")
+    padded = np.zeros((d_pad, d_pad), dtype=np.complex128)
+    padded[: w.shape[0], : w.shape[1]] = w
+    t = np.arange(d_pad)
+    out = []
+    for g in range(d_pad // baby_steps):
+        for b in range(baby_steps):
+            diag = padded[t, (t + g * baby_steps + b) % d_pad]
+            row = np.tile(np.roll(diag, g * baby_steps), slots // d_pad)
+            out.append(single_chain_plaintext(encoder.signed_coefficients(ctx, row, scale, 1), scale))
+    return complex_bsgs_diagonals(bsgs_diagonals(out, d_pad, baby_steps, d_pad // baby_steps))
+
+
 def bsgs_required_steps(baby_steps):
     """src/bsgs.cu:180-191"""
     if baby_steps <= 1:
@@ -894,4 +947,14 @@ def bsgs_matmul_preencoded(ctx, galois_key_, x, diags):
     return bsgs_apply_giants_with_babies(ctx, galois_key_, compute_bsgs_babies(ctx, galois_key_, x, diags.baby_steps), diags)
 
 
+def bsgs_matmul_preencoded_complex(ctx, galois_key_, x, diags):
+    """src/bsgs.cu:517-524: the BSGS structure does not change for complex diagonals"""
+    return bsgs_matmul_preencoded(ctx, galois_key_, x, diags.inner)
+
+
+def bsgs_apply_giants_with_babies_complex(ctx, galois_key_, babies, diags):
+    return bsgs_apply_giants_with_babies(ctx, galois_key_, babies, diags.inner)
+
+
 from .engine import ckks_engine, ckks_engine_config  # noqa: E402,F401
+from .blocks import eval_polynomial, inner_sum, replicate  # noqa: E402,F401

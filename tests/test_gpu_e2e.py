@@ -284,3 +284,42 @@ def test_flow_of_the_ckks_example():
     sq = msg * msg
     want = sq + sum(np.roll(sq, -k) for k in steps)
     assert np.max(np.abs(got - want)) < 1e-3
+
+
+def test_complex_folded_bsgs(kit):
+    """row fold: one product gives rows 0..h-1 in the real part and rows h..2h-1 in the imaginary part"""
+    ctx, enc, sk = kit["ctx"], kit["enc"], kit["sk"]
+    d_pad, M = 16, 4
+    rng = np.random.default_rng(12)
+    W = rng.normal(0, 0.5, (20, 12))
+    v = np.zeros(d_pad)
+    v[:12] = rng.normal(size=12)
+    diags = ph.pre_encode_bsgs_diagonals_complex(ctx, enc, W.ravel(), 20, 12, d_pad, M, SCALE, ph.complex_fold_mode.Rows)
+    ct = sk.encrypt_symmetric(ctx, enc.encode_double_vector(ctx, np.tile(v, enc.slot_count() // d_pad), SCALE, 1))
+    got = enc.decode_complex_vector(ctx, sk.decrypt(ctx, ph.bsgs_matmul_preencoded_complex(ctx, kit["glk"], ct, diags)))[:10]
+    want = W @ v[:12]
+    assert np.max(np.abs(got.real - want[:10])) < 2e-5 and np.max(np.abs(got.imag - want[10:])) < 2e-5
+    cols = ph.pre_encode_bsgs_diagonals_complex(ctx, enc, W.ravel(), 20, 12, 32, M, SCALE, ph.complex_fold_mode.ColsConj)
+    assert len(cols.inner.diagonals) == 32
+    with pytest.raises(ValueError):
+        ph.pre_encode_bsgs_diagonals_complex(ctx, enc, W.ravel(), 20, 12, 8, M, SCALE, ph.complex_fold_mode.Rows)
+
+
+def test_inner_sum_replicate_and_polynomial(kit):
+    ctx, enc, sk = kit["ctx"], kit["enc"], kit["sk"]
+    n = enc.slot_count()
+    x = kit["x"].real
+    cx = sk.encrypt_symmetric(ctx, enc.encode_double_vector(ctx, x, SCALE, 1))
+    got = enc.decode_double_vector(ctx, sk.decrypt(ctx, ph.inner_sum(ctx, kit["glk"], cx, 8)))
+    want = sum(np.roll(x, -k) for k in range(8))
+    assert np.max(np.abs(got - want)) < 1e-5
+    with pytest.raises(ValueError):
+        ph.inner_sum(ctx, kit["glk"], cx, 6)
+    # degree 7 and degree 3 on [-1, 1]; the result sits where the reference's schedule ends
+    for coeffs in ([0.5, -1.0, 0.25, 2.0, -0.75, 0.1, 0.3, -0.2], [1.0, 0.0, -0.5, 0.125]):
+        y = ph.eval_polynomial(ctx, enc, kit["rlk"], cx, coeffs)
+        d = len(coeffs) - 1
+        m = int(np.ceil(np.sqrt(d + 1)))
+        assert y.chain_index() == 1 + m + (d + m) // m - 2 and y.scale() == SCALE
+        got = enc.decode_double_vector(ctx, sk.decrypt(ctx, y))
+        assert np.max(np.abs(got - np.polynomial.polynomial.polyval(x, coeffs))) < 1e-4
