@@ -107,7 +107,7 @@ class ClockSampler:
                 "samples": len(sm), "window": "timed region" if inside else "whole run (timed region shorter than the sampling period)"}
 
 
-def run_reference_arm(args, rank):
+def run_reference_arm(args, rank, out_stream):
     """the reference's algorithm on the host cores (CPU restatement, all threads); rank 0 only"""
     if rank != 0:
         return
@@ -134,7 +134,7 @@ def run_reference_arm(args, rank):
                              "sample": f"{args.steps} key switches, one per step"},
             "e2e": {"value": v, "unit": "KeySwitch/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "note": "the reference has no CPU implementation of this path; this is the CPU restatement in oracle/"}
-    print(json.dumps(line), flush=True)
+    print(json.dumps(line), file=out_stream, flush=True)
 
 
 def cpu_baseline_sample(budget_s=12.0):
@@ -369,7 +369,17 @@ def bsgs_section(ph, torch, np, synth):
             "reference_ms_same_gpu": ref_ms, "reference_source": "tests/golden/full/n16_l16_bsgs_m64g64.json times_us.bsgs_us"}
 
 
+def _claim_stdout():
+    """stdout carries the one JSON line and nothing else: libraries that write to file descriptor 1 on their own (NCCL's
+    version banner does) are pointed at stderr, and the line goes out through a private copy of the original descriptor"""
+    sys.stdout.flush()
+    keep = os.dup(1)
+    os.dup2(2, 1)
+    return os.fdopen(keep, "w")
+
+
 def main():
+    out_stream = _claim_stdout()
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=100)
@@ -390,7 +400,7 @@ def main():
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
 
     if args.impl == "reference":
-        run_reference_arm(args, rank)
+        run_reference_arm(args, rank, out_stream)
         return
 
     import numpy as np
@@ -404,8 +414,6 @@ def main():
         raise SystemExit("bench.py needs a CUDA device: the product has no CPU path")
     torch.cuda.set_device(local_rank)
     if world > 1:
-        # stdout carries the one JSON line and nothing else: NCCL's own banner (printed when NCCL_DEBUG is set) goes to stderr
-        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
 
     # ---- context, keys and ciphertexts ---------------------------------------------------------
@@ -612,7 +620,7 @@ def main():
             "bootstrap": bootstrap,
             "limb_sharded": limb_sharded,
         }
-        print(json.dumps(line), flush=True)
+        print(json.dumps(line), file=out_stream, flush=True)
     if world > 1:
         dist.destroy_process_group()
 
