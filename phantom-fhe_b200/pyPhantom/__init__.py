@@ -958,3 +958,6 @@ def bsgs_apply_giants_with_babies_complex(ctx, galois_key_, babies, diags):
 
 from .engine import ckks_engine, ckks_engine_config  # noqa: E402,F401
 from .blocks import eval_polynomial, inner_sum, replicate  # noqa: E402,F401
+from .model_blocks import (compute_qkt, finalize_softmax, mlp_forward, mlp_forward_complex, mlp_weights,  # noqa: E402,F401
+                           mlp_weights_complex, ps_exp_init, rmsnorm_forward, rmsnorm_params, rmsnorm_weights,
+                           score_times_v, softmax_correct, square_iterations_damped_inplace, square_iterations_inplace)

@@ -35,26 +35,38 @@ def replicate(context, galois_key_, ct, period, num_slots):
     return acc
 
 
+def schedule_chain_index(ct, degree):
+    """where the reference's Paterson-Stockmeyer schedule ends for this degree (src/ps.cu:131-200):
+    input + m + l - 2 with m = ceil(sqrt(d + 1)), l = ceil((d + 1) / m)"""
+    m = math.ceil(math.sqrt(degree + 1))
+    return ct.chain_index() + m + (degree + m) // m - 2
+
+
+def eval_chebyshev_series(context, relin_key_, ct, cheb, out_chain_index):
+    """sum_k cheb[k] T_k(x) on every slot by the bootstrapping pipeline's evaluator (powers of logarithmic depth, scales
+    tracked instead of snapped); the result is dropped to out_chain_index and carries the input's scale"""
+    cheb = np.asarray(cheb, dtype=np.float64).ravel()
+    d = cheb.size - 1
+    ops = boot.CtOps(context, relin_key_)
+    babies = 1 << max(1, math.ceil(math.log2(math.sqrt(d + 1))))
+    ev = bootmath.ChebyshevEvaluator(ops, ct, babies, tight=True)
+    out = ev.evaluate(cheb, ct.scale())
+    if out.chain_index() > out_chain_index:
+        raise ValueError("eval_polynomial: not enough levels left")
+    out = ops.drop(out, context.limbs_at(out_chain_index))
+    out.set_scale(ct.scale())
+    return out
+
+
 def eval_polynomial(context, encoder, relin_key_, ct, coeffs):
     """sum_k coeffs[k] x^k on every slot (src/ps.cu:131-200). The reference runs Paterson-Stockmeyer in the monomial
     basis with a chain of dependent powers; here the polynomial is rewritten in the Chebyshev basis (an exact change of
-    basis) and evaluated by the bootstrapping pipeline's evaluator, whose powers have logarithmic depth and whose
-    scales are tracked instead of snapped. The result is handed back at the chain index the reference ends on
-    (input + m + l - 2 with m = ceil(sqrt(d + 1)), l = ceil((d + 1) / m)) and at the input's scale."""
+    basis) and evaluated by eval_chebyshev_series. The result is handed back at the chain index the reference ends on
+    and at the input's scale."""
     c = np.asarray(coeffs, dtype=np.float64).ravel()
     if c.size < 2:
         raise ValueError("eval_polynomial: degree must be >= 1")
-    d = c.size - 1
-    m = math.ceil(math.sqrt(d + 1))
-    n_chunks = (d + 1 + m - 1) // m
-    ref_out_chain = ct.chain_index() + m + n_chunks - 2
     cheb = np.polynomial.chebyshev.poly2cheb(c)
-    ops = boot.CtOps(context, relin_key_)
-    babies = 1 << max(1, math.ceil(math.log2(math.sqrt(d + 1))))
-    ev = bootmath.ChebyshevEvaluator(ops, ct, babies)
-    out = ev.evaluate(cheb, ct.scale())
-    if out.chain_index() > ref_out_chain:
-        raise ValueError("eval_polynomial: not enough levels left")
-    out = ops.drop(out, context.limbs_at(ref_out_chain))
-    out.set_scale(ct.scale())
-    return out
+    if cheb.size < c.size:
+        cheb = np.concatenate([cheb, np.zeros(c.size - cheb.size)])
+    return eval_chebyshev_series(context, relin_key_, ct, cheb, schedule_chain_index(ct, c.size - 1))

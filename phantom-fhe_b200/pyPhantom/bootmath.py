@@ -192,10 +192,10 @@ def cosine_chebyshev(K, r, degree):
 
 
 def cheb_divide(c, g):
-    """p = q T_g + r for deg p < 2g, all in the Chebyshev basis: T_{g+j} = 2 T_j T_g - T_{g-j}"""
+    """p = q T_g + r for deg p <= 2g, all in the Chebyshev basis: T_{g+j} = 2 T_j T_g - T_{g-j}"""
     d = len(c) - 1
-    if not g <= d < 2 * g:
-        raise ValueError("cheb_divide needs g <= deg < 2g")
+    if not g <= d <= 2 * g:
+        raise ValueError("cheb_divide needs g <= deg <= 2g")
     q = np.zeros(d - g + 1)
     r = np.array(c[:g], dtype=np.float64)
     q[0] = c[g]
@@ -213,8 +213,10 @@ class ChebyshevEvaluator:
     relinearised by ops.mul and rescaled here; constants enter as integers round(c * const_scale), so
     every sum is between operands of equal level whose scales agree to about 2^-52."""
 
-    def __init__(self, ops, u, babies=8):
-        self.ops, self.m = ops, babies
+    def __init__(self, ops, u, babies=8, tight=False):
+        """tight: T_m also serves in the leaves and the giants stop below the degree, so that a polynomial of degree
+        2^k m (not only 2^k m - 1) fits k giants, and the output level is the smallest the coefficients allow"""
+        self.ops, self.m, self.tight = ops, babies, tight
         self.T = {1: u}
         self.giants = None
 
@@ -248,10 +250,11 @@ class ChebyshevEvaluator:
         if getattr(self, "giants", None) is not None:
             return
         g, giants = self.m, []
-        while g <= degree:
+        while g < degree or (g == degree and not self.tight):
             giants.append(g)
             g *= 2
-        need = sorted(set(range(2, min(self.m, degree + 1))) | set(giants))
+        top = min(self.m, degree) + 1 if self.tight else min(self.m, degree + 1)
+        need = sorted(set(range(2, top)) | set(giants))
         by_depth = {}
         for k in need:
             by_depth.setdefault((k - 1).bit_length(), []).append(k)
@@ -289,7 +292,7 @@ class ChebyshevEvaluator:
         while d > 0 and c[d] == 0.0:
             d -= 1
         c = c[: d + 1]
-        if d < self.m:
+        if d < self.m or (self.tight and d == self.m):
             return self._leaf(c, level, scale, ops)
         g = max(x for x in self.giants if x <= d)
         q, r = cheb_divide(c, g)
@@ -300,11 +303,28 @@ class ChebyshevEvaluator:
         prod = ops.rescale(ops.mul(qv, tg))
         return ops.add(prod, rv)
 
+    def _depth(self, c):
+        """levels below T_1 that _eval needs for these coefficients (a dry run of its recursion)"""
+        ops = self.ops
+        c = np.asarray(c, dtype=np.float64)
+        d = len(c) - 1
+        while d > 0 and c[d] == 0.0:
+            d -= 1
+        c = c[: d + 1]
+        top = ops.level(self.T[1])
+        if d < self.m or (self.tight and d == self.m):
+            return 1 + max([top - ops.level(self.T[i]) for i in range(1, d + 1) if c[i] != 0.0], default=0)
+        g = max(x for x in self.giants if x <= d)
+        q, r = cheb_divide(c, g)
+        return max(max(self._depth(q), top - ops.level(self.T[g])) + 1, self._depth(r))
+
     def evaluate(self, coeffs, scale):
         """-> value at level (input level - depth) whose scale is `scale` to about 2^-50"""
         degree = len(coeffs) - 1
         self.prepare(degree)
         ops = self.ops
+        if self.tight:
+            return self._eval(coeffs, ops.level(self.T[1]) - self._depth(coeffs), scale)
         lb = min(ops.level(self.T[k]) for k in range(1, min(self.m, degree + 1)))
         out_level = lb - 1 - len(self.giants)
         return self._eval(coeffs, out_level, scale)

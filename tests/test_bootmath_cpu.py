@@ -72,3 +72,19 @@ def test_eval_round_on_floats(degree):
     assert abs(out.scale / 2.0 ** 58 - 1) < 2.0 ** -45
     assert np.max(np.abs(out.v - I)) < 2e-9    # cubic in the distance to the integer: (2 pi)^2 (2^-11)^3 / 6
     assert ops.muls <= 19
+
+
+@pytest.mark.parametrize("degree,babies,depth", [(3, 2, 2), (7, 4, 4), (8, 4, 4), (9, 4, 4), (15, 4, 5), (16, 4, 5), (4, 4, 3), (1, 2, 1)])
+def test_tight_evaluator_depth_and_value(degree, babies, depth):
+    """tight mode: T_m serves in the leaves, degree 2^k m fits k giants, the output sits at the smallest depth"""
+    primes = [2 ** 58 - 27] + [2 ** 58 - (2 * i + 1) * 2 ** 17 + 1 for i in range(12)]
+    ops = bm.FloatOps(primes)
+    x = np.linspace(-1, 1, 501)
+    c = np.random.default_rng(degree).normal(size=degree + 1)
+    ev = bm.ChebyshevEvaluator(ops, ops.V(x, 13, 2.0 ** 58), babies, tight=True)
+    out = ev.evaluate(c, 2.0 ** 58)
+    assert out.level == 13 - depth and abs(out.scale / 2.0 ** 58 - 1) < 2.0 ** -45
+    assert np.max(np.abs(out.v - np.polynomial.chebyshev.chebval(x, c))) < 1e-11
+    q, r = bm.cheb_divide(np.arange(1.0, 10.0), 4)      # degree exactly 2g
+    assert np.max(np.abs(np.polynomial.chebyshev.chebval(x, q) * np.cos(4 * np.arccos(x)) + np.polynomial.chebyshev.chebval(x, r)
+                         - np.polynomial.chebyshev.chebval(x, np.arange(1.0, 10.0)))) < 1e-12
