@@ -37,16 +37,19 @@ class ckks_engine:
             raise ValueError("CKKSEngine: num_scale_levels must be >= 2")
         if cfg.num_special_primes < 1:
             raise ValueError("CKKSEngine: num_special_primes must be >= 1")
-        if cfg.use_bootstrap_to_17_levels:
-            raise ValueError("CKKSEngine: the use_bootstrap_to_17_levels chain is not built")
         if cfg.user_rotation_target_chain_indices and len(cfg.user_rotation_target_chain_indices) != len(cfg.user_rotation_steps):
             raise ValueError("CKKSEngine: user_rotation_target_chain_indices size must match user_rotation_steps size")
-        size_q = 1 + cfg.num_scale_levels + 3 + 9 + 3
+        deep = bool(cfg.use_bootstrap_to_17_levels)
+        size_q = cfg.num_scale_levels + 14 if deep else 1 + cfg.num_scale_levels + 3 + 9 + 3
         if size_q % cfg.num_special_primes != 0:
             raise ValueError("CKKSEngine: size_Q must be divisible by num_special_primes "
                              "(required by the hybrid KSK decomposition).")
         N = 1 << cfg.log_n
-        bits = [58] + [40] * cfg.num_scale_levels + [58] * 3 + [58] * 9 + [29] * 3 + [58] * cfg.num_special_primes
+        if deep:
+            # src/ckks_engine.cu:99-118: 40 x NSL (the first is the message prime) | 29 | 54 x 12 | 42 | 60 x NSP
+            bits = [40] * cfg.num_scale_levels + [29] + [54] * 12 + [42] + [60] * cfg.num_special_primes
+        else:
+            bits = [58] + [40] * cfg.num_scale_levels + [58] * 3 + [58] * 9 + [29] * 3 + [58] * cfg.num_special_primes
         parms = params(scheme_type.ckks)
         parms.set_poly_modulus_degree(N)
         parms.set_special_modulus_size(cfg.num_special_primes)
@@ -62,6 +65,18 @@ class ckks_engine:
         self._ctx = context(parms)
         self._sk = secret_key(self._ctx)
         self._enc = ckks_encoder(self._ctx)
+        self._scale, self._rescaled = [], []
+        if deep:
+            # src/ckks_engine.cu:171-214: on this chain the reference builds no bootstrap, relinearisation or rotation
+            # keys: encode / encrypt / decrypt and the scale arrays only, and bootstrap_inplace refuses
+            self._bk, self._glk = None, galois_key.from_keys([relin_key() for _ in elts])
+            self._freshest = self._ctx.get_first_index() + 13
+            self._bottom = self._ctx.total_parm_size() - 1
+            if self._freshest + cfg.num_scale_levels != self._bottom:
+                raise RuntimeError("CKKSEngine: BootstrapTo17Levels chain mismatch: freshest + num_scale_levels != bottom.")
+            if cfg.build_two_scale_arrays:
+                self._build_scale_arrays()
+            return
         self._bk = boot.create_bootstrap_key(self._ctx, self._enc, self._sk, cfg.sparse_hw, 9, cfg.user_scale, cfg.split_scale_down)
         # user rotation keys: steps the bootstrap already owns are shared (src/ckks_engine.cu:268-360 registers them as
         # non-owning fallbacks), the rest are generated
@@ -78,7 +93,6 @@ class ckks_engine:
         self._bottom = self._ctx.total_parm_size() - 1
         if self._freshest + cfg.num_scale_levels != self._bottom:
             raise RuntimeError("CKKSEngine: chain layout mismatch")
-        self._scale, self._rescaled = [], []
         if cfg.build_two_scale_arrays:
             self._build_scale_arrays()
 
@@ -134,7 +148,7 @@ class ckks_engine:
         self._assign(dst, sub(self._ctx, dst, src))
 
     def mul_and_relin_inplace(self, dst, src):
-        self._assign(dst, multiply_and_relin(self._ctx, dst, src, self._bk.relin))
+        self._assign(dst, multiply_and_relin(self._ctx, dst, src, self.relin_key()))
 
     def mul_plain_inplace(self, dst, pt):
         self._assign(dst, multiply_plain(self._ctx, dst, pt))
@@ -150,6 +164,9 @@ class ckks_engine:
 
     def bootstrap_inplace(self, ct):
         """src/ckks_engine.cu:557-603: any user level in, user level 0 out, scale snapped to user_scale"""
+        if self._cfg.use_bootstrap_to_17_levels:
+            raise RuntimeError("CKKSEngine::bootstrap_inplace: use_bootstrap_to_17_levels chain does not have a bootstrap "
+                               "algorithm yet. For now the new chain supports encode/encrypt/decrypt only.")
         self.user_level(ct)
         if ct.chain_index() != self._bottom - 1:
             mod_switch_to_inplace(self._ctx, ct, self._bottom - 1)
@@ -171,7 +188,7 @@ class ckks_engine:
         return self._sk
 
     def relin_key(self):
-        return self._bk.relin
+        return self._bk.relin if self._bk is not None else relin_key()
 
     def galois_key(self):
         return self._glk

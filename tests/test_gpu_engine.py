@@ -68,9 +68,29 @@ def test_config_errors():
     cfg.log_n, cfg.num_scale_levels, cfg.num_special_primes = 12, 5, 4   # 21 limbs not divisible by 4
     with pytest.raises(ValueError):
         ph.ckks_engine(cfg)
-    cfg.num_special_primes, cfg.use_bootstrap_to_17_levels = 7, True
+    cfg.num_special_primes, cfg.use_bootstrap_to_17_levels = 7, True     # 5 + 14 limbs not divisible by 7
     with pytest.raises(ValueError):
         ph.ckks_engine(cfg)
     cfg.use_bootstrap_to_17_levels, cfg.num_scale_levels = False, 1
     with pytest.raises(ValueError):
         ph.ckks_engine(cfg)
+
+
+def test_second_chain_layout_has_no_bootstrap():
+    """use_bootstrap_to_17_levels (src/ckks_engine.cu:99-118, 171-214, 570-578): 40 x NSL | 29 | 54 x 12 | 42 | specials;
+    user level 0 sits 13 primes below the top; encode / encrypt / decrypt work, bootstrap_inplace refuses"""
+    cfg = ph.ckks_engine_config()
+    cfg.log_n, cfg.num_scale_levels, cfg.num_special_primes = 12, 6, 5   # 6 + 14 = 20 limbs = 4 x 5
+    cfg.use_bootstrap_to_17_levels, cfg.build_two_scale_arrays = True, True
+    e = ph.ckks_engine(cfg)
+    ctx = e.context()
+    bits = [int(q).bit_length() for q in ctx.primes]
+    assert bits == [40] * 6 + [29] + [54] * 12 + [42] + [60] * 5
+    assert e.user_level_chain_index(0) == ctx.get_first_index() + 13 and e.max_user_level() == 5
+    assert e.scale_array_size() == ctx.total_parm_size()
+    v = np.random.default_rng(3).uniform(-1, 1, e.slot_count())
+    ct = e.encrypt(e.encode(v, 2))
+    assert e.user_level(ct) == 2
+    assert np.max(np.abs(np.array(e.decrypt_decode(ct)).real - v)) < 1e-6
+    with pytest.raises(RuntimeError, match="does not have a bootstrap"):
+        e.bootstrap_inplace(ct)
