@@ -743,6 +743,17 @@ class single_chain_plaintext:
     def coeffs_bytes(self):
         return self.coeffs.numpy().tobytes()
 
+    def get_scale(self):
+        return self.scale
+
+    @property
+    def nbytes(self):
+        return 0 if self.coeffs is None else self.coeffs.numel() * 8
+
+    @property
+    def N(self):
+        return 0 if self.coeffs is None else self.coeffs.numel()
+
 
 def scp_from_bytes(raw, scale):
     """binding.cu:416-516: rebuild a single-chain plaintext from its int64 little-endian bytes"""

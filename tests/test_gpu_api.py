@@ -195,6 +195,7 @@ def test_bsgs_driver_matches_the_reference():
         # round trip of the on-disk form of a single-chain plaintext
         back = ph.scp_from_bytes(diags.diagonals[1].coeffs_bytes(), SCALE)
         assert np.array_equal(back.coeffs.numpy(), diag_h[1])
+        assert (back.N, back.nbytes, back.get_scale(), back.scale) == (N, 8 * N, SCALE, SCALE)
         with pytest.raises(ValueError, match="M\\*G must equal d_pad"):
             ph.bsgs_apply_giants_with_babies(ctx, glk, [x] * M, ph.bsgs_diagonals(diags.diagonals, M * G + 1, M, G))
 
