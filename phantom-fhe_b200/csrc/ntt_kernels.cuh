@@ -289,7 +289,7 @@ struct ArithFp {
 };
 
 // ---- stage runners: compile-time recursion keeps every register index a constant --------------
-// forward: E residues x[], local stages S..R-1 of this round; twiddle index
+// forward: E residues x[], local stages S..R-1 of this stage group; twiddle index
 // (P << (shift + S)) + (k0 << S) + g.
 template <class A, int S, int R, int E>
 __device__ __forceinline__ void ct_stages(typename A::T (&x)[E], const W2 *tw, size_t P, int shift, size_t k0, const typename A::K &k) {
@@ -347,7 +347,7 @@ __device__ __forceinline__ void fwd_body(const NttArgs &a, const Epi &epi, uint6
     const uint32_t n1 = (uint32_t)(N >> LOG_T);  // number of sub-transforms per limb
     const int tid = threadIdx.x;
 
-    // ---- round 1 ---------------------------------------------------------------------------
+    // ---- stage group 1 ---------------------------------------------------------------------------
 #pragma unroll
     for (int gi = 0; gi < EPT / E1; gi++) {
         const int gid = tid + gi * THREADS;
@@ -374,7 +374,7 @@ __device__ __forceinline__ void fwd_body(const NttArgs &a, const Epi &epi, uint6
         }
     }
     __syncthreads();
-    // ---- round 2 ---------------------------------------------------------------------------
+    // ---- stage group 2 ---------------------------------------------------------------------------
     Epi e = epi;
     if (LAST) e.init(a, job, N);
     uint64_t *dst = a.dst + (size_t)job.x * N;
@@ -446,7 +446,7 @@ __device__ __forceinline__ void inv_body(const NttArgs &a, uint64_t *sm, const J
     // stages of the whole transform done before this pass: the row pass comes first
     const int g_pass = COLS ? ((int)a.logN - LOG_T) : 0;
 
-    // ---- round 1: contiguous runs of EA residues ----------------------------------------------
+    // ---- stage group 1: contiguous runs of EA residues ----------------------------------------------
 #pragma unroll
     for (int gi = 0; gi < EPT / EA; gi++) {
         const int gid = tid + gi * THREADS;
@@ -488,7 +488,7 @@ __device__ __forceinline__ void inv_body(const NttArgs &a, uint64_t *sm, const J
         }
     }
     __syncthreads();
-    // ---- round 2: stride EA ---------------------------------------------------------------------
+    // ---- stage group 2: stride EA ---------------------------------------------------------------------
 #pragma unroll
     for (int gi = 0; gi < EPT / EB; gi++) {
         const int gid = tid + gi * THREADS;
@@ -572,7 +572,7 @@ __device__ __forceinline__ void stage_tile(uint64_t *buf, const uint64_t *src, s
 template <int LOG_T, int R1, int R2, int LOG_C, bool COLS, bool LAST, class Epi>
 __global__ void __launch_bounds__((1 << (LOG_C + LOG_T)) / (1 << (R1 > R2 ? R1 : R2)), ntt_min_blocks((1 << (LOG_C + LOG_T)) / (1 << (R1 > R2 ? R1 : R2))))
 ntt_fwd_pipe(NttArgs a, Epi epi, uint32_t total) {
-    static_assert(R1 == R2, "pipelined passes are built for equal rounds");
+    static_assert(R1 == R2, "pipelined passes are built for equal stage groups");
     constexpr int TT = 1 << LOG_T, C = 1 << LOG_C, THREADS = (C * TT) >> R1;
     __shared__ __align__(16) uint64_t buf[2][C * (TT + (TT >> R2))];
     const size_t N = (size_t)1 << a.logN;
@@ -601,7 +601,7 @@ ntt_fwd_pipe(NttArgs a, Epi epi, uint32_t total) {
 template <int LOG_T, int RA, int RB, int LOG_C, bool COLS, bool LAST>
 __global__ void __launch_bounds__((1 << (LOG_C + LOG_T)) / (1 << (RA > RB ? RA : RB)), ntt_min_blocks((1 << (LOG_C + LOG_T)) / (1 << (RA > RB ? RA : RB))))
 ntt_inv_pipe(NttArgs a, uint32_t total) {
-    static_assert(RA == RB, "pipelined passes are built for equal rounds");
+    static_assert(RA == RB, "pipelined passes are built for equal stage groups");
     constexpr int TT = 1 << LOG_T, C = 1 << LOG_C, THREADS = (C * TT) >> RA;
     constexpr bool FIRST = !COLS;
     __shared__ __align__(16) uint64_t buf[2][C * (TT + (TT >> RA))];
