@@ -534,6 +534,29 @@ def main():
         e2e_s = float(t.item())
     e2e_value = world * B * e2e_steps / e2e_s
 
+    # ---- what the link itself gives for this call's traffic: bare pinned copies, both directions at once ----------
+    pcie = None
+    if e2e_steps and world == 1 and not args.no_extras:
+        s_in, s_out = torch.cuda.Stream(), torch.cuda.Stream()
+        d_res = [torch.empty(2, LEVEL, N, dtype=torch.int64, device="cuda") for _ in range(2)]
+
+        def copies(reps):
+            for i in range(reps):
+                with torch.cuda.stream(s_in):
+                    stage[i % len(stage)].copy_(host_ct3[i % B], non_blocking=True)
+                with torch.cuda.stream(s_out):
+                    host_out[i % B].copy_(d_res[i % 2], non_blocking=True)
+            s_in.synchronize()
+            s_out.synchronize()
+
+        copies(8)
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        copies(40)
+        dt = time.perf_counter() - t0
+        pcie = {"h2d_gbs": 40 * 3 * LEVEL * LIMB_BYTES / dt / 1e9, "d2h_gbs": 40 * 2 * LEVEL * LIMB_BYTES / dt / 1e9,
+                "keyswitch_per_s_ceiling": 40 / dt, "what": "bare pinned copies of one call's input and result, both directions at once"}
+
     # ---- N > 1: ONE key switch with its RNS limbs spread over the ranks (two NCCL all-gathers inside) ---------
     limb_sharded = None
     if world > 1:
@@ -620,7 +643,7 @@ def main():
                        "l2": "inputs larger than L2 (one step touches ~670 MB)", "parallelism": f"dp{world}"},
             "clocks": clocks,
             "e2e": {"value": e2e_value, "unit": "KeySwitch/s", "h2d_bytes_per_step": B * 3 * LEVEL * LIMB_BYTES,
-                    "d2h_bytes_per_step": B * 2 * LEVEL * LIMB_BYTES, "api": "pyPhantom.relinearize", "steps": e2e_steps},
+                    "d2h_bytes_per_step": B * 2 * LEVEL * LIMB_BYTES, "api": "pyPhantom.relinearize", "steps": e2e_steps, "streams": len(streams), "pcie": pcie},
             "gpu_launches": launches,
             "roofline": roofline,
             "roofline_keyswitch": {"bound": "hbm", "alg_bytes": KS_BYTES, "us_per_keyswitch": ks_us,
