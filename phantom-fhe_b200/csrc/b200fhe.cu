@@ -647,12 +647,12 @@ static uint32_t pipe_grid(const b2_ctx *c, uint32_t total) {
     return (total + per_cta - 1) / per_cta;
 }
 
-template <int LOG_A, int LOG_B, class Epi>
+template <int LOG_A, int LOG_B, class Epi, int SRC = 0>
 static void launch_fwd(const b2_ctx *c, const NttArgs &a, uint32_t njobs, const Epi &epi, cudaStream_t s) {
     using A = PassCfg<LOG_A>;
     using B = PassCfg<LOG_B>;
     const uint32_t N = 1u << a.logN;
-    if constexpr (LOG_A == 8 && LOG_B == 8) {
+    if constexpr (LOG_A == 8 && LOG_B == 8 && SRC == 0) {
         if (c->use_pipe) {
             const uint32_t total = njobs * (N >> (LOG_A + A::LOG_C));
             {
@@ -669,7 +669,7 @@ static void launch_fwd(const b2_ctx *c, const NttArgs &a, uint32_t njobs, const 
     }
     {
         LaunchScope ls(c, s, "ntt_fwd_cols");
-        ntt_fwd_pass<LOG_A, A::R_STRIDED, A::R_CONTIG, A::LOG_CC, true, false, EpiStore>
+        ntt_fwd_pass<LOG_A, A::R_STRIDED, A::R_CONTIG, A::LOG_CC, true, false, EpiStore, SRC>
             <<<njobs * (N >> (LOG_A + A::LOG_CC)), pass_threads<LOG_A, true>(), 0, s>>>(a, EpiStore{});
     }
     NttArgs b = a;
@@ -710,12 +710,14 @@ static void launch_inv(const b2_ctx *c, const NttArgs &a, uint32_t njobs, cudaSt
         <<<njobs * (N >> (LOG_A + A::LOG_CC)), pass_threads<LOG_A, true>(), 0, s>>>(b);
 }
 
-template <class Epi>
+// SRC != 0: the column pass makes limb job.x from slot job.x / src_div of src (words mod src_q) instead of reading it
+template <class Epi, int SRC = 0>
 static int run_fwd(const b2_ctx *c, const uint64_t *src, uint64_t *dst, const Job *jobs, uint32_t njobs, uint32_t first_prime,
-                   const Epi &epi, cudaStream_t s, uint32_t period = 0) {
+                   const Epi &epi, cudaStream_t s, uint32_t period = 0, uint32_t src_div = 0, uint64_t src_q = 0) {
     if (njobs == 0) return B2_OK;
     if (!aligned32(src) || !aligned32(dst) || !epi.aligned()) return fail(B2_EINVAL, "device buffers must be 32-byte aligned (256-bit accesses)");
-    NttArgs a{src, dst, jobs, first_prime, (uint32_t)c->logN, c->d_tw, c->d_mod, nullptr, period};
+    NttArgs a{src, dst, jobs, first_prime, (uint32_t)c->logN, c->d_tw, c->d_mod, nullptr, period, src_div, src_q};
+    if (SRC != 0 && (c->use_cluster || src_div == 0)) return fail(B2_EINVAL, "the on-the-fly source needs the two-pass transform");
     if (c->use_cluster) {
         static thread_local bool attr_set = false;  // per instantiation (one per epilogue type) and thread
         if (!attr_set) {
@@ -728,11 +730,11 @@ static int run_fwd(const b2_ctx *c, const uint64_t *src, uint64_t *dst, const Jo
         return B2_OK;
     }
     switch (c->logN) {
-        case 16: launch_fwd<8, 8>(c, a, njobs, epi, s); break;
-        case 15: launch_fwd<7, 8>(c, a, njobs, epi, s); break;
-        case 14: launch_fwd<7, 7>(c, a, njobs, epi, s); break;
-        case 13: launch_fwd<6, 7>(c, a, njobs, epi, s); break;
-        case 12: launch_fwd<6, 6>(c, a, njobs, epi, s); break;
+        case 16: launch_fwd<8, 8, Epi, SRC>(c, a, njobs, epi, s); break;
+        case 15: launch_fwd<7, 8, Epi, SRC>(c, a, njobs, epi, s); break;
+        case 14: launch_fwd<7, 7, Epi, SRC>(c, a, njobs, epi, s); break;
+        case 13: launch_fwd<6, 7, Epi, SRC>(c, a, njobs, epi, s); break;
+        case 12: launch_fwd<6, 6, Epi, SRC>(c, a, njobs, epi, s); break;
         default: return fail(B2_ESIZE, "unsupported polynomial degree");
     }
     LAUNCH_CHECK("ntt_fwd_pass");
@@ -1513,6 +1515,30 @@ extern "C" int b2_multiply_and_relin(b2_ctx *c, size_t l, const uint64_t *d_a, c
     return keyswitch_impl(c, l, t3 + 2 * S, rlk, n_evk, d_out, ws, s);
 }
 
+// Second half of a rescale. r [n_poly][N]: the dropped limb of every polynomial in coefficient form. Every remaining
+// limb j gets (in_j - NTT_j(rem mod q_j)) * q_last^-1 with rem = r (MODE 1, the reference's floor: src/rns.cu:1128-1183)
+// or its centred representative (MODE 2, round to nearest). The forward column pass reduces r into q_j as it loads, so
+// the (l-1) reduced copies are never written out; the one-launch and pipelined transform variants have no such load and
+// go through a reduction kernel first.
+template <int MODE>
+static int rescale_tail(const b2_ctx *c, size_t l, size_t n_poly, const uint64_t *r, const uint64_t *d_in, uint64_t *d_out, cudaStream_t s) {
+    const LevelPlan &pl = c->plan[l];
+    EpiSubMul<false> epi{d_in, d_out, pl.qlast_inv};
+    const uint32_t njobs = (uint32_t)(n_poly * (l - 1));
+    if (!c->use_cluster && !c->use_pipe) return run_fwd<EpiSubMul<false>, MODE>(c, r, d_out, pl.jobs_rs_ntt, njobs, 0, epi, s, 0, (uint32_t)(l - 1), c->q[l - 1]);
+    if (MODE == 1) {
+        // r mod q_j for every remaining prime: a base conversion with one input and the matrix [1]
+        int rc = run_bconv(c, false, r, d_out, nullptr, pl.grp_rs, (uint32_t)n_poly, pl.outs_rs, c->d_one, c->d_matd_one, 1, (uint32_t)(l - 1), true, s);
+        if (rc) return rc;
+    } else {
+        const size_t n = n_poly * (l - 1) * c->N;
+        LaunchScope ls(c, s, "rescale_centre");
+        rescale_centre_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(r, d_out, c->d_mod, (uint32_t)c->N, (uint32_t)(l - 1), (uint32_t)n_poly);
+        LAUNCH_CHECK("rescale_centre_kernel");
+    }
+    return run_fwd(c, d_out, d_out, pl.jobs_rs_ntt, njobs, 0, epi, s);
+}
+
 extern "C" int b2_rescale(b2_ctx *c, size_t l, size_t n_poly, const uint64_t *d_in, uint64_t *d_out, void *d_ws, size_t ws_bytes, void *stream) {
     CHECK_CTX(c);
     CHECK_LEVEL(c, l);
@@ -1528,11 +1554,7 @@ extern "C" int b2_rescale(b2_ctx *c, size_t l, size_t n_poly, const uint64_t *d_
         int rc = run_inv(c, d_in, r, pl.jobs_rs_intt, (uint32_t)n_poly, 0, c->d_fin_plain, s);
         if (rc) return rc;
     }
-    // r mod q_j for every remaining prime: a base conversion with one input and the matrix [1]
-    int rc = run_bconv(c, false, r, d_out, nullptr, pl.grp_rs, (uint32_t)n_poly, pl.outs_rs, c->d_one, c->d_matd_one, 1, (uint32_t)(l - 1), true, s);
-    if (rc) return rc;
-    EpiSubMul<false> epi{d_in, d_out, pl.qlast_inv};
-    return run_fwd(c, d_out, d_out, pl.jobs_rs_ntt, (uint32_t)(n_poly * (l - 1)), 0, epi, s);
+    return rescale_tail<1>(c, l, n_poly, r, d_in, d_out, s);
 }
 
 extern "C" int b2_rescale_rounded(b2_ctx *c, size_t l, size_t n_poly, const uint64_t *d_in, uint64_t *d_out, void *d_ws, size_t ws_bytes,
@@ -1551,14 +1573,7 @@ extern "C" int b2_rescale_rounded(b2_ctx *c, size_t l, size_t n_poly, const uint
         int rc = run_inv(c, d_in, r, pl.jobs_rs_intt, (uint32_t)n_poly, 0, c->d_fin_plain, s);
         if (rc) return rc;
     }
-    {
-        const size_t n = n_poly * (l - 1) * c->N;
-        LaunchScope ls(c, s, "rescale_centre");
-        rescale_centre_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(r, d_out, c->d_mod, (uint32_t)c->N, (uint32_t)(l - 1), (uint32_t)n_poly);
-        LAUNCH_CHECK("rescale_centre_kernel");
-    }
-    EpiSubMul<false> epi{d_in, d_out, pl.qlast_inv};
-    return run_fwd(c, d_out, d_out, pl.jobs_rs_ntt, (uint32_t)(n_poly * (l - 1)), 0, epi, s);
+    return rescale_tail<2>(c, l, n_poly, r, d_in, d_out, s);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -1613,10 +1628,7 @@ extern "C" int b2_rescale_static(b2_ctx *c, size_t l, size_t n_poly, const uint6
         rc = run_inv(c, d_in + (p * l + l - 1) * c->N, r + p * c->N, nullptr, 1, (uint32_t)(l - 1), c->d_fin_plain, s);
         if (rc) return rc;
     }
-    rc = run_bconv(c, false, r, d_out, nullptr, pl.grp_rs, (uint32_t)n_poly, pl.outs_rs, c->d_one, c->d_matd_one, 1, (uint32_t)(l - 1), true, s);
-    if (rc) return rc;
-    EpiSubMul<false> epi{d_in, d_out, pl.qlast_inv};
-    return run_fwd(c, d_out, d_out, pl.jobs_rs_ntt, (uint32_t)(n_poly * (l - 1)), 0, epi, s);
+    return rescale_tail<1>(c, l, n_poly, r, d_in, d_out, s);
 }
 
 extern "C" uint32_t b2_galois_elt_from_step(int step, size_t N) {

@@ -47,6 +47,10 @@ struct NttArgs {
     const Mod *mod;        // [size_QP]
     const W2 *fin;         // inverse only: [idx][2] = {scale of the x outputs, last-stage twiddle}
     uint32_t period;       // without a job list: limb j uses prime first_prime + j % period (0: + j), a batch of polynomials
+    // forward column pass with SRC != 0 (rescale): limb job.x is not read from its own slot but made on the fly from
+    // slot job.x / src_div of src, whose words are residues mod src_q, reduced into the limb's prime
+    uint32_t src_div;
+    uint64_t src_q;
 };
 
 __device__ __forceinline__ Job get_job(const NttArgs &a, uint32_t j) {
@@ -329,9 +333,12 @@ __device__ __forceinline__ void gs_stages(typename A::T (&x)[E], const W2 *tw, s
 // STAGED: the tile's input already sits in `sm` itself, dense ([e][c] for the column pass, [c][e] for the row
 // pass), put there by asynchronous copies; it is read into registers, and after a barrier the same buffer
 // serves as the exchange buffer.
-template <class A, int LOG_T, int R1, int R2, int LOG_C, bool COLS, bool LAST, class Epi, bool STAGED = false>
+// SRC (column pass only): 1 = the input word reduced into the limb's prime, 2 = its centred representative
+// (word - src_q when the word exceeds src_q / 2) reduced: the remainder a rescale subtracts, floor or nearest.
+template <class A, int LOG_T, int R1, int R2, int LOG_C, bool COLS, bool LAST, class Epi, bool STAGED = false, int SRC = 0>
 __device__ __forceinline__ void fwd_body(const NttArgs &a, const Epi &epi, uint64_t *sm, const Job &job, const Mod &md, uint32_t tile) {
     using T = typename A::T;
+    static_assert(SRC == 0 || (COLS && !STAGED), "the on-the-fly source belongs to the plain column pass");
     constexpr bool FIRST = COLS;
     constexpr int TT = 1 << LOG_T, E1 = 1 << R1, E2 = 1 << R2, C = 1 << LOG_C;
     constexpr int EPT = E1 > E2 ? E1 : E2;
@@ -340,12 +347,13 @@ __device__ __forceinline__ void fwd_body(const NttArgs &a, const Epi &epi, uint6
     const size_t N = (size_t)1 << a.logN;
     const typename A::K k = A::make(md, (int)a.logN);
     const W2 *tw = a.tw + (size_t)job.y * N;
-    const uint64_t *src = a.src + (size_t)job.x * N;
+    const uint64_t *src = a.src + (size_t)(SRC ? job.x / a.src_div : job.x) * N;
     const size_t estride = COLS ? (N >> LOG_T) : 1;
     const size_t cstride = COLS ? 1 : TT;
     const size_t base = COLS ? (size_t)tile * C : (size_t)tile * C * TT;
     const uint32_t n1 = (uint32_t)(N >> LOG_T);  // number of sub-transforms per limb
     const int tid = threadIdx.x;
+    const uint64_t src_half = SRC == 2 ? a.src_q >> 1 : 0, src_q_red = SRC == 2 ? barrett64(a.src_q, md.q, md.r1) : 0;
 
     // ---- stage group 1 ---------------------------------------------------------------------------
 #pragma unroll
@@ -359,7 +367,12 @@ __device__ __forceinline__ void fwd_body(const NttArgs &a, const Epi &epi, uint6
 #pragma unroll
         for (int i = 0; i < E1; i++) {
             const int e = elo + i * E2;
-            const uint64_t v = STAGED ? sm[COLS ? (e * C + c) : (c * TT + e)] : p[(size_t)i * E2 * estride];
+            uint64_t v = STAGED ? sm[COLS ? (e * C + c) : (c * TT + e)] : p[(size_t)i * E2 * estride];
+            if (SRC) {
+                const uint64_t word = v;
+                v = barrett64(word, md.q, md.r1);
+                if (SRC == 2 && word > src_half) v = sub_mod(v, src_q_red, md.q);
+            }
             x[i] = FIRST ? A::from_u64(v, k) : A::from_raw(v);
         }
         if (STAGED) {
@@ -407,7 +420,7 @@ __device__ __forceinline__ void fwd_body(const NttArgs &a, const Epi &epi, uint6
     }
 }
 
-template <int LOG_T, int R1, int R2, int LOG_C, bool COLS, bool LAST, class Epi>
+template <int LOG_T, int R1, int R2, int LOG_C, bool COLS, bool LAST, class Epi, int SRC = 0>
 __global__ void __launch_bounds__((1 << (LOG_C + LOG_T)) / (1 << (R1 > R2 ? R1 : R2)), ntt_min_blocks((1 << (LOG_C + LOG_T)) / (1 << (R1 > R2 ? R1 : R2))))
 ntt_fwd_pass(NttArgs a, Epi epi) {
     static_assert(R1 + R2 == LOG_T, "stage split");
@@ -417,9 +430,9 @@ ntt_fwd_pass(NttArgs a, Epi epi) {
     const uint32_t jobi = blockIdx.x / tiles, tile = blockIdx.x % tiles;
     const Job job = get_job(a, jobi);
     const Mod md = a.mod[job.y];
-    if (md.q < FP_LIMIT) fwd_body<ArithFp, LOG_T, R1, R2, LOG_C, COLS, LAST, Epi>(a, epi, sm, job, md, tile);
-    else if (md.q < WIDE_LIMIT) fwd_body<ArithInt<true>, LOG_T, R1, R2, LOG_C, COLS, LAST, Epi>(a, epi, sm, job, md, tile);
-    else fwd_body<ArithInt<false>, LOG_T, R1, R2, LOG_C, COLS, LAST, Epi>(a, epi, sm, job, md, tile);
+    if (md.q < FP_LIMIT) fwd_body<ArithFp, LOG_T, R1, R2, LOG_C, COLS, LAST, Epi, false, SRC>(a, epi, sm, job, md, tile);
+    else if (md.q < WIDE_LIMIT) fwd_body<ArithInt<true>, LOG_T, R1, R2, LOG_C, COLS, LAST, Epi, false, SRC>(a, epi, sm, job, md, tile);
+    else fwd_body<ArithInt<false>, LOG_T, R1, R2, LOG_C, COLS, LAST, Epi, false, SRC>(a, epi, sm, job, md, tile);
 }
 
 // ================================================================================================
