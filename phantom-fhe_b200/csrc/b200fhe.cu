@@ -1091,8 +1091,9 @@ __global__ void __launch_bounds__(256) ks_inner_prod_kernel(const uint64_t *__re
 }
 
 // HMult tensor product (src/polymath.cu:463-498): d0 = a0 b0, d2 = a1 b1, d1 = (a0+a1)(b0+b1) - d0 - d2
+// d0, d1 go to out[0..2S), d2 to out2[0..S): the relinearising caller keeps d2 in scratch and the rest in its result
 __global__ void __launch_bounds__(256) tensor_mul_kernel(const uint64_t *__restrict__ a, const uint64_t *__restrict__ b, uint64_t *__restrict__ out,
-                                                        const Mod *mod, uint32_t N, uint32_t l) {
+                                                        uint64_t *__restrict__ out2, const Mod *mod, uint32_t N, uint32_t l) {
     const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     const size_t S = (size_t)l * N;
     if (idx >= S) return;
@@ -1110,7 +1111,7 @@ __global__ void __launch_bounds__(256) tensor_mul_kernel(const uint64_t *__restr
     const uint64_t d1 = barrett128(p, q, md.r0, md.r1);
     out[idx] = d0;
     out[S + idx] = sub_mod(sub_mod(d1, d0, q), d2, q);
-    out[2 * S + idx] = d2;
+    out2[idx] = d2;
 }
 
 // src/polymath.cu:17-180
@@ -1162,6 +1163,25 @@ __global__ void __launch_bounds__(256) galois_gather_kernel(const uint64_t *__re
     if (idx >= (size_t)n_limbs * N) return;
     const size_t limb = idx / N;
     dst[idx] = src[limb * N + perm[idx % N]];
+}
+
+// The automorphism of a ciphertext (c0, c1) as a rotation needs it: perm(c0) goes straight into the result (added to it
+// when ACC: rotations that are summed), perm(c1) into the scratch the key switch reads. limbs [0, l) are c0, [l, 2l) c1.
+template <bool ACC>
+__global__ void __launch_bounds__(256) galois_split_kernel(const uint64_t *__restrict__ src, uint64_t *__restrict__ dst0, uint64_t *__restrict__ dst1,
+                                                          const uint32_t *__restrict__ perm, const Mod *mod, uint32_t N, uint32_t l) {
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t S = (size_t)l * N;
+    if (idx >= 2 * S) return;
+    const size_t limb = idx / N;
+    const uint64_t v = src[limb * N + perm[idx % N]];
+    if (limb >= l) {
+        dst1[idx - S] = v;
+    } else if (ACC) {
+        dst0[idx] = add_mod(dst0[idx], v, mod[limb].q);
+    } else {
+        dst0[idx] = v;
+    }
 }
 
 // Single-chain plaintext expansion (src/bootstrap.cu:660-686, light_pt_expand_per_tower_kernel):
@@ -1495,7 +1515,7 @@ extern "C" int b2_tensor_mul(b2_ctx *c, size_t l, const uint64_t *d_a, const uin
     if (!d_a || !d_b || !d_out) return fail(B2_EINVAL, "tensor_mul: null pointer");
     const size_t n = l * c->N;
     LaunchScope ls(c, (cudaStream_t)stream, "tensor_mul");
-    tensor_mul_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(d_a, d_b, d_out, c->d_mod, (uint32_t)c->N, (uint32_t)l);
+    tensor_mul_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(d_a, d_b, d_out, d_out + 2 * n, c->d_mod, (uint32_t)c->N, (uint32_t)l);
     LAUNCH_CHECK("tensor_mul_kernel");
     return B2_OK;
 }
@@ -1509,9 +1529,13 @@ extern "C" int b2_multiply_and_relin(b2_ctx *c, size_t l, const uint64_t *d_a, c
     cudaStream_t s = (cudaStream_t)stream;
     const size_t S = l * c->N;
     uint64_t *t3 = (uint64_t *)d_ws, *ws = t3 + 3 * S;
-    int rc = b2_tensor_mul(c, l, d_a, d_b, t3, stream);
-    if (rc) return rc;
-    CUDA_TRY(cudaMemcpyAsync(d_out, t3, 2 * S * 8, cudaMemcpyDeviceToDevice, s));
+    {
+        // d0, d1 straight into the result, d2 into scratch for the key switch (every thread reads its own position of
+        // the operands before it writes, so the result may alias an operand)
+        LaunchScope ls(c, s, "tensor_mul");
+        tensor_mul_kernel<<<(unsigned)((S + 255) / 256), 256, 0, s>>>(d_a, d_b, d_out, t3 + 2 * S, c->d_mod, (uint32_t)c->N, (uint32_t)l);
+        LAUNCH_CHECK("tensor_mul_kernel");
+    }
     return keyswitch_impl(c, l, t3 + 2 * S, rlk, n_evk, d_out, ws, s);
 }
 
@@ -1680,6 +1704,15 @@ static int gather_impl(b2_ctx *c, const uint32_t *perm, const uint64_t *src, uin
     return B2_OK;
 }
 
+static int gather_split_impl(b2_ctx *c, const uint32_t *perm, const uint64_t *src, uint64_t *dst0, uint64_t *dst1, size_t l, bool acc, cudaStream_t s) {
+    const size_t n = 2 * l * c->N;
+    LaunchScope ls(c, s, "galois_gather");
+    if (acc) galois_split_kernel<true><<<(unsigned)((n + 255) / 256), 256, 0, s>>>(src, dst0, dst1, perm, c->d_mod, (uint32_t)c->N, (uint32_t)l);
+    else galois_split_kernel<false><<<(unsigned)((n + 255) / 256), 256, 0, s>>>(src, dst0, dst1, perm, c->d_mod, (uint32_t)c->N, (uint32_t)l);
+    LAUNCH_CHECK("galois_split_kernel");
+    return B2_OK;
+}
+
 // tables must exist before an asynchronous sequence starts: creating one synchronises
 static int galois_lookup(b2_ctx *c, uint32_t elt, const uint32_t **out) {
     std::lock_guard<std::mutex> lk(c->mu);
@@ -1710,10 +1743,16 @@ extern "C" int b2_apply_galois(b2_ctx *c, size_t l, uint32_t elt, const uint64_t
     cudaStream_t s = (cudaStream_t)stream;
     const size_t S = l * c->N;
     uint64_t *p = (uint64_t *)d_ws, *ws = p + 2 * S;  // permuted c0 | permuted c1
-    rc = gather_impl(c, perm, d_ct, p, 2 * l, s);  // both polynomials: limb index only selects the row
-    if (rc) return rc;
     // (c0, c1) <- (perm(c0), 0) + key switch of perm(c1)   (src/evaluate.cu:1644-1655)
-    CUDA_TRY(cudaMemcpyAsync(d_out, p, S * 8, cudaMemcpyDeviceToDevice, s));
+    const bool apart = d_out + 2 * S <= d_ct || d_ct + 2 * S <= d_out;
+    if (apart) {
+        rc = gather_split_impl(c, perm, d_ct, d_out, p + S, l, false, s);  // perm(c0) lands in the result
+        if (rc) return rc;
+    } else {
+        rc = gather_impl(c, perm, d_ct, p, 2 * l, s);  // both polynomials: limb index only selects the row
+        if (rc) return rc;
+        CUDA_TRY(cudaMemcpyAsync(d_out, p, S * 8, cudaMemcpyDeviceToDevice, s));
+    }
     CUDA_TRY(cudaMemsetAsync(d_out + S, 0, S * 8, s));
     return keyswitch_impl(c, l, p + S, ksk, n_evk, d_out, ws, s);
 }
@@ -1732,14 +1771,21 @@ extern "C" int b2_apply_galois_accumulate(b2_ctx *c, size_t l, uint32_t elt, con
     cudaStream_t s = (cudaStream_t)stream;
     const size_t N = c->N, S = l * N, lP = l + c->size_P, beta = c->plan[l].beta;
     uint64_t *p = (uint64_t *)d_ws, *t = p + 2 * S, *up = t + S;  // permuted c0 | permuted c1 | t | up
-    rc = gather_impl(c, perm, d_ct, p, 2 * l, s);
-    if (rc) return rc;
-    if (first) {
-        CUDA_TRY(cudaMemcpyAsync(d_acc, p, S * 8, cudaMemcpyDeviceToDevice, s));
-        CUDA_TRY(cudaMemsetAsync(d_acc + S, 0, S * 8, s));
-    } else {
-        rc = b2_poly_op(c, 0, l, d_acc, p, d_acc, stream);
+    if (d_acc + 2 * S <= d_ct || d_ct + 2 * S <= d_acc) {
+        // perm(c0) straight into (or onto) the accumulator, perm(c1) into scratch: one launch
+        rc = gather_split_impl(c, perm, d_ct, d_acc, p + S, l, !first, s);
         if (rc) return rc;
+        if (first) CUDA_TRY(cudaMemsetAsync(d_acc + S, 0, S * 8, s));
+    } else {
+        rc = gather_impl(c, perm, d_ct, p, 2 * l, s);
+        if (rc) return rc;
+        if (first) {
+            CUDA_TRY(cudaMemcpyAsync(d_acc, p, S * 8, cudaMemcpyDeviceToDevice, s));
+            CUDA_TRY(cudaMemsetAsync(d_acc + S, 0, S * 8, s));
+        } else {
+            rc = b2_poly_op(c, 0, l, d_acc, p, d_acc, stream);
+            if (rc) return rc;
+        }
     }
     rc = modup_impl(c, l, p + S, up, t, false, s);
     if (rc) return rc;
