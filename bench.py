@@ -237,8 +237,16 @@ def bootstrap_section(ph, torch, np):
     ct = sk.encrypt_symmetric(ctx, enc.encode_double_vector(ctx, msg, 2.0 ** 40, chain_index=1))
     ph.mod_switch_to_inplace(ctx, ct, ctx.total_parm_size() - 2)
     launches0 = int(ph._native.LIB.b2_launch_count())
-    out = ph.bootstrap(ctx, enc, ct, bk, 2.0 ** 40)   # eager: every kernel is launched from the host and counted
+    ph._native.check(ph._native.LIB.b2_profile_start(ctx._h))
+    out = ph.bootstrap(ctx, enc, ct, bk, 2.0 ** 40)   # eager: every kernel is launched from the host, counted and timed
+    names = ctypes.create_string_buffer(8192)
+    tot, cnt, n_out = (ctypes.c_float * 128)(), (ctypes.c_uint32 * 128)(), ctypes.c_size_t()
+    ph._native.check(ph._native.LIB.b2_profile_stop(ctx._h, names, 8192, tot, cnt, 128, ctypes.byref(n_out)))
     launches = int(ph._native.LIB.b2_launch_count()) - launches0
+    nm = names.value.decode().strip(";").split(";")
+    # summed device time per kernel name with every launch timed on its own stream (they overlap across the pipeline's
+    # streams, so the sum is well above the wall time of one bootstrap: read the shares)
+    kernel_ms = {nm[i]: {"launches": int(cnt[i]), "ms": round(float(tot[i]), 3)} for i in range(n_out.value)}
     for _ in range(3):                                  # the second call captures the CUDA graph, later ones replay it
         out = ph.bootstrap(ctx, enc, ct, bk, 2.0 ** 40)
     torch.cuda.synchronize()
@@ -254,7 +262,7 @@ def bootstrap_section(ph, torch, np):
     return {"ms": float(np.median(times)), "ms_min": float(min(times)), "kernels_per_bootstrap": launches, "mode": "CUDA graph replay",
             "log2_max_err": math.log2(float(err.max())), "max_err": float(err.max()), "mean_err": float(err.mean()),
             "limbs_in": 2, "limbs_out": out.coeff_modulus_size(), "usable_levels_out": out.coeff_modulus_size() - 1, "chain_bits": "58|40x8|58x12|29x3|P 58x8",
-            "secret_hamming_weight": 192, "keygen_s": keygen_s}
+            "secret_hamming_weight": 192, "keygen_s": keygen_s, "kernels_eager": kernel_ms}
 
 
 def compositions_section(ph, ctx, torch, np, synth, primes, keys, N, level, reps=20):
