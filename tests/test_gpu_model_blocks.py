@@ -166,3 +166,32 @@ def test_attention_products(kit):
         ph.score_times_v(ctx, rlk, glk, [], [], mask_pt, d_head, d_total, positions)
     with pytest.raises(ValueError, match="d_head must be a power of 2"):
         ph.score_times_v(ctx, rlk, glk, scores, scores, mask_pt, 3, d_total, positions)
+
+
+def test_streams_do_not_change_the_limbs(kit, monkeypatch):
+    """the pieces issued on side streams give the limbs the same calls give one after the other"""
+    import torch
+    from pyPhantom import model_blocks as mb
+    ctx, enc, rlk, glk = kit["ctx"], kit["enc"], kit["rlk"], kit["glk"]
+    rng = np.random.default_rng(10)
+    d_head, d_total = 4, 8
+    positions = SLOTS // d_total
+    cq = _enc(kit, rng.uniform(-1, 1, SLOTS))
+    ks = [_enc(kit, rng.uniform(-1, 1, SLOTS)) for _ in range(5)]
+    vs = [_enc(kit, rng.uniform(-1, 1, SLOTS)) for _ in range(5)]
+    mask = np.zeros((positions, 2, d_head))
+    mask[:, :, 0] = 1.0
+    mask_pt = enc.encode_double_vector(ctx, mask.ravel(), float(ctx.primes[ctx.limbs_at(2) - 1]), 2)
+
+    def run():
+        scores = ph.compute_qkt(ctx, rlk, glk, cq, ks, d_head)
+        out = ph.score_times_v(ctx, rlk, glk, scores, vs, mask_pt, d_head, d_total, positions)
+        sm = ph.softmax_correct(ctx, enc, rlk, scores[0], scores[1], 2)
+        torch.cuda.synchronize()
+        return [s.data.clone() for s in scores] + [out.data.clone(), sm.data.clone()]
+
+    forked = [run() for _ in range(3)]
+    monkeypatch.setattr(mb, "MAX_LANES", 0)
+    plain = run()
+    for got in forked:
+        assert len(got) == len(plain) and all(torch.equal(a, b) for a, b in zip(got, plain))
