@@ -168,6 +168,10 @@ struct LevelPlan {
     Job *jobs_up_intt = nullptr;   // l
     Job *jobs_up_ntt = nullptr;    // n_up_ntt
     uint32_t n_up_ntt = 0;
+    Job *jobs_up_rows = nullptr;   // the jobs of jobs_up_ntt whose limb is not on an FP64 prime of Q (fused inner product)
+    uint32_t n_up_rows = 0;
+    uint32_t n_wideQ = 0;          // leading Q limbs on primes >= 2^41
+    bool mac_ok = false;           // Q limbs [n_wideQ, l) all on FP64 primes: the fused row pass + inner product applies
     Job *jobs_dn_intt = nullptr;   // 2*alpha (poly-major), prefix alpha for one polynomial
     Job *jobs_dn_ntt = nullptr;    // 2*l
     Job *jobs_dnf_intt = nullptr;  // fused key switch: P limbs live compactly in [2][alpha][N]
@@ -214,6 +218,7 @@ struct b2_ctx {
     bool bconv_fp = false;         // every digit satisfies sum(q_i) < 2^64 and alpha <= 8
     bool use_cluster = false;      // N = 2^16: single-launch transforms on 8-CTA clusters
     bool use_pipe = false;         // N = 2^16: persistent passes with asynchronous double-buffered tile loads
+    bool use_mac = false;          // N = 2^16: ModUp's last forward pass carries the inner product (off with B2_KS_FUSED_IP=0)
     int sm_count = 148;
     // RNS-limb sharding of one ciphertext over `shard_world` GPUs: this rank's slice of every list
     int shard_rank = 0, shard_world = 1;
@@ -296,12 +301,13 @@ static int build_level(b2_ctx *c, size_t l) {
     const size_t n_up_ntt = beta * lP - l;
     const size_t mat_up_words = beta * lP * alpha;
     // host staging mirrors the device blob
-    size_t bytes = 64 + sizeof(Job) * (l + n_up_ntt + 4 * alpha + 4 * l + 3 + 3 * l) + sizeof(W2) * (2 * l + c->size_QP) +
+    size_t bytes = 64 + sizeof(Job) * (l + 2 * n_up_ntt + 4 * alpha + 4 * l + 3 + 3 * l) + sizeof(W2) * (2 * l + c->size_QP) +
                    sizeof(BconvGroup) * (beta + 4 + 3) + sizeof(uint2) * (n_up_ntt + l + l) + 8 * mat_up_words * 4 + 16 * 24;
     std::vector<char> host(bytes, 0);
     char *cur = host.data();
     auto *jobs_up_intt = blob_take<Job>(cur, l);
     auto *jobs_up_ntt = blob_take<Job>(cur, n_up_ntt);
+    auto *jobs_up_rows = blob_take<Job>(cur, n_up_ntt);
     auto *jobs_dn_intt = blob_take<Job>(cur, 2 * alpha);
     auto *jobs_dn_ntt = blob_take<Job>(cur, 2 * l);
     auto *jobs_dnf_intt = blob_take<Job>(cur, 2 * alpha);
@@ -352,6 +358,16 @@ static int build_level(b2_ctx *c, size_t l) {
             up_i++;
         }
     }
+    // limbs whose last forward pass can carry the inner product: Q limbs on FP64 primes behind a prefix of wide ones
+    size_t n_wide = 0;
+    while (n_wide < l && c->q[n_wide] >= b2::FP_LIMIT) n_wide++;
+    bool mac_ok = n_wide < l && beta <= B2_MAC_MAX_BETA;
+    for (size_t i = n_wide; i < l; i++) mac_ok = mac_ok && c->q[i] < b2::FP_LIMIT;
+    size_t n_up_rows = 0;
+    for (size_t j = 0; j < n_up_ntt; j++) {
+        const size_t t = jobs_up_ntt[j].x % lP;
+        if (t < n_wide || t >= l) jobs_up_rows[n_up_rows++] = jobs_up_ntt[j];
+    }
     // ---- ModDown (src/rns_bconv.cu:776-828) ----
     uint32_t p_pieces = 2;
     for (size_t i = 0; i < alpha; i++) p_pieces = std::max(p_pieces, h_npieces(c->q[sQ + i]));
@@ -390,6 +406,10 @@ static int build_level(b2_ctx *c, size_t l) {
     pl.jobs_up_intt = (Job *)dev(jobs_up_intt);
     pl.jobs_up_ntt = (Job *)dev(jobs_up_ntt);
     pl.n_up_ntt = (uint32_t)n_up_ntt;
+    pl.jobs_up_rows = (Job *)dev(jobs_up_rows);
+    pl.n_up_rows = (uint32_t)n_up_rows;
+    pl.n_wideQ = (uint32_t)n_wide;
+    pl.mac_ok = mac_ok;
     pl.jobs_dn_intt = (Job *)dev(jobs_dn_intt);
     pl.jobs_dn_ntt = (Job *)dev(jobs_dn_ntt);
     pl.jobs_dnf_intt = (Job *)dev(jobs_dnf_intt);
@@ -594,6 +614,8 @@ extern "C" int b2_ctx_create(size_t N, const uint64_t *primes, size_t size_QP, s
     c->use_cluster = (c->logN == 16) && env_cl && env_cl[0] == '1';
     const char *env_pipe = getenv("B2_NTT_PIPE");
     c->use_pipe = (c->logN == 16) && env_pipe && env_pipe[0] == '1';
+    const char *env_mac = getenv("B2_KS_FUSED_IP");
+    c->use_mac = (c->logN == 16) && !c->use_cluster && !c->use_pipe && !(env_mac && env_mac[0] == '0');
     cudaDeviceGetAttribute(&c->sm_count, cudaDevAttrMultiProcessorCount, c->device);
     if (c->sm_count < 1) c->sm_count = 148;
     c->plan.resize(sQ + 1);
@@ -1495,6 +1517,56 @@ static int keyswitch_impl(b2_ctx *c, size_t l, const uint64_t *c2, const uint64_
                           cudaStream_t s) {
     const size_t N = c->N, lP = l + c->size_P, beta = c->plan[l].beta;
     uint64_t *t = ws, *up = t + l * N, *cxP = up + beta * lP * N;
+    const LevelPlan &pl = c->plan[l];
+    if (c->use_mac && pl.mac_ok && n_evk >= beta && aligned32(c2) && aligned32(ct) && aligned32(up)) {
+        // ModUp up to the column pass for every limb; the row pass is stored only for the limbs the stand-alone inner
+        // product still handles (wide Q primes and P); for the FP64 limbs of Q it runs inside ntt_fwd_rows_mac
+        using Cfg = PassCfg<8>;
+        int rc = run_inv(c, c2, t, pl.jobs_up_intt, (uint32_t)l, 0, pl.fin_up, s);
+        if (rc) return rc;
+        rc = run_bconv(c, false, t, up, c2, pl.grp_up, pl.beta, pl.outs_up, pl.mat_up, pl.matd_up, (uint32_t)c->size_P, (uint32_t)lP, true, s);
+        if (rc) return rc;
+        NttArgs a{up, up, pl.jobs_up_ntt, 0, (uint32_t)c->logN, c->d_tw, c->d_mod, nullptr, 0};
+        {
+            LaunchScope ls(c, s, "ntt_fwd_cols");
+            ntt_fwd_pass<8, Cfg::R_STRIDED, Cfg::R_CONTIG, Cfg::LOG_CC, true, false, EpiStore>
+                <<<pl.n_up_ntt * (uint32_t)(N >> (8 + Cfg::LOG_CC)), pass_threads<8, true>(), 0, s>>>(a, EpiStore{});
+            LAUNCH_CHECK("ntt_fwd_pass");
+        }
+        if (pl.n_up_rows) {
+            NttArgs b = a;
+            b.jobs = pl.jobs_up_rows;
+            LaunchScope ls(c, s, "ntt_fwd_rows");
+            ntt_fwd_pass<8, Cfg::R_STRIDED, Cfg::R_CONTIG, Cfg::LOG_C, false, true, EpiStore>
+                <<<pl.n_up_rows * (uint32_t)(N >> (8 + Cfg::LOG_C)), pass_threads<8>(), 0, s>>>(b, EpiStore{});
+            LAUNCH_CHECK("ntt_fwd_pass");
+        }
+        const uint4 rest = make_uint4(0, pl.n_wideQ, 0, (uint32_t)c->size_P);
+        rc = inner_prod_impl(c, l, up, c2, evk, n_evk, cxP, ct, true, s, &rest);
+        if (rc) return rc;
+        {
+            MacArgs m{};
+            m.own = c2;
+            for (size_t d = 0; d < beta; d++) {
+                if (!evk[d]) return fail(B2_EINVAL, "null evaluation-key digit");
+                m.evk[d] = evk[d];
+            }
+            m.ct = ct, m.pinv = c->d_Pinv;
+            m.l = (uint32_t)l, m.lP = (uint32_t)lP, m.alpha = (uint32_t)c->size_P, m.beta = (uint32_t)beta, m.size_QP = (uint32_t)c->size_QP;
+            m.first_limb = pl.n_wideQ;
+            LaunchScope ls(c, s, "ntt_fwd_rows_mac");
+            static_assert(Cfg::R_STRIDED == Cfg::R_CONTIG, "the fused pass wants equal stage groups");
+            ntt_fwd_rows_mac<8, Cfg::R_CONTIG, Cfg::LOG_C>
+                <<<(uint32_t)(l - pl.n_wideQ) * (uint32_t)(N >> (8 + Cfg::LOG_C)), pass_threads<8>(), 0, s>>>(a, m);
+            LAUNCH_CHECK("ntt_fwd_rows_mac");
+        }
+        const size_t ap = c->size_P;
+        rc = run_inv(c, cxP, cxP, pl.jobs_dnf_intt, (uint32_t)(2 * ap), 0, c->d_fin_P, s);
+        if (rc) return rc;
+        rc = run_bconv(c, false, cxP, up, nullptr, pl.grp_dnf, 2, pl.outs_dn, c->d_mat_dn_pinv, c->d_matd_dn_pinv, (uint32_t)ap, (uint32_t)l, true, s);
+        if (rc) return rc;
+        return run_fwd(c, up, up, pl.jobs_dnf_ntt, (uint32_t)(2 * l), 0, EpiSubFrom{ct}, s);
+    }
     int rc = modup_impl(c, l, c2, up, t, false, s);  // the inner product reads the own limbs from c2
     if (rc) return rc;
     return ks_tail_fused(c, l, up, c2, evk, n_evk, ct, cxP, up, s);

@@ -436,6 +436,104 @@ ntt_fwd_pass(NttArgs a, Epi epi) {
 }
 
 // ================================================================================================
+// Last forward (row) pass of ModUp fused with the key-switch inner product, for the limbs on FP64 primes.
+// A CTA owns one tile of one output limb t and walks the digits: the digit that holds limb t itself contributes the
+// NTT-form input as it is, every other digit's limb t is finished here (row pass of its column-pass output) and never
+// stored. Both polynomials of the key are multiplied in and accumulated in FP64 (|sum| < beta q), reduced once, and
+// ct[k][t] += sum_k * P^-1 as the stand-alone inner-product kernel does. Same residues as that kernel.
+// ================================================================================================
+#define B2_MAC_MAX_BETA 8
+struct MacArgs {
+    const uint64_t *own;                   // NTT-form input of ModUp, [l][N]
+    const uint64_t *evk[B2_MAC_MAX_BETA];  // digit d: [2][size_QP][N]
+    uint64_t *ct;                          // [2][l][N]
+    const W2 *pinv;                        // per prime: P^-1 {w, shoup}
+    uint32_t l, lP, alpha, beta, size_QP, first_limb;
+};
+
+__device__ __forceinline__ u64x4 ld256_cs(const uint64_t *p) {  // streaming: the key is read once
+    u64x4 v;
+    asm("ld.global.cs.v4.u64 {%0, %1, %2, %3}, [%4];" : "=l"(v.a), "=l"(v.b), "=l"(v.c), "=l"(v.d) : "l"(p));
+    return v;
+}
+
+template <int LOG_T, int R, int LOG_C>
+__global__ void __launch_bounds__((1 << (LOG_C + LOG_T)) >> R) ntt_fwd_rows_mac(NttArgs a, MacArgs m) {
+    using A = ArithFp;
+    static_assert(2 * R == LOG_T, "equal stage groups: one register group per thread in both");
+    constexpr int TT = 1 << LOG_T, E = 1 << R, C = 1 << LOG_C;
+    constexpr int TPAD = TT + (TT >> R);
+    __shared__ uint64_t sm[C * TPAD];
+    const size_t N = (size_t)1 << a.logN;
+    const uint32_t tiles = (uint32_t)(N >> (LOG_T + LOG_C));
+    const uint32_t t = m.first_limb + blockIdx.x / tiles, tile = blockIdx.x % tiles;
+    const Mod md = a.mod[t];
+    const A::K k = A::make(md, (int)a.logN);
+    const W2 *tw = a.tw + (size_t)t * N;
+    const uint32_t n1 = (uint32_t)(N >> LOG_T);
+    const int tid = threadIdx.x;
+    const int c = tid / E, e = tid % E;  // sub-transform of the tile, register group within it (both stage groups)
+    const uint32_t P = n1 + tile * C + c;
+    const size_t base = (size_t)tile * C * TT;
+    const size_t o = base + (size_t)c * TT + (size_t)e * E;  // this thread's E consecutive outputs
+    const uint32_t own_d = t / m.alpha;
+    double acc0[E], acc1[E];
+#pragma unroll
+    for (int i = 0; i < E; i++) acc0[i] = acc1[i] = 0.0;
+    for (uint32_t d = 0; d < m.beta; d++) {
+        double y[E];
+        if (d == own_d) {
+#pragma unroll
+            for (int i = 0; i < E; i += 4) {
+                const u64x4 v = ld256(m.own + (size_t)t * N + o + i);
+                y[i] = A::from_u64(v.a, k), y[i + 1] = A::from_u64(v.b, k), y[i + 2] = A::from_u64(v.c, k), y[i + 3] = A::from_u64(v.d, k);
+            }
+        } else {
+            const uint64_t *src = a.src + ((size_t)d * m.lP + t) * N + base + (size_t)c * TT + e;
+#pragma unroll
+            for (int i = 0; i < E; i++) y[i] = A::from_raw(src[i * E]);
+            ct_stages<A, 0, R, E>(y, tw, P, 0, 0, k);
+#pragma unroll
+            for (int i = 0; i < E; i++) sm[c * TPAD + pad_idx<LOG_T, R>(e + i * E)] = A::to_raw(y[i]);
+            __syncthreads();
+#pragma unroll
+            for (int i = 0; i < E; i++) y[i] = A::from_raw(sm[c * TPAD + pad_idx<LOG_T, R>(e * E + i)]);
+            __syncthreads();  // the next digit refills the buffer
+            ct_stages<A, 0, R, E>(y, tw, P, R, e, k);
+#pragma unroll
+            for (int i = 0; i < E; i++) y[i] = A::reduce(y[i], k);
+        }
+        const uint64_t *k0 = m.evk[d] + (size_t)t * N + o, *k1 = k0 + (size_t)m.size_QP * N;
+#pragma unroll
+        for (int i = 0; i < E; i += 4) {
+            const u64x4 u = ld256_cs(k0 + i), v = ld256_cs(k1 + i);
+            const uint64_t ku[4] = {u.a, u.b, u.c, u.d}, kv[4] = {v.a, v.b, v.c, v.d};
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                const double w0 = A::from_u64(ku[j], k), w1 = A::from_u64(kv[j], k);
+                acc0[i + j] = __dadd_rn(acc0[i + j], A::mulmod(y[i + j], A::Tw{w0, __dmul_rn(w0, k.qinv)}, k));
+                acc1[i + j] = __dadd_rn(acc1[i + j], A::mulmod(y[i + j], A::Tw{w1, __dmul_rn(w1, k.qinv)}, k));
+            }
+        }
+    }
+    const W2 pi = m.pinv[t];
+    const uint64_t q = md.q;
+    uint64_t *c0 = m.ct + (size_t)t * N + o, *c1 = m.ct + ((size_t)m.l + t) * N + o;
+#pragma unroll
+    for (int i = 0; i < E; i += 4) {
+        const u64x4 u = ld256(c0 + i), v = ld256(c1 + i);
+        uint64_t r[4], s[4];
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            r[j] = mul_shoup(A::canon_fwd(acc0[i + j], k), pi, q);
+            s[j] = mul_shoup(A::canon_fwd(acc1[i + j], k), pi, q);
+        }
+        st256(c0 + i, add_mod(u.a, r[0], q), add_mod(u.b, r[1], q), add_mod(u.c, r[2], q), add_mod(u.d, r[3], q));
+        st256(c1 + i, add_mod(v.a, s[0], q), add_mod(v.b, s[1], q), add_mod(v.c, s[2], q), add_mod(v.d, s[3], q));
+    }
+}
+
+// ================================================================================================
 // inverse pass: RA contiguous stages, exchange, RB strided stages
 // ================================================================================================
 template <class A, int LOG_T, int RA, int RB, int LOG_C, bool COLS, bool LAST, bool STAGED = false>

@@ -454,3 +454,21 @@ def test_optional_transform_kernels(monkeypatch, env):
     ws, nb = _ws(ctx, _native.OP_KEYSWITCH, l)
     check(LIB.b2_keyswitch(h, l, c2.data_ptr(), kp.ctypes.data, beta, ct.data_ptr(), ws.data_ptr(), nb, stream()))
     assert hashes(ct, N) == case["hashes"]["keyswitch"]
+
+
+@pytest.mark.parametrize("fused", ["1", "0"])
+@pytest.mark.parametrize("name", ["n16_l5_a8.json", "n16_l24_a8.json"])
+def test_inner_product_inside_the_last_forward_pass(monkeypatch, name, fused):
+    """At N = 2^16 ModUp's last forward pass multiplies the key in for the limbs on FP64 primes and never stores those
+    digits (B2_KS_FUSED_IP=0 switches back to the stand-alone inner product): both give the reference's limbs"""
+    monkeypatch.setenv("B2_KS_FUSED_IP", fused)
+    path = [p for p in GOLDEN if p.endswith(name)][0]
+    case, ctx, o = load_case(path)
+    N, l, seed, h = o.N, case["level"], case["seed"], ctx._h
+    beta = o.beta(l)
+    kt, kp = key_dev(o.synth_key(beta, seed, 10))
+    c2 = dev(o.fill(1, o.primes[:l], seed, 3)[0])
+    ct = dev(o.synth_ct(l, seed, 1))
+    ws, nb = _ws(ctx, _native.OP_KEYSWITCH, l)
+    check(LIB.b2_keyswitch(h, l, c2.data_ptr(), kp.ctypes.data, beta, ct.data_ptr(), ws.data_ptr(), nb, stream()))
+    assert hashes(ct, N) == case["hashes"]["keyswitch"]
