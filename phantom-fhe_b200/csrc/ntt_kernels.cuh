@@ -458,7 +458,7 @@ __device__ __forceinline__ u64x4 ld256_cs(const uint64_t *p) {  // streaming: th
 }
 
 template <int LOG_T, int R, int LOG_C>
-__global__ void __launch_bounds__((1 << (LOG_C + LOG_T)) >> R) ntt_fwd_rows_mac(NttArgs a, MacArgs m) {
+__global__ void __launch_bounds__((1 << (LOG_C + LOG_T)) >> R) ntt_fwd_rows_mac(NttArgs a, const __grid_constant__ MacArgs m) {
     using A = ArithFp;
     static_assert(2 * R == LOG_T, "equal stage groups: one register group per thread in both");
     constexpr int TT = 1 << LOG_T, E = 1 << R, C = 1 << LOG_C;
