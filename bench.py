@@ -162,7 +162,7 @@ def cpu_baseline_sample(budget_s=12.0):
 def kernel_alg_bytes_per_keyswitch():
     l, a, b, lP = LEVEL, SPECIAL, BETA, LEVEL + SPECIAL
     up_ntt = b * lP - l
-    return {
+    alg = {
         "ntt_inv_cluster": 2 * (l + 2 * a) * LIMB_BYTES,
         "ntt_fwd_cluster": 2 * (up_ntt + 2 * l) * LIMB_BYTES,
         "ntt_inv_rows": (l + 2 * a) * LIMB_BYTES,
@@ -172,6 +172,15 @@ def kernel_alg_bytes_per_keyswitch():
         "bconv": ((l + l + b * lP) + (2 * a + 2 * l)) * LIMB_BYTES,
         "ks_inner_prod": (b * lP + 2 * b * lP + 2 * lP) * LIMB_BYTES,
     }
+    if os.environ.get("B2_KS_FUSED_IP", "1")[:1] != "0":
+        # the Q limbs on FP64 primes (all but the leading 60-bit one) take their inner product inside ModUp's last pass:
+        # per such limb (b - 1) unfinished digits + the input's own limb + 2 b key limbs + read and write of both ct limbs
+        wide = sum(1 for x in BITS[:l] if x > 41)
+        nf, rest = l - wide, wide + a
+        alg["ntt_fwd_rows"] = (b * rest - wide + 2 * l) * LIMB_BYTES
+        alg["ks_inner_prod"] = (b * rest + 2 * b * rest + 2 * rest) * LIMB_BYTES
+        alg["ntt_fwd_rows_mac"] = ((b - 1) * nf + nf + 2 * b * nf + 4 * nf) * LIMB_BYTES
+    return alg
 
 
 def ntt_section(ph, ctx, torch, LIB, check, N, n_limbs, reps=20):
