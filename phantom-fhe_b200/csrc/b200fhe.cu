@@ -1512,13 +1512,16 @@ static int ks_tail_fused(b2_ctx *c, size_t l, const uint64_t *digits, const uint
     return run_fwd(c, delta, delta, pl.jobs_dnf_ntt, (uint32_t)(2 * l), 0, EpiSubFrom{ct}, s);
 }
 
-// ws layout of the key switch: t [l] | up [beta][lP] | cxP [2][alpha]; delta reuses `up`
-static int keyswitch_impl(b2_ctx *c, size_t l, const uint64_t *c2, const uint64_t *const *evk, size_t n_evk, uint64_t *ct, uint64_t *ws,
-                          cudaStream_t s) {
+// ModUp and inner product of the fused key switch with the FP64 limbs' inner product inside the last forward pass.
+// Applies at N = 2^16 when the level's Q limbs are FP64 primes behind a prefix of wide ones; *done tells whether it ran.
+// ct [2][l][N] += (inner product) * P^-1 on the Q limbs; cxP [2][alpha][N] = (acc_p: +=) the P limbs of the inner product.
+static int modup_inner_fused(b2_ctx *c, size_t l, const uint64_t *c2, const uint64_t *const *evk, size_t n_evk, uint64_t *ct, uint64_t *cxP,
+                             uint64_t *t, uint64_t *up, bool acc_p, cudaStream_t s, bool *done) {
     const size_t N = c->N, lP = l + c->size_P, beta = c->plan[l].beta;
-    uint64_t *t = ws, *up = t + l * N, *cxP = up + beta * lP * N;
     const LevelPlan &pl = c->plan[l];
-    if (c->use_mac && pl.mac_ok && n_evk >= beta && aligned32(c2) && aligned32(ct) && aligned32(up)) {
+    *done = false;
+    if (!(c->use_mac && pl.mac_ok && n_evk >= beta && aligned32(c2) && aligned32(ct) && aligned32(up))) return B2_OK;
+    {
         // ModUp up to the column pass for every limb; the row pass is stored only for the limbs the stand-alone inner
         // product still handles (wide Q primes and P); for the FP64 limbs of Q it runs inside ntt_fwd_rows_mac
         using Cfg = PassCfg<8>;
@@ -1542,7 +1545,7 @@ static int keyswitch_impl(b2_ctx *c, size_t l, const uint64_t *c2, const uint64_
             LAUNCH_CHECK("ntt_fwd_pass");
         }
         const uint4 rest = make_uint4(0, pl.n_wideQ, 0, (uint32_t)c->size_P);
-        rc = inner_prod_impl(c, l, up, c2, evk, n_evk, cxP, ct, true, s, &rest);
+        rc = inner_prod_impl(c, l, up, c2, evk, n_evk, cxP, ct, true, s, &rest, acc_p);
         if (rc) return rc;
         {
             MacArgs m{};
@@ -1560,6 +1563,21 @@ static int keyswitch_impl(b2_ctx *c, size_t l, const uint64_t *c2, const uint64_
                 <<<(uint32_t)(l - pl.n_wideQ) * (uint32_t)(N >> (8 + Cfg::LOG_C)), pass_threads<8>(), 0, s>>>(a, m);
             LAUNCH_CHECK("ntt_fwd_rows_mac");
         }
+    }
+    *done = true;
+    return B2_OK;
+}
+
+// ws layout of the key switch: t [l] | up [beta][lP] | cxP [2][alpha]; delta reuses `up`
+static int keyswitch_impl(b2_ctx *c, size_t l, const uint64_t *c2, const uint64_t *const *evk, size_t n_evk, uint64_t *ct, uint64_t *ws,
+                          cudaStream_t s) {
+    const size_t N = c->N, lP = l + c->size_P, beta = c->plan[l].beta;
+    uint64_t *t = ws, *up = t + l * N, *cxP = up + beta * lP * N;
+    const LevelPlan &pl = c->plan[l];
+    bool done = false;
+    int rc = modup_inner_fused(c, l, c2, evk, n_evk, ct, cxP, t, up, false, s, &done);
+    if (rc) return rc;
+    if (done) {
         const size_t ap = c->size_P;
         rc = run_inv(c, cxP, cxP, pl.jobs_dnf_intt, (uint32_t)(2 * ap), 0, c->d_fin_P, s);
         if (rc) return rc;
@@ -1567,7 +1585,7 @@ static int keyswitch_impl(b2_ctx *c, size_t l, const uint64_t *c2, const uint64_
         if (rc) return rc;
         return run_fwd(c, up, up, pl.jobs_dnf_ntt, (uint32_t)(2 * l), 0, EpiSubFrom{ct}, s);
     }
-    int rc = modup_impl(c, l, c2, up, t, false, s);  // the inner product reads the own limbs from c2
+    rc = modup_impl(c, l, c2, up, t, false, s);  // the inner product reads the own limbs from c2
     if (rc) return rc;
     return ks_tail_fused(c, l, up, c2, evk, n_evk, ct, cxP, up, s);
 }
@@ -1859,10 +1877,13 @@ extern "C" int b2_apply_galois_accumulate(b2_ctx *c, size_t l, uint32_t elt, con
             if (rc) return rc;
         }
     }
-    rc = modup_impl(c, l, p + S, up, t, false, s);
-    if (rc) return rc;
     (void)beta;
     (void)lP;
+    bool done = false;
+    rc = modup_inner_fused(c, l, p + S, ksk, n_evk, d_acc, d_accP, t, up, !first, s, &done);
+    if (rc || done) return rc;
+    rc = modup_impl(c, l, p + S, up, t, false, s);
+    if (rc) return rc;
     return inner_prod_impl(c, l, up, p + S, ksk, n_evk, d_accP, d_acc, true, s, nullptr, !first);
 }
 
