@@ -256,6 +256,11 @@ int b2_shard_keyswitch_phase(b2_ctx *ctx, size_t size_Ql, int phase, const uint6
  * events on its own stream; stop synchronises the device and returns, per kernel name (names
  * joined by ';'), the summed duration in ms and the number of launches. */
 uint64_t b2_launch_count(void);
+/* b2_device_status: synchronises the context's device and returns in *status the status word its kernels
+ * set (0: nothing happened; bit 0: a bounded wait inside a kernel - the tensor-core base conversion waiting
+ * for its MMA - ran out and that tile's outputs were not written). No counterpart in the reference, whose
+ * kernels have no device-side wait. */
+int b2_device_status(b2_ctx *ctx, uint32_t *status);
 int b2_profile_start(b2_ctx *ctx);
 int b2_profile_stop(b2_ctx *ctx, char *names, size_t names_cap, float *total_ms, uint32_t *launches,
                     size_t cap, size_t *n_out);

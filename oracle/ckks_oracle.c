@@ -637,6 +637,16 @@ void ora_expand_single_chain(const ora_ctx *c, size_t size_Ql, const int64_t *co
     }
 }
 
+/* Fixes the number of OpenMP threads the oracle uses from now on, whatever OMP_NUM_THREADS said when the
+ * library was loaded (launchers such as torchrun export OMP_NUM_THREADS=1). n < 1 leaves it unchanged. */
+void ora_set_threads(int n) {
+#ifdef _OPENMP
+    if (n >= 1) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+
 int ora_num_threads(void) {
 #ifdef _OPENMP
     return omp_get_max_threads();

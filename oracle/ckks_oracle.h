@@ -122,6 +122,7 @@ void ora_mul(const ora_ctx *c, size_t n_limbs, const uint64_t *a, const uint64_t
 
 /* number of OpenMP threads the oracle will use */
 int ora_num_threads(void);
+void ora_set_threads(int n);
 
 #ifdef __cplusplus
 }

@@ -18,6 +18,7 @@
 
 #include "../../include/b200fhe.h"
 #include "ntt_kernels.cuh"
+#include "bconv_tc.cuh"
 
 using namespace b2;
 typedef unsigned __int128 u128_t;
@@ -162,6 +163,14 @@ struct BconvGroup {
     uint32_t in_pieces;      // 21-bit pieces needed to hold an input residue (2 below 2^42, else 3)
 };
 
+// One base conversion launch in tensor-core form: job list (grid.y), the groups and byte images they index
+struct TcSet {
+    const TcJob *jobs = nullptr;
+    const TcGroup *groups = nullptr;
+    const uint8_t *images = nullptr;
+    uint32_t n_jobs = 0, jobs_per_poly = 0, max_alloc = 32;
+};
+
 struct LevelPlan {
     uint32_t l = 0, beta = 0;
     // offsets into the level blob (device), counts
@@ -190,6 +199,8 @@ struct LevelPlan {
     BconvGroup *grp_rs = nullptr;  // 3
     uint2 *outs_rs = nullptr;      // l-1
     void *blob = nullptr;
+    TcSet tc_up, tc_dn, tc_dnf;    // tensor-core form of the ModUp / ModDown / fused-ModDown conversions
+    void *tc_blob = nullptr;
 };
 
 struct b2_ctx {
@@ -216,6 +227,11 @@ struct b2_ctx {
     };
     RedcMeta *d_redc = nullptr;    // [size_QP]
     bool bconv_fp = false;         // every digit satisfies sum(q_i) < 2^64 and alpha <= 8
+    bool bconv_tc = false;         // base conversions on the tensor cores (alpha <= 8, primes above 2^16; off with B2_BCONV=fp|int)
+    bool bconv_int = false;        // B2_BCONV=int: force the 128-bit integer kernel
+    int tc_wg = 2;                 // warpgroups per CTA of the tensor-core conversion (B2_BCONV_WG = 1, 2, 4)
+    uint32_t *d_err = nullptr;     // device status word: set by a kernel whose bounded wait ran out
+    std::vector<uint64_t> h_mat_dn, h_mat_dn_pinv;  // host copies of the ModDown matrices [size_Q][size_P]
     bool use_cluster = false;      // N = 2^16: single-launch transforms on 8-CTA clusters
     bool use_pipe = false;         // N = 2^16: persistent passes with asynchronous double-buffered tile loads
     bool use_mac = false;          // N = 2^16: ModUp's last forward pass carries the inner product (off with B2_KS_FUSED_IP=0)
@@ -230,6 +246,8 @@ struct b2_ctx {
         uint64_t *mat_up = nullptr, *mat_dn = nullptr;
         double *matd_up = nullptr, *matd_dn = nullptr;
         void *blob = nullptr;
+        TcSet tc_up, tc_dn;
+        void *tc_blob = nullptr;
     };
     std::vector<ShardPlan> shard;  // index l; empty until b2_ctx_set_shard
     std::vector<LevelPlan> plan;   // index l (1..size_Q)
@@ -291,6 +309,28 @@ static inline void h_pieces(uint64_t m, uint64_t p, double *out3) {
     out3[2] = (double)(v >> 42);
 }
 static inline uint32_t h_npieces(uint64_t q) { return q < (1ull << 42) ? 2u : 3u; }
+
+// uploads what a TcBuild holds as one blob and points the sets' job lists (given as [first job, count) ranges) into it
+static int tc_upload(const TcBuild &b, void **blob, std::initializer_list<std::pair<TcSet *, std::pair<uint32_t, uint32_t>>> sets) {
+    const size_t jb = (b.jobs.size() * sizeof(TcJob) + 255) & ~size_t(255), gb = (b.groups.size() * sizeof(TcGroup) + 255) & ~size_t(255);
+    const size_t total = jb + gb + b.images.size() + 256;
+    if (cudaMalloc(blob, total) != cudaSuccess) return fail(B2_ENOMEM, "cudaMalloc(tensor-core conversion plan) failed");
+    char *base = (char *)*blob;
+    cudaError_t e = cudaMemcpy(base, b.jobs.data(), b.jobs.size() * sizeof(TcJob), cudaMemcpyHostToDevice);
+    if (e == cudaSuccess) e = cudaMemcpy(base + jb, b.groups.data(), b.groups.size() * sizeof(TcGroup), cudaMemcpyHostToDevice);
+    if (e == cudaSuccess) e = cudaMemcpy(base + jb + gb, b.images.data(), b.images.size(), cudaMemcpyHostToDevice);
+    if (e != cudaSuccess) return fail((int)e, "cudaMemcpy(tensor-core conversion plan) failed");
+    for (auto &s : sets) {
+        TcSet *ts = s.first;
+        ts->jobs = (const TcJob *)base + s.second.first;
+        ts->n_jobs = s.second.second;
+        ts->groups = (const TcGroup *)(base + jb);
+        ts->images = (const uint8_t *)(base + jb + gb);
+        ts->max_alloc = 32;
+        for (uint32_t j = 0; j < s.second.second; j++) ts->max_alloc = std::max(ts->max_alloc, b.jobs[s.second.first + j].alloc_cols);
+    }
+    return B2_OK;
+}
 
 static int build_level(b2_ctx *c, size_t l) {
     const size_t N = c->N, alpha = c->size_P, sQ = c->size_Q;
@@ -427,6 +467,37 @@ static int build_level(b2_ctx *c, size_t l) {
     pl.outs_dn = (uint2 *)dev(outs_dn);
     pl.grp_rs = (BconvGroup *)dev(grp_rs);
     pl.outs_rs = (uint2 *)dev(outs_rs);
+    if (c->bconv_tc) {
+        // the same conversions as tensor-core jobs: ModUp digits, then ModDown of up to two polynomials with the plain
+        // matrix (cx layout [2][lP]) and with the P^-1-carrying one (compact P limbs [2][alpha])
+        TcBuild tb;
+        std::vector<TcSpecOut> outs;
+        uint32_t n_up = 0, n_dn = 0, n_dnf = 0;
+        for (size_t d = 0; d < beta; d++) {
+            const BconvGroup &g = grp_up[d];
+            outs.clear();
+            for (uint32_t j = 0; j < g.n_out; j++) {
+                const uint2 o = outs_up[g.out_begin + j];
+                outs.push_back(TcSpecOut{g.out_slot_base + o.x, c->q[o.y], mat_up + g.mat_off + (size_t)j * g.ni});
+            }
+            n_up += tb.add(g.in_slot0, g.ni, g.copy_dst_slot0, outs);
+        }
+        uint32_t per_poly = 0;
+        for (int fused = 0; fused < 2; fused++)
+            for (size_t k = 0; k < 2; k++) {
+                const BconvGroup &g = fused ? grp_dnf[k] : grp_dn[k];
+                const std::vector<uint64_t> &m = fused ? c->h_mat_dn_pinv : c->h_mat_dn;
+                outs.clear();
+                for (size_t j = 0; j < l; j++) outs.push_back(TcSpecOut{g.out_slot_base + (uint32_t)j, c->q[j], m.data() + j * alpha});
+                per_poly = tb.add(g.in_slot0, g.ni, 0xFFFFFFFFu, outs);
+                (fused ? n_dnf : n_dn) += per_poly;
+            }
+        if (!tb.ok) return fail(B2_EINVAL, "tensor-core base conversion: unsupported prime in the chain");
+        int rc = tc_upload(tb, &pl.tc_blob, {{&pl.tc_up, {0u, n_up}}, {&pl.tc_dn, {n_up, n_dn}}, {&pl.tc_dnf, {n_up + n_dn, n_dnf}}});
+        if (rc) return rc;
+        pl.tc_up.jobs_per_poly = n_up;
+        pl.tc_dn.jobs_per_poly = pl.tc_dnf.jobs_per_poly = per_poly;
+    }
     return B2_OK;
 }
 
@@ -446,8 +517,15 @@ extern "C" void b2_ctx_destroy(b2_ctx *c) {
     cudaFree(c->d_matd_dn_pinv);
     cudaFree(c->d_matd_one);
     cudaFree(c->d_redc);
-    for (auto &pl : c->plan) cudaFree(pl.blob);
-    for (auto &sp : c->shard) cudaFree(sp.blob);
+    for (auto &pl : c->plan) {
+        cudaFree(pl.blob);
+        cudaFree(pl.tc_blob);
+    }
+    cudaFree(c->d_err);
+    for (auto &sp : c->shard) {
+        cudaFree(sp.blob);
+        cudaFree(sp.tc_blob);
+    }
     for (auto &kv : c->galois) cudaFree(kv.second);
     delete c;
 }
@@ -610,6 +688,34 @@ extern "C" int b2_ctx_create(size_t N, const uint64_t *primes, size_t size_QP, s
     // B2_NTT_CLUSTER=1 selects the single-launch cluster transforms at N = 2^16. They are bit-exact
     // but measured slower than the two-launch transforms on B200 (register pressure, two CTAs per
     // SM), so they stay opt-in.
+    c->h_mat_dn = mat_dn;
+    c->h_mat_dn_pinv = mat_dn_pinv;
+    {
+        // B2_BCONV selects the base-conversion kernel: "tc" (default: tensor cores), "fp" (FP64 pieces), "int" (128-bit integers)
+        const char *env_bc = getenv("B2_BCONV");
+        const std::string bc = env_bc ? env_bc : "tc";
+        bool tc_ok = sP <= 8;
+        for (size_t i = 0; i < size_QP; i++) tc_ok = tc_ok && c->q[i] > (1ull << 16);
+        c->bconv_tc = tc_ok && bc == "tc";
+        c->bconv_int = bc == "int";
+        const char *env_wg = getenv("B2_BCONV_WG");
+        c->tc_wg = env_wg ? atoi(env_wg) : 2;
+        if (c->tc_wg != 1 && c->tc_wg != 2 && c->tc_wg != 4) c->tc_wg = 2;
+        if (cudaMalloc((void **)&c->d_err, 4) != cudaSuccess || cudaMemset(c->d_err, 0, 4) != cudaSuccess) {
+            b2_ctx_destroy(c);
+            return fail(B2_ENOMEM, "ctx_create: cudaMalloc(status word) failed");
+        }
+        if (c->bconv_tc) {
+            // per device: the conversion asks for more dynamic shared memory than it uses (see tc_smem_request)
+            cudaError_t ea = cudaFuncSetAttribute(bconv_tc_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TC_SMEM_MAX_REQUEST);
+            if (ea == cudaSuccess) ea = cudaFuncSetAttribute(bconv_tc_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TC_SMEM_MAX_REQUEST);
+            if (ea == cudaSuccess) ea = cudaFuncSetAttribute(bconv_tc_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TC_SMEM_MAX_REQUEST);
+            if (ea != cudaSuccess) {
+                b2_ctx_destroy(c);
+                return fail((int)ea, std::string("ctx_create: cudaFuncSetAttribute(bconv_tc_kernel): ") + cudaGetErrorString(ea));
+            }
+        }
+    }
     const char *env_cl = getenv("B2_NTT_CLUSTER");
     c->use_cluster = (c->logN == 16) && env_cl && env_cl[0] == '1';
     const char *env_pipe = getenv("B2_NTT_PIPE");
@@ -1347,13 +1453,41 @@ __global__ void __launch_bounds__(256) bsgs_mac_multi_kernel(const uint64_t *con
     }
 }
 
+// Shared memory a conversion CTA asks for: what it uses, or enough that no more CTAs fit on an SM (228 KB) than its
+// 512 TMEM columns can serve, whichever is larger - so tcgen05.alloc finds its columns free and never waits.
+static uint32_t tc_smem_request(uint32_t alloc_cols) {
+    const uint32_t fit = 512 / alloc_cols;
+    return std::max(TC_SMEM_BYTES, TC_SM_SMEM / (fit + 1));
+}
+
+// n_jobs: how many of the set's jobs to run (ModDown of one polynomial runs the first half)
+static int run_bconv_tc(const b2_ctx *c, bool copy, const uint64_t *in, uint64_t *out, const uint64_t *copy_src, const TcSet &tc, uint32_t n_jobs,
+                        cudaStream_t s) {
+    const uint32_t N = (uint32_t)c->N;
+    if (n_jobs == 0) return B2_OK;
+    if (copy && !copy_src) return fail(B2_EINVAL, "base conversion: missing copy source");
+    LaunchScope ls(c, s, "bconv");
+    // without the copy the jobs' copy slots are ignored by handing the kernel a null source
+    const uint64_t *cs = copy ? copy_src : nullptr;
+    const dim3 grid(N / 128, n_jobs);
+    const uint32_t smem = tc_smem_request(tc.max_alloc);
+    switch (c->tc_wg) {
+        case 1: bconv_tc_kernel<1><<<grid, 128, smem, s>>>(in, out, cs, tc.jobs, tc.groups, tc.images, N, c->d_err); break;
+        case 4: bconv_tc_kernel<4><<<grid, 512, smem, s>>>(in, out, cs, tc.jobs, tc.groups, tc.images, N, c->d_err); break;
+        default: bconv_tc_kernel<2><<<grid, 256, smem, s>>>(in, out, cs, tc.jobs, tc.groups, tc.images, N, c->d_err); break;
+    }
+    LAUNCH_CHECK("bconv_tc_kernel");
+    return B2_OK;
+}
+
 static int run_bconv(const b2_ctx *c, bool copy, const uint64_t *in, uint64_t *out, const uint64_t *copy_src, const BconvGroup *groups,
                      uint32_t n_groups, const uint2 *outs, const uint64_t *mats, const double *matd, uint32_t max_ni, uint32_t max_out,
-                     bool in3, cudaStream_t s) {
+                     bool in3, cudaStream_t s, const TcSet *tc = nullptr, uint32_t tc_jobs = 0) {
     const uint32_t N = (uint32_t)c->N;
     if (max_ni > 16) return fail(B2_ESIZE, "special_modulus_size above 16 is not built");
+    if (c->bconv_tc && tc && tc->jobs) return run_bconv_tc(c, copy, in, out, copy_src, *tc, tc_jobs ? tc_jobs : tc->n_jobs, s);
     LaunchScope ls(c, s, "bconv");
-    if (c->bconv_fp && matd) {
+    if (c->bconv_fp && matd && !c->bconv_int) {
         dim3 grid(N / 128, n_groups);
         const size_t smem = (size_t)max_out * sizeof(BconvMetaS) + (size_t)max_out * 24 * 8;
         (void)in3;
@@ -1418,7 +1552,7 @@ static int modup_impl(b2_ctx *c, size_t l, const uint64_t *c2, uint64_t *out, ui
     const LevelPlan &pl = c->plan[l];
     int rc = run_inv(c, c2, t, pl.jobs_up_intt, (uint32_t)l, 0, pl.fin_up, s);
     if (rc) return rc;
-    rc = run_bconv(c, copy_own, t, out, c2, pl.grp_up, pl.beta, pl.outs_up, pl.mat_up, pl.matd_up, (uint32_t)c->size_P, (uint32_t)(l + c->size_P), true, s);
+    rc = run_bconv(c, copy_own, t, out, c2, pl.grp_up, pl.beta, pl.outs_up, pl.mat_up, pl.matd_up, (uint32_t)c->size_P, (uint32_t)(l + c->size_P), true, s, &pl.tc_up);
     if (rc) return rc;
     return run_fwd(c, out, out, pl.jobs_up_ntt, pl.n_up_ntt, 0, EpiStore{}, s);
 }
@@ -1476,7 +1610,8 @@ static int moddown_impl(b2_ctx *c, size_t l, size_t n_poly, uint64_t *cx, uint64
     const size_t a = c->size_P;
     int rc = run_inv(c, cx, cx, pl.jobs_dn_intt, (uint32_t)(n_poly * a), 0, c->d_fin_P, s);
     if (rc) return rc;
-    rc = run_bconv(c, false, cx, delta, nullptr, pl.grp_dn, (uint32_t)n_poly, pl.outs_dn, c->d_mat_dn, c->d_matd_dn, (uint32_t)a, (uint32_t)l, true, s);
+    rc = run_bconv(c, false, cx, delta, nullptr, pl.grp_dn, (uint32_t)n_poly, pl.outs_dn, c->d_mat_dn, c->d_matd_dn, (uint32_t)a, (uint32_t)l, true, s, &pl.tc_dn,
+                   (uint32_t)n_poly * pl.tc_dn.jobs_per_poly);
     if (rc) return rc;
     if (accum) {
         EpiSubMul<true> epi{cx, out, c->d_Pinv};
@@ -1507,7 +1642,7 @@ static int ks_tail_fused(b2_ctx *c, size_t l, const uint64_t *digits, const uint
     if (rc) return rc;
     rc = run_inv(c, cxP, cxP, pl.jobs_dnf_intt, (uint32_t)(2 * a), 0, c->d_fin_P, s);
     if (rc) return rc;
-    rc = run_bconv(c, false, cxP, delta, nullptr, pl.grp_dnf, 2, pl.outs_dn, c->d_mat_dn_pinv, c->d_matd_dn_pinv, (uint32_t)a, (uint32_t)l, true, s);
+    rc = run_bconv(c, false, cxP, delta, nullptr, pl.grp_dnf, 2, pl.outs_dn, c->d_mat_dn_pinv, c->d_matd_dn_pinv, (uint32_t)a, (uint32_t)l, true, s, &pl.tc_dnf);
     if (rc) return rc;
     return run_fwd(c, delta, delta, pl.jobs_dnf_ntt, (uint32_t)(2 * l), 0, EpiSubFrom{ct}, s);
 }
@@ -1527,7 +1662,7 @@ static int modup_inner_fused(b2_ctx *c, size_t l, const uint64_t *c2, const uint
         using Cfg = PassCfg<8>;
         int rc = run_inv(c, c2, t, pl.jobs_up_intt, (uint32_t)l, 0, pl.fin_up, s);
         if (rc) return rc;
-        rc = run_bconv(c, false, t, up, c2, pl.grp_up, pl.beta, pl.outs_up, pl.mat_up, pl.matd_up, (uint32_t)c->size_P, (uint32_t)lP, true, s);
+        rc = run_bconv(c, false, t, up, c2, pl.grp_up, pl.beta, pl.outs_up, pl.mat_up, pl.matd_up, (uint32_t)c->size_P, (uint32_t)lP, true, s, &pl.tc_up);
         if (rc) return rc;
         NttArgs a{up, up, pl.jobs_up_ntt, 0, (uint32_t)c->logN, c->d_tw, c->d_mod, nullptr, 0};
         {
@@ -1581,7 +1716,7 @@ static int keyswitch_impl(b2_ctx *c, size_t l, const uint64_t *c2, const uint64_
         const size_t ap = c->size_P;
         rc = run_inv(c, cxP, cxP, pl.jobs_dnf_intt, (uint32_t)(2 * ap), 0, c->d_fin_P, s);
         if (rc) return rc;
-        rc = run_bconv(c, false, cxP, up, nullptr, pl.grp_dnf, 2, pl.outs_dn, c->d_mat_dn_pinv, c->d_matd_dn_pinv, (uint32_t)ap, (uint32_t)l, true, s);
+        rc = run_bconv(c, false, cxP, up, nullptr, pl.grp_dnf, 2, pl.outs_dn, c->d_mat_dn_pinv, c->d_matd_dn_pinv, (uint32_t)ap, (uint32_t)l, true, s, &pl.tc_dnf);
         if (rc) return rc;
         return run_fwd(c, up, up, pl.jobs_dnf_ntt, (uint32_t)(2 * l), 0, EpiSubFrom{ct}, s);
     }
@@ -1898,7 +2033,7 @@ extern "C" int b2_keyswitch_finish(b2_ctx *c, size_t l, uint64_t *d_accP, uint64
     uint64_t *delta = (uint64_t *)d_ws;
     int rc = run_inv(c, d_accP, d_accP, pl.jobs_dnf_intt, (uint32_t)(2 * a), 0, c->d_fin_P, s);
     if (rc) return rc;
-    rc = run_bconv(c, false, d_accP, delta, nullptr, pl.grp_dnf, 2, pl.outs_dn, c->d_mat_dn_pinv, c->d_matd_dn_pinv, (uint32_t)a, (uint32_t)l, true, s);
+    rc = run_bconv(c, false, d_accP, delta, nullptr, pl.grp_dnf, 2, pl.outs_dn, c->d_mat_dn_pinv, c->d_matd_dn_pinv, (uint32_t)a, (uint32_t)l, true, s, &pl.tc_dnf);
     if (rc) return rc;
     return run_fwd(c, delta, delta, pl.jobs_dnf_ntt, (uint32_t)(2 * l), 0, EpiSubFrom{d_acc}, s);
 }
@@ -1967,7 +2102,7 @@ extern "C" int b2_hoisting_sum(b2_ctx *c, size_t l, const uint64_t *d_ct, const 
     }
     rc = run_inv(c, accP, accP, pl.jobs_dnf_intt, (uint32_t)(2 * a), 0, c->d_fin_P, s);
     if (rc) return rc;
-    rc = run_bconv(c, false, accP, delta, nullptr, pl.grp_dnf, 2, pl.outs_dn, c->d_mat_dn_pinv, c->d_matd_dn_pinv, (uint32_t)a, (uint32_t)l, true, s);
+    rc = run_bconv(c, false, accP, delta, nullptr, pl.grp_dnf, 2, pl.outs_dn, c->d_mat_dn_pinv, c->d_matd_dn_pinv, (uint32_t)a, (uint32_t)l, true, s, &pl.tc_dnf);
     if (rc) return rc;
     return run_fwd(c, delta, delta, pl.jobs_dnf_ntt, (uint32_t)(2 * l), 0, EpiSubFrom{d_out}, s);
 }
@@ -2121,6 +2256,14 @@ extern "C" int b2_ct_lincomb(b2_ctx *c, size_t l, size_t n_poly, size_t n_terms,
 // ------------------------------------------------------------------------------------------------
 // per-kernel timing for the benchmark
 // ------------------------------------------------------------------------------------------------
+extern "C" int b2_device_status(b2_ctx *c, uint32_t *status) {
+    CHECK_CTX(c);
+    if (!status) return fail(B2_EINVAL, "device_status: null pointer");
+    CUDA_TRY(cudaDeviceSynchronize());
+    CUDA_TRY(cudaMemcpy(status, c->d_err, 4, cudaMemcpyDeviceToHost));
+    return B2_OK;
+}
+
 extern "C" int b2_profile_start(b2_ctx *c) {
     CHECK_CTX(c);
     for (auto &r : c->prof) {
@@ -2271,6 +2414,32 @@ static int build_shard_level(b2_ctx *c, size_t l) {
     sp.mat_dn = (uint64_t *)dptr[8];
     sp.matd_up = (double *)dptr[9];
     sp.matd_dn = (double *)dptr[10];
+    if (c->bconv_tc) {
+        // tensor-core jobs over the rank's outputs (a rank may own no output of a digit, or no Q limb at all)
+        TcBuild tb;
+        std::vector<TcSpecOut> outs;
+        uint32_t n_up = 0, n_dn = 0;
+        for (size_t d = 0; d < beta; d++) {
+            const BconvGroup &g = grp_up[d];
+            if (g.n_out == 0) continue;
+            outs.clear();
+            for (uint32_t j = 0; j < g.n_out; j++) {
+                const uint2 o = outs_up[g.out_begin + j];
+                outs.push_back(TcSpecOut{g.out_slot_base + o.x, c->q[o.y], mat_up.data() + g.mat_off + (size_t)j * g.ni});
+            }
+            n_up += tb.add(g.in_slot0, g.ni, 0xFFFFFFFFu, outs);
+        }
+        for (size_t k = 0; k < 2 && sp.nq; k++) {
+            outs.clear();
+            for (uint32_t j = 0; j < sp.nq; j++) outs.push_back(TcSpecOut{(uint32_t)(k * l) + sp.q0 + j, c->q[sp.q0 + j], mat_dn.data() + (size_t)j * alpha});
+            n_dn += tb.add((uint32_t)(k * alpha), (uint32_t)alpha, 0xFFFFFFFFu, outs);
+        }
+        if (!tb.ok) return fail(B2_EINVAL, "tensor-core base conversion: unsupported prime in the chain");
+        if (n_up + n_dn) {
+            int rc = tc_upload(tb, &sp.tc_blob, {{&sp.tc_up, {0u, n_up}}, {&sp.tc_dn, {n_up, n_dn}}});
+            if (rc) return rc;
+        }
+    }
     return B2_OK;
 }
 
@@ -2278,7 +2447,10 @@ extern "C" int b2_ctx_set_shard(b2_ctx *c, int rank, int world) {
     CHECK_CTX(c);
     if (world < 1 || rank < 0 || rank >= world) return fail(B2_EINVAL, "set_shard: rank must be in [0, world)");
     CUDA_TRY(cudaDeviceSynchronize());
-    for (auto &sp : c->shard) cudaFree(sp.blob);
+    for (auto &sp : c->shard) {
+        cudaFree(sp.blob);
+        cudaFree(sp.tc_blob);
+    }
     c->shard.clear();
     c->shard_rank = rank;
     c->shard_world = world;
@@ -2318,7 +2490,7 @@ extern "C" int b2_shard_keyswitch_phase(b2_ctx *c, size_t l, int phase, const ui
         case 0:
             return run_inv(c, d_c2, t, pl.jobs_up_intt + sp.q0, sp.nq, 0, pl.fin_up, s);
         case 1: {
-            rc = run_bconv(c, false, t, up, d_c2, sp.grp_up, (uint32_t)beta, sp.outs_up, sp.mat_up, sp.matd_up, (uint32_t)a, (uint32_t)lP, true, s);
+            rc = run_bconv(c, false, t, up, d_c2, sp.grp_up, (uint32_t)beta, sp.outs_up, sp.mat_up, sp.matd_up, (uint32_t)a, (uint32_t)lP, true, s, &sp.tc_up);
             if (rc) return rc;
             rc = run_fwd(c, up, up, sp.jobs_up_ntt, sp.n_up_ntt, 0, EpiStore{}, s);
             if (rc) return rc;
@@ -2329,7 +2501,7 @@ extern "C" int b2_shard_keyswitch_phase(b2_ctx *c, size_t l, int phase, const ui
         }
         case 2:
             if (sp.nq == 0) return B2_OK;
-            rc = run_bconv(c, false, cxP, up, nullptr, sp.grp_dn, 2, sp.outs_dn, sp.mat_dn, sp.matd_dn, (uint32_t)a, (uint32_t)l, true, s);
+            rc = run_bconv(c, false, cxP, up, nullptr, sp.grp_dn, 2, sp.outs_dn, sp.mat_dn, sp.matd_dn, (uint32_t)a, (uint32_t)l, true, s, &sp.tc_dn);
             if (rc) return rc;
             return run_fwd(c, up, up, sp.jobs_dn_ntt, 2 * sp.nq, 0, EpiSubFrom{d_ct}, s);
         default:

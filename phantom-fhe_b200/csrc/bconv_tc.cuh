@@ -1,0 +1,175 @@
+// bconv_tc.cuh - fast base conversion on the sm_100a tensor cores (tcgen05.mma kind::i8, accumulators in TMEM).
+// The formulation, the data structures and the host-side planning are in bconv_tc_plan.h.
+//
+// CTA = 128 coefficients (M = 128: TMEM lane = coefficient) x one job. The threads put the tile's input limbs into
+// shared memory as the rows of A (the raw 8 bytes of each residue) and copy the job's ready-made B image next to it;
+// one thread issues two MMAs (K = 2 x 32, N = 16 * groups <= 256) and commits them to an mbarrier; every warp then
+// reads its 32 TMEM lanes (tcgen05.ld 32x32b: one coefficient per thread, 16 columns = one output group at a time),
+// reduces and stores 8-byte words that are contiguous across the warp. 128 * WG threads: warp w reads lanes
+// 32 (w % 4) .. +31 and warpgroup w / 4 takes every WG-th column group.
+// No multicast, no cluster; the only wait (MMA completion) is bounded and reports through a status word instead of
+// spinning forever; TMEM is released on every path.
+#pragma once
+#include <cstdint>
+#include <cuda_runtime.h>
+
+#include "bconv_tc_plan.h"
+
+namespace b2 {
+
+constexpr uint32_t TC_SMEM_A = 128 * 64;            // one tile of A
+constexpr uint32_t TC_SMEM_B = 256 * 64;            // largest B image
+constexpr uint32_t TC_SMEM_CTRL = TC_SMEM_A + TC_SMEM_B;
+constexpr uint32_t TC_SMEM_BYTES = TC_SMEM_CTRL + 32;
+constexpr uint32_t TC_WAIT_LIMIT = 1u << 22;        // polls of the MMA barrier before giving up
+constexpr uint32_t TC_SM_SMEM = 233472;             // shared memory of one SM (228 KB)
+constexpr uint32_t TC_SMEM_MAX_REQUEST = TC_SM_SMEM / 2;
+
+__device__ __forceinline__ uint32_t tc_smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+// shared-memory matrix descriptor: K-major, no swizzle, LBO = 128 B, SBO = 512 B, descriptor version 1 (sm_100)
+__device__ __forceinline__ uint64_t tc_desc(uint32_t smem_addr) {
+    return (uint64_t)((smem_addr & 0x3FFFFu) >> 4) | ((uint64_t)(128u >> 4) << 16) | ((uint64_t)(512u >> 4) << 32) | ((uint64_t)1 << 46);
+}
+
+__device__ __forceinline__ void tc_mma_i8(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t"
+        "}\n" ::"r"(d_tmem),
+        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+// 16 consecutive accumulator columns of this thread's TMEM lane; the wait is part of the same statement so
+// that no use of the registers can be scheduled ahead of it
+__device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t (&c)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];\n\t"
+        "tcgen05.wait::ld.sync.aligned;\n"
+        : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3]), "=r"(c[4]), "=r"(c[5]), "=r"(c[6]), "=r"(c[7]), "=r"(c[8]), "=r"(c[9]),
+          "=r"(c[10]), "=r"(c[11]), "=r"(c[12]), "=r"(c[13]), "=r"(c[14]), "=r"(c[15])
+        : "r"(taddr)
+        : "memory");
+}
+
+template <int NB>
+__device__ __forceinline__ void tc_group_outputs(const uint32_t (&c)[16], const TcGroup *g, uint32_t n_valid, uint64_t *__restrict__ out, size_t N,
+                                                 uint32_t n) {
+    constexpr int OPG = 16 / NB;
+#pragma unroll
+    for (int o = 0; o < OPG; o++) {
+        if (o < (int)n_valid) {
+            const uint4 raw = __ldg(reinterpret_cast<const uint4 *>(&g->o[o]));
+            const uint64_t p = (uint64_t)raw.x | ((uint64_t)raw.y << 32);
+            out[(size_t)raw.w * N + n] = tc_reduce<NB>(&c[o * NB], p, raw.z);
+        }
+    }
+}
+
+// grid = (N / 128, jobs); dynamic shared memory >= TC_SMEM_BYTES (the launcher asks for more, so that the CTAs
+// resident on one SM can never want more than its 512 TMEM columns and the allocation never has to wait)
+template <int WG>
+__global__ void __launch_bounds__(128 * WG) bconv_tc_kernel(const uint64_t *__restrict__ in, uint64_t *__restrict__ out,
+                                                            const uint64_t *__restrict__ copy_src, const TcJob *__restrict__ jobs,
+                                                            const TcGroup *__restrict__ groups, const uint8_t *__restrict__ images, uint32_t N,
+                                                            uint32_t *err) {
+    extern __shared__ __align__(1024) uint8_t tc_smem[];
+    uint8_t *sA = tc_smem, *sB = tc_smem + TC_SMEM_A;
+    uint64_t *bar = reinterpret_cast<uint64_t *>(tc_smem + TC_SMEM_CTRL);
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(tc_smem + TC_SMEM_CTRL + 8);
+    const TcJob job = jobs[blockIdx.y];
+    const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const uint32_t n0 = blockIdx.x * 128;
+
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tc_smem_u32(tmem_slot)), "r"(job.alloc_cols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    if (tid == 0) {
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(tc_smem_u32(bar)) : "memory");
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    // B: the ready-made byte image of this job
+    {
+        const int4 *src = reinterpret_cast<const int4 *>(images + job.img_off);
+        int4 *dst = reinterpret_cast<int4 *>(sB);
+        for (uint32_t i = tid; i < job.n_groups * 64; i += 128 * WG) dst[i] = __ldg(src + i);
+    }
+    // A: row = coefficient, the 8 bytes of input limb i at k = 8 i .. 8 i + 7 (two limbs per 16-byte store)
+    {
+        const uint32_t r = tid & 127, part = tid >> 7;
+        constexpr int PAIRS = 4 / WG;
+        const bool copy = copy_src != nullptr && job.copy_dst_slot0 != 0xFFFFFFFFu;
+#pragma unroll
+        for (int pp = 0; pp < PAIRS; pp++) {
+            const uint32_t i = 2 * (part * PAIRS + pp);
+            uint64_t v[2] = {0, 0};
+#pragma unroll
+            for (int h = 0; h < 2; h++) {
+                if (i + h < job.ni) {
+                    const size_t off = (size_t)(job.in_slot0 + i + h) * N + n0 + r;
+                    v[h] = in[off];
+                    if (copy) out[(size_t)(job.copy_dst_slot0 + i + h) * N + n0 + r] = copy_src[off];
+                }
+            }
+            *reinterpret_cast<ulonglong2 *>(sA + (r >> 3) * 512 + (i >> 1) * 128 + (r & 7) * 16) = make_ulonglong2(v[0], v[1]);
+        }
+    }
+    // generic-proxy writes of A and B become visible to the tensor core's (async-proxy) reads
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = *tmem_slot;
+    if (tid == 0) {
+        const uint64_t adesc = tc_desc(tc_smem_u32(sA)), bdesc = tc_desc(tc_smem_u32(sB));
+        // D s32, A and B u8, both K-major, N = 16 * groups, M = 128
+        const uint32_t idesc = (2u << 4) | (((16u * job.n_groups) >> 3) << 17) | ((128u >> 4) << 24);
+        tc_mma_i8(tmem, adesc, bdesc, idesc, 0u);
+        tc_mma_i8(tmem, adesc + (256u >> 4), bdesc + (256u >> 4), idesc, 1u);  // k = 32..63: two core matrices further
+        asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(tc_smem_u32(bar)) : "memory");
+    }
+    // bounded wait for the accumulators
+    uint32_t done = 0;
+    for (uint32_t it = 0; it < TC_WAIT_LIMIT && !done; it++) {
+        asm volatile(
+            "{\n\t"
+            ".reg .pred P1;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 P1, [%1], %2;\n\t"
+            "selp.b32 %0, 1, 0, P1;\n\t"
+            "}\n"
+            : "=r"(done)
+            : "r"(tc_smem_u32(bar)), "r"(0u)
+            : "memory");
+    }
+    const bool ok = __all_sync(0xFFFFFFFFu, done != 0);
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    if (ok) {
+        const uint32_t wq = warp & 3, wg = warp >> 2;
+        const uint32_t n = n0 + wq * 32 + lane;
+        const uint32_t lane_base = tmem + ((wq * 32u) << 16);
+        for (uint32_t g = wg; g < job.n_groups; g += WG) {
+            uint32_t c[16];
+            tc_ld16(lane_base + g * 16, c);
+            const TcGroup *G = groups + job.grp_off + g;
+            const uint2 hdr = __ldg(reinterpret_cast<const uint2 *>(G));
+            switch (hdr.x) {
+                case 4: tc_group_outputs<4>(c, G, hdr.y, out, N, n); break;
+                case 5: tc_group_outputs<5>(c, G, hdr.y, out, N, n); break;
+                case 6: tc_group_outputs<6>(c, G, hdr.y, out, N, n); break;
+                case 7: tc_group_outputs<7>(c, G, hdr.y, out, N, n); break;
+                default: tc_group_outputs<8>(c, G, hdr.y, out, N, n); break;
+            }
+        }
+    } else if (lane == 0) {
+        atomicExch(err, 1u);  // the MMA never signalled: outputs of this tile are not written
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(job.alloc_cols) : "memory");
+}
+
+}  // namespace b2

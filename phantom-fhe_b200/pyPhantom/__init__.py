@@ -184,6 +184,12 @@ class context:
     def beta(self, l):
         return int(LIB.b2_ctx_beta(self._h, l))
 
+    def device_status(self):
+        """Synchronises the device and returns the status word its kernels set (0 = no bounded wait ran out)."""
+        st = _native.ctypes.c_uint32(0)
+        check(LIB.b2_device_status(self._h, _native.ctypes.byref(st)))
+        return int(st.value)
+
     def workspace(self, op, l):
         nbytes = int(LIB.b2_workspace_bytes(self._h, op, l))
         return torch.empty(max(nbytes // 8, 1), dtype=torch.int64, device=self.device), nbytes

@@ -57,6 +57,7 @@ SIGNATURES = {
     "b2_shard_limbs": (_int, [_vp, _sz, _vp]),
     "b2_shard_keyswitch_phase": (_int, [_vp, _sz, _int, _vp, _vp, _sz, _vp, _vp, _sz, _vp]),
     "b2_launch_count": (_u64, []),
+    "b2_device_status": (_int, [_vp, _vp]),
     "b2_profile_start": (_int, [_vp]),
     "b2_profile_stop": (_int, [_vp, _vp, _sz, _vp, _vp, _sz, _vp]),
 }

@@ -60,6 +60,7 @@ def _load():
         "ora_sub": (None, [_vp, _sz, _vp, _vp, _vp]),
         "ora_mul": (None, [_vp, _sz, _vp, _vp, _vp]),
         "ora_num_threads": (_int, []),
+        "ora_set_threads": (None, [_int]),
     }
     for name, (res, args) in sig.items():
         fn = getattr(L, name)
@@ -68,6 +69,14 @@ def _load():
 
 
 LIB = _load()
+
+
+def use_all_cores():
+    """Pins the oracle's OpenMP thread count to the cores this process may run on (a launcher's OMP_NUM_THREADS=1 does
+    not apply to the timed CPU baseline) and returns that count."""
+    n = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    LIB.ora_set_threads(n)
+    return int(LIB.ora_num_threads())
 
 
 def _p(a):

@@ -85,7 +85,7 @@ def test_serialisation_header_layout():
 
 
 def test_numpy_generator_matches_the_golden_generator():
-    from pyPhantom import synth
+    import synth
     from oracle_lib import Oracle
     N = 4096
     pr = create_coeff_modulus(N, [60, 36, 50])

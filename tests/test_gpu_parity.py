@@ -472,3 +472,47 @@ def test_inner_product_inside_the_last_forward_pass(monkeypatch, name, fused):
     ws, nb = _ws(ctx, _native.OP_KEYSWITCH, l)
     check(LIB.b2_keyswitch(h, l, c2.data_ptr(), kp.ctypes.data, beta, ct.data_ptr(), ws.data_ptr(), nb, stream()))
     assert hashes(ct, N) == case["hashes"]["keyswitch"]
+
+
+@pytest.mark.parametrize("mode", ["tc:1", "tc:2", "tc:4", "fp", "int"])
+@pytest.mark.parametrize("shape", ["n12_ragged", "n16_headline", "n13_many_limbs"])
+def test_base_conversion_kernels_agree(mode, shape, monkeypatch):
+    """ModUp, ModDown (one and two polynomials) and the whole key switch through each base-conversion kernel - tensor
+    cores with 1, 2 and 4 warpgroups per CTA, FP64 pieces, 128-bit integers - against the oracle. The context reads the
+    selection from the environment when it is created."""
+    kind, _, wg = mode.partition(":")
+    monkeypatch.setenv("B2_BCONV", kind)
+    if wg:
+        monkeypatch.setenv("B2_BCONV_WG", wg)
+    if shape == "n12_ragged":
+        N, bits, special, levels = 4096, [55, 40, 41, 42, 43, 44, 45, 46, 58, 59, 60], 3, [1, 5, 8]
+    elif shape == "n16_headline":
+        N, bits, special, levels = 65536, [60] + [40] * 23 + [60] * 8, 8, [24, 11]
+    else:  # 50 Q limbs in digits of 5: ModDown has 100 outputs (two jobs per polynomial), ModUp digits 50
+        N, bits, special, levels = 8192, [60] + [36, 50, 44, 58, 30, 52, 40] * 7 + [60] * 5, 5, [50, 23]
+    ctx, o = make_ctx(N, bits, special)
+    for l in levels:
+        beta, lP = o.beta(l), l + o.size_P
+        c2_h, ct_h = o.fill(1, o.primes[:l], 31, 3)[0], o.synth_ct(l, 31, 1)
+        c2 = dev(c2_h)
+        up = ctx.empty(beta, lP)
+        ws, nb = _ws(ctx, _native.OP_MODUP, l)
+        check(LIB.b2_modup(ctx._h, l, c2.data_ptr(), up.data_ptr(), ws.data_ptr(), nb, stream()))
+        up_h = o.modup(l, c2_h)
+        assert np.array_equal(host(up).reshape(up_h.shape), up_h), (mode, l, "modup")
+        cx_h = o.fill(2, list(o.primes[:l]) + list(o.primes[o.size_QP - o.size_P:]), 32, 5)
+        want = np.stack([o.moddown(l, cx_h[0]), o.moddown(l, cx_h[1])])
+        ws, nb = _ws(ctx, _native.OP_MODDOWN, l)
+        dn = ctx.empty(2, l)
+        check(LIB.b2_moddown(ctx._h, l, 2, dev(cx_h).data_ptr(), dn.data_ptr(), ws.data_ptr(), nb, stream()))
+        assert np.array_equal(host(dn), want), (mode, l, "moddown")
+        dn1 = ctx.empty(1, l)
+        check(LIB.b2_moddown(ctx._h, l, 1, dev(cx_h[1]).data_ptr(), dn1.data_ptr(), ws.data_ptr(), nb, stream()))
+        assert np.array_equal(host(dn1)[0], want[1]), (mode, l, "moddown, one polynomial")
+        key = o.synth_key(beta, 31, 10)
+        kt, kp = key_dev(key)
+        ct = dev(ct_h)
+        ws, nb = _ws(ctx, _native.OP_KEYSWITCH, l)
+        check(LIB.b2_keyswitch(ctx._h, l, c2.data_ptr(), kp.ctypes.data, beta, ct.data_ptr(), ws.data_ptr(), nb, stream()))
+        assert np.array_equal(host(ct), o.keyswitch(l, c2_h, key, ct_h)), (mode, l, "keyswitch")
+    assert ctx.device_status() == 0
