@@ -424,7 +424,9 @@ def main():
     import torch
     import torch.distributed as dist
     import pyPhantom as ph
-    from pyPhantom import _native, synth
+    from pyPhantom import _native
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import synth  # the seeded generator of synthetic limbs the tests use
     from pyPhantom._native import LIB, check
 
     if not torch.cuda.is_available():

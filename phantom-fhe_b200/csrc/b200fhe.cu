@@ -229,7 +229,8 @@ struct b2_ctx {
     bool bconv_fp = false;         // every digit satisfies sum(q_i) < 2^64 and alpha <= 8
     bool bconv_tc = false;         // base conversions on the tensor cores (alpha <= 8, primes above 2^16; off with B2_BCONV=fp|int)
     bool bconv_int = false;        // B2_BCONV=int: force the 128-bit integer kernel
-    int tc_wg = 2;                 // warpgroups per CTA of the tensor-core conversion (B2_BCONV_WG = 1, 2, 4)
+    int tc_wg = 4;                 // warpgroups per CTA of the tensor-core conversion (B2_BCONV_WG = 1, 2, 4)
+    bool tc_simple = false;        // B2_BCONV_TC_SIMPLE=1: one CTA per tile instead of the persistent pipelined kernel
     uint32_t *d_err = nullptr;     // device status word: set by a kernel whose bounded wait ran out
     std::vector<uint64_t> h_mat_dn, h_mat_dn_pinv;  // host copies of the ModDown matrices [size_Q][size_P]
     bool use_cluster = false;      // N = 2^16: single-launch transforms on 8-CTA clusters
@@ -699,8 +700,10 @@ extern "C" int b2_ctx_create(size_t N, const uint64_t *primes, size_t size_QP, s
         c->bconv_tc = tc_ok && bc == "tc";
         c->bconv_int = bc == "int";
         const char *env_wg = getenv("B2_BCONV_WG");
-        c->tc_wg = env_wg ? atoi(env_wg) : 2;
-        if (c->tc_wg != 1 && c->tc_wg != 2 && c->tc_wg != 4) c->tc_wg = 2;
+        c->tc_wg = env_wg ? atoi(env_wg) : 4;
+        if (c->tc_wg != 1 && c->tc_wg != 2 && c->tc_wg != 4) c->tc_wg = 4;
+        const char *env_simple = getenv("B2_BCONV_TC_SIMPLE");
+        c->tc_simple = env_simple && env_simple[0] == '1';
         if (cudaMalloc((void **)&c->d_err, 4) != cudaSuccess || cudaMemset(c->d_err, 0, 4) != cudaSuccess) {
             b2_ctx_destroy(c);
             return fail(B2_ENOMEM, "ctx_create: cudaMalloc(status word) failed");
@@ -710,6 +713,9 @@ extern "C" int b2_ctx_create(size_t N, const uint64_t *primes, size_t size_QP, s
             cudaError_t ea = cudaFuncSetAttribute(bconv_tc_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TC_SMEM_MAX_REQUEST);
             if (ea == cudaSuccess) ea = cudaFuncSetAttribute(bconv_tc_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TC_SMEM_MAX_REQUEST);
             if (ea == cudaSuccess) ea = cudaFuncSetAttribute(bconv_tc_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TC_SMEM_MAX_REQUEST);
+            if (ea == cudaSuccess) ea = cudaFuncSetAttribute(bconv_tc_persist<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TC_SMEM_MAX_REQUEST);
+            if (ea == cudaSuccess) ea = cudaFuncSetAttribute(bconv_tc_persist<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TC_SMEM_MAX_REQUEST);
+            if (ea == cudaSuccess) ea = cudaFuncSetAttribute(bconv_tc_persist<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TC_SMEM_MAX_REQUEST);
             if (ea != cudaSuccess) {
                 b2_ctx_destroy(c);
                 return fail((int)ea, std::string("ctx_create: cudaFuncSetAttribute(bconv_tc_kernel): ") + cudaGetErrorString(ea));
@@ -1455,9 +1461,9 @@ __global__ void __launch_bounds__(256) bsgs_mac_multi_kernel(const uint64_t *con
 
 // Shared memory a conversion CTA asks for: what it uses, or enough that no more CTAs fit on an SM (228 KB) than its
 // 512 TMEM columns can serve, whichever is larger - so tcgen05.alloc finds its columns free and never waits.
-static uint32_t tc_smem_request(uint32_t alloc_cols) {
+static uint32_t tc_smem_request(uint32_t alloc_cols, uint32_t used) {
     const uint32_t fit = 512 / alloc_cols;
-    return std::max(TC_SMEM_BYTES, TC_SM_SMEM / (fit + 1));
+    return std::max(used, TC_SM_SMEM / (fit + 1));
 }
 
 // n_jobs: how many of the set's jobs to run (ModDown of one polynomial runs the first half)
@@ -1469,14 +1475,29 @@ static int run_bconv_tc(const b2_ctx *c, bool copy, const uint64_t *in, uint64_t
     LaunchScope ls(c, s, "bconv");
     // without the copy the jobs' copy slots are ignored by handing the kernel a null source
     const uint64_t *cs = copy ? copy_src : nullptr;
-    const dim3 grid(N / 128, n_jobs);
-    const uint32_t smem = tc_smem_request(tc.max_alloc);
-    switch (c->tc_wg) {
-        case 1: bconv_tc_kernel<1><<<grid, 128, smem, s>>>(in, out, cs, tc.jobs, tc.groups, tc.images, N, c->d_err); break;
-        case 4: bconv_tc_kernel<4><<<grid, 512, smem, s>>>(in, out, cs, tc.jobs, tc.groups, tc.images, N, c->d_err); break;
-        default: bconv_tc_kernel<2><<<grid, 256, smem, s>>>(in, out, cs, tc.jobs, tc.groups, tc.images, N, c->d_err); break;
+    if (c->tc_simple) {
+        const dim3 grid(N / 128, n_jobs);
+        const uint32_t smem = tc_smem_request(tc.max_alloc, TC_SMEM_BYTES);
+        switch (c->tc_wg) {
+            case 1: bconv_tc_kernel<1><<<grid, 128, smem, s>>>(in, out, cs, tc.jobs, tc.groups, tc.images, N, c->d_err); break;
+            case 4: bconv_tc_kernel<4><<<grid, 512, smem, s>>>(in, out, cs, tc.jobs, tc.groups, tc.images, N, c->d_err); break;
+            default: bconv_tc_kernel<2><<<grid, 256, smem, s>>>(in, out, cs, tc.jobs, tc.groups, tc.images, N, c->d_err); break;
+        }
+        LAUNCH_CHECK("bconv_tc_kernel");
+        return B2_OK;
     }
-    LAUNCH_CHECK("bconv_tc_kernel");
+    // persistent CTAs: as many as stay resident (TMEM columns, threads), each walking its share of the (job, tile) items
+    const uint32_t threads = 128u * (uint32_t)c->tc_wg;
+    const uint32_t fit = std::min(512u / tc.max_alloc, 2048u / threads);
+    const uint32_t total = n_jobs * (N / 128);
+    const uint32_t grid = std::min(total, fit * (uint32_t)c->sm_count);
+    const uint32_t smem = tc_smem_request(tc.max_alloc, TCP_SMEM_BYTES);
+    switch (c->tc_wg) {
+        case 1: bconv_tc_persist<1><<<grid, 128, smem, s>>>(in, out, cs, tc.jobs, tc.groups, tc.images, N, n_jobs, tc.max_alloc, c->d_err); break;
+        case 2: bconv_tc_persist<2><<<grid, 256, smem, s>>>(in, out, cs, tc.jobs, tc.groups, tc.images, N, n_jobs, tc.max_alloc, c->d_err); break;
+        default: bconv_tc_persist<4><<<grid, 512, smem, s>>>(in, out, cs, tc.jobs, tc.groups, tc.images, N, n_jobs, tc.max_alloc, c->d_err); break;
+    }
+    LAUNCH_CHECK("bconv_tc_persist");
     return B2_OK;
 }
 

@@ -69,6 +69,21 @@ __device__ __forceinline__ void tc_group_outputs(const uint32_t (&c)[16], const 
     }
 }
 
+
+// the same with the group table in shared memory
+template <int NB>
+__device__ __forceinline__ void tc_group_outputs_s(const uint32_t (&c)[16], const TcGroup *g, uint32_t n_valid, uint64_t *__restrict__ out, size_t N,
+                                                   uint32_t n) {
+    constexpr int OPG = 16 / NB;
+#pragma unroll
+    for (int o = 0; o < OPG; o++) {
+        if (o < (int)n_valid) {
+            const TcOut m = g->o[o];
+            out[(size_t)m.slot * N + n] = tc_reduce<NB>(&c[o * NB], m.p, m.mu);
+        }
+    }
+}
+
 // grid = (N / 128, jobs); dynamic shared memory >= TC_SMEM_BYTES (the launcher asks for more, so that the CTAs
 // resident on one SM can never want more than its 512 TMEM columns and the allocation never has to wait)
 template <int WG>
@@ -170,6 +185,165 @@ __global__ void __launch_bounds__(128 * WG) bconv_tc_kernel(const uint64_t *__re
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(job.alloc_cols) : "memory");
+}
+
+
+// ================================================================================================
+// Persistent form: a CTA stays on its SM and walks over work items (job, tile), job-major, with stride gridDim.x.
+// The job's B image and group table stay in shared memory until the job changes; the next item's A tile is fetched
+// with cp.async into the second A buffer while the current tile's accumulators are reduced and stored, so global
+// latency, the MMA and the epilogue overlap inside one CTA (and across the CTAs sharing the SM). TMEM is allocated
+// once per CTA. One mbarrier, used with alternating phase parity, signals each tile's MMA pair.
+// ================================================================================================
+constexpr uint32_t TCP_SMEM_A0 = 0, TCP_SMEM_A1 = TC_SMEM_A, TCP_SMEM_B = 2 * TC_SMEM_A, TCP_SMEM_GRP = TCP_SMEM_B + TC_SMEM_B;
+constexpr uint32_t TCP_SMEM_CTRL = TCP_SMEM_GRP + 16 * sizeof(TcGroup);
+constexpr uint32_t TCP_SMEM_BYTES = TCP_SMEM_CTRL + 32;
+
+__device__ __forceinline__ void tc_cp_async8(uint32_t smem_dst, const void *gsrc) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(smem_dst), "l"(gsrc) : "memory");
+}
+__device__ __forceinline__ void tc_cp_async16(uint32_t smem_dst, const void *gsrc) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_dst), "l"(gsrc) : "memory");
+}
+
+// the rows of A for tile `tile` of `job`: 8 bytes per (coefficient, input limb), zeros for limbs the job does not have
+template <int WG>
+__device__ __forceinline__ void tcp_fetch_a(uint8_t *sA, const uint64_t *__restrict__ in, const TcJob &job, uint32_t N, uint32_t tile) {
+    const uint32_t tid = threadIdx.x, r = tid & 127, part = tid >> 7;
+    constexpr int LIMBS = 8 / WG;
+#pragma unroll
+    for (int j = 0; j < LIMBS; j++) {
+        const uint32_t i = part * LIMBS + j;
+        uint8_t *dst = sA + (r >> 3) * 512 + (i >> 1) * 128 + (r & 7) * 16 + (i & 1) * 8;
+        if (i < job.ni) tc_cp_async8(tc_smem_u32(dst), in + (size_t)(job.in_slot0 + i) * N + (size_t)tile * 128 + r);
+        else *reinterpret_cast<uint64_t *>(dst) = 0;
+    }
+}
+
+template <int WG>
+__global__ void __launch_bounds__(128 * WG) bconv_tc_persist(const uint64_t *__restrict__ in, uint64_t *__restrict__ out,
+                                                             const uint64_t *__restrict__ copy_src, const TcJob *__restrict__ jobs,
+                                                             const TcGroup *__restrict__ groups, const uint8_t *__restrict__ images, uint32_t N,
+                                                             uint32_t n_jobs, uint32_t alloc_cols, uint32_t *err) {
+    extern __shared__ __align__(1024) uint8_t tc_smem[];
+    uint8_t *sB = tc_smem + TCP_SMEM_B;
+    TcGroup *sG = reinterpret_cast<TcGroup *>(tc_smem + TCP_SMEM_GRP);
+    uint64_t *bar = reinterpret_cast<uint64_t *>(tc_smem + TCP_SMEM_CTRL);
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(tc_smem + TCP_SMEM_CTRL + 8);
+    constexpr uint32_t THREADS = 128 * WG;
+    const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const uint32_t tiles = N >> 7, total = n_jobs * tiles;
+
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tc_smem_u32(tmem_slot)), "r"(alloc_cols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    if (tid == 0) {
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(tc_smem_u32(bar)) : "memory");
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    uint32_t item = blockIdx.x, cur = 0, phase = 0, loaded_job = 0xFFFFFFFFu;
+    bool ok = true;
+    TcJob job{};
+    if (item < total) {
+        job = jobs[item / tiles];
+        tcp_fetch_a<WG>(tc_smem + TCP_SMEM_A0, in, job, N, item % tiles);
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = *tmem_slot;
+    const uint32_t wq = warp & 3, wg = warp >> 2;
+    const uint32_t lane_base = tmem + ((wq * 32u) << 16);
+
+    while (item < total && ok) {
+        const uint32_t jb = item / tiles, tile = item % tiles;
+        if (jb != loaded_job) {
+            // a new job: its B image and group table (the MMA that read the old image has completed: every thread
+            // waited for it before the previous epilogue, and the barrier at the end of that iteration has passed)
+            job = jobs[jb];
+            const uint8_t *img = images + job.img_off;
+            for (uint32_t i = tid; i < job.n_groups * 64; i += THREADS) tc_cp_async16(tc_smem_u32(sB + 16 * i), img + 16 * i);
+            const uint8_t *grp = reinterpret_cast<const uint8_t *>(groups + job.grp_off);
+            for (uint32_t i = tid; i < job.n_groups * 5; i += THREADS) tc_cp_async16(tc_smem_u32(reinterpret_cast<uint8_t *>(sG) + 16 * i), grp + 16 * i);
+            asm volatile("cp.async.commit_group;" ::: "memory");
+            loaded_job = jb;
+        }
+        asm volatile("cp.async.wait_all;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncthreads();
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        uint8_t *sA = tc_smem + (cur ? TCP_SMEM_A1 : TCP_SMEM_A0);
+        if (tid == 0) {
+            const uint64_t adesc = tc_desc(tc_smem_u32(sA)), bdesc = tc_desc(tc_smem_u32(sB));
+            const uint32_t idesc = (2u << 4) | (((16u * job.n_groups) >> 3) << 17) | ((128u >> 4) << 24);
+            tc_mma_i8(tmem, adesc, bdesc, idesc, 0u);
+            tc_mma_i8(tmem, adesc + (256u >> 4), bdesc + (256u >> 4), idesc, 1u);
+            asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(tc_smem_u32(bar)) : "memory");
+        }
+        // next item's rows of A into the other buffer (its last reader, the MMA of the previous iteration, is done)
+        const uint32_t next = item + gridDim.x;
+        if (next < total) {
+            const uint32_t njb = next / tiles;
+            if (njb == jb) {
+                tcp_fetch_a<WG>(tc_smem + (cur ? TCP_SMEM_A0 : TCP_SMEM_A1), in, job, N, next % tiles);
+            } else {
+                const TcJob nj = jobs[njb];
+                tcp_fetch_a<WG>(tc_smem + (cur ? TCP_SMEM_A0 : TCP_SMEM_A1), in, nj, N, next % tiles);
+            }
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        // ModUp: the digit's own limbs travel from the NTT-form input to the output buffer
+        if (copy_src != nullptr && job.copy_dst_slot0 != 0xFFFFFFFFu) {
+            const uint32_t r = tid & 127, part = tid >> 7;
+            for (uint32_t i = part; i < job.ni; i += WG)
+                out[(size_t)(job.copy_dst_slot0 + i) * N + (size_t)tile * 128 + r] = copy_src[(size_t)(job.in_slot0 + i) * N + (size_t)tile * 128 + r];
+        }
+        // bounded wait for the accumulators
+        uint32_t done = 0;
+        for (uint32_t it = 0; it < TC_WAIT_LIMIT && !done; it++) {
+            asm volatile(
+                "{\n\t"
+                ".reg .pred P1;\n\t"
+                "mbarrier.try_wait.parity.shared::cta.b64 P1, [%1], %2;\n\t"
+                "selp.b32 %0, 1, 0, P1;\n\t"
+                "}\n"
+                : "=r"(done)
+                : "r"(tc_smem_u32(bar)), "r"(phase)
+                : "memory");
+        }
+        phase ^= 1u;
+        ok = __all_sync(0xFFFFFFFFu, done != 0);
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        if (ok) {
+            const uint32_t n = tile * 128 + wq * 32 + lane;
+            for (uint32_t g = wg; g < job.n_groups; g += WG) {
+                uint32_t c[16];
+                tc_ld16(lane_base + g * 16, c);
+                const TcGroup *G = sG + g;
+                const uint32_t nb = G->nb, nv = G->n_valid;
+                switch (nb) {
+                    case 4: tc_group_outputs_s<4>(c, G, nv, out, N, n); break;
+                    case 5: tc_group_outputs_s<5>(c, G, nv, out, N, n); break;
+                    case 6: tc_group_outputs_s<6>(c, G, nv, out, N, n); break;
+                    case 7: tc_group_outputs_s<7>(c, G, nv, out, N, n); break;
+                    default: tc_group_outputs_s<8>(c, G, nv, out, N, n); break;
+                }
+            }
+        } else if (lane == 0) {
+            atomicExch(err, 1u);  // the MMA never signalled: this CTA stops, its remaining tiles are not written
+        }
+        // a CTA whose wait ran out must stop as a whole: make the verdict uniform over the CTA
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        ok = __syncthreads_and(ok);
+        cur ^= 1u;
+        item = next;
+    }
+    asm volatile("cp.async.wait_all;" ::: "memory");
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(alloc_cols) : "memory");
 }
 
 }  // namespace b2

@@ -474,14 +474,15 @@ def test_inner_product_inside_the_last_forward_pass(monkeypatch, name, fused):
     assert hashes(ct, N) == case["hashes"]["keyswitch"]
 
 
-@pytest.mark.parametrize("mode", ["tc:1", "tc:2", "tc:4", "fp", "int"])
+@pytest.mark.parametrize("mode", ["tc:1", "tc:2", "tc:4", "tcs:1", "tcs:4", "fp", "int"])
 @pytest.mark.parametrize("shape", ["n12_ragged", "n16_headline", "n13_many_limbs"])
 def test_base_conversion_kernels_agree(mode, shape, monkeypatch):
     """ModUp, ModDown (one and two polynomials) and the whole key switch through each base-conversion kernel - tensor
-    cores with 1, 2 and 4 warpgroups per CTA, FP64 pieces, 128-bit integers - against the oracle. The context reads the
-    selection from the environment when it is created."""
+    cores (persistent pipelined kernel, and "tcs": one CTA per tile) with 1, 2 and 4 warpgroups per CTA, FP64 pieces,
+    128-bit integers - against the oracle. The context reads the selection from the environment when it is created."""
     kind, _, wg = mode.partition(":")
-    monkeypatch.setenv("B2_BCONV", kind)
+    monkeypatch.setenv("B2_BCONV_TC_SIMPLE", "1" if kind == "tcs" else "0")
+    monkeypatch.setenv("B2_BCONV", "tc" if kind == "tcs" else kind)
     if wg:
         monkeypatch.setenv("B2_BCONV_WG", wg)
     if shape == "n12_ragged":
