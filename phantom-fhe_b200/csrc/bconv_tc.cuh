@@ -70,17 +70,72 @@ __device__ __forceinline__ void tc_group_outputs(const uint32_t (&c)[16], const 
 }
 
 
-// the same with the group table in shared memory
+// ---- lean epilogue of the persistent kernel ------------------------------------------------------------------------
+// One output as the epilogue wants it, 16 bytes in shared memory (one LDS.128): prime, reciprocal, and the output
+// limb's first element (slot * N); 0xFFFFFFFF marks a slot of a group that holds no output (p = 1 keeps its
+// arithmetic harmless), so the group is processed without a branch per output and only the store is predicated.
+struct TcOutS {
+    uint32_t p_lo, p_hi, mu, off;
+};
+
+// One output, written so that it costs about twenty instructions: the planes are paired with shift-adds, joined by one
+// (two for 7 and 8 planes) wide multiply-add, the quotient estimate is one high multiply, and the two subtractions, the
+// choice between r and r - p (sign of the difference: r < 2p < 2^62) and the predicated store are spelled out in PTX so
+// that no branch and no 64-bit compare is generated. Same value as tc_reduce / tc_reduce_dev (bconv_tc_plan.h).
 template <int NB>
-__device__ __forceinline__ void tc_group_outputs_s(const uint32_t (&c)[16], const TcGroup *g, uint32_t n_valid, uint64_t *__restrict__ out, size_t N,
-                                                   uint32_t n) {
+__device__ __forceinline__ void tc_output(const uint32_t *c, const uint4 m, uint64_t *__restrict__ out_n) {
+    constexpr int SH = 8 * NB - 17;
+    const uint32_t x0 = c[0] + (c[1] << 8), x1 = c[2] + (c[3] << 8);
+    uint32_t vl, vh, vq;  // V mod 2^64 as two words; V >> SH
+    if constexpr (NB <= 6) {
+        const uint32_t x2 = NB == 4 ? 0u : (NB == 5 ? c[4] : c[4] + (c[5] << 8));
+        const uint64_t v = (uint64_t)x1 * 65536u + (((uint64_t)x2 << 32) | x0);
+        vl = (uint32_t)v, vh = (uint32_t)(v >> 32);
+        vq = __funnelshift_r(vl, vh, SH);
+    } else {
+        const uint32_t x2 = c[4] + (c[5] << 8), x3 = NB == 7 ? c[6] : c[6] + (c[7] << 8);
+        const uint64_t a = (uint64_t)x1 * 65536u + x0, b = (uint64_t)x3 * 65536u + x2;
+        const uint64_t mid = (a >> 32) + b;
+        vl = (uint32_t)a, vh = (uint32_t)mid;
+        vq = __funnelshift_r((uint32_t)mid, (uint32_t)(mid >> 32), SH - 32);
+    }
+    const uint32_t qhat = __umulhi(vq, m.z);
+    const uint64_t qp = (uint64_t)qhat * m.x;
+    const uint32_t ql = (uint32_t)qp, qh = (uint32_t)(qp >> 32) + qhat * m.y;
+    uint32_t rl, rh;
+    // plain asm (no volatile): independent outputs of a group may be interleaved by the scheduler
+    asm("{\n\t"
+        ".reg .u32 tl, th;\n\t"
+        ".reg .pred pn;\n\t"
+        "sub.cc.u32 %0, %2, %4;\n\t"
+        "subc.u32 %1, %3, %5;\n\t"
+        "sub.cc.u32 tl, %0, %6;\n\t"
+        "subc.u32 th, %1, %7;\n\t"
+        "setp.lt.s32 pn, th, 0;\n\t"
+        "selp.u32 %0, %0, tl, pn;\n\t"
+        "selp.u32 %1, %1, th, pn;\n\t"
+        "}\n"
+        : "=&r"(rl), "=&r"(rh)
+        : "r"(vl), "r"(vh), "r"(ql), "r"(qh), "r"(m.x), "r"(m.y));
+    asm volatile(
+        "{\n\t"
+        ".reg .pred pv;\n\t"
+        "setp.ne.u32 pv, %3, 0xFFFFFFFF;\n\t"
+        "@pv st.global.v2.u32 [%0], {%1, %2};\n\t"
+        "}\n" ::"l"(out_n + m.w),
+        "r"(rl), "r"(rh), "r"(m.w)
+        : "memory");
+}
+
+template <int NB>
+__device__ __forceinline__ void tc_group_lean(const uint32_t (&c)[16], uint32_t mo_smem, uint64_t *__restrict__ out_n) {
     constexpr int OPG = 16 / NB;
 #pragma unroll
     for (int o = 0; o < OPG; o++) {
-        if (o < (int)n_valid) {
-            const TcOut m = g->o[o];
-            out[(size_t)m.slot * N + n] = tc_reduce<NB>(&c[o * NB], m.p, m.mu);
-        }
+        uint4 m;
+        // the records do not change while a job's tiles are reduced: the load may move freely
+        asm("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(m.x), "=r"(m.y), "=r"(m.z), "=r"(m.w) : "r"(mo_smem + 16 * o));
+        tc_output<NB>(&c[o * NB], m, out_n);
     }
 }
 
@@ -196,7 +251,7 @@ __global__ void __launch_bounds__(128 * WG) bconv_tc_kernel(const uint64_t *__re
 // once per CTA. One mbarrier, used with alternating phase parity, signals each tile's MMA pair.
 // ================================================================================================
 constexpr uint32_t TCP_SMEM_A0 = 0, TCP_SMEM_A1 = TC_SMEM_A, TCP_SMEM_B = 2 * TC_SMEM_A, TCP_SMEM_GRP = TCP_SMEM_B + TC_SMEM_B;
-constexpr uint32_t TCP_SMEM_CTRL = TCP_SMEM_GRP + 16 * sizeof(TcGroup);
+constexpr uint32_t TCP_SMEM_CTRL = TCP_SMEM_GRP + 16 * 4 * 16 + 64;  // 16 groups x 4 output records, then one byte count per group
 constexpr uint32_t TCP_SMEM_BYTES = TCP_SMEM_CTRL + 32;
 
 __device__ __forceinline__ void tc_cp_async8(uint32_t smem_dst, const void *gsrc) {
@@ -227,12 +282,13 @@ __global__ void __launch_bounds__(128 * WG) bconv_tc_persist(const uint64_t *__r
                                                              uint32_t n_jobs, uint32_t alloc_cols, uint32_t *err) {
     extern __shared__ __align__(1024) uint8_t tc_smem[];
     uint8_t *sB = tc_smem + TCP_SMEM_B;
-    TcGroup *sG = reinterpret_cast<TcGroup *>(tc_smem + TCP_SMEM_GRP);
+    TcOutS *sOut = reinterpret_cast<TcOutS *>(tc_smem + TCP_SMEM_GRP);              // [16][4]
+    uint32_t *sNb = reinterpret_cast<uint32_t *>(tc_smem + TCP_SMEM_GRP + 16 * 4 * 16);  // [16]
     uint64_t *bar = reinterpret_cast<uint64_t *>(tc_smem + TCP_SMEM_CTRL);
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(tc_smem + TCP_SMEM_CTRL + 8);
     constexpr uint32_t THREADS = 128 * WG;
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const uint32_t tiles = N >> 7, total = n_jobs * tiles;
+    const uint32_t tiles = N >> 7, tile_mask = tiles - 1, log_tiles = 31 - __clz(tiles), total = n_jobs * tiles;  // N is a power of two
 
     if (warp == 0) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tc_smem_u32(tmem_slot)), "r"(alloc_cols) : "memory");
@@ -246,8 +302,8 @@ __global__ void __launch_bounds__(128 * WG) bconv_tc_persist(const uint64_t *__r
     bool ok = true;
     TcJob job{};
     if (item < total) {
-        job = jobs[item / tiles];
-        tcp_fetch_a<WG>(tc_smem + TCP_SMEM_A0, in, job, N, item % tiles);
+        job = jobs[item >> log_tiles];
+        tcp_fetch_a<WG>(tc_smem + TCP_SMEM_A0, in, job, N, item & tile_mask);
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -258,16 +314,27 @@ __global__ void __launch_bounds__(128 * WG) bconv_tc_persist(const uint64_t *__r
     const uint32_t lane_base = tmem + ((wq * 32u) << 16);
 
     while (item < total && ok) {
-        const uint32_t jb = item / tiles, tile = item % tiles;
+        const uint32_t jb = item >> log_tiles, tile = item & tile_mask;
         if (jb != loaded_job) {
             // a new job: its B image and group table (the MMA that read the old image has completed: every thread
             // waited for it before the previous epilogue, and the barrier at the end of that iteration has passed)
             job = jobs[jb];
             const uint8_t *img = images + job.img_off;
             for (uint32_t i = tid; i < job.n_groups * 64; i += THREADS) tc_cp_async16(tc_smem_u32(sB + 16 * i), img + 16 * i);
-            const uint8_t *grp = reinterpret_cast<const uint8_t *>(groups + job.grp_off);
-            for (uint32_t i = tid; i < job.n_groups * 5; i += THREADS) tc_cp_async16(tc_smem_u32(reinterpret_cast<uint8_t *>(sG) + 16 * i), grp + 16 * i);
             asm volatile("cp.async.commit_group;" ::: "memory");
+            // output records in the epilogue's form (nobody reads the old ones any more: see above)
+            if (tid < job.n_groups * 4) {
+                const TcGroup *G = groups + job.grp_off + (tid >> 2);
+                const uint32_t o = tid & 3;
+                const uint2 hdr = __ldg(reinterpret_cast<const uint2 *>(G));
+                TcOutS rec{1u, 0u, 0u, 0xFFFFFFFFu};
+                if (o < hdr.y) {
+                    const uint4 raw = __ldg(reinterpret_cast<const uint4 *>(&G->o[o]));
+                    rec = TcOutS{raw.x, raw.y, raw.z, raw.w * N};
+                }
+                sOut[tid] = rec;
+                if (o == 0) sNb[tid >> 2] = hdr.x;
+            }
             loaded_job = jb;
         }
         asm volatile("cp.async.wait_all;" ::: "memory");
@@ -285,12 +352,12 @@ __global__ void __launch_bounds__(128 * WG) bconv_tc_persist(const uint64_t *__r
         // next item's rows of A into the other buffer (its last reader, the MMA of the previous iteration, is done)
         const uint32_t next = item + gridDim.x;
         if (next < total) {
-            const uint32_t njb = next / tiles;
+            const uint32_t njb = next >> log_tiles;
             if (njb == jb) {
-                tcp_fetch_a<WG>(tc_smem + (cur ? TCP_SMEM_A0 : TCP_SMEM_A1), in, job, N, next % tiles);
+                tcp_fetch_a<WG>(tc_smem + (cur ? TCP_SMEM_A0 : TCP_SMEM_A1), in, job, N, next & tile_mask);
             } else {
                 const TcJob nj = jobs[njb];
-                tcp_fetch_a<WG>(tc_smem + (cur ? TCP_SMEM_A0 : TCP_SMEM_A1), in, nj, N, next % tiles);
+                tcp_fetch_a<WG>(tc_smem + (cur ? TCP_SMEM_A0 : TCP_SMEM_A1), in, nj, N, next & tile_mask);
             }
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
@@ -317,18 +384,17 @@ __global__ void __launch_bounds__(128 * WG) bconv_tc_persist(const uint64_t *__r
         ok = __all_sync(0xFFFFFFFFu, done != 0);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         if (ok) {
-            const uint32_t n = tile * 128 + wq * 32 + lane;
+            uint64_t *out_n = out + (tile * 128 + wq * 32 + lane);
             for (uint32_t g = wg; g < job.n_groups; g += WG) {
                 uint32_t c[16];
                 tc_ld16(lane_base + g * 16, c);
-                const TcGroup *G = sG + g;
-                const uint32_t nb = G->nb, nv = G->n_valid;
-                switch (nb) {
-                    case 4: tc_group_outputs_s<4>(c, G, nv, out, N, n); break;
-                    case 5: tc_group_outputs_s<5>(c, G, nv, out, N, n); break;
-                    case 6: tc_group_outputs_s<6>(c, G, nv, out, N, n); break;
-                    case 7: tc_group_outputs_s<7>(c, G, nv, out, N, n); break;
-                    default: tc_group_outputs_s<8>(c, G, nv, out, N, n); break;
+                const uint32_t mo = tc_smem_u32(sOut + 4 * g);
+                switch (sNb[g]) {
+                    case 4: tc_group_lean<4>(c, mo, out_n); break;
+                    case 5: tc_group_lean<5>(c, mo, out_n); break;
+                    case 6: tc_group_lean<6>(c, mo, out_n); break;
+                    case 7: tc_group_lean<7>(c, mo, out_n); break;
+                    default: tc_group_lean<8>(c, mo, out_n); break;
                 }
             }
         } else if (lane == 0) {

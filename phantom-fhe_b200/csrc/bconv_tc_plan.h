@@ -83,6 +83,32 @@ B2_HD uint64_t tc_reduce(const uint32_t *c, uint64_t p, uint32_t mu) {
     return r >= p ? r - p : r;
 }
 
+// tc_reduce with the prime as two words and the last subtraction chosen by the sign of (r - p): r < 2p < 2^62
+template <int NB>
+B2_HD uint64_t tc_reduce_dev(const uint32_t *c, uint32_t p_lo, uint32_t p_hi, uint32_t mu) {
+    constexpr int SH = 8 * NB - 17;
+    const uint32_t x0 = c[0] + (c[1] << 8), x1 = c[2] + (c[3] << 8);
+    uint64_t vlo;
+    uint32_t vh;
+    if constexpr (NB <= 6) {
+        const uint32_t x2 = NB == 4 ? 0u : (NB == 5 ? c[4] : c[4] + (c[5] << 8));
+        vlo = (uint64_t)x1 * 65536u + x0;               // one wide multiply-add
+        vlo += (uint64_t)x2 << 32;                      // touches the high word only
+        vh = (uint32_t)(vlo >> SH);
+    } else {
+        const uint32_t x2 = c[4] + (c[5] << 8), x3 = NB == 7 ? c[6] : c[6] + (c[7] << 8);
+        const uint64_t a = (uint64_t)x1 * 65536u + x0, b = (uint64_t)x3 * 65536u + x2;
+        const uint64_t mid = (a >> 32) + b;
+        vlo = (a & 0xFFFFFFFFull) | (mid << 32);
+        vh = (uint32_t)(mid >> (SH - 32));
+    }
+    const uint32_t qhat = (uint32_t)(((uint64_t)vh * mu) >> 32);
+    const uint64_t p = ((uint64_t)p_hi << 32) | p_lo;
+    const uint64_t r = vlo - ((uint64_t)qhat * p_lo + ((uint64_t)(qhat * p_hi) << 32));
+    const uint64_t t = r - p;
+    return (int64_t)t < 0 ? r : t;
+}
+
 struct TcSpecOut {
     uint32_t slot;        // absolute output limb
     uint64_t p;           // its prime

@@ -72,6 +72,16 @@ static int run_case(int ni, const std::vector<int> &in_bits, const std::vector<i
                         case 7: got = b2::tc_reduce<7>(&c[o * 7], m.p, m.mu); break;
                         default: got = b2::tc_reduce<8>(&c[o * 8], m.p, m.mu); break;
                     }
+                    uint64_t lean;
+                    const uint32_t plo = (uint32_t)m.p, phi = (uint32_t)(m.p >> 32);
+                    switch (G.nb) {
+                        case 4: lean = b2::tc_reduce_dev<4>(&c[o * 4], plo, phi, m.mu); break;
+                        case 5: lean = b2::tc_reduce_dev<5>(&c[o * 5], plo, phi, m.mu); break;
+                        case 6: lean = b2::tc_reduce_dev<6>(&c[o * 6], plo, phi, m.mu); break;
+                        case 7: lean = b2::tc_reduce_dev<7>(&c[o * 7], plo, phi, m.mu); break;
+                        default: lean = b2::tc_reduce_dev<8>(&c[o * 8], plo, phi, m.mu); break;
+                    }
+                    if (lean != got) return printf("the two forms of the reduction disagree\n"), 1;
                     const size_t j = m.slot - 100;
                     if (j >= out_bits.size() || m.p != p[j]) return printf("bad output record\n"), 1;
                     seen[j] = 1;
