@@ -4,15 +4,20 @@
 Workload (the configuration the headline metric is quoted on): 24 Q limbs (one 60-bit prime and 23
 primes of 40 bits), 8 special primes of 60 bits, alpha = 8, 3 digits; ciphertext and evaluation-key
 limbs uniform in [0, q_i) from a seeded generator (synthetic; the path is integer-only).
-A step = one batch of BATCH key switches on distinct ciphertexts cycling over KEYS distinct
-evaluation keys, so one step touches ~670 MB, far more than the 126 MB L2 (that is this file's
-answer to the L2-flush rule: inputs larger than L2).
+A step = one batch of BATCH (default 64) key switches on distinct ciphertexts cycling over KEYS
+distinct evaluation keys, so one step touches several GB, far more than the 126 MB L2 (that is this
+file's answer to the L2-flush rule: inputs larger than L2).
 
   value : KeySwitch/s over all ranks, inputs resident in HBM, device time (CUDA events, max over ranks)
   e2e   : the same metric through the reference-facing Python call (pyPhantom.relinearize, the
           pybind11 surface of the reference) with HOST buffers: every key switch copies its
           3-polynomial ciphertext in from pinned memory and its 2-polynomial result back out
-  roofline : the dominant kernel, timed live with CUDA events on its own stream
+  roofline : the WHOLE key switch against the HBM roofline: 312 limbs = 163.6 MB of compulsory traffic
+          (c2, key digits, ciphertext in and out) over the measured time per key switch
+  roofline_issue : the same time against the instruction-issue roofline (warp instructions per key
+          switch from the committed ncu capture over 148 SMs x 4 schedulers x the sampled SM clock)
+  kernels : per kernel, timed live with CUDA events on its own stream: algorithmic bytes beside the DRAM
+          bytes ncu saw, and what actually bounds it
   cpu_baseline : the CPU restatement (oracle/) timed on this box's cores on a bounded sample
 
 Multi-GPU: one process per GPU (torchrun); the path shards by independent ciphertexts, every rank
@@ -107,12 +112,23 @@ class ClockSampler:
                 "samples": len(sm), "window": "timed region" if inside else "whole run (timed region shorter than the sampling period)"}
 
 
-def run_reference_arm(args, rank, out_stream):
-    """the reference's algorithm on the host cores (CPU restatement, all threads); rank 0 only"""
+def config_dict(args, world):
+    """what both arms report as `config`: the workload and how a step is made of it"""
+    S = max(1, min(args.streams, args.batch))
+    return {"workload": WORKLOAD, "batch_per_step_per_gpu": args.batch, "distinct_keys": args.keys, "streams": S,
+            "l2": "inputs larger than L2 (a step touches %.1f GB)" % (args.batch * 3 * LEVEL * LIMB_BYTES / 1e9 + args.keys * 0.1),
+            "parallelism": f"dp{world}"}
+
+
+def run_reference_arm(args, rank, world, out_stream):
+    """the reference's algorithm on the host cores (CPU restatement, every core this process may use, whatever
+    OMP_NUM_THREADS the launcher exported); rank 0 only. A step of this arm is ONE key switch of the workload (a bounded
+    sample of the batch the GPU arm runs per step): the value is key switches per second either way."""
     if rank != 0:
         return
     sys.path.insert(0, os.path.join(ROOT, "tests"))
-    from oracle_lib import Oracle, create_coeff_modulus, LIB as ORA
+    from oracle_lib import Oracle, create_coeff_modulus, use_all_cores
+    cores = use_all_cores()
     primes = create_coeff_modulus(N, BITS)
     o = Oracle(N, primes, SPECIAL)
     key = o.synth_key(BETA, 2, 10)
@@ -125,13 +141,12 @@ def run_reference_arm(args, rank, out_stream):
         o.keyswitch(LEVEL, c2, key, ct)
     dt = time.perf_counter() - t0
     v = args.steps / dt
-    cores = int(ORA.ora_num_threads())
     line = {"impl": "reference", "metric": "KeySwitch/s", "value": v, "unit": "KeySwitch/s", "n_gpus": args.gpus,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * dt / args.steps, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "u64", "data": "synthetic",
-            "config": {"workload": WORKLOAD, "batch_per_step": 1},
+            "config": config_dict(args, world),
             "cpu_baseline": {"value": v, "unit": "KeySwitch/s", "cores": cores, "kind": "port",
-                             "sample": f"{args.steps} key switches, one per step"},
+                             "sample": f"{args.steps} key switches of the workload, one per step (a bounded sample of the batch)"},
             "e2e": {"value": v, "unit": "KeySwitch/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "note": "the reference has no CPU implementation of this path; this is the CPU restatement in oracle/"}
     print(json.dumps(line), file=out_stream, flush=True)
@@ -139,7 +154,8 @@ def run_reference_arm(args, rank, out_stream):
 
 def cpu_baseline_sample(budget_s=12.0):
     sys.path.insert(0, os.path.join(ROOT, "tests"))
-    from oracle_lib import Oracle, create_coeff_modulus, LIB as ORA
+    from oracle_lib import Oracle, create_coeff_modulus, use_all_cores
+    cores = use_all_cores()
     primes = create_coeff_modulus(N, BITS)
     o = Oracle(N, primes, SPECIAL)
     key = o.synth_key(BETA, 2, 10)
@@ -153,7 +169,7 @@ def cpu_baseline_sample(budget_s=12.0):
         dt = time.perf_counter() - t0
         if dt > budget_s or n >= 64:
             break
-    return {"value": n / dt, "unit": "KeySwitch/s", "cores": int(ORA.ora_num_threads()), "kind": "port",
+    return {"value": n / dt, "unit": "KeySwitch/s", "cores": cores, "kind": "port",
             "sample": f"{n} key switches of the same workload in {dt:.1f} s"}
 
 
@@ -276,8 +292,8 @@ def bootstrap_section(ph, torch, np):
 
 def compositions_section(ph, ctx, torch, np, synth, primes, keys, N, level, reps=20):
     """the evaluator calls built on the key switch, at the bench level (24 limbs), through the pyPhantom surface:
-    one stream (latency, what the reference's own timings in tests/golden/n16_l24_a8.json measure) and a batch of 8
-    over 4 streams (throughput)"""
+    one stream (latency; the reference's own kernels, timed in the same run, are under `reference_gpu`) and a batch
+    of 8 over 4 streams (throughput)"""
     from pyPhantom import _native
     def ct_of(buf, n_poly=2):
         c = ph.ciphertext()
@@ -322,13 +338,6 @@ def compositions_section(ph, ctx, torch, np, synth, primes, keys, N, level, reps
         e1.record()
         torch.cuda.synchronize()
         out[name] = {"us_one_stream": one, "per_s_batch8_streams4": 8 * reps / (e0.elapsed_time(e1) / 1e3)}
-    try:  # the unmodified reference's own timings on a B200, recorded with the golden hashes
-        t = json.load(open(os.path.join(ROOT, "tests", "golden", "n16_l24_a8.json")))["times_us"]
-        out["reference_us_same_gpu"] = {"multiply_and_relin": t["mul_relin_us"], "multiply_and_relin_rescale": t["mul_relin_rescale_us"],
-                                        "rotate": t["rotate_us"], "hoist_rotations_x3": t["hoist_rotations_us"], "keyswitch": t["keyswitch_us"],
-                                        "source": "tests/golden/n16_l24_a8.json times_us"}
-    except (OSError, KeyError, ValueError):
-        out["reference_us_same_gpu"] = None
     return out
 
 
@@ -386,6 +395,85 @@ def bsgs_section(ph, torch, np, synth):
             "reference_ms_same_gpu": ref_ms, "reference_source": "tests/golden/full/n16_l16_bsgs_m64g64.json times_us.bsgs_us"}
 
 
+def hmult_section(torch, dist, ctx, LIB, check, _native, dev_ct3, key_tabs, world, streams_n, reps=5):
+    """BASELINE config 3: HMult + relinearise + rescale on 64 independent ciphertext pairs at 24 limbs, sharded data-parallel
+    (64 / world pairs per rank, no collective), resident, spread over the same number of streams as the headline batch.
+    Algorithmic bytes per pair: 4l + 2 beta (l + alpha) + 2 (l - 1) = 334 limbs = 175.1 MB."""
+    pairs = max(1, 64 // world)
+    B = len(dev_ct3)
+    S = max(1, min(streams_n, pairs))
+    main = torch.cuda.current_stream()
+    side = [torch.cuda.Stream() for _ in range(S)] if S > 1 else [main]
+    prod = [torch.empty(2, LEVEL, N, dtype=torch.int64, device="cuda") for _ in range(S)]
+    outs = [torch.empty(2, LEVEL - 1, N, dtype=torch.int64, device="cuda") for _ in range(S)]
+    ws_m = [ctx.workspace(_native.OP_MUL_RELIN, LEVEL) for _ in range(S)]
+    ws_r = [ctx.workspace(_native.OP_RESCALE, LEVEL) for _ in range(S)]
+
+    def run():
+        for sd in side:
+            sd.wait_stream(main)
+        for p in range(pairs):
+            i = p % S
+            a, b = dev_ct3[p % B], dev_ct3[(p + 1) % B]
+            st = side[i].cuda_stream
+            check(LIB.b2_multiply_and_relin(ctx._h, LEVEL, a.data_ptr(), b.data_ptr(), key_tabs[p % len(key_tabs)].ctypes.data, BETA,
+                                            prod[i].data_ptr(), ws_m[i][0].data_ptr(), ws_m[i][1], st))
+            check(LIB.b2_rescale(ctx._h, LEVEL, 2, prod[i].data_ptr(), outs[i].data_ptr(), ws_r[i][0].data_ptr(), ws_r[i][1], st))
+        for sd in side:
+            main.wait_stream(sd)
+
+    run()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(main)
+    for _ in range(reps):
+        run()
+    e1.record(main)
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([ms], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    per_s = world * pairs * reps / (ms / 1e3)
+    limbs = 4 * LEVEL + 2 * BETA * (LEVEL + SPECIAL) + 2 * (LEVEL - 1)
+    peak, peak_kind = peaks()
+    return {"workload": "64 ciphertext pairs, HMult + relinearise + rescale, N=65536, 24 limbs, dnum 3", "pairs_per_gpu": pairs, "streams": S,
+            "pairs_per_s": per_s, "us_per_pair_per_gpu": 1e3 * ms / (pairs * reps), "alg_bytes_per_pair": limbs * LIMB_BYTES,
+            "hbm_frac": per_s / world * limbs * LIMB_BYTES / 1e9 / peak, "peak_kind": peak_kind, "reps": reps}
+
+
+def reference_gpu_section():
+    """the unmodified reference's own kernels on this GPU, measured in this run through oracle/_ref/ref_harness (built from the
+    reference's sources where a checkout was present; None when it is absent): the key switch and its callers on one stream,
+    and the key switch from four host threads (the reference runs on per-thread default streams)"""
+    h = os.path.join(ROOT, "oracle", "_ref", "ref_harness")
+    if not os.path.exists(h):
+        return None
+    import tempfile
+    bits = ",".join(str(b) for b in BITS)
+    with tempfile.TemporaryDirectory() as tmp:
+        out = os.path.join(tmp, "ref.json")
+        cmd = [h, "--logn", str(LOGN), "--bits", bits, "--special", str(SPECIAL), "--level", str(LEVEL), "--seed", "2", "--steps", "1,2,-1",
+               "--time", "40", "--threads", "4", "--out", out]
+        try:
+            r = subprocess.run(cmd, capture_output=True, text=True, timeout=300)
+            if r.returncode != 0:
+                return {"error": (r.stderr or r.stdout)[-300:]}
+            t = json.load(open(out))["times_us"]
+        except (OSError, subprocess.SubprocessError, ValueError, KeyError) as e:
+            return {"error": str(e)[:300]}
+    res = {"keyswitch_us": t.get("keyswitch_us"), "multiply_and_relin_us": t.get("mul_relin_us"), "multiply_and_relin_rescale_us": t.get("mul_relin_rescale_us"),
+           "rotate_us": t.get("rotate_us"), "hoist_rotations_x3_us": t.get("hoist_rotations_us"), "ntt_fwd_32_limbs_us": t.get("ntt_fwd_us"),
+           "modup_us": t.get("modup_us"), "inner_prod_us": t.get("inner_prod_us"), "moddown_x2_us": t.get("moddown_x2_us"),
+           "source": "oracle/_ref/ref_harness --time 40 --threads 4, run inside this bench"}
+    if t.get("keyswitch_mt_us"):
+        res["keyswitch_per_s_4_threads"] = 4e6 / t["keyswitch_mt_us"]
+    return res
+
+
 def _claim_stdout():
     """stdout carries the one JSON line and nothing else: libraries that write to file descriptor 1 on their own (NCCL's
     version banner does) are pointed at stderr, and the line goes out through a private copy of the original descriptor"""
@@ -402,7 +490,7 @@ def main():
     ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--batch", type=int, default=8, help="key switches per step per GPU")
+    ap.add_argument("--batch", type=int, default=64, help="key switches per step per GPU")
     ap.add_argument("--keys", type=int, default=4, help="distinct evaluation keys cycled over")
     ap.add_argument("--streams", type=int, default=4, help="CUDA streams the batch of independent key switches is spread over")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -417,7 +505,7 @@ def main():
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
 
     if args.impl == "reference":
-        run_reference_arm(args, rank, out_stream)
+        run_reference_arm(args, rank, world, out_stream)
         return
 
     import numpy as np
@@ -449,10 +537,17 @@ def main():
     keys = [ph.relin_key.from_numpy(ctx, [synth.poly(N, primes, 2, seed, 10 + 8 * k + d) for d in range(BETA)])
             for k in range(K)]
     key_tabs = [k.pointer_table() for k in keys]
-    host_ct3 = [torch.from_numpy(synth.poly(N, primes[:LEVEL], 3, seed, 200 + b).view(np.int64)).pin_memory()
-                for b in range(B)]
-    dev_ct3 = [t.cuda() for t in host_ct3]          # resident inputs: (c0, c1, c2)
-    host_out = [torch.empty(2, LEVEL, N, dtype=torch.int64).pin_memory() for _ in range(B)]
+    # ciphertexts (c0, c1, c2): limb j uniform in [0, q_j), drawn on the device (64 of them from the host generator would
+    # take half a minute); the e2e arm copies them out to pinned host buffers once, before its timed region
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(seed)
+    dev_ct3 = [torch.stack([torch.randint(0, int(q), (3, N), dtype=torch.int64, device="cuda", generator=gen) for q in primes[:LEVEL]], dim=1)
+               for _ in range(B)]
+    n_host = 0 if args.no_e2e else B
+    host_ct3 = [torch.empty(3, LEVEL, N, dtype=torch.int64).pin_memory() for _ in range(n_host)]
+    for h, d in zip(host_ct3, dev_ct3):
+        h.copy_(d)
+    host_out = [torch.empty(2, LEVEL, N, dtype=torch.int64).pin_memory() for _ in range(n_host)]
     S = max(1, min(args.streams, B))
     wss = [ctx.workspace(_native.OP_KEYSWITCH, LEVEL) for _ in range(S)]
     stream = torch.cuda.current_stream()
@@ -601,14 +696,15 @@ def main():
                         "note": "latency of one key switch sharded by RNS limb (weak-scaling value above is data parallel)"}
 
     # ---- per-kernel timing (live, CUDA events on the launching stream) and roofline -------------
-    roofline, kernels = None, None
+    roofline, roofline_issue, kernels = None, None, None
     if rank == 0:
         # one stream here: a kernel's event pair must time that kernel alone, not a mix of streams
         check(LIB.b2_profile_start(ctx._h))
         prof_steps = 2
         ws0, ws0_bytes = wss[0]
+        PB = min(B, 8)
         for _ in range(prof_steps):
-            for b in range(B):
+            for b in range(PB):
                 t = dev_ct3[b]
                 check(LIB.b2_keyswitch(ctx._h, LEVEL, t[2].data_ptr(), key_tabs[b % K].ctypes.data, BETA, t.data_ptr(),
                                        ws0.data_ptr(), ws0_bytes, stream.cuda_stream))
@@ -619,30 +715,49 @@ def main():
         check(LIB.b2_profile_stop(ctx._h, names, 4096, tot, cnt, 64, ctypes.byref(n_out)))
         nm = names.value.decode().strip(";").split(";")
         alg = kernel_alg_bytes_per_keyswitch()
-        n_ks = prof_steps * B
+        n_ks = prof_steps * PB
         total_ms = sum(tot[i] for i in range(n_out.value))
+        # what ncu saw for the same kernels (committed summary of one capture; cold caches, one stream)
+        ncu = {}
+        tp = os.path.join(ROOT, "profiles", "ncu_traffic.json")
+        if os.path.exists(tp):
+            ncu = json.load(open(tp))
         kernels = {}
         for i in range(n_out.value):
             per_ks_ms = tot[i] / n_ks
             gbs = alg.get(nm[i], 0) / (per_ks_ms * 1e-3) / 1e9 if per_ks_ms > 0 else 0.0
+            rec = ncu.get(nm[i], {})
             kernels[nm[i]] = {"launches_per_keyswitch": cnt[i] / n_ks, "us_per_keyswitch": 1e3 * per_ks_ms,
-                              "share": tot[i] / total_ms, "alg_gbs": gbs}
-        top = max(kernels, key=lambda k: kernels[k]["us_per_keyswitch"])
+                              "share": tot[i] / total_ms, "alg_bytes_per_keyswitch": alg.get(nm[i]), "alg_gbs": gbs,
+                              "dram_bytes_per_keyswitch": rec.get("dram_bytes_per_keyswitch"),
+                              "warp_instructions_per_keyswitch": rec.get("warp_instructions_per_keyswitch"),
+                              "bound": rec.get("bound")}
         peak, peak_kind = peaks()
-        traffic = None
-        tp = os.path.join(ROOT, "profiles", "ncu_traffic.json")
-        if os.path.exists(tp):
-            traffic = json.load(open(tp)).get(top, {}).get("dram_bytes_per_keyswitch")
-        roofline = {"kernel": top, "bound": "hbm", "achieved": kernels[top]["alg_gbs"], "peak": peak, "unit": "GB/s",
-                    "frac": kernels[top]["alg_gbs"] / peak, "peak_kind": peak_kind, "traffic": traffic,
-                    "alg_bytes_per_keyswitch": alg.get(top)}
+        ks_us = 1e3 * ms / (B * args.steps)
+        dram = [k.get("dram_bytes_per_keyswitch") for k in kernels.values()]
+        roofline = {"what": "one hybrid key switch (all its kernels)", "bound": "hbm", "alg_bytes": KS_BYTES, "us_per_keyswitch": ks_us,
+                    "achieved": KS_BYTES / (ks_us * 1e-6) / 1e9, "peak": peak, "unit": "GB/s",
+                    "frac": KS_BYTES / (ks_us * 1e-6) / 1e9 / peak, "peak_kind": peak_kind,
+                    "traffic": sum(dram) if dram and all(d is not None for d in dram) else None,
+                    "traffic_note": "sum over the key switch's kernels of dram read + write bytes, each kernel captured with cold caches (upper bound)"}
+        instr = [k.get("warp_instructions_per_keyswitch") for k in kernels.values()]
+        if instr and all(v is not None for v in instr) and clocks and clocks.get("sm_mhz"):
+            slots = 148 * 4 * clocks["sm_mhz"] * 1e6
+            roofline_issue = {"bound": "issue", "warp_instructions_per_keyswitch": sum(instr), "issue_slots_per_s": slots,
+                              "achieved": sum(instr) / (ks_us * 1e-6), "frac": sum(instr) / (ks_us * 1e-6) / slots, "unit": "warp instructions/s",
+                              "floor_us_per_keyswitch": 1e6 * sum(instr) / slots}
 
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         cpu = cpu_baseline_sample()
 
+    hmult = None
+    if not args.no_extras:
+        hmult = hmult_section(torch, dist, ctx, LIB, check, _native, dev_ct3, key_tabs, world, S)
+    reference_gpu = None
     ntt, bootstrap, compositions, bsgs = None, None, None, None
     if rank == 0 and world == 1 and not args.no_extras:
+        reference_gpu = reference_gpu_section()
         ntt = ntt_section(ph, ctx, torch, LIB, check, N, len(primes))
         compositions = compositions_section(ph, ctx, torch, np, synth, primes, keys, N, LEVEL)
         del dev_ct3, keys, stage
@@ -652,24 +767,22 @@ def main():
         bootstrap = bootstrap_section(ph, torch, np)
 
     if rank == 0:
-        peak, peak_kind = peaks()
-        ks_us = 1e3 * ms / (B * args.steps)
         line = {
             "metric": "KeySwitch/s", "value": value, "unit": "KeySwitch/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "u64", "data": "synthetic",
-            "config": {"workload": WORKLOAD, "batch_per_step_per_gpu": B, "distinct_keys": K, "streams": S,
-                       "l2": "inputs larger than L2 (one step touches ~670 MB)", "parallelism": f"dp{world}"},
+            "config": config_dict(args, world),
             "clocks": clocks,
             "e2e": {"value": e2e_value, "unit": "KeySwitch/s", "h2d_bytes_per_step": B * 3 * LEVEL * LIMB_BYTES,
                     "d2h_bytes_per_step": B * 2 * LEVEL * LIMB_BYTES, "api": "pyPhantom.relinearize", "steps": e2e_steps, "streams": len(streams), "pcie": pcie},
             "gpu_launches": launches,
+            "device_status": ctx.device_status(),
             "roofline": roofline,
-            "roofline_keyswitch": {"bound": "hbm", "alg_bytes": KS_BYTES, "us_per_keyswitch": ks_us,
-                                   "achieved": KS_BYTES / (ks_us * 1e-6) / 1e9 * 1.0, "peak": peak, "unit": "GB/s",
-                                   "frac": KS_BYTES / (ks_us * 1e-6) / 1e9 / peak, "peak_kind": peak_kind},
+            "roofline_issue": roofline_issue,
             "kernels": kernels,
             "cpu_baseline": cpu,
+            "reference_gpu": reference_gpu,
+            "hmult_batch64": hmult,
             "ntt": ntt,
             "compositions": compositions,
             "bsgs_matvec": bsgs,

@@ -4,20 +4,29 @@
 // CPU oracle (ckks_oracle.c, compiled into this binary for the data generator and the hash).
 //
 // usage: ref_harness --logn 12 --bits 50,36,36,36,36,36,50,50 --special 2 --level 6 --seed 7
-//                    --steps 1,2,-1 --out case.json [--time ITERS]
+//                    --steps 1,2,-1 --out case.json [--time ITERS [--threads T]]
+//        ref_harness --bootstrap DIR [--boot-dense 1]   the reference's own bootstrap on its test's chain (N = 2^16):
+//                    milliseconds, its decode's error, and the key / result / message files for decoding elsewhere
+//        ref_harness --selftest 1 --logn .. --bits .. --special ..   encode -> decode and encrypt -> decrypt -> decode
 // Needs a CUDA device (the reference has no CPU path for any of this).
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
 #include <cmath>
+#include <algorithm>
+#include <atomic>
+#include <chrono>
 #include <fstream>
 #include <functional>
+#include <random>
 #include <sstream>
 #include <string>
+#include <thread>
 #include <vector>
 
 #include "phantom.h"
 #include "bsgs.h"
+#include "bootstrap.h"
 #include "ckks_oracle.h"
 
 using namespace phantom;
@@ -98,8 +107,122 @@ static double time_us(const std::function<void()> &op, int warm, int iters) {
     return ms * 1000.0 / iters;
 }
 
+// ---- the reference's bootstrap on the chain of its own round-trip test (test/bootstrap_test.cu:517-662): same parameters
+// (N = 2^16, 58 | 40x4 | 58x12 | 29x3 | P 58x4, encapsulation weight 128, 2^15 real slots uniform in (-0.5, 0.5) from
+// mt19937_64(0xB007B007), scale 2^40, input left on two primes); dense: the test's default secret, else weight 128 as
+// python/examples/bootstrap.py. Writes DIR/boot_sk.bin, boot_ct.bin (the refreshed ciphertext), boot_msg.bin (doubles).
+static int run_bootstrap(const std::string &dir, bool dense) {
+    const size_t log_n = 16, N = size_t(1) << log_n, HW = 128;
+    const double user_scale = std::pow(2.0, 40);
+    EncryptionParameters parms(scheme_type::ckks);
+    parms.set_poly_modulus_degree(N);
+    parms.set_special_modulus_size(4);
+    std::vector<int> bits{58};
+    bits.insert(bits.end(), 4, 40);
+    bits.insert(bits.end(), 12, 58);
+    bits.insert(bits.end(), 3, 29);
+    bits.insert(bits.end(), 4, 58);
+    parms.set_coeff_modulus(CoeffModulus::Create(N, bits));
+    auto c2s = build_c2s_diagonals((int) log_n, {5, 5, 5});
+    auto s2c = build_s2c_diagonals((int) log_n, {5, 5, 5});
+    std::vector<int> steps = c2s_required_rotation_steps(c2s, (int) (N >> 1));
+    for (int v : c2s_required_rotation_steps(s2c, (int) (N >> 1))) steps.push_back(v);
+    std::sort(steps.begin(), steps.end());
+    steps.erase(std::unique(steps.begin(), steps.end()), steps.end());
+    auto elts = get_elts_from_steps(steps, N);
+    elts.push_back((uint32_t) (2 * N - 1));
+    parms.set_galois_elts(elts);
+    PhantomContext context(parms);
+    PhantomSecretKey sk;
+    if (dense) sk = PhantomSecretKey(context);
+    else sk.generate_sparse(context, HW);
+    PhantomCKKSEncoder encoder(context);
+    auto t0 = std::chrono::steady_clock::now();
+    BootstrapKey bk = create_bootstrap_key(context, encoder, sk, HW, 9, user_scale);
+    cudaDeviceSynchronize();
+    const double keygen_s = std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count();
+    const size_t slots = encoder.slot_count();
+    std::mt19937_64 rng(0xB007B007UL);
+    std::uniform_real_distribution<double> dist(-0.5, 0.5);
+    std::vector<double> msg(slots);
+    std::vector<cuDoubleComplex> z(slots);
+    for (size_t i = 0; i < slots; i++) { msg[i] = dist(rng); z[i] = make_cuDoubleComplex(msg[i], 0.0); }
+    PhantomPlaintext pt;
+    encoder.encode(context, z, user_scale, pt);
+    PhantomCiphertext ct;
+    sk.encrypt_symmetric(context, pt, ct);
+    mod_switch_to_inplace(context, ct, context.total_parm_size() - 2);
+    PhantomCiphertext out = bootstrap(context, encoder, ct, bk, user_scale);   // warm-up: tables, allocations
+    cudaDeviceSynchronize();
+    std::vector<double> ms;
+    for (int it = 0; it < 3; it++) {
+        auto b0 = std::chrono::steady_clock::now();
+        out = bootstrap(context, encoder, ct, bk, user_scale);
+        cudaDeviceSynchronize();
+        ms.push_back(1e3 * std::chrono::duration<double>(std::chrono::steady_clock::now() - b0).count());
+    }
+    std::sort(ms.begin(), ms.end());
+    PhantomPlaintext dec;
+    sk.decrypt(context, out, dec);
+    std::vector<cuDoubleComplex> got;
+    encoder.decode(context, dec, got);
+    double max_err = 0, sum = 0;
+    for (size_t i = 0; i < slots; i++) { const double e = std::fabs(got[i].x - msg[i]); max_err = std::max(max_err, e); sum += e; }
+    {
+        std::ofstream f1(dir + "/boot_sk.bin", std::ios::binary), f2(dir + "/boot_ct.bin", std::ios::binary), f3(dir + "/boot_msg.bin", std::ios::binary);
+        sk.save(f1);
+        out.save(f2);
+        f3.write(reinterpret_cast<const char *>(msg.data()), msg.size() * sizeof(double));
+    }
+    printf("{\"reference_bootstrap\": {\"secret\": \"%s\", \"ms_median\": %.3f, \"ms_min\": %.3f, \"keygen_s\": %.2f, \"out_chain_index\": %zu, "
+           "\"out_limbs\": %zu, \"out_scale_log2\": %.3f, \"own_decode_max_err\": %.6e, \"own_decode_mean_err\": %.6e, \"cuda\": \"%s\"}}\n",
+           dense ? "dense" : "sparse128", ms[1], ms[0], keygen_s, out.chain_index(), out.coeff_modulus_size(), std::log2(out.scale()),
+           max_err, sum / slots, cudaGetErrorString(cudaGetLastError()));
+    return 0;
+}
+
+// encode -> decode, and encode -> encrypt -> decrypt -> decode, with the reference's own encoder: where its decode goes wrong
+static int run_selftest(int logn, const std::vector<int> &bits, int special) {
+    const size_t N = size_t(1) << logn;
+    EncryptionParameters parms(scheme_type::ckks);
+    parms.set_poly_modulus_degree(N);
+    parms.set_coeff_modulus(CoeffModulus::Create(N, bits));
+    parms.set_special_modulus_size(special);
+    PhantomContext context(parms);
+    PhantomCKKSEncoder encoder(context);
+    const size_t slots = encoder.slot_count();
+    std::vector<cuDoubleComplex> z(slots), got;
+    for (size_t j = 0; j < slots; j++) z[j] = make_cuDoubleComplex(cos((double) j), sin(2.0 * j) / 2);
+    auto err = [&](const std::vector<cuDoubleComplex> &g) {
+        double e = 0;
+        for (size_t j = 0; j < slots; j++) e = std::max(e, std::hypot(g[j].x - z[j].x, g[j].y - z[j].y));
+        return e;
+    };
+    const double scale = 1099511627776.0;
+    for (size_t chain = 1; chain < context.total_parm_size(); chain += 2) {
+        PhantomPlaintext pt;
+        encoder.encode(context, z, scale, pt, chain);
+        encoder.decode(context, pt, got);
+        printf("selftest: chain %zu (%zu limbs) encode->decode max error %.3e\n", chain, context.get_context_data(chain).parms().coeff_modulus().size(), err(got));
+    }
+    PhantomSecretKey sk(context);
+    PhantomPlaintext pt;
+    encoder.encode(context, z, scale, pt);
+    PhantomCiphertext ct;
+    sk.encrypt_symmetric(context, pt, ct);
+    PhantomPlaintext dec;
+    sk.decrypt(context, ct, dec);
+    encoder.decode(context, dec, got);
+    printf("selftest: encrypt->decrypt->decode max error %.3e (plaintext chain %zu scale 2^%.1f)\n", err(got), dec.chain_index(), std::log2(dec.scale()));
+    PhantomPlaintext dec2 = sk.decrypt(context, ct);
+    encoder.decode(context, dec2, got);
+    printf("selftest: decrypt (returning form) ->decode max error %.3e (plaintext chain %zu scale 2^%.1f)\n", err(got), dec2.chain_index(), std::log2(dec2.scale()));
+    return 0;
+}
+
 int main(int argc, char **argv) {
-    int logn = 12, special = 2, level = -1, time_iters = 0;
+    int logn = 12, special = 2, level = -1, time_iters = 0, n_threads = 0, selftest = 0, boot_dense = 0;
+    std::string boot_dir;
     std::vector<int> bsgs;  // {baby steps M, giant steps G}: also run the BSGS matrix-vector driver
     uint64_t seed = 1;
     std::vector<int> bits = {50, 36, 36, 36, 36, 36, 50, 50}, steps = {1, 2, -1};
@@ -119,8 +242,14 @@ int main(int argc, char **argv) {
         else if (k == "--interop-read") interop_read = v;
         else if (k == "--interop-prefix") interop_prefix = v;
         else if (k == "--time") time_iters = atoi(v);
+        else if (k == "--threads") n_threads = atoi(v);
+        else if (k == "--selftest") selftest = atoi(v);
+        else if (k == "--bootstrap") boot_dir = v;
+        else if (k == "--boot-dense") boot_dense = atoi(v);
         else { fprintf(stderr, "unknown arg %s\n", argv[i]); return 2; }
     }
+    if (!boot_dir.empty()) return run_bootstrap(boot_dir, boot_dense != 0);
+    if (selftest) return run_selftest(logn, bits, special);
     const size_t N = size_t(1) << logn;
     const size_t size_QP = bits.size(), size_P = special, size_Q = size_QP - size_P;
     const size_t l = level < 0 ? size_Q : size_t(level);   // number of Q limbs of the data
@@ -272,6 +401,34 @@ int main(int argc, char **argv) {
         if (time_iters) {
             g_times.push_back({"keyswitch_us", time_us([&] {
                 keyswitch_inplace(context, ct, c2.get(), rlk, true, s); }, 5, time_iters)});
+            if (n_threads > 1) {
+                // the same call from n_threads host threads, each on its own per-thread default stream with its own ciphertext and
+                // input: keyswitch_mt_us = wall time per round of n_threads concurrent key switches
+                std::vector<std::thread> th;
+                std::atomic<int> ready{0};
+                std::atomic<bool> go{false};
+                std::vector<double> secs(n_threads, 0.0);
+                for (int t = 0; t < n_threads; t++)
+                    th.emplace_back([&, t] {
+                        const auto &ts = cudaStreamPerThread;
+                        PhantomCiphertext my = make_ct(primes, chain, 2, N, l, scale, seed, 1);
+                        auto my_c2 = make_cuda_auto_ptr<uint64_t>(l * N, ts);
+                        cudaMemcpyAsync(my_c2.get(), h.data(), h.size() * 8, cudaMemcpyHostToDevice, ts);
+                        for (int i = 0; i < 5; i++) keyswitch_inplace(context, my, my_c2.get(), rlk, true, ts);
+                        cudaStreamSynchronize(ts);
+                        ready++;
+                        while (!go.load()) std::this_thread::yield();
+                        auto b0 = std::chrono::steady_clock::now();
+                        for (int i = 0; i < time_iters; i++) keyswitch_inplace(context, my, my_c2.get(), rlk, true, ts);
+                        cudaStreamSynchronize(ts);
+                        secs[t] = std::chrono::duration<double>(std::chrono::steady_clock::now() - b0).count();
+                    });
+                while (ready.load() < n_threads) std::this_thread::yield();
+                go = true;
+                for (auto &t : th) t.join();
+                g_times.push_back({"keyswitch_mt_us", 1e6 * *std::max_element(secs.begin(), secs.end()) / time_iters});
+                g_times.push_back({"keyswitch_mt_threads", (double) n_threads});
+            }
         }
     }
 

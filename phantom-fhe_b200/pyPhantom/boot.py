@@ -44,13 +44,16 @@ def _elt(step, N):
 def bootstrap_required_galois_elts(log_n, stages_per_layer=(5, 5, 5)):
     """python/src/binding.cu:301-318: Galois elements of every rotation CoeffToSlot and SlotToCoeff use,
     plus the conjugation 2N - 1. `stages_per_layer` is CoeffToSlot's grouping of the log2(N/2) radix-2
-    stages; SlotToCoeff always runs in two layers."""
+    stages; SlotToCoeff always runs in two layers. On chains with short CoeffToSlot primes the key runs CoeffToSlot
+    in two layers as well (see create_bootstrap_key), whatever the grouping given here: the list covers both."""
     N = 1 << log_n
     stages = list(stages_per_layer)
     if sum(stages) != log_n - 1:
         stages = bootmath.split_stages(log_n - 1, C2S_LAYERS)
-    steps = bootmath.required_rotation_steps(log_n, stages, bootmath.split_stages(log_n - 1, S2C_LAYERS))
-    return [_elt(s, N) for s in steps] + [2 * N - 1]
+    two = bootmath.split_stages(log_n - 1, S2C_LAYERS)
+    steps = set(bootmath.required_rotation_steps(log_n, stages, two))
+    steps.update(bootmath.required_rotation_steps(log_n, stages if len(stages) == 2 else two, two))
+    return [_elt(s, N) for s in sorted(steps)] + [2 * N - 1]
 
 
 # ---- arithmetic on ciphertexts with (level, scale) bookkeeping: the `ops` of bootmath ---------------------
@@ -196,8 +199,9 @@ class CtOps:
 class _Layer:
     """the LayerPlan of bootmath with every pre-rotated diagonal encoded at (limbs, scale) and resident in HBM"""
 
-    def __init__(self, ctx, encoder, plan, limbs, scale, value_factor=1.0):
+    def __init__(self, ctx, encoder, plan, limbs, scale, value_factor=1.0, rescales=1):
         self.limbs, self.scale, self.n = limbs, float(scale), plan.n
+        self.rescales = rescales  # primes the layer's plaintext scale spans: that many rescales end the transform
         self.baby_steps = [(b, (b * plan.unit) % plan.n) for b in plan.babies]
         chain_index = ctx.size_Q - limbs + 1
         self.giants = []  # (rotation step, [baby position], device pointer table, plaintext tensors)
@@ -306,18 +310,33 @@ def create_bootstrap_key(context, encoder, dense_sk, sparse_hamming_weight=128, 
     bk.small.to_dense = dense_sk._kswitch_key(ctx, sparse.data)
     bk.relin = dense_sk.gen_relinkey(ctx)
     # linear transforms
-    c2s_stages = list(stages_per_layer) if stages_per_layer and sum(stages_per_layer) == logn else bootmath.split_stages(logn, C2S_LAYERS)
-    s2c_stages = bootmath.split_stages(logn, S2C_LAYERS)
     q0 = float(ctx.primes[0])
     eval_top = sQ - C2S_LAYERS                     # limbs at EvalRound's input
     bk.eval_scale = float(ctx.primes[eval_top - 1])
     # CoeffToSlot: slots of the raised ciphertext read at scale q0*K are t/(q0 K); the unnormalised inverse
-    # FFT multiplies by n and the real/imaginary split wants another 1/2: both go into the plaintext scales
+    # FFT multiplies by n and the real/imaginary split wants another 1/2: that factor, eval_scale / (2 n q0 K) (about
+    # 2^-21 at N = 2^16), has to come out of the plaintext scales, i.e. out of the bits the three primes provide.
     sigma0 = q0 * K_RANGE
-    ratio = (bk.eval_scale / (2.0 * n * sigma0)) ** (1.0 / C2S_LAYERS)
-    for i, layer in enumerate(bootmath.fft_layers(n, c2s_stages, True)):
-        limbs = sQ - i
-        bk.c2s.append(_Layer(ctx, encoder, bootmath.LayerPlan(layer, n), limbs, float(ctx.primes[limbs - 1]) * ratio))
+    whole = bk.eval_scale / (2.0 * n * sigma0)
+    wide = float(ctx.primes[sQ - 1]) * float(ctx.primes[sQ - 2]) * whole
+    user_split = list(stages_per_layer) if stages_per_layer and sum(stages_per_layer) == logn else None
+    if (user_split is None or len(user_split) == 2) and wide < 2.0 ** 60:
+        # Short CoeffToSlot primes (the reference's chains give it three 29-bit ones): three even layers would encode
+        # their diagonals with (87 - 21) / 3 = 22 bits each, and the 2e-6 error that leaves in u = t/(q0 K) is what
+        # EvalRound's second-order terms turn into most of the bootstrap's final error. Two layers instead: the first
+        # spends two primes (plaintext scale p p' 2^-21, about 2^37, two rescales), the second the third prime at
+        # its full 29 bits - 2^-27 in u, at the price of more diagonals per layer.
+        c2s_stages = user_split or bootmath.split_stages(logn, 2)
+        la, lb = bootmath.fft_layers(n, c2s_stages, True)
+        bk.c2s.append(_Layer(ctx, encoder, bootmath.LayerPlan(la, n), sQ, wide, rescales=2))
+        bk.c2s.append(_Layer(ctx, encoder, bootmath.LayerPlan(lb, n), sQ - 2, float(ctx.primes[sQ - 3])))
+    else:
+        c2s_stages = user_split if user_split and len(user_split) == C2S_LAYERS else bootmath.split_stages(logn, C2S_LAYERS)
+        ratio = whole ** (1.0 / C2S_LAYERS)
+        for i, layer in enumerate(bootmath.fft_layers(n, c2s_stages, True)):
+            limbs = sQ - i
+            bk.c2s.append(_Layer(ctx, encoder, bootmath.LayerPlan(layer, n), limbs, float(ctx.primes[limbs - 1]) * ratio))
+    s2c_stages = bootmath.split_stages(logn, S2C_LAYERS)
     # SlotToCoeff: the first layer at its own prime; the scale of the last one depends on the caller's scale
     # (see _configure_scale), so its plan is kept for re-encoding
     s2c_top = eval_top - EVAL_LEVELS
@@ -458,7 +477,9 @@ def linear_transform(ctx, bk, ct, layer, ops):
                 part.record_stream(main)
         piece = ct._like(part, scale=ct._scale * layer.scale)
         total = piece if total is None else ops.add(total, piece)
-    return ops.rescale(total)
+    for _ in range(layer.rescales):
+        total = ops.rescale(total)
+    return total
 
 
 def _times_i(ctx, bk, ct, negate=False):

@@ -1,6 +1,7 @@
 """Bootstrapping end to end through the pyPhantom surface (python/examples/bootstrap.py is the model):
-deplete a ciphertext, bootstrap it, decrypt and compare with the message. N = 2^12 and 2^13 keep the
-test short; the pipeline is the one that runs at N = 2^16."""
+deplete a ciphertext, bootstrap it, decrypt and compare with the message. N = 2^12 and 2^13 keep most
+tests short; test_full_size_bootstrap_meets_the_reference_bar runs N = 2^16 against the reference test's
+own bar."""
 import importlib
 import math
 
@@ -63,6 +64,40 @@ def test_bootstrap_round_trip(log_n, n_user, alpha, c2s_bits, sparse_main):
     sq = ph.rescale_to_next(ctx, ph.multiply_and_relin(ctx, out, out, bk.relin))
     got2 = enc.decode_double_vector(ctx, sk.decrypt(ctx, sq))
     assert np.max(np.abs(got2 - msg * msg)) < 1e-4
+
+
+@pytest.mark.parametrize("chain", ["example", "bench"])
+def test_full_size_bootstrap_meets_the_reference_bar(chain):
+    """N = 2^16 with the inputs of the reference's own round-trip test (test/bootstrap_test.cu:517-662): 2^15 real slots
+    uniform in (-0.5, 0.5) from mt19937_64(0xB007B007), scale 2^40, encapsulation weight 128, input left on two primes,
+    and its bar, max |error| <= 5e-6 (:654). "example": the chain and sparse secret (weight 128) of
+    python/examples/bootstrap.py, 58 | 40x4 | 58x12 | 29x3 | P 58x4; "bench": the 24-limb dnum-3 chain of bench.py,
+    58 | 40x8 | 58x12 | 29x3 | P 58x8, sparse secret of weight 192. tests/golden/bootstrap/ref_bootstrap_n16.json holds what the
+    reference itself gives on the example chain on a B200 (8.6e-5, 125 ms) beside this pipeline."""
+    from gpu_helpers import mt19937_64_doubles
+    log_n = 16
+    N, n = 1 << log_n, 1 << (log_n - 1)
+    n_user, alpha, hw = (4, 4, 128) if chain == "example" else (8, 8, 192)
+    bits = [58] + [40] * n_user + [58] * 12 + [29] * 3 + [58] * alpha
+    parms = ph.params(ph.scheme_type.ckks)
+    parms.set_poly_modulus_degree(N)
+    parms.set_special_modulus_size(alpha)
+    parms.set_coeff_modulus(ph.create_coeff_modulus(N, bits))
+    parms.set_galois_elts(ph.bootstrap_required_galois_elts(log_n, [5, 5, 5]))
+    ctx = ph.context(parms)
+    sk = ph.secret_key(ctx, seed=2026)
+    sk.generate_sparse(ctx, hw)
+    enc = ph.ckks_encoder(ctx)
+    scale = 2.0 ** 40
+    bk = ph.create_bootstrap_key(ctx, enc, sk, sparse_hamming_weight=128, eval_mod_levels=9, user_scale=scale)
+    msg = mt19937_64_doubles(0xB007B007, n, -0.5, 0.5)
+    ct = sk.encrypt_symmetric(ctx, enc.encode_double_vector(ctx, msg, scale, chain_index=1))
+    ph.mod_switch_to_inplace(ctx, ct, ctx.total_parm_size() - 2)
+    out = ph.bootstrap(ctx, enc, ct, bk, scale)
+    assert out.coeff_modulus_size() == n_user + 1 and out.scale() == scale
+    err = np.abs(enc.decode_double_vector(ctx, sk.decrypt(ctx, out)) - msg)
+    assert err.max() <= 5e-6, err.max()
+    assert ctx.device_status() == 0
 
 
 def test_stages_against_the_plain_computation():
