@@ -671,13 +671,21 @@ def main():
         pcie = {"h2d_gbs": 40 * 3 * LEVEL * LIMB_BYTES / dt / 1e9, "d2h_gbs": 40 * 2 * LEVEL * LIMB_BYTES / dt / 1e9,
                 "keyswitch_per_s_ceiling": 40 / dt, "what": "bare pinned copies of one call's input and result, both directions at once"}
 
-    # ---- N > 1: ONE key switch with its RNS limbs spread over the ranks (two NCCL all-gathers inside) ---------
+    # ---- N > 1: key switches with their RNS limbs spread over the ranks (NCCL all-gathers between the phases) ---------
     limb_sharded = None
     if world > 1:
-        from pyPhantom.parallel import LimbShardedKeySwitch
-        sh = LimbShardedKeySwitch(ctx)
+        from pyPhantom.parallel import BatchedLimbShardedKeySwitch
+        sh = BatchedLimbShardedKeySwitch(ctx)
         ws_sh, _ = sh.workspace(LEVEL)
         c2_sh, ct_sh = dev_ct3[0][2], dev_ct3[0][:2].clone()
+        # what the sharded ranks produce is what one GPU's b2_keyswitch produces: gather the limbs and compare (every rank)
+        want = dev_ct3[0][:2].clone()
+        ws1, ws1_bytes = wss[0]
+        check(LIB.b2_keyswitch(ctx._h, LEVEL, c2_sh.data_ptr(), key_tabs[0].ctypes.data, BETA, want.data_ptr(), ws1.data_ptr(), ws1_bytes,
+                               stream.cuda_stream))
+        sh.keyswitch(LEVEL, c2_sh, keys[0], ct_sh, ws_sh)
+        sh.allgather_ct(LEVEL, ct_sh)
+        ok = torch.equal(ct_sh, want)
         for _ in range(3):
             sh.keyswitch(LEVEL, c2_sh, keys[0], ct_sh, ws_sh)
         barrier()
@@ -690,10 +698,66 @@ def main():
         barrier()
         t = torch.tensor([s0.elapsed_time(s1)], device="cuda")
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        us = 1e3 * float(t.item()) / n_sh
-        limb_sharded = {"us_per_keyswitch": us, "keyswitch_per_s": 1e6 / us, "ranks": world,
-                        "nvlink_bytes_received_per_gpu_per_keyswitch": int((LEVEL + 2 * SPECIAL) * LIMB_BYTES * (1 - 1 / world)),
-                        "note": "latency of one key switch sharded by RNS limb (weak-scaling value above is data parallel)"}
+        us_one = 1e3 * float(t.item()) / n_sh
+        # throughput: batches of LB ciphertexts, NB batches in flight on two lanes (own stream and communicator each)
+        LB, NB = max(1, min(8, B // 4)), 4
+        lanes = sh.make_lanes(2)
+        wsb = [sh.batch_workspace(LEVEL, LB)[0] for _ in lanes]
+        batches = [(torch.stack([dev_ct3[(i * LB + b) % B][2] for b in range(LB)]), torch.stack([dev_ct3[(i * LB + b) % B][:2] for b in range(LB)]))
+                   for i in range(NB)]
+        want_b = batches[0][1][0].clone()
+        check(LIB.b2_keyswitch(ctx._h, LEVEL, batches[0][0][0].data_ptr(), key_tabs[0].ctypes.data, BETA, want_b.data_ptr(), ws1.data_ptr(), ws1_bytes,
+                               stream.cuda_stream))
+        sh.pipeline(LEVEL, batches, keys[0], lanes, wsb)
+        got_b = batches[0][1][0].clone()
+        sh.allgather_ct(LEVEL, got_b)
+        ok = ok and torch.equal(got_b, want_b)
+        flag = torch.tensor([1 if ok else 0], device="cuda")
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        if int(flag.item()) != 1:
+            raise RuntimeError("limb-sharded key switch differs from the one-GPU key switch")
+        for _ in range(2):
+            sh.pipeline(LEVEL, batches, keys[0], lanes, wsb)
+        barrier()
+        n_pb = max(5, min(args.steps, 20))
+        s0.record(stream)
+        for _ in range(n_pb):
+            sh.pipeline(LEVEL, batches, keys[0], lanes, wsb)
+        s1.record(stream)
+        barrier()
+        t = torch.tensor([s0.elapsed_time(s1)], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        us_b = 1e3 * float(t.item()) / (n_pb * NB * LB)
+        # the same batches with the exchanges alone (no kernels): what the collectives cost by themselves
+        tviews = [sh._views(LEVEL, LB, w) for w in wsb]
+        def exchanges():
+            for i in range(NB):
+                st, grp = lanes[i % 2]
+                st.wait_stream(stream)
+                with torch.cuda.stream(st):
+                    from pyPhantom.parallel import allgather_limbs
+                    allgather_limbs(tviews[i % 2][0], LEVEL, sh.rank, sh.world, grp)
+                    allgather_limbs(tviews[i % 2][1], SPECIAL, sh.rank, sh.world, grp)
+            for st, _ in lanes:
+                stream.wait_stream(st)
+        exchanges()
+        barrier()
+        s0.record(stream)
+        for _ in range(n_pb):
+            exchanges()
+        s1.record(stream)
+        barrier()
+        t = torch.tensor([s0.elapsed_time(s1)], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        us_x = 1e3 * float(t.item()) / (n_pb * NB * LB)
+        rx = int((LEVEL + 2 * SPECIAL) * LIMB_BYTES * (1 - 1 / world))
+        limb_sharded = {"verified": True, "ranks": world, "keyswitch_per_s": 1e6 / us_b, "us_per_keyswitch": us_b,
+                        "batch_per_lane": LB, "batches_in_flight": NB, "lanes": 2,
+                        "one_ciphertext_latency_us": us_one,
+                        "nvlink_bytes_received_per_gpu_per_keyswitch": rx,
+                        "nvlink_gbs_per_gpu": rx / (us_b * 1e-6) / 1e9, "nvlink_frac_of_900": rx / (us_b * 1e-6) / 1e9 / 900.0,
+                        "collectives_alone_us_per_keyswitch": us_x, "collectives_share": us_x / us_b,
+                        "note": "every ciphertext's limbs are spread over all ranks (the weak-scaling value above is data parallel)"}
 
     # ---- per-kernel timing (live, CUDA events on the launching stream) and roofline -------------
     roofline, roofline_issue, kernels = None, None, None

@@ -250,6 +250,19 @@ int b2_shard_keyswitch_phase(b2_ctx *ctx, size_t size_Ql, int phase, const uint6
                              const uint64_t *const *evk, size_t n_evk, uint64_t *d_ct, void *d_ws,
                              size_t ws_bytes, void *stream);
 
+/* The same three phases for `batch` ciphertexts at once, all switched with one key: d_c2 [batch][size_Ql][N], d_ct
+ * [batch][2][size_Ql][N]. Every kernel of a phase is one launch over the whole batch, so a rank that owns an eighth of the
+ * limbs still fills its GPU. Workspace (b2_shard_batch_workspace_bytes), in limbs of N words:
+ *   T   [size_Ql][batch]           scaled coefficient form of c2; this rank's Q limbs are one contiguous block
+ *   CXP [alpha][2][batch]          P limbs of both polynomials; this rank's P limbs are one contiguous block
+ *   UP  [batch][beta][size_Ql + alpha]
+ * so the caller needs ONE all-gather of T after phase 0 and ONE of CXP after phase 1. Needs the tensor-core base
+ * conversion (the default where alpha <= 8). No counterpart in the reference, which has no multi-GPU path. */
+size_t b2_shard_batch_workspace_bytes(const b2_ctx *ctx, size_t size_Ql, size_t batch);
+int b2_shard_keyswitch_phase_batch(b2_ctx *ctx, size_t size_Ql, int phase, size_t batch, const uint64_t *d_c2,
+                                   const uint64_t *const *evk, size_t n_evk, uint64_t *d_ct, void *d_ws,
+                                   size_t ws_bytes, void *stream);
+
 /* Measurement hooks (no counterpart in the reference, which times with CUDATimer around whole
  * calls, include/cuda_wrapper.cuh:191-283). b2_launch_count: kernels launched by this library in
  * this process so far. b2_profile_start/stop: while on, every kernel launch is bracketed by CUDA

@@ -248,6 +248,10 @@ struct b2_ctx {
         double *matd_up = nullptr, *matd_dn = nullptr;
         void *blob = nullptr;
         TcSet tc_up, tc_dn;
+        // the batched phases keep the P limbs of a batch as [P limb][polynomial][set]: this rank's P limbs are one
+        // contiguous block, so the exchange before ModDown is a single all-gather
+        Job *jobs_dn_intt_b = nullptr;
+        TcSet tc_dn_b;
         void *tc_blob = nullptr;
     };
     std::vector<ShardPlan> shard;  // index l; empty until b2_ctx_set_shard
@@ -782,7 +786,7 @@ static uint32_t pipe_grid(const b2_ctx *c, uint32_t total) {
 }
 
 template <int LOG_A, int LOG_B, class Epi, int SRC = 0>
-static void launch_fwd(const b2_ctx *c, const NttArgs &a, uint32_t njobs, const Epi &epi, cudaStream_t s) {
+static void launch_fwd(const b2_ctx *c, const NttArgs &a, uint32_t njobs, const Epi &epi, cudaStream_t s, uint32_t batch = 1) {
     using A = PassCfg<LOG_A>;
     using B = PassCfg<LOG_B>;
     const uint32_t N = 1u << a.logN;
@@ -804,17 +808,18 @@ static void launch_fwd(const b2_ctx *c, const NttArgs &a, uint32_t njobs, const 
     {
         LaunchScope ls(c, s, "ntt_fwd_cols");
         ntt_fwd_pass<LOG_A, A::R_STRIDED, A::R_CONTIG, A::LOG_CC, true, false, EpiStore, SRC>
-            <<<njobs * (N >> (LOG_A + A::LOG_CC)), pass_threads<LOG_A, true>(), 0, s>>>(a, EpiStore{});
+            <<<dim3(njobs * (N >> (LOG_A + A::LOG_CC)), batch), pass_threads<LOG_A, true>(), 0, s>>>(a, EpiStore{});
     }
     NttArgs b = a;
     b.src = a.dst;  // second pass works in place on the first pass's output
+    b.src_lm1 = a.dst_lm1, b.src_bs = a.dst_bs;
     LaunchScope ls(c, s, "ntt_fwd_rows");
     ntt_fwd_pass<LOG_B, B::R_STRIDED, B::R_CONTIG, B::LOG_C, false, true, Epi>
-        <<<njobs * (N >> (LOG_B + B::LOG_C)), pass_threads<LOG_B>(), 0, s>>>(b, epi);
+        <<<dim3(njobs * (N >> (LOG_B + B::LOG_C)), batch), pass_threads<LOG_B>(), 0, s>>>(b, epi);
 }
 
 template <int LOG_A, int LOG_B>
-static void launch_inv(const b2_ctx *c, const NttArgs &a, uint32_t njobs, cudaStream_t s) {
+static void launch_inv(const b2_ctx *c, const NttArgs &a, uint32_t njobs, cudaStream_t s, uint32_t batch = 1) {
     using A = PassCfg<LOG_A>;
     using B = PassCfg<LOG_B>;
     const uint32_t N = 1u << a.logN;
@@ -835,22 +840,29 @@ static void launch_inv(const b2_ctx *c, const NttArgs &a, uint32_t njobs, cudaSt
     {
         LaunchScope ls(c, s, "ntt_inv_rows");
         ntt_inv_pass<LOG_B, B::R_CONTIG, B::R_STRIDED, B::LOG_C, false, false>
-            <<<njobs * (N >> (LOG_B + B::LOG_C)), pass_threads<LOG_B>(), 0, s>>>(a);
+            <<<dim3(njobs * (N >> (LOG_B + B::LOG_C)), batch), pass_threads<LOG_B>(), 0, s>>>(a);
     }
     NttArgs b = a;
     b.src = a.dst;
+    b.src_lm1 = a.dst_lm1, b.src_bs = a.dst_bs;
     LaunchScope ls(c, s, "ntt_inv_cols");
     ntt_inv_pass<LOG_A, A::R_CONTIG, A::R_STRIDED, A::LOG_CC, true, true>
-        <<<njobs * (N >> (LOG_A + A::LOG_CC)), pass_threads<LOG_A, true>(), 0, s>>>(b);
+        <<<dim3(njobs * (N >> (LOG_A + A::LOG_CC)), batch), pass_threads<LOG_A, true>(), 0, s>>>(b);
 }
 
 // SRC != 0: the column pass makes limb job.x from slot job.x / src_div of src (words mod src_q) instead of reading it
+// A batched launch: `batch` polynomial sets, slot s of set b at s * (lm1 + 1) + b * bs of the source / destination
+struct BatchDims {
+    uint32_t batch = 1, src_lm1 = 0, src_bs = 0, dst_lm1 = 0, dst_bs = 0;
+};
+
 template <class Epi, int SRC = 0>
 static int run_fwd(const b2_ctx *c, const uint64_t *src, uint64_t *dst, const Job *jobs, uint32_t njobs, uint32_t first_prime,
-                   const Epi &epi, cudaStream_t s, uint32_t period = 0, uint32_t src_div = 0, uint64_t src_q = 0) {
+                   const Epi &epi, cudaStream_t s, uint32_t period = 0, uint32_t src_div = 0, uint64_t src_q = 0, const BatchDims &bd = BatchDims{}) {
     if (njobs == 0) return B2_OK;
     if (!aligned32(src) || !aligned32(dst) || !epi.aligned()) return fail(B2_EINVAL, "device buffers must be 32-byte aligned (256-bit accesses)");
-    NttArgs a{src, dst, jobs, first_prime, (uint32_t)c->logN, c->d_tw, c->d_mod, nullptr, period, src_div, src_q};
+    NttArgs a{src, dst, jobs, first_prime, (uint32_t)c->logN, c->d_tw, c->d_mod, nullptr, period, src_div, src_q, bd.src_lm1, bd.src_bs, bd.dst_lm1, bd.dst_bs};
+    if (bd.batch != 1 && (c->use_cluster || c->use_pipe)) return fail(B2_EINVAL, "batched transforms need the two-pass kernels");
     if (SRC != 0 && (c->use_cluster || src_div == 0)) return fail(B2_EINVAL, "the on-the-fly source needs the two-pass transform");
     if (c->use_cluster) {
         static thread_local bool attr_set = false;  // per instantiation (one per epilogue type) and thread
@@ -864,11 +876,11 @@ static int run_fwd(const b2_ctx *c, const uint64_t *src, uint64_t *dst, const Jo
         return B2_OK;
     }
     switch (c->logN) {
-        case 16: launch_fwd<8, 8, Epi, SRC>(c, a, njobs, epi, s); break;
-        case 15: launch_fwd<7, 8, Epi, SRC>(c, a, njobs, epi, s); break;
-        case 14: launch_fwd<7, 7, Epi, SRC>(c, a, njobs, epi, s); break;
-        case 13: launch_fwd<6, 7, Epi, SRC>(c, a, njobs, epi, s); break;
-        case 12: launch_fwd<6, 6, Epi, SRC>(c, a, njobs, epi, s); break;
+        case 16: launch_fwd<8, 8, Epi, SRC>(c, a, njobs, epi, s, bd.batch); break;
+        case 15: launch_fwd<7, 8, Epi, SRC>(c, a, njobs, epi, s, bd.batch); break;
+        case 14: launch_fwd<7, 7, Epi, SRC>(c, a, njobs, epi, s, bd.batch); break;
+        case 13: launch_fwd<6, 7, Epi, SRC>(c, a, njobs, epi, s, bd.batch); break;
+        case 12: launch_fwd<6, 6, Epi, SRC>(c, a, njobs, epi, s, bd.batch); break;
         default: return fail(B2_ESIZE, "unsupported polynomial degree");
     }
     LAUNCH_CHECK("ntt_fwd_pass");
@@ -876,10 +888,11 @@ static int run_fwd(const b2_ctx *c, const uint64_t *src, uint64_t *dst, const Jo
 }
 
 static int run_inv(const b2_ctx *c, const uint64_t *src, uint64_t *dst, const Job *jobs, uint32_t njobs, uint32_t first_prime,
-                   const W2 *fin, cudaStream_t s) {
+                   const W2 *fin, cudaStream_t s, const BatchDims &bd = BatchDims{}) {
     if (njobs == 0) return B2_OK;
     if (!aligned32(src) || !aligned32(dst)) return fail(B2_EINVAL, "device buffers must be 32-byte aligned (256-bit accesses)");
-    NttArgs a{src, dst, jobs, first_prime, (uint32_t)c->logN, c->d_itw, c->d_mod, fin, 0};
+    NttArgs a{src, dst, jobs, first_prime, (uint32_t)c->logN, c->d_itw, c->d_mod, fin, 0, 0, 0, bd.src_lm1, bd.src_bs, bd.dst_lm1, bd.dst_bs};
+    if (bd.batch != 1 && (c->use_cluster || c->use_pipe)) return fail(B2_EINVAL, "batched transforms need the two-pass kernels");
     if (c->use_cluster) {
         static thread_local bool attr_set = false;
         if (!attr_set) {
@@ -892,11 +905,11 @@ static int run_inv(const b2_ctx *c, const uint64_t *src, uint64_t *dst, const Jo
         return B2_OK;
     }
     switch (c->logN) {
-        case 16: launch_inv<8, 8>(c, a, njobs, s); break;
-        case 15: launch_inv<7, 8>(c, a, njobs, s); break;
-        case 14: launch_inv<7, 7>(c, a, njobs, s); break;
-        case 13: launch_inv<6, 7>(c, a, njobs, s); break;
-        case 12: launch_inv<6, 6>(c, a, njobs, s); break;
+        case 16: launch_inv<8, 8>(c, a, njobs, s, bd.batch); break;
+        case 15: launch_inv<7, 8>(c, a, njobs, s, bd.batch); break;
+        case 14: launch_inv<7, 7>(c, a, njobs, s, bd.batch); break;
+        case 13: launch_inv<6, 7>(c, a, njobs, s, bd.batch); break;
+        case 12: launch_inv<6, 6>(c, a, njobs, s, bd.batch); break;
         default: return fail(B2_ESIZE, "unsupported polynomial degree");
     }
     LAUNCH_CHECK("ntt_inv_pass");
@@ -1092,6 +1105,13 @@ struct EvkPtrs {
     const uint64_t *p[64];
 };
 
+// A batch of inner products in one launch (FUSED form): blockIdx.y = set b. Digits, the NTT-form input and the ciphertext
+// of set b start b * dig_bs / own_bs / ct_bs limbs further; P limb i of polynomial k lands at slot
+// (i * p_mul_i + k * p_mul_k) * (p_lm1 + 1) + b * p_bs of the P-limb buffer. One set: {0, 0, 0, 1, alpha, 0, 0}.
+struct IpBatch {
+    uint32_t dig_bs, own_bs, ct_bs, p_mul_i, p_mul_k, p_lm1, p_bs;
+};
+
 // Key-switch inner product (src/eval_key_switch.cu:175-230): for logical limb t (physical prime pp)
 //   acc[k][t][n] = (sum_d digits[d][t][n] * evk[d][k][pp][n]) mod q_pp,   k = 0, 1
 // accumulated in 128 bits and reduced once. Pure streaming: two coefficients per thread, 16-byte
@@ -1107,9 +1127,12 @@ __global__ void __launch_bounds__(256) ks_inner_prod_kernel(const uint64_t *__re
                                                            EvkPtrs evk, uint64_t *__restrict__ out, uint64_t *__restrict__ ct,
                                                            const W2 *__restrict__ pinv, const Mod *mod, const b2_ctx::RedcMeta *redc,
                                                            uint32_t N, uint32_t l, uint32_t lP, uint32_t size_Q, uint32_t size_QP,
-                                                           uint32_t beta, uint4 own_range) {
+                                                           uint32_t beta, uint4 own_range, const IpBatch ib) {
     // own_range = (first Q limb, number of Q limbs, first P limb, number of P limbs) this launch
     // covers: everything on one GPU, the rank's slice under RNS-limb sharding
+    digits += (size_t)blockIdx.y * ib.dig_bs * N;
+    if (own) own += (size_t)blockIdx.y * ib.own_bs * N;
+    if (FUSED) ct += (size_t)blockIdx.y * ib.ct_bs * N;
     const size_t jdx = 2 * ((size_t)blockIdx.x * blockDim.x + threadIdx.x);
     if (jdx >= (size_t)(own_range.y + own_range.w) * N) return;
     const uint32_t jl = (uint32_t)(jdx / N), n = (uint32_t)(jdx % N);
@@ -1167,13 +1190,14 @@ __global__ void __launch_bounds__(256) ks_inner_prod_kernel(const uint64_t *__re
             *reinterpret_cast<ulonglong2 *>(c0) = make_ulonglong2(add_mod(u0.x, r[0], md.q), add_mod(u0.y, r[1], md.q));
             *reinterpret_cast<ulonglong2 *>(c1) = make_ulonglong2(add_mod(u1.x, r[2], md.q), add_mod(u1.y, r[3], md.q));
         } else {
-            const size_t alpha = lP - l, o = (size_t)(t - l) * N + n;
+            const size_t o = ((size_t)(t - l) * ib.p_mul_i * (ib.p_lm1 + 1) + (size_t)blockIdx.y * ib.p_bs) * N + n;
+            const size_t o1 = o + (size_t)ib.p_mul_k * (ib.p_lm1 + 1) * N;
             if (ACCP) {
-                const ulonglong2 p0 = *reinterpret_cast<const ulonglong2 *>(out + o), p1 = *reinterpret_cast<const ulonglong2 *>(out + alpha * N + o);
+                const ulonglong2 p0 = *reinterpret_cast<const ulonglong2 *>(out + o), p1 = *reinterpret_cast<const ulonglong2 *>(out + o1);
                 r[0] = add_mod(r[0], p0.x, md.q), r[1] = add_mod(r[1], p0.y, md.q), r[2] = add_mod(r[2], p1.x, md.q), r[3] = add_mod(r[3], p1.y, md.q);
             }
             *reinterpret_cast<ulonglong2 *>(out + o) = make_ulonglong2(r[0], r[1]);
-            *reinterpret_cast<ulonglong2 *>(out + alpha * N + o) = make_ulonglong2(r[2], r[3]);
+            *reinterpret_cast<ulonglong2 *>(out + o1) = make_ulonglong2(r[2], r[3]);
         }
         return;
     }
@@ -1214,13 +1238,14 @@ __global__ void __launch_bounds__(256) ks_inner_prod_kernel(const uint64_t *__re
         *reinterpret_cast<ulonglong2 *>(c1) =
             make_ulonglong2(add_mod(u1.x, mul_shoup(r10, pi, md.q), md.q), add_mod(u1.y, mul_shoup(r11, pi, md.q), md.q));
     } else {
-        const size_t alpha = lP - l, o = (size_t)(t - l) * N + n;
+        const size_t o = ((size_t)(t - l) * ib.p_mul_i * (ib.p_lm1 + 1) + (size_t)blockIdx.y * ib.p_bs) * N + n;
+        const size_t o1 = o + (size_t)ib.p_mul_k * (ib.p_lm1 + 1) * N;
         if (ACCP) {
-            const ulonglong2 p0 = *reinterpret_cast<const ulonglong2 *>(out + o), p1 = *reinterpret_cast<const ulonglong2 *>(out + alpha * N + o);
+            const ulonglong2 p0 = *reinterpret_cast<const ulonglong2 *>(out + o), p1 = *reinterpret_cast<const ulonglong2 *>(out + o1);
             r00 = add_mod(r00, p0.x, md.q), r01 = add_mod(r01, p0.y, md.q), r10 = add_mod(r10, p1.x, md.q), r11 = add_mod(r11, p1.y, md.q);
         }
         *reinterpret_cast<ulonglong2 *>(out + o) = make_ulonglong2(r00, r01);
-        *reinterpret_cast<ulonglong2 *>(out + alpha * N + o) = make_ulonglong2(r10, r11);
+        *reinterpret_cast<ulonglong2 *>(out + o1) = make_ulonglong2(r10, r11);
     }
 }
 
@@ -1468,10 +1493,12 @@ static uint32_t tc_smem_request(uint32_t alloc_cols, uint32_t used) {
 
 // n_jobs: how many of the set's jobs to run (ModDown of one polynomial runs the first half)
 static int run_bconv_tc(const b2_ctx *c, bool copy, const uint64_t *in, uint64_t *out, const uint64_t *copy_src, const TcSet &tc, uint32_t n_jobs,
-                        cudaStream_t s) {
+                        cudaStream_t s, const TcBatch *tbp = nullptr) {
     const uint32_t N = (uint32_t)c->N;
     if (n_jobs == 0) return B2_OK;
     if (copy && !copy_src) return fail(B2_EINVAL, "base conversion: missing copy source");
+    const TcBatch tb = tbp ? *tbp : TcBatch{1, 0, 0, 0, 0};
+    if (tb.batch != 1 && (copy || c->tc_simple)) return fail(B2_EINVAL, "a batched base conversion runs on the persistent kernel, without the own-limb copy");
     LaunchScope ls(c, s, "bconv");
     // without the copy the jobs' copy slots are ignored by handing the kernel a null source
     const uint64_t *cs = copy ? copy_src : nullptr;
@@ -1489,13 +1516,13 @@ static int run_bconv_tc(const b2_ctx *c, bool copy, const uint64_t *in, uint64_t
     // persistent CTAs: as many as stay resident (TMEM columns, threads), each walking its share of the (job, tile) items
     const uint32_t threads = 128u * (uint32_t)c->tc_wg;
     const uint32_t fit = std::min(512u / tc.max_alloc, 2048u / threads);
-    const uint32_t total = n_jobs * (N / 128);
+    const uint32_t total = n_jobs * (N / 128) * tb.batch;
     const uint32_t grid = std::min(total, fit * (uint32_t)c->sm_count);
     const uint32_t smem = tc_smem_request(tc.max_alloc, TCP_SMEM_BYTES);
     switch (c->tc_wg) {
-        case 1: bconv_tc_persist<1><<<grid, 128, smem, s>>>(in, out, cs, tc.jobs, tc.groups, tc.images, N, n_jobs, tc.max_alloc, c->d_err); break;
-        case 2: bconv_tc_persist<2><<<grid, 256, smem, s>>>(in, out, cs, tc.jobs, tc.groups, tc.images, N, n_jobs, tc.max_alloc, c->d_err); break;
-        default: bconv_tc_persist<4><<<grid, 512, smem, s>>>(in, out, cs, tc.jobs, tc.groups, tc.images, N, n_jobs, tc.max_alloc, c->d_err); break;
+        case 1: bconv_tc_persist<1><<<grid, 128, smem, s>>>(in, out, cs, tc.jobs, tc.groups, tc.images, N, n_jobs, tc.max_alloc, c->d_err, tb); break;
+        case 2: bconv_tc_persist<2><<<grid, 256, smem, s>>>(in, out, cs, tc.jobs, tc.groups, tc.images, N, n_jobs, tc.max_alloc, c->d_err, tb); break;
+        default: bconv_tc_persist<4><<<grid, 512, smem, s>>>(in, out, cs, tc.jobs, tc.groups, tc.images, N, n_jobs, tc.max_alloc, c->d_err, tb); break;
     }
     LAUNCH_CHECK("bconv_tc_persist");
     return B2_OK;
@@ -1588,7 +1615,8 @@ extern "C" int b2_modup(b2_ctx *c, size_t l, const uint64_t *d_c2, uint64_t *d_o
 
 // fused = false: out = cx [2][lP][N]. fused = true: Q limbs accumulate into ct, out = [2][alpha][N].
 static int inner_prod_impl(b2_ctx *c, size_t l, const uint64_t *digits, const uint64_t *own, const uint64_t *const *evk, size_t n_evk,
-                           uint64_t *out, uint64_t *ct, bool fused, cudaStream_t s, const uint4 *range = nullptr, bool acc_p = false) {
+                           uint64_t *out, uint64_t *ct, bool fused, cudaStream_t s, const uint4 *range = nullptr, bool acc_p = false,
+                           uint32_t batch = 1, const IpBatch *ipb = nullptr) {
     const size_t beta = c->plan[l].beta, lP = l + c->size_P;
     if (n_evk < beta) return fail(B2_EINVAL, "key has fewer digits than this level needs");
     if (beta > 64) return fail(B2_ESIZE, "more than 64 digits");
@@ -1600,17 +1628,19 @@ static int inner_prod_impl(b2_ctx *c, size_t l, const uint64_t *digits, const ui
     const uint4 rg = range ? *range : make_uint4(0, (uint32_t)l, 0, (uint32_t)c->size_P);
     const size_t pairs = (size_t)(rg.y + rg.w) * c->N / 2;
     if (pairs == 0) return B2_OK;
-    const unsigned grid = (unsigned)((pairs + 255) / 256);
+    if (batch != 1 && (!fused || !ipb)) return fail(B2_EINVAL, "a batched inner product runs in the fused form");
+    const dim3 grid((unsigned)((pairs + 255) / 256), batch);
+    const IpBatch ib = ipb ? *ipb : IpBatch{0, 0, 0, 1, (uint32_t)c->size_P, 0, 0};
     LaunchScope ls(c, s, "ks_inner_prod");
     if (fused && acc_p)
         ks_inner_prod_kernel<3, true, true><<<grid, 256, 0, s>>>(digits, own, ep, out, ct, c->d_Pinv, c->d_mod, c->d_redc, (uint32_t)c->N, (uint32_t)l,
-                                                               (uint32_t)lP, (uint32_t)c->size_Q, (uint32_t)c->size_QP, (uint32_t)beta, rg);
+                                                               (uint32_t)lP, (uint32_t)c->size_Q, (uint32_t)c->size_QP, (uint32_t)beta, rg, ib);
     else if (fused)
         ks_inner_prod_kernel<3, true><<<grid, 256, 0, s>>>(digits, own, ep, out, ct, c->d_Pinv, c->d_mod, c->d_redc, (uint32_t)c->N, (uint32_t)l, (uint32_t)lP,
-                                                         (uint32_t)c->size_Q, (uint32_t)c->size_QP, (uint32_t)beta, rg);
+                                                         (uint32_t)c->size_Q, (uint32_t)c->size_QP, (uint32_t)beta, rg, ib);
     else
         ks_inner_prod_kernel<3, false><<<grid, 256, 0, s>>>(digits, own, ep, out, nullptr, nullptr, c->d_mod, c->d_redc, (uint32_t)c->N, (uint32_t)l, (uint32_t)lP,
-                                                          (uint32_t)c->size_Q, (uint32_t)c->size_QP, (uint32_t)beta, rg);
+                                                          (uint32_t)c->size_Q, (uint32_t)c->size_QP, (uint32_t)beta, rg, ib);
     LAUNCH_CHECK("ks_inner_prod_kernel");
     return B2_OK;
 }
@@ -2352,7 +2382,7 @@ static int build_shard_level(b2_ctx *c, size_t l) {
     shard_range(l, c->shard_rank, c->shard_world, &sp.q0, &sp.nq);
     shard_range(alpha, c->shard_rank, c->shard_world, &sp.p0, &sp.np);
     auto owned = [&](size_t t) { return t < l ? (t >= sp.q0 && t < sp.q0 + sp.nq) : (t - l >= sp.p0 && t - l < sp.p0 + sp.np); };
-    std::vector<Job> jobs_up, jobs_di, jobs_dn;
+    std::vector<Job> jobs_up, jobs_di, jobs_dn, jobs_di_b;
     std::vector<BconvGroup> grp_up(beta), grp_dn(2);
     std::vector<uint2> outs_up, outs_dn;
     std::vector<uint64_t> mat_up, mat_dn;
@@ -2395,8 +2425,10 @@ static int build_shard_level(b2_ctx *c, size_t l) {
         }
     }
     for (size_t k = 0; k < 2; k++) {
-        for (size_t i = sp.p0; i < sp.p0 + sp.np; i++)
+        for (size_t i = sp.p0; i < sp.p0 + sp.np; i++) {
             jobs_di.push_back(make_uint4((uint32_t)(k * alpha + i), (uint32_t)(sQ + i), (uint32_t)i, (uint32_t)(k * alpha + i)));
+            jobs_di_b.push_back(make_uint4((uint32_t)(2 * i + k), (uint32_t)(sQ + i), (uint32_t)i, (uint32_t)(2 * i + k)));
+        }
         for (size_t j = sp.q0; j < sp.q0 + sp.nq; j++)
             jobs_dn.push_back(make_uint4((uint32_t)(k * l + j), (uint32_t)j, 0, (uint32_t)(k * l + j)));
         grp_dn[k] = BconvGroup{(uint32_t)(k * alpha), (uint32_t)alpha, 0, 0, sp.nq, (uint32_t)(k * l), 0, p_pieces};
@@ -2407,19 +2439,20 @@ static int build_shard_level(b2_ctx *c, size_t l) {
     const size_t sz[] = {al(jobs_up.size() * sizeof(Job)), al(jobs_di.size() * sizeof(Job)), al(jobs_dn.size() * sizeof(Job)),
                          al(grp_up.size() * sizeof(BconvGroup)), al(grp_dn.size() * sizeof(BconvGroup)), al(outs_up.size() * sizeof(uint2)),
                          al(outs_dn.size() * sizeof(uint2)), al(mat_up.size() * 8), al(mat_dn.size() * 8), al(matd_up.size() * 8),
-                         al(matd_dn.size() * 8)};
+                         al(matd_dn.size() * 8), al(jobs_di_b.size() * sizeof(Job))};
     const void *srcs[] = {jobs_up.data(), jobs_di.data(), jobs_dn.data(), grp_up.data(), grp_dn.data(), outs_up.data(),
-                          outs_dn.data(), mat_up.data(), mat_dn.data(), matd_up.data(), matd_dn.data()};
+                          outs_dn.data(), mat_up.data(), mat_dn.data(), matd_up.data(), matd_dn.data(), jobs_di_b.data()};
     const size_t raw[] = {jobs_up.size() * sizeof(Job), jobs_di.size() * sizeof(Job), jobs_dn.size() * sizeof(Job),
                           grp_up.size() * sizeof(BconvGroup), grp_dn.size() * sizeof(BconvGroup), outs_up.size() * sizeof(uint2),
-                          outs_dn.size() * sizeof(uint2), mat_up.size() * 8, mat_dn.size() * 8, matd_up.size() * 8, matd_dn.size() * 8};
+                          outs_dn.size() * sizeof(uint2), mat_up.size() * 8, mat_dn.size() * 8, matd_up.size() * 8, matd_dn.size() * 8,
+                          jobs_di_b.size() * sizeof(Job)};
     size_t total = 256;
     for (size_t x : sz) total += x;
     CUDA_TRY(cudaMalloc(&sp.blob, total));
     char *base = (char *)sp.blob;
-    void *dptr[11];
+    void *dptr[12];
     size_t off = 0;
-    for (int i = 0; i < 11; i++) {
+    for (int i = 0; i < 12; i++) {
         dptr[i] = base + off;
         if (raw[i]) CUDA_TRY(cudaMemcpy(dptr[i], srcs[i], raw[i], cudaMemcpyHostToDevice));
         off += sz[i];
@@ -2435,11 +2468,12 @@ static int build_shard_level(b2_ctx *c, size_t l) {
     sp.mat_dn = (uint64_t *)dptr[8];
     sp.matd_up = (double *)dptr[9];
     sp.matd_dn = (double *)dptr[10];
+    sp.jobs_dn_intt_b = (Job *)dptr[11];
     if (c->bconv_tc) {
         // tensor-core jobs over the rank's outputs (a rank may own no output of a digit, or no Q limb at all)
         TcBuild tb;
         std::vector<TcSpecOut> outs;
-        uint32_t n_up = 0, n_dn = 0;
+        uint32_t n_up = 0, n_dn = 0, n_dn_b = 0;
         for (size_t d = 0; d < beta; d++) {
             const BconvGroup &g = grp_up[d];
             if (g.n_out == 0) continue;
@@ -2455,9 +2489,14 @@ static int build_shard_level(b2_ctx *c, size_t l) {
             for (uint32_t j = 0; j < sp.nq; j++) outs.push_back(TcSpecOut{(uint32_t)(k * l) + sp.q0 + j, c->q[sp.q0 + j], mat_dn.data() + (size_t)j * alpha});
             n_dn += tb.add((uint32_t)(k * alpha), (uint32_t)alpha, 0xFFFFFFFFu, outs);
         }
+        for (size_t k = 0; k < 2 && sp.nq; k++) {  // the same conversion reading P limb i of polynomial k at slot 2 i + k
+            outs.clear();
+            for (uint32_t j = 0; j < sp.nq; j++) outs.push_back(TcSpecOut{(uint32_t)(k * l) + sp.q0 + j, c->q[sp.q0 + j], mat_dn.data() + (size_t)j * alpha});
+            n_dn_b += tb.add((uint32_t)k, (uint32_t)alpha, 0xFFFFFFFFu, outs, 2);
+        }
         if (!tb.ok) return fail(B2_EINVAL, "tensor-core base conversion: unsupported prime in the chain");
         if (n_up + n_dn) {
-            int rc = tc_upload(tb, &sp.tc_blob, {{&sp.tc_up, {0u, n_up}}, {&sp.tc_dn, {n_up, n_dn}}});
+            int rc = tc_upload(tb, &sp.tc_blob, {{&sp.tc_up, {0u, n_up}}, {&sp.tc_dn, {n_up, n_dn}}, {&sp.tc_dn_b, {n_up + n_dn, n_dn_b}}});
             if (rc) return rc;
         }
     }
@@ -2527,5 +2566,61 @@ extern "C" int b2_shard_keyswitch_phase(b2_ctx *c, size_t l, int phase, const ui
             return run_fwd(c, up, up, sp.jobs_dn_ntt, 2 * sp.nq, 0, EpiSubFrom{d_ct}, s);
         default:
             return fail(B2_EINVAL, "shard_keyswitch_phase: phase must be 0, 1 or 2");
+    }
+}
+
+extern "C" size_t b2_shard_batch_workspace_bytes(const b2_ctx *c, size_t l, size_t batch) {
+    if (!c || l < 1 || l > c->size_Q || batch < 1) return 0;
+    const size_t a = c->size_P, beta = (l + a - 1) / a, lP = l + a;
+    return batch * (l + 2 * a + beta * lP) * limb_bytes(c);
+}
+
+// The three phases for `batch` ciphertexts at once (one key for all of them): every kernel of a phase is one launch over the
+// whole batch, so a rank that owns an eighth of the limbs still fills the GPU. Workspace, in limbs:
+//   T   [l][batch]            scaled coefficient form of c2, limb-major: this rank's Q limbs are one contiguous block
+//   CXP [alpha][2][batch]     P limbs of both polynomials, limb-major likewise
+//   UP  [batch][beta][l+alpha]  ModUp digits (its front also holds ModDown's delta)
+// The caller all-gathers T after phase 0 and CXP after phase 1 (one collective each).
+extern "C" int b2_shard_keyswitch_phase_batch(b2_ctx *c, size_t l, int phase, size_t batch, const uint64_t *d_c2, const uint64_t *const *evk,
+                                              size_t n_evk, uint64_t *d_ct, void *d_ws, size_t ws_bytes, void *stream) {
+    CHECK_CTX(c);
+    CHECK_LEVEL(c, l);
+    if (c->shard.empty()) return fail(B2_EINVAL, "shard_keyswitch_phase_batch: call b2_ctx_set_shard first");
+    if (!d_c2 || !evk || !d_ct || !d_ws || batch < 1 || batch > 65535) return fail(B2_EINVAL, "shard_keyswitch_phase_batch: bad argument");
+    if (ws_bytes < b2_shard_batch_workspace_bytes(c, l, batch)) return fail(B2_EWS, "shard_keyswitch_phase_batch: workspace too small");
+    if (!c->bconv_tc || c->tc_simple) return fail(B2_EINVAL, "shard_keyswitch_phase_batch: needs the persistent tensor-core base conversion");
+    cudaStream_t s = (cudaStream_t)stream;
+    const LevelPlan &pl = c->plan[l];
+    const b2_ctx::ShardPlan &sp = c->shard[l];
+    const size_t N = c->N, a = c->size_P, lP = l + a, beta = pl.beta;
+    const uint32_t B = (uint32_t)batch, per = (uint32_t)(beta * lP);
+    uint64_t *T = (uint64_t *)d_ws, *CXP = T + l * batch * N, *UP = CXP + 2 * a * batch * N;
+    int rc;
+    switch (phase) {
+        case 0:
+            return run_inv(c, d_c2, T, pl.jobs_up_intt + sp.q0, sp.nq, 0, pl.fin_up, s, BatchDims{B, 0, (uint32_t)l, B - 1, 1});
+        case 1: {
+            const TcBatch tb{B, B - 1, 1, 0, per};
+            if (sp.tc_up.jobs) {
+                rc = run_bconv_tc(c, false, T, UP, nullptr, sp.tc_up, sp.tc_up.n_jobs, s, &tb);
+                if (rc) return rc;
+            }
+            rc = run_fwd(c, UP, UP, sp.jobs_up_ntt, sp.n_up_ntt, 0, EpiStore{}, s, 0, 0, 0, BatchDims{B, 0, per, 0, per});
+            if (rc) return rc;
+            const uint4 rg = make_uint4(sp.q0, sp.nq, sp.p0, sp.np);
+            const IpBatch ib{per, (uint32_t)l, (uint32_t)(2 * l), 2, 1, B - 1, 1};
+            rc = inner_prod_impl(c, l, UP, d_c2, evk, n_evk, CXP, d_ct, true, s, &rg, false, B, &ib);
+            if (rc) return rc;
+            return run_inv(c, CXP, CXP, sp.jobs_dn_intt_b, 2 * sp.np, 0, c->d_fin_P, s, BatchDims{B, B - 1, 1, B - 1, 1});
+        }
+        case 2: {
+            if (sp.nq == 0) return B2_OK;
+            const TcBatch tb{B, B - 1, 1, 0, per};
+            rc = run_bconv_tc(c, false, CXP, UP, nullptr, sp.tc_dn_b, sp.tc_dn_b.n_jobs, s, &tb);
+            if (rc) return rc;
+            return run_fwd(c, UP, UP, sp.jobs_dn_ntt, 2 * sp.nq, 0, EpiSubFrom{d_ct, (uint32_t)(2 * l)}, s, 0, 0, 0, BatchDims{B, 0, per, 0, per});
+        }
+        default:
+            return fail(B2_EINVAL, "shard_keyswitch_phase_batch: phase must be 0, 1 or 2");
     }
 }

@@ -262,16 +262,27 @@ __device__ __forceinline__ void tc_cp_async16(uint32_t smem_dst, const void *gsr
 }
 
 // the rows of A for tile `tile` of `job`: 8 bytes per (coefficient, input limb), zeros for limbs the job does not have
+// A batch of conversions in one launch: set b reads input limb slot s at s * (in_lm1 + 1) + b * in_bs and writes output limb
+// slot s at s * (out_lm1 + 1) + b * out_bs (batch-major and limb-major buffers as for the transforms, ntt_kernels.cuh)
+struct TcBatch {
+    uint32_t batch, in_lm1, in_bs, out_lm1, out_bs;
+};
+
 template <int WG>
-__device__ __forceinline__ void tcp_fetch_a(uint8_t *sA, const uint64_t *__restrict__ in, const TcJob &job, uint32_t N, uint32_t tile) {
+__device__ __forceinline__ void tcp_fetch_a(uint8_t *sA, const uint64_t *__restrict__ in, const TcJob &job, uint32_t N, uint32_t tile, uint32_t b,
+                                            const TcBatch &tb) {
     const uint32_t tid = threadIdx.x, r = tid & 127, part = tid >> 7;
     constexpr int LIMBS = 8 / WG;
 #pragma unroll
     for (int j = 0; j < LIMBS; j++) {
         const uint32_t i = part * LIMBS + j;
         uint8_t *dst = sA + (r >> 3) * 512 + (i >> 1) * 128 + (r & 7) * 16 + (i & 1) * 8;
-        if (i < job.ni) tc_cp_async8(tc_smem_u32(dst), in + (size_t)(job.in_slot0 + i) * N + (size_t)tile * 128 + r);
-        else *reinterpret_cast<uint64_t *>(dst) = 0;
+        if (i < job.ni) {
+            const size_t slot = (size_t)(job.in_slot0 + i * (job.in_stride1 + 1)) * (tb.in_lm1 + 1) + (size_t)b * tb.in_bs;
+            tc_cp_async8(tc_smem_u32(dst), in + slot * N + (size_t)tile * 128 + r);
+        } else {
+            *reinterpret_cast<uint64_t *>(dst) = 0;
+        }
     }
 }
 
@@ -279,7 +290,7 @@ template <int WG>
 __global__ void __launch_bounds__(128 * WG) bconv_tc_persist(const uint64_t *__restrict__ in, uint64_t *__restrict__ out,
                                                              const uint64_t *__restrict__ copy_src, const TcJob *__restrict__ jobs,
                                                              const TcGroup *__restrict__ groups, const uint8_t *__restrict__ images, uint32_t N,
-                                                             uint32_t n_jobs, uint32_t alloc_cols, uint32_t *err) {
+                                                             uint32_t n_jobs, uint32_t alloc_cols, uint32_t *err, const TcBatch tb) {
     extern __shared__ __align__(1024) uint8_t tc_smem[];
     uint8_t *sB = tc_smem + TCP_SMEM_B;
     TcOutS *sOut = reinterpret_cast<TcOutS *>(tc_smem + TCP_SMEM_GRP);              // [16][4]
@@ -288,7 +299,8 @@ __global__ void __launch_bounds__(128 * WG) bconv_tc_persist(const uint64_t *__r
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(tc_smem + TCP_SMEM_CTRL + 8);
     constexpr uint32_t THREADS = 128 * WG;
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const uint32_t tiles = N >> 7, tile_mask = tiles - 1, log_tiles = 31 - __clz(tiles), total = n_jobs * tiles;  // N is a power of two
+    // items: job-major, then set of the batch, then tile (N is a power of two)
+    const uint32_t tiles = N >> 7, tile_mask = tiles - 1, log_tiles = 31 - __clz(tiles), per_job = tb.batch << log_tiles, total = n_jobs * per_job;
 
     if (warp == 0) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tc_smem_u32(tmem_slot)), "r"(alloc_cols) : "memory");
@@ -302,8 +314,8 @@ __global__ void __launch_bounds__(128 * WG) bconv_tc_persist(const uint64_t *__r
     bool ok = true;
     TcJob job{};
     if (item < total) {
-        job = jobs[item >> log_tiles];
-        tcp_fetch_a<WG>(tc_smem + TCP_SMEM_A0, in, job, N, item & tile_mask);
+        job = jobs[item / per_job];
+        tcp_fetch_a<WG>(tc_smem + TCP_SMEM_A0, in, job, N, item & tile_mask, (item % per_job) >> log_tiles, tb);
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -314,7 +326,7 @@ __global__ void __launch_bounds__(128 * WG) bconv_tc_persist(const uint64_t *__r
     const uint32_t lane_base = tmem + ((wq * 32u) << 16);
 
     while (item < total && ok) {
-        const uint32_t jb = item >> log_tiles, tile = item & tile_mask;
+        const uint32_t jb = item / per_job, tile = item & tile_mask, bset = (item - jb * per_job) >> log_tiles;
         if (jb != loaded_job) {
             // a new job: its B image and group table (the MMA that read the old image has completed: every thread
             // waited for it before the previous epilogue, and the barrier at the end of that iteration has passed)
@@ -330,7 +342,7 @@ __global__ void __launch_bounds__(128 * WG) bconv_tc_persist(const uint64_t *__r
                 TcOutS rec{1u, 0u, 0u, 0xFFFFFFFFu};
                 if (o < hdr.y) {
                     const uint4 raw = __ldg(reinterpret_cast<const uint4 *>(&G->o[o]));
-                    rec = TcOutS{raw.x, raw.y, raw.z, raw.w * N};
+                    rec = TcOutS{raw.x, raw.y, raw.z, raw.w * (tb.out_lm1 + 1) * N};
                 }
                 sOut[tid] = rec;
                 if (o == 0) sNb[tid >> 2] = hdr.x;
@@ -352,16 +364,16 @@ __global__ void __launch_bounds__(128 * WG) bconv_tc_persist(const uint64_t *__r
         // next item's rows of A into the other buffer (its last reader, the MMA of the previous iteration, is done)
         const uint32_t next = item + gridDim.x;
         if (next < total) {
-            const uint32_t njb = next >> log_tiles;
+            const uint32_t njb = next / per_job, nb = (next - njb * per_job) >> log_tiles;
             if (njb == jb) {
-                tcp_fetch_a<WG>(tc_smem + (cur ? TCP_SMEM_A0 : TCP_SMEM_A1), in, job, N, next & tile_mask);
+                tcp_fetch_a<WG>(tc_smem + (cur ? TCP_SMEM_A0 : TCP_SMEM_A1), in, job, N, next & tile_mask, nb, tb);
             } else {
                 const TcJob nj = jobs[njb];
-                tcp_fetch_a<WG>(tc_smem + (cur ? TCP_SMEM_A0 : TCP_SMEM_A1), in, nj, N, next & tile_mask);
+                tcp_fetch_a<WG>(tc_smem + (cur ? TCP_SMEM_A0 : TCP_SMEM_A1), in, nj, N, next & tile_mask, nb, tb);
             }
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
-        // ModUp: the digit's own limbs travel from the NTT-form input to the output buffer
+        // ModUp: the digit's own limbs travel from the NTT-form input to the output buffer (single set only)
         if (copy_src != nullptr && job.copy_dst_slot0 != 0xFFFFFFFFu) {
             const uint32_t r = tid & 127, part = tid >> 7;
             for (uint32_t i = part; i < job.ni; i += WG)
@@ -384,7 +396,7 @@ __global__ void __launch_bounds__(128 * WG) bconv_tc_persist(const uint64_t *__r
         ok = __all_sync(0xFFFFFFFFu, done != 0);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         if (ok) {
-            uint64_t *out_n = out + (tile * 128 + wq * 32 + lane);
+            uint64_t *out_n = out + (size_t)bset * tb.out_bs * N + (tile * 128 + wq * 32 + lane);
             for (uint32_t g = wg; g < job.n_groups; g += WG) {
                 uint32_t c[16];
                 tc_ld16(lane_base + g * 16, c);

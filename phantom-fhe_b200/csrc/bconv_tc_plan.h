@@ -52,7 +52,7 @@ struct TcJob {
     uint32_t img_off;          // byte offset of the B image (n_groups * 1024 bytes)
     uint32_t grp_off;          // first TcGroup of the job
     uint32_t alloc_cols;       // TMEM columns to allocate: power of two >= max(32, 16 n_groups)
-    uint32_t pad;
+    uint32_t in_stride1;       // input limb i sits at slot in_slot0 + i * (in_stride1 + 1)
 };
 static_assert(sizeof(TcOut) == 16 && sizeof(TcGroup) == 80 && sizeof(TcJob) == 32, "device layouts");
 
@@ -124,7 +124,7 @@ struct TcBuild {
     bool ok = true;
     // One conversion (a digit, a polynomial): outputs are packed, in order, into 16-column groups of equal byte count;
     // more than 16 groups spill into further jobs over the same inputs. Returns the number of jobs added.
-    uint32_t add(uint32_t in_slot0, uint32_t ni, uint32_t copy_dst, const std::vector<TcSpecOut> &outs) {
+    uint32_t add(uint32_t in_slot0, uint32_t ni, uint32_t copy_dst, const std::vector<TcSpecOut> &outs, uint32_t in_stride = 1) {
         if (ni < 1 || ni > 8 || outs.empty()) {
             ok = false;
             return 0;
@@ -132,7 +132,7 @@ struct TcBuild {
         uint32_t added = 0;
         size_t i = 0;
         while (i < outs.size()) {
-            TcJob job{in_slot0, ni, added == 0 ? copy_dst : 0xFFFFFFFFu, 0, (uint32_t)images.size(), (uint32_t)groups.size(), 32, 0};
+            TcJob job{in_slot0, ni, added == 0 ? copy_dst : 0xFFFFFFFFu, 0, (uint32_t)images.size(), (uint32_t)groups.size(), 32, in_stride - 1};
             std::vector<std::pair<size_t, uint32_t>> placed;  // (output index, first column) of this job
             while (i < outs.size() && job.n_groups < 16) {
                 const uint32_t nb = tc_nbytes(outs[i].p), opg = 16 / nb;

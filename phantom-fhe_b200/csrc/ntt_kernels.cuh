@@ -51,7 +51,14 @@ struct NttArgs {
     // slot job.x / src_div of src, whose words are residues mod src_q, reduced into the limb's prime
     uint32_t src_div;
     uint64_t src_q;
+    // A batch of polynomial sets in one launch (the two-pass kernels only): blockIdx.y = set b, and limb slot s of set b
+    // lives at slot s * (lm1 + 1) + b * bs of the buffer. Zero-initialised fields mean one set, slots as they are.
+    // Batch-major buffers [b][slots] use lm1 = 0, bs = slots per set; limb-major ones [slot][b] use lm1 = batch - 1, bs = 1.
+    uint32_t src_lm1, src_bs, dst_lm1, dst_bs;
 };
+
+__device__ __forceinline__ size_t src_slot(const NttArgs &a, uint32_t slot) { return (size_t)slot * (a.src_lm1 + 1) + (size_t)blockIdx.y * a.src_bs; }
+__device__ __forceinline__ size_t dst_slot(const NttArgs &a, uint32_t slot) { return (size_t)slot * (a.dst_lm1 + 1) + (size_t)blockIdx.y * a.dst_bs; }
 
 __device__ __forceinline__ Job get_job(const NttArgs &a, uint32_t j) {
     if (a.jobs) return a.jobs[j];
@@ -83,7 +90,7 @@ struct EpiStore {
     uint64_t *dst;
     bool aligned() const { return true; }  // dst is the transform's own output, checked by the launcher
     template <int E> struct Regs {};
-    __device__ __forceinline__ void init(const NttArgs &a, const Job &job, size_t N) { dst = a.dst + (size_t)job.x * N; }
+    __device__ __forceinline__ void init(const NttArgs &a, const Job &job, size_t N) { dst = a.dst + dst_slot(a, job.x) * N; }
     template <int E> __device__ __forceinline__ void preload(Regs<E> &, size_t) const {}
     template <int E> __device__ __forceinline__ void finish(const Regs<E> &, size_t o, uint64_t (&x)[E], uint64_t) const {
 #pragma unroll
@@ -141,12 +148,13 @@ struct EpiSubMul {
 // ct + cx * P^-1 in `out`, and the ModDown matrix carries P^-1, so only the subtraction remains)
 struct EpiSubFrom {
     uint64_t *out;
-    uint64_t *o_;
+    uint32_t bs = 0;  // batch stride of `out` in limbs (set b of a batched launch: see NttArgs)
+    uint64_t *o_ = nullptr;
     bool aligned() const { return aligned32(out); }
     template <int E> struct Regs {
         u64x4 u[E / 4];
     };
-    __device__ __forceinline__ void init(const NttArgs &, const Job &job, size_t N) { o_ = out + (size_t)job.w * N; }
+    __device__ __forceinline__ void init(const NttArgs &, const Job &job, size_t N) { o_ = out + ((size_t)job.w + (size_t)blockIdx.y * bs) * N; }
     template <int E> __device__ __forceinline__ void preload(Regs<E> &r, size_t o) const {
 #pragma unroll
         for (int i = 0; i < E / 4; i++) r.u[i] = ld256(o_ + o + 4 * i);
@@ -347,7 +355,7 @@ __device__ __forceinline__ void fwd_body(const NttArgs &a, const Epi &epi, uint6
     const size_t N = (size_t)1 << a.logN;
     const typename A::K k = A::make(md, (int)a.logN);
     const W2 *tw = a.tw + (size_t)job.y * N;
-    const uint64_t *src = a.src + (size_t)(SRC ? job.x / a.src_div : job.x) * N;
+    const uint64_t *src = a.src + src_slot(a, SRC ? job.x / a.src_div : job.x) * N;
     const size_t estride = COLS ? (N >> LOG_T) : 1;
     const size_t cstride = COLS ? 1 : TT;
     const size_t base = COLS ? (size_t)tile * C : (size_t)tile * C * TT;
@@ -390,7 +398,7 @@ __device__ __forceinline__ void fwd_body(const NttArgs &a, const Epi &epi, uint6
     // ---- stage group 2 ---------------------------------------------------------------------------
     Epi e = epi;
     if (LAST) e.init(a, job, N);
-    uint64_t *dst = a.dst + (size_t)job.x * N;
+    uint64_t *dst = a.dst + dst_slot(a, job.x) * N;
 #pragma unroll
     for (int gi = 0; gi < EPT / E2; gi++) {
         const int gid = tid + gi * THREADS;
@@ -547,8 +555,8 @@ __device__ __forceinline__ void inv_body(const NttArgs &a, uint64_t *sm, const J
     const size_t N = (size_t)1 << a.logN;
     const typename A::K k = A::make(md, (int)a.logN);
     const W2 *tw = a.tw + (size_t)job.y * N;
-    const uint64_t *src = a.src + (size_t)(FIRST ? job.x : job.w) * N;  // the second pass works in place on dst
-    uint64_t *dst = a.dst + (size_t)job.w * N;
+    const uint64_t *src = a.src + src_slot(a, FIRST ? job.x : job.w) * N;  // the second pass works in place on dst
+    uint64_t *dst = a.dst + dst_slot(a, job.w) * N;
     const size_t estride = COLS ? (N >> LOG_T) : 1;
     const size_t cstride = COLS ? 1 : TT;
     const size_t base = COLS ? (size_t)tile * C : (size_t)tile * C * TT;

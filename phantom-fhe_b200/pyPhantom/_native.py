@@ -56,6 +56,8 @@ SIGNATURES = {
     "b2_ctx_set_shard": (_int, [_vp, _int, _int]),
     "b2_shard_limbs": (_int, [_vp, _sz, _vp]),
     "b2_shard_keyswitch_phase": (_int, [_vp, _sz, _int, _vp, _vp, _sz, _vp, _vp, _sz, _vp]),
+    "b2_shard_batch_workspace_bytes": (_sz, [_vp, _sz, _sz]),
+    "b2_shard_keyswitch_phase_batch": (_int, [_vp, _sz, _int, _sz, _vp, _vp, _sz, _vp, _vp, _sz, _vp]),
     "b2_launch_count": (_u64, []),
     "b2_device_status": (_int, [_vp, _vp]),
     "b2_profile_start": (_int, [_vp]),

@@ -96,3 +96,60 @@ class LimbShardedKeySwitch:
     def allgather_ct(self, l, ct):
         for k in range(ct.shape[0]):
             allgather_limbs(ct[k], l, self.rank, self.world, self.group)
+
+
+class BatchedLimbShardedKeySwitch(LimbShardedKeySwitch):
+    """A batch of ciphertexts, all switched with one key, with their limbs spread over the ranks.
+
+    c2: [batch][l][N], ct: [batch][2][l][N] (only this rank's limbs need to hold data; only they are updated).
+    Every kernel of a phase covers the whole batch in one launch, and each of the two exchanges is ONE all-gather:
+    the batch's scaled coefficient-form limbs T [l][batch][N] after phase 0, the P limbs CXP [alpha][2][batch][N]
+    after phase 1. `pipeline` runs several batches on alternating streams, each with its own communicator, so one
+    batch's all-gathers overlap another's kernels."""
+
+    def batch_workspace(self, l, batch):
+        nbytes = int(LIB.b2_shard_batch_workspace_bytes(self.ctx._h, l, batch))
+        return torch.empty(nbytes // 8, dtype=torch.int64, device=torch.device("cuda", self.ctx.device)), nbytes
+
+    def _views(self, l, batch, ws):
+        N, a = self.ctx.N, self.ctx.size_P
+        t = ws[: l * batch * N].view(l, batch * N)
+        cxp = ws[l * batch * N: (l + 2 * a) * batch * N].view(a, 2 * batch * N)
+        return t, cxp
+
+    def phase_batch(self, l, phase, batch, c2, key_table, ct, ws, ws_bytes, stream=None):
+        s = torch.cuda.current_stream().cuda_stream if stream is None else stream
+        check(LIB.b2_shard_keyswitch_phase_batch(self.ctx._h, l, phase, batch, c2.data_ptr(), key_table.ctypes.data, len(key_table),
+                                                 ct.data_ptr(), ws.data_ptr(), ws_bytes, s))
+
+    def keyswitch_batch(self, l, c2, key, ct, ws, group=None):
+        """the three phases and two all-gathers of one batch, on the current stream"""
+        batch = c2.shape[0]
+        ws_bytes = ws.numel() * 8
+        tab = key.pointer_table()
+        t, cxp = self._views(l, batch, ws)
+        g = self.group if group is None else group
+        self.phase_batch(l, 0, batch, c2, tab, ct, ws, ws_bytes)
+        allgather_limbs(t, l, self.rank, self.world, g)
+        self.phase_batch(l, 1, batch, c2, tab, ct, ws, ws_bytes)
+        allgather_limbs(cxp, self.ctx.size_P, self.rank, self.world, g)
+        self.phase_batch(l, 2, batch, c2, tab, ct, ws, ws_bytes)
+
+    def make_lanes(self, n_lanes):
+        """(stream, process group) pairs for `pipeline`: every lane has its own communicator, so that collectives of
+        different lanes do not queue behind one another. Collective: every rank must call it."""
+        ranks = list(range(self.world))
+        return [(torch.cuda.Stream(), dist.new_group(ranks) if self.world > 1 else None) for _ in range(n_lanes)]
+
+    def pipeline(self, l, batches, key, lanes, workspaces):
+        """batches: list of (c2, ct); batch i runs on lane i % len(lanes) with that lane's workspace. Returns after
+        queueing everything; the caller's stream waits for every lane."""
+        main = torch.cuda.current_stream()
+        for st, _ in lanes:
+            st.wait_stream(main)
+        for i, (c2, ct) in enumerate(batches):
+            st, grp = lanes[i % len(lanes)]
+            with torch.cuda.stream(st):
+                self.keyswitch_batch(l, c2, key, ct, workspaces[i % len(lanes)], grp)
+        for st, _ in lanes:
+            main.wait_stream(st)

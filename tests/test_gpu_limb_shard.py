@@ -49,6 +49,42 @@ def test_emulated_ranks_reproduce_the_key_switch(world, l):
     assert np.array_equal(host(ct2), want)
 
 
+@pytest.mark.parametrize("world,batch", [(1, 3), (2, 4), (3, 2), (8, 5)])
+@pytest.mark.parametrize("shape", ["n12", "n16"])
+def test_emulated_ranks_reproduce_a_batch_of_key_switches(world, batch, shape):
+    """the batched phases (one launch per kernel over the whole batch, limb-major exchange buffers) with the ranks run one
+    after another on shared buffers: every ciphertext of the batch must come out as the unsharded key switch gives it"""
+    if shape == "n12":
+        N, bits, special, levels = 4096, [55, 40, 41, 42, 43, 44, 45, 46, 58, 59, 60], 3, [8, 5]
+    else:
+        N, bits, special, levels = 65536, [60] + [40] * 23 + [60] * 8, 8, [24]
+        if world == 3:
+            pytest.skip("one ragged case is enough")
+    ctx, o = make_ctx(N, bits, special)
+    for l in levels:
+        beta = o.beta(l)
+        key = o.synth_key(beta, 71, 10)
+        kt, kp = key_dev(key)
+        c2_h = np.stack([o.fill(1, o.primes[:l], 71, 30 + b)[0] for b in range(batch)])
+        ct_h = np.stack([o.synth_ct(l, 71, 60 + b) for b in range(batch)])
+        c2, ct = dev(c2_h), dev(ct_h)
+        nbytes = int(LIB.b2_shard_batch_workspace_bytes(ctx._h, l, batch))
+        ws = torch.zeros(nbytes // 8, dtype=torch.int64, device="cuda")
+        for phase in range(3):
+            for r in range(world):
+                check(LIB.b2_ctx_set_shard(ctx._h, r, world))
+                check(LIB.b2_shard_keyswitch_phase_batch(ctx._h, l, phase, batch, c2.data_ptr(), kp.ctypes.data, beta, ct.data_ptr(),
+                                                         ws.data_ptr(), nbytes, stream()))
+        got = host(ct)
+        ref_ws, ref_nb = ctx.workspace(_native.OP_KEYSWITCH, l)
+        for b in range(batch):
+            one = dev(ct_h[b])
+            check(LIB.b2_keyswitch(ctx._h, l, c2[b].data_ptr(), kp.ctypes.data, beta, one.data_ptr(), ref_ws.data_ptr(), ref_nb, stream()))
+            assert np.array_equal(got[b], host(one)), (l, b)
+        assert np.array_equal(got[0], o.keyswitch(l, c2_h[0], key, ct_h[0]))
+    assert ctx.device_status() == 0
+
+
 def test_shard_argument_checks():
     ctx, o = make_ctx(4096, [40, 40, 50], 1)
     x = ctx.empty(2, 2)
@@ -83,6 +119,23 @@ c2, ct = dev(c2_h), dev(ct_h)
 sh.keyswitch(l, c2, key, ct)
 sh.allgather_ct(l, ct)
 ok = np.array_equal(host(ct), o.keyswitch(l, c2_h, key_h, ct_h))
+# batches of three on two lanes (own stream and communicator each), four batches in flight
+from pyPhantom.parallel import BatchedLimbShardedKeySwitch
+bs = BatchedLimbShardedKeySwitch(ctx)
+lanes = bs.make_lanes(2)
+B, n_batches = 3, 4
+c2s = [np.stack([o.fill(1, o.primes[:l], 72, 100 * i + b)[0] for b in range(B)]) for i in range(n_batches)]
+cts = [np.stack([o.synth_ct(l, 72, 1000 + 100 * i + b) for b in range(B)]) for i in range(n_batches)]
+batches = [(dev(a), dev(b)) for a, b in zip(c2s, cts)]
+wss = [bs.batch_workspace(l, B)[0] for _ in lanes]
+bs.pipeline(l, batches, key, lanes, wss)
+torch.cuda.synchronize()
+for i, (c2d, ctd) in enumerate(batches):
+    for b in range(B):
+        one = ctd[b]
+        bs.allgather_ct(l, one)
+        ok = ok and np.array_equal(host(one), o.keyswitch(l, c2s[i][b], key_h, cts[i][b]))
+ok = ok and ctx.device_status() == 0
 t = torch.tensor([1 if ok else 0], device="cuda"); dist.all_reduce(t, op=dist.ReduceOp.MIN)
 dist.destroy_process_group()
 sys.exit(0 if int(t.item()) == 1 else 1)
