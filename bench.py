@@ -677,38 +677,47 @@ def main():
         from pyPhantom.parallel import BatchedLimbShardedKeySwitch
         sh = BatchedLimbShardedKeySwitch(ctx)
         ws_sh, _ = sh.workspace(LEVEL)
-        c2_sh, ct_sh = dev_ct3[0][2], dev_ct3[0][:2].clone()
+        # one ciphertext spread over the ranks: every rank holds the SAME key and ciphertexts here (the data-parallel arm above
+        # gives each rank its own), drawn from a seed common to all ranks
+        key_sh = ph.relin_key.from_numpy(ctx, [synth.poly(N, primes, 2, 999, 10 + d) for d in range(BETA)])
+        key_sh_tab = key_sh.pointer_table()
+        gen_sh = torch.Generator(device="cuda")
+        gen_sh.manual_seed(999)
+        n_sh_ct = max(1, min(B, 32))
+        sh_ct3 = [torch.stack([torch.randint(0, int(q), (3, N), dtype=torch.int64, device="cuda", generator=gen_sh) for q in primes[:LEVEL]], dim=1)
+                  for _ in range(n_sh_ct)]
+        c2_sh, ct_sh = sh_ct3[0][2], sh_ct3[0][:2].clone()
         # what the sharded ranks produce is what one GPU's b2_keyswitch produces: gather the limbs and compare (every rank)
-        want = dev_ct3[0][:2].clone()
+        want = sh_ct3[0][:2].clone()
         ws1, ws1_bytes = wss[0]
-        check(LIB.b2_keyswitch(ctx._h, LEVEL, c2_sh.data_ptr(), key_tabs[0].ctypes.data, BETA, want.data_ptr(), ws1.data_ptr(), ws1_bytes,
+        check(LIB.b2_keyswitch(ctx._h, LEVEL, c2_sh.data_ptr(), key_sh_tab.ctypes.data, BETA, want.data_ptr(), ws1.data_ptr(), ws1_bytes,
                                stream.cuda_stream))
-        sh.keyswitch(LEVEL, c2_sh, keys[0], ct_sh, ws_sh)
+        sh.keyswitch(LEVEL, c2_sh, key_sh, ct_sh, ws_sh)
         sh.allgather_ct(LEVEL, ct_sh)
         ok = torch.equal(ct_sh, want)
         for _ in range(3):
-            sh.keyswitch(LEVEL, c2_sh, keys[0], ct_sh, ws_sh)
+            sh.keyswitch(LEVEL, c2_sh, key_sh, ct_sh, ws_sh)
         barrier()
         n_sh = max(10, min(args.steps, 50))
         s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         s0.record(stream)
         for _ in range(n_sh):
-            sh.keyswitch(LEVEL, c2_sh, keys[0], ct_sh, ws_sh)
+            sh.keyswitch(LEVEL, c2_sh, key_sh, ct_sh, ws_sh)
         s1.record(stream)
         barrier()
         t = torch.tensor([s0.elapsed_time(s1)], device="cuda")
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         us_one = 1e3 * float(t.item()) / n_sh
         # throughput: batches of LB ciphertexts, NB batches in flight on two lanes (own stream and communicator each)
-        LB, NB = max(1, min(8, B // 4)), 4
+        LB, NB = max(1, min(8, n_sh_ct // 4)), 4
         lanes = sh.make_lanes(2)
         wsb = [sh.batch_workspace(LEVEL, LB)[0] for _ in lanes]
-        batches = [(torch.stack([dev_ct3[(i * LB + b) % B][2] for b in range(LB)]), torch.stack([dev_ct3[(i * LB + b) % B][:2] for b in range(LB)]))
-                   for i in range(NB)]
+        batches = [(torch.stack([sh_ct3[(i * LB + b) % n_sh_ct][2] for b in range(LB)]),
+                    torch.stack([sh_ct3[(i * LB + b) % n_sh_ct][:2] for b in range(LB)])) for i in range(NB)]
         want_b = batches[0][1][0].clone()
-        check(LIB.b2_keyswitch(ctx._h, LEVEL, batches[0][0][0].data_ptr(), key_tabs[0].ctypes.data, BETA, want_b.data_ptr(), ws1.data_ptr(), ws1_bytes,
+        check(LIB.b2_keyswitch(ctx._h, LEVEL, batches[0][0][0].data_ptr(), key_sh_tab.ctypes.data, BETA, want_b.data_ptr(), ws1.data_ptr(), ws1_bytes,
                                stream.cuda_stream))
-        sh.pipeline(LEVEL, batches, keys[0], lanes, wsb)
+        sh.pipeline(LEVEL, batches, key_sh, lanes, wsb)
         got_b = batches[0][1][0].clone()
         sh.allgather_ct(LEVEL, got_b)
         ok = ok and torch.equal(got_b, want_b)
@@ -717,12 +726,12 @@ def main():
         if int(flag.item()) != 1:
             raise RuntimeError("limb-sharded key switch differs from the one-GPU key switch")
         for _ in range(2):
-            sh.pipeline(LEVEL, batches, keys[0], lanes, wsb)
+            sh.pipeline(LEVEL, batches, key_sh, lanes, wsb)
         barrier()
         n_pb = max(5, min(args.steps, 20))
         s0.record(stream)
         for _ in range(n_pb):
-            sh.pipeline(LEVEL, batches, keys[0], lanes, wsb)
+            sh.pipeline(LEVEL, batches, key_sh, lanes, wsb)
         s1.record(stream)
         barrier()
         t = torch.tensor([s0.elapsed_time(s1)], device="cuda")

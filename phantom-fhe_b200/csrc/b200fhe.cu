@@ -541,6 +541,7 @@ extern "C" int b2_ctx_create(size_t N, const uint64_t *primes, size_t size_QP, s
     if (N < 4096 || N > 65536 || (N & (N - 1))) return fail(B2_ESIZE, "ctx_create: poly_modulus_degree must be a power of two in [4096, 65536]");
     if (size_QP < 2 || size_QP > 64) return fail(B2_ESIZE, "ctx_create: the coefficient modulus must hold 2..64 primes");
     if (size_P < 1 || size_P >= size_QP) return fail(B2_EINVAL, "ctx_create: special_modulus_size must be in [1, size_QP)");
+    if (size_P > 16) return fail(B2_ESIZE, "ctx_create: special_modulus_size above 16 is not built");
     int ndev = 0;
     cudaError_t de = cudaGetDeviceCount(&ndev);
     if (de != cudaSuccess || ndev == 0) return fail(de != cudaSuccess ? (int)de : (int)cudaErrorNoDevice, "ctx_create: no CUDA device (this library has no CPU path)");
@@ -865,11 +866,9 @@ static int run_fwd(const b2_ctx *c, const uint64_t *src, uint64_t *dst, const Jo
     if (bd.batch != 1 && (c->use_cluster || c->use_pipe)) return fail(B2_EINVAL, "batched transforms need the two-pass kernels");
     if (SRC != 0 && (c->use_cluster || src_div == 0)) return fail(B2_EINVAL, "the on-the-fly source needs the two-pass transform");
     if (c->use_cluster) {
-        static thread_local bool attr_set = false;  // per instantiation (one per epilogue type) and thread
-        if (!attr_set) {
-            CUDA_TRY(cudaFuncSetAttribute(ntt_fwd_cluster<Epi>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)CL_SMEM));
-            attr_set = true;
-        }
+        // the attribute belongs to the (function, device) pair; setting it is cheap, so it is set on every launch path
+        // rather than remembered per thread (a thread may drive contexts on several devices)
+        CUDA_TRY(cudaFuncSetAttribute(ntt_fwd_cluster<Epi>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)CL_SMEM));
         LaunchScope ls(c, s, "ntt_fwd_cluster");
         ntt_fwd_cluster<Epi><<<njobs * CL_SIZE, CL_THREADS, CL_SMEM, s>>>(a, epi);
         LAUNCH_CHECK("ntt_fwd_cluster");
@@ -894,11 +893,7 @@ static int run_inv(const b2_ctx *c, const uint64_t *src, uint64_t *dst, const Jo
     NttArgs a{src, dst, jobs, first_prime, (uint32_t)c->logN, c->d_itw, c->d_mod, fin, 0, 0, 0, bd.src_lm1, bd.src_bs, bd.dst_lm1, bd.dst_bs};
     if (bd.batch != 1 && (c->use_cluster || c->use_pipe)) return fail(B2_EINVAL, "batched transforms need the two-pass kernels");
     if (c->use_cluster) {
-        static thread_local bool attr_set = false;
-        if (!attr_set) {
-            CUDA_TRY(cudaFuncSetAttribute(ntt_inv_cluster, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)CL_SMEM));
-            attr_set = true;
-        }
+        CUDA_TRY(cudaFuncSetAttribute(ntt_inv_cluster, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)CL_SMEM));
         LaunchScope ls(c, s, "ntt_inv_cluster");
         ntt_inv_cluster<<<njobs * CL_SIZE, CL_THREADS, CL_SMEM, s>>>(a);
         LAUNCH_CHECK("ntt_inv_cluster");

@@ -304,7 +304,7 @@ def create_bootstrap_key(context, encoder, dense_sk, sparse_hamming_weight=128, 
     bk.user_limbs = sQ - BOOT_LEVELS
     # sparse-secret encapsulation: s -> s' at the bottom prime, s' -> s at the top (src/bootstrap.cu:183-216)
     sparse = secret_key(seed=None)
-    sparse._rng = dense_sk._rng
+    sparse._rng, sparse._rng_pub = dense_sk._rng, dense_sk._rng_pub
     sparse.generate_sparse(ctx, sparse_hamming_weight)
     bk.small.to_sparse = sparse._kswitch_key(ctx, dense_sk.data)
     bk.small.to_dense = dense_sk._kswitch_key(ctx, sparse.data)

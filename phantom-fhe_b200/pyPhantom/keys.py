@@ -1,20 +1,82 @@
 """Key generation, symmetric encryption and decryption (binding.cu:77-98; src/secretkey.cu).
 
-Sampling is done on the host with numpy (key generation is set-up work, not the hot path); every
-polynomial operation - reduction into the limbs, NTT, products, sums - is a call into the C ABI.
-The reference seeds its samplers from std::random_device (include/prng.cuh:12-21), so keys are not
-reproducible there either: what is kept is the distributions (ternary or fixed-Hamming-weight
+Sampling is done on the host (key generation is set-up work, not the hot path); every polynomial
+operation - reduction into the limbs, NTT, products, sums - is a call into the C ABI.
+Randomness comes from a cryptographic generator: an AES-256-CTR keystream keyed from os.urandom,
+one stream for secret material (secrets, errors, encryption randomness) and an independent one for
+the public uniform masks, as the reference draws from a salsa20 stream seeded from
+std::random_device (src/prng.cu, include/prng.cuh:12-21). `seed=` swaps in numpy's PCG64 so that
+tests and benchmarks are reproducible: it is NOT secure and is meant for nothing else.
+Keys are not reproducible in the reference either: what is kept is the distributions (ternary or fixed-Hamming-weight
 secret, centred-binomial error with 21 coin pairs, uniform masks), the algebra
 (pk = (-(a s + e), a); digit d of a switching key adds P s' on the Q limbs of digit d,
 src/secretkey.cu:354-398, src/polymath.cu:317-337) and the save()/load() byte layouts, so keys and
 ciphertexts made here work with the reference's evaluator and the other way round.
 """
+import os
 import struct
 
 import numpy as np
 import torch
 
 from ._native import LIB, check
+
+
+class _CtrDrbg:
+    """The sampling calls this module makes (integers, binomial, choice) on an AES-256-CTR keystream keyed from
+    os.urandom. Uniform draws below a bound use rejection on words masked to the bound's bit length, so they are exactly
+    uniform; nothing here depends on a value already drawn except how many more words are fetched."""
+
+    def __init__(self):
+        from cryptography.hazmat.primitives.ciphers import Cipher, algorithms, modes
+        self._enc = Cipher(algorithms.AES(os.urandom(32)), modes.CTR(os.urandom(16))).encryptor()
+
+    def _words(self, n):
+        return np.frombuffer(self._enc.update(bytes(8 * int(n))), dtype=np.uint64)
+
+    def _below(self, bound, size):
+        bound = int(bound)
+        mask = np.uint64((1 << max(1, (bound - 1).bit_length())) - 1)
+        out = np.empty(size, dtype=np.uint64)
+        have = 0
+        while have < size:
+            w = self._words(max(64, int(1.25 * (size - have)) + 16)) & mask
+            w = w[w < np.uint64(bound)][: size - have]
+            out[have: have + w.size] = w
+            have += w.size
+        return out
+
+    def integers(self, low, high=None, size=None, dtype=np.int64):
+        if high is None:
+            low, high = 0, low
+        v = self._below(int(high) - int(low), int(size))
+        if np.dtype(dtype) == np.uint64:
+            return v + np.uint64(int(low))
+        return v.astype(np.int64) + int(low)
+
+    def binomial(self, n, p, size):
+        """number of heads in n <= 32 fair coins per sample (p must be 0.5)"""
+        if p != 0.5 or not 0 < n <= 32:
+            raise ValueError("fair coins only")
+        w = self._words((int(size) + 1) // 2).view(np.uint32)[: int(size)] & np.uint32((1 << n) - 1)
+        return np.unpackbits(w.view(np.uint8).reshape(-1, 4), axis=1).sum(axis=1).astype(np.int64)
+
+    def choice(self, a, size, replace=True):
+        if isinstance(a, (int, np.integer)):
+            if replace:
+                return self.integers(0, int(a), size)
+            keys = self._words(int(a))          # a uniform random subset: the positions of the `size` smallest keys
+            return np.argpartition(keys, int(size))[: int(size)]
+        a = np.asarray(a)
+        return a[self.integers(0, len(a), size)]
+
+
+def _rng_pair(seed):
+    """(secret stream, public-mask stream): cryptographic unless a test seed is given"""
+    if seed is None:
+        return _CtrDrbg(), _CtrDrbg()
+    a, b = np.random.SeedSequence(seed).spawn(2)
+    return np.random.default_rng(a), np.random.default_rng(b)
 
 _SK_HDR = struct.Struct("<QQQ")  # sk_max_power, N, coeff_mod_size (include/secretkey.h:537-554)
 
@@ -57,7 +119,7 @@ class public_key:
         from . import _native, ciphertext
         if self.pk is None:
             raise ValueError("PhantomPublicKey has not been generated")
-        rng = np.random.default_rng(seed)
+        rng, _ = _rng_pair(seed)
         n_all, sQ = ctx.size_QP, ctx.size_Q
         u = _expand(ctx, rng.integers(-1, 2, ctx.N).astype(np.int64), n_all)
         cx = ctx.empty(2, n_all)
@@ -92,7 +154,7 @@ class secret_key:
     by one with exactly `hamming_weight` non-zero (+-1) coefficients (src/secretkey.cu:513-590)."""
 
     def __init__(self, ctx=None, seed=None):
-        self._rng = np.random.default_rng(seed)
+        self._rng, self._rng_pub = _rng_pair(seed)  # secret material / public masks
         self.data = None  # [size_QP][N], NTT form, key level
         self.coeffs = None
         if ctx is not None:
@@ -113,7 +175,7 @@ class secret_key:
 
     # ---- encryption of zero under this secret: (-(a s + e), a) over the first n_limbs primes -------
     def _encrypt_zero(self, ctx, n_limbs):
-        a = _uniform(ctx, self._rng, n_limbs)
+        a = _uniform(ctx, self._rng_pub, n_limbs)
         e = _error(ctx, self._rng, n_limbs)
         c0 = ctx.empty(n_limbs)
         _poly(ctx, 2, n_limbs, a, self.data[:n_limbs], c0)

@@ -92,3 +92,24 @@ def test_numpy_generator_matches_the_golden_generator():
     o = Oracle(N, pr, 1)
     assert np.array_equal(synth.poly(N, pr, 2, 7, 3), o.fill(2, pr, 7, 3))
     assert np.array_equal(synth.fill_limbs(N, pr[:2], 9, 50), o.fill(1, pr[:2], 9, 50)[0])
+
+
+def test_key_sampling_uses_a_cryptographic_generator():
+    """secret material and public masks come from independent AES-CTR streams keyed from os.urandom unless a test seed is
+    given; the draws keep their distributions (exactly uniform below a bound, fair-coin binomial, distinct positions)"""
+    from pyPhantom import keys
+    a, b = keys._rng_pair(None)
+    assert isinstance(a, keys._CtrDrbg) and isinstance(b, keys._CtrDrbg) and a is not b
+    q = 1152921504606584833
+    x, y = a.integers(0, q, 1 << 16, dtype=np.uint64), b.integers(0, q, 1 << 16, dtype=np.uint64)
+    assert x.dtype == np.uint64 and int(x.max()) < q and not np.array_equal(x, y)
+    assert abs(float(x.astype(np.float64).mean()) / q - 0.5) < 0.01
+    t = a.integers(-1, 2, 1 << 16)
+    assert set(np.unique(t)) == {-1, 0, 1} and abs(np.bincount(t + 1) / (1 << 16) - 1 / 3).max() < 0.01
+    e = a.binomial(21, 0.5, 1 << 16) - a.binomial(21, 0.5, 1 << 16)
+    assert abs(e.mean()) < 0.05 and abs(e.var() - 10.5) < 0.3 and np.abs(e).max() <= 21
+    pos = a.choice(4096, size=128, replace=False)
+    assert len(set(pos.tolist())) == 128 and pos.min() >= 0 and pos.max() < 4096
+    assert set(np.unique(a.choice(np.array([-1, 1]), size=256))) == {-1, 1}
+    s1, s2 = keys._rng_pair(7)   # the reproducible test hook
+    assert isinstance(s1, np.random.Generator) and s1.integers(0, 10, 4).tolist() == keys._rng_pair(7)[0].integers(0, 10, 4).tolist()
