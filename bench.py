@@ -287,7 +287,9 @@ def bootstrap_section(ph, torch, np):
     return {"ms": float(np.median(times)), "ms_min": float(min(times)), "kernels_per_bootstrap": launches, "mode": "CUDA graph replay",
             "log2_max_err": math.log2(float(err.max())), "max_err": float(err.max()), "mean_err": float(err.mean()),
             "limbs_in": 2, "limbs_out": out.coeff_modulus_size(), "usable_levels_out": out.coeff_modulus_size() - 1, "chain_bits": "58|40x8|58x12|29x3|P 58x8",
-            "secret_hamming_weight": 192, "keygen_s": keygen_s, "kernels_eager": kernel_ms}
+            "secret_hamming_weight": 192, "keygen_s": keygen_s,
+            "key_bytes": int(bk.key_bytes), "key_bytes_what": "rotation keys (each with only the digits its shallowest use needs), conjugation and relinearisation key",
+            "kernels_eager": kernel_ms}
 
 
 def compositions_section(ph, ctx, torch, np, synth, primes, keys, N, level, reps=20):
@@ -709,8 +711,10 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         us_one = 1e3 * float(t.item()) / n_sh
         # throughput: batches of LB ciphertexts, NB batches in flight on two lanes (own stream and communicator each)
-        LB, NB = max(1, min(8, n_sh_ct // 4)), 4
-        lanes = sh.make_lanes(2)
+        n_lanes = max(1, int(os.environ.get("B2_SHARD_LANES", "2")))
+        LB = max(1, min(int(os.environ.get("B2_SHARD_BATCH", "8")), n_sh_ct // 4))
+        NB = max(4, 2 * n_lanes)
+        lanes = sh.make_lanes(n_lanes)
         wsb = [sh.batch_workspace(LEVEL, LB)[0] for _ in lanes]
         batches = [(torch.stack([sh_ct3[(i * LB + b) % n_sh_ct][2] for b in range(LB)]),
                     torch.stack([sh_ct3[(i * LB + b) % n_sh_ct][:2] for b in range(LB)])) for i in range(NB)]
@@ -741,12 +745,12 @@ def main():
         tviews = [sh._views(LEVEL, LB, w) for w in wsb]
         def exchanges():
             for i in range(NB):
-                st, grp = lanes[i % 2]
+                st, grp = lanes[i % n_lanes]
                 st.wait_stream(stream)
                 with torch.cuda.stream(st):
                     from pyPhantom.parallel import allgather_limbs
-                    allgather_limbs(tviews[i % 2][0], LEVEL, sh.rank, sh.world, grp)
-                    allgather_limbs(tviews[i % 2][1], SPECIAL, sh.rank, sh.world, grp)
+                    allgather_limbs(tviews[i % n_lanes][0], LEVEL, sh.rank, sh.world, grp)
+                    allgather_limbs(tviews[i % n_lanes][1], SPECIAL, sh.rank, sh.world, grp)
             for st, _ in lanes:
                 stream.wait_stream(st)
         exchanges()
@@ -761,7 +765,7 @@ def main():
         us_x = 1e3 * float(t.item()) / (n_pb * NB * LB)
         rx = int((LEVEL + 2 * SPECIAL) * LIMB_BYTES * (1 - 1 / world))
         limb_sharded = {"verified": True, "ranks": world, "keyswitch_per_s": 1e6 / us_b, "us_per_keyswitch": us_b,
-                        "batch_per_lane": LB, "batches_in_flight": NB, "lanes": 2,
+                        "batch_per_lane": LB, "batches_in_flight": NB, "lanes": n_lanes,
                         "one_ciphertext_latency_us": us_one,
                         "nvlink_bytes_received_per_gpu_per_keyswitch": rx,
                         "nvlink_gbs_per_gpu": rx / (us_b * 1e-6) / 1e9, "nvlink_frac_of_900": rx / (us_b * 1e-6) / 1e9 / 900.0,

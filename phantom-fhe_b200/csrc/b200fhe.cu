@@ -231,6 +231,7 @@ struct b2_ctx {
     bool bconv_int = false;        // B2_BCONV=int: force the 128-bit integer kernel
     int tc_wg = 4;                 // warpgroups per CTA of the tensor-core conversion (B2_BCONV_WG = 1, 2, 4)
     bool tc_simple = false;        // B2_BCONV_TC_SIMPLE=1: one CTA per tile instead of the persistent pipelined kernel
+    uint32_t tc_max_groups = 16;   // B2_BCONV_GROUPS: column groups per conversion job (8: at most 128 TMEM columns, four CTAs per SM)
     uint32_t *d_err = nullptr;     // device status word: set by a kernel whose bounded wait ran out
     std::vector<uint64_t> h_mat_dn, h_mat_dn_pinv;  // host copies of the ModDown matrices [size_Q][size_P]
     bool use_cluster = false;      // N = 2^16: single-launch transforms on 8-CTA clusters
@@ -476,6 +477,7 @@ static int build_level(b2_ctx *c, size_t l) {
         // the same conversions as tensor-core jobs: ModUp digits, then ModDown of up to two polynomials with the plain
         // matrix (cx layout [2][lP]) and with the P^-1-carrying one (compact P limbs [2][alpha])
         TcBuild tb;
+        tb.max_groups = c->tc_max_groups;
         std::vector<TcSpecOut> outs;
         uint32_t n_up = 0, n_dn = 0, n_dnf = 0;
         for (size_t d = 0; d < beta; d++) {
@@ -707,11 +709,23 @@ extern "C" int b2_ctx_create(size_t N, const uint64_t *primes, size_t size_QP, s
         const char *env_wg = getenv("B2_BCONV_WG");
         c->tc_wg = env_wg ? atoi(env_wg) : 4;
         if (c->tc_wg != 1 && c->tc_wg != 2 && c->tc_wg != 4) c->tc_wg = 4;
+        const char *env_groups = getenv("B2_BCONV_GROUPS");
+        if (env_groups && atoi(env_groups) >= 1 && atoi(env_groups) <= 16) c->tc_max_groups = (uint32_t)atoi(env_groups);
         const char *env_simple = getenv("B2_BCONV_TC_SIMPLE");
         c->tc_simple = env_simple && env_simple[0] == '1';
         if (cudaMalloc((void **)&c->d_err, 4) != cudaSuccess || cudaMemset(c->d_err, 0, 4) != cudaSuccess) {
             b2_ctx_destroy(c);
             return fail(B2_ENOMEM, "ctx_create: cudaMalloc(status word) failed");
+        }
+        if (c->logN == 16) {
+            // per device: the fused row pass stages a key tile next to its exchange buffer (49 KB, above the 48 KB default)
+            // <8, 4, 3> = the row-pass configuration of N = 2^16 (PassCfg<8>, asserted where the kernel is launched)
+            cudaError_t em = cudaFuncSetAttribute(ntt_fwd_rows_mac<8, 4, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                  (int)mac_smem_bytes<8, 4, 3>());
+            if (em != cudaSuccess) {
+                b2_ctx_destroy(c);
+                return fail((int)em, std::string("ctx_create: cudaFuncSetAttribute(ntt_fwd_rows_mac): ") + cudaGetErrorString(em));
+            }
         }
         if (c->bconv_tc) {
             // per device: the conversion asks for more dynamic shared memory than it uses (see tc_smem_request)
@@ -1740,8 +1754,9 @@ static int modup_inner_fused(b2_ctx *c, size_t l, const uint64_t *c2, const uint
             m.first_limb = pl.n_wideQ;
             LaunchScope ls(c, s, "ntt_fwd_rows_mac");
             static_assert(Cfg::R_STRIDED == Cfg::R_CONTIG, "the fused pass wants equal stage groups");
+            static_assert(Cfg::R_CONTIG == 4 && Cfg::LOG_C == 3, "b2_ctx_create raises the shared-memory limit of this instantiation");
             ntt_fwd_rows_mac<8, Cfg::R_CONTIG, Cfg::LOG_C>
-                <<<(uint32_t)(l - pl.n_wideQ) * (uint32_t)(N >> (8 + Cfg::LOG_C)), pass_threads<8>(), 0, s>>>(a, m);
+                <<<(uint32_t)(l - pl.n_wideQ) * (uint32_t)(N >> (8 + Cfg::LOG_C)), pass_threads<8>(), mac_smem_bytes<8, Cfg::R_CONTIG, Cfg::LOG_C>(), s>>>(a, m);
             LAUNCH_CHECK("ntt_fwd_rows_mac");
         }
     }
@@ -2467,6 +2482,7 @@ static int build_shard_level(b2_ctx *c, size_t l) {
     if (c->bconv_tc) {
         // tensor-core jobs over the rank's outputs (a rank may own no output of a digit, or no Q limb at all)
         TcBuild tb;
+        tb.max_groups = c->tc_max_groups;
         std::vector<TcSpecOut> outs;
         uint32_t n_up = 0, n_dn = 0, n_dn_b = 0;
         for (size_t d = 0; d < beta; d++) {

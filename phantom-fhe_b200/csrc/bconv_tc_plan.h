@@ -122,8 +122,9 @@ struct TcBuild {
     std::vector<TcGroup> groups;
     std::vector<uint8_t> images;
     bool ok = true;
+    uint32_t max_groups = 16;  // column groups per job: 16 -> up to 256 TMEM columns (two CTAs per SM), 8 -> 128 (four)
     // One conversion (a digit, a polynomial): outputs are packed, in order, into 16-column groups of equal byte count;
-    // more than 16 groups spill into further jobs over the same inputs. Returns the number of jobs added.
+    // more than max_groups groups are dealt evenly over further jobs on the same inputs. Returns the number of jobs added.
     uint32_t add(uint32_t in_slot0, uint32_t ni, uint32_t copy_dst, const std::vector<TcSpecOut> &outs, uint32_t in_stride = 1) {
         if (ni < 1 || ni > 8 || outs.empty()) {
             ok = false;
@@ -131,10 +132,20 @@ struct TcBuild {
         }
         uint32_t added = 0;
         size_t i = 0;
+        // groups the outputs need in all -> jobs of equal size
+        uint32_t total_groups = 0;
+        for (size_t k = 0; k < outs.size();) {
+            const uint32_t nb = tc_nbytes(outs[k].p), opg = 16 / nb;
+            uint32_t cnt = 0;
+            while (k < outs.size() && cnt < opg && tc_nbytes(outs[k].p) == nb) cnt++, k++;
+            total_groups++;
+        }
+        const uint32_t cap = std::max(1u, std::min(max_groups, 16u));
+        const uint32_t n_split = (total_groups + cap - 1) / cap, per_job = (total_groups + n_split - 1) / n_split;
         while (i < outs.size()) {
             TcJob job{in_slot0, ni, added == 0 ? copy_dst : 0xFFFFFFFFu, 0, (uint32_t)images.size(), (uint32_t)groups.size(), 32, in_stride - 1};
             std::vector<std::pair<size_t, uint32_t>> placed;  // (output index, first column) of this job
-            while (i < outs.size() && job.n_groups < 16) {
+            while (i < outs.size() && job.n_groups < per_job) {
                 const uint32_t nb = tc_nbytes(outs[i].p), opg = 16 / nb;
                 TcGroup g{};
                 g.nb = nb;

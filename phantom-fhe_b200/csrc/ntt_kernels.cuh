@@ -465,13 +465,32 @@ __device__ __forceinline__ u64x4 ld256_cs(const uint64_t *p) {  // streaming: th
     return v;
 }
 
+__device__ __forceinline__ void cp_async16(void *smem_dst, const void *gsrc) {
+    const uint32_t d = (uint32_t)__cvta_generic_to_shared(smem_dst);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(gsrc) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int KEEP>
+__device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;" ::"n"(KEEP) : "memory");
+}
+
+// bytes of dynamic shared memory the kernel wants: the exchange buffer and one digit's two key polynomials for the tile
+template <int LOG_T, int R, int LOG_C>
+constexpr size_t mac_smem_bytes() {
+    return (size_t)((1 << LOG_C) * ((1 << LOG_T) + ((1 << LOG_T) >> R)) + 2 * (1 << (LOG_C + LOG_T))) * 8;
+}
+
 template <int LOG_T, int R, int LOG_C>
 __global__ void __launch_bounds__((1 << (LOG_C + LOG_T)) >> R) ntt_fwd_rows_mac(NttArgs a, const __grid_constant__ MacArgs m) {
     using A = ArithFp;
     static_assert(2 * R == LOG_T, "equal stage groups: one register group per thread in both");
     constexpr int TT = 1 << LOG_T, E = 1 << R, C = 1 << LOG_C;
-    constexpr int TPAD = TT + (TT >> R);
-    __shared__ uint64_t sm[C * TPAD];
+    constexpr int TPAD = TT + (TT >> R), THREADS = (C * TT) >> R;
+    static_assert(E == 16, "the key staging below gives every thread eight 16-byte chunks per polynomial");
+    extern __shared__ __align__(16) uint64_t mac_smem[];
+    uint64_t *sm = mac_smem;             // [C][TPAD] exchange buffer of the row pass
+    uint64_t *kb = mac_smem + C * TPAD;  // [2][C * TT] the tile of both key polynomials of the digit in hand
     const size_t N = (size_t)1 << a.logN;
     const uint32_t tiles = (uint32_t)(N >> (LOG_T + LOG_C));
     const uint32_t t = m.first_limb + blockIdx.x / tiles, tile = blockIdx.x % tiles;
@@ -483,12 +502,25 @@ __global__ void __launch_bounds__((1 << (LOG_C + LOG_T)) >> R) ntt_fwd_rows_mac(
     const int c = tid / E, e = tid % E;  // sub-transform of the tile, register group within it (both stage groups)
     const uint32_t P = n1 + tile * C + c;
     const size_t base = (size_t)tile * C * TT;
-    const size_t o = base + (size_t)c * TT + (size_t)e * E;  // this thread's E consecutive outputs
+    const size_t o = base + (size_t)c * TT + (size_t)e * E;  // this thread's E consecutive outputs: tid * 16 into the tile
     const uint32_t own_d = t / m.alpha;
     double acc0[E], acc1[E];
 #pragma unroll
     for (int i = 0; i < E; i++) acc0[i] = acc1[i] = 0.0;
     for (uint32_t d = 0; d < m.beta; d++) {
+        // The digit's key tile starts its way from HBM now (cp.async, L1 bypassed: the key is read once) and is waited for
+        // only after this digit's butterflies: a thread's eight 16-byte chunks of a polynomial are XOR-swizzled inside its
+        // 128-byte row so that the 128-bit reads below are free of bank conflicts.
+        {
+            const uint64_t *g0 = m.evk[d] + (size_t)t * N + base, *g1 = g0 + (size_t)m.size_QP * N;
+#pragma unroll
+            for (int g = tid; g < C * TT / 2; g += THREADS) {
+                const int owner = g >> 3, chunk = g & 7, off = owner * 16 + ((chunk ^ (owner & 7)) << 1);
+                cp_async16(kb + off, g0 + 2 * g);
+                cp_async16(kb + C * TT + off, g1 + 2 * g);
+            }
+            cp_async_commit();
+        }
         double y[E];
         if (d == own_d) {
 #pragma unroll
@@ -506,23 +538,25 @@ __global__ void __launch_bounds__((1 << (LOG_C + LOG_T)) >> R) ntt_fwd_rows_mac(
             __syncthreads();
 #pragma unroll
             for (int i = 0; i < E; i++) y[i] = A::from_raw(sm[c * TPAD + pad_idx<LOG_T, R>(e * E + i)]);
-            __syncthreads();  // the next digit refills the buffer
             ct_stages<A, 0, R, E>(y, tw, P, R, e, k);
 #pragma unroll
             for (int i = 0; i < E; i++) y[i] = A::reduce(y[i], k);
         }
-        const uint64_t *k0 = m.evk[d] + (size_t)t * N + o, *k1 = k0 + (size_t)m.size_QP * N;
+        cp_async_wait<0>();
+        __syncthreads();  // every thread's share of the key tile has landed
 #pragma unroll
-        for (int i = 0; i < E; i += 4) {
-            const u64x4 u = ld256_cs(k0 + i), v = ld256_cs(k1 + i);
-            const uint64_t ku[4] = {u.a, u.b, u.c, u.d}, kv[4] = {v.a, v.b, v.c, v.d};
+        for (int i = 0; i < E; i += 2) {
+            const int off = tid * 16 + (((i >> 1) ^ (tid & 7)) << 1);
+            const ulonglong2 u = *reinterpret_cast<const ulonglong2 *>(kb + off), v = *reinterpret_cast<const ulonglong2 *>(kb + C * TT + off);
+            const uint64_t ku[2] = {u.x, u.y}, kv[2] = {v.x, v.y};
 #pragma unroll
-            for (int j = 0; j < 4; j++) {
+            for (int j = 0; j < 2; j++) {
                 const double w0 = A::from_u64(ku[j], k), w1 = A::from_u64(kv[j], k);
                 acc0[i + j] = __dadd_rn(acc0[i + j], A::mulmod(y[i + j], A::Tw{w0, __dmul_rn(w0, k.qinv)}, k));
                 acc1[i + j] = __dadd_rn(acc1[i + j], A::mulmod(y[i + j], A::Tw{w1, __dmul_rn(w1, k.qinv)}, k));
             }
         }
+        __syncthreads();  // the key tile and the exchange buffer are free for the next digit
     }
     const W2 pi = m.pinv[t];
     const uint64_t q = md.q;
@@ -661,16 +695,6 @@ ntt_inv_pass(NttArgs a) {
 // copy, L1 bypassed). The plain kernels above have bytes in flight only during the load phase of each CTA,
 // which bounds them near 2.5 TB/s; here every resident CTA always has a whole tile in flight.
 // ================================================================================================
-__device__ __forceinline__ void cp_async16(void *smem_dst, const void *gsrc) {
-    const uint32_t d = (uint32_t)__cvta_generic_to_shared(smem_dst);
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(gsrc) : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int KEEP>
-__device__ __forceinline__ void cp_async_wait() {
-    asm volatile("cp.async.wait_group %0;" ::"n"(KEEP) : "memory");
-}
-
 // tile `tile` of limb slot `slot` of src -> dense buffer ([e][c] or [c][e])
 template <int LOG_T, int LOG_C, bool COLS, int THREADS>
 __device__ __forceinline__ void stage_tile(uint64_t *buf, const uint64_t *src, size_t N, uint32_t slot, uint32_t tile) {

@@ -361,6 +361,24 @@ class relin_key:
             self._ptrs = np.array([pk.data.data_ptr() for pk in self.public_keys], dtype=np.uint64)
         return self._ptrs
 
+    def mod_drop_to_inplace(self, context, target_chain_index):
+        """src/secretkey.cu:301-352: keep only the ceil(size_Ql / alpha) digits a key switch at `target_chain_index` (or any
+        deeper level) reads; the digits beyond are released. A key that already has that many digits is left alone."""
+        if not self.public_keys:
+            raise ValueError("mod_drop_to_inplace: KSK not generated")
+        ctx = context
+        if target_chain_index < 1 or target_chain_index > ctx.size_Q:
+            raise ValueError("mod_drop_to_inplace: target_chain_index out of range")
+        beta_k = ctx.beta(ctx.limbs_at(target_chain_index))
+        if beta_k > len(self.public_keys):
+            raise RuntimeError("mod_drop_to_inplace: target chain requires more dnum entries than KSK has")
+        if beta_k < len(self.public_keys):
+            del self.public_keys[beta_k:]
+            self._ptrs = None
+
+    def device_bytes(self):
+        return sum(pk.data.numel() * 8 for pk in self.public_keys)
+
     def save(self, stream):
         if not self.public_keys:
             raise ValueError("PhantomRelinKey has not been generated")

@@ -260,11 +260,13 @@ class bootstrap_key:
         self.mono_i_neg = None  # -X^(N/2)
 
 
-def _key_for_elt(sk, ctx, elt):
+def _key_for_elt(sk, ctx, elt, limbs=0):
     check(LIB.b2_galois_prepare(ctx._h, elt))
     rot = ctx.empty(ctx.size_QP)
     check(LIB.b2_galois_permute(ctx._h, elt, sk.data.data_ptr(), rot.data_ptr(), ctx.size_QP, _stream()))
-    return sk._kswitch_key(ctx, rot)
+    # `limbs`: the most limbs any ciphertext has when this key switches it: only that level's digits are generated
+    # (the reference's per-level bootstrap keys, src/bootstrap.cu:1040-1158, src/secretkey.cu:400-472)
+    return sk._kswitch_key(ctx, rot, ctx.size_Q - limbs + 1 if limbs else 0)
 
 
 def _configure_scale(ctx, encoder, bk, user_scale):
@@ -347,12 +349,15 @@ def create_bootstrap_key(context, encoder, dense_sk, sparse_hamming_weight=128, 
     bk.s2c.append(None)
     _configure_scale(ctx, encoder, bk, user_scale)
     # rotation keys
-    steps = set()
+    # one key per rotation step, generated once at the shallowest level that uses it and shared by the deeper layers
+    need = {}
     for layer in bk.c2s + bk.s2c:
-        steps.update(layer.steps())
-    for s in sorted(steps):
-        bk.rot[s] = _key_for_elt(dense_sk, ctx, _elt(s, N))
-    bk.conj = _key_for_elt(dense_sk, ctx, 2 * N - 1)
+        for s in layer.steps():
+            need[s] = max(need.get(s, 0), layer.limbs)
+    for s in sorted(need):
+        bk.rot[s] = _key_for_elt(dense_sk, ctx, _elt(s, N), need[s])
+    bk.conj = _key_for_elt(dense_sk, ctx, 2 * N - 1, eval_top)
+    bk.key_bytes = sum(k.device_bytes() for k in bk.rot.values()) + bk.conj.device_bytes() + bk.relin.device_bytes()
     mono = np.zeros(N, dtype=np.int64)
     mono[N // 2] = 1
     d = torch.from_numpy(mono).to(ctx.device)

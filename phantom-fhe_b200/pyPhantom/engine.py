@@ -82,12 +82,14 @@ class ckks_engine:
         # non-owning fallbacks), the rest are generated
         n = N // 2
         self._glk = galois_key.from_keys([relin_key() for _ in elts])
-        for s, e in zip(user_steps, user_elts):
+        targets = list(cfg.user_rotation_target_chain_indices) or [0] * len(user_steps)
+        for s, e, target in zip(user_steps, user_elts, targets):
             shared = self._bk.rot.get(s % n)
             if shared is not None:
                 self._glk.set_fallback(elts.index(e), shared)
             else:
-                self._glk.relin_keys[elts.index(e)] = boot._key_for_elt(self._sk, self._ctx, e)
+                # generated with the digits its target chain index needs (src/ckks_engine.cu:300-352; 0: every digit)
+                self._glk.relin_keys[elts.index(e)] = boot._key_for_elt(self._sk, self._ctx, e, self._ctx.limbs_at(target) if target else 0)
         self._glk.set_fallback(elts.index(2 * N - 1), self._bk.conj)
         self._freshest = self._ctx.get_first_index() + boot.BOOT_LEVELS
         self._bottom = self._ctx.total_parm_size() - 1

@@ -192,11 +192,17 @@ class secret_key:
         pk.pk = ct
         return pk
 
-    def _kswitch_key(self, ctx, new_key):
-        """src/secretkey.cu:354-398: one (-(a s + e) + P s' [limb in digit d], a) per digit"""
+    def _kswitch_key(self, ctx, new_key, target_chain_index=0):
+        """src/secretkey.cu:354-398: one (-(a s + e) + P s' [limb in digit d], a) per digit. With a target chain index
+        (src/secretkey.cu:400-472) only the ceil(size_Ql / alpha) digits a key switch at that level or deeper reads are
+        made; each is still a key-level ciphertext, the missing ones are never materialised."""
         from . import ciphertext, relin_key
         a, sQ, N = ctx.size_P, ctx.size_Q, ctx.N
         dnum = (sQ + a - 1) // a
+        if target_chain_index:
+            if target_chain_index < 1 or target_chain_index > sQ:
+                raise ValueError("generate_one_kswitch_key_at_level: target_chain_index out of range")
+            dnum = ctx.beta(ctx.limbs_at(target_chain_index))
         P = 1
         for p in ctx.primes[sQ:]:
             P *= int(p)
@@ -233,10 +239,12 @@ class secret_key:
         return self._kswitch_key(ctx, s2)
 
     def create_one_galois_key(self, ctx, galois_elt_idx, target_chain_index=0):
+        """src/secretkey.cu:684-724: the key of one Galois element, with only the digits `target_chain_index` needs
+        (0: every digit)"""
         elt = ctx.galois_elts[galois_elt_idx]
         rot = ctx.empty(ctx.size_QP)
         check(LIB.b2_galois_permute(ctx._h, elt, self.data.data_ptr(), rot.data_ptr(), ctx.size_QP, _stream()))
-        return self._kswitch_key(ctx, rot)
+        return self._kswitch_key(ctx, rot, target_chain_index)
 
     def create_galois_keys(self, ctx):
         """one key per Galois element of the context, same order (src/secretkey.cu:642-682)"""
@@ -244,17 +252,16 @@ class secret_key:
         return galois_key.from_keys([self.create_one_galois_key(ctx, i) for i in range(len(ctx.galois_elts))])
 
     def create_galois_keys_per_level(self, ctx, indices, target_chain_indices):
-        """src/secretkey.cu:726-775: keys only for the listed Galois-element indices; the other slots stay empty (to be
-        served by fallbacks). The reference truncates each key to the limbs its target chain index needs; here every key
-        is generated at full size, which serves any level."""
+        """src/secretkey.cu:726-775: keys only for the listed Galois-element indices, each with the digits its target
+        chain index needs (0: all of them); the other slots stay empty (to be served by fallbacks)."""
         from . import galois_key, relin_key
         if len(indices) != len(target_chain_indices):
             raise ValueError("create_galois_keys_per_level: indices and target_chain_indices must have the same length")
         out = galois_key.from_keys([relin_key() for _ in ctx.galois_elts])
-        for idx in indices:
+        for idx, target in zip(indices, target_chain_indices):
             if idx >= len(ctx.galois_elts):
                 raise IndexError("create_galois_keys_per_level: index out of range")
-            out.relin_keys[idx] = self.create_one_galois_key(ctx, idx)
+            out.relin_keys[idx] = self.create_one_galois_key(ctx, idx, int(target))
         return out
 
     # ---- data path ------------------------------------------------------------------------------------

@@ -20,6 +20,7 @@ static uint64_t rnd() {
 }
 static uint64_t rnd_odd_bits(int bits) { return ((rnd() >> (64 - bits)) | (1ull << (bits - 1)) | 1ull); }
 
+static uint32_t g_max_groups = 16;
 static int run_case(int ni, const std::vector<int> &in_bits, const std::vector<int> &out_bits, bool extremes) {
     std::vector<uint64_t> q(ni), p(out_bits.size());
     for (int i = 0; i < ni; i++) q[i] = rnd_odd_bits(in_bits[i]);
@@ -31,6 +32,7 @@ static int run_case(int ni, const std::vector<int> &in_bits, const std::vector<i
         outs.push_back(b2::TcSpecOut{(uint32_t)(100 + j), p[j], &mat[j * ni]});
     }
     b2::TcBuild tb;
+    tb.max_groups = g_max_groups;
     const uint32_t n_jobs = tb.add(3, (uint32_t)ni, 0xFFFFFFFFu, outs);
     if (!tb.ok || n_jobs == 0) return printf("planner refused a valid case\n"), 1;
     const int ROWS = 128;
@@ -47,7 +49,7 @@ static int run_case(int ni, const std::vector<int> &in_bits, const std::vector<i
     std::vector<char> seen(out_bits.size(), 0);
     for (uint32_t jb = 0; jb < n_jobs; jb++) {
         const b2::TcJob &job = tb.jobs[jb];
-        if (job.n_groups < 1 || job.n_groups > 16 || job.alloc_cols < 16 * job.n_groups || (job.alloc_cols & (job.alloc_cols - 1)) || job.alloc_cols < 32 ||
+        if (job.n_groups < 1 || job.n_groups > g_max_groups || job.alloc_cols < 16 * job.n_groups || (job.alloc_cols & (job.alloc_cols - 1)) || job.alloc_cols < 32 ||
             job.alloc_cols > 512 || (job.img_off & 15))
             return printf("bad job header\n"), 1;
         const uint8_t *B = tb.images.data() + job.img_off;
@@ -109,10 +111,14 @@ int main(int argc, char **argv) {
     for (int i = 0; i < 15; i++) up1_out.push_back(40);
     for (int i = 0; i < 8; i++) up1_out.push_back(60);
     std::vector<int> in_d0{60, 40, 40, 40, 40, 40, 40, 40};
-    for (int ex = 0; ex < 2; ex++) {
-        if (run_case(8, p60, dn_out, ex) || run_case(8, in_d0, up0_out, ex) || run_case(8, p40, up1_out, ex)) return 1;
-        cases += 3;
+    for (uint32_t mg : {16u, 8u, 3u}) {   // column groups per job: the default, the four-CTAs-per-SM split, a tiny one
+        g_max_groups = mg;
+        for (int ex = 0; ex < 2; ex++) {
+            if (run_case(8, p60, dn_out, ex) || run_case(8, in_d0, up0_out, ex) || run_case(8, p40, up1_out, ex)) return 1;
+            cases += 3;
+        }
     }
+    g_max_groups = 16;
     // every byte count, ragged inputs, more outputs than one job holds, 61-bit primes
     for (int bits = 17; bits <= 61; bits++) {
         std::vector<int> out(5, bits);

@@ -323,3 +323,50 @@ def test_inner_sum_replicate_and_polynomial(kit):
         assert y.chain_index() == 1 + m + (d + m) // m - 2 and y.scale() == SCALE
         got = enc.decode_double_vector(ctx, sk.decrypt(ctx, y))
         assert np.max(np.abs(got - np.polynomial.polynomial.polyval(x, coeffs))) < 1e-4
+
+
+def test_level_truncated_keys(kit, tmp_path):
+    """Keys with only the digits a level needs (src/secretkey.cu:301-352, 400-472, 726-775): 5 Q limbs in digits of 2 give
+    3 digits at the top; a ciphertext with 2 limbs needs one. A truncated key switches that level like the full key does
+    in meaning (other randomness: compare decryptions), refuses levels that need more digits, survives save / load, and
+    serves as a fallback of a Galois-key bundle."""
+    ctx, sk, enc = kit["ctx"], kit["sk"], kit["enc"]
+    assert ctx.beta(ctx.size_Q) == 3
+    low_chain = ctx.size_Q - 2 + 1                       # chain index whose ciphertexts have 2 limbs
+    x = kit["x"]
+    ct_low = sk.encrypt_symmetric(ctx, enc.encode_complex_vector(ctx, x, SCALE, low_chain))
+    assert ct_low.coeff_modulus_size() == 2
+    full = sk.gen_relinkey(ctx)
+    assert full.dnum() == 3
+    dropped = sk.gen_relinkey(ctx)
+    dropped.mod_drop_to_inplace(ctx, low_chain)
+    assert dropped.dnum() == 1 and dropped.device_bytes() * 3 == full.device_bytes()
+    dropped.mod_drop_to_inplace(ctx, low_chain)           # already there: nothing happens
+    assert dropped.dnum() == 1
+    with pytest.raises(RuntimeError, match="more dnum entries"):
+        dropped.mod_drop_to_inplace(ctx, 1)
+    with pytest.raises(ValueError):
+        dropped.mod_drop_to_inplace(ctx, 0)
+    sq = ph.rescale_to_next(ctx, ph.multiply_and_relin(ctx, ct_low, ct_low, dropped))
+    assert np.max(np.abs(_dec(kit, sq) - x * x)) < 1e-4
+    with pytest.raises(ValueError, match="fewer digits"):
+        ph.multiply_and_relin(ctx, kit["cx"], kit["cx"], dropped)   # 5 limbs need all three digits
+    # generated at a level: the same number of digits, never more
+    idx = ctx.galois_elts.index(ph.get_elt_from_step(1, N))
+    one = sk.create_one_galois_key(ctx, idx, low_chain)
+    assert one.dnum() == 1 and sk.create_one_galois_key(ctx, idx).dnum() == 3
+    want = np.roll(x, -1)
+    assert np.max(np.abs(_dec(kit, ph.rotate_with_key(ctx, ct_low, 1, one)) - want)) < 1e-6
+    per_level = sk.create_galois_keys_per_level(ctx, [idx], [low_chain])
+    assert per_level.get_relin_keys(idx).dnum() == 1 and per_level.resolve(idx + 1 if idx + 1 < len(ctx.galois_elts) else 0) is None
+    assert np.max(np.abs(_dec(kit, ph.rotate(ctx, ct_low, 1, per_level)) - want)) < 1e-6
+    with pytest.raises(ValueError):
+        sk.create_galois_keys_per_level(ctx, [idx], [low_chain, 1])
+    # bytes: a truncated key is its first digits, in the reference's layout
+    with open(tmp_path / "k.bin", "wb") as f:
+        one.save(f)
+    back = ph.relin_key().load(open(tmp_path / "k.bin", "rb"))
+    assert back.dnum() == 1 and torch.equal(back.public_keys[0].data, one.public_keys[0].data)
+    bundle = ph.galois_key.from_keys([ph.relin_key() for _ in ctx.galois_elts])
+    bundle.set_fallback(idx, back)
+    assert np.max(np.abs(_dec(kit, ph.rotate(ctx, ct_low, 1, bundle)) - want)) < 1e-6
