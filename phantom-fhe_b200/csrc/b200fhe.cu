@@ -215,6 +215,7 @@ struct b2_ctx {
     W2 *d_fin_plain = nullptr;  // [size_QP][2] = {N^-1, itw[1]}
     W2 *d_fin_P = nullptr;      // [size_P][2]  = the same times (P/p_i)^-1 mod p_i
     W2 *d_Pinv = nullptr;       // [size_QP] indexed by prime (valid for Q primes): P^-1 mod q_j
+    W2 *d_macfin = nullptr;     // [size_QP] closing constant of the fused inner product's Montgomery sums: P^-1 * 2^64 mod q_j, 2^64 mod p_i
     uint64_t *d_mat_dn = nullptr;  // [size_Q][size_P]: (P/p_i) mod q_j
     uint64_t *d_mat_dn_pinv = nullptr;  // the same times P^-1 mod q_j (fused key switch)
     uint64_t *d_one = nullptr;     // [size_QP] ones: the [n_out][1] "matrix" of the rescale reduction
@@ -231,11 +232,18 @@ struct b2_ctx {
     bool bconv_int = false;        // B2_BCONV=int: force the 128-bit integer kernel
     int tc_wg = 4;                 // warpgroups per CTA of the tensor-core conversion (B2_BCONV_WG = 1, 2, 4)
     bool tc_simple = false;        // B2_BCONV_TC_SIMPLE=1: one CTA per tile instead of the persistent pipelined kernel
+    bool tc_serial_ld = false;     // B2_BCONV_SERIAL_LD=1: the epilogue waits for every TMEM load before it reduces (no load in flight)
     uint32_t tc_max_groups = 16;   // B2_BCONV_GROUPS: column groups per conversion job (8: at most 128 TMEM columns, four CTAs per SM)
     uint32_t *d_err = nullptr;     // device status word: set by a kernel whose bounded wait ran out
     std::vector<uint64_t> h_mat_dn, h_mat_dn_pinv;  // host copies of the ModDown matrices [size_Q][size_P]
     bool use_cluster = false;      // N = 2^16: single-launch transforms on 8-CTA clusters
     bool use_pipe = false;         // N = 2^16: persistent passes with asynchronous double-buffered tile loads
+    bool mac_interleave = false;   // B2_KS_FUSED_ORDER=1: consecutive CTAs of the fused pass walk limbs, not tiles (measured slower)
+    // B2_KS_FUSED_WIDE=1: the fused pass also takes the limbs on primes of 41 bits and more (q0 and P at the usual
+    // parameters), 10 launches per key switch instead of 12 and no stored digits at all. Measured on B200 at N = 2^16,
+    // l = 24: 8 us less for a lone key switch, but 4 % fewer key switches per second over four streams (the stand-alone
+    // inner product is memory-bound and hides behind other streams' transforms; fused, it is integer-multiply work).
+    bool mac_wide = false;
     bool use_mac = false;          // N = 2^16: ModUp's last forward pass carries the inner product (off with B2_KS_FUSED_IP=0)
     int sm_count = 148;
     // RNS-limb sharding of one ciphertext over `shard_world` GPUs: this rank's slice of every list
@@ -517,6 +525,7 @@ extern "C" void b2_ctx_destroy(b2_ctx *c) {
     cudaFree(c->d_fin_plain);
     cudaFree(c->d_fin_P);
     cudaFree(c->d_Pinv);
+    cudaFree(c->d_macfin);
     cudaFree(c->d_mat_dn);
     cudaFree(c->d_mat_dn_pinv);
     cudaFree(c->d_one);
@@ -682,6 +691,14 @@ extern "C" int b2_ctx_create(size_t N, const uint64_t *primes, size_t size_QP, s
     }
     if (e == cudaSuccess) e = up((void **)&c->d_fin_P, fin_P.data(), sizeof(W2) * 2 * sP);
     if (e == cudaSuccess) e = up((void **)&c->d_Pinv, Pinv.data(), sizeof(W2) * size_QP);
+    {
+        std::vector<W2> macfin(size_QP);
+        for (size_t j = 0; j < size_QP; j++) {
+            const uint64_t r64 = (uint64_t)((((unsigned __int128)1) << 64) % c->q[j]);
+            macfin[j] = h_w2(j < sQ ? h_mulmod(Pinv[j].w, r64, c->q[j]) : r64, c->q[j]);
+        }
+        if (e == cudaSuccess) e = up((void **)&c->d_macfin, macfin.data(), sizeof(W2) * size_QP);
+    }
     if (e == cudaSuccess) e = up((void **)&c->d_mat_dn, mat_dn.data(), 8 * sQ * sP);
     if (e == cudaSuccess) e = up((void **)&c->d_mat_dn_pinv, mat_dn_pinv.data(), 8 * sQ * sP);
     if (e == cudaSuccess) e = up((void **)&c->d_one, ones.data(), 8 * size_QP);
@@ -709,6 +726,8 @@ extern "C" int b2_ctx_create(size_t N, const uint64_t *primes, size_t size_QP, s
         const char *env_wg = getenv("B2_BCONV_WG");
         c->tc_wg = env_wg ? atoi(env_wg) : 4;
         if (c->tc_wg != 1 && c->tc_wg != 2 && c->tc_wg != 4) c->tc_wg = 4;
+        const char *env_sld = getenv("B2_BCONV_SERIAL_LD");
+        c->tc_serial_ld = env_sld && env_sld[0] == '1';
         const char *env_groups = getenv("B2_BCONV_GROUPS");
         if (env_groups && atoi(env_groups) >= 1 && atoi(env_groups) <= 16) c->tc_max_groups = (uint32_t)atoi(env_groups);
         const char *env_simple = getenv("B2_BCONV_TC_SIMPLE");
@@ -746,6 +765,8 @@ extern "C" int b2_ctx_create(size_t N, const uint64_t *primes, size_t size_QP, s
     const char *env_pipe = getenv("B2_NTT_PIPE");
     c->use_pipe = (c->logN == 16) && env_pipe && env_pipe[0] == '1';
     const char *env_mac = getenv("B2_KS_FUSED_IP");
+    if (const char *e = getenv("B2_KS_FUSED_WIDE")) c->mac_wide = e[0] != '0';
+    if (const char *e = getenv("B2_KS_FUSED_ORDER")) c->mac_interleave = e[0] == '1';
     c->use_mac = (c->logN == 16) && !c->use_cluster && !c->use_pipe && !(env_mac && env_mac[0] == '0');
     cudaDeviceGetAttribute(&c->sm_count, cudaDevAttrMultiProcessorCount, c->device);
     if (c->sm_count < 1) c->sm_count = 148;
@@ -1506,7 +1527,8 @@ static int run_bconv_tc(const b2_ctx *c, bool copy, const uint64_t *in, uint64_t
     const uint32_t N = (uint32_t)c->N;
     if (n_jobs == 0) return B2_OK;
     if (copy && !copy_src) return fail(B2_EINVAL, "base conversion: missing copy source");
-    const TcBatch tb = tbp ? *tbp : TcBatch{1, 0, 0, 0, 0};
+    TcBatch tb = tbp ? *tbp : TcBatch{1, 0, 0, 0, 0, 0};
+    tb.serial_ld = c->tc_serial_ld ? 1u : 0u;
     if (tb.batch != 1 && (copy || c->tc_simple)) return fail(B2_EINVAL, "a batched base conversion runs on the persistent kernel, without the own-limb copy");
     LaunchScope ls(c, s, "bconv");
     // without the copy the jobs' copy slots are ignored by handing the kernel a null source
@@ -1715,7 +1737,7 @@ static int modup_inner_fused(b2_ctx *c, size_t l, const uint64_t *c2, const uint
     const size_t N = c->N, lP = l + c->size_P, beta = c->plan[l].beta;
     const LevelPlan &pl = c->plan[l];
     *done = false;
-    if (!(c->use_mac && pl.mac_ok && n_evk >= beta && aligned32(c2) && aligned32(ct) && aligned32(up))) return B2_OK;
+    if (!(c->use_mac && (pl.mac_ok || (c->mac_wide && beta <= B2_MAC_MAX_BETA)) && n_evk >= beta && aligned32(c2) && aligned32(ct) && aligned32(up) && aligned32(cxP))) return B2_OK;
     {
         // ModUp up to the column pass for every limb; the row pass is stored only for the limbs the stand-alone inner
         // product still handles (wide Q primes and P); for the FP64 limbs of Q it runs inside ntt_fwd_rows_mac
@@ -1731,7 +1753,10 @@ static int modup_inner_fused(b2_ctx *c, size_t l, const uint64_t *c2, const uint
                 <<<pl.n_up_ntt * (uint32_t)(N >> (8 + Cfg::LOG_CC)), pass_threads<8, true>(), 0, s>>>(a, EpiStore{});
             LAUNCH_CHECK("ntt_fwd_pass");
         }
-        if (pl.n_up_rows) {
+        // the limbs on 60-bit primes (q0, P) either ride on the fused pass too (integer arithmetic) or, mac_wide off,
+        // keep the stored row pass and the stand-alone inner product
+        const bool wide = c->mac_wide;
+        if (!wide && pl.n_up_rows) {
             NttArgs b = a;
             b.jobs = pl.jobs_up_rows;
             LaunchScope ls(c, s, "ntt_fwd_rows");
@@ -1739,9 +1764,11 @@ static int modup_inner_fused(b2_ctx *c, size_t l, const uint64_t *c2, const uint
                 <<<pl.n_up_rows * (uint32_t)(N >> (8 + Cfg::LOG_C)), pass_threads<8>(), 0, s>>>(b, EpiStore{});
             LAUNCH_CHECK("ntt_fwd_pass");
         }
-        const uint4 rest = make_uint4(0, pl.n_wideQ, 0, (uint32_t)c->size_P);
-        rc = inner_prod_impl(c, l, up, c2, evk, n_evk, cxP, ct, true, s, &rest, acc_p);
-        if (rc) return rc;
+        if (!wide) {
+            const uint4 rest = make_uint4(0, pl.n_wideQ, 0, (uint32_t)c->size_P);
+            rc = inner_prod_impl(c, l, up, c2, evk, n_evk, cxP, ct, true, s, &rest, acc_p);
+            if (rc) return rc;
+        }
         {
             MacArgs m{};
             m.own = c2;
@@ -1749,14 +1776,17 @@ static int modup_inner_fused(b2_ctx *c, size_t l, const uint64_t *c2, const uint
                 if (!evk[d]) return fail(B2_EINVAL, "null evaluation-key digit");
                 m.evk[d] = evk[d];
             }
-            m.ct = ct, m.pinv = c->d_Pinv;
-            m.l = (uint32_t)l, m.lP = (uint32_t)lP, m.alpha = (uint32_t)c->size_P, m.beta = (uint32_t)beta, m.size_QP = (uint32_t)c->size_QP;
-            m.first_limb = pl.n_wideQ;
+            m.ct = ct, m.cxp = cxP, m.pinv = c->d_Pinv, m.fin = c->d_macfin;
+            m.l = (uint32_t)l, m.lP = (uint32_t)lP, m.alpha = (uint32_t)c->size_P, m.beta = (uint32_t)beta;
+            m.size_Q = (uint32_t)c->size_Q, m.size_QP = (uint32_t)c->size_QP;
+            m.first_limb = wide ? 0 : pl.n_wideQ, m.p_first = wide ? (uint32_t)c->size_P : 0, m.acc_p = acc_p ? 1 : 0;
+            m.interleave = c->mac_interleave ? 1 : 0;
+            const uint32_t n_limbs = (uint32_t)l - m.first_limb + m.p_first;
             LaunchScope ls(c, s, "ntt_fwd_rows_mac");
             static_assert(Cfg::R_STRIDED == Cfg::R_CONTIG, "the fused pass wants equal stage groups");
             static_assert(Cfg::R_CONTIG == 4 && Cfg::LOG_C == 3, "b2_ctx_create raises the shared-memory limit of this instantiation");
             ntt_fwd_rows_mac<8, Cfg::R_CONTIG, Cfg::LOG_C>
-                <<<(uint32_t)(l - pl.n_wideQ) * (uint32_t)(N >> (8 + Cfg::LOG_C)), pass_threads<8>(), mac_smem_bytes<8, Cfg::R_CONTIG, Cfg::LOG_C>(), s>>>(a, m);
+                <<<n_limbs * (uint32_t)(N >> (8 + Cfg::LOG_C)), pass_threads<8>(), mac_smem_bytes<8, Cfg::R_CONTIG, Cfg::LOG_C>(), s>>>(a, m);
             LAUNCH_CHECK("ntt_fwd_rows_mac");
         }
     }
@@ -2611,7 +2641,7 @@ extern "C" int b2_shard_keyswitch_phase_batch(b2_ctx *c, size_t l, int phase, si
         case 0:
             return run_inv(c, d_c2, T, pl.jobs_up_intt + sp.q0, sp.nq, 0, pl.fin_up, s, BatchDims{B, 0, (uint32_t)l, B - 1, 1});
         case 1: {
-            const TcBatch tb{B, B - 1, 1, 0, per};
+            const TcBatch tb{B, B - 1, 1, 0, per, 0};
             if (sp.tc_up.jobs) {
                 rc = run_bconv_tc(c, false, T, UP, nullptr, sp.tc_up, sp.tc_up.n_jobs, s, &tb);
                 if (rc) return rc;
@@ -2626,7 +2656,7 @@ extern "C" int b2_shard_keyswitch_phase_batch(b2_ctx *c, size_t l, int phase, si
         }
         case 2: {
             if (sp.nq == 0) return B2_OK;
-            const TcBatch tb{B, B - 1, 1, 0, per};
+            const TcBatch tb{B, B - 1, 1, 0, per, 0};
             rc = run_bconv_tc(c, false, CXP, UP, nullptr, sp.tc_dn_b, sp.tc_dn_b.n_jobs, s, &tb);
             if (rc) return rc;
             return run_fwd(c, UP, UP, sp.jobs_dn_ntt, 2 * sp.nq, 0, EpiSubFrom{d_ct, (uint32_t)(2 * l)}, s, 0, 0, 0, BatchDims{B, 0, per, 0, per});

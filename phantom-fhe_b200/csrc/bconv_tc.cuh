@@ -55,6 +55,24 @@ __device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t (&c)[16]) {
         : "memory");
 }
 
+// the same load without the wait, and the wait as a statement that owns the registers: a group's planes can be on their way
+// while the previous group is reduced
+__device__ __forceinline__ void tc_ld16_nowait(uint32_t taddr, uint32_t (&c)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];\n"
+        : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3]), "=r"(c[4]), "=r"(c[5]), "=r"(c[6]), "=r"(c[7]), "=r"(c[8]), "=r"(c[9]),
+          "=r"(c[10]), "=r"(c[11]), "=r"(c[12]), "=r"(c[13]), "=r"(c[14]), "=r"(c[15])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tc_wait_ld(uint32_t (&c)[16]) {
+    asm volatile("tcgen05.wait::ld.sync.aligned;\n"
+                 : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3]), "+r"(c[4]), "+r"(c[5]), "+r"(c[6]), "+r"(c[7]), "+r"(c[8]), "+r"(c[9]),
+                   "+r"(c[10]), "+r"(c[11]), "+r"(c[12]), "+r"(c[13]), "+r"(c[14]), "+r"(c[15])
+                 :
+                 : "memory");
+}
+
 template <int NB>
 __device__ __forceinline__ void tc_group_outputs(const uint32_t (&c)[16], const TcGroup *g, uint32_t n_valid, uint64_t *__restrict__ out, size_t N,
                                                  uint32_t n) {
@@ -266,6 +284,7 @@ __device__ __forceinline__ void tc_cp_async16(uint32_t smem_dst, const void *gsr
 // slot s at s * (out_lm1 + 1) + b * out_bs (batch-major and limb-major buffers as for the transforms, ntt_kernels.cuh)
 struct TcBatch {
     uint32_t batch, in_lm1, in_bs, out_lm1, out_bs;
+    uint32_t serial_ld;  // 1: wait for every TMEM load before reducing it (no second register set in flight)
 };
 
 template <int WG>
@@ -399,9 +418,7 @@ __global__ void __launch_bounds__(128 * WG) bconv_tc_persist(const uint64_t *__r
             uint64_t *out_n = out + (size_t)bset * tb.out_bs * N + (tile * 128 + wq * 32 + lane);
             // (dealing single outputs instead of whole groups over the warpgroups evens the work but triples the TMEM loads:
             // measured 56 against 37 us per key switch)
-            for (uint32_t g = wg; g < job.n_groups; g += WG) {
-                uint32_t c[16];
-                tc_ld16(lane_base + g * 16, c);
+            auto reduce_group = [&](const uint32_t (&c)[16], uint32_t g) {
                 const uint32_t mo = tc_smem_u32(sOut + 4 * g);
                 switch (sNb[g]) {
                     case 4: tc_group_lean<4>(c, mo, out_n); break;
@@ -409,6 +426,30 @@ __global__ void __launch_bounds__(128 * WG) bconv_tc_persist(const uint64_t *__r
                     case 6: tc_group_lean<6>(c, mo, out_n); break;
                     case 7: tc_group_lean<7>(c, mo, out_n); break;
                     default: tc_group_lean<8>(c, mo, out_n); break;
+                }
+            };
+            // two register sets: the next group's planes travel from TMEM while this one is reduced
+            uint32_t ca[16], cb[16];
+            uint32_t g = wg;
+            if (tb.serial_ld) {
+                for (; g < job.n_groups; g += WG) {
+                    tc_ld16(lane_base + g * 16, ca);
+                    reduce_group(ca, g);
+                }
+            } else {
+                if (g < job.n_groups) tc_ld16_nowait(lane_base + g * 16, ca);
+                while (g < job.n_groups) {
+                    tc_wait_ld(ca);
+                    uint32_t gn = g + WG;
+                    if (gn < job.n_groups) tc_ld16_nowait(lane_base + gn * 16, cb);
+                    reduce_group(ca, g);
+                    g = gn;
+                    if (g >= job.n_groups) break;
+                    tc_wait_ld(cb);
+                    gn = g + WG;
+                    if (gn < job.n_groups) tc_ld16_nowait(lane_base + gn * 16, ca);
+                    reduce_group(cb, g);
+                    g = gn;
                 }
             }
         } else if (lane == 0) {

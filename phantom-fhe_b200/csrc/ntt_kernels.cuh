@@ -18,6 +18,7 @@
 //       index = ((T >> (u + 1)) * P) + k'
 // Lazy ranges: forward keeps [0,4q), inverse keeps [0,2q); the last pass stores canonical values.
 #pragma once
+#include <type_traits>
 #include "modarith.cuh"
 
 namespace b2 {
@@ -455,8 +456,12 @@ struct MacArgs {
     const uint64_t *own;                   // NTT-form input of ModUp, [l][N]
     const uint64_t *evk[B2_MAC_MAX_BETA];  // digit d: [2][size_QP][N]
     uint64_t *ct;                          // [2][l][N]
+    uint64_t *cxp;                         // [2][alpha][N]: the P limbs of the inner product
     const W2 *pinv;                        // per prime: P^-1 {w, shoup}
-    uint32_t l, lP, alpha, beta, size_QP, first_limb;
+    const W2 *fin;                         // per prime, for the integer path: P^-1 * 2^64 mod q (Q), 2^64 mod p (P)
+    uint32_t l, lP, alpha, beta, size_Q, size_QP, acc_p;
+    uint32_t interleave;                   // consecutive CTAs walk the limbs of one tile (else the tiles of one limb)
+    uint32_t p_first, first_limb;          // the grid covers p_first P limbs, then the Q limbs from first_limb on
 };
 
 __device__ __forceinline__ u64x4 ld256_cs(const uint64_t *p) {  // streaming: the key is read once
@@ -481,38 +486,82 @@ constexpr size_t mac_smem_bytes() {
     return (size_t)((1 << LOG_C) * ((1 << LOG_T) + ((1 << LOG_T) >> R)) + 2 * (1 << (LOG_C + LOG_T))) * 8;
 }
 
-template <int LOG_T, int R, int LOG_C>
-__global__ void __launch_bounds__((1 << (LOG_C + LOG_T)) >> R) ntt_fwd_rows_mac(NttArgs a, const __grid_constant__ MacArgs m) {
-    using A = ArithFp;
-    static_assert(2 * R == LOG_T, "equal stage groups: one register group per thread in both");
+// How the fused pass multiplies a finished digit residue into a key word and sums over the digits, per arithmetic.
+// FP64 primes: the signed products (below q in magnitude) are summed as doubles and reduced once.
+// Integer primes: a Montgomery product y * key * 2^-64 (four 64-bit multiplies, no correction step: the key word is
+// below q, so any 64-bit y gives a value below 2q) summed in one 64-bit word - 128-bit accumulators for sixteen residues
+// times two polynomials would not fit the register file, and a Barrett reduction per product costs twice the multiplies.
+// The factor 2^-64 is undone by the constant of the final multiplication (MacArgs::fin).
+template <class A> struct MacAcc;
+template <> struct MacAcc<ArithFp> {
+    using T = double;
+    using K = ArithFp::K;
+    struct C {};
+    __device__ __forceinline__ static C make(const Mod &) { return C{}; }
+    __device__ __forceinline__ static T zero() { return 0.0; }
+    __device__ __forceinline__ static double operand(double y, const K &k) { return ArithFp::reduce(y, k); }
+    __device__ __forceinline__ static void mac(T &acc, double y, uint64_t key, const K &k, const C &) {
+        const double w = ArithFp::from_u64(key, k);
+        acc = __dadd_rn(acc, ArithFp::mulmod(y, ArithFp::Tw{w, __dmul_rn(w, k.qinv)}, k));
+    }
+    // canonical residue of the sum
+    __device__ __forceinline__ static uint64_t finish(T acc, W2, const K &k, const C &) { return ArithFp::canon_fwd(acc, k); }
+};
+template <bool WIDE> struct MacAcc<ArithInt<WIDE>> {
+    using T = uint64_t;
+    using K = typename ArithInt<WIDE>::K;
+    struct C {
+        uint64_t q, q2, ninv;  // ninv = -q^-1 mod 2^64
+        bool tight;            // 2 * beta * q could pass 2^64: keep the sum below 2q after every term
+    };
+    __device__ __forceinline__ static C make(const Mod &md) {
+        uint64_t x = md.q;  // q * q = 1 mod 8; every Newton step doubles the valid bits
+#pragma unroll
+        for (int i = 0; i < 5; i++) x *= 2 - md.q * x;
+        return C{md.q, 2 * md.q, 0 - x, (md.q >> 59) != 0};
+    }
+    __device__ __forceinline__ static T zero() { return 0; }
+    __device__ __forceinline__ static uint64_t operand(uint64_t y, const K &) { return y; }  // lazy values (below 2^63) do
+    __device__ __forceinline__ static void mac(T &acc, uint64_t y, uint64_t key, const K &, const C &c) {
+        const uint64_t lo = y * key, hi = __umul64hi(y, key);
+        const uint64_t m = lo * c.ninv;
+        // (y key + m q) / 2^64: the low words cancel, carrying one unless lo is zero
+        acc += hi + __umul64hi(m, c.q) + (lo != 0);
+        if (c.tight) acc = csub(acc, c.q2);
+    }
+    // sum * 2^-64 times the limb's closing constant, canonical
+    __device__ __forceinline__ static uint64_t finish(T acc, W2 fin, const K &, const C &c) { return mul_shoup(acc, fin, c.q); }
+};
+
+// One tile of one output limb t (logical index: Q limbs 0 .. l-1, then the P limbs) through all digits.
+template <class A, int LOG_T, int R, int LOG_C>
+__device__ __forceinline__ void mac_body(const NttArgs &a, const MacArgs &m, uint64_t *sm, uint64_t *kb, uint32_t t, uint32_t pp, uint32_t tile,
+                                         const Mod &md) {
+    using T = typename A::T;
+    using Acc = MacAcc<A>;
     constexpr int TT = 1 << LOG_T, E = 1 << R, C = 1 << LOG_C;
     constexpr int TPAD = TT + (TT >> R), THREADS = (C * TT) >> R;
     static_assert(E == 16, "the key staging below gives every thread eight 16-byte chunks per polynomial");
-    extern __shared__ __align__(16) uint64_t mac_smem[];
-    uint64_t *sm = mac_smem;             // [C][TPAD] exchange buffer of the row pass
-    uint64_t *kb = mac_smem + C * TPAD;  // [2][C * TT] the tile of both key polynomials of the digit in hand
     const size_t N = (size_t)1 << a.logN;
-    const uint32_t tiles = (uint32_t)(N >> (LOG_T + LOG_C));
-    const uint32_t t = m.first_limb + blockIdx.x / tiles, tile = blockIdx.x % tiles;
-    const Mod md = a.mod[t];
-    const A::K k = A::make(md, (int)a.logN);
-    const W2 *tw = a.tw + (size_t)t * N;
+    const typename A::K k = A::make(md, (int)a.logN);
+    const W2 *tw = a.tw + (size_t)pp * N;
     const uint32_t n1 = (uint32_t)(N >> LOG_T);
     const int tid = threadIdx.x;
     const int c = tid / E, e = tid % E;  // sub-transform of the tile, register group within it (both stage groups)
     const uint32_t P = n1 + tile * C + c;
     const size_t base = (size_t)tile * C * TT;
     const size_t o = base + (size_t)c * TT + (size_t)e * E;  // this thread's E consecutive outputs: tid * 16 into the tile
-    const uint32_t own_d = t / m.alpha;
-    double acc0[E], acc1[E];
+    const uint32_t own_d = t < m.l ? t / m.alpha : 0xFFFFFFFFu;  // a P limb belongs to no digit
+    const typename Acc::C mc = Acc::make(md);
+    typename Acc::T acc0[E], acc1[E];
 #pragma unroll
-    for (int i = 0; i < E; i++) acc0[i] = acc1[i] = 0.0;
+    for (int i = 0; i < E; i++) acc0[i] = acc1[i] = Acc::zero();
     for (uint32_t d = 0; d < m.beta; d++) {
         // The digit's key tile starts its way from HBM now (cp.async, L1 bypassed: the key is read once) and is waited for
         // only after this digit's butterflies: a thread's eight 16-byte chunks of a polynomial are XOR-swizzled inside its
         // 128-byte row so that the 128-bit reads below are free of bank conflicts.
         {
-            const uint64_t *g0 = m.evk[d] + (size_t)t * N + base, *g1 = g0 + (size_t)m.size_QP * N;
+            const uint64_t *g0 = m.evk[d] + (size_t)pp * N + base, *g1 = g0 + (size_t)m.size_QP * N;
 #pragma unroll
             for (int g = tid; g < C * TT / 2; g += THREADS) {
                 const int owner = g >> 3, chunk = g & 7, off = owner * 16 + ((chunk ^ (owner & 7)) << 1);
@@ -521,7 +570,7 @@ __global__ void __launch_bounds__((1 << (LOG_C + LOG_T)) >> R) ntt_fwd_rows_mac(
             }
             cp_async_commit();
         }
-        double y[E];
+        T y[E];
         if (d == own_d) {
 #pragma unroll
             for (int i = 0; i < E; i += 4) {
@@ -540,7 +589,7 @@ __global__ void __launch_bounds__((1 << (LOG_C + LOG_T)) >> R) ntt_fwd_rows_mac(
             for (int i = 0; i < E; i++) y[i] = A::from_raw(sm[c * TPAD + pad_idx<LOG_T, R>(e * E + i)]);
             ct_stages<A, 0, R, E>(y, tw, P, R, e, k);
 #pragma unroll
-            for (int i = 0; i < E; i++) y[i] = A::reduce(y[i], k);
+            for (int i = 0; i < E; i++) y[i] = Acc::operand(y[i], k);
         }
         cp_async_wait<0>();
         __syncthreads();  // every thread's share of the key tile has landed
@@ -548,31 +597,75 @@ __global__ void __launch_bounds__((1 << (LOG_C + LOG_T)) >> R) ntt_fwd_rows_mac(
         for (int i = 0; i < E; i += 2) {
             const int off = tid * 16 + (((i >> 1) ^ (tid & 7)) << 1);
             const ulonglong2 u = *reinterpret_cast<const ulonglong2 *>(kb + off), v = *reinterpret_cast<const ulonglong2 *>(kb + C * TT + off);
-            const uint64_t ku[2] = {u.x, u.y}, kv[2] = {v.x, v.y};
-#pragma unroll
-            for (int j = 0; j < 2; j++) {
-                const double w0 = A::from_u64(ku[j], k), w1 = A::from_u64(kv[j], k);
-                acc0[i + j] = __dadd_rn(acc0[i + j], A::mulmod(y[i + j], A::Tw{w0, __dmul_rn(w0, k.qinv)}, k));
-                acc1[i + j] = __dadd_rn(acc1[i + j], A::mulmod(y[i + j], A::Tw{w1, __dmul_rn(w1, k.qinv)}, k));
-            }
+            Acc::mac(acc0[i], y[i], u.x, k, mc);
+            Acc::mac(acc0[i + 1], y[i + 1], u.y, k, mc);
+            Acc::mac(acc1[i], y[i], v.x, k, mc);
+            Acc::mac(acc1[i + 1], y[i + 1], v.y, k, mc);
         }
         __syncthreads();  // the key tile and the exchange buffer are free for the next digit
     }
-    const W2 pi = m.pinv[t];
     const uint64_t q = md.q;
-    uint64_t *c0 = m.ct + (size_t)t * N + o, *c1 = m.ct + ((size_t)m.l + t) * N + o;
+    if (t < m.l) {
+        // a Q limb: ct[k][t] += sum * P^-1. FP64 sums are canonical first and take P^-1; integer sums carry 2^-64 and
+        // take P^-1 * 2^64 in the same single multiplication.
+        constexpr bool FP = std::is_same<A, ArithFp>::value;
+        const W2 pi = FP ? m.pinv[pp] : m.fin[pp];
+        uint64_t *c0 = m.ct + (size_t)t * N + o, *c1 = m.ct + ((size_t)m.l + t) * N + o;
 #pragma unroll
-    for (int i = 0; i < E; i += 4) {
-        const u64x4 u = ld256(c0 + i), v = ld256(c1 + i);
-        uint64_t r[4], s[4];
+        for (int i = 0; i < E; i += 4) {
+            const u64x4 u = ld256(c0 + i), v = ld256(c1 + i);
+            uint64_t r[4], s[4];
 #pragma unroll
-        for (int j = 0; j < 4; j++) {
-            r[j] = mul_shoup(A::canon_fwd(acc0[i + j], k), pi, q);
-            s[j] = mul_shoup(A::canon_fwd(acc1[i + j], k), pi, q);
+            for (int j = 0; j < 4; j++) {
+                r[j] = Acc::finish(acc0[i + j], pi, k, mc);
+                s[j] = Acc::finish(acc1[i + j], pi, k, mc);
+                if (FP) r[j] = mul_shoup(r[j], pi, q), s[j] = mul_shoup(s[j], pi, q);
+            }
+            st256(c0 + i, add_mod(u.a, r[0], q), add_mod(u.b, r[1], q), add_mod(u.c, r[2], q), add_mod(u.d, r[3], q));
+            st256(c1 + i, add_mod(v.a, s[0], q), add_mod(v.b, s[1], q), add_mod(v.c, s[2], q), add_mod(v.d, s[3], q));
         }
-        st256(c0 + i, add_mod(u.a, r[0], q), add_mod(u.b, r[1], q), add_mod(u.c, r[2], q), add_mod(u.d, r[3], q));
-        st256(c1 + i, add_mod(v.a, s[0], q), add_mod(v.b, s[1], q), add_mod(v.c, s[2], q), add_mod(v.d, s[3], q));
+    } else {
+        // a P limb: kept (or, acc_p, added to what is there) in the compact buffer [2][alpha][N] for the ModDown that
+        // follows; the closing constant of an integer prime is 2^64 mod p
+        const W2 fin = m.fin[pp];
+        uint64_t *p0 = m.cxp + (size_t)(t - m.l) * N + o, *p1 = p0 + (size_t)m.alpha * N;
+#pragma unroll
+        for (int i = 0; i < E; i += 4) {
+            uint64_t r[4], s[4];
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                r[j] = Acc::finish(acc0[i + j], fin, k, mc);
+                s[j] = Acc::finish(acc1[i + j], fin, k, mc);
+            }
+            if (m.acc_p) {
+                const u64x4 u = ld256(p0 + i), v = ld256(p1 + i);
+                r[0] = add_mod(r[0], u.a, q), r[1] = add_mod(r[1], u.b, q), r[2] = add_mod(r[2], u.c, q), r[3] = add_mod(r[3], u.d, q);
+                s[0] = add_mod(s[0], v.a, q), s[1] = add_mod(s[1], v.b, q), s[2] = add_mod(s[2], v.c, q), s[3] = add_mod(s[3], v.d, q);
+            }
+            st256(p0 + i, r[0], r[1], r[2], r[3]);
+            st256(p1 + i, s[0], s[1], s[2], s[3]);
+        }
     }
+}
+
+template <int LOG_T, int R, int LOG_C>
+__global__ void __launch_bounds__((1 << (LOG_C + LOG_T)) >> R, 3) ntt_fwd_rows_mac(NttArgs a, const __grid_constant__ MacArgs m) {
+    static_assert(2 * R == LOG_T, "equal stage groups: one register group per thread in both");
+    constexpr int TT = 1 << LOG_T, C = 1 << LOG_C;
+    constexpr int TPAD = TT + (TT >> R);
+    extern __shared__ __align__(16) uint64_t mac_smem[];
+    uint64_t *sm = mac_smem;             // [C][TPAD] exchange buffer of the row pass
+    uint64_t *kb = mac_smem + C * TPAD;  // [2][C * TT] the tile of both key polynomials of the digit in hand
+    const uint32_t tiles = (uint32_t)(((size_t)1 << a.logN) >> (LOG_T + LOG_C));
+    // the P limbs (60-bit primes: the long CTAs) go first so that they do not form the tail of the grid
+    const uint32_t n_limbs = gridDim.x / tiles;
+    const uint32_t i = m.interleave ? blockIdx.x % n_limbs : blockIdx.x / tiles, tile = m.interleave ? blockIdx.x / n_limbs : blockIdx.x % tiles;
+    const uint32_t t = i < m.p_first ? m.l + i : m.first_limb + (i - m.p_first);
+    const uint32_t pp = t < m.l ? t : m.size_Q + (t - m.l);  // the limb's prime
+    const Mod md = a.mod[pp];
+    if (md.q < FP_LIMIT) mac_body<ArithFp, LOG_T, R, LOG_C>(a, m, sm, kb, t, pp, tile, md);
+    else if (md.q < WIDE_LIMIT) mac_body<ArithInt<true>, LOG_T, R, LOG_C>(a, m, sm, kb, t, pp, tile, md);
+    else mac_body<ArithInt<false>, LOG_T, R, LOG_C>(a, m, sm, kb, t, pp, tile, md);
 }
 
 // ================================================================================================

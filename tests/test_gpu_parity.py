@@ -456,12 +456,14 @@ def test_optional_transform_kernels(monkeypatch, env):
     assert hashes(ct, N) == case["hashes"]["keyswitch"]
 
 
-@pytest.mark.parametrize("fused", ["1", "0"])
+@pytest.mark.parametrize("fused", ["all", "fp64", "0"])
 @pytest.mark.parametrize("name", ["n16_l5_a8.json", "n16_l24_a8.json"])
 def test_inner_product_inside_the_last_forward_pass(monkeypatch, name, fused):
-    """At N = 2^16 ModUp's last forward pass multiplies the key in for the limbs on FP64 primes and never stores those
-    digits (B2_KS_FUSED_IP=0 switches back to the stand-alone inner product): both give the reference's limbs"""
-    monkeypatch.setenv("B2_KS_FUSED_IP", fused)
+    """At N = 2^16 ModUp's last forward pass multiplies the key in and never stores the digits: for every limb ("all"),
+    only for the limbs on FP64 primes (the default; the 60-bit limbs keep the stored pass and the stand-alone
+    inner product), or not at all (B2_KS_FUSED_IP=0). All three give the reference's limbs"""
+    monkeypatch.setenv("B2_KS_FUSED_IP", "0" if fused == "0" else "1")
+    monkeypatch.setenv("B2_KS_FUSED_WIDE", "1" if fused == "all" else "0")
     path = [p for p in GOLDEN if p.endswith(name)][0]
     case, ctx, o = load_case(path)
     N, l, seed, h = o.N, case["level"], case["seed"], ctx._h
@@ -472,6 +474,36 @@ def test_inner_product_inside_the_last_forward_pass(monkeypatch, name, fused):
     ws, nb = _ws(ctx, _native.OP_KEYSWITCH, l)
     check(LIB.b2_keyswitch(h, l, c2.data_ptr(), kp.ctypes.data, beta, ct.data_ptr(), ws.data_ptr(), nb, stream()))
     assert hashes(ct, N) == case["hashes"]["keyswitch"]
+
+
+@pytest.mark.parametrize("l", [7, 4])
+def test_fused_pass_on_every_prime_class(l, monkeypatch):
+    """N = 2^16 with Q and P limbs on primes of every arithmetic class (FP64 below 2^41, the lazy integer path below
+    2^46, Harvey butterflies above), a ragged last digit at l = 4: the key switch, and the sum of hoisted rotations
+    (whose second and later rotations add into the P limbs kept for the shared ModDown), against the oracle"""
+    N = 65536
+    monkeypatch.setenv("B2_KS_FUSED_WIDE", "1")
+    ctx, o = make_ctx(N, [60, 45, 38, 52, 43, 40, 30, 60, 44, 39], 3)
+    beta = o.beta(l)
+    key = o.synth_key(beta, 77, 10)
+    kt, kp = key_dev(key)
+    c2_h, ct_h = o.fill(1, o.primes[:l], 77, 3)[0], o.synth_ct(l, 77, 1)
+    c2, ct = dev(c2_h), dev(ct_h)
+    ws, nb = _ws(ctx, _native.OP_KEYSWITCH, l)
+    check(LIB.b2_keyswitch(ctx._h, l, c2.data_ptr(), kp.ctypes.data, beta, ct.data_ptr(), ws.data_ptr(), nb, stream()))
+    assert np.array_equal(host(ct), o.keyswitch(l, c2_h, key, ct_h))
+    elts = [ph.get_elt_from_step(s, N) for s in (1, 5)]
+    for e in elts:
+        check(LIB.b2_galois_prepare(ctx._h, e))
+    keys = [o.synth_key(beta, 77, 100 + 8 * e) for e in range(len(elts))]
+    kd = [key_dev(k) for k in keys]
+    ksk = np.concatenate([k[1] for k in kd])
+    e32 = np.array(elts, dtype=np.uint32)
+    summed = ctx.empty(2, l)
+    ws, nb = _ws(ctx, _native.OP_HOIST, l)
+    check(LIB.b2_hoisting_sum(ctx._h, l, ct.data_ptr(), e32.ctypes.data, len(elts), ksk.ctypes.data, beta, summed.data_ptr(),
+                              ws.data_ptr(), nb, stream()))
+    assert np.array_equal(host(summed), o.hoisting_sum(l, host(ct), elts, keys))
 
 
 @pytest.mark.parametrize("mode", ["tc:1", "tc:2", "tc:4", "tcs:1", "tcs:4", "fp", "int"])
