@@ -112,10 +112,35 @@ class ClockSampler:
                 "samples": len(sm), "window": "timed region" if inside else "whole run (timed region shorter than the sampling period)"}
 
 
+def bind_to_gpu_numa_node(torch, local_rank):
+    """Pinned host buffers are placed by first touch: running this rank's threads on the cores of the NUMA node its GPU
+    hangs off keeps the e2e arm's staging memory on that node, so that eight ranks do not all copy through one socket's
+    memory controller. Returns what was done, for the line; does nothing where the node is not exposed (-1)."""
+    try:
+        pr = torch.cuda.get_device_properties(local_rank)
+        bus = "%04x:%02x:%02x.0" % (pr.pci_domain_id, pr.pci_bus_id, pr.pci_device_id)
+        node = int(open(f"/sys/bus/pci/devices/{bus}/numa_node").read())
+        if node < 0:
+            return {"node": None, "why": "the GPU's NUMA node is not exposed"}
+        cpus = set()
+        for part in open(f"/sys/devices/system/node/node{node}/cpulist").read().strip().split(","):
+            a, _, b = part.partition("-")
+            cpus.update(range(int(a), int(b or a) + 1))
+        cpus &= os.sched_getaffinity(0)
+        if not cpus:
+            return {"node": node, "why": "none of the node's cores is in this process's affinity mask"}
+        os.sched_setaffinity(0, cpus)
+        return {"node": node, "cores": len(cpus)}
+    except (OSError, ValueError, AttributeError) as e:
+        return {"node": None, "why": str(e)[:120]}
+
+
 def config_dict(args, world):
     """what both arms report as `config`: the workload and how a step is made of it"""
     S = max(1, min(args.streams, args.batch))
     return {"workload": WORKLOAD, "batch_per_step_per_gpu": args.batch, "distinct_keys": args.keys, "streams": S,
+            "launch": ("b2_keyswitch_batch: one call per key over its %d ciphertexts" % (-(-args.batch // args.keys))) if args.launch == "batched"
+            else "b2_keyswitch: one call per ciphertext",
             "l2": "inputs larger than L2 (a step touches %.1f GB)" % (args.batch * 3 * LEVEL * LIMB_BYTES / 1e9 + args.keys * 0.1),
             "parallelism": f"dp{world}"}
 
@@ -495,6 +520,8 @@ def main():
     ap.add_argument("--batch", type=int, default=64, help="key switches per step per GPU")
     ap.add_argument("--keys", type=int, default=4, help="distinct evaluation keys cycled over")
     ap.add_argument("--streams", type=int, default=4, help="CUDA streams the batch of independent key switches is spread over")
+    ap.add_argument("--launch", default="batched", choices=["batched", "single"],
+                    help="batched: the ciphertexts of one key go through b2_keyswitch_batch in one call; single: one b2_keyswitch call each")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer arm (used for ncu captures)")
     ap.add_argument("--e2e-streams", type=int, default=4, help="streams of the host-buffer arm (copy in, key switch, copy out per stream)")
@@ -543,22 +570,56 @@ def main():
     # take half a minute); the e2e arm copies them out to pinned host buffers once, before its timed region
     gen = torch.Generator(device="cuda")
     gen.manual_seed(seed)
-    dev_ct3 = [torch.stack([torch.randint(0, int(q), (3, N), dtype=torch.int64, device="cuda", generator=gen) for q in primes[:LEVEL]], dim=1)
-               for _ in range(B)]
+    # Ciphertext b is switched with key b % K: the ciphertexts of one key sit in one tensor [B / K][3][limbs][N], so that the
+    # batched entry point can take them in one call.
+    per_key = [len(range(k, B, K)) for k in range(K)]
+    dev_groups = [torch.stack([torch.randint(0, int(q), (n, 3, N), dtype=torch.int64, device="cuda", generator=gen) for q in primes[:LEVEL]], dim=2)
+                  if n else None for n in per_key]
+    dev_ct3 = [dev_groups[b % K][b // K] for b in range(B)]
     n_host = 0 if args.no_e2e else B
+    affinity = os.sched_getaffinity(0)
+    numa = None if args.no_e2e else bind_to_gpu_numa_node(torch, local_rank)
     host_ct3 = [torch.empty(3, LEVEL, N, dtype=torch.int64).pin_memory() for _ in range(n_host)]
     for h, d in zip(host_ct3, dev_ct3):
         h.copy_(d)
     host_out = [torch.empty(2, LEVEL, N, dtype=torch.int64).pin_memory() for _ in range(n_host)]
+    for h in host_out:
+        h.zero_()  # first touch while still bound to the GPU's node
+    os.sched_setaffinity(0, affinity)
     S = max(1, min(args.streams, B))
     wss = [ctx.workspace(_native.OP_KEYSWITCH, LEVEL) for _ in range(S)]
+    batched = args.launch == "batched"
+    if batched:
+        wsb = [ph.keyswitch_batch_workspace(ctx, LEVEL, max(per_key)) for _ in range(min(S, K))]
     stream = torch.cuda.current_stream()
     side = [torch.cuda.Stream() for _ in range(S)] if S > 1 else [stream]
     fork, joins = torch.cuda.Event(), [torch.cuda.Event() for _ in range(S)]
 
+    def step_batched():
+        # the ciphertexts that share a key go through b2_keyswitch_batch in one call (every kernel one launch over them);
+        # the keys' groups are spread over the streams
+        L = len(wsb)
+        if L > 1:
+            fork.record(stream)
+        for i in range(L):
+            st = side[i] if L > 1 else stream
+            if L > 1:
+                st.wait_event(fork)
+            for k in range(i, K, L):
+                g = dev_groups[k]
+                if g is None:
+                    continue
+                check(LIB.b2_keyswitch_batch(ctx._h, LEVEL, g.shape[0], g[0, 2].data_ptr(), 3 * LEVEL, key_tabs[k].ctypes.data, BETA,
+                                             g.data_ptr(), 3 * LEVEL, wsb[i].data_ptr(), wsb[i].numel() * 8, st.cuda_stream))
+            if L > 1:
+                joins[i].record(st)
+                stream.wait_event(joins[i])
+
     def step_resident():
         # the batch's key switches are independent: spread them over S streams (each with its own
         # scratch) so that one ciphertext's memory phases overlap another's arithmetic
+        if batched:
+            return step_batched()
         if S > 1:
             fork.record(stream)
         for i, st in enumerate(side):
@@ -780,7 +841,14 @@ def main():
         prof_steps = 2
         ws0, ws0_bytes = wss[0]
         PB = min(B, 8)
-        for _ in range(prof_steps):
+        if batched:
+            # the timed region's own call, on one stream: one key's ciphertexts per launch
+            g = dev_groups[0]
+            PB = int(g.shape[0])
+            for _ in range(prof_steps):
+                check(LIB.b2_keyswitch_batch(ctx._h, LEVEL, PB, g[0, 2].data_ptr(), 3 * LEVEL, key_tabs[0].ctypes.data, BETA, g.data_ptr(),
+                                             3 * LEVEL, wsb[0].data_ptr(), wsb[0].numel() * 8, stream.cuda_stream))
+        for _ in range(0 if batched else prof_steps):
             for b in range(PB):
                 t = dev_ct3[b]
                 check(LIB.b2_keyswitch(ctx._h, LEVEL, t[2].data_ptr(), key_tabs[b % K].ctypes.data, BETA, t.data_ptr(),
@@ -837,7 +905,9 @@ def main():
         reference_gpu = reference_gpu_section()
         ntt = ntt_section(ph, ctx, torch, LIB, check, N, len(primes))
         compositions = compositions_section(ph, ctx, torch, np, synth, primes, keys, N, LEVEL)
-        del dev_ct3, keys, stage
+        del dev_ct3, dev_groups, keys, stage
+        if batched:
+            del wsb
         torch.cuda.empty_cache()
         bsgs = bsgs_section(ph, torch, np, synth)
         torch.cuda.empty_cache()
@@ -851,7 +921,7 @@ def main():
             "config": config_dict(args, world),
             "clocks": clocks,
             "e2e": {"value": e2e_value, "unit": "KeySwitch/s", "h2d_bytes_per_step": B * 3 * LEVEL * LIMB_BYTES,
-                    "d2h_bytes_per_step": B * 2 * LEVEL * LIMB_BYTES, "api": "pyPhantom.relinearize", "steps": e2e_steps, "streams": len(streams), "pcie": pcie},
+                    "d2h_bytes_per_step": B * 2 * LEVEL * LIMB_BYTES, "api": "pyPhantom.relinearize", "steps": e2e_steps, "streams": len(streams), "pcie": pcie, "numa": numa},
             "gpu_launches": launches,
             "device_status": ctx.device_status(),
             "roofline": roofline,

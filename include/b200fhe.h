@@ -95,6 +95,16 @@ int b2_moddown(b2_ctx *ctx, size_t size_Ql, size_t n_poly, uint64_t *d_cx, uint6
 int b2_keyswitch(b2_ctx *ctx, size_t size_Ql, const uint64_t *d_c2, const uint64_t *const *evk,
                  size_t n_evk, uint64_t *d_ct, void *d_ws, size_t ws_bytes, void *stream);
 
+/* keyswitch_inplace (src/eval_key_switch.cu:294-381) for `batch` ciphertexts switched with ONE key (a batch of
+ * relinearisations, or of rotations by one step): set b reads d_c2 + b * c2_stride limbs and updates
+ * d_ct + b * ct_stride limbs ([2][size_Ql][N] each); strides in limbs of N words. Every kernel is one launch over the
+ * batch where the fused pipeline applies (N = 2^16), else the key switches run one after another. Same limbs as
+ * `batch` calls of b2_keyswitch. d_ws: b2_keyswitch_batch_workspace_bytes(). */
+size_t b2_keyswitch_batch_workspace_bytes(const b2_ctx *ctx, size_t size_Ql, size_t batch);
+int b2_keyswitch_batch(b2_ctx *ctx, size_t size_Ql, size_t batch, const uint64_t *d_c2, size_t c2_stride,
+                       const uint64_t *const *evk, size_t n_evk, uint64_t *d_ct, size_t ct_stride,
+                       void *d_ws, size_t ws_bytes, void *stream);
+
 /* replaces bgv_ckks_multiply's tensor product (src/evaluate.cu:345-397, src/polymath.cu:463-540):
  * d_a, d_b [2][size_Ql][N] -> d_out [3][size_Ql][N] */
 int b2_tensor_mul(b2_ctx *ctx, size_t size_Ql, const uint64_t *d_a, const uint64_t *d_b,

@@ -821,6 +821,9 @@ static uint32_t pipe_grid(const b2_ctx *c, uint32_t total) {
     return (total + per_cta - 1) / per_cta;
 }
 
+// grid of a two-pass transform kernel over `work` tiles and `batch` sets
+static dim3 pass_grid(NttArgs &, uint32_t work, uint32_t batch) { return dim3(work, batch); }
+
 template <int LOG_A, int LOG_B, class Epi, int SRC = 0>
 static void launch_fwd(const b2_ctx *c, const NttArgs &a, uint32_t njobs, const Epi &epi, cudaStream_t s, uint32_t batch = 1) {
     using A = PassCfg<LOG_A>;
@@ -842,16 +845,17 @@ static void launch_fwd(const b2_ctx *c, const NttArgs &a, uint32_t njobs, const 
         }
     }
     {
+        NttArgs a1 = a;
+        const dim3 grid = pass_grid(a1, njobs * (N >> (LOG_A + A::LOG_CC)), batch);
         LaunchScope ls(c, s, "ntt_fwd_cols");
-        ntt_fwd_pass<LOG_A, A::R_STRIDED, A::R_CONTIG, A::LOG_CC, true, false, EpiStore, SRC>
-            <<<dim3(njobs * (N >> (LOG_A + A::LOG_CC)), batch), pass_threads<LOG_A, true>(), 0, s>>>(a, EpiStore{});
+        ntt_fwd_pass<LOG_A, A::R_STRIDED, A::R_CONTIG, A::LOG_CC, true, false, EpiStore, SRC><<<grid, pass_threads<LOG_A, true>(), 0, s>>>(a1, EpiStore{});
     }
     NttArgs b = a;
     b.src = a.dst;  // second pass works in place on the first pass's output
     b.src_lm1 = a.dst_lm1, b.src_bs = a.dst_bs;
+    const dim3 grid = pass_grid(b, njobs * (N >> (LOG_B + B::LOG_C)), batch);
     LaunchScope ls(c, s, "ntt_fwd_rows");
-    ntt_fwd_pass<LOG_B, B::R_STRIDED, B::R_CONTIG, B::LOG_C, false, true, Epi>
-        <<<dim3(njobs * (N >> (LOG_B + B::LOG_C)), batch), pass_threads<LOG_B>(), 0, s>>>(b, epi);
+    ntt_fwd_pass<LOG_B, B::R_STRIDED, B::R_CONTIG, B::LOG_C, false, true, Epi><<<grid, pass_threads<LOG_B>(), 0, s>>>(b, epi);
 }
 
 template <int LOG_A, int LOG_B>
@@ -874,16 +878,17 @@ static void launch_inv(const b2_ctx *c, const NttArgs &a, uint32_t njobs, cudaSt
         }
     }
     {
+        NttArgs a1 = a;
+        const dim3 grid = pass_grid(a1, njobs * (N >> (LOG_B + B::LOG_C)), batch);
         LaunchScope ls(c, s, "ntt_inv_rows");
-        ntt_inv_pass<LOG_B, B::R_CONTIG, B::R_STRIDED, B::LOG_C, false, false>
-            <<<dim3(njobs * (N >> (LOG_B + B::LOG_C)), batch), pass_threads<LOG_B>(), 0, s>>>(a);
+        ntt_inv_pass<LOG_B, B::R_CONTIG, B::R_STRIDED, B::LOG_C, false, false><<<grid, pass_threads<LOG_B>(), 0, s>>>(a1);
     }
     NttArgs b = a;
     b.src = a.dst;
     b.src_lm1 = a.dst_lm1, b.src_bs = a.dst_bs;
+    const dim3 grid = pass_grid(b, njobs * (N >> (LOG_A + A::LOG_CC)), batch);
     LaunchScope ls(c, s, "ntt_inv_cols");
-    ntt_inv_pass<LOG_A, A::R_CONTIG, A::R_STRIDED, A::LOG_CC, true, true>
-        <<<dim3(njobs * (N >> (LOG_A + A::LOG_CC)), batch), pass_threads<LOG_A, true>(), 0, s>>>(b);
+    ntt_inv_pass<LOG_A, A::R_CONTIG, A::R_STRIDED, A::LOG_CC, true, true><<<grid, pass_threads<LOG_A, true>(), 0, s>>>(b);
 }
 
 // SRC != 0: the column pass makes limb job.x from slot job.x / src_div of src (words mod src_q) instead of reading it
@@ -1140,6 +1145,7 @@ struct EvkPtrs {
 // (i * p_mul_i + k * p_mul_k) * (p_lm1 + 1) + b * p_bs of the P-limb buffer. One set: {0, 0, 0, 1, alpha, 0, 0}.
 struct IpBatch {
     uint32_t dig_bs, own_bs, ct_bs, p_mul_i, p_mul_k, p_lm1, p_bs;
+    uint32_t batch_x;  // the grid is (sets, blocks of pairs) instead of (blocks of pairs, sets); measured 13 % slower on B200, so left at 0
 };
 
 // Key-switch inner product (src/eval_key_switch.cu:175-230): for logical limb t (physical prime pp)
@@ -1160,10 +1166,11 @@ __global__ void __launch_bounds__(256) ks_inner_prod_kernel(const uint64_t *__re
                                                            uint32_t beta, uint4 own_range, const IpBatch ib) {
     // own_range = (first Q limb, number of Q limbs, first P limb, number of P limbs) this launch
     // covers: everything on one GPU, the rank's slice under RNS-limb sharding
-    digits += (size_t)blockIdx.y * ib.dig_bs * N;
-    if (own) own += (size_t)blockIdx.y * ib.own_bs * N;
-    if (FUSED) ct += (size_t)blockIdx.y * ib.ct_bs * N;
-    const size_t jdx = 2 * ((size_t)blockIdx.x * blockDim.x + threadIdx.x);
+    const uint32_t bset = ib.batch_x ? blockIdx.x : blockIdx.y, blk = ib.batch_x ? blockIdx.y : blockIdx.x;
+    digits += (size_t)bset * ib.dig_bs * N;
+    if (own) own += (size_t)bset * ib.own_bs * N;
+    if (FUSED) ct += (size_t)bset * ib.ct_bs * N;
+    const size_t jdx = 2 * ((size_t)blk * blockDim.x + threadIdx.x);
     if (jdx >= (size_t)(own_range.y + own_range.w) * N) return;
     const uint32_t jl = (uint32_t)(jdx / N), n = (uint32_t)(jdx % N);
     const uint32_t t = jl < own_range.y ? own_range.x + jl : l + own_range.z + (jl - own_range.y);
@@ -1220,7 +1227,7 @@ __global__ void __launch_bounds__(256) ks_inner_prod_kernel(const uint64_t *__re
             *reinterpret_cast<ulonglong2 *>(c0) = make_ulonglong2(add_mod(u0.x, r[0], md.q), add_mod(u0.y, r[1], md.q));
             *reinterpret_cast<ulonglong2 *>(c1) = make_ulonglong2(add_mod(u1.x, r[2], md.q), add_mod(u1.y, r[3], md.q));
         } else {
-            const size_t o = ((size_t)(t - l) * ib.p_mul_i * (ib.p_lm1 + 1) + (size_t)blockIdx.y * ib.p_bs) * N + n;
+            const size_t o = ((size_t)(t - l) * ib.p_mul_i * (ib.p_lm1 + 1) + (size_t)bset * ib.p_bs) * N + n;
             const size_t o1 = o + (size_t)ib.p_mul_k * (ib.p_lm1 + 1) * N;
             if (ACCP) {
                 const ulonglong2 p0 = *reinterpret_cast<const ulonglong2 *>(out + o), p1 = *reinterpret_cast<const ulonglong2 *>(out + o1);
@@ -1268,7 +1275,7 @@ __global__ void __launch_bounds__(256) ks_inner_prod_kernel(const uint64_t *__re
         *reinterpret_cast<ulonglong2 *>(c1) =
             make_ulonglong2(add_mod(u1.x, mul_shoup(r10, pi, md.q), md.q), add_mod(u1.y, mul_shoup(r11, pi, md.q), md.q));
     } else {
-        const size_t o = ((size_t)(t - l) * ib.p_mul_i * (ib.p_lm1 + 1) + (size_t)blockIdx.y * ib.p_bs) * N + n;
+        const size_t o = ((size_t)(t - l) * ib.p_mul_i * (ib.p_lm1 + 1) + (size_t)bset * ib.p_bs) * N + n;
         const size_t o1 = o + (size_t)ib.p_mul_k * (ib.p_lm1 + 1) * N;
         if (ACCP) {
             const ulonglong2 p0 = *reinterpret_cast<const ulonglong2 *>(out + o), p1 = *reinterpret_cast<const ulonglong2 *>(out + o1);
@@ -1660,8 +1667,10 @@ static int inner_prod_impl(b2_ctx *c, size_t l, const uint64_t *digits, const ui
     const size_t pairs = (size_t)(rg.y + rg.w) * c->N / 2;
     if (pairs == 0) return B2_OK;
     if (batch != 1 && (!fused || !ipb)) return fail(B2_EINVAL, "a batched inner product runs in the fused form");
-    const dim3 grid((unsigned)((pairs + 255) / 256), batch);
-    const IpBatch ib = ipb ? *ipb : IpBatch{0, 0, 0, 1, (uint32_t)c->size_P, 0, 0};
+    const unsigned blocks = (unsigned)((pairs + 255) / 256);
+    IpBatch ib = ipb ? *ipb : IpBatch{0, 0, 0, 1, (uint32_t)c->size_P, 0, 0, 0};
+    ib.batch_x = 0;
+    const dim3 grid = ib.batch_x ? dim3(batch, blocks) : dim3(blocks, batch);
     LaunchScope ls(c, s, "ks_inner_prod");
     if (fused && acc_p)
         ks_inner_prod_kernel<3, true, true><<<grid, 256, 0, s>>>(digits, own, ep, out, ct, c->d_Pinv, c->d_mod, c->d_redc, (uint32_t)c->N, (uint32_t)l,
@@ -1732,8 +1741,14 @@ static int ks_tail_fused(b2_ctx *c, size_t l, const uint64_t *digits, const uint
 // ModUp and inner product of the fused key switch with the FP64 limbs' inner product inside the last forward pass.
 // Applies at N = 2^16 when the level's Q limbs are FP64 primes behind a prefix of wide ones; *done tells whether it ran.
 // ct [2][l][N] += (inner product) * P^-1 on the Q limbs; cxP [2][alpha][N] = (acc_p: +=) the P limbs of the inner product.
+// A batch of key switches with one key, every kernel one launch over the batch: set b's input, ciphertext, and its scratch
+// blocks t [l], up [beta][l+alpha], cxP [2][alpha] start b * c2_bs / ct_bs / l / beta (l+alpha) / 2 alpha limbs further.
+struct KsBatch {
+    uint32_t batch = 1, c2_bs = 0, ct_bs = 0;
+};
+
 static int modup_inner_fused(b2_ctx *c, size_t l, const uint64_t *c2, const uint64_t *const *evk, size_t n_evk, uint64_t *ct, uint64_t *cxP,
-                             uint64_t *t, uint64_t *up, bool acc_p, cudaStream_t s, bool *done) {
+                             uint64_t *t, uint64_t *up, bool acc_p, cudaStream_t s, bool *done, const KsBatch &kb = KsBatch{}) {
     const size_t N = c->N, lP = l + c->size_P, beta = c->plan[l].beta;
     const LevelPlan &pl = c->plan[l];
     *done = false;
@@ -1742,15 +1757,25 @@ static int modup_inner_fused(b2_ctx *c, size_t l, const uint64_t *c2, const uint
         // ModUp up to the column pass for every limb; the row pass is stored only for the limbs the stand-alone inner
         // product still handles (wide Q primes and P); for the FP64 limbs of Q it runs inside ntt_fwd_rows_mac
         using Cfg = PassCfg<8>;
-        int rc = run_inv(c, c2, t, pl.jobs_up_intt, (uint32_t)l, 0, pl.fin_up, s);
+        const uint32_t B = kb.batch, per = (uint32_t)(beta * lP), a2 = (uint32_t)(2 * c->size_P);
+        const bool batched = B != 1;
+        if (batched && (!c->bconv_tc || c->tc_simple || !pl.tc_up.jobs || !pl.tc_dnf.jobs)) return B2_OK;  // the caller falls back to one key switch at a time
+        int rc = run_inv(c, c2, t, pl.jobs_up_intt, (uint32_t)l, 0, pl.fin_up, s, BatchDims{B, 0, kb.c2_bs, 0, (uint32_t)l});
         if (rc) return rc;
-        rc = run_bconv(c, false, t, up, c2, pl.grp_up, pl.beta, pl.outs_up, pl.mat_up, pl.matd_up, (uint32_t)c->size_P, (uint32_t)lP, true, s, &pl.tc_up);
+        if (batched) {
+            const TcBatch tb{B, 0, (uint32_t)l, 0, per, c->tc_serial_ld ? 1u : 0u};
+            rc = run_bconv_tc(c, false, t, up, nullptr, pl.tc_up, pl.tc_up.n_jobs, s, &tb);
+        } else {
+            rc = run_bconv(c, false, t, up, c2, pl.grp_up, pl.beta, pl.outs_up, pl.mat_up, pl.matd_up, (uint32_t)c->size_P, (uint32_t)lP, true, s, &pl.tc_up);
+        }
         if (rc) return rc;
         NttArgs a{up, up, pl.jobs_up_ntt, 0, (uint32_t)c->logN, c->d_tw, c->d_mod, nullptr, 0};
+        a.src_bs = a.dst_bs = batched ? per : 0;
         {
+            NttArgs a1 = a;
+            const dim3 grid = pass_grid(a1, pl.n_up_ntt * (uint32_t)(N >> (8 + Cfg::LOG_CC)), B);
             LaunchScope ls(c, s, "ntt_fwd_cols");
-            ntt_fwd_pass<8, Cfg::R_STRIDED, Cfg::R_CONTIG, Cfg::LOG_CC, true, false, EpiStore>
-                <<<pl.n_up_ntt * (uint32_t)(N >> (8 + Cfg::LOG_CC)), pass_threads<8, true>(), 0, s>>>(a, EpiStore{});
+            ntt_fwd_pass<8, Cfg::R_STRIDED, Cfg::R_CONTIG, Cfg::LOG_CC, true, false, EpiStore><<<grid, pass_threads<8, true>(), 0, s>>>(a1, EpiStore{});
             LAUNCH_CHECK("ntt_fwd_pass");
         }
         // the limbs on 60-bit primes (q0, P) either ride on the fused pass too (integer arithmetic) or, mac_wide off,
@@ -1759,14 +1784,15 @@ static int modup_inner_fused(b2_ctx *c, size_t l, const uint64_t *c2, const uint
         if (!wide && pl.n_up_rows) {
             NttArgs b = a;
             b.jobs = pl.jobs_up_rows;
+            const dim3 grid = pass_grid(b, pl.n_up_rows * (uint32_t)(N >> (8 + Cfg::LOG_C)), B);
             LaunchScope ls(c, s, "ntt_fwd_rows");
-            ntt_fwd_pass<8, Cfg::R_STRIDED, Cfg::R_CONTIG, Cfg::LOG_C, false, true, EpiStore>
-                <<<pl.n_up_rows * (uint32_t)(N >> (8 + Cfg::LOG_C)), pass_threads<8>(), 0, s>>>(b, EpiStore{});
+            ntt_fwd_pass<8, Cfg::R_STRIDED, Cfg::R_CONTIG, Cfg::LOG_C, false, true, EpiStore><<<grid, pass_threads<8>(), 0, s>>>(b, EpiStore{});
             LAUNCH_CHECK("ntt_fwd_pass");
         }
         if (!wide) {
             const uint4 rest = make_uint4(0, pl.n_wideQ, 0, (uint32_t)c->size_P);
-            rc = inner_prod_impl(c, l, up, c2, evk, n_evk, cxP, ct, true, s, &rest, acc_p);
+            const IpBatch ib{per, kb.c2_bs, kb.ct_bs, 1, (uint32_t)c->size_P, 0, a2};
+            rc = inner_prod_impl(c, l, up, c2, evk, n_evk, cxP, ct, true, s, &rest, acc_p, B, batched ? &ib : nullptr);
             if (rc) return rc;
         }
         {
@@ -1781,12 +1807,13 @@ static int modup_inner_fused(b2_ctx *c, size_t l, const uint64_t *c2, const uint
             m.size_Q = (uint32_t)c->size_Q, m.size_QP = (uint32_t)c->size_QP;
             m.first_limb = wide ? 0 : pl.n_wideQ, m.p_first = wide ? (uint32_t)c->size_P : 0, m.acc_p = acc_p ? 1 : 0;
             m.interleave = c->mac_interleave ? 1 : 0;
+            m.dig_bs = per, m.own_bs = kb.c2_bs, m.ct_bs = kb.ct_bs, m.cxp_bs = a2;
             const uint32_t n_limbs = (uint32_t)l - m.first_limb + m.p_first;
             LaunchScope ls(c, s, "ntt_fwd_rows_mac");
             static_assert(Cfg::R_STRIDED == Cfg::R_CONTIG, "the fused pass wants equal stage groups");
             static_assert(Cfg::R_CONTIG == 4 && Cfg::LOG_C == 3, "b2_ctx_create raises the shared-memory limit of this instantiation");
             ntt_fwd_rows_mac<8, Cfg::R_CONTIG, Cfg::LOG_C>
-                <<<n_limbs * (uint32_t)(N >> (8 + Cfg::LOG_C)), pass_threads<8>(), mac_smem_bytes<8, Cfg::R_CONTIG, Cfg::LOG_C>(), s>>>(a, m);
+                <<<dim3(B, n_limbs * (uint32_t)(N >> (8 + Cfg::LOG_C))), pass_threads<8>(), mac_smem_bytes<8, Cfg::R_CONTIG, Cfg::LOG_C>(), s>>>(a, m);
             LAUNCH_CHECK("ntt_fwd_rows_mac");
         }
     }
@@ -1823,6 +1850,55 @@ extern "C" int b2_keyswitch(b2_ctx *c, size_t l, const uint64_t *d_c2, const uin
     if (!d_c2 || !evk || !d_ct || !d_ws) return fail(B2_EINVAL, "keyswitch: null pointer");
     if (ws_bytes < b2_workspace_bytes(c, B2_OP_KEYSWITCH, l)) return fail(B2_EWS, "keyswitch: workspace too small");
     return keyswitch_impl(c, l, d_c2, evk, n_evk, d_ct, (uint64_t *)d_ws, (cudaStream_t)stream);
+}
+
+extern "C" size_t b2_keyswitch_batch_workspace_bytes(const b2_ctx *c, size_t l, size_t batch) {
+    if (!c || l < 1 || l > c->size_Q || batch < 1) return 0;
+    const size_t a = c->size_P, beta = (l + a - 1) / a, lP = l + a;
+    return batch * (l + 2 * a + beta * lP) * limb_bytes(c);
+}
+
+// `batch` key switches with ONE key: ct_b [2][l][N] += ModDown(<ModUp(c2_b), key>), set b's input at d_c2 + b * c2_stride
+// limbs and its ciphertext at d_ct + b * ct_stride limbs. Where the fused pipeline applies (N = 2^16, tensor-core base
+// conversion) every kernel is one launch over the whole batch - 10 to 12 launches for the batch instead of per key
+// switch, grids that fill the GPU at every level, and the key read from HBM once per batch: the fused inner product
+// puts the sets that share a key tile next to one another in the grid, so all but the first find it in L2. Elsewhere the
+// key switches run one after another on the same stream. Workspace: t [batch][l] | up [batch][beta][l+alpha] | cxP [batch][2][alpha].
+extern "C" int b2_keyswitch_batch(b2_ctx *c, size_t l, size_t batch, const uint64_t *d_c2, size_t c2_stride, const uint64_t *const *evk, size_t n_evk,
+                                  uint64_t *d_ct, size_t ct_stride, void *d_ws, size_t ws_bytes, void *stream) {
+    CHECK_CTX(c);
+    CHECK_LEVEL(c, l);
+    if (!d_c2 || !evk || !d_ct || !d_ws || batch < 1 || batch > 65535) return fail(B2_EINVAL, "keyswitch_batch: bad argument");
+    if (c2_stride < l || ct_stride < 2 * l || c2_stride > 0xFFFFFFFFull || ct_stride > 0xFFFFFFFFull)
+        return fail(B2_EINVAL, "keyswitch_batch: a set's stride is smaller than the set");
+    if (ws_bytes < b2_keyswitch_batch_workspace_bytes(c, l, batch)) return fail(B2_EWS, "keyswitch_batch: workspace too small");
+    cudaStream_t s = (cudaStream_t)stream;
+    const LevelPlan &pl = c->plan[l];
+    const size_t N = c->N, a = c->size_P, lP = l + a, beta = pl.beta;
+    const uint32_t B = (uint32_t)batch, per = (uint32_t)(beta * lP);
+    uint64_t *t = (uint64_t *)d_ws, *up = t + batch * l * N, *cxP = up + batch * per * N;
+    bool done = false;
+    int rc = B2_OK;
+    if (batch > 1) {
+        rc = modup_inner_fused(c, l, d_c2, evk, n_evk, d_ct, cxP, t, up, false, s, &done, KsBatch{B, (uint32_t)c2_stride, (uint32_t)ct_stride});
+        if (rc) return rc;
+    }
+    if (!done) {
+        // one at a time, each in its own block of the workspace
+        const size_t one = l + beta * lP + 2 * a;
+        for (size_t b = 0; b < batch; b++) {
+            rc = keyswitch_impl(c, l, d_c2 + b * c2_stride * N, evk, n_evk, d_ct + b * ct_stride * N, (uint64_t *)d_ws + b * one * N, s);
+            if (rc) return rc;
+        }
+        return B2_OK;
+    }
+    // ModDown of the P limbs of both polynomials of every set; delta takes the front of each set's `up` block
+    rc = run_inv(c, cxP, cxP, pl.jobs_dnf_intt, (uint32_t)(2 * a), 0, c->d_fin_P, s, BatchDims{B, 0, (uint32_t)(2 * a), 0, (uint32_t)(2 * a)});
+    if (rc) return rc;
+    const TcBatch tb{B, 0, (uint32_t)(2 * a), 0, per, 0};
+    rc = run_bconv_tc(c, false, cxP, up, nullptr, pl.tc_dnf, pl.tc_dnf.n_jobs, s, &tb);
+    if (rc) return rc;
+    return run_fwd(c, up, up, pl.jobs_dnf_ntt, (uint32_t)(2 * l), 0, EpiSubFrom{d_ct, (uint32_t)ct_stride}, s, 0, 0, 0, BatchDims{B, 0, per, 0, per});
 }
 
 extern "C" int b2_tensor_mul(b2_ctx *c, size_t l, const uint64_t *d_a, const uint64_t *d_b, uint64_t *d_out, void *stream) {

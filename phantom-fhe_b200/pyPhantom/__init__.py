@@ -569,6 +569,28 @@ def relinearize(ctx, ct, rlk):
     return ct._like(out)
 
 
+def relinearize_batch(ctx, data, rlk, ws=None):
+    """relinearize (src/evaluate.cu:1342-1374) for a batch of three-polynomial ciphertexts held in one tensor
+    data [batch][3][limbs][N], all with the one relinearisation key: data[:, :2] += KeySwitch(data[:, 2]) in place, every
+    kernel one launch over the batch (b2_keyswitch_batch). Returns the view data[:, :2]; `ws` (from
+    `keyswitch_batch_workspace`) may be passed to keep the call allocation-free."""
+    if data.dim() != 4 or data.shape[1] != 3 or not data.is_contiguous():
+        raise ValueError("data must be a contiguous [batch][3][limbs][N] tensor")
+    batch, l = int(data.shape[0]), int(data.shape[2])
+    if ws is None:
+        ws = keyswitch_batch_workspace(ctx, l, batch)
+    tab = _key_table(ctx, rlk, l)
+    check(LIB.b2_keyswitch_batch(ctx._h, l, batch, data[0, 2].data_ptr(), 3 * l, tab.ctypes.data, len(tab), data.data_ptr(), 3 * l,
+                                 ws.data_ptr(), ws.numel() * 8, _stream()))
+    return data[:, :2]
+
+
+def keyswitch_batch_workspace(ctx, l, batch):
+    """scratch tensor for `relinearize_batch` / b2_keyswitch_batch at `l` limbs"""
+    nbytes = int(LIB.b2_keyswitch_batch_workspace_bytes(ctx._h, l, batch))
+    return torch.empty(max(nbytes // 8, 1), dtype=torch.int64, device=ctx.device)
+
+
 def multiply_and_relin(ctx, a, b, rlk):
     """src/evaluate.cu:1061-1104"""
     _check_pair(a, b)

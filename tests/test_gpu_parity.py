@@ -476,6 +476,53 @@ def test_inner_product_inside_the_last_forward_pass(monkeypatch, name, fused):
     assert hashes(ct, N) == case["hashes"]["keyswitch"]
 
 
+@pytest.mark.parametrize("case", ["n16_headline", "n16_wide", "n16_l11", "n13_fallback"])
+def test_batched_key_switch_equals_single_ones(case, monkeypatch):
+    """b2_keyswitch_batch (every kernel one launch over a batch that shares the key; strided sets) gives, set by set, the limbs
+    of b2_keyswitch - at the headline shape also the oracle's - with the stand-alone inner product for the 60-bit limbs and
+    with every limb in the fused pass, at a level with a ragged last digit, and where the fused pipeline does not apply
+    (N = 2^13: the sets run one after another)"""
+    monkeypatch.setenv("B2_KS_FUSED_WIDE", "1" if case == "n16_wide" else "0")
+    if case == "n13_fallback":
+        N, bits, special, l, batch = 8192, [55, 40, 41, 42, 43, 44, 45, 46, 58, 59, 60], 3, 7, 3
+    else:
+        N, bits, special, l, batch = 65536, [60] + [40] * 23 + [60] * 8, 8, 11 if case == "n16_l11" else 24, 5
+    ctx, o = make_ctx(N, bits, special)
+    beta = o.beta(l)
+    key = o.synth_key(beta, 5, 10)
+    kt, kp = key_dev(key)
+    g = torch.Generator(device="cuda")
+    g.manual_seed(17)
+    # sets of three polynomials (c0, c1, c2) with a gap of one limb between sets: strides are not the packed ones
+    stride = 3 * l + 1
+    buf = torch.stack([torch.randint(0, int(q), (batch, 4, N), dtype=torch.int64, device="cuda", generator=g) for q in o.primes[:l]], dim=2)
+    flat = torch.zeros(batch, stride, N, dtype=torch.int64, device="cuda")
+    flat[:, :3 * l] = buf[:, :3].reshape(batch, 3 * l, N)
+    want = []
+    ws, nb = _ws(ctx, _native.OP_KEYSWITCH, l)
+    for b in range(batch):
+        ct = flat[b, :2 * l].clone()
+        check(LIB.b2_keyswitch(ctx._h, l, flat[b, 2 * l].data_ptr(), kp.ctypes.data, beta, ct.data_ptr(), ws.data_ptr(), nb, stream()))
+        want.append(ct)
+    if case == "n16_headline":
+        c2_h, ct_h = host(flat[0, 2 * l:3 * l]), host(flat[0, :2 * l]).reshape(2, l, N)
+        assert np.array_equal(host(want[0]).reshape(2, l, N), o.keyswitch(l, c2_h, key, ct_h))
+    nbytes = int(LIB.b2_keyswitch_batch_workspace_bytes(ctx._h, l, batch))
+    wsb = torch.empty(nbytes // 8, dtype=torch.int64, device="cuda")
+    check(LIB.b2_keyswitch_batch(ctx._h, l, batch, flat[0, 2 * l].data_ptr(), stride, kp.ctypes.data, beta, flat.data_ptr(), stride,
+                                 wsb.data_ptr(), nbytes, stream()))
+    torch.cuda.synchronize()
+    for b in range(batch):
+        assert torch.equal(flat[b, :2 * l], want[b]), f"set {b}"
+        assert not flat[b, 3 * l].any(), "the gap between sets must stay untouched"
+    assert ctx.device_status() == 0
+    # a workspace one byte short is refused, as is a stride smaller than the set
+    assert LIB.b2_keyswitch_batch(ctx._h, l, batch, flat[0, 2 * l].data_ptr(), stride, kp.ctypes.data, beta, flat.data_ptr(), stride,
+                                  wsb.data_ptr(), nbytes - 8, stream()) != 0
+    assert LIB.b2_keyswitch_batch(ctx._h, l, batch, flat[0, 2 * l].data_ptr(), l - 1, kp.ctypes.data, beta, flat.data_ptr(), stride,
+                                  wsb.data_ptr(), nbytes, stream()) != 0
+
+
 @pytest.mark.parametrize("l", [7, 4])
 def test_fused_pass_on_every_prime_class(l, monkeypatch):
     """N = 2^16 with Q and P limbs on primes of every arithmetic class (FP64 below 2^41, the lazy integer path below
