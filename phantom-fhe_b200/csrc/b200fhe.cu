@@ -239,11 +239,12 @@ struct b2_ctx {
     bool use_cluster = false;      // N = 2^16: single-launch transforms on 8-CTA clusters
     bool use_pipe = false;         // N = 2^16: persistent passes with asynchronous double-buffered tile loads
     bool mac_interleave = false;   // B2_KS_FUSED_ORDER=1: consecutive CTAs of the fused pass walk limbs, not tiles (measured slower)
-    // B2_KS_FUSED_WIDE=1: the fused pass also takes the limbs on primes of 41 bits and more (q0 and P at the usual
-    // parameters), 10 launches per key switch instead of 12 and no stored digits at all. Measured on B200 at N = 2^16,
-    // l = 24: 8 us less for a lone key switch, but 4 % fewer key switches per second over four streams (the stand-alone
-    // inner product is memory-bound and hides behind other streams' transforms; fused, it is integer-multiply work).
-    bool mac_wide = false;
+    // The fused pass may also take the limbs on primes of 41 bits and more (q0 and P at the usual parameters): 10 launches
+    // instead of 12 and no stored digits at all. Measured on B200 at N = 2^16, l = 24: single calls lose 4 % of their
+    // four-stream throughput to it (the stand-alone inner product is memory-bound and hides behind other streams' transforms;
+    // fused, it is integer-multiply work) though a lone key switch gains 8 us; batched calls gain 1 %. So it is on for
+    // batched calls and off for single ones unless B2_KS_FUSED_WIDE = 0 | 1 says otherwise.
+    int mac_wide = -1;
     bool use_mac = false;          // N = 2^16: ModUp's last forward pass carries the inner product (off with B2_KS_FUSED_IP=0)
     int sm_count = 148;
     // RNS-limb sharding of one ciphertext over `shard_world` GPUs: this rank's slice of every list
@@ -765,7 +766,7 @@ extern "C" int b2_ctx_create(size_t N, const uint64_t *primes, size_t size_QP, s
     const char *env_pipe = getenv("B2_NTT_PIPE");
     c->use_pipe = (c->logN == 16) && env_pipe && env_pipe[0] == '1';
     const char *env_mac = getenv("B2_KS_FUSED_IP");
-    if (const char *e = getenv("B2_KS_FUSED_WIDE")) c->mac_wide = e[0] != '0';
+    if (const char *e = getenv("B2_KS_FUSED_WIDE")) c->mac_wide = e[0] != '0' ? 1 : 0;
     if (const char *e = getenv("B2_KS_FUSED_ORDER")) c->mac_interleave = e[0] == '1';
     c->use_mac = (c->logN == 16) && !c->use_cluster && !c->use_pipe && !(env_mac && env_mac[0] == '0');
     cudaDeviceGetAttribute(&c->sm_count, cudaDevAttrMultiProcessorCount, c->device);
@@ -1145,7 +1146,6 @@ struct EvkPtrs {
 // (i * p_mul_i + k * p_mul_k) * (p_lm1 + 1) + b * p_bs of the P-limb buffer. One set: {0, 0, 0, 1, alpha, 0, 0}.
 struct IpBatch {
     uint32_t dig_bs, own_bs, ct_bs, p_mul_i, p_mul_k, p_lm1, p_bs;
-    uint32_t batch_x;  // the grid is (sets, blocks of pairs) instead of (blocks of pairs, sets); measured 13 % slower on B200, so left at 0
 };
 
 // Key-switch inner product (src/eval_key_switch.cu:175-230): for logical limb t (physical prime pp)
@@ -1166,11 +1166,12 @@ __global__ void __launch_bounds__(256) ks_inner_prod_kernel(const uint64_t *__re
                                                            uint32_t beta, uint4 own_range, const IpBatch ib) {
     // own_range = (first Q limb, number of Q limbs, first P limb, number of P limbs) this launch
     // covers: everything on one GPU, the rank's slice under RNS-limb sharding
-    const uint32_t bset = ib.batch_x ? blockIdx.x : blockIdx.y, blk = ib.batch_x ? blockIdx.y : blockIdx.x;
-    digits += (size_t)bset * ib.dig_bs * N;
-    if (own) own += (size_t)bset * ib.own_bs * N;
-    if (FUSED) ct += (size_t)bset * ib.ct_bs * N;
-    const size_t jdx = 2 * ((size_t)blk * blockDim.x + threadIdx.x);
+    // The sets are the slow grid dimension: with the sets fastest (the CTAs that read one piece of the key next to one another) this
+    // kernel ran 13 % slower on B200.
+    digits += (size_t)blockIdx.y * ib.dig_bs * N;
+    if (own) own += (size_t)blockIdx.y * ib.own_bs * N;
+    if (FUSED) ct += (size_t)blockIdx.y * ib.ct_bs * N;
+    const size_t jdx = 2 * ((size_t)blockIdx.x * blockDim.x + threadIdx.x);
     if (jdx >= (size_t)(own_range.y + own_range.w) * N) return;
     const uint32_t jl = (uint32_t)(jdx / N), n = (uint32_t)(jdx % N);
     const uint32_t t = jl < own_range.y ? own_range.x + jl : l + own_range.z + (jl - own_range.y);
@@ -1227,7 +1228,7 @@ __global__ void __launch_bounds__(256) ks_inner_prod_kernel(const uint64_t *__re
             *reinterpret_cast<ulonglong2 *>(c0) = make_ulonglong2(add_mod(u0.x, r[0], md.q), add_mod(u0.y, r[1], md.q));
             *reinterpret_cast<ulonglong2 *>(c1) = make_ulonglong2(add_mod(u1.x, r[2], md.q), add_mod(u1.y, r[3], md.q));
         } else {
-            const size_t o = ((size_t)(t - l) * ib.p_mul_i * (ib.p_lm1 + 1) + (size_t)bset * ib.p_bs) * N + n;
+            const size_t o = ((size_t)(t - l) * ib.p_mul_i * (ib.p_lm1 + 1) + (size_t)blockIdx.y * ib.p_bs) * N + n;
             const size_t o1 = o + (size_t)ib.p_mul_k * (ib.p_lm1 + 1) * N;
             if (ACCP) {
                 const ulonglong2 p0 = *reinterpret_cast<const ulonglong2 *>(out + o), p1 = *reinterpret_cast<const ulonglong2 *>(out + o1);
@@ -1275,7 +1276,7 @@ __global__ void __launch_bounds__(256) ks_inner_prod_kernel(const uint64_t *__re
         *reinterpret_cast<ulonglong2 *>(c1) =
             make_ulonglong2(add_mod(u1.x, mul_shoup(r10, pi, md.q), md.q), add_mod(u1.y, mul_shoup(r11, pi, md.q), md.q));
     } else {
-        const size_t o = ((size_t)(t - l) * ib.p_mul_i * (ib.p_lm1 + 1) + (size_t)bset * ib.p_bs) * N + n;
+        const size_t o = ((size_t)(t - l) * ib.p_mul_i * (ib.p_lm1 + 1) + (size_t)blockIdx.y * ib.p_bs) * N + n;
         const size_t o1 = o + (size_t)ib.p_mul_k * (ib.p_lm1 + 1) * N;
         if (ACCP) {
             const ulonglong2 p0 = *reinterpret_cast<const ulonglong2 *>(out + o), p1 = *reinterpret_cast<const ulonglong2 *>(out + o1);
@@ -1667,10 +1668,8 @@ static int inner_prod_impl(b2_ctx *c, size_t l, const uint64_t *digits, const ui
     const size_t pairs = (size_t)(rg.y + rg.w) * c->N / 2;
     if (pairs == 0) return B2_OK;
     if (batch != 1 && (!fused || !ipb)) return fail(B2_EINVAL, "a batched inner product runs in the fused form");
-    const unsigned blocks = (unsigned)((pairs + 255) / 256);
-    IpBatch ib = ipb ? *ipb : IpBatch{0, 0, 0, 1, (uint32_t)c->size_P, 0, 0, 0};
-    ib.batch_x = 0;
-    const dim3 grid = ib.batch_x ? dim3(batch, blocks) : dim3(blocks, batch);
+    const dim3 grid((unsigned)((pairs + 255) / 256), batch);
+    const IpBatch ib = ipb ? *ipb : IpBatch{0, 0, 0, 1, (uint32_t)c->size_P, 0, 0};
     LaunchScope ls(c, s, "ks_inner_prod");
     if (fused && acc_p)
         ks_inner_prod_kernel<3, true, true><<<grid, 256, 0, s>>>(digits, own, ep, out, ct, c->d_Pinv, c->d_mod, c->d_redc, (uint32_t)c->N, (uint32_t)l,
@@ -1752,7 +1751,8 @@ static int modup_inner_fused(b2_ctx *c, size_t l, const uint64_t *c2, const uint
     const size_t N = c->N, lP = l + c->size_P, beta = c->plan[l].beta;
     const LevelPlan &pl = c->plan[l];
     *done = false;
-    if (!(c->use_mac && (pl.mac_ok || (c->mac_wide && beta <= B2_MAC_MAX_BETA)) && n_evk >= beta && aligned32(c2) && aligned32(ct) && aligned32(up) && aligned32(cxP))) return B2_OK;
+    const bool wide = (c->mac_wide < 0 ? kb.batch > 1 : c->mac_wide == 1) && beta <= B2_MAC_MAX_BETA;
+    if (!(c->use_mac && (pl.mac_ok || wide) && n_evk >= beta && aligned32(c2) && aligned32(ct) && aligned32(up) && aligned32(cxP))) return B2_OK;
     {
         // ModUp up to the column pass for every limb; the row pass is stored only for the limbs the stand-alone inner
         // product still handles (wide Q primes and P); for the FP64 limbs of Q it runs inside ntt_fwd_rows_mac
@@ -1780,7 +1780,6 @@ static int modup_inner_fused(b2_ctx *c, size_t l, const uint64_t *c2, const uint
         }
         // the limbs on 60-bit primes (q0, P) either ride on the fused pass too (integer arithmetic) or, mac_wide off,
         // keep the stored row pass and the stand-alone inner product
-        const bool wide = c->mac_wide;
         if (!wide && pl.n_up_rows) {
             NttArgs b = a;
             b.jobs = pl.jobs_up_rows;

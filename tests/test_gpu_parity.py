@@ -482,7 +482,10 @@ def test_batched_key_switch_equals_single_ones(case, monkeypatch):
     of b2_keyswitch - at the headline shape also the oracle's - with the stand-alone inner product for the 60-bit limbs and
     with every limb in the fused pass, at a level with a ragged last digit, and where the fused pipeline does not apply
     (N = 2^13: the sets run one after another)"""
-    monkeypatch.setenv("B2_KS_FUSED_WIDE", "1" if case == "n16_wide" else "0")
+    if case == "n16_l11":
+        monkeypatch.delenv("B2_KS_FUSED_WIDE", raising=False)  # the default: every limb in the fused pass for batched calls only
+    else:
+        monkeypatch.setenv("B2_KS_FUSED_WIDE", "1" if case == "n16_wide" else "0")
     if case == "n13_fallback":
         N, bits, special, l, batch = 8192, [55, 40, 41, 42, 43, 44, 45, 46, 58, 59, 60], 3, 7, 3
     else:
