@@ -105,6 +105,16 @@ int b2_keyswitch_batch(b2_ctx *ctx, size_t size_Ql, size_t batch, const uint64_t
                        const uint64_t *const *evk, size_t n_evk, uint64_t *d_ct, size_t ct_stride,
                        void *d_ws, size_t ws_bytes, void *stream);
 
+/* multiply_and_relin (src/evaluate.cu:1061-1104) and, rescale != 0, rescale_to_next (src/evaluate.cu:1413-1464) for
+ * `batch` ciphertext pairs with ONE relinearisation key, every kernel one launch over the batch. Pair b reads
+ * d_a + b * a_stride and d_b + b * b_stride limbs ([2][size_Ql][N] each) and writes d_out + b * out_stride limbs:
+ * [2][size_Ql][N], or [2][size_Ql-1][N] after the rescale. Same limbs as b2_multiply_and_relin followed by b2_rescale. */
+size_t b2_multiply_relin_batch_workspace_bytes(const b2_ctx *ctx, size_t size_Ql, size_t batch);
+int b2_multiply_relin_rescale_batch(b2_ctx *ctx, size_t size_Ql, size_t batch, const uint64_t *d_a, size_t a_stride,
+                                    const uint64_t *d_b, size_t b_stride, const uint64_t *const *rlk, size_t n_evk,
+                                    uint64_t *d_out, size_t out_stride, int rescale, void *d_ws, size_t ws_bytes,
+                                    void *stream);
+
 /* replaces bgv_ckks_multiply's tensor product (src/evaluate.cu:345-397, src/polymath.cu:463-540):
  * d_a, d_b [2][size_Ql][N] -> d_out [3][size_Ql][N] */
 int b2_tensor_mul(b2_ctx *ctx, size_t size_Ql, const uint64_t *d_a, const uint64_t *d_b,

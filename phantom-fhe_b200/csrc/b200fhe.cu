@@ -1289,11 +1289,13 @@ __global__ void __launch_bounds__(256) ks_inner_prod_kernel(const uint64_t *__re
 
 // HMult tensor product (src/polymath.cu:463-498): d0 = a0 b0, d2 = a1 b1, d1 = (a0+a1)(b0+b1) - d0 - d2
 // d0, d1 go to out[0..2S), d2 to out2[0..S): the relinearising caller keeps d2 in scratch and the rest in its result
+// A batch in one launch: blockIdx.y = pair b, whose operands, result and d2 start b * bs.x / .y / .z / .w limbs further.
 __global__ void __launch_bounds__(256) tensor_mul_kernel(const uint64_t *__restrict__ a, const uint64_t *__restrict__ b, uint64_t *__restrict__ out,
-                                                        uint64_t *__restrict__ out2, const Mod *mod, uint32_t N, uint32_t l) {
+                                                        uint64_t *__restrict__ out2, const Mod *mod, uint32_t N, uint32_t l, uint4 bs) {
     const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     const size_t S = (size_t)l * N;
     if (idx >= S) return;
+    a += (size_t)blockIdx.y * bs.x * N, b += (size_t)blockIdx.y * bs.y * N, out += (size_t)blockIdx.y * bs.z * N, out2 += (size_t)blockIdx.y * bs.w * N;
     const Mod md = mod[idx / N];
     const uint64_t q = md.q;
     const uint64_t a0 = a[idx], a1 = a[S + idx], b0 = b[idx], b1 = b[S + idx];
@@ -1863,15 +1865,8 @@ extern "C" size_t b2_keyswitch_batch_workspace_bytes(const b2_ctx *c, size_t l, 
 // switch, grids that fill the GPU at every level, and the key read from HBM once per batch: the fused inner product
 // puts the sets that share a key tile next to one another in the grid, so all but the first find it in L2. Elsewhere the
 // key switches run one after another on the same stream. Workspace: t [batch][l] | up [batch][beta][l+alpha] | cxP [batch][2][alpha].
-extern "C" int b2_keyswitch_batch(b2_ctx *c, size_t l, size_t batch, const uint64_t *d_c2, size_t c2_stride, const uint64_t *const *evk, size_t n_evk,
-                                  uint64_t *d_ct, size_t ct_stride, void *d_ws, size_t ws_bytes, void *stream) {
-    CHECK_CTX(c);
-    CHECK_LEVEL(c, l);
-    if (!d_c2 || !evk || !d_ct || !d_ws || batch < 1 || batch > 65535) return fail(B2_EINVAL, "keyswitch_batch: bad argument");
-    if (c2_stride < l || ct_stride < 2 * l || c2_stride > 0xFFFFFFFFull || ct_stride > 0xFFFFFFFFull)
-        return fail(B2_EINVAL, "keyswitch_batch: a set's stride is smaller than the set");
-    if (ws_bytes < b2_keyswitch_batch_workspace_bytes(c, l, batch)) return fail(B2_EWS, "keyswitch_batch: workspace too small");
-    cudaStream_t s = (cudaStream_t)stream;
+static int keyswitch_batch_impl(b2_ctx *c, size_t l, size_t batch, const uint64_t *d_c2, size_t c2_stride, const uint64_t *const *evk, size_t n_evk,
+                                  uint64_t *d_ct, size_t ct_stride, void *d_ws, cudaStream_t s) {
     const LevelPlan &pl = c->plan[l];
     const size_t N = c->N, a = c->size_P, lP = l + a, beta = pl.beta;
     const uint32_t B = (uint32_t)batch, per = (uint32_t)(beta * lP);
@@ -1900,13 +1895,24 @@ extern "C" int b2_keyswitch_batch(b2_ctx *c, size_t l, size_t batch, const uint6
     return run_fwd(c, up, up, pl.jobs_dnf_ntt, (uint32_t)(2 * l), 0, EpiSubFrom{d_ct, (uint32_t)ct_stride}, s, 0, 0, 0, BatchDims{B, 0, per, 0, per});
 }
 
+extern "C" int b2_keyswitch_batch(b2_ctx *c, size_t l, size_t batch, const uint64_t *d_c2, size_t c2_stride, const uint64_t *const *evk, size_t n_evk,
+                                  uint64_t *d_ct, size_t ct_stride, void *d_ws, size_t ws_bytes, void *stream) {
+    CHECK_CTX(c);
+    CHECK_LEVEL(c, l);
+    if (!d_c2 || !evk || !d_ct || !d_ws || batch < 1 || batch > 65535) return fail(B2_EINVAL, "keyswitch_batch: bad argument");
+    if (c2_stride < l || ct_stride < 2 * l || c2_stride > 0xFFFFFFFFull || ct_stride > 0xFFFFFFFFull)
+        return fail(B2_EINVAL, "keyswitch_batch: a set's stride is smaller than the set");
+    if (ws_bytes < b2_keyswitch_batch_workspace_bytes(c, l, batch)) return fail(B2_EWS, "keyswitch_batch: workspace too small");
+    return keyswitch_batch_impl(c, l, batch, d_c2, c2_stride, evk, n_evk, d_ct, ct_stride, d_ws, (cudaStream_t)stream);
+}
+
 extern "C" int b2_tensor_mul(b2_ctx *c, size_t l, const uint64_t *d_a, const uint64_t *d_b, uint64_t *d_out, void *stream) {
     CHECK_CTX(c);
     CHECK_LEVEL(c, l);
     if (!d_a || !d_b || !d_out) return fail(B2_EINVAL, "tensor_mul: null pointer");
     const size_t n = l * c->N;
     LaunchScope ls(c, (cudaStream_t)stream, "tensor_mul");
-    tensor_mul_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(d_a, d_b, d_out, d_out + 2 * n, c->d_mod, (uint32_t)c->N, (uint32_t)l);
+    tensor_mul_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(d_a, d_b, d_out, d_out + 2 * n, c->d_mod, (uint32_t)c->N, (uint32_t)l, make_uint4(0, 0, 0, 0));
     LAUNCH_CHECK("tensor_mul_kernel");
     return B2_OK;
 }
@@ -1924,7 +1930,7 @@ extern "C" int b2_multiply_and_relin(b2_ctx *c, size_t l, const uint64_t *d_a, c
         // d0, d1 straight into the result, d2 into scratch for the key switch (every thread reads its own position of
         // the operands before it writes, so the result may alias an operand)
         LaunchScope ls(c, s, "tensor_mul");
-        tensor_mul_kernel<<<(unsigned)((S + 255) / 256), 256, 0, s>>>(d_a, d_b, d_out, t3 + 2 * S, c->d_mod, (uint32_t)c->N, (uint32_t)l);
+        tensor_mul_kernel<<<(unsigned)((S + 255) / 256), 256, 0, s>>>(d_a, d_b, d_out, t3 + 2 * S, c->d_mod, (uint32_t)c->N, (uint32_t)l, make_uint4(0, 0, 0, 0));
         LAUNCH_CHECK("tensor_mul_kernel");
     }
     return keyswitch_impl(c, l, t3 + 2 * S, rlk, n_evk, d_out, ws, s);
@@ -1989,6 +1995,64 @@ extern "C" int b2_rescale_rounded(b2_ctx *c, size_t l, size_t n_poly, const uint
         if (rc) return rc;
     }
     return rescale_tail<2>(c, l, n_poly, r, d_in, d_out, s);
+}
+
+extern "C" size_t b2_multiply_relin_batch_workspace_bytes(const b2_ctx *c, size_t l, size_t batch) {
+    if (!c || l < 1 || l > c->size_Q || batch < 1) return 0;
+    return batch * (3 * l + 2) * limb_bytes(c) + b2_keyswitch_batch_workspace_bytes(c, l, batch);
+}
+
+// HMult + relinearise (+ rescale) of `batch` ciphertext pairs with ONE relinearisation key, every kernel one launch over
+// the batch: tensor product, b2_keyswitch_batch's pipeline, and - rescale != 0 - the drop of the last prime
+// (src/evaluate.cu:1061-1104, 1413-1464). Pair b reads d_a + b * a_stride and d_b + b * b_stride limbs ([2][l][N] each)
+// and writes d_out + b * out_stride limbs: [2][l][N], or [2][l-1][N] after the rescale. Same limbs as b2_multiply_and_relin
+// followed by b2_rescale. Workspace: prod [batch][3][l] | r [batch][2] | the key switch's.
+extern "C" int b2_multiply_relin_rescale_batch(b2_ctx *c, size_t l, size_t batch, const uint64_t *d_a, size_t a_stride, const uint64_t *d_b,
+                                               size_t b_stride, const uint64_t *const *rlk, size_t n_evk, uint64_t *d_out, size_t out_stride,
+                                               int rescale, void *d_ws, size_t ws_bytes, void *stream) {
+    CHECK_CTX(c);
+    CHECK_LEVEL(c, l);
+    if (!d_a || !d_b || !rlk || !d_out || !d_ws || batch < 1 || batch > 65535) return fail(B2_EINVAL, "multiply_relin_rescale_batch: bad argument");
+    if (rescale && l < 2) return fail(B2_EINVAL, "multiply_relin_rescale_batch: no prime left to drop");
+    const size_t out_limbs = 2 * (rescale ? l - 1 : l);
+    if (a_stride < 2 * l || b_stride < 2 * l || out_stride < out_limbs || a_stride > 0xFFFFFFFFull || b_stride > 0xFFFFFFFFull || out_stride > 0xFFFFFFFFull)
+        return fail(B2_EINVAL, "multiply_relin_rescale_batch: a pair's stride is smaller than the pair");
+    if (ws_bytes < b2_multiply_relin_batch_workspace_bytes(c, l, batch)) return fail(B2_EWS, "multiply_relin_rescale_batch: workspace too small");
+    if (!aligned32(d_a) || !aligned32(d_b) || !aligned32(d_out) || !aligned32(d_ws)) return fail(B2_EINVAL, "device buffers must be 32-byte aligned (256-bit accesses)");
+    cudaStream_t s = (cudaStream_t)stream;
+    const size_t N = c->N, S = l * N;
+    const uint32_t B = (uint32_t)batch;
+    uint64_t *prod = (uint64_t *)d_ws, *r = prod + batch * 3 * S, *ws = r + batch * 2 * N;
+    {
+        LaunchScope ls(c, s, "tensor_mul");
+        tensor_mul_kernel<<<dim3((unsigned)((S + 255) / 256), B), 256, 0, s>>>(d_a, d_b, prod, prod + 2 * S, c->d_mod, (uint32_t)N, (uint32_t)l,
+                                                                             make_uint4((uint32_t)a_stride, (uint32_t)b_stride, (uint32_t)(3 * l), (uint32_t)(3 * l)));
+        LAUNCH_CHECK("tensor_mul_kernel");
+    }
+    int rc = keyswitch_batch_impl(c, l, batch, prod + 2 * S, 3 * l, rlk, n_evk, prod, 3 * l, ws, s);
+    if (rc) return rc;
+    if (!rescale) {
+        for (size_t b = 0; b < batch; b++)
+            CUDA_TRY(cudaMemcpyAsync(d_out + b * out_stride * N, prod + b * 3 * S, 2 * S * 8, cudaMemcpyDeviceToDevice, s));
+        return B2_OK;
+    }
+    if (c->use_cluster || c->use_pipe) {
+        for (size_t b = 0; b < batch; b++) {
+            rc = run_inv(c, prod + b * 3 * S, r, c->plan[l].jobs_rs_intt, 2, 0, c->d_fin_plain, s);
+            if (rc) return rc;
+            rc = rescale_tail<1>(c, l, 2, r, prod + b * 3 * S, d_out + b * out_stride * N, s);
+            if (rc) return rc;
+        }
+        return B2_OK;
+    }
+    const LevelPlan &pl = c->plan[l];
+    // the dropped limb of both polynomials of every pair, then every remaining limb (in_j - NTT_j(r mod q_j)) * q_last^-1
+    rc = run_inv(c, prod, r, pl.jobs_rs_intt, 2, 0, c->d_fin_plain, s, BatchDims{B, 0, (uint32_t)(3 * l), 0, 2});
+    if (rc) return rc;
+    EpiSubMul<false> epi{prod, d_out, pl.qlast_inv};
+    epi.m_bs = (uint32_t)(3 * l), epi.o_bs = (uint32_t)out_stride;
+    return run_fwd<EpiSubMul<false>, 1>(c, r, d_out, pl.jobs_rs_ntt, (uint32_t)(2 * (l - 1)), 0, epi, s, 0, (uint32_t)(l - 1), c->q[l - 1],
+                                         BatchDims{B, 0, 2, 0, (uint32_t)out_stride});
 }
 
 // ------------------------------------------------------------------------------------------------

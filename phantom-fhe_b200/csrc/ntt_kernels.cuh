@@ -111,17 +111,18 @@ struct EpiSubMul {
     const uint64_t *minuend;  // [slots][N]
     uint64_t *out;            // [slots][N]
     const W2 *k;              // per prime
-    const uint64_t *m_;
-    uint64_t *o_;
-    W2 kk;
+    uint32_t m_bs = 0, o_bs = 0;  // batch strides in limbs (set b of a batched launch: see NttArgs)
+    const uint64_t *m_ = nullptr;
+    uint64_t *o_ = nullptr;
+    W2 kk = W2{0, 0};
     bool aligned() const { return aligned32(minuend) && aligned32(out); }
     template <int E> struct Regs {
         u64x4 m[E / 4];
         u64x4 acc[ACCUM ? E / 4 : 1];
     };
-    __device__ __forceinline__ void init(const NttArgs &, const Job &job, size_t N) {
-        m_ = minuend + (size_t)job.z * N;
-        o_ = out + (size_t)job.w * N;
+    __device__ __forceinline__ void init(const NttArgs &a, const Job &job, size_t N) {
+        m_ = minuend + ((size_t)job.z + (size_t)set_idx(a) * m_bs) * N;
+        o_ = out + ((size_t)job.w + (size_t)set_idx(a) * o_bs) * N;
         kk = k[job.y];
     }
     template <int E> __device__ __forceinline__ void preload(Regs<E> &r, size_t o) const {

@@ -585,6 +585,26 @@ def relinearize_batch(ctx, data, rlk, ws=None):
     return data[:, :2]
 
 
+def multiply_relin_rescale_batch(ctx, a, b, rlk, rescale=True, out=None, ws=None):
+    """multiply_and_relin (src/evaluate.cu:1061-1104) followed, if `rescale`, by rescale_to_next (src/evaluate.cu:1413-1464) for a
+    batch of ciphertext pairs held as tensors a, b [batch][2][limbs][N], all relinearised with the one key; every kernel is
+    one launch over the batch (b2_multiply_relin_rescale_batch). Returns [batch][2][limbs - 1 or limbs][N]; the caller
+    keeps track of scale and chain index as for the single calls."""
+    if a.dim() != 4 or a.shape != b.shape or a.shape[1] != 2 or not (a.is_contiguous() and b.is_contiguous()):
+        raise ValueError("a and b must be contiguous [batch][2][limbs][N] tensors of one shape")
+    batch, l = int(a.shape[0]), int(a.shape[2])
+    lo = l - 1 if rescale else l
+    if out is None:
+        out = torch.empty(batch, 2, lo, ctx.N, dtype=torch.int64, device=a.device)
+    if ws is None:
+        nbytes = int(LIB.b2_multiply_relin_batch_workspace_bytes(ctx._h, l, batch))
+        ws = torch.empty(max(nbytes // 8, 1), dtype=torch.int64, device=a.device)
+    tab = _key_table(ctx, rlk, l)
+    check(LIB.b2_multiply_relin_rescale_batch(ctx._h, l, batch, a.data_ptr(), 2 * l, b.data_ptr(), 2 * l, tab.ctypes.data, len(tab),
+                                              out.data_ptr(), 2 * lo, 1 if rescale else 0, ws.data_ptr(), ws.numel() * 8, _stream()))
+    return out
+
+
 def keyswitch_batch_workspace(ctx, l, batch):
     """scratch tensor for `relinearize_batch` / b2_keyswitch_batch at `l` limbs"""
     nbytes = int(LIB.b2_keyswitch_batch_workspace_bytes(ctx._h, l, batch))

@@ -56,6 +56,16 @@ def test_multiply_relin_rescale_chain(env):
     # a level down the same key still works (fewer digits needed)
     r2 = ph.multiply_and_relin(ctx, r, r, env["rlk"])
     assert np.array_equal(r2.numpy(), o.multiply_and_relin(l - 1, r.numpy(), r.numpy(), env["rlk_h"]))
+    # the batched forms: pairs (a, b) and (b, a) in one call; three-polynomial products relinearised in one call
+    import torch
+    A, B = torch.stack([env["a"].data, env["b"].data]), torch.stack([env["b"].data, env["a"].data])
+    got = ph.multiply_relin_rescale_batch(ctx, A, B, env["rlk"], rescale=True)
+    assert np.array_equal(got[0].cpu().numpy().astype(np.uint64), r.numpy()) and torch.equal(got[0], got[1])
+    got = ph.multiply_relin_rescale_batch(ctx, A, B, env["rlk"], rescale=False)
+    assert np.array_equal(got[1].cpu().numpy().astype(np.uint64), want)
+    m3b = torch.stack([m3.data, m3.data]).contiguous()
+    two = ph.relinearize_batch(ctx, m3b, env["rlk"])
+    assert np.array_equal(two[1].cpu().numpy().astype(np.uint64), want) and torch.equal(two[0], two[1])
 
 
 def test_add_sub_negate_plain(env):

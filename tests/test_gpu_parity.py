@@ -526,6 +526,48 @@ def test_batched_key_switch_equals_single_ones(case, monkeypatch):
                                   wsb.data_ptr(), nbytes, stream()) != 0
 
 
+@pytest.mark.parametrize("shape", ["n16_headline", "n13"])
+@pytest.mark.parametrize("rescale", [1, 0])
+def test_batched_multiply_relin_rescale_equals_single_calls(shape, rescale):
+    """b2_multiply_relin_rescale_batch (tensor product, key switch and rescale each one launch over the batch) against
+    b2_multiply_and_relin + b2_rescale pair by pair, whose limbs the reference's hashes pin (mul_relin, mul_relin_rescale)"""
+    if shape == "n13":
+        N, bits, special, l, batch = 8192, [55, 40, 41, 42, 43, 44, 45, 46, 58, 59, 60], 3, 6, 3
+    else:
+        N, bits, special, l, batch = 65536, [60] + [40] * 23 + [60] * 8, 8, 24, 4
+    ctx, o = make_ctx(N, bits, special)
+    beta = o.beta(l)
+    kt, kp = key_dev(o.synth_key(beta, 9, 10))
+    g = torch.Generator(device="cuda")
+    g.manual_seed(23)
+    a = torch.stack([torch.randint(0, int(q), (batch, 2, N), dtype=torch.int64, device="cuda", generator=g) for q in o.primes[:l]], dim=2).contiguous()
+    b = torch.stack([torch.randint(0, int(q), (batch, 2, N), dtype=torch.int64, device="cuda", generator=g) for q in o.primes[:l]], dim=2).contiguous()
+    lo = l - 1 if rescale else l
+    want = []
+    ws, nb = _ws(ctx, _native.OP_MUL_RELIN, l)
+    wr, nr = _ws(ctx, _native.OP_RESCALE, l)
+    for i in range(batch):
+        m = ctx.empty(2, l)
+        check(LIB.b2_multiply_and_relin(ctx._h, l, a[i].data_ptr(), b[i].data_ptr(), kp.ctypes.data, beta, m.data_ptr(), ws.data_ptr(), nb, stream()))
+        if rescale:
+            r = ctx.empty(2, lo)
+            check(LIB.b2_rescale(ctx._h, l, 2, m.data_ptr(), r.data_ptr(), wr.data_ptr(), nr, stream()))
+            m = r
+        want.append(m)
+    stride = 2 * lo + 3  # pairs of the result are not packed
+    out = torch.zeros(batch, stride, N, dtype=torch.int64, device="cuda")
+    nbytes = int(LIB.b2_multiply_relin_batch_workspace_bytes(ctx._h, l, batch))
+    wsb = torch.empty(nbytes // 8, dtype=torch.int64, device="cuda")
+    check(LIB.b2_multiply_relin_rescale_batch(ctx._h, l, batch, a.data_ptr(), 2 * l, b.data_ptr(), 2 * l, kp.ctypes.data, beta, out.data_ptr(), stride,
+                                              rescale, wsb.data_ptr(), nbytes, stream()))
+    torch.cuda.synchronize()
+    for i in range(batch):
+        assert torch.equal(out[i, :2 * lo].reshape(2, lo, N), want[i]), f"pair {i}"
+        assert not out[i, 2 * lo:].any(), "the gap between pairs must stay untouched"
+    assert LIB.b2_multiply_relin_rescale_batch(ctx._h, l, batch, a.data_ptr(), 2 * l, b.data_ptr(), 2 * l, kp.ctypes.data, beta, out.data_ptr(), stride,
+                                               rescale, wsb.data_ptr(), nbytes - 8, stream()) != 0
+
+
 @pytest.mark.parametrize("l", [7, 4])
 def test_fused_pass_on_every_prime_class(l, monkeypatch):
     """N = 2^16 with Q and P limbs on primes of every arithmetic class (FP64 below 2^41, the lazy integer path below
