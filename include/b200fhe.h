@@ -115,6 +115,13 @@ int b2_multiply_relin_rescale_batch(b2_ctx *ctx, size_t size_Ql, size_t batch, c
                                     uint64_t *d_out, size_t out_stride, int rescale, void *d_ws, size_t ws_bytes,
                                     void *stream);
 
+/* replaces sample_uniform_poly / sample_error_poly / sample_ternary_poly (src/prng.cu:142-240): polynomials drawn on the
+ * device from a ChaCha20 keystream (32-byte key, 12-byte nonce, both host pointers read at call time; never reuse a pair).
+ * kind 0: uniform residues, d_out uint64 [n_limbs][N] for primes first_prime ..; kind 1: centred binomial, 21 coin pairs;
+ * kind 2: uniform ternary; kinds 1 and 2 write int64 [N] signed coefficients (spread them with b2_expand_signed). */
+int b2_sample(b2_ctx *ctx, int kind, const uint8_t *key32, const uint8_t *nonce12, size_t first_prime, size_t n_limbs,
+              void *d_out, void *stream);
+
 /* replaces bgv_ckks_multiply's tensor product (src/evaluate.cu:345-397, src/polymath.cu:463-540):
  * d_a, d_b [2][size_Ql][N] -> d_out [3][size_Ql][N] */
 int b2_tensor_mul(b2_ctx *ctx, size_t size_Ql, const uint64_t *d_a, const uint64_t *d_b,

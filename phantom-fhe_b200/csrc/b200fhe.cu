@@ -18,6 +18,7 @@
 
 #include "../../include/b200fhe.h"
 #include "ntt_kernels.cuh"
+#include "sampler.cuh"
 #include "bconv_tc.cuh"
 
 using namespace b2;
@@ -2376,6 +2377,31 @@ extern "C" int b2_expand_signed(b2_ctx *c, size_t first_prime, size_t n_limbs, c
     }
     if (!to_ntt) return B2_OK;
     return run_fwd(c, d_out, d_out, nullptr, (uint32_t)n_limbs, (uint32_t)first_prime, EpiStore{}, s);
+}
+
+// Sampling on the device from a ChaCha20 keystream (sampler.cuh): kind 0 = uniform residues of n_limbs limbs starting at prime
+// first_prime (d_out uint64 [n_limbs][N]), kind 1 = centred-binomial error, kind 2 = uniform ternary (d_out int64 [N], signed
+// coefficients for b2_expand_signed). key: 32 bytes, nonce: 12 bytes, both read on the host at call time; a (key, nonce) pair
+// must never be used for two draws.
+extern "C" int b2_sample(b2_ctx *c, int kind, const uint8_t *key32, const uint8_t *nonce12, size_t first_prime, size_t n_limbs, void *d_out,
+                         void *stream) {
+    CHECK_CTX(c);
+    if (!key32 || !nonce12 || !d_out || kind < 0 || kind > 2) return fail(B2_EINVAL, "sample: bad argument");
+    if (kind == 0 && (n_limbs < 1 || first_prime + n_limbs > c->size_QP)) return fail(B2_EINVAL, "sample: limb range outside the modulus chain");
+    b2::ChaChaKey k;
+    memcpy(k.k, key32, 32);
+    memcpy(k.n, nonce12, 12);
+    cudaStream_t s = (cudaStream_t)stream;
+    const size_t blocks = (kind == 0 ? n_limbs : 1) * (c->N / 8);
+    if (blocks * (size_t)(b2::B2_SAMPLE_RESERVE + 1) > 0xFFFFFFFFull) return fail(B2_ESIZE, "sample: the draw does not fit the block counter");
+    LaunchScope ls(c, s, "sample");
+    if (kind == 0)
+        b2::sample_uniform_kernel<<<(unsigned)((blocks + 127) / 128), 128, 0, s>>>((uint64_t *)d_out, k, c->d_mod, (uint32_t)first_prime, (uint32_t)c->N,
+                                                                                  (uint32_t)blocks);
+    else
+        b2::sample_small_kernel<<<(unsigned)((blocks + 127) / 128), 128, 0, s>>>((int64_t *)d_out, k, kind, (uint32_t)blocks);
+    LAUNCH_CHECK("sample kernel");
+    return B2_OK;
 }
 
 extern "C" int b2_expand_single_chain(b2_ctx *c, size_t l, const int64_t *d_signed, uint64_t *d_out, void *stream) {

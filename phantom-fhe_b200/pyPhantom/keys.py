@@ -1,9 +1,11 @@
 """Key generation, symmetric encryption and decryption (binding.cu:77-98; src/secretkey.cu).
 
-Sampling is done on the host (key generation is set-up work, not the hot path); every polynomial
+The secret itself (one polynomial, a choice of positions for the sparse form) is drawn on the host; the uniform masks,
+the errors and the ternary encryption randomness - the bulk: gigabytes for a bootstrapping key set - are drawn on the
+device by b2_sample from ChaCha20 keystreams whose keys and nonces come from the host generator; every polynomial
 operation - reduction into the limbs, NTT, products, sums - is a call into the C ABI.
-Randomness comes from a cryptographic generator: an AES-256-CTR keystream keyed from os.urandom,
-one stream for secret material (secrets, errors, encryption randomness) and an independent one for
+The host generator is cryptographic: an AES-256-CTR keystream keyed from os.urandom,
+one stream for secret material (secrets, error and encryption-randomness keys) and an independent one for
 the public uniform masks, as the reference draws from a salsa20 stream seeded from
 std::random_device (src/prng.cu, include/prng.cuh:12-21). `seed=` swaps in numpy's PCG64 so that
 tests and benchmarks are reproducible: it is NOT secure and is meant for nothing else.
@@ -33,6 +35,9 @@ class _CtrDrbg:
 
     def _words(self, n):
         return np.frombuffer(self._enc.update(bytes(8 * int(n))), dtype=np.uint64)
+
+    def bytes(self, n):
+        return self._enc.update(bytes(int(n)))
 
     def _below(self, bound, size):
         bound = int(bound)
@@ -97,16 +102,30 @@ def _expand(ctx, coeffs_i64, n_limbs, ntt=True):
     return out
 
 
+def _device_draw(ctx, rng, kind, n_limbs, out):
+    """one draw of b2_sample (src/prng.cu:142-240's three samplers): a fresh ChaCha20 key and nonce from the host
+    generator, the polynomial itself made on the device"""
+    kn = np.frombuffer(rng.bytes(44), dtype=np.uint8).copy()
+    check(LIB.b2_sample(ctx._h, kind, kn.ctypes.data, kn[32:].ctypes.data, 0, n_limbs, out.data_ptr(), _stream()))
+    return out
+
+
+def _signed_draw(ctx, rng, kind, n_limbs, ntt=True):
+    """kind 1: centred-binomial error, kind 2: uniform ternary; the same integer in every limb, NTT form by default"""
+    d = _device_draw(ctx, rng, kind, 1, torch.empty(ctx.N, dtype=torch.int64, device=ctx.device))
+    out = ctx.empty(n_limbs)
+    check(LIB.b2_expand_signed(ctx._h, 0, n_limbs, d.data_ptr(), out.data_ptr(), 1 if ntt else 0, _stream()))
+    return out
+
+
 def _uniform(ctx, rng, n_limbs):
     """[n_limbs][N] uniform residues (already a valid NTT-form polynomial)"""
-    host = np.stack([rng.integers(0, int(q), ctx.N, dtype=np.uint64) for q in ctx.primes[:n_limbs]])
-    return torch.from_numpy(host.view(np.int64)).to(ctx.device)
+    return _device_draw(ctx, rng, 0, n_limbs, ctx.empty(n_limbs))
 
 
 def _error(ctx, rng, n_limbs):
     """centred binomial, 21 coin pairs: standard deviation sqrt(21/2) = 3.24 (include/prng.cuh:67-76)"""
-    e = rng.binomial(21, 0.5, ctx.N).astype(np.int64) - rng.binomial(21, 0.5, ctx.N).astype(np.int64)
-    return _expand(ctx, e, n_limbs)
+    return _signed_draw(ctx, rng, 1, n_limbs)
 
 
 class public_key:
@@ -121,7 +140,7 @@ class public_key:
             raise ValueError("PhantomPublicKey has not been generated")
         rng, _ = _rng_pair(seed)
         n_all, sQ = ctx.size_QP, ctx.size_Q
-        u = _expand(ctx, rng.integers(-1, 2, ctx.N).astype(np.int64), n_all)
+        u = _signed_draw(ctx, rng, 2, n_all)
         cx = ctx.empty(2, n_all)
         for i in range(2):
             _poly(ctx, 2, n_all, self.pk.data[i], u, cx[i])
