@@ -115,6 +115,21 @@ int b2_multiply_relin_rescale_batch(b2_ctx *ctx, size_t size_Ql, size_t batch, c
                                     uint64_t *d_out, size_t out_stride, int rescale, void *d_ws, size_t ws_bytes,
                                     void *stream);
 
+/* replaces special_fft_backward / special_fft_forward with their bit reversals (src/fft.cu:90-346, src/ckks.cu:97-105, 176-183):
+ * n = N/2 complex doubles; d_rot uint32 [n] = 5^j mod 2N, d_ksi complex double [2N + 1] = exp(2 pi i k / 2N).
+ * inverse = 1 (encode): d_vals (overwritten) -> d_out = preimage of the embedding times scale; inverse = 0 (decode):
+ * d_vals -> d_out = slot values times scale. d_vals and d_out must not overlap. */
+int b2_special_fft(b2_ctx *ctx, void *d_vals, void *d_out, const uint32_t *d_rot, const void *d_ksi, int inverse,
+                   double scale, void *stream);
+/* the rounding step of encode_internal (src/ckks.cu:107-131): N/2 complex doubles -> int64 [N] signed coefficients
+ * (real parts first, then imaginary parts); spread them over the limbs with b2_expand_signed */
+int b2_encode_round(b2_ctx *ctx, const void *d_u, int64_t *d_coeffs, void *stream);
+/* replaces DBaseConverter::compose_array (src/rns_base.cu:173-234): coefficient-form residues d_res [size_Ql][N] -> N/2
+ * complex doubles (centred value times inv_scale; coefficient k real part of entry k, k + N/2 its imaginary part).
+ * d_tab: 64-bit words hat [l][l] (Q/q_i) | inv [l] ((Q/q_i)^-1 mod q_i) | Q [l] | floor(Q/2) [l], little endian */
+int b2_decode_compose(b2_ctx *ctx, size_t size_Ql, const uint64_t *d_res, const uint64_t *d_tab, double inv_scale,
+                      void *d_out, void *stream);
+
 /* replaces sample_uniform_poly / sample_error_poly / sample_ternary_poly (src/prng.cu:142-240): polynomials drawn on the
  * device from a ChaCha20 keystream (32-byte key, 12-byte nonce, both host pointers read at call time; never reuse a pair).
  * kind 0: uniform residues, d_out uint64 [n_limbs][N] for primes first_prime ..; kind 1: centred binomial, 21 coin pairs;

@@ -6,7 +6,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 SRC = os.path.join(HERE, "csrc", "b200fhe.cu")
 OUT = os.path.join(HERE, "libb200fhe.so")
-DEPS = [SRC] + [os.path.join(HERE, "csrc", f) for f in ("ntt_kernels.cuh", "modarith.cuh", "bconv_tc.cuh", "bconv_tc_plan.h", "sampler.cuh")] + [
+DEPS = [SRC] + [os.path.join(HERE, "csrc", f) for f in ("ntt_kernels.cuh", "modarith.cuh", "bconv_tc.cuh", "bconv_tc_plan.h", "sampler.cuh", "encoder.cuh")] + [
         os.path.join(os.path.dirname(HERE), "include", "b200fhe.h")]
 FLAGS = ["-std=c++17", "-O3", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
          "-Xcompiler", "-fPIC,-fopenmp", "-shared", "-lgomp"]

@@ -19,6 +19,7 @@
 #include "../../include/b200fhe.h"
 #include "ntt_kernels.cuh"
 #include "sampler.cuh"
+#include "encoder.cuh"
 #include "bconv_tc.cuh"
 
 using namespace b2;
@@ -2377,6 +2378,56 @@ extern "C" int b2_expand_signed(b2_ctx *c, size_t first_prime, size_t n_limbs, c
     }
     if (!to_ntt) return B2_OK;
     return run_fwd(c, d_out, d_out, nullptr, (uint32_t)n_limbs, (uint32_t)first_prime, EpiStore{}, s);
+}
+
+// The encoder's transform (encoder.cuh): n = N/2 complex values, rot = 5^j mod 2N (uint32 [n]), ksi = exp(2 pi i k / 2N)
+// (double2 [2N + 1]). inverse = 1 (encode): d_vals (natural order, overwritten) -> d_out = the embedding's preimage times
+// `scale`; inverse = 0 (decode): d_vals -> d_out = slot values times `scale`. d_vals and d_out must not overlap.
+extern "C" int b2_special_fft(b2_ctx *c, void *d_vals, void *d_out, const uint32_t *d_rot, const void *d_ksi, int inverse, double scale, void *stream) {
+    CHECK_CTX(c);
+    if (!d_vals || !d_out || !d_rot || !d_ksi || d_vals == d_out) return fail(B2_EINVAL, "special_fft: bad argument");
+    cudaStream_t s = (cudaStream_t)stream;
+    const uint32_t n = (uint32_t)(c->N / 2), M = (uint32_t)(2 * c->N), logn = (uint32_t)c->logN - 1;
+    double2 *v = (double2 *)d_vals, *o = (double2 *)d_out;
+    LaunchScope ls(c, s, "special_fft");
+    if (inverse) {
+        for (uint32_t len = n; len >= 2; len >>= 1)
+            b2::cfft_stage_kernel<<<(n / 2 + 255) / 256, 256, 0, s>>>(v, n, len, d_rot, (const double2 *)d_ksi, M, 1);
+        b2::cfft_bitrev_kernel<<<(n + 255) / 256, 256, 0, s>>>(o, v, n, logn, scale);
+    } else {
+        b2::cfft_bitrev_kernel<<<(n + 255) / 256, 256, 0, s>>>(o, v, n, logn, scale);
+        for (uint32_t len = 2; len <= n; len <<= 1)
+            b2::cfft_stage_kernel<<<(n / 2 + 255) / 256, 256, 0, s>>>(o, n, len, d_rot, (const double2 *)d_ksi, M, 0);
+    }
+    LAUNCH_CHECK("special_fft kernels");
+    return B2_OK;
+}
+
+// d_u: N/2 complex values (the scaled preimage, every part below 2^62 in magnitude) -> d_coeffs int64 [N]: coefficient k =
+// round(Re u_k), coefficient k + N/2 = round(Im u_k) (src/ckks.cu:97-131 before the decomposition into limbs)
+extern "C" int b2_encode_round(b2_ctx *c, const void *d_u, int64_t *d_coeffs, void *stream) {
+    CHECK_CTX(c);
+    if (!d_u || !d_coeffs) return fail(B2_EINVAL, "encode_round: null pointer");
+    const uint32_t n = (uint32_t)(c->N / 2);
+    LaunchScope ls(c, (cudaStream_t)stream, "encode_round");
+    b2::encode_round_kernel<<<(n + 255) / 256, 256, 0, (cudaStream_t)stream>>>((const double2 *)d_u, n, d_coeffs);
+    LAUNCH_CHECK("encode_round_kernel");
+    return B2_OK;
+}
+
+// CRT composition of a coefficient-form plaintext of l limbs (src/rns_base.cu:173-234): d_res [l][N] -> d_out N/2 complex
+// values (coefficient k in the real part of entry k, coefficient k + N/2 in its imaginary part), centred and multiplied by
+// inv_scale. d_tab: the level's constants as 64-bit little-endian words, hat [l][l] | inv [l] | Q [l] | floor(Q/2) [l].
+extern "C" int b2_decode_compose(b2_ctx *c, size_t l, const uint64_t *d_res, const uint64_t *d_tab, double inv_scale, void *d_out, void *stream) {
+    CHECK_CTX(c);
+    CHECK_LEVEL(c, l);
+    if (!d_res || !d_tab || !d_out) return fail(B2_EINVAL, "decode_compose: null pointer");
+    if (l > (size_t)b2::B2_CRT_MAX_LIMBS) return fail(B2_ESIZE, "decode_compose: more than 64 limbs");
+    LaunchScope ls(c, (cudaStream_t)stream, "decode_compose");
+    b2::decode_compose_kernel<<<(unsigned)((c->N + 127) / 128), 128, 0, (cudaStream_t)stream>>>(d_res, d_tab, c->d_mod, (uint32_t)c->N, (uint32_t)l, inv_scale,
+                                                                                              (double2 *)d_out);
+    LAUNCH_CHECK("decode_compose_kernel");
+    return B2_OK;
 }
 
 // Sampling on the device from a ChaCha20 keystream (sampler.cuh): kind 0 = uniform residues of n_limbs limbs starting at prime

@@ -34,6 +34,9 @@ SIGNATURES = {
     "b2_keyswitch_batch": (_int, [_vp, _sz, _sz, _vp, _sz, _vp, _sz, _vp, _sz, _vp, _sz, _vp]),
     "b2_multiply_relin_batch_workspace_bytes": (_sz, [_vp, _sz, _sz]),
     "b2_multiply_relin_rescale_batch": (_int, [_vp, _sz, _sz, _vp, _sz, _vp, _sz, _vp, _sz, _vp, _sz, _int, _vp, _sz, _vp]),
+    "b2_special_fft": (_int, [_vp, _vp, _vp, _vp, _vp, _int, ctypes.c_double, _vp]),
+    "b2_encode_round": (_int, [_vp, _vp, _vp, _vp]),
+    "b2_decode_compose": (_int, [_vp, _sz, _vp, _vp, ctypes.c_double, _vp, _vp]),
     "b2_sample": (_int, [_vp, _int, _vp, _vp, _sz, _sz, _vp, _vp]),
     "b2_tensor_mul": (_int, [_vp, _sz, _vp, _vp, _vp, _vp]),
     "b2_multiply_and_relin": (_int, [_vp, _sz, _vp, _vp, _vp, _sz, _vp, _vp, _sz, _vp]),

@@ -7,6 +7,8 @@ import math
 
 import numpy as np
 import pytest
+
+import encoder_ref
 import torch
 
 pytestmark = pytest.mark.gpu
@@ -110,7 +112,7 @@ def test_stages_against_the_plain_computation():
     ct = sk.encrypt_symmetric(ctx, enc.encode_double_vector(ctx, msg, scale, chain_index=ctx.size_Q))
     raised = boot.mod_raise(ctx, bk, ct)
     assert raised.coeff_modulus_size() == ctx.size_Q
-    coef = enc._centred_coefficients(ctx, sk.decrypt(ctx, raised))
+    coef = encoder_ref.centred_coefficients(ctx, sk.decrypt(ctx, raised))
     q0 = int(ctx.primes[0])
     I = np.array([(2 * int(v) + q0) // (2 * q0) for v in coef])
     assert np.abs(I).max() < boot.K_RANGE                       # the sparse secret keeps q0*I small
@@ -128,7 +130,7 @@ def test_stages_against_the_plain_computation():
     assert np.max(np.abs(dec(ints[0]) - I[:n][P])) < 1e-8
     assert np.max(np.abs(dec(ints[1]) - I[n:][P])) < 1e-8
     qi = boot.slot_to_coeff(ctx, bk, ints[0], ints[1], ops)
-    cq = enc._centred_coefficients(ctx, sk.decrypt(ctx, qi))
+    cq = encoder_ref.centred_coefficients(ctx, sk.decrypt(ctx, qi))
     # the coefficients hold I times the key's target scale (q0, times down_const / p_x when the key scales the input up)
     assert max(abs(float(int(a)) / bk.final_target - float(i)) for a, i in zip(cq, I)) < 1e-8
 
