@@ -46,7 +46,7 @@ int b2_create_coeff_modulus(size_t N, const int *bit_sizes, size_t count, uint64
 
 /* replaces PhantomContext(params) (src/context.cu:125-232; python/src/binding.cu:72):
  * primes[0..size_QP) = Q primes then the size_P special primes. Builds every table of every
- * level on the host and uploads it to `device`. N in [2^12, 2^16]. */
+ * level on the host and uploads it to `device`. N in [2^12, 2^17]. */
 int b2_ctx_create(size_t N, const uint64_t *primes, size_t size_QP, size_t size_P, int device,
                   b2_ctx **out);
 void b2_ctx_destroy(b2_ctx *ctx);

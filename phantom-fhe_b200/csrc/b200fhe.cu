@@ -552,7 +552,7 @@ extern "C" void b2_ctx_destroy(b2_ctx *c) {
 extern "C" int b2_ctx_create(size_t N, const uint64_t *primes, size_t size_QP, size_t size_P, int device, b2_ctx **out) {
     if (!primes || !out) return fail(B2_EINVAL, "ctx_create: null argument");
     *out = nullptr;
-    if (N < 4096 || N > 65536 || (N & (N - 1))) return fail(B2_ESIZE, "ctx_create: poly_modulus_degree must be a power of two in [4096, 65536]");
+    if (N < 4096 || N > 131072 || (N & (N - 1))) return fail(B2_ESIZE, "ctx_create: poly_modulus_degree must be a power of two in [4096, 131072]");
     if (size_QP < 2 || size_QP > 64) return fail(B2_ESIZE, "ctx_create: the coefficient modulus must hold 2..64 primes");
     if (size_P < 1 || size_P >= size_QP) return fail(B2_EINVAL, "ctx_create: special_modulus_size must be in [1, size_QP)");
     if (size_P > 16) return fail(B2_ESIZE, "ctx_create: special_modulus_size above 16 is not built");
@@ -807,6 +807,8 @@ template <int LOG_T> struct PassCfg;
 #ifndef B2_NTT_LOG_CC8
 #define B2_NTT_LOG_CC8 3
 #endif
+// 512-point sub-transforms (the row pass of N = 2^17): 4 + 5 stages, 32 residues per thread in the second group
+template <> struct PassCfg<9> { static constexpr int R_STRIDED = 4, R_CONTIG = 5, LOG_C = 2, LOG_CC = 3; };
 template <> struct PassCfg<8> { static constexpr int R_STRIDED = 4, R_CONTIG = 4, LOG_C = 3, LOG_CC = B2_NTT_LOG_CC8; };
 template <> struct PassCfg<7> { static constexpr int R_STRIDED = 3, R_CONTIG = 4, LOG_C = 4, LOG_CC = 4; };
 template <> struct PassCfg<6> { static constexpr int R_STRIDED = 3, R_CONTIG = 3, LOG_C = 4, LOG_CC = 4; };
@@ -918,6 +920,7 @@ static int run_fwd(const b2_ctx *c, const uint64_t *src, uint64_t *dst, const Jo
         return B2_OK;
     }
     switch (c->logN) {
+        case 17: launch_fwd<8, 9, Epi, SRC>(c, a, njobs, epi, s, bd.batch); break;
         case 16: launch_fwd<8, 8, Epi, SRC>(c, a, njobs, epi, s, bd.batch); break;
         case 15: launch_fwd<7, 8, Epi, SRC>(c, a, njobs, epi, s, bd.batch); break;
         case 14: launch_fwd<7, 7, Epi, SRC>(c, a, njobs, epi, s, bd.batch); break;
@@ -943,6 +946,7 @@ static int run_inv(const b2_ctx *c, const uint64_t *src, uint64_t *dst, const Jo
         return B2_OK;
     }
     switch (c->logN) {
+        case 17: launch_inv<8, 9>(c, a, njobs, s, bd.batch); break;
         case 16: launch_inv<8, 8>(c, a, njobs, s, bd.batch); break;
         case 15: launch_inv<7, 8>(c, a, njobs, s, bd.batch); break;
         case 14: launch_inv<7, 7>(c, a, njobs, s, bd.batch); break;

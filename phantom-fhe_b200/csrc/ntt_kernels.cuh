@@ -36,7 +36,10 @@ using Job = uint4;
 #ifndef B2_NTT_RESIDENT_THREADS
 #define B2_NTT_RESIDENT_THREADS 768
 #endif
-constexpr int ntt_min_blocks(int threads) { return B2_NTT_RESIDENT_THREADS / threads > 0 ? B2_NTT_RESIDENT_THREADS / threads : 1; }
+// (a pass whose threads hold 32 residues each - the 512-point pass of N = 2^17 - gets twice the registers: half the threads)
+constexpr int ntt_min_blocks(int threads, int residues_per_thread = 16) {
+    return (B2_NTT_RESIDENT_THREADS / (residues_per_thread > 16 ? 2 : 1)) / threads > 0 ? (B2_NTT_RESIDENT_THREADS / (residues_per_thread > 16 ? 2 : 1)) / threads : 1;
+}
 
 struct NttArgs {
     const uint64_t *src;  // limb `slot` at src + slot * N
@@ -435,7 +438,7 @@ __device__ __forceinline__ void fwd_body(const NttArgs &a, const Epi &epi, uint6
 }
 
 template <int LOG_T, int R1, int R2, int LOG_C, bool COLS, bool LAST, class Epi, int SRC = 0>
-__global__ void __launch_bounds__((1 << (LOG_C + LOG_T)) / (1 << (R1 > R2 ? R1 : R2)), ntt_min_blocks((1 << (LOG_C + LOG_T)) / (1 << (R1 > R2 ? R1 : R2))))
+__global__ void __launch_bounds__((1 << (LOG_C + LOG_T)) / (1 << (R1 > R2 ? R1 : R2)), ntt_min_blocks((1 << (LOG_C + LOG_T)) / (1 << (R1 > R2 ? R1 : R2)), 1 << (R1 > R2 ? R1 : R2)))
 ntt_fwd_pass(NttArgs a, Epi epi) {
     static_assert(R1 + R2 == LOG_T, "stage split");
     constexpr int TT = 1 << LOG_T, C = 1 << LOG_C;
@@ -777,7 +780,7 @@ __device__ __forceinline__ void inv_body(const NttArgs &a, uint64_t *sm, const J
 }
 
 template <int LOG_T, int RA, int RB, int LOG_C, bool COLS, bool LAST>
-__global__ void __launch_bounds__((1 << (LOG_C + LOG_T)) / (1 << (RA > RB ? RA : RB)), ntt_min_blocks((1 << (LOG_C + LOG_T)) / (1 << (RA > RB ? RA : RB))))
+__global__ void __launch_bounds__((1 << (LOG_C + LOG_T)) / (1 << (RA > RB ? RA : RB)), ntt_min_blocks((1 << (LOG_C + LOG_T)) / (1 << (RA > RB ? RA : RB)), 1 << (RA > RB ? RA : RB)))
 ntt_inv_pass(NttArgs a) {
     static_assert(RA + RB == LOG_T, "stage split");
     constexpr int TT = 1 << LOG_T, C = 1 << LOG_C;

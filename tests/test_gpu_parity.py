@@ -37,7 +37,7 @@ def test_tables_match_oracle(logn):
         assert [int(x) for x in ws] == [(int(v) << 64) // q for v in w]  # src/host/ntt.cu compute_shoup
 
 
-@pytest.mark.parametrize("logn", [12, 13, 14, 15, 16])
+@pytest.mark.parametrize("logn", [12, 13, 14, 15, 16, 17])
 def test_ntt_against_oracle_and_roundtrip(logn):
     N = 1 << logn
     ctx, o = make_ctx(N, [60, 30, 40, 50, 59, 60], 2)
@@ -60,6 +60,41 @@ def test_ntt_against_oracle_and_roundtrip(logn):
     got = host(d)
     assert not got[0].any()
     assert np.array_equal(got[1], o.ntt_forward(edge[1:2], first_prime=1)[0])
+
+
+def test_largest_degree_key_switch_and_rescale():
+    """N = 2^17 (the reference's largest degree, include/host/defines.h:18-23): 17 butterfly stages stretch the lazy
+    ranges of every arithmetic class, so the chain holds primes at the top of each class (41 bits: FP64, 46 bits: integer
+    without corrections, 60 bits) and the inputs include the all-(q-1) polynomial; transforms, a key switch with a ragged
+    last digit, and both rescales against the oracle"""
+    N = 131072
+    ctx, o = make_ctx(N, [60, 41, 46, 45, 30, 60, 59], 2)
+    nq = o.size_Q
+    x = o.fill(1, o.primes, 9, 50)[0]
+    x[:, 0] = [int(q) - 1 for q in o.primes]
+    x[1] = int(o.primes[1]) - 1
+    x[2] = int(o.primes[2]) - 1
+    d = dev(x)
+    check(LIB.b2_ntt_forward(ctx._h, d.data_ptr(), o.size_QP, 0, stream()))
+    assert np.array_equal(host(d), o.ntt_forward(x))
+    check(LIB.b2_ntt_inverse(ctx._h, d.data_ptr(), o.size_QP, 0, stream()))
+    assert np.array_equal(host(d), x)
+    for l in (nq, 3):
+        beta = o.beta(l)
+        key = o.synth_key(beta, 3, 10)
+        kt, kp = key_dev(key)
+        c2_h, ct_h = o.fill(1, o.primes[:l], 3, 3)[0], o.synth_ct(l, 3, 1)
+        c2, ct = dev(c2_h), dev(ct_h)
+        ws, nb = _ws(ctx, _native.OP_KEYSWITCH, l)
+        check(LIB.b2_keyswitch(ctx._h, l, c2.data_ptr(), kp.ctypes.data, beta, ct.data_ptr(), ws.data_ptr(), nb, stream()))
+        assert np.array_equal(host(ct), o.keyswitch(l, c2_h, key, ct_h))
+        r = ctx.empty(2, l - 1)
+        ws, nb = _ws(ctx, _native.OP_RESCALE, l)
+        check(LIB.b2_rescale(ctx._h, l, 2, dev(ct_h).data_ptr(), r.data_ptr(), ws.data_ptr(), nb, stream()))
+        assert np.array_equal(host(r), o.rescale(l, ct_h))
+        check(LIB.b2_rescale_rounded(ctx._h, l, 2, dev(ct_h).data_ptr(), r.data_ptr(), ws.data_ptr(), nb, stream()))
+        assert np.array_equal(host(r), o.rescale_rounded(l, ct_h))
+    assert ctx.device_status() == 0
 
 
 @pytest.mark.parametrize("path", GOLDEN, ids=IDS)
