@@ -337,7 +337,13 @@ int main(int argc, char **argv) {
             std::ofstream f1(interop_write + "/ref_sk.bin", std::ios::binary), f2(interop_write + "/ref_ct.bin", std::ios::binary);
             sk.save(f1);
             ct.save(f2);
-            printf("interop: wrote ref_sk.bin ref_ct.bin\n");
+            // a relinearisation key cut down to the digits chain index 3 reads (src/secretkey.cu:301-352)
+            PhantomRelinKey rlk = sk.gen_relinkey(context);
+            const size_t full = rlk.dnum();
+            rlk.mod_drop_to_inplace(context, 3);
+            std::ofstream f3(interop_write + "/ref_rlk_trunc.bin", std::ios::binary);
+            rlk.save(f3);
+            printf("interop: wrote ref_sk.bin ref_ct.bin ref_rlk_trunc.bin (%zu of %zu digits)\n", rlk.dnum(), full);
         }
         if (!interop_read.empty()) {
             std::ifstream f1(interop_read + "/" + interop_prefix + "_sk.bin", std::ios::binary), f2(interop_read + "/" + interop_prefix + "_ct.bin", std::ios::binary);

@@ -162,6 +162,16 @@ def test_interchange_with_the_reference_library(tmp_path):
     ct = ph.ciphertext().load(open(tmp_path / "ref_ct.bin", "rb"))
     assert ct.chain_index() == 1 and ct.scale() == SCALE
     assert np.max(np.abs(enc.decode_complex_vector(ctx, sk.decrypt(ctx, ct)) - z)) < 1e-6
+    # the reference's relinearisation key after its mod_drop_to_inplace(3): one digit of two; it relinearises here at chain
+    # index 3 (two limbs, one digit), and is refused a level up where two digits are needed
+    rlk = ph.relin_key().load(open(tmp_path / "ref_rlk_trunc.bin", "rb"))
+    assert rlk.dnum() == 1
+    low = ph.mod_switch_to(ctx, ct, 3)
+    sq = ph.multiply_and_relin(ctx, low, low, rlk)
+    got = enc.decode_complex_vector(ctx, sk.decrypt(ctx, sq))
+    assert np.max(np.abs(got - z * z)) < 1e-4
+    with pytest.raises(ValueError):
+        ph.multiply_and_relin(ctx, ct, ct, rlk)
     mine = ph.secret_key(ctx, seed=99)
     with open(tmp_path / "b2_sk.bin", "wb") as f:
         mine.save(f)
