@@ -618,7 +618,7 @@ def main():
     wss = [ctx.workspace(_native.OP_KEYSWITCH, LEVEL) for _ in range(S)]
     batched = args.launch == "batched"
     if batched:
-        wsb = [ph.keyswitch_batch_workspace(ctx, LEVEL, max(per_key)) for _ in range(min(S, K))]
+        ks_wsb = [ph.keyswitch_batch_workspace(ctx, LEVEL, max(per_key)) for _ in range(min(S, K))]
     stream = torch.cuda.current_stream()
     side = [torch.cuda.Stream() for _ in range(S)] if S > 1 else [stream]
     fork, joins = torch.cuda.Event(), [torch.cuda.Event() for _ in range(S)]
@@ -626,7 +626,7 @@ def main():
     def step_batched():
         # the ciphertexts that share a key go through b2_keyswitch_batch in one call (every kernel one launch over them);
         # the keys' groups are spread over the streams
-        L = len(wsb)
+        L = len(ks_wsb)
         if L > 1:
             fork.record(stream)
         for i in range(L):
@@ -638,7 +638,7 @@ def main():
                 if g is None:
                     continue
                 check(LIB.b2_keyswitch_batch(ctx._h, LEVEL, g.shape[0], g[0, 2].data_ptr(), 3 * LEVEL, key_tabs[k].ctypes.data, BETA,
-                                             g.data_ptr(), 3 * LEVEL, wsb[i].data_ptr(), wsb[i].numel() * 8, st.cuda_stream))
+                                             g.data_ptr(), 3 * LEVEL, ks_wsb[i].data_ptr(), ks_wsb[i].numel() * 8, st.cuda_stream))
             if L > 1:
                 joins[i].record(st)
                 stream.wait_event(joins[i])
@@ -800,7 +800,7 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         us_one = 1e3 * float(t.item()) / n_sh
         # throughput: batches of LB ciphertexts, NB batches in flight on two lanes (own stream and communicator each)
-        n_lanes = max(1, int(os.environ.get("B2_SHARD_LANES", "2")))
+        n_lanes = max(1, int(os.environ.get("B2_SHARD_LANES", "4")))
         LB = max(1, min(int(os.environ.get("B2_SHARD_BATCH", "8")), n_sh_ct // 4))
         NB = max(4, 2 * n_lanes)
         lanes = sh.make_lanes(n_lanes)
@@ -875,7 +875,7 @@ def main():
             PB = int(g.shape[0])
             for _ in range(prof_steps):
                 check(LIB.b2_keyswitch_batch(ctx._h, LEVEL, PB, g[0, 2].data_ptr(), 3 * LEVEL, key_tabs[0].ctypes.data, BETA, g.data_ptr(),
-                                             3 * LEVEL, wsb[0].data_ptr(), wsb[0].numel() * 8, stream.cuda_stream))
+                                             3 * LEVEL, ks_wsb[0].data_ptr(), ks_wsb[0].numel() * 8, stream.cuda_stream))
         for _ in range(0 if batched else prof_steps):
             for b in range(PB):
                 t = dev_ct3[b]
@@ -935,7 +935,7 @@ def main():
         compositions = compositions_section(ph, ctx, torch, np, synth, primes, keys, N, LEVEL)
         del dev_ct3, dev_groups, keys, stage
         if batched:
-            del wsb
+            del ks_wsb
         torch.cuda.empty_cache()
         bsgs = bsgs_section(ph, torch, np, synth)
         torch.cuda.empty_cache()
