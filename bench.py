@@ -801,7 +801,7 @@ def main():
         us_one = 1e3 * float(t.item()) / n_sh
         # throughput: batches of LB ciphertexts, NB batches in flight on two lanes (own stream and communicator each)
         n_lanes = max(1, int(os.environ.get("B2_SHARD_LANES", "4")))
-        LB = max(1, min(int(os.environ.get("B2_SHARD_BATCH", "8")), n_sh_ct // 4))
+        LB = max(1, min(int(os.environ.get("B2_SHARD_BATCH", "32")), 32))
         NB = max(4, 2 * n_lanes)
         lanes = sh.make_lanes(n_lanes)
         wsb = [sh.batch_workspace(LEVEL, LB)[0] for _ in lanes]
