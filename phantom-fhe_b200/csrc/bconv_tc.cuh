@@ -455,7 +455,7 @@ __global__ void __launch_bounds__(128 * WG) bconv_tc_persist(const uint64_t *__r
         } else if (lane == 0) {
             atomicExch(err, 1u);  // the MMA never signalled: this CTA stops, its remaining tiles are not written
         }
-        // a CTA whose wait ran out must stop as a whole: make the verdict uniform over the CTA
+        // a CTA whose wait ran out must stop as a whole: make the outcome uniform over the CTA
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
         ok = __syncthreads_and(ok);
         cur ^= 1u;
