@@ -100,7 +100,7 @@ struct TcOutS {
 // (two for 7 and 8 planes) wide multiply-add, the quotient estimate is one high multiply, and the two subtractions, the
 // choice between r and r - p (sign of the difference: r < 2p < 2^62) and the predicated store are spelled out in PTX so
 // that no branch and no 64-bit compare is generated. Same value as tc_reduce / tc_reduce_dev (bconv_tc_plan.h).
-template <int NB>
+template <int NB, bool ALWAYS = false>
 __device__ __forceinline__ void tc_output(const uint32_t *c, const uint4 m, uint64_t *__restrict__ out_n) {
     constexpr int SH = 8 * NB - 17;
     const uint32_t x0 = c[0] + (c[1] << 8), x1 = c[2] + (c[3] << 8);
@@ -135,25 +135,31 @@ __device__ __forceinline__ void tc_output(const uint32_t *c, const uint4 m, uint
         "}\n"
         : "=&r"(rl), "=&r"(rh)
         : "r"(vl), "r"(vh), "r"(ql), "r"(qh), "r"(m.x), "r"(m.y));
-    asm volatile(
-        "{\n\t"
-        ".reg .pred pv;\n\t"
-        "setp.ne.u32 pv, %3, 0xFFFFFFFF;\n\t"
-        "@pv st.global.v2.u32 [%0], {%1, %2};\n\t"
-        "}\n" ::"l"(out_n + m.w),
-        "r"(rl), "r"(rh), "r"(m.w)
-        : "memory");
+    if constexpr (ALWAYS) {
+        asm volatile("st.global.v2.u32 [%0], {%1, %2};" ::"l"(out_n + m.w), "r"(rl), "r"(rh) : "memory");
+    } else {
+        asm volatile(
+            "{\n\t"
+            ".reg .pred pv;\n\t"
+            "setp.ne.u32 pv, %3, 0xFFFFFFFF;\n\t"
+            "@pv st.global.v2.u32 [%0], {%1, %2};\n\t"
+            "}\n" ::"l"(out_n + m.w),
+            "r"(rl), "r"(rh), "r"(m.w)
+            : "memory");
+    }
 }
 
-template <int NB>
+// NV = number of outputs the group holds (0: not known at compile time, every slot is processed and the store of an empty
+// one is predicated off)
+template <int NB, int NV = 0>
 __device__ __forceinline__ void tc_group_lean(const uint32_t (&c)[16], uint32_t mo_smem, uint64_t *__restrict__ out_n) {
-    constexpr int OPG = 16 / NB;
+    constexpr int OPG = NV ? NV : 16 / NB;
 #pragma unroll
     for (int o = 0; o < OPG; o++) {
         uint4 m;
         // the records do not change while a job's tiles are reduced: the load may move freely
         asm("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(m.x), "=r"(m.y), "=r"(m.z), "=r"(m.w) : "r"(mo_smem + 16 * o));
-        tc_output<NB>(&c[o * NB], m, out_n);
+        tc_output<NB, NV != 0>(&c[o * NB], m, out_n);
     }
 }
 
@@ -364,7 +370,7 @@ __global__ void __launch_bounds__(128 * WG) bconv_tc_persist(const uint64_t *__r
                     rec = TcOutS{raw.x, raw.y, raw.z, raw.w * (tb.out_lm1 + 1) * N};
                 }
                 sOut[tid] = rec;
-                if (o == 0) sNb[tid >> 2] = hdr.x;
+                if (o == 0) sNb[tid >> 2] = hdr.x * 8 + hdr.y;  // bytes per output, outputs in the group
             }
             loaded_job = jb;
         }
@@ -420,12 +426,22 @@ __global__ void __launch_bounds__(128 * WG) bconv_tc_persist(const uint64_t *__r
             // measured 56 against 37 us per key switch)
             auto reduce_group = [&](const uint32_t (&c)[16], uint32_t g) {
                 const uint32_t mo = tc_smem_u32(sOut + 4 * g);
+                // one case per (bytes per output, outputs in the group): no slot is processed in vain and no store is predicated
                 switch (sNb[g]) {
-                    case 4: tc_group_lean<4>(c, mo, out_n); break;
-                    case 5: tc_group_lean<5>(c, mo, out_n); break;
-                    case 6: tc_group_lean<6>(c, mo, out_n); break;
-                    case 7: tc_group_lean<7>(c, mo, out_n); break;
-                    default: tc_group_lean<8>(c, mo, out_n); break;
+                    case 4 * 8 + 1: tc_group_lean<4, 1>(c, mo, out_n); break;
+                    case 4 * 8 + 2: tc_group_lean<4, 2>(c, mo, out_n); break;
+                    case 4 * 8 + 3: tc_group_lean<4, 3>(c, mo, out_n); break;
+                    case 4 * 8 + 4: tc_group_lean<4, 4>(c, mo, out_n); break;
+                    case 5 * 8 + 1: tc_group_lean<5, 1>(c, mo, out_n); break;
+                    case 5 * 8 + 2: tc_group_lean<5, 2>(c, mo, out_n); break;
+                    case 5 * 8 + 3: tc_group_lean<5, 3>(c, mo, out_n); break;
+                    case 6 * 8 + 1: tc_group_lean<6, 1>(c, mo, out_n); break;
+                    case 6 * 8 + 2: tc_group_lean<6, 2>(c, mo, out_n); break;
+                    case 7 * 8 + 1: tc_group_lean<7, 1>(c, mo, out_n); break;
+                    case 7 * 8 + 2: tc_group_lean<7, 2>(c, mo, out_n); break;
+                    case 8 * 8 + 1: tc_group_lean<8, 1>(c, mo, out_n); break;
+                    case 8 * 8 + 2: tc_group_lean<8, 2>(c, mo, out_n); break;
+                    default: break;  // an empty group: the planner makes none
                 }
             };
             // two register sets: the next group's planes travel from TMEM while this one is reduced
