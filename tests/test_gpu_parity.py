@@ -427,7 +427,7 @@ def test_error_behaviour():
         check(LIB.b2_galois_permute(h, 12345, x.data_ptr(), ws.data_ptr(), 1, s))
     import ctypes
     hh = ctypes.c_void_p()
-    for bad_n in (2048, 1 << 17, 5000):
+    for bad_n in (2048, 1 << 18, 5000):
         assert LIB.b2_ctx_create(bad_n, o.primes.ctypes.data, 5, 2, 0, ctypes.byref(hh)) == -2
     comp = np.array([4097 * 3, int(o.primes[1])], dtype=np.uint64)
     assert LIB.b2_ctx_create(4096, comp.ctypes.data, 2, 1, 0, ctypes.byref(hh)) == -1
