@@ -1169,7 +1169,9 @@ __global__ void __launch_bounds__(256) ks_inner_prod_kernel(const uint64_t *__re
                                                            EvkPtrs evk, uint64_t *__restrict__ out, uint64_t *__restrict__ ct,
                                                            const W2 *__restrict__ pinv, const Mod *mod, const b2_ctx::RedcMeta *redc,
                                                            uint32_t N, uint32_t l, uint32_t lP, uint32_t size_Q, uint32_t size_QP,
-                                                           uint32_t beta, uint4 own_range, const IpBatch ib) {
+                                                           uint32_t beta, uint4 own_range, const IpBatch ib, const uint32_t *__restrict__ perm) {
+    // perm (optional): the digits are read through the NTT-domain permutation of a Galois element, digit[perm[n]] - hoisted
+    // rotations, whose permuted copy of the ModUp digits is then never written (src/evaluate.cu:2041-2045 permutes into a buffer)
     // own_range = (first Q limb, number of Q limbs, first P limb, number of P limbs) this launch
     // covers: everything on one GPU, the rank's slice under RNS-limb sharding
     // The sets are the slow grid dimension: with the sets fastest (the CTAs that read one piece of the key next to one another) this
@@ -1187,6 +1189,7 @@ __global__ void __launch_bounds__(256) ks_inner_prod_kernel(const uint64_t *__re
     // `own` (optional): the NTT-form input of ModUp; limb t of digit t / alpha is that input itself
     // (src/rns_bconv.cu:522-528), so the digit buffer need not hold a copy of it
     const uint32_t own_d = (own && t < l) ? t / (lP - l) : 0xFFFFFFFFu;
+    const uint2 p2 = perm ? *reinterpret_cast<const uint2 *>(perm + n) : make_uint2(0, 0);
     if (md.q < b2::FP_LIMIT) {
         // Small prime (uniform over the block): digits and key words are below 2^41, so each product
         // is four exact FP64 FMAs on 21-bit pieces instead of five wide integer multiplies, and the
@@ -1199,8 +1202,14 @@ __global__ void __launch_bounds__(256) ks_inner_prod_kernel(const uint64_t *__re
         auto lo = [](uint64_t v) { return __dsub_rn(__longlong_as_double((long long)((v & 0x1FFFFF) | 0x4330000000000000ull)), 4503599627370496.0); };
         auto hi = [](uint64_t v) { return __dsub_rn(__longlong_as_double((long long)((v >> 21) | 0x4330000000000000ull)), 4503599627370496.0); };
         for (uint32_t d = 0; d < beta; d++) {
-            const ulonglong2 x = (d == own_d) ? *reinterpret_cast<const ulonglong2 *>(own + (size_t)t * N + n)
-                                              : *reinterpret_cast<const ulonglong2 *>(digits + ((size_t)d * lP + t) * N + n);
+            ulonglong2 x;
+            if (perm) {
+                const uint64_t *dg = digits + ((size_t)d * lP + t) * N;
+                x = make_ulonglong2(dg[p2.x], dg[p2.y]);
+            } else {
+                x = (d == own_d) ? *reinterpret_cast<const ulonglong2 *>(own + (size_t)t * N + n)
+                                 : *reinterpret_cast<const ulonglong2 *>(digits + ((size_t)d * lP + t) * N + n);
+            }
             const uint64_t *e = evk.p[d] + (size_t)pp * N + n;
             const ulonglong2 e0 = __ldcs(reinterpret_cast<const ulonglong2 *>(e));
             const ulonglong2 e1 = __ldcs(reinterpret_cast<const ulonglong2 *>(e + (size_t)size_QP * N));
@@ -1251,8 +1260,13 @@ __global__ void __launch_bounds__(256) ks_inner_prod_kernel(const uint64_t *__re
 #pragma unroll
         for (int i = 0; i < MAX_BETA; i++) {
             if (d0 + i < beta) {
-                x[i] = (d0 + i == own_d) ? *reinterpret_cast<const ulonglong2 *>(own + (size_t)t * N + n)
-                                         : *reinterpret_cast<const ulonglong2 *>(digits + ((size_t)(d0 + i) * lP + t) * N + n);
+                if (perm) {
+                    const uint64_t *dg = digits + ((size_t)(d0 + i) * lP + t) * N;
+                    x[i] = make_ulonglong2(dg[p2.x], dg[p2.y]);
+                } else {
+                    x[i] = (d0 + i == own_d) ? *reinterpret_cast<const ulonglong2 *>(own + (size_t)t * N + n)
+                                             : *reinterpret_cast<const ulonglong2 *>(digits + ((size_t)(d0 + i) * lP + t) * N + n);
+                }
                 const uint64_t *e = evk.p[d0 + i] + (size_t)pp * N + n;
                 e0[i] = __ldcs(reinterpret_cast<const ulonglong2 *>(e));
                 e1[i] = __ldcs(reinterpret_cast<const ulonglong2 *>(e + (size_t)size_QP * N));
@@ -1663,8 +1677,9 @@ extern "C" int b2_modup(b2_ctx *c, size_t l, const uint64_t *d_c2, uint64_t *d_o
 // fused = false: out = cx [2][lP][N]. fused = true: Q limbs accumulate into ct, out = [2][alpha][N].
 static int inner_prod_impl(b2_ctx *c, size_t l, const uint64_t *digits, const uint64_t *own, const uint64_t *const *evk, size_t n_evk,
                            uint64_t *out, uint64_t *ct, bool fused, cudaStream_t s, const uint4 *range = nullptr, bool acc_p = false,
-                           uint32_t batch = 1, const IpBatch *ipb = nullptr) {
+                           uint32_t batch = 1, const IpBatch *ipb = nullptr, const uint32_t *perm = nullptr) {
     const size_t beta = c->plan[l].beta, lP = l + c->size_P;
+    if (perm && own) return fail(B2_EINVAL, "a permuted inner product reads every limb from the digit buffer");
     if (n_evk < beta) return fail(B2_EINVAL, "key has fewer digits than this level needs");
     if (beta > 64) return fail(B2_ESIZE, "more than 64 digits");
     EvkPtrs ep;
@@ -1681,13 +1696,13 @@ static int inner_prod_impl(b2_ctx *c, size_t l, const uint64_t *digits, const ui
     LaunchScope ls(c, s, "ks_inner_prod");
     if (fused && acc_p)
         ks_inner_prod_kernel<3, true, true><<<grid, 256, 0, s>>>(digits, own, ep, out, ct, c->d_Pinv, c->d_mod, c->d_redc, (uint32_t)c->N, (uint32_t)l,
-                                                               (uint32_t)lP, (uint32_t)c->size_Q, (uint32_t)c->size_QP, (uint32_t)beta, rg, ib);
+                                                               (uint32_t)lP, (uint32_t)c->size_Q, (uint32_t)c->size_QP, (uint32_t)beta, rg, ib, perm);
     else if (fused)
         ks_inner_prod_kernel<3, true><<<grid, 256, 0, s>>>(digits, own, ep, out, ct, c->d_Pinv, c->d_mod, c->d_redc, (uint32_t)c->N, (uint32_t)l, (uint32_t)lP,
-                                                         (uint32_t)c->size_Q, (uint32_t)c->size_QP, (uint32_t)beta, rg, ib);
+                                                         (uint32_t)c->size_Q, (uint32_t)c->size_QP, (uint32_t)beta, rg, ib, perm);
     else
         ks_inner_prod_kernel<3, false><<<grid, 256, 0, s>>>(digits, own, ep, out, nullptr, nullptr, c->d_mod, c->d_redc, (uint32_t)c->N, (uint32_t)l, (uint32_t)lP,
-                                                          (uint32_t)c->size_Q, (uint32_t)c->size_QP, (uint32_t)beta, rg, ib);
+                                                          (uint32_t)c->size_Q, (uint32_t)c->size_QP, (uint32_t)beta, rg, ib, perm);
     LAUNCH_CHECK("ks_inner_prod_kernel");
     return B2_OK;
 }
@@ -1733,10 +1748,10 @@ extern "C" int b2_moddown(b2_ctx *c, size_t l, size_t n_poly, uint64_t *d_cx, ui
 // [2][alpha][N]); their inverse transform, the base conversion with the P^-1-carrying matrix and a
 // forward transform whose epilogue subtracts from ct finish the job. `delta`: 2*l limbs of scratch.
 static int ks_tail_fused(b2_ctx *c, size_t l, const uint64_t *digits, const uint64_t *own, const uint64_t *const *evk, size_t n_evk, uint64_t *ct,
-                         uint64_t *cxP, uint64_t *delta, cudaStream_t s) {
+                         uint64_t *cxP, uint64_t *delta, cudaStream_t s, const uint32_t *perm = nullptr) {
     const LevelPlan &pl = c->plan[l];
     const size_t a = c->size_P;
-    int rc = inner_prod_impl(c, l, digits, own, evk, n_evk, cxP, ct, true, s);
+    int rc = inner_prod_impl(c, l, digits, own, evk, n_evk, cxP, ct, true, s, nullptr, false, 1, nullptr, perm);
     if (rc) return rc;
     rc = run_inv(c, cxP, cxP, pl.jobs_dnf_intt, (uint32_t)(2 * a), 0, c->d_fin_P, s);
     if (rc) return rc;
@@ -2295,12 +2310,11 @@ extern "C" int b2_hoist_rotations(b2_ctx *c, size_t l, const uint64_t *d_ct, con
         if (!d_outs[i]) return fail(B2_EINVAL, "hoist_rotations: null output");
         rc = gather_impl(c, perms[i], d_ct, pc0, l, s);
         if (rc) return rc;
-        rc = gather_impl(c, perms[i], up, pup, beta * lP, s);  // permute AFTER ModUp (src/evaluate.cu:2041-2045)
-        if (rc) return rc;
-        // c0_out = perm(c0) + ModDown(cx0); c1_out = ModDown(cx1)
+        // c0_out = perm(c0) + ModDown(cx0); c1_out = ModDown(cx1). The digits are permuted AFTER ModUp
+        // (src/evaluate.cu:2041-2045): the inner product reads them through the permutation, `pup` only serves as delta
         CUDA_TRY(cudaMemcpyAsync(d_outs[i], pc0, S * 8, cudaMemcpyDeviceToDevice, s));
         CUDA_TRY(cudaMemsetAsync(d_outs[i] + S, 0, S * 8, s));
-        rc = ks_tail_fused(c, l, pup, nullptr, ksk + i * n_evk, n_evk, d_outs[i], cx, pup, s);
+        rc = ks_tail_fused(c, l, up, nullptr, ksk + i * n_evk, n_evk, d_outs[i], cx, pup, s, perms[i]);
         if (rc) return rc;
     }
     return B2_OK;
@@ -2322,7 +2336,7 @@ extern "C" int b2_hoisting_sum(b2_ctx *c, size_t l, const uint64_t *d_ct, const 
         if (rc) return rc;
     }
     // ws: t [l] | up [beta][lP] | pup [beta][lP] | accP [2][alpha] + delta [2][l] (the 2*lP limbs of cx) | pc0 [l]
-    uint64_t *t = (uint64_t *)d_ws, *up = t + S, *pup = up + beta * lP * N, *accP = pup + beta * lP * N, *delta = accP + 2 * a * N,
+    uint64_t *t = (uint64_t *)d_ws, *up = t + S, *pup = up + beta * lP * N /* unused: the digits are read through the permutation */, *accP = pup + beta * lP * N, *delta = accP + 2 * a * N,
              *pc0 = accP + 2 * lP * N;
     int rc = modup_impl(c, l, d_ct + S, up, t, true, s);
     if (rc) return rc;
@@ -2331,9 +2345,7 @@ extern "C" int b2_hoisting_sum(b2_ctx *c, size_t l, const uint64_t *d_ct, const 
         if (rc) return rc;
         if (i == 0) CUDA_TRY(cudaMemsetAsync(d_out + S, 0, S * 8, s));
         else if ((rc = b2_poly_op(c, 0, l, d_out, pc0, d_out, stream))) return rc;
-        rc = gather_impl(c, perms[i], up, pup, beta * lP, s);
-        if (rc) return rc;
-        rc = inner_prod_impl(c, l, pup, nullptr, ksk + i * n_evk, n_evk, accP, d_out, true, s, nullptr, i > 0);
+        rc = inner_prod_impl(c, l, up, nullptr, ksk + i * n_evk, n_evk, accP, d_out, true, s, nullptr, i > 0, 1, nullptr, perms[i]);
         if (rc) return rc;
     }
     rc = run_inv(c, accP, accP, pl.jobs_dnf_intt, (uint32_t)(2 * a), 0, c->d_fin_P, s);
