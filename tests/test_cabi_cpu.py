@@ -113,3 +113,16 @@ def test_key_sampling_uses_a_cryptographic_generator():
     assert set(np.unique(a.choice(np.array([-1, 1]), size=256))) == {-1, 1}
     s1, s2 = keys._rng_pair(7)   # the reproducible test hook
     assert isinstance(s1, np.random.Generator) and s1.integers(0, 10, 4).tolist() == keys._rng_pair(7)[0].integers(0, 10, 4).tolist()
+
+
+def test_batched_wrappers_check_their_arguments_before_any_device_call():
+    """relinearize_batch and multiply_relin_rescale_batch want contiguous [batch][3 or 2][limbs][N] tensors: a wrong shape is a
+    ValueError raised on the host (no GPU needed to see it)"""
+    import torch
+    import pyPhantom as ph
+    with pytest.raises(ValueError, match="contiguous"):
+        ph.relinearize_batch(None, torch.zeros(2, 2, 3, 8, dtype=torch.int64), None)
+    with pytest.raises(ValueError, match="contiguous"):
+        ph.relinearize_batch(None, torch.zeros(2, 3, 3, 8, dtype=torch.int64).transpose(2, 3), None)
+    with pytest.raises(ValueError, match="one shape"):
+        ph.multiply_relin_rescale_batch(None, torch.zeros(2, 2, 3, 8, dtype=torch.int64), torch.zeros(2, 2, 4, 8, dtype=torch.int64), None)

@@ -554,6 +554,12 @@ def test_batched_key_switch_equals_single_ones(case, monkeypatch):
         assert torch.equal(flat[b, :2 * l], want[b]), f"set {b}"
         assert not flat[b, 3 * l].any(), "the gap between sets must stay untouched"
     assert ctx.device_status() == 0
+    # a batch of one takes the single-call path and gives the same limbs
+    one = torch.zeros(1, stride, N, dtype=torch.int64, device="cuda")
+    one[0, :3 * l] = buf[0, :3].reshape(3 * l, N)
+    check(LIB.b2_keyswitch_batch(ctx._h, l, 1, one[0, 2 * l].data_ptr(), stride, kp.ctypes.data, beta, one.data_ptr(), stride,
+                                 wsb.data_ptr(), nbytes, stream()))
+    assert torch.equal(one[0, :2 * l], want[0])
     # a workspace one byte short is refused, as is a stride smaller than the set
     assert LIB.b2_keyswitch_batch(ctx._h, l, batch, flat[0, 2 * l].data_ptr(), stride, kp.ctypes.data, beta, flat.data_ptr(), stride,
                                   wsb.data_ptr(), nbytes - 8, stream()) != 0
