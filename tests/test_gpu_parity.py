@@ -511,20 +511,21 @@ def test_inner_product_inside_the_last_forward_pass(monkeypatch, name, fused):
     assert hashes(ct, N) == case["hashes"]["keyswitch"]
 
 
-@pytest.mark.parametrize("case", ["n16_headline", "n16_wide", "n16_l11", "n13_fallback"])
+@pytest.mark.parametrize("case", ["n16_headline", "n16_wide", "n16_l11", "n16_l5", "n16_l1", "n13_fallback"])
 def test_batched_key_switch_equals_single_ones(case, monkeypatch):
     """b2_keyswitch_batch (every kernel one launch over a batch that shares the key; strided sets) gives, set by set, the limbs
     of b2_keyswitch - at the headline shape also the oracle's - with the stand-alone inner product for the 60-bit limbs and
     with every limb in the fused pass, at a level with a ragged last digit, and where the fused pipeline does not apply
     (N = 2^13: the sets run one after another)"""
-    if case == "n16_l11":
+    if case in ("n16_l11", "n16_l5", "n16_l1"):
         monkeypatch.delenv("B2_KS_FUSED_WIDE", raising=False)  # the default: every limb in the fused pass for batched calls only
     else:
         monkeypatch.setenv("B2_KS_FUSED_WIDE", "1" if case == "n16_wide" else "0")
     if case == "n13_fallback":
         N, bits, special, l, batch = 8192, [55, 40, 41, 42, 43, 44, 45, 46, 58, 59, 60], 3, 7, 3
     else:
-        N, bits, special, l, batch = 65536, [60] + [40] * 23 + [60] * 8, 8, 11 if case == "n16_l11" else 24, 5
+        N, bits, special, batch = 65536, [60] + [40] * 23 + [60] * 8, 8, 5
+        l = {"n16_l11": 11, "n16_l5": 5, "n16_l1": 1}.get(case, 24)  # 5 and 1: a single digit, every Q limb its own
     ctx, o = make_ctx(N, bits, special)
     beta = o.beta(l)
     key = o.synth_key(beta, 5, 10)
