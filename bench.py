@@ -814,7 +814,13 @@ def main():
         LB = max(1, min(int(os.environ.get("B2_SHARD_BATCH", "32")), 32))
         NB = max(4, 2 * n_lanes)
         lanes = sh.make_lanes(n_lanes)
-        wsb = [sh.batch_workspace(LEVEL, LB)[0] for _ in lanes]
+        # four or more workspaces: the staggered pipeline keeps three batches in flight. Peer-writable ones where the ranks can
+        # map one another's memory (the exchanges are then copy-engine pushes, B2_SHARD_EXCHANGE=nccl keeps the all-gathers)
+        n_ws = max(4, n_lanes)
+        wsb = None if os.environ.get("B2_SHARD_EXCHANGE", "peer") == "nccl" else sh.peer_workspaces(LEVEL, LB, n_ws)
+        exchange_kind = "peer copies (DMA) + one-word all-reduce" if wsb is not None else "NCCL all-gather"
+        if wsb is None:
+            wsb = [sh.batch_workspace(LEVEL, LB)[0] for _ in range(n_ws)]
         batches = [(torch.stack([sh_ct3[(i * LB + b) % n_sh_ct][2] for b in range(LB)]),
                     torch.stack([sh_ct3[(i * LB + b) % n_sh_ct][:2] for b in range(LB)])) for i in range(NB)]
         want_b = batches[0][1][0].clone()
@@ -841,17 +847,14 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         us_b = 1e3 * float(t.item()) / (n_pb * NB * LB)
         # the same batches with the exchanges alone (no kernels): what the collectives cost by themselves
-        tviews = [sh._views(LEVEL, LB, w) for w in wsb]
         def exchanges():
-            for i in range(NB):
-                st, grp = lanes[i % n_lanes]
-                st.wait_stream(stream)
-                with torch.cuda.stream(st):
-                    from pyPhantom.parallel import allgather_limbs
-                    allgather_limbs(tviews[i % n_lanes][0], LEVEL, sh.rank, sh.world, grp)
-                    allgather_limbs(tviews[i % n_lanes][1], SPECIAL, sh.rank, sh.world, grp)
-            for st, _ in lanes:
-                stream.wait_stream(st)
+            st, grp = lanes[0]
+            st.wait_stream(stream)
+            with torch.cuda.stream(st):
+                for i in range(NB):
+                    sh.exchange(LEVEL, LB, wsb[i % len(wsb)], 0, grp)
+                    sh.exchange(LEVEL, LB, wsb[i % len(wsb)], 1, grp)
+            stream.wait_stream(st)
         exchanges()
         barrier()
         s0.record(stream)
@@ -862,14 +865,41 @@ def main():
         t = torch.tensor([s0.elapsed_time(s1)], device="cuda")
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         us_x = 1e3 * float(t.item()) / (n_pb * NB * LB)
+        # and the kernels alone (the three phases without the exchanges between them: results are not used): with both in
+        # hand one reads how much of the shorter one the lanes hide
+        def kernels_only():
+            for i in range(NB):
+                st, _ = lanes[i % n_lanes]
+                st.wait_stream(stream)
+                with torch.cuda.stream(st):
+                    c2_b, ct_b = batches[i]
+                    w = wsb[i % len(wsb)]
+                    for ph_i in (0, 1, 2):
+                        sh.phase_batch(LEVEL, ph_i, LB, c2_b, key_sh_tab, ct_b, w, w.numel() * 8)
+            for st, _ in lanes:
+                stream.wait_stream(st)
+        kernels_only()
+        barrier()
+        s0.record(stream)
+        for _ in range(n_pb):
+            kernels_only()
+        s1.record(stream)
+        barrier()
+        t = torch.tensor([s0.elapsed_time(s1)], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        us_k = 1e3 * float(t.item()) / (n_pb * NB * LB)
         rx = int((LEVEL + 2 * SPECIAL) * LIMB_BYTES * (1 - 1 / world))
         limb_sharded = {"verified": True, "ranks": world, "keyswitch_per_s": 1e6 / us_b, "us_per_keyswitch": us_b,
-                        "batch_per_lane": LB, "batches_in_flight": NB, "lanes": n_lanes,
+                        "batch_per_lane": LB, "batches_in_flight": NB, "lanes": n_lanes, "exchange": exchange_kind,
                         "one_ciphertext_latency_us": us_one,
                         "nvlink_bytes_received_per_gpu_per_keyswitch": rx,
                         "nvlink_gbs_per_gpu": rx / (us_b * 1e-6) / 1e9, "nvlink_frac_of_900": rx / (us_b * 1e-6) / 1e9 / 900.0,
-                        "collectives_alone_us_per_keyswitch": us_x, "collectives_share": us_x / us_b,
+                        "kernels_alone_us_per_keyswitch": us_k, "collectives_alone_us_per_keyswitch": us_x, "collectives_share": us_x / us_b,
                         "note": "every ciphertext's limbs are spread over all ranks (the weak-scaling value above is data parallel)"}
+        barrier()
+        for w in wsb:
+            if hasattr(w, "close"):
+                w.close()
 
     # ---- per-kernel timing (live, CUDA events on the launching stream) and roofline -------------
     roofline, roofline_issue, kernels = None, None, None

@@ -292,6 +292,16 @@ int b2_shard_keyswitch_phase(b2_ctx *ctx, size_t size_Ql, int phase, const uint6
                              const uint64_t *const *evk, size_t n_evk, uint64_t *d_ct, void *d_ws,
                              size_t ws_bytes, void *stream);
 
+/* Exchange buffers for the limb-sharded pipeline on one node (no counterpart in the reference): device memory with a 64-byte
+ * CUDA IPC handle (b2_peer_alloc), a peer's mapping of it (b2_peer_open / b2_peer_close), and an asynchronous copy into it on
+ * a stream (b2_peer_copy: DMA over NVLink, no kernel). The caller orders a consumer after every peer's copies (a collective
+ * barrier on the same stream does). */
+int b2_peer_alloc(size_t bytes, void **d_ptr, uint8_t *handle64);
+int b2_peer_open(const uint8_t *handle64, void **d_ptr);
+int b2_peer_close(void *d_ptr);
+int b2_peer_free(void *d_ptr);
+int b2_peer_copy(void *d_dst, const void *d_src, size_t bytes, void *stream);
+
 /* The same three phases for `batch` ciphertexts at once, all switched with one key: d_c2 [batch][size_Ql][N], d_ct
  * [batch][2][size_Ql][N]. Every kernel of a phase is one launch over the whole batch, so a rank that owns an eighth of the
  * limbs still fills its GPU. Workspace (b2_shard_batch_workspace_bytes), in limbs of N words:

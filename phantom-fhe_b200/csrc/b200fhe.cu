@@ -2842,6 +2842,54 @@ extern "C" int b2_shard_keyswitch_phase(b2_ctx *c, size_t l, int phase, const ui
     }
 }
 
+// Exchange buffers that the other ranks of one node can write: device memory with a CUDA IPC handle, the peers' mappings of
+// it, and plain asynchronous copies into them. The limb-sharded pipeline pushes a rank's block of the exchanged limbs into every
+// peer's buffer with these copies (DMA engines over NVLink, no SM involved, so they overlap the transforms of other batches),
+// where an all-gather kernel would compete with those transforms for SMs. No kernel of this library reads or writes peer
+// memory; nothing here waits on the device.
+extern "C" int b2_peer_alloc(size_t bytes, void **d_ptr, uint8_t *handle64) {
+    if (!d_ptr || !handle64 || bytes == 0) return fail(B2_EINVAL, "peer_alloc: bad argument");
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "the handle travels as 64 bytes");
+    CUDA_TRY(cudaMalloc(d_ptr, bytes));
+    cudaIpcMemHandle_t h;
+    cudaError_t e = cudaIpcGetMemHandle(&h, *d_ptr);
+    if (e != cudaSuccess) {
+        cudaFree(*d_ptr);
+        *d_ptr = nullptr;
+        return fail((int)e, std::string("peer_alloc: cudaIpcGetMemHandle: ") + cudaGetErrorString(e));
+    }
+    memcpy(handle64, &h, 64);
+    return B2_OK;
+}
+
+extern "C" int b2_peer_open(const uint8_t *handle64, void **d_ptr) {
+    if (!handle64 || !d_ptr) return fail(B2_EINVAL, "peer_open: null pointer");
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle64, 64);
+    CUDA_TRY(cudaIpcOpenMemHandle(d_ptr, h, cudaIpcMemLazyEnablePeerAccess));
+    return B2_OK;
+}
+
+extern "C" int b2_peer_close(void *d_ptr) {
+    if (!d_ptr) return B2_OK;
+    CUDA_TRY(cudaIpcCloseMemHandle(d_ptr));
+    return B2_OK;
+}
+
+extern "C" int b2_peer_free(void *d_ptr) {
+    if (!d_ptr) return B2_OK;
+    CUDA_TRY(cudaFree(d_ptr));
+    return B2_OK;
+}
+
+// bytes from this GPU's memory into a peer's mapped buffer (or any two device addresses of the process), on `stream`
+extern "C" int b2_peer_copy(void *d_dst, const void *d_src, size_t bytes, void *stream) {
+    if (!d_dst || !d_src) return fail(B2_EINVAL, "peer_copy: null pointer");
+    if (bytes == 0) return B2_OK;
+    CUDA_TRY(cudaMemcpyAsync(d_dst, d_src, bytes, cudaMemcpyDefault, (cudaStream_t)stream));
+    return B2_OK;
+}
+
 extern "C" size_t b2_shard_batch_workspace_bytes(const b2_ctx *c, size_t l, size_t batch) {
     if (!c || l < 1 || l > c->size_Q || batch < 1) return 0;
     const size_t a = c->size_P, beta = (l + a - 1) / a, lP = l + a;

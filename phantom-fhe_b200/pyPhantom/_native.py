@@ -37,6 +37,11 @@ SIGNATURES = {
     "b2_special_fft": (_int, [_vp, _vp, _vp, _vp, _vp, _int, ctypes.c_double, _vp]),
     "b2_encode_round": (_int, [_vp, _vp, _vp, _vp]),
     "b2_decode_compose": (_int, [_vp, _sz, _vp, _vp, ctypes.c_double, _vp, _vp]),
+    "b2_peer_alloc": (_int, [_sz, ctypes.POINTER(_vp), _vp]),
+    "b2_peer_open": (_int, [_vp, ctypes.POINTER(_vp)]),
+    "b2_peer_close": (_int, [_vp]),
+    "b2_peer_free": (_int, [_vp]),
+    "b2_peer_copy": (_int, [_vp, _vp, _sz, _vp]),
     "b2_sample": (_int, [_vp, _int, _vp, _vp, _sz, _sz, _vp, _vp]),
     "b2_tensor_mul": (_int, [_vp, _sz, _vp, _vp, _vp, _vp]),
     "b2_multiply_and_relin": (_int, [_vp, _sz, _vp, _vp, _vp, _sz, _vp, _vp, _sz, _vp]),

@@ -10,6 +10,8 @@ independent engine per GPU from Python threads, python/llm_project/mrpc_sweep_pa
   two all-gathers (the l scaled coefficient-form limbs of ModUp, the 2*alpha P limbs of ModDown).
   The exchanged limbs land in local HBM first; kernels only ever read local memory.
 """
+import ctypes
+
 import numpy as np
 import torch
 import torch.distributed as dist
@@ -98,6 +100,57 @@ class LimbShardedKeySwitch:
             allgather_limbs(ct[k], l, self.rank, self.world, self.group)
 
 
+class PeerWorkspace:
+    """A batch workspace of the limb-sharded pipeline that the other ranks of the node can write into: device memory with a
+    CUDA IPC handle (b2_peer_alloc) and, after `connect`, every peer's mapping of its own. `push` copies a block of this
+    rank's buffer to the same offset of every peer's with plain asynchronous copies (DMA over NVLink: no SM, so they run
+    beside the kernels of other batches). Collective: every rank creates and connects the same number of them in the same
+    order."""
+
+    def __init__(self, nbytes):
+        self.nbytes = int(nbytes)
+        p, h = ctypes.c_void_p(), (ctypes.c_uint8 * 64)()
+        check(LIB.b2_peer_alloc(self.nbytes, ctypes.byref(p), h))
+        self.ptr, self.handle = int(p.value), bytes(h)
+        self.peers = None  # device addresses of every rank's buffer as mapped into this process (own one included)
+
+    def data_ptr(self):
+        return self.ptr
+
+    def numel(self):
+        return self.nbytes // 8
+
+    def connect(self, rank, world, group=None):
+        handles = [None] * world
+        dist.all_gather_object(handles, self.handle, group=group)
+        self.peers = []
+        for r, h in enumerate(handles):
+            if r == rank:
+                self.peers.append(self.ptr)
+            else:
+                p = ctypes.c_void_p()
+                check(LIB.b2_peer_open((ctypes.c_uint8 * 64).from_buffer_copy(h), ctypes.byref(p)))
+                self.peers.append(int(p.value))
+        self.rank = rank
+        return self
+
+    def push(self, offset_bytes, nbytes, stream):
+        """this rank's bytes [offset, offset + nbytes) into every peer's buffer at the same offset"""
+        for r, base in enumerate(self.peers):
+            if r != self.rank and nbytes:
+                check(LIB.b2_peer_copy(base + offset_bytes, self.ptr + offset_bytes, nbytes, stream))
+
+    def close(self):
+        if self.peers:
+            for r, base in enumerate(self.peers):
+                if r != self.rank:
+                    LIB.b2_peer_close(base)
+            self.peers = None
+        if self.ptr:
+            LIB.b2_peer_free(self.ptr)
+            self.ptr = 0
+
+
 class BatchedLimbShardedKeySwitch(LimbShardedKeySwitch):
     """A batch of ciphertexts, all switched with one key, with their limbs spread over the ranks.
 
@@ -110,6 +163,39 @@ class BatchedLimbShardedKeySwitch(LimbShardedKeySwitch):
     def batch_workspace(self, l, batch):
         nbytes = int(LIB.b2_shard_batch_workspace_bytes(self.ctx._h, l, batch))
         return torch.empty(nbytes // 8, dtype=torch.int64, device=torch.device("cuda", self.ctx.device)), nbytes
+
+    def peer_workspaces(self, l, batch, count):
+        """`count` batch workspaces whose exchange blocks the peers push into directly (`pipeline` then needs no all-gather
+        kernel); None when the ranks cannot map one another's memory (the caller falls back to `batch_workspace`).
+        Collective: every rank must call it."""
+        nbytes = int(LIB.b2_shard_batch_workspace_bytes(self.ctx._h, l, batch))
+        made, ok = [], 1
+        try:
+            for _ in range(count):
+                made.append(PeerWorkspace(nbytes))
+        except ValueError:
+            ok = 0
+        flag = torch.tensor([ok], device=torch.device("cuda", self.ctx.device))
+        if self.world > 1:
+            dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=self.group)
+        if int(flag.item()) != 1:
+            for w in made:
+                w.close()
+            return None
+        try:
+            for w in made:
+                w.connect(self.rank, self.world, self.group)
+            ok = 1
+        except ValueError:
+            ok = 0
+        flag.fill_(ok)
+        if self.world > 1:
+            dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=self.group)
+        if int(flag.item()) != 1:
+            for w in made:
+                w.close()
+            return None
+        return made
 
     def _views(self, l, batch, ws):
         N, a = self.ctx.N, self.ctx.size_P
@@ -139,11 +225,35 @@ class BatchedLimbShardedKeySwitch(LimbShardedKeySwitch):
         """(stream, process group) pairs for `pipeline`: every lane has its own communicator, so that collectives of
         different lanes do not queue behind one another. Collective: every rank must call it."""
         ranks = list(range(self.world))
-        return [(torch.cuda.Stream(), dist.new_group(ranks) if self.world > 1 else None) for _ in range(n_lanes)]
+        import os
+        pri = -1 if os.environ.get("B2_SHARD_COMM_PRIORITY", "1") == "1" else 0
+        return [(torch.cuda.Stream(priority=pri), dist.new_group(ranks) if self.world > 1 else None) for _ in range(n_lanes)]
 
-    def pipeline(self, l, batches, key, lanes, workspaces):
+    def exchange(self, l, batch, ws, which, group=None):
+        """One exchange of a batch on the current stream. which = 0: the scaled coefficient-form limbs T [l][batch][N] after
+        phase 0; 1: the P limbs CXP [alpha][2][batch][N] after phase 1. A tensor workspace goes through one NCCL all-gather; a
+        PeerWorkspace pushes this rank's block into every peer's buffer with asynchronous copies and then joins a one-word
+        all-reduce: a rank queues its copies before its contribution, so when the reduction completes here every peer's block
+        has landed, and the kernels that read the blocks are ordered after it."""
+        a = self.ctx.size_P
+        if not isinstance(ws, PeerWorkspace):
+            return allgather_limbs(self._views(l, batch, ws)[which], a if which else l, self.rank, self.world, group)
+        limb = self.ctx.N * 8
+        first, cnt = limb_range(a if which else l, self.rank, self.world)
+        row = (2 * batch if which else batch) * limb
+        base = l * batch * limb if which else 0
+        ws.push(base + first * row, cnt * row, torch.cuda.current_stream().cuda_stream)
+        if self.world > 1:
+            if not hasattr(self, "_xflag"):
+                self._xflag = torch.zeros(1, dtype=torch.int32, device=torch.device("cuda", self.ctx.device))
+            dist.all_reduce(self._xflag, group=group)
+
+    def pipeline_lanes(self, l, batches, key, lanes, workspaces):
         """batches: list of (c2, ct); batch i runs on lane i % len(lanes) with that lane's workspace. Returns after
-        queueing everything; the caller's stream waits for every lane."""
+        queueing everything; the caller's stream waits for every lane. (The lanes start in step and stay in step - all
+        of them compute, then all of them exchange - so this form hides little of the exchanges; `pipeline` staggers.)"""
+        if isinstance(workspaces[0], PeerWorkspace):
+            raise ValueError("peer workspaces go with the staggered pipeline: pass four or more")
         main = torch.cuda.current_stream()
         for st, _ in lanes:
             st.wait_stream(main)
@@ -153,3 +263,56 @@ class BatchedLimbShardedKeySwitch(LimbShardedKeySwitch):
                 self.keyswitch_batch(l, c2, key, ct, workspaces[i % len(lanes)], grp)
         for st, _ in lanes:
             main.wait_stream(st)
+
+    def pipeline(self, l, batches, key, lanes, workspaces):
+        """Software pipeline over the batches: all kernels go to the caller's stream in the order
+        phase 0 of batch s, phase 1 of batch s - 1, phase 2 of batch s - 3 (s = 0, 1, ..), and the two exchanges of a batch go
+        to the communication lane (lanes[0]: a stream and its communicator) as soon as the phase that feeds them is queued.
+        An exchange thus has the kernels of the neighbouring batches to hide behind - the first one phases 1 and 2 of other
+        batches, the second one two steps' worth - instead of every lane exchanging at the same moment. Batch i uses
+        workspace i % len(workspaces); four or more workspaces are needed (three batches are in flight), else the lanes form
+        is used. Returns after queueing everything; the caller's stream has waited for the last exchange."""
+        D = len(workspaces)
+        if D < 4 or len(batches) < 2:
+            return self.pipeline_lanes(l, batches, key, lanes, workspaces)
+        cs = torch.cuda.current_stream()
+        ms, grp = lanes[0]
+        ms.wait_stream(cs)
+        NB = len(batches)
+        tab = key.pointer_table()
+        LB = batches[0][0].shape[0]
+        ev_p0 = [torch.cuda.Event() for _ in range(NB)]
+        ev_p1 = [torch.cuda.Event() for _ in range(NB)]
+        ev_x1 = [torch.cuda.Event() for _ in range(NB)]
+        ev_x2 = [torch.cuda.Event() for _ in range(NB)]
+
+        def exchange(i, which):
+            self.exchange(l, LB, workspaces[i % D], which, grp)
+
+        def phase(i, ph):
+            c2, ct = batches[i]
+            w = workspaces[i % D]
+            self.phase_batch(l, ph, c2.shape[0], c2, tab, ct, w, w.numel() * 8)
+
+        for s in range(NB + 3):
+            if s < NB:                      # phase 0 of batch s, then its first exchange on the communication lane
+                phase(s, 0)
+                ev_p0[s].record(cs)
+                with torch.cuda.stream(ms):
+                    ms.wait_event(ev_p0[s])
+                    exchange(s, 0)
+                    ev_x1[s].record(ms)
+            i = s - 1
+            if 0 <= i < NB:                 # phase 1 of batch s - 1, then its second exchange
+                cs.wait_event(ev_x1[i])
+                phase(i, 1)
+                ev_p1[i].record(cs)
+                with torch.cuda.stream(ms):
+                    ms.wait_event(ev_p1[i])
+                    exchange(i, 1)
+                    ev_x2[i].record(ms)
+            i = s - 3
+            if 0 <= i < NB:                 # phase 2 of batch s - 3
+                cs.wait_event(ev_x2[i])
+                phase(i, 2)
+        cs.wait_stream(ms)

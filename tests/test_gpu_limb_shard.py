@@ -12,6 +12,7 @@ import torch
 
 pytestmark = pytest.mark.gpu
 
+import pyPhantom as ph
 from pyPhantom import _native
 from pyPhantom._native import LIB, check
 from gpu_helpers import dev, host, key_dev, make_ctx, stream
@@ -85,6 +86,34 @@ def test_emulated_ranks_reproduce_a_batch_of_key_switches(world, batch, shape):
     assert ctx.device_status() == 0
 
 
+def test_staggered_pipeline_schedule_on_one_rank():
+    """the software pipeline of BatchedLimbShardedKeySwitch.pipeline (phase 0 of batch s, phase 1 of batch s - 1, phase 2 of
+    batch s - 3 on one stream, exchanges on a second) with a world of one rank: seven batches through five workspaces, twice,
+    every ciphertext equal to the single key switch"""
+    from pyPhantom.parallel import BatchedLimbShardedKeySwitch
+    N, l, B, n_batches = 8192, 7, 3, 7
+    ctx, o = make_ctx(N, [58, 40, 40, 40, 40, 40, 40, 60, 60, 60], 3)
+    key_h = o.synth_key(o.beta(l), 71, 10)
+    key = ph.relin_key.from_numpy(ctx, key_h)
+    bs = BatchedLimbShardedKeySwitch(ctx, rank=0, world=1)
+    lanes = bs.make_lanes(1)
+    wss = [bs.batch_workspace(l, B)[0] for _ in range(5)]
+    c2s = [np.stack([o.fill(1, o.primes[:l], 75, 100 * i + b)[0] for b in range(B)]) for i in range(n_batches)]
+    cts = [np.stack([o.synth_ct(l, 75, 1000 + 100 * i + b) for b in range(B)]) for i in range(n_batches)]
+    kt, kp = key_dev(key_h)
+    ws1, nb1 = ctx.workspace(_native.OP_KEYSWITCH, l)
+    for rep in range(2):
+        batches = [(dev(a), dev(b)) for a, b in zip(c2s, cts)]
+        bs.pipeline(l, batches, key, lanes, wss)
+        torch.cuda.synchronize()
+        for i, (c2d, ctd) in enumerate(batches):
+            for b in range(B):
+                one = dev(cts[i][b])
+                check(LIB.b2_keyswitch(ctx._h, l, c2d[b].data_ptr(), kp.ctypes.data, o.beta(l), one.data_ptr(), ws1.data_ptr(), nb1, stream()))
+                assert torch.equal(ctd[b], one), (rep, i, b)
+    assert ctx.device_status() == 0
+
+
 def test_shard_argument_checks():
     ctx, o = make_ctx(4096, [40, 40, 50], 1)
     x = ctx.empty(2, 2)
@@ -119,22 +148,33 @@ c2, ct = dev(c2_h), dev(ct_h)
 sh.keyswitch(l, c2, key, ct)
 sh.allgather_ct(l, ct)
 ok = np.array_equal(host(ct), o.keyswitch(l, c2_h, key_h, ct_h))
-# batches of three on two lanes (own stream and communicator each), four batches in flight
+# batches of three: on two lanes (own stream and communicator each: two workspaces select that form), and as the staggered
+# software pipeline (five workspaces, seven batches: workspaces are reused while three batches are in flight), twice in a row
 from pyPhantom.parallel import BatchedLimbShardedKeySwitch
 bs = BatchedLimbShardedKeySwitch(ctx)
 lanes = bs.make_lanes(2)
-B, n_batches = 3, 4
-c2s = [np.stack([o.fill(1, o.primes[:l], 72, 100 * i + b)[0] for b in range(B)]) for i in range(n_batches)]
-cts = [np.stack([o.synth_ct(l, 72, 1000 + 100 * i + b) for b in range(B)]) for i in range(n_batches)]
-batches = [(dev(a), dev(b)) for a, b in zip(c2s, cts)]
-wss = [bs.batch_workspace(l, B)[0] for _ in lanes]
-bs.pipeline(l, batches, key, lanes, wss)
-torch.cuda.synchronize()
-for i, (c2d, ctd) in enumerate(batches):
-    for b in range(B):
-        one = ctd[b]
-        bs.allgather_ct(l, one)
-        ok = ok and np.array_equal(host(one), o.keyswitch(l, c2s[i][b], key_h, cts[i][b]))
+B = 3
+# and the staggered pipeline once more on peer-writable workspaces (exchanges as copy-engine pushes + a one-word all-reduce)
+for n_ws, n_batches, repeats, peer in ((2, 4, 1, False), (5, 7, 2, False), (4, 9, 2, True)):
+    c2s = [np.stack([o.fill(1, o.primes[:l], 72 + n_ws, 100 * i + b)[0] for b in range(B)]) for i in range(n_batches)]
+    cts = [np.stack([o.synth_ct(l, 72 + n_ws, 1000 + 100 * i + b) for b in range(B)]) for i in range(n_batches)]
+    wss = bs.peer_workspaces(l, B, n_ws) if peer else [bs.batch_workspace(l, B)[0] for _ in range(n_ws)]
+    if wss is None:
+        print("peer workspaces unavailable: skipped", flush=True)
+        continue
+    for rep in range(repeats):
+        batches = [(dev(a), dev(b)) for a, b in zip(c2s, cts)]
+        bs.pipeline(l, batches, key, lanes, wss)
+        torch.cuda.synchronize()
+        for i, (c2d, ctd) in enumerate(batches):
+            for b in range(B):
+                one = ctd[b]
+                bs.allgather_ct(l, one)
+                ok = ok and np.array_equal(host(one), o.keyswitch(l, c2s[i][b], key_h, cts[i][b]))
+    if peer:
+        dist.barrier()
+        for w in wss:
+            w.close()
 ok = ok and ctx.device_status() == 0
 t = torch.tensor([1 if ok else 0], device="cuda"); dist.all_reduce(t, op=dist.ReduceOp.MIN)
 dist.destroy_process_group()
