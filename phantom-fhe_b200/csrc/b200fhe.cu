@@ -1830,6 +1830,7 @@ static int modup_inner_fused(b2_ctx *c, size_t l, const uint64_t *c2, const uint
             m.first_limb = wide ? 0 : pl.n_wideQ, m.p_first = wide ? (uint32_t)c->size_P : 0, m.acc_p = acc_p ? 1 : 0;
             m.interleave = c->mac_interleave ? 1 : 0;
             m.dig_bs = per, m.own_bs = kb.c2_bs, m.ct_bs = kb.ct_bs, m.cxp_bs = a2;
+            m.p_off = 0, m.cxp_i = 1, m.cxp_k = (uint32_t)c->size_P;
             const uint32_t n_limbs = (uint32_t)l - m.first_limb + m.p_first;
             LaunchScope ls(c, s, "ntt_fwd_rows_mac");
             static_assert(Cfg::R_STRIDED == Cfg::R_CONTIG, "the fused pass wants equal stage groups");
@@ -2926,12 +2927,44 @@ extern "C" int b2_shard_keyswitch_phase_batch(b2_ctx *c, size_t l, int phase, si
                 rc = run_bconv_tc(c, false, T, UP, nullptr, sp.tc_up, sp.tc_up.n_jobs, s, &tb);
                 if (rc) return rc;
             }
-            rc = run_fwd(c, UP, UP, sp.jobs_up_ntt, sp.n_up_ntt, 0, EpiStore{}, s, 0, 0, 0, BatchDims{B, 0, per, 0, per});
-            if (rc) return rc;
-            const uint4 rg = make_uint4(sp.q0, sp.nq, sp.p0, sp.np);
-            const IpBatch ib{per, (uint32_t)l, (uint32_t)(2 * l), 2, 1, B - 1, 1};
-            rc = inner_prod_impl(c, l, UP, d_c2, evk, n_evk, CXP, d_ct, true, s, &rg, false, B, &ib);
-            if (rc) return rc;
+            const bool fused = c->use_mac && beta <= B2_MAC_MAX_BETA && n_evk >= beta && (sp.nq + sp.np) > 0;
+            if (fused) {
+                // column pass of the rank's digit limbs, then the row pass with the inner product inside it (every limb of the
+                // rank's slice: its P limbs first), as the one-GPU batched key switch does; the P limbs go straight into the
+                // limb-major exchange buffer
+                using Cfg = PassCfg<8>;
+                NttArgs na{UP, UP, sp.jobs_up_ntt, 0, (uint32_t)c->logN, c->d_tw, c->d_mod, nullptr, 0};
+                na.src_bs = na.dst_bs = per;
+                if (sp.n_up_ntt) {
+                    LaunchScope ls(c, s, "ntt_fwd_cols");
+                    ntt_fwd_pass<8, Cfg::R_STRIDED, Cfg::R_CONTIG, Cfg::LOG_CC, true, false, EpiStore>
+                        <<<dim3(sp.n_up_ntt * (uint32_t)(N >> (8 + Cfg::LOG_CC)), B), pass_threads<8, true>(), 0, s>>>(na, EpiStore{});
+                    LAUNCH_CHECK("ntt_fwd_pass");
+                }
+                MacArgs m{};
+                m.own = d_c2;
+                for (size_t d = 0; d < beta; d++) {
+                    if (!evk[d]) return fail(B2_EINVAL, "null evaluation-key digit");
+                    m.evk[d] = evk[d];
+                }
+                m.ct = d_ct, m.cxp = CXP, m.pinv = c->d_Pinv, m.fin = c->d_macfin;
+                m.l = (uint32_t)l, m.lP = (uint32_t)lP, m.alpha = (uint32_t)a, m.beta = (uint32_t)beta;
+                m.size_Q = (uint32_t)c->size_Q, m.size_QP = (uint32_t)c->size_QP;
+                m.first_limb = sp.q0, m.p_first = sp.np, m.p_off = sp.p0, m.acc_p = 0, m.interleave = 0;
+                m.dig_bs = per, m.own_bs = (uint32_t)l, m.ct_bs = (uint32_t)(2 * l);
+                m.cxp_i = 2 * B, m.cxp_k = B, m.cxp_bs = 1;
+                LaunchScope ls(c, s, "ntt_fwd_rows_mac");
+                ntt_fwd_rows_mac<8, Cfg::R_CONTIG, Cfg::LOG_C>
+                    <<<dim3(B, (sp.nq + sp.np) * (uint32_t)(N >> (8 + Cfg::LOG_C))), pass_threads<8>(), mac_smem_bytes<8, Cfg::R_CONTIG, Cfg::LOG_C>(), s>>>(na, m);
+                LAUNCH_CHECK("ntt_fwd_rows_mac");
+            } else {
+                rc = run_fwd(c, UP, UP, sp.jobs_up_ntt, sp.n_up_ntt, 0, EpiStore{}, s, 0, 0, 0, BatchDims{B, 0, per, 0, per});
+                if (rc) return rc;
+                const uint4 rg = make_uint4(sp.q0, sp.nq, sp.p0, sp.np);
+                const IpBatch ib{per, (uint32_t)l, (uint32_t)(2 * l), 2, 1, B - 1, 1};
+                rc = inner_prod_impl(c, l, UP, d_c2, evk, n_evk, CXP, d_ct, true, s, &rg, false, B, &ib);
+                if (rc) return rc;
+            }
             return run_inv(c, CXP, CXP, sp.jobs_dn_intt_b, 2 * sp.np, 0, c->d_fin_P, s, BatchDims{B, B - 1, 1, B - 1, 1});
         }
         case 2: {

@@ -474,6 +474,10 @@ struct MacArgs {
     // b * dig_bs / own_bs / ct_bs / cxp_bs limbs further
     uint32_t dig_bs, own_bs, ct_bs, cxp_bs;  // (with the sets as the slow dimension instead the pass took 30.7 instead of 27.8 us per key switch)
     uint32_t p_first, first_limb;          // the grid covers p_first P limbs, then the Q limbs from first_limb on
+    uint32_t p_off;                        // index of the first of those P limbs (a rank's slice under limb sharding; else 0)
+    // P limb i of polynomial k of set b lands at limb slot i * cxp_i + k * cxp_k + b * cxp_bs of cxp: [set][2][alpha] is
+    // (1, alpha, 2 alpha), the limb-major exchange buffer [alpha][2][sets] is (2 sets, sets, 1)
+    uint32_t cxp_i, cxp_k;
 };
 
 __device__ __forceinline__ u64x4 ld256_cs(const uint64_t *p) {  // streaming: the key is read once
@@ -640,7 +644,7 @@ __device__ __forceinline__ void mac_body(const NttArgs &a, const MacArgs &m, uin
         // a P limb: kept (or, acc_p, added to what is there) in the compact buffer [2][alpha][N] for the ModDown that
         // follows; the closing constant of an integer prime is 2^64 mod p
         const W2 fin = m.fin[pp];
-        uint64_t *p0 = m.cxp + ((size_t)bset * m.cxp_bs + (t - m.l)) * N + o, *p1 = p0 + (size_t)m.alpha * N;
+        uint64_t *p0 = m.cxp + ((size_t)bset * m.cxp_bs + (size_t)(t - m.l) * m.cxp_i) * N + o, *p1 = p0 + (size_t)m.cxp_k * N;
 #pragma unroll
         for (int i = 0; i < E; i += 4) {
             uint64_t r[4], s[4];
@@ -672,7 +676,7 @@ __global__ void __launch_bounds__((1 << (LOG_C + LOG_T)) >> R, 3) ntt_fwd_rows_m
     // the P limbs (60-bit primes: the long CTAs) go first so that they do not form the tail of the grid
     const uint32_t n_limbs = gridDim.y / tiles, bset = blockIdx.x;
     const uint32_t i = m.interleave ? blockIdx.y % n_limbs : blockIdx.y / tiles, tile = m.interleave ? blockIdx.y / n_limbs : blockIdx.y % tiles;
-    const uint32_t t = i < m.p_first ? m.l + i : m.first_limb + (i - m.p_first);
+    const uint32_t t = i < m.p_first ? m.l + m.p_off + i : m.first_limb + (i - m.p_first);
     const uint32_t pp = t < m.l ? t : m.size_Q + (t - m.l);  // the limb's prime
     const Mod md = a.mod[pp];
     if (md.q < FP_LIMIT) mac_body<ArithFp, LOG_T, R, LOG_C>(a, m, sm, kb, t, pp, tile, bset, md);

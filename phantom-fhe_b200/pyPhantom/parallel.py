@@ -134,11 +134,32 @@ class PeerWorkspace:
         self.rank = rank
         return self
 
-    def push(self, offset_bytes, nbytes, stream):
-        """this rank's bytes [offset, offset + nbytes) into every peer's buffer at the same offset"""
-        for r, base in enumerate(self.peers):
-            if r != self.rank and nbytes:
-                check(LIB.b2_peer_copy(base + offset_bytes, self.ptr + offset_bytes, nbytes, stream))
+    def push(self, offset_bytes, nbytes, stream=None):
+        """this rank's bytes [offset, offset + nbytes) into every peer's buffer at the same offset, ordered after the work
+        queued on the current stream and before what is queued on it next. One copy per peer, spread over a few side streams
+        so that several copy engines drive the links at once (one stream of seven copies in a row reached 210 GB/s on eight
+        B200s)."""
+        if not nbytes or len(self.peers) < 2:
+            return
+        cur = torch.cuda.current_stream()
+        if len(self.peers) == 2:
+            r = 1 - self.rank
+            check(LIB.b2_peer_copy(self.peers[r] + offset_bytes, self.ptr + offset_bytes, nbytes, cur.cuda_stream))
+            return
+        if not hasattr(self, "_side"):
+            self._side = [torch.cuda.Stream() for _ in range(min(len(self.peers) - 1, 4))]
+        start = torch.cuda.Event()
+        start.record(cur)
+        others = [(self.rank + 1 + k) % len(self.peers) for k in range(len(self.peers) - 1)]  # start with the next rank: no hot spot
+        for k, r in enumerate(others):
+            st = self._side[k % len(self._side)]
+            if k < len(self._side):
+                st.wait_event(start)
+            check(LIB.b2_peer_copy(self.peers[r] + offset_bytes, self.ptr + offset_bytes, nbytes, st.cuda_stream))
+        for st in self._side:
+            done = torch.cuda.Event()
+            done.record(st)
+            cur.wait_event(done)
 
     def close(self):
         if self.peers:
@@ -242,7 +263,7 @@ class BatchedLimbShardedKeySwitch(LimbShardedKeySwitch):
         first, cnt = limb_range(a if which else l, self.rank, self.world)
         row = (2 * batch if which else batch) * limb
         base = l * batch * limb if which else 0
-        ws.push(base + first * row, cnt * row, torch.cuda.current_stream().cuda_stream)
+        ws.push(base + first * row, cnt * row)
         if self.world > 1:
             if not hasattr(self, "_xflag"):
                 self._xflag = torch.zeros(1, dtype=torch.int32, device=torch.device("cuda", self.ctx.device))
