@@ -817,7 +817,10 @@ def main():
         # four or more workspaces: the staggered pipeline keeps three batches in flight. Peer-writable ones where the ranks can
         # map one another's memory (the exchanges are then copy-engine pushes, B2_SHARD_EXCHANGE=nccl keeps the all-gathers)
         n_ws = max(4, n_lanes)
-        wsb = None if os.environ.get("B2_SHARD_EXCHANGE", "peer") == "nccl" else sh.peer_workspaces(LEVEL, LB, n_ws)
+        # (measured on B200s: pushes win at 2 and 4 ranks, 10380 vs 9680 and 19250 vs 16810 KeySwitch/s; at 8 ranks seven DMA
+        # copies per exchange reach 420 GB/s where the all-gather reaches 590, 18520 vs 21900: B2_SHARD_EXCHANGE=peer|nccl overrides)
+        xmode = os.environ.get("B2_SHARD_EXCHANGE", "peer" if world <= 4 else "nccl")
+        wsb = None if xmode == "nccl" else sh.peer_workspaces(LEVEL, LB, n_ws)
         exchange_kind = "peer copies (DMA) + one-word all-reduce" if wsb is not None else "NCCL all-gather"
         if wsb is None:
             wsb = [sh.batch_workspace(LEVEL, LB)[0] for _ in range(n_ws)]
