@@ -100,6 +100,34 @@ class LimbShardedKeySwitch:
             allgather_limbs(ct[k], l, self.rank, self.world, self.group)
 
 
+def exchange_block(l, alpha, batch, N, which, rank, world):
+    """(offset, size) in bytes of the block of a limb-major batch workspace T [l][batch][N] | CXP [alpha][2][batch][N] | ..
+    that `rank` owns in exchange `which` (0: its Q limbs of T, 1: its P limbs of CXP): what it pushes into every peer's
+    workspace, and what an all-gather over the same rows would send"""
+    limb = N * 8
+    first, cnt = limb_range(alpha if which else l, rank, world)
+    row = (2 * batch if which else batch) * limb
+    base = l * batch * limb if which else 0
+    return base + first * row, cnt * row
+
+
+def pipeline_schedule(n_batches):
+    """Issue order of the staggered pipeline as a list of ("phase", batch, p) and ("exchange", batch, which) items: step s queues
+    phase 0 of batch s and its first exchange, phase 1 of batch s - 1 and its second exchange, phase 2 of batch s - 3. Phases go
+    to the compute stream in this order, exchanges to the communication stream in this order; an exchange waits for the phase
+    listed just before it, a phase 1 (2) waits for exchange 0 (1) of its batch. With this order batch i + 4 may reuse the
+    workspace of batch i: everything of batch i is queued before phase 0 of batch i + 4."""
+    out = []
+    for s in range(n_batches + 3):
+        if s < n_batches:
+            out += [("phase", s, 0), ("exchange", s, 0)]
+        if 0 <= s - 1 < n_batches:
+            out += [("phase", s - 1, 1), ("exchange", s - 1, 1)]
+        if 0 <= s - 3 < n_batches:
+            out.append(("phase", s - 3, 2))
+    return out
+
+
 class PeerWorkspace:
     """A batch workspace of the limb-sharded pipeline that the other ranks of the node can write into: device memory with a
     CUDA IPC handle (b2_peer_alloc) and, after `connect`, every peer's mapping of its own. `push` copies a block of this
@@ -259,11 +287,7 @@ class BatchedLimbShardedKeySwitch(LimbShardedKeySwitch):
         a = self.ctx.size_P
         if not isinstance(ws, PeerWorkspace):
             return allgather_limbs(self._views(l, batch, ws)[which], a if which else l, self.rank, self.world, group)
-        limb = self.ctx.N * 8
-        first, cnt = limb_range(a if which else l, self.rank, self.world)
-        row = (2 * batch if which else batch) * limb
-        base = l * batch * limb if which else 0
-        ws.push(base + first * row, cnt * row)
+        ws.push(*exchange_block(l, a, batch, self.ctx.N, which, self.rank, self.world))
         if self.world > 1:
             if not hasattr(self, "_xflag"):
                 self._xflag = torch.zeros(1, dtype=torch.int32, device=torch.device("cuda", self.ctx.device))
@@ -315,25 +339,18 @@ class BatchedLimbShardedKeySwitch(LimbShardedKeySwitch):
             w = workspaces[i % D]
             self.phase_batch(l, ph, c2.shape[0], c2, tab, ct, w, w.numel() * 8)
 
-        for s in range(NB + 3):
-            if s < NB:                      # phase 0 of batch s, then its first exchange on the communication lane
-                phase(s, 0)
-                ev_p0[s].record(cs)
+        waits = {1: ev_x1, 2: ev_x2}       # phase p waits for the exchange that feeds it
+        after = {0: (ev_p0, ev_x1), 1: (ev_p1, ev_x2)}
+        for kind, i, p in pipeline_schedule(NB):
+            if kind == "phase":
+                if p in waits:
+                    cs.wait_event(waits[p][i])
+                phase(i, p)
+                if p in after:
+                    after[p][0][i].record(cs)
+            else:
                 with torch.cuda.stream(ms):
-                    ms.wait_event(ev_p0[s])
-                    exchange(s, 0)
-                    ev_x1[s].record(ms)
-            i = s - 1
-            if 0 <= i < NB:                 # phase 1 of batch s - 1, then its second exchange
-                cs.wait_event(ev_x1[i])
-                phase(i, 1)
-                ev_p1[i].record(cs)
-                with torch.cuda.stream(ms):
-                    ms.wait_event(ev_p1[i])
-                    exchange(i, 1)
-                    ev_x2[i].record(ms)
-            i = s - 3
-            if 0 <= i < NB:                 # phase 2 of batch s - 3
-                cs.wait_event(ev_x2[i])
-                phase(i, 2)
+                    ms.wait_event(after[p][0][i])
+                    exchange(i, p)
+                    after[p][1][i].record(ms)
         cs.wait_stream(ms)
